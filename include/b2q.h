@@ -1,0 +1,196 @@
+/*
+ * b2q — B200-native (sm_100a) quantized linear-layer kernels behind a C ABI.
+ *
+ * Every entry point is the drop-in replacement for one item of the reference
+ * (OxiCUDA, paths relative to its repository root) and cites it.  Conventions,
+ * all taken from the reference's BLAS layer:
+ *   - the caller owns every buffer; pointers are raw DEVICE pointers (the
+ *     reference passes CUdeviceptr as u64, crates/oxicuda-blas/src/types.rs:540-552);
+ *   - every call enqueues on the handle's stream and returns at once; the caller
+ *     synchronises before reading (crates/oxicuda-blas/src/level3/gemm/dispatch.rs:1115-1117);
+ *   - errors are int32 status codes, one per variant of BlasError
+ *     (crates/oxicuda-blas/src/error.rs:17-60) / QuantError
+ *     (crates/oxicuda-quant/src/error.rs:10-58); b2q_last_error() gives the text;
+ *   - a handle is owned by one host thread (BlasHandle is Send, not Sync:
+ *     crates/oxicuda-blas/src/handle.rs:39-42).
+ * There is no CPU fallback: without a CUDA device b2q_create fails.
+ */
+#ifndef B2Q_H
+#define B2Q_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct b2q_handle_s* b2q_handle;
+
+typedef enum {
+  B2Q_OK = 0,
+  B2Q_ERR_CUDA = 1,                  /* BlasError::Cuda */
+  B2Q_ERR_INVALID_DIMENSION = 2,     /* BlasError::InvalidDimension */
+  B2Q_ERR_BUFFER_TOO_SMALL = 3,      /* BlasError::BufferTooSmall */
+  B2Q_ERR_DIMENSION_MISMATCH = 4,    /* BlasError::DimensionMismatch / QuantError::DimensionMismatch */
+  B2Q_ERR_UNSUPPORTED = 5,           /* BlasError::UnsupportedOperation */
+  B2Q_ERR_LAUNCH_FAILED = 7,         /* BlasError::LaunchFailed */
+  B2Q_ERR_INVALID_ARGUMENT = 8,      /* BlasError::InvalidArgument */
+  B2Q_ERR_EMPTY_INPUT = 20,          /* QuantError::EmptyInput */
+  B2Q_ERR_GROUP_SIZE_MISMATCH = 21,  /* QuantError::GroupSizeMismatch */
+  B2Q_ERR_INVALID_SCALE = 22,        /* QuantError::InvalidScale */
+  B2Q_ERR_NON_FINITE_FP8 = 23,       /* QuantError::NonFiniteFp8 */
+  B2Q_ERR_INVALID_CONFIG = 24,       /* QuantError::InvalidConfig */
+  B2Q_ERR_TIMEOUT = 40               /* a bounded device-side wait gave up */
+} b2q_status;
+
+typedef enum { B2Q_FP8_E4M3 = 0, B2Q_FP8_E5M2 = 1 } b2q_fp8_format;  /* Fp8Format, crates/oxicuda-quant/src/scheme/fp8.rs:32-37 */
+/* B2Q_ROUND_REF reproduces Fp8Codec bit for bit (truncating mantissa, fp8.rs:163-208);
+ * B2Q_ROUND_RNE is round-to-nearest-even saturating (== cvt.rn.satfinite.e4m3x2.f32 and the
+ * encoder of crates/oxicuda-dnn/src/quantize/fp8_quantize.rs:325). */
+typedef enum { B2Q_ROUND_REF = 0, B2Q_ROUND_RNE = 1 } b2q_rounding;
+typedef enum { B2Q_FP4_E2M1 = 0, B2Q_FP4_INT4 = 1 } b2q_fp4_format;  /* Fp4Format, crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:107-114 */
+/* Block-scale storage.  F32 is what every reference code path stores
+ * (MicroScalingQuantizer::compute_scales, fp4_fp6_ops.rs:763-782); E8M0 has no
+ * counterpart in the reference: scale = 2^ceil(log2(absmax/6)), byte = exponent+127. */
+typedef enum { B2Q_SCALE_F32 = 0, B2Q_SCALE_E8M0 = 1 } b2q_scale_format;
+typedef enum { B2Q_SYMMETRIC = 0, B2Q_ASYMMETRIC = 1 } b2q_quant_scheme; /* QuantScheme, crates/oxicuda-quant/src/scheme/minmax.rs:26-32 */
+typedef enum { B2Q_OUT_BF16 = 0, B2Q_OUT_F32 = 1 } b2q_out_type;
+typedef enum { B2Q_SCALE_SCALAR = 0, B2Q_SCALE_PER_ROW = 1 } b2q_scale_kind;
+
+/* ---- handle: BlasHandle::{new,set_stream,sm_version} crates/oxicuda-blas/src/handle.rs:80-95, :243-255 ---- */
+int32_t b2q_create(b2q_handle* out, int device);
+int32_t b2q_destroy(b2q_handle h);
+/* stream is a cudaStream_t passed as void*; NULL = the legacy default stream */
+int32_t b2q_set_stream(b2q_handle h, void* stream);
+int32_t b2q_get_sm(b2q_handle h, int* sm);              /* 100 on a B200 */
+int32_t b2q_get_sm_count(b2q_handle h, int* count);
+const char* b2q_last_error(b2q_handle h);
+/* Reads (and clears) the device-side status word written by kernels that validate
+ * their input on the device (non-finite FP8 input, invalid scale, bounded waits).
+ * Synchronises the handle stream.  Returns B2Q_OK or the recorded status. */
+int32_t b2q_check(b2q_handle h);
+
+/* ---- MinMaxQuantizer: crates/oxicuda-quant/src/scheme/minmax.rs ---- */
+/* calibrate (:134-171), calibrate_2d (:179-207), calibrate_slice (:209-243): one (scale, zero point)
+ * per slice of `cols` contiguous elements; rows=1 is PerTensor, rows=len/group is PerGroup. */
+int32_t b2q_minmax_calibrate_f32(b2q_handle h, const float* x, int64_t rows, int64_t cols, int bits,
+                                 int scheme, float* scales, int32_t* zero_points);
+/* quantize (:252-268) / quantize_grouped (:275-299): codes are i32 as in the reference (Vec<i32>). */
+int32_t b2q_minmax_quantize_f32(b2q_handle h, const float* x, int64_t rows, int64_t cols, const float* scales,
+                                const int32_t* zero_points, int bits, int scheme, int32_t* codes);
+/* dequantize (:302-306) / dequantize_grouped (:309-324) */
+int32_t b2q_minmax_dequantize_f32(b2q_handle h, const int32_t* codes, int64_t rows, int64_t cols,
+                                  const float* scales, const int32_t* zero_points, float* out);
+/* fake_quant_inplace kernel (crates/oxicuda-quant/src/ptx_kernels.rs:55-121) with the rounding of its
+ * CPU definition FakeQuantize::forward (crates/oxicuda-quant/src/qat/fake_quant.rs:118-133). */
+int32_t b2q_fake_quant_inplace_f32(b2q_handle h, float* x, int64_t n, float scale, float zero_point,
+                                   float qmin, float qmax);
+
+/* ---- Fp8Codec: crates/oxicuda-quant/src/scheme/fp8.rs ---- */
+/* encode (:135-137): clamp to +-max then encode.  A NaN/Inf input records B2Q_ERR_NON_FINITE_FP8 in the
+ * device status word (encode_f32 :115-118); read it with b2q_check. */
+int32_t b2q_fp8_encode_f32(b2q_handle h, const float* x, int64_t n, int fmt, int rounding, uint8_t* codes);
+/* decode (:140-142).  rounding=B2Q_ROUND_REF decodes as the reference codec does (:210-261);
+ * B2Q_ROUND_RNE decodes IEEE-style (true subnormals), which is what the tensor core computes with. */
+int32_t b2q_fp8_decode_f32(b2q_handle h, const uint8_t* codes, int64_t n, int fmt, int rounding, float* out);
+/* Absmax-scaled quantization of `rows` slices: scale = absmax/max_val (1.0 for an all-zero slice),
+ * code = encode(x/scale).  The per-tensor rule of crates/oxicuda-dnn/src/quantize/fp8_quantize.rs:28-34
+ * composed with the codec; rows=1 is per-tensor, rows>1 per-row (per-token / per-output-channel). */
+int32_t b2q_fp8_quantize_rows_f32(b2q_handle h, const float* x, int64_t rows, int64_t cols, int fmt,
+                                  int rounding, float* scales, uint8_t* codes);
+/* Same, bf16 input (activations). */
+int32_t b2q_fp8_quantize_rows_bf16(b2q_handle h, const void* x_bf16, int64_t rows, int64_t cols, int fmt,
+                                   int rounding, float* scales, uint8_t* codes);
+
+/* ---- MicroScalingQuantizer / Fp4Quantizer / PackedFp4: crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs ---- */
+/* quantize_fp4 (:849-876): blocks of `block` in {32,64,128} over the flat array (validate :205-214),
+ * two codes per byte, element 2i in the low nibble (PackedFp4::pack :465-472).  n must be a multiple of
+ * `block` on the device path.  scales: ceil(n/block) floats (B2Q_SCALE_F32) or bytes (B2Q_SCALE_E8M0). */
+int32_t b2q_fp4_block_quantize_f32(b2q_handle h, const float* x, int64_t n, int block, int format,
+                                   int scale_format, uint8_t* packed, void* scales);
+/* dequantize_fp4 (:879-897) */
+int32_t b2q_fp4_block_dequantize_f32(b2q_handle h, const uint8_t* packed, int64_t n, int block, int format,
+                                     int scale_format, const void* scales, float* out);
+
+/* ---- Nf4Quantizer::decode / nf4_dequant kernel: crates/oxicuda-quant/src/scheme/nf4.rs:127-150,
+ *      crates/oxicuda-quant/src/ptx_kernels.rs:267-412 ---- */
+int32_t b2q_nf4_decode_f32(b2q_handle h, const uint8_t* packed, int64_t nbytes, int block,
+                           const float* absmaxs, float* out);
+/* Nf4Quantizer::encode (nf4.rs:93-125) */
+int32_t b2q_nf4_encode_f32(b2q_handle h, const float* x, int64_t n, int block, uint8_t* packed, float* absmaxs);
+
+/* ---- int8_quant / int8_dequant kernels: crates/oxicuda-quant/src/ptx_kernels.rs:129-252 ----
+ * out = i8(clamp(rni(x/scale), -127, 127)) (ties to even, as cvt.rni) ; out = f32(q)*scale */
+int32_t b2q_int8_quant_f32(b2q_handle h, const float* x, int64_t n, float scale, int8_t* out);
+int32_t b2q_int8_dequant_f32(b2q_handle h, const int8_t* q, int64_t n, float scale, float* out);
+
+/* ---- dist-infer "FP8" (INT8 in a u8): crates/oxicuda-dist-infer/src/quantisation/fp8_infer.rs:61-142 ----
+ * per-block absmax is stored; block >= n gives the per-tensor variant. */
+int32_t b2q_distfp8_quantize_block_f32(b2q_handle h, const float* x, int64_t n, int64_t block, uint8_t* q,
+                                       float* absmaxs);
+int32_t b2q_distfp8_dequantize_block_f32(b2q_handle h, const uint8_t* q, int64_t n, int64_t block,
+                                         const float* absmaxs, float* out);
+
+/* ---- LlmInt8Quantizer::matmul: crates/oxicuda-quant/src/scheme/llm_int8.rs:175-288 ----
+ * x [samples x cols] f32, w [rows x cols] f32 -> out [samples x rows] f32.  Per-row INT8 of W and per-token
+ * (row_wise != 0) or per-tensor INT8 of X over the non-outlier columns, exact integer accumulation,
+ * out = f32(acc)*(sx*sw[k]) + f32 dot over outlier columns (a column whose max |x| >= threshold).
+ * Optional dumps for parity checks (each may be NULL): wq [rows x cols] i8, sw [rows], xq [samples x cols] i8,
+ * sx [samples], acc [samples x rows] i32, n_outliers (1 x i32, device). */
+int32_t b2q_llm_int8_linear_f32(b2q_handle h, const float* x, const float* w, int64_t samples, int64_t rows,
+                                int64_t cols, float threshold, int row_wise, float* out, int8_t* wq, float* sw,
+                                int8_t* xq, float* sx, int32_t* acc, int32_t* n_outliers);
+
+/* ---- INT8 GEMM: Int8GemmConfig / generate_int8_gemm_ptx crates/oxicuda-blas/src/precision/int_ops.rs:78-189, :446-583 ----
+ * C[m,n] = sum_k A[m,k]*B[n,k], exact s32.  A [M x K] row-major, B [N x K] row-major ("out x in" weights; the
+ * reference's K-packed-by-4 [K/4 x N] u32 operand holds the same values).  K % 4 == 0 (validate :113-118).
+ * c_s32 and/or c_f32 (AccType::F32: cvt.rn.f32.s32 times scale_a[m]*scale_b[n] when scales are given). */
+int32_t b2q_gemm_i8(b2q_handle h, const int8_t* a, const int8_t* b, int64_t M, int64_t N, int64_t K,
+                    int32_t* c_s32, float* c_f32, const float* scale_a, const float* scale_b);
+
+/* ---- FP8 GEMM: gemm::<E4M3> crates/oxicuda-blas/src/level3/gemm_api.rs:82-231 (the reference's generator
+ *      rejects FP8, crates/oxicuda-ptx/src/templates/gemm.rs:800-809; this is the working path) ----
+ * out[m,n] = (sum_k A[m,k]*W[n,k]) * sa * sw, f32 accumulate in TMEM, bf16 (RNE) or f32 store.
+ * A [M x K] codes row-major, W [N x K] codes row-major (K-major both: tcgen05 "TN").
+ * scale_a: 1 float (B2Q_SCALE_SCALAR) or M floats (B2Q_SCALE_PER_ROW); scale_w: 1 or N floats.
+ * Validation order follows gemm_impl: zero dims -> INVALID_DIMENSION (:142-146); K % 16 != 0 -> INVALID_DIMENSION
+ * (TMA row pitch); C overlapping A/W -> INVALID_ARGUMENT (:189-195). */
+int32_t b2q_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,
+                     const float* scale_a, int scale_a_kind, const float* scale_w, int scale_w_kind,
+                     void* out, int out_type);
+/* Checker path on the GPU: software decode (reference or IEEE), k-ascending fp32 FMA, one thread per output
+ * — the arithmetic of the reference's naive kernel (crates/oxicuda-ptx/src/templates/gemm.rs:373-447). */
+int32_t b2q_gemm_fp8_simt(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,
+                          int decode_mode, const float* scale_a, int scale_a_kind, const float* scale_w,
+                          int scale_w_kind, void* out, int out_type);
+
+/* ---- FP4 weight-only decode GEMV: Fp4GemmConfig / generate_fp4_gemm_ptx
+ *      crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:337-395, :1237-1362; semantics = dequantize_fp4 (:879-897)
+ *      followed by a dot product.  The reference's M (quantized rows) is `N` here, its N (columns of dense B) is
+ *      `tokens`; activations are taken token-major [tokens x K] bf16 instead of [K x tokens] f32.
+ * codes [N x K/2] (E2M1, low nibble first), scales [N x K/32] f32 or E8M0 bytes, x [tokens x K] bf16,
+ * out [tokens x N] bf16 or f32.  tokens <= 32, K % 128 == 0, block == 32. */
+int32_t b2q_gemv_fp4_wo(b2q_handle h, const uint8_t* codes, const void* scales, int scale_format, int block,
+                        const void* x_bf16, int64_t tokens, int64_t N, int64_t K, void* out, int out_type);
+
+/* ---- tile heuristics: classify_workload / Fp8TileHeuristic::select crates/oxicuda-blas/src/precision/fp8_ops.rs:67-107,
+ *      :239-304; select_fp4_tile fp4_fp6_ops.rs:996-1075; Int8GemmConfig::tile_config int_ops.rs:141-176 ---- */
+typedef struct {
+  uint32_t tile_m, tile_n, tile_k, warp_m, warp_n, stages, use_tensor_core, split_k;
+} b2q_tile_config;  /* TileConfig, crates/oxicuda-blas/src/level3/gemm/dispatch.rs:57-107 */
+/* 0 SmallSquare, 1 LargeSquare, 2 SkinnyM, 3 SkinnyN, 4 SkinnyK, 5 General */
+int32_t b2q_classify_workload(uint32_t m, uint32_t n, uint32_t k);
+/* The reference's Blackwell heuristic (what Fp8Config::tile_config(Sm100, ..) returns); dtype 0 fp8, 1 fp4, 2 int8. */
+int32_t b2q_ref_tile_config(int dtype, uint32_t m, uint32_t n, uint32_t k, b2q_tile_config* out);
+/* Fp8Config::compute_split_k (fp8_ops.rs:389-396) */
+uint32_t b2q_fp8_compute_split_k(uint32_t m, uint32_t n, uint32_t k);
+/* The static per-shape table this library actually dispatches with (replaces the autotuner role,
+ * crates/oxicuda-autotune/src/dispatch.rs:36-196): the CTA tile, pipeline depth and kernel family chosen for
+ * (dtype, m, n, k).  kernel_id: 0 simt, 1 tcgen05 128x256, 2 tcgen05 128x128, 3 warp gemv. */
+int32_t b2q_select_tile(int dtype, uint32_t m, uint32_t n, uint32_t k, b2q_tile_config* out, int* kernel_id);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B2Q_H */

@@ -1,0 +1,304 @@
+"""numpy front end of the CPU oracle (oracle/oracle.cpp -> oracle/liboracle.so).
+
+TEST INFRASTRUCTURE ONLY: imported by tests/, by __graft_entry__.smoke() and by the
+cpu_baseline / reference legs of bench.py — never by the oxicuda_b200 package.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+
+_DIR = Path(__file__).resolve().parent
+_LIB = _DIR / "liboracle.so"
+_lib = None
+
+
+def build(force: bool = False) -> Path:
+    src = _DIR / "oracle.cpp"
+    if force or not _LIB.exists() or _LIB.stat().st_mtime < src.stat().st_mtime:
+        r = subprocess.run(["make", "-C", str(_DIR), "-B" if force else "-s", "liboracle.so"], capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError("building the oracle failed:\n" + r.stdout + r.stderr)
+    return _LIB
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        build()
+        L = C.CDLL(str(_LIB))
+        L.orc_fp8_encode.restype = C.c_int64
+        L.orc_fp8_quantize_rows.restype = C.c_int64
+        L.orc_llm_int8_matmul.restype = C.c_int64
+        L.orc_fp4_quantize_one.restype = C.c_uint8
+        L.orc_fp4_quantize_one.argtypes = [C.c_float, C.c_int]
+        L.orc_fp4_dequantize_one.restype = C.c_float
+        L.orc_fp4_dequantize_one.argtypes = [C.c_uint8, C.c_int]
+        L.orc_e8m0_from_absmax.restype = C.c_uint8
+        L.orc_e8m0_from_absmax.argtypes = [C.c_float]
+        L.orc_fp8_split_k.restype = C.c_uint32
+        _lib = L
+    return _lib
+
+
+def _p(a):
+    return C.c_void_p(0) if a is None else C.c_void_p(a.ctypes.data)
+
+
+def _f32(a):
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _i64(v):
+    return C.c_int64(int(v))
+
+
+def num_threads() -> int:
+    return lib().orc_num_threads()
+
+
+def set_threads(n: int):
+    lib().orc_set_threads(int(n))
+
+
+# ---- MinMax ----
+def minmax_calibrate(x, rows, cols, bits=8, scheme=0):
+    x = _f32(x).reshape(-1)
+    scales = np.zeros(rows, np.float32)
+    zps = np.zeros(rows, np.int32)
+    st = lib().orc_minmax_calibrate(_p(x), _i64(rows), _i64(cols), bits, scheme, _p(scales), _p(zps))
+    return scales, zps, st
+
+
+def minmax_quantize(x, rows, cols, scales, zps, bits=8, scheme=0):
+    x = _f32(x).reshape(-1)
+    codes = np.zeros(rows * cols, np.int32)
+    lib().orc_minmax_quantize(_p(x), _i64(rows), _i64(cols), _p(_f32(scales)), _p(np.ascontiguousarray(zps, np.int32)),
+                              bits, scheme, _p(codes))
+    return codes
+
+
+def minmax_dequantize(codes, rows, cols, scales, zps):
+    codes = np.ascontiguousarray(codes, np.int32).reshape(-1)
+    out = np.zeros(rows * cols, np.float32)
+    lib().orc_minmax_dequantize(_p(codes), _i64(rows), _i64(cols), _p(_f32(scales)),
+                                _p(np.ascontiguousarray(zps, np.int32)), _p(out))
+    return out
+
+
+def fake_quant(x, scale, zp, qmin, qmax):
+    x = _f32(x).reshape(-1)
+    out = np.zeros_like(x)
+    lib().orc_fake_quant(_p(x), _i64(x.size), C.c_float(scale), C.c_float(zp), C.c_float(qmin), C.c_float(qmax), _p(out))
+    return out
+
+
+# ---- FP8 ----
+def fp8_encode(x, fmt=0, mode=0):
+    """mode 0 = reference codec, 1 = RNE.  Returns (codes, index_of_first_nonfinite or -1)."""
+    x = _f32(x).reshape(-1)
+    out = np.zeros(x.size, np.uint8)
+    bad = lib().orc_fp8_encode(_p(x), _i64(x.size), fmt, mode, _p(out))
+    return out, int(bad)
+
+
+def fp8_decode(codes, fmt=0, mode=0):
+    codes = np.ascontiguousarray(codes, np.uint8).reshape(-1)
+    out = np.zeros(codes.size, np.float32)
+    lib().orc_fp8_decode(_p(codes), _i64(codes.size), fmt, mode, _p(out))
+    return out
+
+
+def fp8_quantize_rows(x, rows, cols, fmt=0, mode=0):
+    x = _f32(x).reshape(-1)
+    scales = np.zeros(rows, np.float32)
+    codes = np.zeros(rows * cols, np.uint8)
+    bad = lib().orc_fp8_quantize_rows(_p(x), _i64(rows), _i64(cols), fmt, mode, _p(scales), _p(codes))
+    return codes, scales, int(bad)
+
+
+# ---- FP4 ----
+def fp4_quantize_one(v, fmt=0):
+    return int(lib().orc_fp4_quantize_one(float(v), fmt))
+
+
+def fp4_dequantize_one(raw, fmt=0):
+    return float(lib().orc_fp4_dequantize_one(int(raw), fmt))
+
+
+def e8m0_from_absmax(a):
+    return int(lib().orc_e8m0_from_absmax(float(a)))
+
+
+def fp4_quantize(x, fmt=0):
+    x = _f32(x).reshape(-1)
+    out = np.zeros(x.size // 2, np.uint8)
+    lib().orc_fp4_quantize(_p(x), _i64(x.size), fmt, _p(out))
+    return out
+
+
+def fp4_dequantize(packed, fmt=0):
+    packed = np.ascontiguousarray(packed, np.uint8).reshape(-1)
+    out = np.zeros(packed.size * 2, np.float32)
+    lib().orc_fp4_dequantize(_p(packed), _i64(packed.size), fmt, _p(out))
+    return out
+
+
+def fp4_block_quantize(x, block=32, fmt=0, scale_mode=0):
+    """scale_mode 0: f32 scales (reference), 1: E8M0 bytes.  Returns (packed, scales)."""
+    x = _f32(x).reshape(-1)
+    nb = -(-x.size // block)
+    packed = np.zeros((x.size + 1) // 2, np.uint8)
+    sf = np.zeros(nb, np.float32)
+    se = np.zeros(nb, np.uint8)
+    lib().orc_fp4_block_quantize(_p(x), _i64(x.size), block, fmt, scale_mode, _p(packed), _p(sf), _p(se))
+    return packed, (sf if scale_mode == 0 else se)
+
+
+def fp4_block_dequantize(packed, scales, n, block=32, fmt=0):
+    packed = np.ascontiguousarray(packed, np.uint8).reshape(-1)
+    scale_mode = 1 if scales.dtype == np.uint8 else 0
+    out = np.zeros(n, np.float32)
+    s = np.ascontiguousarray(scales)
+    lib().orc_fp4_block_dequantize(_p(packed), _i64(n), block, fmt, scale_mode,
+                                   _p(s) if scale_mode == 0 else _p(None), _p(s) if scale_mode == 1 else _p(None), _p(out))
+    return out
+
+
+# ---- NF4 ----
+def nf4_encode(x, block=64):
+    x = _f32(x).reshape(-1)
+    packed = np.zeros(x.size // 2, np.uint8)
+    absmaxs = np.zeros(x.size // block, np.float32)
+    lib().orc_nf4_encode(_p(x), _i64(x.size), block, _p(packed), _p(absmaxs))
+    return packed, absmaxs
+
+
+def nf4_decode(packed, absmaxs, block=64):
+    packed = np.ascontiguousarray(packed, np.uint8).reshape(-1)
+    out = np.zeros(packed.size * 2, np.float32)
+    lib().orc_nf4_decode(_p(packed), _i64(packed.size), block, _p(_f32(absmaxs)), _p(out))
+    return out
+
+
+# ---- dist-infer INT8-in-u8 ----
+def distfp8_quantize_block(x, block):
+    x = _f32(x).reshape(-1)
+    block = max(1, int(block))
+    q = np.zeros(x.size, np.uint8)
+    absmaxs = np.zeros(-(-x.size // block), np.float32)
+    lib().orc_distfp8_quantize_block(_p(x), _i64(x.size), _i64(block), _p(q), _p(absmaxs))
+    return q, absmaxs
+
+
+def distfp8_dequantize_block(q, absmaxs, block):
+    q = np.ascontiguousarray(q, np.uint8).reshape(-1)
+    out = np.zeros(q.size, np.float32)
+    lib().orc_distfp8_dequantize_block(_p(q), _i64(q.size), _i64(max(1, int(block))), _p(_f32(absmaxs)), _p(out))
+    return out
+
+
+# ---- LLM.int8 ----
+def llm_int8_matmul(x, w, samples, rows, cols, threshold=6.0, row_wise=True):
+    x = _f32(x).reshape(-1)
+    w = _f32(w).reshape(-1)
+    out = np.zeros(samples * rows, np.float32)
+    wq = np.zeros(rows * cols, np.int8)
+    sw = np.zeros(rows, np.float32)
+    xq = np.zeros(samples * cols, np.int8)
+    sx = np.zeros(samples, np.float32)
+    acc = np.zeros(samples * rows, np.int32)
+    mask = np.zeros(cols, np.uint8)
+    n_out = lib().orc_llm_int8_matmul(_p(x), _p(w), _i64(samples), _i64(rows), _i64(cols), C.c_float(threshold),
+                                      int(bool(row_wise)), _p(out), _p(wq), _p(sw), _p(xq), _p(sx), _p(acc), _p(mask))
+    return dict(output=out, w_q=wq, s_w=sw, x_q=xq, s_x=sx, acc=acc, outlier_mask=mask, n_outliers=int(n_out))
+
+
+def gemm_i8(a, b):
+    a = np.ascontiguousarray(a, np.int8)
+    b = np.ascontiguousarray(b, np.int8)
+    M, K = a.shape
+    N = b.shape[0]
+    c = np.zeros((M, N), np.int32)
+    lib().orc_gemm_i8(_p(a), _p(b), _i64(M), _i64(N), _i64(K), _p(c))
+    return c
+
+
+# ---- FP8 GEMM / FP4 GEMV compositions ----
+def bf16_bits_to_f32(b):
+    return (np.ascontiguousarray(b, np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def f32_to_bf16_bits(x):
+    u = _f32(x).view(np.uint32).astype(np.uint64)
+    lsb = (u >> 16) & 1
+    return ((u + 0x7FFF + lsb) >> 16).astype(np.uint16)
+
+
+def gemm_fp8(a_codes, w_codes, sa, sw, fmt=0, decode_mode=0, want="bf16"):
+    """a [M,K] u8, w [N,K] u8, sa 1 or M floats, sw 1 or N floats.  Returns f32 values
+    (bf16-rounded when want == 'bf16')."""
+    a = np.ascontiguousarray(a_codes, np.uint8)
+    w = np.ascontiguousarray(w_codes, np.uint8)
+    M, K = a.shape
+    N = w.shape[0]
+    sa = _f32(sa).reshape(-1)
+    sw = _f32(sw).reshape(-1)
+    ob = np.zeros((M, N), np.uint16) if want == "bf16" else None
+    of = np.zeros((M, N), np.float32) if want != "bf16" else None
+    lib().orc_gemm_fp8(_p(a), _p(w), _i64(M), _i64(N), _i64(K), fmt, decode_mode, _p(sa), int(sa.size > 1), _p(sw),
+                       int(sw.size > 1), _p(ob), _p(of))
+    return bf16_bits_to_f32(ob).reshape(M, N) if want == "bf16" else of
+
+
+def gemv_fp4(codes, scales, x_bf16_bits, M, N, K, block=32, want="bf16"):
+    codes = np.ascontiguousarray(codes, np.uint8).reshape(-1)
+    scale_mode = 1 if scales.dtype == np.uint8 else 0
+    s = np.ascontiguousarray(scales).reshape(-1)
+    xb = np.ascontiguousarray(x_bf16_bits, np.uint16).reshape(-1)
+    ob = np.zeros((M, N), np.uint16) if want == "bf16" else None
+    of = np.zeros((M, N), np.float32) if want != "bf16" else None
+    lib().orc_gemv_fp4(_p(codes), scale_mode, _p(s) if scale_mode == 0 else _p(None), _p(s) if scale_mode == 1 else _p(None),
+                       block, _p(xb), _i64(M), _i64(N), _i64(K), _p(ob), _p(of))
+    return bf16_bits_to_f32(ob).reshape(M, N) if want == "bf16" else of
+
+
+# ---- tensor parallel ----
+def column_linear(x, w, bias, batch, in_f, out_f, tp):
+    out = np.zeros(batch * out_f, np.float32)
+    lib().orc_column_linear(_p(_f32(x).reshape(-1)), _p(_f32(w).reshape(-1)), _p(None if bias is None else _f32(bias)),
+                            _i64(batch), _i64(in_f), _i64(out_f), tp, _p(out))
+    return out.reshape(batch, out_f)
+
+
+def row_linear(x, w, bias, batch, in_f, out_f, tp):
+    out = np.zeros(batch * out_f, np.float32)
+    lib().orc_row_linear(_p(_f32(x).reshape(-1)), _p(_f32(w).reshape(-1)), _p(None if bias is None else _f32(bias)),
+                         _i64(batch), _i64(in_f), _i64(out_f), tp, _p(out))
+    return out.reshape(batch, out_f)
+
+
+def swiglu(gate, up):
+    g = _f32(gate).reshape(-1)
+    u = _f32(up).reshape(-1)
+    h = np.zeros_like(g)
+    lib().orc_swiglu(_p(g), _p(u), _i64(g.size), _p(h))
+    return h.reshape(np.shape(gate))
+
+
+# ---- heuristics ----
+def classify_workload(m, n, k):
+    return int(lib().orc_classify_workload(C.c_uint32(m), C.c_uint32(n), C.c_uint32(k)))
+
+
+def tile_config(dtype, m, n, k):
+    out = np.zeros(8, np.uint32)
+    lib().orc_tile_config(dtype, C.c_uint32(m), C.c_uint32(n), C.c_uint32(k), _p(out))
+    return tuple(int(v) for v in out)
+
+
+def fp8_split_k(m, n, k):
+    return int(lib().orc_fp8_split_k(C.c_uint32(m), C.c_uint32(n), C.c_uint32(k)))

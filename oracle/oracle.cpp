@@ -1,0 +1,724 @@
+// CPU oracle for the quantized-linear hot path.
+//
+// TEST INFRASTRUCTURE ONLY.  This file restates, function by function, the CPU
+// arithmetic of the reference (OxiCUDA, a pure-Rust workspace) for the
+// quantize/dequantize entry points and the INT8 / FP8 / block-scaled-FP4
+// GEMM / GEMV compositions.  It is what the CUDA path is checked against and
+// what the CPU baseline leg of the benchmark times; nothing in the shipped
+// library may call it.
+//
+// The reference cannot be compiled in an environment without a Rust toolchain,
+// so every function here cites the reference file:line it follows and is pinned
+// against the known-answer vectors of the reference's own unit tests
+// (tests/golden/reference_kat.json).  Items that exist in no reference test or
+// source (E8M0 scales) are marked "parity unpinned".
+//
+// Build: g++ -O2 -ffp-contract=off -fno-fast-math -fopenmp -shared -fPIC
+// (-ffp-contract=off matters: Rust never fuses a*b+c unless mul_add is written.)
+
+#include <cmath>
+#include <cstdint>
+#include <cstring>
+#include <cstdlib>
+#include <vector>
+#include <algorithm>
+#include <limits>
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+namespace {
+
+inline uint32_t f2u(float f) { uint32_t u; std::memcpy(&u, &f, 4); return u; }
+inline float u2f(uint32_t u) { float f; std::memcpy(&f, &u, 4); return f; }
+
+// Rust `f32::max`: returns the non-NaN operand when one is NaN (IEEE maxNum).
+inline float rmax(float a, float b) { return std::fmax(a, b); }
+inline float rmin(float a, float b) { return std::fmin(a, b); }
+
+// Rust `f32::clamp(lo, hi)`: NaN stays NaN; otherwise plain comparisons.
+inline float rclamp(float v, float lo, float hi) {
+  if (v < lo) return lo;
+  if (v > hi) return hi;
+  return v;
+}
+
+// Rust `as i32` from f32: saturating, NaN -> 0.
+inline int32_t f32_as_i32(float v) {
+  if (std::isnan(v)) return 0;
+  if (v >= 2147483648.0f) return INT32_MAX;
+  if (v <= -2147483648.0f) return INT32_MIN;
+  return (int32_t)v;
+}
+inline int8_t f32_as_i8(float v) {
+  if (std::isnan(v)) return 0;
+  if (v >= 127.0f) return 127;
+  if (v <= -128.0f) return -128;
+  return (int8_t)v;
+}
+
+// bf16 <-> f32 (round to nearest even; the bf16 outputs of the GEMM/GEMV
+// compositions use RNE, as the hardware cvt.rn.bf16.f32 does).
+inline uint16_t f32_to_bf16_rne(float f) {
+  uint32_t u = f2u(f);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return (uint16_t)((u >> 16) | 0x40);
+  uint32_t lsb = (u >> 16) & 1u;
+  u += 0x7fffu + lsb;
+  return (uint16_t)(u >> 16);
+}
+inline float bf16_to_f32(uint16_t h) { return u2f((uint32_t)h << 16); }
+
+// ---------------------------------------------------------------------------
+// FP8 codecs
+// ---------------------------------------------------------------------------
+struct Fp8Fmt { int exp_bits, man_bits, bias; float max_val; uint8_t sat; };
+const Fp8Fmt kE4M3 = {4, 3, 7, 448.0f, 0x7E};
+const Fp8Fmt kE5M2 = {5, 2, 15, 57344.0f, 0x7B};
+inline const Fp8Fmt& fmt_of(int f) { return f == 0 ? kE4M3 : kE5M2; }
+
+// Fp8Codec::fp32_to_fp8 — crates/oxicuda-quant/src/scheme/fp8.rs:163-208.
+// Mantissa is TRUNCATED; any biased exponent >= 2^eb-1 saturates (so E4M3
+// magnitudes >= 256 all become 0x7E); the subnormal branch shifts one bit too
+// far.  Reproduced as written.
+uint8_t fp8_encode_ref(float v, const Fp8Fmt& F) {
+  uint32_t bits = f2u(v);
+  uint8_t sign = (uint8_t)(bits >> 31);
+  int exp32 = (int)((bits >> 23) & 0xFF);
+  uint32_t man32 = bits & 0x007FFFFFu;
+  if (v == 0.0f) return (uint8_t)(sign << 7);
+  int exp8_raw = exp32 - 127 + F.bias;
+  uint32_t man_shift = 23 - F.man_bits;
+  if (exp8_raw <= 0) {
+    uint32_t full_man = (man32 | 0x00800000u) >> 1;
+    uint32_t shift = (uint32_t)(1 - exp8_raw) + man_shift;
+    if (shift >= 24) return (uint8_t)(sign << 7);
+    uint8_t man8 = (uint8_t)((full_man >> shift) & ((1u << F.man_bits) - 1));
+    return (uint8_t)((sign << 7) | man8);
+  }
+  int max_exp = (1 << F.exp_bits) - 1;
+  if (exp8_raw >= max_exp) return (uint8_t)((sign << 7) | F.sat);
+  uint8_t man8 = (uint8_t)((man32 >> man_shift) & ((1u << F.man_bits) - 1));
+  return (uint8_t)((sign << 7) | ((uint8_t)exp8_raw << F.man_bits) | man8);
+}
+
+// Fp8Codec::fp8_to_fp32 — fp8.rs:210-261.  `leading` is always 0 in the
+// reference (leading_zeros of a u32 clipped to man_bits-1), so subnormal codes
+// decode as 2^(1-bias) * (1 + m/2^mb).
+float fp8_decode_ref(uint8_t b, const Fp8Fmt& F) {
+  uint32_t sign = b >> 7;
+  uint32_t exp8 = (b >> F.man_bits) & ((1u << F.exp_bits) - 1);
+  uint32_t man8 = b & ((1u << F.man_bits) - 1);
+  uint32_t all_exp = (1u << F.exp_bits) - 1;
+  if (F.exp_bits == 4) {
+    if (exp8 == all_exp && man8 == (1u << F.man_bits) - 1) return std::numeric_limits<float>::quiet_NaN();
+  } else if (exp8 == all_exp) {
+    if (man8 == 0) return sign ? -INFINITY : INFINITY;
+    return std::numeric_limits<float>::quiet_NaN();
+  }
+  uint32_t man_shift = 23 - F.man_bits;
+  if (exp8 == 0) {
+    if (man8 == 0) return u2f(sign << 31);
+    uint32_t exp32 = (uint32_t)(127 + 1 - F.bias);
+    uint32_t lz = (uint32_t)__builtin_clz(man8);           // u32::leading_zeros
+    uint32_t leading = (uint32_t)F.man_bits - 1 - std::min<uint32_t>(lz, F.man_bits - 1);
+    uint32_t exp32_adj = exp32 - leading;
+    uint32_t m32 = ((man8 << leading) & ((1u << F.man_bits) - 1)) << man_shift;
+    return u2f((sign << 31) | (exp32_adj << 23) | m32);
+  }
+  uint32_t exp32 = (uint32_t)((int)exp8 - F.bias + 127);
+  return u2f((sign << 31) | (exp32 << 23) | (man8 << man_shift));
+}
+
+// Round-to-nearest-even, saturate-to-finite encoder.  For E4M3 this equals the
+// RNE model in crates/oxicuda-dnn/src/quantize/fp8_quantize.rs:925-974 and the
+// hardware cvt.rn.satfinite.e4m3x2.f32 on finite inputs.
+uint8_t fp8_encode_rne(float v, const Fp8Fmt& F) {
+  uint32_t bits = f2u(v);
+  uint8_t sign = (uint8_t)((bits >> 31) << 7);
+  float a = std::fabs(v);
+  if (std::isnan(v)) return (uint8_t)(sign | 0x7F);
+  if (a >= F.max_val) return (uint8_t)(sign | F.sat);
+  int min_exp = 1 - F.bias;                         // exponent of the smallest normal
+  float step_sub = std::ldexp(1.0f, min_exp - F.man_bits);
+  if (a < std::ldexp(1.0f, min_exp)) {
+    // subnormal: round a/step to nearest even integer
+    float q = a / step_sub;                         // exact (power of two)
+    float r = std::nearbyint(q);                    // default mode = RNE
+    uint32_t m = (uint32_t)r;                       // 0..2^mb (2^mb == smallest normal code)
+    return (uint8_t)(sign | m);
+  }
+  int e; float fr = std::frexp(a, &e);              // a = fr*2^e, fr in [0.5,1)
+  (void)fr;
+  int eu = e - 1;                                   // unbiased exponent
+  float ulp = std::ldexp(1.0f, eu - F.man_bits);
+  float q = a / ulp;                                // in [2^mb, 2^(mb+1)), exact
+  uint32_t m = (uint32_t)std::nearbyint(q);
+  if (m == (2u << F.man_bits)) { m >>= 1; eu += 1; }
+  uint32_t code = ((uint32_t)(eu + F.bias) << F.man_bits) | (m & ((1u << F.man_bits) - 1));
+  if (code > F.sat) code = F.sat;
+  return (uint8_t)(sign | code);
+}
+
+// IEEE-style decode (true subnormals m * 2^(1-bias-mb)); what the tensor core sees.
+float fp8_decode_ieee(uint8_t b, const Fp8Fmt& F) {
+  uint32_t sign = b >> 7;
+  uint32_t exp8 = (b >> F.man_bits) & ((1u << F.exp_bits) - 1);
+  uint32_t man8 = b & ((1u << F.man_bits) - 1);
+  uint32_t all_exp = (1u << F.exp_bits) - 1;
+  float s = sign ? -1.0f : 1.0f;
+  if (F.exp_bits == 4) {
+    if (exp8 == all_exp && man8 == 7) return std::numeric_limits<float>::quiet_NaN();
+  } else if (exp8 == all_exp) {
+    if (man8 == 0) return sign ? -INFINITY : INFINITY;
+    return std::numeric_limits<float>::quiet_NaN();
+  }
+  if (exp8 == 0) return s * std::ldexp((float)man8, 1 - F.bias - F.man_bits);
+  return s * std::ldexp(1.0f + (float)man8 / (float)(1u << F.man_bits), (int)exp8 - F.bias);
+}
+
+// ---------------------------------------------------------------------------
+// E2M1 (FP4)
+// ---------------------------------------------------------------------------
+// Fp4Quantizer::quantize_one (E2M1) — crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:638-663.
+// The reference computes floor(log2(a)); only the thresholds 0.5, 1, 2, 4 change
+// the biased exponent, and on them the IEEE exponent of `a` gives the same
+// answer as a correctly rounded log2, so the exponent is extracted from the bits.
+uint8_t e2m1_encode_ref(float value) {
+  if (value == 0.0f) return 0;                      // -0.0 also returns 0 (sign lost)
+  uint8_t sign = value < 0.0f ? 1 : 0;
+  float a = rmin(std::fabs(value), 6.0f);           // NaN.min(6) == 6
+  int eu;
+  {
+    uint32_t u = f2u(a);
+    int e = (int)((u >> 23) & 0xFF);
+    eu = e == 0 ? -127 : e - 127;                   // subnormal f32: far below 0.5 anyway
+  }
+  int eb = std::min(3, std::max(0, eu + 1));
+  int ea = eb - 1;
+  float sig = a / std::ldexp(1.0f, ea);
+  uint8_t m = ((sig - 1.0f) >= 0.5f) ? 1 : 0;
+  return (uint8_t)((sign << 3) | ((uint8_t)eb << 1) | m);
+}
+// Fp4Quantizer::quantize_one (Int4) — fp4_fp6_ops.rs:641-644.
+uint8_t int4_encode_ref(float value) {
+  float c = rclamp(std::round(value), -8.0f, 7.0f);
+  int8_t q = f32_as_i8(c);
+  return (uint8_t)q & 0x0F;
+}
+// Fp4Quantizer::dequantize_one — fp4_fp6_ops.rs:667-699.
+float e2m1_decode_ref(uint8_t raw) {
+  uint8_t sign = (raw >> 3) & 1, exponent = (raw >> 1) & 3, mant = raw & 1;
+  if (exponent == 0 && mant == 0) return sign ? -0.0f : 0.0f;
+  float v = exponent == 0 ? (float)mant * 0.5f
+                          : (1.0f + (float)mant * 0.5f) * std::ldexp(1.0f, (int)exponent - 1);
+  return sign ? -v : v;
+}
+float int4_decode_ref(uint8_t raw) {
+  uint8_t nib = raw & 0x0F;
+  return (nib & 8) ? (float)(int8_t)(0xF0u | nib) : (float)nib;
+}
+
+// E8M0 scale rule (NOT in the reference — parity unpinned): the smallest power
+// of two that is >= absmax/6, exponent clamped to [-127,127], stored biased by
+// 127; an all-zero block stores exponent 0 (scale 1.0).
+uint8_t e8m0_from_absmax(float absmax) {
+  if (!(absmax > 0.0f)) return 127;
+  float s = absmax / 6.0f;
+  int e; float fr = std::frexp(s, &e);              // s = fr * 2^e, fr in [0.5,1)
+  int p = (fr == 0.5f) ? e - 1 : e;                 // ceil(log2 s)
+  p = std::min(127, std::max(-127, p));
+  return (uint8_t)(p + 127);
+}
+inline float e8m0_to_f32(uint8_t b) { return std::ldexp(1.0f, (int)b - 127); }
+
+// NF4 — crates/oxicuda-quant/src/scheme/nf4.rs:33-50 (table), :181-203 (search).
+const float NF4_LUT[16] = {
+  -1.0f, -0.69619286f, -0.52507305f, -0.3949175f, -0.28444138f, -0.18477343f, -0.09105003f, 0.0f,
+  0.0795803f, 0.1609302f, 0.2461123f, 0.33791524f, 0.44070983f, 0.562617f, 0.72295684f, 1.0f};
+int nearest_nf4(float v) {
+  int lo = 0, hi = 16;
+  while (lo < hi) { int mid = lo + (hi - lo) / 2; if (NF4_LUT[mid] < v) lo = mid + 1; else hi = mid; }
+  if (lo == 0) return 0;
+  if (lo == 16) return 15;
+  float d_lo = std::fabs(v - NF4_LUT[lo - 1]);
+  float d_hi = std::fabs(NF4_LUT[lo] - v);
+  return d_lo <= d_hi ? lo - 1 : lo;
+}
+
+}  // namespace
+
+extern "C" {
+
+int orc_num_threads() {
+#ifdef _OPENMP
+  return omp_get_max_threads();
+#else
+  return 1;
+#endif
+}
+void orc_set_threads(int n) {
+#ifdef _OPENMP
+  omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
+// ---------------------------------------------------------------------------
+// MinMaxQuantizer — crates/oxicuda-quant/src/scheme/minmax.rs
+// ---------------------------------------------------------------------------
+// calibrate_slice (:209-243) applied to each of `rows` contiguous slices of
+// `cols` elements (rows=1: per-tensor `calibrate`; rows=n/group: PerGroup
+// `calibrate` :146-165; rows=channels: `calibrate_2d` :179-207).
+// scheme: 0 symmetric, 1 asymmetric.  Returns 0, or 1+row of the first slice
+// whose scale is not finite/positive (QuantError::InvalidScale).
+int orc_minmax_calibrate(const float* x, int64_t rows, int64_t cols, int bits, int scheme,
+                         float* scales, int32_t* zps) {
+  for (int64_t r = 0; r < rows; ++r) {
+    const float* s = x + r * cols;
+    float fmin = INFINITY, fmax = -INFINITY;
+    for (int64_t i = 0; i < cols; ++i) { float v = s[i]; if (v < fmin) fmin = v; if (v > fmax) fmax = v; }
+    float scale; int32_t zp;
+    if (scheme == 0) {
+      float q_max = (float)(1 << (bits - 1)) - 1.0f;
+      float abs_max = rmax(rmax(std::fabs(fmin), std::fabs(fmax)), 1e-8f);
+      scale = abs_max / q_max; zp = 0;
+    } else {
+      float q_range = (float)((1 << bits) - 1);
+      float range = rmax(fmax - fmin, 1e-8f);
+      scale = range / q_range;
+      zp = f32_as_i32(rclamp(std::round(-fmin / scale), 0.0f, q_range));
+    }
+    if (!std::isfinite(scale) || scale <= 0.0f) return (int)(1 + r);
+    scales[r] = scale; zps[r] = zp;
+  }
+  return 0;
+}
+
+// quantize (:252-268) / quantize_grouped (:275-299): row r uses scales[r], zps[r].
+void orc_minmax_quantize(const float* x, int64_t rows, int64_t cols, const float* scales,
+                         const int32_t* zps, int bits, int scheme, int32_t* codes) {
+  float q_max = scheme == 0 ? (float)(1 << (bits - 1)) - 1.0f : (float)(1 << bits) - 1.0f;
+  float q_min = scheme == 0 ? -(float)(1 << (bits - 1)) : 0.0f;
+  for (int64_t r = 0; r < rows; ++r) {
+    float scale = scales[r], zp = (float)zps[r];
+    for (int64_t i = 0; i < cols; ++i) {
+      float xq = rclamp(std::round(x[r * cols + i] / scale + zp), q_min, q_max);
+      codes[r * cols + i] = f32_as_i32(xq);
+    }
+  }
+}
+
+// dequantize (:302-306) / dequantize_grouped (:309-324).
+void orc_minmax_dequantize(const int32_t* codes, int64_t rows, int64_t cols, const float* scales,
+                           const int32_t* zps, float* out) {
+  for (int64_t r = 0; r < rows; ++r)
+    for (int64_t i = 0; i < cols; ++i)
+      out[r * cols + i] = (float)(int32_t)((uint32_t)codes[r * cols + i] - (uint32_t)zps[r]) * scales[r];
+}
+
+// FakeQuantize::forward — crates/oxicuda-quant/src/qat/fake_quant.rs:118-133
+// (the CPU oracle of the fake_quant PTX kernel, ptx_kernels.rs:55-121).
+void orc_fake_quant(const float* x, int64_t n, float scale, float zp, float qmin, float qmax, float* out) {
+  for (int64_t i = 0; i < n; ++i) {
+    float q = rclamp(std::round(x[i] / scale + zp), qmin, qmax);
+    out[i] = (q - zp) * scale;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Fp8Codec — crates/oxicuda-quant/src/scheme/fp8.rs
+// ---------------------------------------------------------------------------
+// encode (:135-137) -> encode_f32 (:115-122).  fmt: 0 E4M3, 1 E5M2.
+// mode: 0 = reference codec (truncating), 1 = RNE/saturating (hardware).
+// Returns -1, or the index of the first non-finite input (NonFiniteFp8).
+int64_t orc_fp8_encode(const float* x, int64_t n, int fmt, int mode, uint8_t* out) {
+  const Fp8Fmt& F = fmt_of(fmt);
+  for (int64_t i = 0; i < n; ++i) {
+    float v = x[i];
+    if (!std::isfinite(v)) return i;
+    float vs = rclamp(v, -F.max_val, F.max_val);
+    out[i] = mode == 0 ? fp8_encode_ref(vs, F) : fp8_encode_rne(vs, F);
+  }
+  return -1;
+}
+// decode (:140-142).  mode 0 = reference decode, 1 = IEEE decode.
+void orc_fp8_decode(const uint8_t* codes, int64_t n, int fmt, int mode, float* out) {
+  const Fp8Fmt& F = fmt_of(fmt);
+  for (int64_t i = 0; i < n; ++i) out[i] = mode == 0 ? fp8_decode_ref(codes[i], F) : fp8_decode_ieee(codes[i], F);
+}
+
+// Absmax-scaled FP8 quantization of `rows` slices of `cols` elements:
+// scale = absmax/max_val (1.0 when the slice is all zero), code = encode(x/scale).
+// Composition of the scale rule of crates/oxicuda-dnn/src/quantize/fp8_quantize.rs:28-34,
+// :591-596 (div.rn then clamp) with the Fp8Codec above.  rows=1 is per-tensor.
+int64_t orc_fp8_quantize_rows(const float* x, int64_t rows, int64_t cols, int fmt, int mode,
+                              float* scales, uint8_t* codes) {
+  const Fp8Fmt& F = fmt_of(fmt);
+  for (int64_t r = 0; r < rows; ++r) {
+    const float* s = x + r * cols;
+    float amax = 0.0f;
+    for (int64_t i = 0; i < cols; ++i) { if (!std::isfinite(s[i])) return r * cols + i; amax = rmax(amax, std::fabs(s[i])); }
+    float scale = amax > 0.0f ? amax / F.max_val : 1.0f;
+    scales[r] = scale;
+    for (int64_t i = 0; i < cols; ++i) {
+      float vs = rclamp(s[i] / scale, -F.max_val, F.max_val);
+      codes[r * cols + i] = mode == 0 ? fp8_encode_ref(vs, F) : fp8_encode_rne(vs, F);
+    }
+  }
+  return -1;
+}
+
+// ---------------------------------------------------------------------------
+// FP4 / micro-scaling — crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs
+// ---------------------------------------------------------------------------
+uint8_t orc_fp4_quantize_one(float v, int format) { return format == 0 ? e2m1_encode_ref(v) : int4_encode_ref(v); }
+float orc_fp4_dequantize_one(uint8_t raw, int format) { return format == 0 ? e2m1_decode_ref(raw) : int4_decode_ref(raw); }
+uint8_t orc_e8m0_from_absmax(float a) { return e8m0_from_absmax(a); }
+
+// Fp4Quantizer::quantize (:708-723) + PackedFp4::pack (:465-472): n must be even;
+// element 2i goes to the low nibble of byte i.
+void orc_fp4_quantize(const float* x, int64_t n, int format, uint8_t* packed) {
+  for (int64_t i = 0; i < n / 2; ++i) {
+    uint8_t v0 = orc_fp4_quantize_one(x[2 * i], format), v1 = orc_fp4_quantize_one(x[2 * i + 1], format);
+    packed[i] = (uint8_t)(v0 | (v1 << 4));
+  }
+}
+void orc_fp4_dequantize(const uint8_t* packed, int64_t nbytes, int format, float* out) {
+  for (int64_t i = 0; i < nbytes; ++i) {
+    out[2 * i] = orc_fp4_dequantize_one(packed[i] & 0x0F, format);
+    out[2 * i + 1] = orc_fp4_dequantize_one((packed[i] >> 4) & 0x0F, format);
+  }
+}
+
+// MicroScalingQuantizer::compute_scales (:763-782) + quantize_fp4 (:849-876).
+// Blocks of `block` run over the flat array; the last block may be short; an odd
+// length is padded with one 0.0.  scale_mode 0: f32 scale absmax/target_max
+// (reference); scale_mode 1: E8M0 byte (parity unpinned, see e8m0_from_absmax).
+// `scales_f32` receives ceil(n/block) floats (mode 0) and/or `scales_e8m0`
+// ceil(n/block) bytes (mode 1).  packed receives ceil(n/2) bytes.
+void orc_fp4_block_quantize(const float* x, int64_t n, int block, int format, int scale_mode,
+                            uint8_t* packed, float* scales_f32, uint8_t* scales_e8m0) {
+  float target_max = format == 0 ? 6.0f : 8.0f;
+  int64_t nb = (n + block - 1) / block;
+  int64_t nbytes = (n + 1) / 2;
+  std::memset(packed, 0, (size_t)nbytes);
+#pragma omp parallel for schedule(static)
+  for (int64_t b = 0; b < nb; ++b) {
+    int64_t s = b * block, e = std::min<int64_t>(s + block, n);
+    float amax = 0.0f;
+    for (int64_t i = s; i < e; ++i) amax = rmax(amax, std::fabs(x[i]));
+    float scale;
+    if (scale_mode == 0) {
+      scale = amax == 0.0f ? 1.0f : amax / target_max;
+      scales_f32[b] = scale;
+    } else {
+      uint8_t eb = e8m0_from_absmax(amax);
+      scales_e8m0[b] = eb;
+      scale = e8m0_to_f32(eb);
+    }
+    for (int64_t i = s; i < e; ++i) {
+      uint8_t c = orc_fp4_quantize_one(x[i] / scale, format);
+      // block is even, so two elements of one byte never belong to different threads
+      if (i & 1) packed[i >> 1] |= (uint8_t)(c << 4); else packed[i >> 1] |= c;
+    }
+  }
+}
+
+// dequantize_fp4 (:879-897): decode(code) * scale[i / block].
+void orc_fp4_block_dequantize(const uint8_t* packed, int64_t n, int block, int format, int scale_mode,
+                              const float* scales_f32, const uint8_t* scales_e8m0, float* out) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) {
+    uint8_t byte = packed[i >> 1];
+    uint8_t raw = (i & 1) ? (byte >> 4) & 0x0F : byte & 0x0F;
+    float scale = scale_mode == 0 ? scales_f32[i / block] : e8m0_to_f32(scales_e8m0[i / block]);
+    out[i] = orc_fp4_dequantize_one(raw, format) * scale;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// NF4 — crates/oxicuda-quant/src/scheme/nf4.rs:93-150
+// ---------------------------------------------------------------------------
+void orc_nf4_encode(const float* x, int64_t n, int block, uint8_t* packed, float* absmaxs) {
+  std::memset(packed, 0, (size_t)(n / 2));
+  for (int64_t b = 0; b < n / block; ++b) {
+    const float* s = x + b * block;
+    float amax = 0.0f;
+    for (int i = 0; i < block; ++i) amax = rmax(amax, std::fabs(s[i]));
+    if (amax < 1e-8f) amax = 1e-8f;
+    absmaxs[b] = amax;
+    int64_t base = b * block / 2;
+    for (int i = 0; i < block; ++i) {
+      float normed = rclamp(s[i] / amax, -1.0f, 1.0f);
+      uint8_t code = (uint8_t)nearest_nf4(normed);
+      if (i % 2 == 0) packed[base + i / 2] = code; else packed[base + i / 2] |= (uint8_t)(code << 4);
+    }
+  }
+}
+void orc_nf4_decode(const uint8_t* packed, int64_t nbytes, int block, const float* absmaxs, float* out) {
+  for (int64_t i = 0; i < nbytes; ++i) {
+    float amax = absmaxs[(2 * i) / block];
+    out[2 * i] = NF4_LUT[packed[i] & 0x0F] * amax;
+    out[2 * i + 1] = NF4_LUT[packed[i] >> 4] * amax;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// dist-infer "FP8" (INT8 in a u8) — crates/oxicuda-dist-infer/src/quantisation/fp8_infer.rs:61-142
+// ---------------------------------------------------------------------------
+// quantize_fp8_block: per-block absmax is STORED (not a scale); block >= n is per-tensor.
+void orc_distfp8_quantize_block(const float* x, int64_t n, int64_t block, uint8_t* q, float* absmaxs) {
+  if (block < 1) block = 1;
+  for (int64_t s = 0, b = 0; s < n; s += block, ++b) {
+    int64_t e = std::min(s + block, n);
+    float amax = 0.0f;
+    for (int64_t i = s; i < e; ++i) amax = rmax(amax, std::fabs(x[i]));
+    absmaxs[b] = amax;
+    if (amax == 0.0f) { for (int64_t i = s; i < e; ++i) q[i] = 0; continue; }
+    float scale = 127.0f / amax;
+    for (int64_t i = s; i < e; ++i) q[i] = (uint8_t)f32_as_i8(std::round(rclamp(x[i] * scale, -127.0f, 127.0f)));
+  }
+}
+void orc_distfp8_dequantize_block(const uint8_t* q, int64_t n, int64_t block, const float* absmaxs, float* out) {
+  if (block < 1) block = 1;
+  for (int64_t i = 0; i < n; ++i) out[i] = (float)(int8_t)q[i] * (absmaxs[i / block] / 127.0f);
+}
+
+// ---------------------------------------------------------------------------
+// LLM.int8 — crates/oxicuda-quant/src/scheme/llm_int8.rs:175-288
+// ---------------------------------------------------------------------------
+// x [samples x cols], w [rows x cols] row-major -> out [samples x rows].
+// Optional dumps (may be null): wq [rows x cols] i8, sw [rows], xq [samples x cols] i8,
+// sx [samples], acc [samples x rows] i32 (the integer accumulator, exact),
+// outlier [cols] u8.  Returns the number of outlier columns.
+int64_t orc_llm_int8_matmul(const float* x, const float* w, int64_t samples, int64_t rows, int64_t cols,
+                            float threshold, int row_wise, float* out,
+                            int8_t* wq_out, float* sw_out, int8_t* xq_out, float* sx_out,
+                            int32_t* acc_out, uint8_t* outlier_out) {
+  // detect_outliers (:128-157)
+  std::vector<float> col_max((size_t)cols, 0.0f);
+  for (int64_t r = 0; r < samples; ++r)
+    for (int64_t c = 0; c < cols; ++c) { float a = std::fabs(x[r * cols + c]); if (a > col_max[c]) col_max[c] = a; }
+  std::vector<uint8_t> is_out((size_t)cols, 0);
+  int64_t n_out = 0;
+  for (int64_t c = 0; c < cols; ++c) if (col_max[c] >= threshold) { is_out[c] = 1; ++n_out; }
+  if (outlier_out) std::memcpy(outlier_out, is_out.data(), (size_t)cols);
+
+  // per-weight-row scales and codes (:207-229)
+  std::vector<float> sw((size_t)rows);
+  std::vector<int8_t> wq((size_t)(rows * cols), 0);
+#pragma omp parallel for schedule(static)
+  for (int64_t k = 0; k < rows; ++k) {
+    float amax = 0.0f;
+    for (int64_t c = 0; c < cols; ++c) if (!is_out[c]) amax = rmax(amax, std::fabs(w[k * cols + c]));
+    sw[k] = amax > 0.0f ? amax / 127.0f : 1.0f;
+    float inv = 1.0f / sw[k];
+    for (int64_t c = 0; c < cols; ++c)
+      if (!is_out[c]) wq[k * cols + c] = f32_as_i8(rclamp(std::round(w[k * cols + c] * inv), -127.0f, 127.0f));
+  }
+  if (sw_out) std::memcpy(sw_out, sw.data(), sizeof(float) * (size_t)rows);
+  if (wq_out) std::memcpy(wq_out, wq.data(), (size_t)(rows * cols));
+
+  float sx_global = 1.0f;
+  if (!row_wise) {                                  // (:247-257)
+    float amax = 0.0f;
+    for (int64_t i = 0; i < samples * cols; ++i) if (!is_out[i % cols]) amax = rmax(amax, std::fabs(x[i]));
+    sx_global = amax > 0.0f ? amax / 127.0f : 1.0f;
+  }
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < samples; ++r) {
+    const float* xr = x + r * cols;
+    float sx;
+    if (row_wise) {
+      float amax = 0.0f;
+      for (int64_t c = 0; c < cols; ++c) if (!is_out[c]) amax = rmax(amax, std::fabs(xr[c]));
+      sx = amax > 0.0f ? amax / 127.0f : 1.0f;
+    } else sx = sx_global;
+    float inv_sx = 1.0f / sx;
+    std::vector<int32_t> xq((size_t)cols, 0);
+    for (int64_t c = 0; c < cols; ++c)
+      if (!is_out[c]) xq[c] = f32_as_i32(rclamp(std::round(xr[c] * inv_sx), -127.0f, 127.0f));
+    if (sx_out) sx_out[r] = sx;
+    if (xq_out) for (int64_t c = 0; c < cols; ++c) xq_out[r * cols + c] = (int8_t)xq[c];
+    for (int64_t k = 0; k < rows; ++k) {
+      int64_t acc_int = 0; float acc_fp = 0.0f;
+      for (int64_t c = 0; c < cols; ++c) {
+        if (is_out[c]) acc_fp += xr[c] * w[k * cols + c];
+        else acc_int += (int64_t)xq[c] * (int64_t)wq[k * cols + c];
+      }
+      if (acc_out) acc_out[r * rows + k] = (int32_t)acc_int;
+      out[r * rows + k] = (float)acc_int * (sx * sw[k]) + acc_fp;
+    }
+  }
+  return n_out;
+}
+
+// Exact INT8 GEMM with s32 accumulation: C[m,n] = sum_k A[m,k]*B[n,k].
+// Semantics of generate_int8_gemm_ptx (crates/oxicuda-blas/src/precision/int_ops.rs:446-583):
+// dp4a.s32.s32 over K, AccType::I32 store.  B is given here as [N x K] row-major
+// (weight layout); the reference kernel's K-packed [K/4 x N] u32 operand holds the same values.
+void orc_gemm_i8(const int8_t* a, const int8_t* b, int64_t M, int64_t N, int64_t K, int32_t* c) {
+#pragma omp parallel for schedule(static) collapse(2)
+  for (int64_t m = 0; m < M; ++m)
+    for (int64_t n = 0; n < N; ++n) {
+      int32_t acc = 0;
+      for (int64_t k = 0; k < K; ++k) acc += (int32_t)a[m * K + k] * (int32_t)b[n * K + k];
+      c[m * N + n] = acc;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// FP8 GEMM composition (parity unpinned by any reference test: the reference's
+// only complete GEMM generator rejects FP8, crates/oxicuda-ptx/src/templates/gemm.rs:800-809).
+// Defined as: decode codes (Fp8Codec decode, or IEEE decode), then the arithmetic
+// order of the reference's naive kernel (gemm.rs:373-447): k-ascending fma.rn.f32,
+// acc*alpha, then scale, stored as bf16 (RNE) or f32.
+// a [M x K] codes, w [N x K] codes ("out x in" weights).  sa: 1 or M floats
+// (sa_rows = 0/1); sw: 1 or N floats.  out = acc * (sa * sw).
+// ---------------------------------------------------------------------------
+void orc_gemm_fp8(const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt, int decode_mode,
+                  const float* sa, int sa_rows, const float* sw, int sw_rows,
+                  uint16_t* out_bf16, float* out_f32) {
+  const Fp8Fmt& F = fmt_of(fmt);
+  float lut[256];
+  for (int i = 0; i < 256; ++i) lut[i] = decode_mode == 0 ? fp8_decode_ref((uint8_t)i, F) : fp8_decode_ieee((uint8_t)i, F);
+  std::vector<float> af((size_t)(M * K)), wf((size_t)(N * K));
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < M * K; ++i) af[i] = lut[a[i]];
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < N * K; ++i) wf[i] = lut[w[i]];
+#pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; ++m) {
+    const float* ar = af.data() + m * K;
+    for (int64_t n = 0; n < N; ++n) {
+      const float* wr = wf.data() + n * K;
+      float acc = 0.0f;
+      for (int64_t k = 0; k < K; ++k) acc = std::fmaf(ar[k], wr[k], acc);
+      float s = (sa_rows ? sa[m] : sa[0]) * (sw_rows ? sw[n] : sw[0]);
+      float v = acc * s;
+      if (out_bf16) out_bf16[m * N + n] = f32_to_bf16_rne(v);
+      if (out_f32) out_f32[m * N + n] = v;
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// FP4 weight-only GEMV/GEMM composition: dequantize_fp4 (fp4_fp6_ops.rs:879-897)
+// then an f32 dot product, k ascending, against bf16 activations widened to f32.
+// The reference's own FP4 GEMM kernel text (fp4_fp6_ops.rs:1237-1362) is never
+// launched and decodes nibbles as INT4, so the defined semantics are this
+// composition (parity unpinned).
+// codes [N x K/2], scales [N x K/block], x [M x K] bf16 -> out [M x N].
+// ---------------------------------------------------------------------------
+void orc_gemv_fp4(const uint8_t* codes, int scale_mode, const float* scales_f32, const uint8_t* scales_e8m0,
+                  int block, const uint16_t* x_bf16, int64_t M, int64_t N, int64_t K,
+                  uint16_t* out_bf16, float* out_f32) {
+  std::vector<float> xf((size_t)(M * K));
+  for (int64_t i = 0; i < M * K; ++i) xf[i] = bf16_to_f32(x_bf16[i]);
+#pragma omp parallel
+  {
+    std::vector<float> wrow((size_t)K);
+#pragma omp for schedule(static)
+    for (int64_t n = 0; n < N; ++n) {
+      for (int64_t k = 0; k < K; ++k) {
+        uint8_t byte = codes[(n * K + k) >> 1];
+        uint8_t raw = (k & 1) ? (byte >> 4) & 0x0F : byte & 0x0F;
+        int64_t bi = (n * K + k) / block;
+        float scale = scale_mode == 0 ? scales_f32[bi] : e8m0_to_f32(scales_e8m0[bi]);
+        wrow[k] = e2m1_decode_ref(raw) * scale;
+      }
+      for (int64_t m = 0; m < M; ++m) {
+        float acc = 0.0f;
+        const float* xr = xf.data() + m * K;
+        for (int64_t k = 0; k < K; ++k) acc += xr[k] * wrow[k];
+        if (out_bf16) out_bf16[m * N + n] = f32_to_bf16_rne(acc);
+        if (out_f32) out_f32[m * N + n] = acc;
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Tensor-parallel linears — crates/oxicuda-dist-infer/src/tensor_parallel
+// ---------------------------------------------------------------------------
+// ColumnLinear: shard r owns rows [r*out/tp, (r+1)*out/tp) of W[out x in]
+// (column_parallel.rs:115-166); forward acc = bias; acc += x*w, k ascending, unfused
+// (:77-95); all_gather places shard r at columns [r*out/tp, ...) (:181-204).
+// bias may be null (zeros).  Returns the gathered [batch x out].
+void orc_column_linear(const float* x, const float* w, const float* bias, int64_t batch, int64_t in_f,
+                       int64_t out_f, int tp, float* out) {
+  int64_t local_out = out_f / tp;
+  for (int r = 0; r < tp; ++r) {
+#pragma omp parallel for schedule(static)
+    for (int64_t b = 0; b < batch; ++b)
+      for (int64_t o = 0; o < local_out; ++o) {
+        int64_t row = r * local_out + o;
+        float acc = bias ? bias[row] : 0.0f;
+        for (int64_t i = 0; i < in_f; ++i) acc += x[b * in_f + i] * w[row * in_f + i];
+        out[b * out_f + row] = acc;
+      }
+  }
+}
+// RowLinear: shard r owns columns [r*in/tp, ...) of every row (row_parallel.rs:109-168);
+// forward_partial acc=0; acc += x_s*w_s; bias added on rank 0 only (:67-89);
+// all_reduce sums the partials in rank order 0,1,... (:202-223).
+void orc_row_linear(const float* x, const float* w, const float* bias, int64_t batch, int64_t in_f,
+                    int64_t out_f, int tp, float* out) {
+  int64_t local_in = in_f / tp;
+#pragma omp parallel for schedule(static)
+  for (int64_t b = 0; b < batch; ++b)
+    for (int64_t o = 0; o < out_f; ++o) {
+      float total = 0.0f;
+      for (int r = 0; r < tp; ++r) {
+        float acc = 0.0f;
+        for (int64_t i = 0; i < local_in; ++i) acc += x[b * in_f + r * local_in + i] * w[o * in_f + r * local_in + i];
+        if (r == 0 && bias) acc += bias[o];
+        total = r == 0 ? acc : total + acc;
+      }
+      out[b * out_f + o] = total;
+    }
+}
+// silu — crates/oxicuda-lm/src/layer/ffn.rs:25-27: x / (1 + exp(-x)).
+void orc_swiglu(const float* gate, const float* up, int64_t n, float* h) {
+  for (int64_t i = 0; i < n; ++i) h[i] = (gate[i] / (1.0f + std::exp(-gate[i]))) * up[i];
+}
+
+// ---------------------------------------------------------------------------
+// Tile heuristics — crates/oxicuda-blas/src/precision/fp8_ops.rs:67-87 (classify),
+// :239-304 (Blackwell table), :389-396 (split-K); fp4_fp6_ops.rs:996-1075;
+// int_ops.rs:141-176.  Class ids: 0 SmallSquare, 1 LargeSquare, 2 SkinnyM,
+// 3 SkinnyN, 4 SkinnyK, 5 General.
+// ---------------------------------------------------------------------------
+int orc_classify_workload(uint32_t m, uint32_t n, uint32_t k) {
+  uint64_t mn = (uint64_t)m * n;
+  if (mn < 8192) return 0;
+  if (m < 128 && n >= 128) return 2;
+  if (n < 128 && m >= 128) return 3;
+  if (k < 64) return 4;
+  if (m >= 1024 && n >= 1024) return 1;
+  return 5;
+}
+// out[8] = tile_m, tile_n, tile_k, warp_m, warp_n, stages, use_tensor_core, split_k
+// dtype: 0 fp8, 1 fp4, 2 int8; sm: 100 (Blackwell table).
+void orc_tile_config(int dtype, uint32_t m, uint32_t n, uint32_t k, uint32_t* out) {
+  int cls = orc_classify_workload(m, n, k);
+  uint32_t stages = k < 64 ? 2 : 4;
+  if (dtype == 2) { uint32_t t[8] = {128, 128, 64, 64, 64, 4, 1, 1}; std::memcpy(out, t, 32); return; }
+  uint32_t t[8] = {0, 0, 128, 0, 0, stages, 1, 1};
+  switch (cls) {
+    case 0: t[0] = 64; t[1] = 64; t[2] = 64; t[3] = 32; t[4] = 32; break;
+    case 2: t[0] = 64; t[1] = 256; t[3] = 32; t[4] = 128; break;
+    case 3: t[0] = 256; t[1] = 64; t[3] = 128; t[4] = 32; break;
+    case 1: t[0] = 256; t[1] = 256; t[3] = 64; t[4] = 128; break;
+    case 4: t[0] = 256; t[1] = 256; t[3] = 64; t[4] = 128; t[5] = 2; if (dtype == 1) t[2] = 64; break;
+    default: t[0] = dtype == 1 ? 128 : 256; t[1] = 256; t[3] = 64; t[4] = 128; break;
+  }
+  std::memcpy(out, t, 32);
+}
+uint32_t orc_fp8_split_k(uint32_t m, uint32_t n, uint32_t k) {
+  if (m * n < 2048 && k > 32768) { uint32_t f = k / 8192; return f < 2 ? 2 : (f > 64 ? 64 : f); }
+  return 1;
+}
+
+}  // extern "C"

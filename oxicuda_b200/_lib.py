@@ -1,0 +1,204 @@
+"""ctypes binding of libb2q.so — the C ABI declared in include/b2q.h.
+
+The library is the product; this module only loads it and maps status codes to
+exceptions named after the reference's error variants
+(crates/oxicuda-blas/src/error.rs:17-60, crates/oxicuda-quant/src/error.rs:10-58).
+There is no fallback: if the shared library is missing, importing a symbol fails
+loudly, and without a CUDA device `Handle()` raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_PKG = Path(__file__).resolve().parent
+LIB_PATH = _PKG / "libb2q.so"
+
+# status codes (include/b2q.h)
+OK = 0
+ERR_CUDA, ERR_INVALID_DIMENSION, ERR_BUFFER_TOO_SMALL, ERR_DIMENSION_MISMATCH = 1, 2, 3, 4
+ERR_UNSUPPORTED, ERR_LAUNCH_FAILED, ERR_INVALID_ARGUMENT = 5, 7, 8
+ERR_EMPTY_INPUT, ERR_GROUP_SIZE_MISMATCH, ERR_INVALID_SCALE, ERR_NON_FINITE_FP8, ERR_INVALID_CONFIG = 20, 21, 22, 23, 24
+ERR_TIMEOUT = 40
+
+FP8_E4M3, FP8_E5M2 = 0, 1
+ROUND_REF, ROUND_RNE = 0, 1
+FP4_E2M1, FP4_INT4 = 0, 1
+SCALE_F32, SCALE_E8M0 = 0, 1
+SYMMETRIC, ASYMMETRIC = 0, 1
+OUT_BF16, OUT_F32 = 0, 1
+SCALE_SCALAR, SCALE_PER_ROW = 0, 1
+
+
+class B2qError(RuntimeError):
+    """Base of every error raised for a non-zero b2q status."""
+    status = -1
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"[b2q status {status}] {message}")
+        self.status = status
+        self.message = message
+
+
+class CudaError(B2qError): pass
+class InvalidDimension(B2qError): pass
+class BufferTooSmall(B2qError): pass
+class DimensionMismatch(B2qError): pass
+class UnsupportedOperation(B2qError): pass
+class LaunchFailed(B2qError): pass
+class InvalidArgument(B2qError): pass
+class EmptyInput(B2qError): pass
+class GroupSizeMismatch(B2qError): pass
+class InvalidScale(B2qError): pass
+class NonFiniteFp8(B2qError): pass
+class InvalidConfig(B2qError): pass
+class DeviceTimeout(B2qError): pass
+
+
+_ERRORS = {
+    ERR_CUDA: CudaError, ERR_INVALID_DIMENSION: InvalidDimension, ERR_BUFFER_TOO_SMALL: BufferTooSmall,
+    ERR_DIMENSION_MISMATCH: DimensionMismatch, ERR_UNSUPPORTED: UnsupportedOperation, ERR_LAUNCH_FAILED: LaunchFailed,
+    ERR_INVALID_ARGUMENT: InvalidArgument, ERR_EMPTY_INPUT: EmptyInput, ERR_GROUP_SIZE_MISMATCH: GroupSizeMismatch,
+    ERR_INVALID_SCALE: InvalidScale, ERR_NON_FINITE_FP8: NonFiniteFp8, ERR_INVALID_CONFIG: InvalidConfig,
+    ERR_TIMEOUT: DeviceTimeout,
+}
+
+
+class TileConfig(C.Structure):
+    """TileConfig, crates/oxicuda-blas/src/level3/gemm/dispatch.rs:57-107."""
+    _fields_ = [(n, C.c_uint32) for n in
+                ("tile_m", "tile_n", "tile_k", "warp_m", "warp_n", "stages", "use_tensor_core", "split_k")]
+
+    def as_tuple(self):
+        return tuple(getattr(self, n) for n, _ in self._fields_)
+
+
+_H = C.c_void_p
+_P = C.c_void_p
+_I64 = C.c_int64
+_I = C.c_int
+_F = C.c_float
+_U32 = C.c_uint32
+
+# name -> (restype, argtypes); must list every symbol include/b2q.h declares
+SIGNATURES = {
+    "b2q_create": (C.c_int32, [C.POINTER(_H), _I]),
+    "b2q_destroy": (C.c_int32, [_H]),
+    "b2q_set_stream": (C.c_int32, [_H, _P]),
+    "b2q_get_sm": (C.c_int32, [_H, C.POINTER(_I)]),
+    "b2q_get_sm_count": (C.c_int32, [_H, C.POINTER(_I)]),
+    "b2q_last_error": (C.c_char_p, [_H]),
+    "b2q_check": (C.c_int32, [_H]),
+    "b2q_minmax_calibrate_f32": (C.c_int32, [_H, _P, _I64, _I64, _I, _I, _P, _P]),
+    "b2q_minmax_quantize_f32": (C.c_int32, [_H, _P, _I64, _I64, _P, _P, _I, _I, _P]),
+    "b2q_minmax_dequantize_f32": (C.c_int32, [_H, _P, _I64, _I64, _P, _P, _P]),
+    "b2q_fake_quant_inplace_f32": (C.c_int32, [_H, _P, _I64, _F, _F, _F, _F]),
+    "b2q_fp8_encode_f32": (C.c_int32, [_H, _P, _I64, _I, _I, _P]),
+    "b2q_fp8_decode_f32": (C.c_int32, [_H, _P, _I64, _I, _I, _P]),
+    "b2q_fp8_quantize_rows_f32": (C.c_int32, [_H, _P, _I64, _I64, _I, _I, _P, _P]),
+    "b2q_fp8_quantize_rows_bf16": (C.c_int32, [_H, _P, _I64, _I64, _I, _I, _P, _P]),
+    "b2q_fp4_block_quantize_f32": (C.c_int32, [_H, _P, _I64, _I, _I, _I, _P, _P]),
+    "b2q_fp4_block_dequantize_f32": (C.c_int32, [_H, _P, _I64, _I, _I, _I, _P, _P]),
+    "b2q_nf4_decode_f32": (C.c_int32, [_H, _P, _I64, _I, _P, _P]),
+    "b2q_nf4_encode_f32": (C.c_int32, [_H, _P, _I64, _I, _P, _P]),
+    "b2q_int8_quant_f32": (C.c_int32, [_H, _P, _I64, _F, _P]),
+    "b2q_int8_dequant_f32": (C.c_int32, [_H, _P, _I64, _F, _P]),
+    "b2q_distfp8_quantize_block_f32": (C.c_int32, [_H, _P, _I64, _I64, _P, _P]),
+    "b2q_distfp8_dequantize_block_f32": (C.c_int32, [_H, _P, _I64, _I64, _P, _P]),
+    "b2q_llm_int8_linear_f32": (C.c_int32, [_H, _P, _P, _I64, _I64, _I64, _F, _I, _P, _P, _P, _P, _P, _P, _P]),
+    "b2q_gemm_i8": (C.c_int32, [_H, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P]),
+    "b2q_gemm_fp8": (C.c_int32, [_H, _P, _P, _I64, _I64, _I64, _I, _P, _I, _P, _I, _P, _I]),
+    "b2q_gemm_fp8_simt": (C.c_int32, [_H, _P, _P, _I64, _I64, _I64, _I, _I, _P, _I, _P, _I, _P, _I]),
+    "b2q_gemv_fp4_wo": (C.c_int32, [_H, _P, _P, _I, _I, _P, _I64, _I64, _I64, _P, _I]),
+    "b2q_classify_workload": (C.c_int32, [_U32, _U32, _U32]),
+    "b2q_ref_tile_config": (C.c_int32, [_I, _U32, _U32, _U32, C.POINTER(TileConfig)]),
+    "b2q_fp8_compute_split_k": (_U32, [_U32, _U32, _U32]),
+    "b2q_select_tile": (C.c_int32, [_I, _U32, _U32, _U32, C.POINTER(TileConfig), C.POINTER(_I)]),
+}
+
+_lib = None
+
+
+def lib() -> C.CDLL:
+    """The loaded shared library; raises if it has not been built."""
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise ImportError(
+                f"{LIB_PATH} is missing: build it with `python -m oxicuda_b200._build` "
+                "(there is no CPU or PyTorch fallback for the CUDA kernels)")
+        L = C.CDLL(str(LIB_PATH))
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)           # AttributeError if the library lacks a declared symbol
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def ptr(t) -> C.c_void_p:
+    """Device (or host) address of a torch tensor / numpy array / None."""
+    if t is None:
+        return C.c_void_p(0)
+    if hasattr(t, "data_ptr"):
+        return C.c_void_p(t.data_ptr())
+    return C.c_void_p(t.ctypes.data)
+
+
+class Handle:
+    """BlasHandle equivalent (crates/oxicuda-blas/src/handle.rs:43-264): one per host thread."""
+
+    def __init__(self, device: int = 0):
+        self._h = _H()
+        st = lib().b2q_create(C.byref(self._h), device)
+        if st != OK:
+            raise _ERRORS.get(st, B2qError)(st, "b2q_create failed (no CUDA device, or not an sm_100 GPU)")
+        self.device = device
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib().b2q_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def call(self, name: str, *args):
+        st = getattr(lib(), name)(self._h, *args)
+        if st != OK:
+            msg = lib().b2q_last_error(self._h)
+            raise _ERRORS.get(st, B2qError)(st, msg.decode() if msg else name)
+
+    def set_stream(self, stream_ptr: int):
+        self.call("b2q_set_stream", C.c_void_p(stream_ptr))
+
+    def sm_version(self) -> int:
+        v = _I()
+        self.call("b2q_get_sm", C.byref(v))
+        return v.value
+
+    def sm_count(self) -> int:
+        v = _I()
+        self.call("b2q_get_sm_count", C.byref(v))
+        return v.value
+
+    def check(self):
+        """Synchronise and raise what the kernels recorded on the device (NonFiniteFp8, InvalidScale, timeout)."""
+        self.call("b2q_check")
+
+
+_default = {}
+
+
+def default_handle(device: int | None = None) -> Handle:
+    import torch
+    if device is None:
+        device = torch.cuda.current_device()
+    h = _default.get(device)
+    if h is None:
+        h = _default[device] = Handle(device)
+    h.set_stream(torch.cuda.current_stream(device).cuda_stream)
+    return h

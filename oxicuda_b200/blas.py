@@ -1,0 +1,210 @@
+"""Host-side mirror of the oxicuda-blas quantized GEMM/GEMV surface on this path.
+
+Names follow `crates/oxicuda-blas/src/precision/{fp8_ops,fp4_fp6_ops,int_ops}.rs` and
+`level3/gemm_api.rs`; every numeric call goes through the C ABI to a CUDA kernel.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from enum import Enum
+
+import torch
+
+from . import _lib as L
+from ._lib import TileConfig, default_handle, lib, ptr
+from .quant import _back, _dev
+
+
+class Fp8WorkloadClass(Enum):
+    """crates/oxicuda-blas/src/precision/fp8_ops.rs:42-61"""
+    SmallSquare = 0
+    LargeSquare = 1
+    SkinnyM = 2
+    SkinnyN = 3
+    SkinnyK = 4
+    General = 5
+
+
+def classify_workload(m: int, n: int, k: int) -> Fp8WorkloadClass:
+    """fp8_ops.rs:67-87"""
+    return Fp8WorkloadClass(lib().b2q_classify_workload(m, n, k))
+
+
+def _ref_tile(dtype: int, m: int, n: int, k: int) -> TileConfig:
+    t = TileConfig()
+    st = lib().b2q_ref_tile_config(dtype, m, n, k, C.byref(t))
+    if st == L.ERR_INVALID_DIMENSION:
+        raise L.InvalidDimension(st, f"GEMM dimensions must be non-zero: m={m}, n={n}, k={k}")
+    if st != L.OK:
+        raise L.InvalidArgument(st, "b2q_ref_tile_config")
+    return t
+
+
+class Fp8Config:
+    """Fp8Config, crates/oxicuda-blas/src/precision/fp8_ops.rs:320-397 (Blackwell arm)."""
+    ELEMENT_BYTES = 1
+
+    @staticmethod
+    def tile_config(m: int, n: int, k: int) -> TileConfig:
+        return _ref_tile(0, m, n, k)
+
+    @staticmethod
+    def compute_split_k(m: int, n: int, k: int) -> int:
+        return int(lib().b2q_fp8_compute_split_k(m, n, k))
+
+
+def select_fp4_tile(m: int, n: int, k: int) -> TileConfig:
+    """select_fp4_tile, crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:996-1075 (Sm100 arm)."""
+    return _ref_tile(1, m, n, k)
+
+
+def int8_tile_config(m: int, n: int, k: int) -> TileConfig:
+    """Int8GemmConfig::tile_config, crates/oxicuda-blas/src/precision/int_ops.rs:141-176 (Sm100 arm)."""
+    return _ref_tile(2, m, n, k)
+
+
+def select_tile(dtype: str, m: int, n: int, k: int):
+    """The static per-shape table the kernels are dispatched with: (TileConfig, kernel_id)."""
+    t, kid = TileConfig(), C.c_int()
+    st = lib().b2q_select_tile({"fp8": 0, "fp4": 1, "int8": 2}[dtype], m, n, k, C.byref(t), C.byref(kid))
+    if st != L.OK:
+        raise L.InvalidDimension(st, "b2q_select_tile")
+    return t, kid.value
+
+
+# ---------------------------------------------------------------------------
+# FP4 / micro-scaling
+# ---------------------------------------------------------------------------
+class Fp4Format(Enum):
+    """crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:107-134"""
+    E2M1 = 0
+    Int4 = 1
+
+    def max_value(self) -> float:
+        return 6.0 if self is Fp4Format.E2M1 else 8.0
+
+
+class ScalingFormat(Enum):
+    """fp4_fp6_ops.rs:142-171, plus E8M0 (absent from the reference)."""
+    Fp32 = 0
+    E8M0 = 1
+
+
+@dataclass
+class MicroScalingConfig:
+    """fp4_fp6_ops.rs:190-225"""
+    block_size: int = 32
+    scaling_format: ScalingFormat = ScalingFormat.Fp32
+    VALID_BLOCK_SIZES = (32, 64, 128)
+
+    def validate(self):
+        if self.block_size not in self.VALID_BLOCK_SIZES:
+            raise L.InvalidArgument(L.ERR_INVALID_ARGUMENT,
+                                    f"MicroScaling block_size must be one of [32, 64, 128], got {self.block_size}")
+
+    def num_scales(self, num_elements: int) -> int:
+        return -(-num_elements // self.block_size)
+
+
+class PackedFp4:
+    """PackedFp4::{pack,unpack}, fp4_fp6_ops.rs:452-481 (pure byte helpers)."""
+
+    @staticmethod
+    def pack(v0: int, v1: int) -> int:
+        if v0 > 15 or v1 > 15:
+            raise L.InvalidArgument(L.ERR_INVALID_ARGUMENT, f"FP4 raw values must be <= 15: got ({v0}, {v1})")
+        return v0 | (v1 << 4)
+
+    @staticmethod
+    def unpack(b: int):
+        return b & 0x0F, (b >> 4) & 0x0F
+
+
+class MicroScalingQuantizer:
+    """MicroScalingQuantizer, fp4_fp6_ops.rs:746-898: block absmax scale + E2M1/INT4 codes."""
+
+    def __init__(self, config: MicroScalingConfig):
+        self.config = config
+
+    def quantize_fp4(self, values: torch.Tensor, format: Fp4Format = Fp4Format.E2M1):
+        """fp4_fp6_ops.rs:849-876 -> (packed u8 [n/2], scales f32 or u8 [n/block])."""
+        self.config.validate()
+        x, was_host = _dev(values.reshape(-1), torch.float32)
+        n, blk = x.numel(), self.config.block_size
+        e8 = self.config.scaling_format == ScalingFormat.E8M0
+        packed = torch.empty((n + 1) // 2, dtype=torch.uint8, device=x.device)
+        scales = torch.empty(-(-n // blk), dtype=torch.uint8 if e8 else torch.float32, device=x.device)
+        default_handle().call("b2q_fp4_block_quantize_f32", ptr(x), n, blk, format.value,
+                              L.SCALE_E8M0 if e8 else L.SCALE_F32, ptr(packed), ptr(scales))
+        return _back(packed, was_host), _back(scales, was_host)
+
+    def dequantize_fp4(self, packed: torch.Tensor, scales: torch.Tensor, format: Fp4Format, original_len: int):
+        """fp4_fp6_ops.rs:879-897"""
+        self.config.validate()
+        p, was_host = _dev(packed.reshape(-1), torch.uint8)
+        e8 = self.config.scaling_format == ScalingFormat.E8M0
+        s, _ = _dev(scales.reshape(-1), torch.uint8 if e8 else torch.float32)
+        out = torch.empty(original_len, dtype=torch.float32, device=p.device)
+        default_handle().call("b2q_fp4_block_dequantize_f32", ptr(p), original_len, self.config.block_size,
+                              format.value, L.SCALE_E8M0 if e8 else L.SCALE_F32, ptr(s), ptr(out))
+        return _back(out, was_host)
+
+
+# ---------------------------------------------------------------------------
+# GEMM / GEMV (device tensors in, device tensors out; asynchronous on the current stream)
+# ---------------------------------------------------------------------------
+def _scale_kind(s: torch.Tensor, n: int) -> int:
+    if s.numel() == 1:
+        return L.SCALE_SCALAR
+    if s.numel() == n:
+        return L.SCALE_PER_ROW
+    raise L.DimensionMismatch(L.ERR_DIMENSION_MISMATCH, f"scale has {s.numel()} entries, expected 1 or {n}")
+
+
+def gemm_fp8(a: torch.Tensor, w: torch.Tensor, scale_a: torch.Tensor, scale_w: torch.Tensor, out: torch.Tensor = None,
+             out_dtype=torch.bfloat16, fmt: int = L.FP8_E4M3, simt_decode: str = None) -> torch.Tensor:
+    """out[M,N] = (A[M,K] . W[N,K]^T) * scale_a * scale_w.  The working replacement of gemm::<E4M3>
+    (crates/oxicuda-blas/src/level3/gemm_api.rs:82-231).  `simt_decode` in {"ref","ieee"} runs the
+    k-ascending fp32 checker kernel instead of the tensor-core kernel."""
+    M, K = a.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise L.DimensionMismatch(L.ERR_DIMENSION_MISMATCH, f"inner dimensions differ: {K} vs {K2}")
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    ot = L.OUT_BF16 if out.dtype == torch.bfloat16 else L.OUT_F32
+    h = default_handle()
+    args = (ptr(scale_a), _scale_kind(scale_a, M), ptr(scale_w), _scale_kind(scale_w, N), ptr(out), ot)
+    if simt_decode is None:
+        h.call("b2q_gemm_fp8", ptr(a), ptr(w), M, N, K, fmt, *args)
+    else:
+        h.call("b2q_gemm_fp8_simt", ptr(a), ptr(w), M, N, K, fmt, 0 if simt_decode == "ref" else 1, *args)
+    return out
+
+
+def gemm_i8(a: torch.Tensor, b: torch.Tensor, scale_a: torch.Tensor = None, scale_b: torch.Tensor = None,
+            want_s32: bool = True, want_f32: bool = False):
+    """C[M,N] = A[M,K] . B[N,K]^T with exact s32 accumulation (Int8GemmConfig,
+    crates/oxicuda-blas/src/precision/int_ops.rs:78-189).  Returns (c_s32 | None, c_f32 | None)."""
+    M, K = a.shape
+    N, K2 = b.shape
+    if K != K2:
+        raise L.DimensionMismatch(L.ERR_DIMENSION_MISMATCH, f"inner dimensions differ: {K} vs {K2}")
+    c32 = torch.empty(M, N, dtype=torch.int32, device=a.device) if want_s32 else None
+    cf = torch.empty(M, N, dtype=torch.float32, device=a.device) if want_f32 else None
+    default_handle().call("b2q_gemm_i8", ptr(a), ptr(b), M, N, K, ptr(c32), ptr(cf), ptr(scale_a), ptr(scale_b))
+    return c32, cf
+
+
+def gemv_fp4_wo(codes: torch.Tensor, scales: torch.Tensor, x: torch.Tensor, N: int, K: int, out: torch.Tensor = None,
+                out_dtype=torch.bfloat16, block: int = 32) -> torch.Tensor:
+    """out[tokens,N] = x[tokens,K] . dequant(codes[N,K/2], scales[N,K/block])^T  (tokens <= 32).
+    Fp4GemmConfig semantics, crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:337-395 / :879-897."""
+    tokens = x.shape[0]
+    if out is None:
+        out = torch.empty(tokens, N, dtype=out_dtype, device=x.device)
+    sf = L.SCALE_E8M0 if scales.dtype == torch.uint8 else L.SCALE_F32
+    ot = L.OUT_BF16 if out.dtype == torch.bfloat16 else L.OUT_F32
+    default_handle().call("b2q_gemv_fp4_wo", ptr(codes), ptr(scales), sf, block, ptr(x), tokens, N, K, ptr(out), ot)
+    return out

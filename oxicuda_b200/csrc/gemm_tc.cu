@@ -1,0 +1,441 @@
+// Prefill-shaped quantized GEMM on the 5th-generation tensor cores (sm_100a):
+//   out[m,n] = (sum_k A[m,k] * W[n,k]) * scale_a * scale_w
+// A [M x K] and W [N x K] are 8-bit codes (E4M3/E5M2, or INT8), both K-major.
+//
+// One persistent CTA per SM, 6 warps:
+//   warp 0      TMA producer: cp.async.bulk.tensor (no multicast) into a ring of
+//               128-byte-swizzled shared-memory stages, completion on mbarriers;
+//   warp 1      allocates TMEM and issues tcgen05.mma (one elected thread), the
+//               accumulator (128 lanes x BN fp32/s32 columns) lives in TMEM and is
+//               double-buffered so the epilogue of tile i overlaps the MMAs of i+1;
+//   warps 2..5  epilogue: tcgen05.ld of their 32-lane quarter, scale, convert to
+//               bf16/f32 (or raw s32), vectorised global stores.
+// Every mbarrier wait is bounded (wall-clock limit); on expiry the kernel records
+// B2Q_ERR_TIMEOUT in the status word, drains what it issued, frees TMEM and returns.
+#include "common.cuh"
+#include <cuda.h>
+
+namespace tc {
+
+constexpr int BM = 128;        // accumulator rows (= TMEM lanes)
+constexpr int BK = 128;        // K bytes per stage: one 128-byte swizzle atom
+constexpr int UMMA_K = 32;     // K per tcgen05.mma for 8-bit operands
+constexpr int kThreads = 192;
+constexpr int GROUP_M = 8;     // tile rasterisation: 8 row-blocks share each W panel in L2
+constexpr uint64_t kWaitLimitNs = 2000000000ull;
+
+enum Kind { kF8 = 0, kI8 = 1 };
+
+template <int BN> struct Cfg {
+  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr int kBytesA = BM * BK;
+  static constexpr int kBytesB = BN * BK;
+  static constexpr int kStageBytes = kBytesA + kBytesB;
+  static constexpr int kTmemCols = 2 * BN;                       // two accumulators
+  static constexpr int kSmem = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+struct Params {
+  int64_t M, N, K;
+  int tiles_m, tiles_n;
+  uint32_t idesc;
+  const float* scale_a; int scale_a_rows;
+  const float* scale_w; int scale_w_rows;
+  void* out; int out_type;          // kF8: bf16 / f32 scaled
+  int32_t* c_s32; float* c_f32;     // kI8: raw accumulators and/or scaled f32
+  int32_t* status;
+};
+
+// ---- PTX wrappers ----------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint64_t globaltimer_ns() { uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
+// Bounded wait: false when the limit expired or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if (((++spins) & 0x3F) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+template <int KIND>
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  if constexpr (KIND == kF8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  }
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor for a K-major tile stored as rows of 128 bytes
+// with the 128-byte swizzle (what TMA SWIZZLE_128B writes): 8-row groups are
+// 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;                     // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;           // stride byte offset
+  d |= (uint64_t)1 << 46;                     // descriptor version (sm_100)
+  d |= (uint64_t)2 << 61;                     // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& mb, int& nb) {
+  const int group_size = GROUP_M * tiles_n;
+  const int group = tile / group_size;
+  const int first_m = group * GROUP_M;
+  const int gm = min(tiles_m - first_m, GROUP_M);
+  const int in_group = tile - group * group_size;
+  mb = first_m + in_group % gm;
+  nb = in_group / gm;
+}
+
+template <int BN, int KIND>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const Params p) {
+  using C = Cfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = base + C::kStages * C::kStageBytes;
+  // barrier layout (8 bytes each): full[stages], empty[stages], tmem_full[2], tmem_empty[2], drain
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (C::kStages + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * C::kStages + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * C::kStages + 2 + b); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * C::kStages + 4);
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int total_tiles = p.tiles_m * p.tiles_n;
+  const int num_kb = (int)((p.K + BK - 1) / BK);
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < C::kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
+    mbar_init(drain_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&s_tmem_base), C::kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  volatile int* abort_flag = &s_abort;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        int mb, nb;
+        tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % C::kStages;
+          const uint32_t ph = (it / C::kStages) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag)) { ok = false; break; }
+          const uint32_t sa = base + s * C::kStageBytes, sb = sa + C::kBytesA;
+          mbar_expect_tx(full_bar(s), C::kStageBytes);
+          tma_load_2d(sa, &map_a, full_bar(s), kb * BK, mb * BM);
+          tma_load_2d(sb, &map_w, full_bar(s), kb * BK, nb * BN);
+        }
+      }
+      if (!ok) {
+        // give every copy already issued a bounded chance to land before shared memory is released
+        const uint32_t issued = it < (uint32_t)C::kStages ? it : (uint32_t)C::kStages;
+        for (uint32_t j = 0; j < issued; ++j) {
+          const uint32_t q = it - 1 - j;
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(full_bar(q % C::kStages), (q / C::kStages) & 1))
+            if (globaltimer_ns() - t0 > 100000000ull) break;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      uint32_t it = 0, tile_it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_it) {
+        const uint32_t buf = tile_it & 1, aph = (tile_it >> 1) & 1;
+        if (!mbar_wait(tempty_bar(buf), aph ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % C::kStages;
+          const uint32_t ph = (it / C::kStages) & 1;
+          if (!mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = base + s * C::kStageBytes, sb = sa + C::kBytesA;
+          const uint64_t adesc = make_smem_desc(sa), bdesc = make_smem_desc(sb);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // advancing K inside the swizzle atom: +32 bytes on the start address (16-byte units)
+            umma<KIND>(tmem_d, adesc + (uint64_t)(k * (UMMA_K >> 4)), bdesc + (uint64_t)(k * (UMMA_K >> 4)), p.idesc,
+                       (uint32_t)((kb | k) != 0));
+          }
+          tc_commit(empty_bar(s));          // stage reusable once these MMAs have read it
+        }
+        if (ok) tc_commit(tfull_bar(buf));  // accumulator complete
+      }
+      if (!ok) {                            // wait (bounded) for MMAs in flight before TMEM is freed
+        tc_commit(drain_bar);
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(drain_bar, 0))
+          if (globaltimer_ns() - t0 > 100000000ull) break;
+      }
+    }
+  } else {
+    // ---------------- epilogue (4 warps) ----------------
+    const int q = warp & 3;                 // TMEM lane quarter this warp may access
+    uint32_t tile_it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_it) {
+      int mb, nb;
+      tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
+      const uint32_t buf = tile_it & 1, aph = (tile_it >> 1) & 1;
+      if (!mbar_wait(tfull_bar(buf), aph, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int64_t m = (int64_t)mb * BM + q * 32 + lane;
+      const int64_t n0 = (int64_t)nb * BN;
+      const bool row_ok = m < p.M;
+      const float sa = row_ok && p.scale_a ? (p.scale_a_rows ? p.scale_a[m] : p.scale_a[0]) : 1.0f;
+      const float sw0 = p.scale_w && !p.scale_w_rows ? p.scale_w[0] : 1.0f;
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem_base + buf * BN + c + ((uint32_t)(q * 32) << 16), r);
+        tmem_ld_wait();
+        const int64_t n = n0 + c;
+        if (!row_ok || n >= p.N) continue;
+        const bool full = n + 32 <= p.N;
+        if constexpr (KIND == kF8) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float sw = p.scale_w_rows ? (n + j < p.N ? __ldg(p.scale_w + n + j) : 0.0f) : sw0;
+            v[j] = __uint_as_float(r[j]) * (sa * sw);
+          }
+          if (p.out_type == B2Q_OUT_BF16) {
+            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + m * p.N + n;
+            if (full && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 pk;
+                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]), h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                *reinterpret_cast<uint4*>(o + j) = pk;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (n + j < p.N) o[j] = __float2bfloat16_rn(v[j]);
+            }
+          } else {
+            float* o = reinterpret_cast<float*>(p.out) + m * p.N + n;
+            if (full && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (n + j < p.N) o[j] = v[j];
+            }
+          }
+        } else {
+          if (p.c_s32) {
+            int32_t* o = p.c_s32 + m * p.N + n;
+            if (full && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) if (n + j < p.N) o[j] = (int32_t)r[j];
+            }
+          }
+          if (p.c_f32) {
+            float* o = p.c_f32 + m * p.N + n;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (n + j < p.N) {
+                float f = __int2float_rn((int32_t)r[j]);
+                if (p.scale_a) f = __fmul_rn(f, __fmul_rn(sa, p.scale_w[n + j]));
+                o[j] = f;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(buf));
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+  if (threadIdx.x == 0 && s_abort) atomicCAS(p.status, 0, (int)B2Q_ERR_TIMEOUT);
+}
+
+// ---- host side --------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  }
+  return fn;
+}
+
+// rows x K bytes, K-major; box = 128 bytes x box_rows, 128-byte swizzle, zero fill out of bounds.
+int32_t make_map(b2q_handle h, CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) B2Q_FAIL(h, B2Q_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)K};
+  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) B2Q_FAIL(h, B2Q_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return B2Q_OK;
+}
+
+template <int BN, int KIND>
+int32_t launch(b2q_handle h, const void* a, const void* w, Params p) {
+  using C = Cfg<BN>;
+  CUtensorMap map_a, map_w;
+  int32_t st = make_map(h, &map_a, a, p.M, p.K, BM);
+  if (st != B2Q_OK) return st;
+  st = make_map(h, &map_w, w, p.N, p.K, BN);
+  if (st != B2Q_OK) return st;
+  p.tiles_m = (int)ceil_div64(p.M, BM);
+  p.tiles_n = (int)ceil_div64(p.N, BN);
+  // instruction descriptor: dense, D format, A/B formats, both K-major, N>>3 at bit 17, M>>4 at bit 24
+  const uint32_t shape = ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+  p.idesc = KIND == kF8 ? (p.idesc | (1u << 4) | shape) : ((2u << 4) | (1u << 7) | (1u << 10) | shape);
+  static bool attr_set = false;
+  if (!attr_set) {
+    B2Q_CUDA(h, cudaFuncSetAttribute(gemm_tc_kernel<BN, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
+    attr_set = true;
+  }
+  int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
+  int grid = (int)(tiles < h->sm_count ? tiles : h->sm_count);
+  gemm_tc_kernel<BN, KIND><<<grid, kThreads, C::kSmem, h->stream>>>(map_a, map_w, p);
+  B2Q_LAUNCH_CHECK(h, "gemm_tc_kernel");
+  return B2Q_OK;
+}
+
+}  // namespace tc
+
+int32_t b2q_validate_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,
+                              const float* scale_a, int ka, const float* scale_w, int kw, void* out, int out_type);
+
+int32_t b2q_gemm_i8_tc(b2q_handle h, const int8_t* a, const int8_t* b, int64_t M, int64_t N, int64_t K, int32_t* c_s32,
+                       float* c_f32, const float* sa, const float* sb) {
+  if (K % 16 != 0 || ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) != 0 || N < 64)
+    return B2Q_ERR_UNSUPPORTED;
+  tc::Params p{};
+  p.M = M; p.N = N; p.K = K;
+  p.scale_a = sa; p.scale_a_rows = 1; p.scale_w = sb; p.scale_w_rows = 1;
+  p.c_s32 = c_s32; p.c_f32 = c_f32; p.status = h->d_status;
+  b2q_tile_config t; int kid = 0;
+  b2q_select_tile(2, (uint32_t)M, (uint32_t)N, (uint32_t)K, &t, &kid);
+  return kid == 1 ? tc::launch<256, tc::kI8>(h, a, b, p) : tc::launch<128, tc::kI8>(h, a, b, p);
+}
+
+extern "C" int32_t b2q_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,
+                                const float* scale_a, int scale_a_kind, const float* scale_w, int scale_w_kind, void* out,
+                                int out_type) {
+  B2Q_REQUIRE_HANDLE(h);
+  int32_t st = b2q_validate_gemm_fp8(h, a, w, M, N, K, fmt, scale_a, scale_a_kind, scale_w, scale_w_kind, out, out_type);
+  if (st != B2Q_OK) return st;
+  b2q_tile_config t; int kid = 0;
+  b2q_select_tile(0, (uint32_t)M, (uint32_t)N, (uint32_t)K, &t, &kid);
+  const bool tma_ok = K % 16 == 0 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
+  if (kid == 0 || !tma_ok)
+    return b2q_gemm_fp8_simt(h, a, w, M, N, K, fmt, /*IEEE decode, as the tensor core*/ 1, scale_a, scale_a_kind, scale_w,
+                             scale_w_kind, out, out_type);
+  tc::Params p{};
+  p.M = M; p.N = N; p.K = K;
+  p.scale_a = scale_a; p.scale_a_rows = scale_a_kind; p.scale_w = scale_w; p.scale_w_rows = scale_w_kind;
+  p.out = out; p.out_type = out_type; p.status = h->d_status;
+  p.idesc = ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10);   // A/B format: 0 = E4M3, 1 = E5M2
+  return kid == 1 ? tc::launch<256, tc::kF8>(h, a, w, p) : tc::launch<128, tc::kF8>(h, a, w, p);
+}

@@ -1,0 +1,259 @@
+// Block-scaled FP4 (E2M1) weight-only decode GEMV, tokens <= 32 (HBM-bound):
+//   out[t, n] = sum_k x[t, k] * decode(codes[n, k]) * scale[n, k / 32]
+//
+// Work decomposition
+//   * a CTA owns R = 16 * WARPS consecutive weight rows and one K slice; a thread-block
+//     cluster of `split_k` CTAs covers the whole K of those rows and reduces the
+//     partial sums through distributed shared memory (no global scratch, no atomics);
+//   * a warp owns 16 weight rows.  Per 128-wide K step every lane issues two 128-bit
+//     streaming loads (row g and row g+8, 32 codes = one scale block each), so a warp
+//     instruction covers 8 rows x 64 contiguous bytes;
+//   * codes are expanded in registers: cvt.rn.f16x2.e2m1x2 (one instruction per byte)
+//     and one HMUL2 by the block scale, which directly yields the A fragments of
+//     mma.sync.m16n8k16 (the K order inside an MMA is permuted consistently for A and B);
+//   * activations are converted bf16 -> f16 once per 512-wide K chunk and staged in
+//     shared memory in fragment order, so B fragments are conflict-free 128-bit loads;
+//   * fp32 accumulation in the MMA; bf16 (RNE) or f32 store.
+// f16 is used because E2M1 -> f16x2 is a single hardware conversion; activations
+// beyond +-65504 saturate and block scales outside [2^-24, 2^15] are not representable.
+#include "common.cuh"
+#include <cooperative_groups.h>
+
+namespace cg = cooperative_groups;
+
+namespace gemv {
+
+constexpr int KC = 512;   // K elements per staged activation chunk (4 steps of 128)
+
+__device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  return r;
+}
+
+// Four bytes (eight E2M1 codes) -> four f16x2 registers; low nibble is the low half.
+__device__ __forceinline__ void cvt_e2m1x8(uint32_t w, uint32_t (&h)[4]) {
+  asm volatile(
+      "{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+      : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3]) : "r"(w));
+}
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2_sat(uint32_t v) {
+  float lo = __uint_as_float(v << 16), hi = __uint_as_float(v & 0xFFFF0000u);
+  lo = fminf(fmaxf(lo, -65504.0f), 65504.0f);
+  hi = fminf(fmaxf(hi, -65504.0f), 65504.0f);
+  __half2 h = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t scale_to_h2(float s) {
+  __half2 h = __float2half2_rn(s);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// MT: token tiles of 8 (tokens padded to 8*MT).  WARPS: warps per CTA (16 rows each).
+template <int MT, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32) gemv_fp4_kernel(const uint8_t* __restrict__ codes, const float* __restrict__ scales_f32,
+                                                              const uint8_t* __restrict__ scales_e8m0,
+                                                              const __nv_bfloat16* __restrict__ x, int tokens, int64_t N, int64_t K,
+                                                              void* out, int out_type, int split_k) {
+  constexpr int MPAD = 8 * MT;
+  constexpr int R = 16 * WARPS;
+  constexpr int NT = WARPS * 32;
+  extern __shared__ __align__(16) uint8_t smem[];        // activation chunk, later the partial sums
+  uint4* xs = reinterpret_cast<uint4*>(smem);            // [step 4][jj 4][MPAD][tig 4] x 16 bytes
+  float* red = reinterpret_cast<float*>(smem);           // [MPAD][R]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, tig = lane & 3;
+  const int ks = blockIdx.x % split_k;
+  const int64_t row_tile = blockIdx.x / split_k;
+  const int64_t n0 = row_tile * R + warp * 16;
+  // clamp so that loads stay in bounds; rows >= N are dropped at the store
+  const int64_t r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);
+  const int64_t kblocks = K >> 5;                        // scale blocks per row
+  const uint8_t* w0 = codes + r0 * (K >> 1);
+  const uint8_t* w1 = codes + r1 * (K >> 1);
+
+  const int chunks_total = (int)((K + KC - 1) / KC);
+  const int cpc = (chunks_total + split_k - 1) / split_k;
+  const int c_begin = ks * cpc, c_end = min(c_begin + cpc, chunks_total);
+
+  float acc[MT][4];
+#pragma unroll
+  for (int t = 0; t < MT; ++t) { acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.0f; }
+
+  for (int c = c_begin; c < c_end; ++c) {
+    const int64_t k0 = (int64_t)c * KC;
+    // ---- issue this chunk's weight and scale loads first (they are the long-latency HBM stream) ----
+    uint4 wa[4], wb[4];
+    uint32_t sa[4], sb[4];
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      const int64_t k = k0 + s * 128 + tig * 32;
+      if (k < K) {
+        wa[s] = ld_stream_v4(w0 + (k >> 1));
+        wb[s] = ld_stream_v4(w1 + (k >> 1));
+        const int64_t kb = k >> 5;
+        float fa, fb;
+        if (scales_e8m0) {
+          fa = e8m0_to_f32_dev(__ldg(scales_e8m0 + r0 * kblocks + kb));
+          fb = e8m0_to_f32_dev(__ldg(scales_e8m0 + r1 * kblocks + kb));
+        } else {
+          fa = __ldg(scales_f32 + r0 * kblocks + kb);
+          fb = __ldg(scales_f32 + r1 * kblocks + kb);
+        }
+        sa[s] = scale_to_h2(fa);
+        sb[s] = scale_to_h2(fb);
+      } else {
+        wa[s] = make_uint4(0, 0, 0, 0);
+        wb[s] = make_uint4(0, 0, 0, 0);
+        sa[s] = sb[s] = 0;
+      }
+    }
+    // ---- stage activations of this chunk: bf16 -> f16, fragment order ----
+    __syncthreads();                                     // previous chunk's readers are done
+    for (int i = threadIdx.x; i < 16 * MPAD; i += NT) {
+      const int ttig = i & 3, tok = (i >> 2) % MPAD, step = i / (4 * MPAD);
+      const int64_t k = k0 + step * 128 + ttig * 32;
+      const bool live = tok < tokens && k < K;
+      const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)tok * K + k);
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        uint4 v = live ? __ldg(src + jj) : make_uint4(0, 0, 0, 0);
+        uint4 h;
+        h.x = bf16x2_to_f16x2_sat(v.x); h.y = bf16x2_to_f16x2_sat(v.y);
+        h.z = bf16x2_to_f16x2_sat(v.z); h.w = bf16x2_to_f16x2_sat(v.w);
+        xs[((step * 4 + jj) * MPAD + tok) * 4 + ttig] = h;
+      }
+    }
+    __syncthreads();
+    // ---- expand codes and multiply ----
+#pragma unroll
+    for (int s = 0; s < 4; ++s) {
+      const uint32_t wav[4] = {wa[s].x, wa[s].y, wa[s].z, wa[s].w};
+      const uint32_t wbv[4] = {wb[s].x, wb[s].y, wb[s].z, wb[s].w};
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {                   // 8 codes per row = two MMA k-steps
+        uint32_t ha[4], hb[4];
+        cvt_e2m1x8(wav[jj], ha);
+        cvt_e2m1x8(wbv[jj], hb);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { ha[i] = hmul2_u32(ha[i], sa[s]); hb[i] = hmul2_u32(hb[i], sb[s]); }
+#pragma unroll
+        for (int t = 0; t < MT; ++t) {
+          const uint4 xv = xs[((s * 4 + jj) * MPAD + (t * 8 + g)) * 4 + tig];
+          mma_f16(acc[t], ha[0], hb[0], ha[1], hb[1], xv.x, xv.y);
+          mma_f16(acc[t], ha[2], hb[2], ha[3], hb[3], xv.z, xv.w);
+        }
+      }
+    }
+  }
+
+  // ---- partial sums to shared memory: red[token][row within the CTA] ----
+  __syncthreads();
+#pragma unroll
+  for (int t = 0; t < MT; ++t) {
+    const int tok = t * 8 + tig * 2;
+    red[(tok + 0) * R + warp * 16 + g] = acc[t][0];
+    red[(tok + 1) * R + warp * 16 + g] = acc[t][1];
+    red[(tok + 0) * R + warp * 16 + g + 8] = acc[t][2];
+    red[(tok + 1) * R + warp * 16 + g + 8] = acc[t][3];
+  }
+  cg::cluster_group cluster = cg::this_cluster();
+  if (split_k > 1) cluster.sync(); else __syncthreads();
+  // ---- each CTA of the cluster reduces and stores its share of the [MPAD x R] tile ----
+  const int E = MPAD * R;
+  const int per = (E + split_k - 1) / split_k;
+  const int e_begin = ks * per, e_end = min(e_begin + per, E);
+  for (int e = e_begin + threadIdx.x; e < e_end; e += NT) {
+    float v = 0.0f;
+    if (split_k > 1) {
+      for (int pr = 0; pr < split_k; ++pr) v += cluster.map_shared_rank(red, pr)[e];
+    } else {
+      v = red[e];
+    }
+    const int tok = e / R;
+    const int64_t n = row_tile * R + (e % R);
+    if (tok < tokens && n < N) {
+      if (out_type == B2Q_OUT_BF16) reinterpret_cast<__nv_bfloat16*>(out)[(int64_t)tok * N + n] = __float2bfloat16_rn(v);
+      else reinterpret_cast<float*>(out)[(int64_t)tok * N + n] = v;
+    }
+  }
+  if (split_k > 1) cluster.sync();                       // peers may still be reading this CTA's partials
+}
+
+template <int MT, int WARPS>
+int32_t launch(b2q_handle h, const uint8_t* codes, const void* scales, int scale_format, const void* x, int tokens, int64_t N,
+               int64_t K, void* out, int out_type) {
+  constexpr int R = 16 * WARPS;
+  const int64_t row_tiles = ceil_div64(N, R);
+  const int chunks = (int)ceil_div64(K, KC);
+  // K split: enough CTAs for ~2 per SM, a divisor-friendly cluster size of at most 8
+  int split = 1;
+  while (split < 8 && row_tiles * split < 2 * (int64_t)h->sm_count && split * 2 <= chunks) split *= 2;
+  if (chunks % split != 0) {                             // prefer an even split when one exists nearby
+    for (int s = split; s >= 1; --s) if (chunks % s == 0 && s * 2 > split) { split = s; break; }
+    if (chunks == 28 && row_tiles * 7 >= (int64_t)h->sm_count) split = 7;
+  }
+  if (chunks % 7 == 0 && split == 4 && row_tiles * 7 <= 3 * (int64_t)h->sm_count) split = 7;
+  const size_t smem = (size_t)1024 * 8 * MT > (size_t)8 * MT * R * 4 ? (size_t)1024 * 8 * MT : (size_t)8 * MT * R * 4;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(row_tiles * split));
+  cfg.blockDim = dim3(WARPS * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = h->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)split;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const float* sf = scale_format == B2Q_SCALE_F32 ? (const float*)scales : nullptr;
+  const uint8_t* se = scale_format == B2Q_SCALE_E8M0 ? (const uint8_t*)scales : nullptr;
+  B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, gemv_fp4_kernel<MT, WARPS>, codes, sf, se, (const __nv_bfloat16*)x, tokens, N, K, out,
+                                 out_type, split));
+  return B2Q_OK;
+}
+
+}  // namespace gemv
+
+extern "C" int32_t b2q_gemv_fp4_wo(b2q_handle h, const uint8_t* codes, const void* scales, int scale_format, int block,
+                                   const void* x_bf16, int64_t tokens, int64_t N, int64_t K, void* out, int out_type) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (tokens <= 0 || N <= 0 || K <= 0)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "FP4 GEMM dimensions must be non-zero: m=%lld, n=%lld, k=%lld", (long long)N, (long long)tokens, (long long)K);
+  if (K % 2 != 0) B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "FP4 GEMM K dimension must be even for packing, got k=%lld", (long long)K);
+  if (block != 32 && block != 64 && block != 128)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "MicroScaling block_size must be one of [32, 64, 128], got %d", block);
+  if (block != 32) B2Q_FAIL(h, B2Q_ERR_UNSUPPORTED, "gemv_fp4_wo: only 32-element scale blocks are implemented");
+  if (tokens > 32) B2Q_FAIL(h, B2Q_ERR_UNSUPPORTED, "gemv_fp4_wo: decode path takes at most 32 tokens, got %lld", (long long)tokens);
+  if (K % 128 != 0) B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "gemv_fp4_wo: K must be a multiple of 128, got %lld", (long long)K);
+  if (!codes || !scales || !x_bf16 || !out || scale_format < 0 || scale_format > 1 || out_type < 0 || out_type > 1)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemv_fp4_wo: bad argument");
+  if (((reinterpret_cast<uintptr_t>(codes) | reinterpret_cast<uintptr_t>(x_bf16)) & 15) != 0)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemv_fp4_wo: codes and activations must be 16-byte aligned");
+  const int t = (int)tokens;
+  const bool small_n = N <= 2048;
+  if (t <= 8) return small_n ? gemv::launch<1, 4>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type)
+                             : gemv::launch<1, 8>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type);
+  if (t <= 16) return small_n ? gemv::launch<2, 4>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type)
+                              : gemv::launch<2, 8>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type);
+  return small_n ? gemv::launch<4, 4>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type)
+                 : gemv::launch<4, 8>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type);
+}

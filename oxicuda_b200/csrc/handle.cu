@@ -1,0 +1,159 @@
+// Handle lifetime, status word and the host-side tile heuristics of libb2q.
+#include "common.cuh"
+
+extern "C" {
+
+int32_t b2q_create(b2q_handle* out, int device) {
+  if (!out) return B2Q_ERR_INVALID_ARGUMENT;
+  *out = nullptr;
+  int count = 0;
+  if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0) return B2Q_ERR_CUDA;  // no CPU fallback
+  if (device < 0 || device >= count) return B2Q_ERR_INVALID_ARGUMENT;
+  b2q_handle h = new b2q_handle_s();
+  memset(h, 0, sizeof(*h));
+  h->device = device;
+  cudaDeviceProp prop;
+  if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
+    delete h;
+    return B2Q_ERR_CUDA;
+  }
+  h->sm = prop.major * 10 + prop.minor;
+  h->sm_count = prop.multiProcessorCount;
+  if (h->sm != 100) {  // the kernels are built for sm_100a only
+    delete h;
+    return B2Q_ERR_UNSUPPORTED;
+  }
+  if (cudaMalloc(&h->d_status, sizeof(int32_t)) != cudaSuccess ||
+      cudaMalloc(&h->d_scratch, kScratchWords * sizeof(uint32_t)) != cudaSuccess ||
+      cudaMemset(h->d_status, 0, sizeof(int32_t)) != cudaSuccess ||
+      cudaMemset(h->d_scratch, 0, kScratchWords * sizeof(uint32_t)) != cudaSuccess) {
+    cudaFree(h->d_status);
+    cudaFree(h->d_scratch);
+    delete h;
+    return B2Q_ERR_CUDA;
+  }
+  h->stream = nullptr;
+  *out = h;
+  return B2Q_OK;
+}
+
+int32_t b2q_destroy(b2q_handle h) {
+  if (!h) return B2Q_OK;
+  cudaSetDevice(h->device);
+  cudaFree(h->d_status);
+  cudaFree(h->d_scratch);
+  delete h;
+  return B2Q_OK;
+}
+
+int32_t b2q_set_stream(b2q_handle h, void* stream) {
+  B2Q_REQUIRE_HANDLE(h);
+  h->stream = (cudaStream_t)stream;
+  return B2Q_OK;
+}
+
+int32_t b2q_get_sm(b2q_handle h, int* sm) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (!sm) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "b2q_get_sm: null output");
+  *sm = h->sm;
+  return B2Q_OK;
+}
+
+int32_t b2q_get_sm_count(b2q_handle h, int* count) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (!count) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "b2q_get_sm_count: null output");
+  *count = h->sm_count;
+  return B2Q_OK;
+}
+
+const char* b2q_last_error(b2q_handle h) { return h ? h->err : "null handle"; }
+
+int32_t b2q_check(b2q_handle h) {
+  B2Q_REQUIRE_HANDLE(h);
+  int32_t st = 0;
+  B2Q_CUDA(h, cudaMemcpyAsync(&st, h->d_status, sizeof(st), cudaMemcpyDeviceToHost, h->stream));
+  B2Q_CUDA(h, cudaStreamSynchronize(h->stream));
+  if (st != 0) {
+    B2Q_CUDA(h, cudaMemsetAsync(h->d_status, 0, sizeof(int32_t), h->stream));
+    B2Q_CUDA(h, cudaStreamSynchronize(h->stream));
+    B2Q_FAIL(h, st, "device-side validation recorded status %d", (int)st);
+  }
+  return B2Q_OK;
+}
+
+// ---------------------------------------------------------------------------
+// Tile heuristics (pure host functions)
+// ---------------------------------------------------------------------------
+int32_t b2q_classify_workload(uint32_t m, uint32_t n, uint32_t k) {
+  uint64_t mn = (uint64_t)m * (uint64_t)n;
+  if (mn < 8192) return 0;               // SmallSquare
+  if (m < 128 && n >= 128) return 2;     // SkinnyM
+  if (n < 128 && m >= 128) return 3;     // SkinnyN
+  if (k < 64) return 4;                  // SkinnyK
+  if (m >= 1024 && n >= 1024) return 1;  // LargeSquare
+  return 5;                              // General
+}
+
+int32_t b2q_ref_tile_config(int dtype, uint32_t m, uint32_t n, uint32_t k, b2q_tile_config* out) {
+  if (!out || dtype < 0 || dtype > 2) return B2Q_ERR_INVALID_ARGUMENT;
+  if (m == 0 || n == 0 || k == 0) return B2Q_ERR_INVALID_DIMENSION;
+  if (dtype == 2) {  // Int8GemmConfig::tile_config, Sm100 arm
+    *out = b2q_tile_config{128, 128, 64, 64, 64, 4, 1, 1};
+    return B2Q_OK;
+  }
+  const uint32_t stages = k < 64 ? 2u : 4u;
+  b2q_tile_config t{0, 0, 128, 0, 0, stages, 1, 1};
+  switch (b2q_classify_workload(m, n, k)) {
+    case 0: t.tile_m = 64; t.tile_n = 64; t.tile_k = 64; t.warp_m = 32; t.warp_n = 32; break;
+    case 2: t.tile_m = 64; t.tile_n = 256; t.warp_m = 32; t.warp_n = 128; break;
+    case 3: t.tile_m = 256; t.tile_n = 64; t.warp_m = 128; t.warp_n = 32; break;
+    case 1: t.tile_m = 256; t.tile_n = 256; t.warp_m = 64; t.warp_n = 128; break;
+    case 4:
+      t.tile_m = 256; t.tile_n = 256; t.warp_m = 64; t.warp_n = 128; t.stages = 2;
+      if (dtype == 1) t.tile_k = 64;
+      break;
+    default:
+      t.tile_m = dtype == 1 ? 128u : 256u; t.tile_n = 256; t.warp_m = 64; t.warp_n = 128;
+      break;
+  }
+  *out = t;
+  return B2Q_OK;
+}
+
+uint32_t b2q_fp8_compute_split_k(uint32_t m, uint32_t n, uint32_t k) {
+  if (m * n < 2048 && k > 32768) {
+    uint32_t f = k / 8192;
+    return f < 2 ? 2 : (f > 64 ? 64 : f);
+  }
+  return 1;
+}
+
+// The static per-shape table: which kernel family and CTA tile each (dtype, shape)
+// dispatches to.  dtype 0 fp8, 1 fp4 (weight-only), 2 int8.
+int32_t b2q_select_tile(int dtype, uint32_t m, uint32_t n, uint32_t k, b2q_tile_config* out, int* kernel_id) {
+  if (!out || !kernel_id || dtype < 0 || dtype > 2) return B2Q_ERR_INVALID_ARGUMENT;
+  if (m == 0 || n == 0 || k == 0) return B2Q_ERR_INVALID_DIMENSION;
+  if (dtype == 1) {  // FP4 weight-only: warp-level mma GEMV, 16 output rows per warp
+    uint32_t rows = n <= 2048 ? 64u : 128u;
+    *out = b2q_tile_config{m <= 8 ? 8u : (m <= 16 ? 16u : 32u), rows, 512, 8, 16, 1, 1, 1};
+    *kernel_id = 3;
+    return B2Q_OK;
+  }
+  if (m < 64 || k % 16 != 0) {  // decode-sized or TMA-incompatible pitch: SIMT path
+    *out = b2q_tile_config{16, 16, 16, 16, 16, 1, 0, 1};
+    *kernel_id = 0;
+    return B2Q_OK;
+  }
+  // tcgen05: one 128-row accumulator per CTA; the wide tile when it wastes no wave
+  const uint32_t tm = (m + 127) / 128;
+  const uint32_t t256 = tm * ((n + 255) / 256), t128 = tm * ((n + 127) / 128);
+  const uint32_t sms = 148;
+  const double eff256 = (double)t256 / (double)(((t256 + sms - 1) / sms) * sms);
+  const double eff128 = (double)t128 / (double)(((t128 + sms - 1) / sms) * sms) * 0.92;  // N=128 MMAs run below peak
+  const bool wide = n >= 256 && eff256 >= eff128;
+  *out = b2q_tile_config{128, wide ? 256u : 128u, 128, 128, wide ? 256u : 128u, wide ? 4u : 6u, 1, 1};
+  *kernel_id = wide ? 1 : 2;
+  return B2Q_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,651 @@
+// Quantize / dequantize kernels (HBM-bound byte and integer work): MinMax INT-N,
+// FP8 codec + absmax-scaled FP8, block-scaled FP4, NF4, INT8 scalar-scale and the
+// dist-infer INT8-in-u8 flavour.  All kernels are grid-stride, 128-bit vectorised
+// where the pointers allow it, and launched on the handle's stream.
+#include "common.cuh"
+
+namespace {
+
+constexpr int kThreads = 256;
+
+inline int grid_for(const b2q_handle h, int64_t work_items, int per_block) {
+  int64_t g = ceil_div64(work_items, per_block);
+  int64_t cap = (int64_t)h->sm_count * 16;
+  if (g > cap) g = cap;
+  if (g < 1) g = 1;
+  return (int)g;
+}
+
+template <typename T> __device__ __forceinline__ float load_as_f32(const T* p, int64_t i);
+template <> __device__ __forceinline__ float load_as_f32<float>(const float* p, int64_t i) { return p[i]; }
+template <> __device__ __forceinline__ float load_as_f32<__nv_bfloat16>(const __nv_bfloat16* p, int64_t i) {
+  return __bfloat162float(p[i]);
+}
+
+// ---------------------------------------------------------------------------
+// Row statistics.  One warp per row (rows of any length, good up to a few
+// thousand columns) or several blocks per row with ordered-key atomics in the
+// handle scratch (long rows, e.g. per-tensor over millions of elements).
+// NaN never wins a comparison, exactly like the reference's `<` / `>` scan and
+// f32::max.  `nonfinite` (optional) is set when an Inf/NaN is seen.
+// ---------------------------------------------------------------------------
+struct RowStat { float fmin, fmax, amax; int bad; };
+
+template <typename T>
+__device__ __forceinline__ RowStat scan_segment(const T* row, int64_t begin, int64_t end, int lane, int stride) {
+  RowStat s{__uint_as_float(0x7F800000u), __uint_as_float(0xFF800000u), 0.0f, 0};
+  for (int64_t i = begin + lane; i < end; i += stride) {
+    float v = load_as_f32<T>(row, i);
+    if (v < s.fmin) s.fmin = v;
+    if (v > s.fmax) s.fmax = v;
+    s.amax = fmaxf(s.amax, fabsf(v));
+    s.bad |= !isfinite(v);
+  }
+  return s;
+}
+
+// Specialisation with float4 loads for f32 rows whose start is 16-byte aligned.
+__device__ __forceinline__ RowStat scan_segment_f4(const float* row, int64_t n, int lane, int stride) {
+  RowStat s{__uint_as_float(0x7F800000u), __uint_as_float(0xFF800000u), 0.0f, 0};
+  const float4* r4 = reinterpret_cast<const float4*>(row);
+  int64_t n4 = n >> 2;
+  for (int64_t i = lane; i < n4; i += stride) {
+    float4 q = r4[i];
+    float vv[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float v = vv[j];
+      if (v < s.fmin) s.fmin = v;
+      if (v > s.fmax) s.fmax = v;
+      s.amax = fmaxf(s.amax, fabsf(v));
+      s.bad |= !isfinite(v);
+    }
+  }
+  for (int64_t i = (n4 << 2) + lane; i < n; i += stride) {
+    float v = row[i];
+    if (v < s.fmin) s.fmin = v;
+    if (v > s.fmax) s.fmax = v;
+    s.amax = fmaxf(s.amax, fabsf(v));
+    s.bad |= !isfinite(v);
+  }
+  return s;
+}
+
+__device__ __forceinline__ RowStat warp_reduce_stat(RowStat s) {
+  s.fmin = warp_min(s.fmin);
+  s.fmax = warp_max(s.fmax);
+  s.amax = warp_max(s.amax);
+  s.bad = __any_sync(0xffffffffu, s.bad) ? 1 : 0;
+  return s;
+}
+
+// What to do with a finished row statistic.
+enum StatMode { kMinMaxParams = 0, kFp8Scale = 1, kAbsmaxOnly = 2 };
+struct StatArgs {
+  int mode;
+  int bits, scheme;        // kMinMaxParams
+  float max_val;           // kFp8Scale
+  float* scales;           // per-row output (scale or absmax)
+  int32_t* zps;            // kMinMaxParams
+  int32_t* status;
+  int flag_nonfinite;      // record B2Q_ERR_NON_FINITE_FP8 when an Inf/NaN was scanned
+};
+
+__device__ __forceinline__ void finish_row(const StatArgs& a, int64_t r, RowStat s) {
+  if (a.flag_nonfinite && s.bad) atomicCAS(a.status, 0, (int)B2Q_ERR_NON_FINITE_FP8);
+  if (a.mode == kMinMaxParams) {
+    float scale; int32_t zp;
+    if (a.scheme == 0) {
+      float q_max = (float)(1 << (a.bits - 1)) - 1.0f;
+      float abs_max = fmaxf(fmaxf(fabsf(s.fmin), fabsf(s.fmax)), 1e-8f);
+      scale = __fdiv_rn(abs_max, q_max);
+      zp = 0;
+    } else {
+      float q_range = (float)((1 << a.bits) - 1);
+      float range = fmaxf(__fsub_rn(s.fmax, s.fmin), 1e-8f);
+      scale = __fdiv_rn(range, q_range);
+      float z = roundf(__fdiv_rn(-s.fmin, scale));
+      z = z < 0.0f ? 0.0f : (z > q_range ? q_range : z);   // f32::clamp keeps NaN
+      zp = isnan(z) ? 0 : (int32_t)z;
+    }
+    if (!isfinite(scale) || scale <= 0.0f) atomicCAS(a.status, 0, (int)B2Q_ERR_INVALID_SCALE);
+    a.scales[r] = scale;
+    a.zps[r] = zp;
+  } else if (a.mode == kFp8Scale) {
+    a.scales[r] = s.amax > 0.0f ? __fdiv_rn(s.amax, a.max_val) : 1.0f;
+  } else {
+    a.scales[r] = s.amax;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) row_stat_warp_kernel(const T* x, int64_t rows, int64_t cols, StatArgs a) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * (kThreads / 32);
+  for (int64_t r = warp; r < rows; r += nwarps) {
+    const T* row = x + r * cols;
+    RowStat s;
+    if (sizeof(T) == 4 && ((reinterpret_cast<uintptr_t>(row) & 15) == 0))
+      s = scan_segment_f4(reinterpret_cast<const float*>(row), cols, lane, 32);
+    else
+      s = scan_segment<T>(row, 0, cols, lane, 32);
+    s = warp_reduce_stat(s);
+    if (lane == 0) finish_row(a, r, s);
+  }
+}
+
+// keys: [rows][4] = {min key, max key, absmax bits, bad flag}
+__global__ void stat_keys_init_kernel(uint32_t* keys, int64_t rows) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < rows) {
+    keys[4 * i + 0] = 0xFFFFFFFFu;
+    keys[4 * i + 1] = 0u;
+    keys[4 * i + 2] = 0u;
+    keys[4 * i + 3] = 0u;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads) row_stat_split_kernel(const T* x, int64_t cols, int64_t seg, uint32_t* keys) {
+  const int64_t r = blockIdx.y;
+  const int64_t begin = (int64_t)blockIdx.x * seg;
+  const int64_t end = begin + seg < cols ? begin + seg : cols;
+  const T* row = x + r * cols;
+  RowStat s;
+  if (sizeof(T) == 4 && ((reinterpret_cast<uintptr_t>(row + begin) & 15) == 0) && begin < end)
+    s = scan_segment_f4(reinterpret_cast<const float*>(row + begin), end - begin, threadIdx.x, kThreads);
+  else
+    s = scan_segment<T>(row, begin, end, threadIdx.x, kThreads);
+  s = warp_reduce_stat(s);
+  __shared__ RowStat sh[kThreads / 32];
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < kThreads / 32; ++w) {
+      s.fmin = fminf(s.fmin, sh[w].fmin);
+      s.fmax = fmaxf(s.fmax, sh[w].fmax);
+      s.amax = fmaxf(s.amax, sh[w].amax);
+      s.bad |= sh[w].bad;
+    }
+    atomicMin(&keys[4 * r + 0], float_order_key(s.fmin));
+    atomicMax(&keys[4 * r + 1], float_order_key(s.fmax));
+    atomicMax(&keys[4 * r + 2], __float_as_uint(s.amax));
+    if (s.bad) atomicOr(&keys[4 * r + 3], 1u);
+  }
+}
+
+__global__ void stat_keys_finish_kernel(const uint32_t* keys, int64_t rows, StatArgs a) {
+  int64_t r = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (r < rows) {
+    RowStat s{float_from_order_key(keys[4 * r + 0]), float_from_order_key(keys[4 * r + 1]),
+              __uint_as_float(keys[4 * r + 2]), (int)keys[4 * r + 3]};
+    finish_row(a, r, s);
+  }
+}
+
+template <typename T>
+int32_t launch_row_stats(b2q_handle h, const T* x, int64_t rows, int64_t cols, const StatArgs& a) {
+  const bool split = cols >= (1 << 15) && rows * 4 <= (int64_t)kScratchWords && rows <= 65535;
+  if (!split) {
+    int grid = grid_for(h, rows, kThreads / 32);
+    row_stat_warp_kernel<T><<<grid, kThreads, 0, h->stream>>>(x, rows, cols, a);
+    B2Q_LAUNCH_CHECK(h, "row_stat_warp_kernel");
+    return B2Q_OK;
+  }
+  int64_t want_blocks = (int64_t)h->sm_count * 8;
+  int64_t bpr = ceil_div64(want_blocks, rows);
+  int64_t seg = ceil_div64(cols, bpr);
+  seg = ceil_div64(seg, 4 * kThreads) * 4 * kThreads;     // keeps segment starts 16-byte aligned
+  bpr = ceil_div64(cols, seg);
+  stat_keys_init_kernel<<<(int)ceil_div64(rows, 256), 256, 0, h->stream>>>(h->d_scratch, rows);
+  row_stat_split_kernel<T><<<dim3((unsigned)bpr, (unsigned)rows), kThreads, 0, h->stream>>>(x, cols, seg, h->d_scratch);
+  stat_keys_finish_kernel<<<(int)ceil_div64(rows, 256), 256, 0, h->stream>>>(h->d_scratch, rows, a);
+  B2Q_LAUNCH_CHECK(h, "row_stat_split_kernel");
+  return B2Q_OK;
+}
+
+// ---------------------------------------------------------------------------
+// MinMax quantize / dequantize / fake-quant
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) minmax_quantize_kernel(const float* x, int64_t n, int64_t cols,
+                                                                   const float* scales, const int32_t* zps,
+                                                                   float q_min, float q_max, int32_t* codes) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t r = i / cols;
+    float t = roundf(__fadd_rn(__fdiv_rn(x[i], scales[r]), (float)zps[r]));
+    t = t < q_min ? q_min : (t > q_max ? q_max : t);
+    codes[i] = isnan(t) ? 0 : (int32_t)t;
+  }
+}
+__global__ void __launch_bounds__(kThreads) minmax_dequantize_kernel(const int32_t* codes, int64_t n, int64_t cols,
+                                                                     const float* scales, const int32_t* zps, float* out) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t r = i / cols;
+    int32_t d = (int32_t)((uint32_t)codes[i] - (uint32_t)zps[r]);
+    out[i] = __fmul_rn((float)d, scales[r]);
+  }
+}
+__global__ void __launch_bounds__(kThreads) fake_quant_kernel(float* x, int64_t n, float scale, float zp, float qmin, float qmax) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    float q = roundf(__fadd_rn(__fdiv_rn(x[i], scale), zp));
+    q = q < qmin ? qmin : (q > qmax ? qmax : q);
+    x[i] = __fmul_rn(__fsub_rn(q, zp), scale);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// FP8 encode / decode
+// ---------------------------------------------------------------------------
+// SCALED: divide by scales[row] first.  Four elements per thread when aligned.
+template <typename T, bool SCALED>
+__global__ void __launch_bounds__(kThreads) fp8_encode_kernel(const T* x, int64_t n, int64_t cols, const float* scales,
+                                                              int fmt, int rounding, uint8_t* codes, int32_t* status,
+                                                              int vec_ok) {
+  const Fp8Fmt F = fp8_fmt(fmt);
+  auto enc1 = [&](float v, int64_t idx) -> uint32_t {
+    if (!isfinite(v)) { atomicCAS(status, 0, (int)B2Q_ERR_NON_FINITE_FP8); }
+    if (SCALED) v = __fdiv_rn(v, scales[idx / cols]);
+    v = v < -F.max_val ? -F.max_val : (v > F.max_val ? F.max_val : v);
+    return rounding == 0 ? fp8_encode_ref_dev(v, F) : fp8_encode_rne_dev(v, fmt);
+  };
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nth = (int64_t)gridDim.x * blockDim.x;
+  if (vec_ok) {
+    const int64_t n4 = n >> 2;
+    for (int64_t i = tid; i < n4; i += nth) {
+      float v[4];
+      if (sizeof(T) == 4) {
+        float4 q = reinterpret_cast<const float4*>(x)[i];
+        v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+      } else {
+        uint2 q = reinterpret_cast<const uint2*>(x)[i];
+        v[0] = __uint_as_float(q.x << 16); v[1] = __uint_as_float(q.x & 0xFFFF0000u);
+        v[2] = __uint_as_float(q.y << 16); v[3] = __uint_as_float(q.y & 0xFFFF0000u);
+      }
+      uint32_t w = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w |= enc1(v[j], 4 * i + j) << (8 * j);
+      reinterpret_cast<uint32_t*>(codes)[i] = w;
+    }
+    for (int64_t i = (n4 << 2) + tid; i < n; i += nth) codes[i] = (uint8_t)enc1(load_as_f32<T>(x, i), i);
+  } else {
+    for (int64_t i = tid; i < n; i += nth) codes[i] = (uint8_t)enc1(load_as_f32<T>(x, i), i);
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) fp8_decode_kernel(const uint8_t* codes, int64_t n, int fmt, int mode, float* out) {
+  __shared__ float lut[256];
+  const Fp8Fmt F = fp8_fmt(fmt);
+  for (int i = threadIdx.x; i < 256; i += blockDim.x)
+    lut[i] = mode == 0 ? fp8_decode_ref_dev((uint32_t)i, F) : fp8_decode_ieee_dev((uint32_t)i, F);
+  __syncthreads();
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nth = (int64_t)gridDim.x * blockDim.x;
+  const bool vec = ((reinterpret_cast<uintptr_t>(codes) & 3) == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+  if (vec) {
+    const int64_t n4 = n >> 2;
+    for (int64_t i = tid; i < n4; i += nth) {
+      uint32_t w = reinterpret_cast<const uint32_t*>(codes)[i];
+      reinterpret_cast<float4*>(out)[i] =
+          make_float4(lut[w & 0xFF], lut[(w >> 8) & 0xFF], lut[(w >> 16) & 0xFF], lut[w >> 24]);
+    }
+    for (int64_t i = (n4 << 2) + tid; i < n; i += nth) out[i] = lut[codes[i]];
+  } else {
+    for (int64_t i = tid; i < n; i += nth) out[i] = lut[codes[i]];
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Block-scaled FP4.  block/4 lanes cooperate on one block: each lane loads one
+// float4, the absmax is reduced with xor-shuffles inside the lane group, and each
+// lane emits two bytes (four codes).  A warp therefore reads 512 contiguous bytes
+// per instruction and writes 64.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) fp4_block_quantize_kernel(const float* x, int64_t n, int block, int format,
+                                                                      int scale_format, uint8_t* packed,
+                                                                      float* scales_f32, uint8_t* scales_e8m0) {
+  const int lanes = block >> 2;                               // 8, 16 or 32
+  const float target = format == 0 ? 6.0f : 8.0f;
+  const int64_t n4 = n >> 2;                                  // n is a multiple of block
+  const int64_t span = (int64_t)gridDim.x * blockDim.x;
+  // every lane of a warp runs the same number of iterations (n4 is a multiple of `lanes`, span of 32)
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < ((n4 + 31) & ~(int64_t)31); i += span) {
+    const bool live = i < n4;
+    float4 q = live ? reinterpret_cast<const float4*>(x)[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    float amax = fmaxf(fmaxf(fabsf(q.x), fabsf(q.y)), fmaxf(fabsf(q.z), fabsf(q.w)));
+    for (int o = lanes >> 1; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    float scale;
+    uint32_t eb = 127;
+    if (scale_format == 0) scale = amax == 0.0f ? 1.0f : __fdiv_rn(amax, target);
+    else { eb = e8m0_from_absmax_dev(amax); scale = e8m0_to_f32_dev(eb); }
+    if (live) {
+      float v[4] = {q.x, q.y, q.z, q.w};
+      uint32_t c[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float s = __fdiv_rn(v[j], scale);
+        c[j] = format == 0 ? e2m1_encode_ref_dev(s) : int4_encode_ref_dev(s);
+      }
+      reinterpret_cast<uint16_t*>(packed)[i] = (uint16_t)(c[0] | (c[1] << 4) | (c[2] << 8) | (c[3] << 12));
+      if ((i % lanes) == 0) {
+        int64_t b = i / lanes;
+        if (scale_format == 0) scales_f32[b] = scale; else scales_e8m0[b] = (uint8_t)eb;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kThreads) fp4_block_dequantize_kernel(const uint8_t* packed, int64_t n, int block,
+                                                                        int format, int scale_format,
+                                                                        const float* scales_f32,
+                                                                        const uint8_t* scales_e8m0, float* out) {
+  const int64_t n4 = n >> 2;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+    uint32_t w = reinterpret_cast<const uint16_t*>(packed)[i];
+    int64_t b = (4 * i) / block;
+    float scale = scale_format == 0 ? scales_f32[b] : e8m0_to_f32_dev(scales_e8m0[b]);
+    float r[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t c = (w >> (4 * j)) & 0xF;
+      r[j] = __fmul_rn(format == 0 ? e2m1_decode_dev(c) : int4_decode_dev(c), scale);
+    }
+    reinterpret_cast<float4*>(out)[i] = make_float4(r[0], r[1], r[2], r[3]);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// NF4
+// ---------------------------------------------------------------------------
+__constant__ float kNf4Lut[16] = {
+    -1.0f, -0.69619286f, -0.52507305f, -0.3949175f, -0.28444138f, -0.18477343f, -0.09105003f, 0.0f,
+    0.0795803f, 0.1609302f, 0.2461123f, 0.33791524f, 0.44070983f, 0.562617f, 0.72295684f, 1.0f};
+
+__global__ void __launch_bounds__(kThreads) nf4_decode_kernel(const uint8_t* packed, int64_t nbytes, int block,
+                                                              const float* absmaxs, float* out) {
+  __shared__ float lut[16];
+  if (threadIdx.x < 16) lut[threadIdx.x] = kNf4Lut[threadIdx.x];
+  __syncthreads();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nbytes; i += (int64_t)gridDim.x * blockDim.x) {
+    uint32_t b = packed[i];
+    float amax = absmaxs[(2 * i) / block];
+    reinterpret_cast<float2*>(out)[i] = make_float2(__fmul_rn(lut[b & 0xF], amax), __fmul_rn(lut[b >> 4], amax));
+  }
+}
+
+__device__ __forceinline__ uint32_t nearest_nf4_dev(const float* lut, float v) {
+  int lo = 0, hi = 16;
+  while (lo < hi) {
+    int mid = lo + (hi - lo) / 2;
+    if (lut[mid] < v) lo = mid + 1; else hi = mid;
+  }
+  if (lo == 0) return 0;
+  if (lo == 16) return 15;
+  float d_lo = fabsf(__fsub_rn(v, lut[lo - 1]));
+  float d_hi = fabsf(__fsub_rn(lut[lo], v));
+  return d_lo <= d_hi ? lo - 1 : lo;
+}
+
+// one warp per block of `block` (even) elements
+__global__ void __launch_bounds__(kThreads) nf4_encode_kernel(const float* x, int64_t nblocks, int block, uint8_t* packed,
+                                                              float* absmaxs) {
+  __shared__ float lut[16];
+  if (threadIdx.x < 16) lut[threadIdx.x] = kNf4Lut[threadIdx.x];
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * (kThreads / 32);
+  for (int64_t b = warp; b < nblocks; b += nwarps) {
+    const float* s = x + b * block;
+    float amax = 0.0f;
+    for (int i = lane; i < block; i += 32) amax = fmaxf(amax, fabsf(s[i]));
+    amax = warp_max(amax);
+    if (amax < 1e-8f) amax = 1e-8f;
+    if (lane == 0) absmaxs[b] = amax;
+    for (int p = lane; p < block / 2; p += 32) {
+      float a = __fdiv_rn(s[2 * p], amax), c = __fdiv_rn(s[2 * p + 1], amax);
+      a = a < -1.0f ? -1.0f : (a > 1.0f ? 1.0f : a);
+      c = c < -1.0f ? -1.0f : (c > 1.0f ? 1.0f : c);
+      packed[b * (block / 2) + p] = (uint8_t)(nearest_nf4_dev(lut, a) | (nearest_nf4_dev(lut, c) << 4));
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// INT8 with a scalar scale (quant: ties-to-even as cvt.rni, clamp +-127)
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) int8_quant_kernel(const float* x, int64_t n, float scale, int8_t* out) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    float t = rintf(__fdiv_rn(x[i], scale));
+    t = fminf(fmaxf(t, -127.0f), 127.0f);
+    out[i] = (int8_t)(int)t;
+  }
+}
+__global__ void __launch_bounds__(kThreads) int8_dequant_kernel(const int8_t* q, int64_t n, float scale, float* out) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    out[i] = __fmul_rn((float)q[i], scale);
+}
+
+// ---------------------------------------------------------------------------
+// dist-infer INT8-in-u8 ("fp8_infer"): q = round(clamp(v*(127/absmax), +-127)) as i8 as u8
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads) distfp8_quantize_kernel(const float* x, int64_t n, int64_t block,
+                                                                    const float* absmaxs, uint8_t* q) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    float amax = absmaxs[i / block];
+    if (amax == 0.0f) { q[i] = 0; continue; }
+    float scale = __fdiv_rn(127.0f, amax);
+    float t = __fmul_rn(x[i], scale);
+    t = t < -127.0f ? -127.0f : (t > 127.0f ? 127.0f : t);
+    t = roundf(t);
+    q[i] = (uint8_t)(int8_t)(isnan(t) ? 0 : (int)t);
+  }
+}
+__global__ void __launch_bounds__(kThreads) distfp8_dequantize_kernel(const uint8_t* q, int64_t n, int64_t block,
+                                                                      const float* absmaxs, float* out) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    out[i] = __fmul_rn((float)(int8_t)q[i], __fdiv_rn(absmaxs[i / block], 127.0f));
+}
+
+template <typename T>
+int32_t fp8_quantize_rows_impl(b2q_handle h, const T* x, int64_t rows, int64_t cols, int fmt, int rounding,
+                               float* scales, uint8_t* codes) {
+  if (rows <= 0 || cols <= 0) B2Q_FAIL(h, B2Q_ERR_EMPTY_INPUT, "fp8_quantize_rows: empty input");
+  if (!x || !scales || !codes) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "fp8_quantize_rows: null pointer");
+  if (fmt < 0 || fmt > 1 || rounding < 0 || rounding > 1) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "fp8_quantize_rows: bad format/rounding");
+  StatArgs a{kFp8Scale, 0, 0, fp8_fmt(fmt).max_val, scales, nullptr, h->d_status, 1};
+  int32_t st = launch_row_stats<T>(h, x, rows, cols, a);
+  if (st != B2Q_OK) return st;
+  const int64_t n = rows * cols;
+  const int vec_ok = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((reinterpret_cast<uintptr_t>(codes) & 3) == 0);
+  fp8_encode_kernel<T, true><<<grid_for(h, n, kThreads * 4), kThreads, 0, h->stream>>>(
+      x, n, cols, scales, fmt, rounding, codes, h->d_status, vec_ok);
+  B2Q_LAUNCH_CHECK(h, "fp8_encode_kernel");
+  return B2Q_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+int32_t b2q_minmax_calibrate_f32(b2q_handle h, const float* x, int64_t rows, int64_t cols, int bits, int scheme,
+                                 float* scales, int32_t* zero_points) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (rows <= 0) B2Q_FAIL(h, B2Q_ERR_EMPTY_INPUT, "minmax_calibrate: rows == 0");
+  if (cols <= 0) B2Q_FAIL(h, B2Q_ERR_DIMENSION_MISMATCH, "minmax_calibrate: cols == 0");
+  if (bits < 1 || bits > 16) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "bits must be in [1, 16]");
+  if (scheme < 0 || scheme > 1 || !x || !scales || !zero_points) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "minmax_calibrate: bad argument");
+  StatArgs a{kMinMaxParams, bits, scheme, 0.0f, scales, zero_points, h->d_status, 0};
+  return launch_row_stats<float>(h, x, rows, cols, a);
+}
+
+int32_t b2q_minmax_quantize_f32(b2q_handle h, const float* x, int64_t rows, int64_t cols, const float* scales,
+                                const int32_t* zero_points, int bits, int scheme, int32_t* codes) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (rows <= 0 || cols <= 0) B2Q_FAIL(h, B2Q_ERR_EMPTY_INPUT, "minmax_quantize: empty input");
+  if (bits < 1 || bits > 16 || scheme < 0 || scheme > 1 || !x || !scales || !zero_points || !codes)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "minmax_quantize: bad argument");
+  float q_max = scheme == 0 ? (float)(1 << (bits - 1)) - 1.0f : (float)(1 << bits) - 1.0f;
+  float q_min = scheme == 0 ? -(float)(1 << (bits - 1)) : 0.0f;
+  int64_t n = rows * cols;
+  minmax_quantize_kernel<<<grid_for(h, n, kThreads), kThreads, 0, h->stream>>>(x, n, cols, scales, zero_points, q_min, q_max, codes);
+  B2Q_LAUNCH_CHECK(h, "minmax_quantize_kernel");
+  return B2Q_OK;
+}
+
+int32_t b2q_minmax_dequantize_f32(b2q_handle h, const int32_t* codes, int64_t rows, int64_t cols, const float* scales,
+                                  const int32_t* zero_points, float* out) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (rows <= 0 || cols <= 0) B2Q_FAIL(h, B2Q_ERR_EMPTY_INPUT, "minmax_dequantize: empty input");
+  if (!codes || !scales || !zero_points || !out) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "minmax_dequantize: null pointer");
+  int64_t n = rows * cols;
+  minmax_dequantize_kernel<<<grid_for(h, n, kThreads), kThreads, 0, h->stream>>>(codes, n, cols, scales, zero_points, out);
+  B2Q_LAUNCH_CHECK(h, "minmax_dequantize_kernel");
+  return B2Q_OK;
+}
+
+int32_t b2q_fake_quant_inplace_f32(b2q_handle h, float* x, int64_t n, float scale, float zero_point, float qmin, float qmax) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (n <= 0) B2Q_FAIL(h, B2Q_ERR_EMPTY_INPUT, "fake_quant: empty input");
+  if (!(scale > 0.0f) || !isfinite(scale)) B2Q_FAIL(h, B2Q_ERR_INVALID_SCALE, "fake_quant: scale %g", (double)scale);
+  if (!x) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "fake_quant: null pointer");
+  fake_quant_kernel<<<grid_for(h, n, kThreads), kThreads, 0, h->stream>>>(x, n, scale, zero_point, qmin, qmax);
+  B2Q_LAUNCH_CHECK(h, "fake_quant_kernel");
+  return B2Q_OK;
+}
+
+int32_t b2q_fp8_encode_f32(b2q_handle h, const float* x, int64_t n, int fmt, int rounding, uint8_t* codes) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (n == 0) return B2Q_OK;  // encode of an empty slice is an empty Vec
+  if (n < 0 || !x || !codes || fmt < 0 || fmt > 1 || rounding < 0 || rounding > 1)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "fp8_encode: bad argument");
+  const int vec_ok = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((reinterpret_cast<uintptr_t>(codes) & 3) == 0);
+  fp8_encode_kernel<float, false><<<grid_for(h, n, kThreads * 4), kThreads, 0, h->stream>>>(
+      x, n, 1, nullptr, fmt, rounding, codes, h->d_status, vec_ok);
+  B2Q_LAUNCH_CHECK(h, "fp8_encode_kernel");
+  return B2Q_OK;
+}
+
+int32_t b2q_fp8_decode_f32(b2q_handle h, const uint8_t* codes, int64_t n, int fmt, int rounding, float* out) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (n == 0) return B2Q_OK;
+  if (n < 0 || !codes || !out || fmt < 0 || fmt > 1 || rounding < 0 || rounding > 1)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "fp8_decode: bad argument");
+  fp8_decode_kernel<<<grid_for(h, n, kThreads * 4), kThreads, 0, h->stream>>>(codes, n, fmt, rounding, out);
+  B2Q_LAUNCH_CHECK(h, "fp8_decode_kernel");
+  return B2Q_OK;
+}
+
+int32_t b2q_fp8_quantize_rows_f32(b2q_handle h, const float* x, int64_t rows, int64_t cols, int fmt, int rounding,
+                                  float* scales, uint8_t* codes) {
+  B2Q_REQUIRE_HANDLE(h);
+  return fp8_quantize_rows_impl<float>(h, x, rows, cols, fmt, rounding, scales, codes);
+}
+int32_t b2q_fp8_quantize_rows_bf16(b2q_handle h, const void* x, int64_t rows, int64_t cols, int fmt, int rounding,
+                                   float* scales, uint8_t* codes) {
+  B2Q_REQUIRE_HANDLE(h);
+  return fp8_quantize_rows_impl<__nv_bfloat16>(h, (const __nv_bfloat16*)x, rows, cols, fmt, rounding, scales, codes);
+}
+
+int32_t b2q_fp4_block_quantize_f32(b2q_handle h, const float* x, int64_t n, int block, int format, int scale_format,
+                                   uint8_t* packed, void* scales) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (block != 32 && block != 64 && block != 128)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "MicroScaling block_size must be one of [32, 64, 128], got %d", block);
+  if (n <= 0) return B2Q_OK;
+  if (n % block != 0) B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "fp4_block_quantize: n=%lld is not a multiple of block=%d", (long long)n, block);
+  if (!x || !packed || !scales || format < 0 || format > 1 || scale_format < 0 || scale_format > 1)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "fp4_block_quantize: bad argument");
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(packed) & 1))
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "fp4_block_quantize: x must be 16-byte and packed 2-byte aligned");
+  fp4_block_quantize_kernel<<<grid_for(h, n / 4, kThreads), kThreads, 0, h->stream>>>(
+      x, n, block, format, scale_format, packed, (float*)scales, (uint8_t*)scales);
+  B2Q_LAUNCH_CHECK(h, "fp4_block_quantize_kernel");
+  return B2Q_OK;
+}
+
+int32_t b2q_fp4_block_dequantize_f32(b2q_handle h, const uint8_t* packed, int64_t n, int block, int format,
+                                     int scale_format, const void* scales, float* out) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (block != 32 && block != 64 && block != 128)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "MicroScaling block_size must be one of [32, 64, 128], got %d", block);
+  if (n <= 0) return B2Q_OK;
+  if (n % block != 0) B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "fp4_block_dequantize: n=%lld is not a multiple of block=%d", (long long)n, block);
+  if (!packed || !scales || !out || format < 0 || format > 1 || scale_format < 0 || scale_format > 1)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "fp4_block_dequantize: bad argument");
+  if ((reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(packed) & 1))
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "fp4_block_dequantize: out must be 16-byte and packed 2-byte aligned");
+  fp4_block_dequantize_kernel<<<grid_for(h, n / 4, kThreads), kThreads, 0, h->stream>>>(
+      packed, n, block, format, scale_format, (const float*)scales, (const uint8_t*)scales, out);
+  B2Q_LAUNCH_CHECK(h, "fp4_block_dequantize_kernel");
+  return B2Q_OK;
+}
+
+int32_t b2q_nf4_decode_f32(b2q_handle h, const uint8_t* packed, int64_t nbytes, int block, const float* absmaxs, float* out) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (block <= 0 || block % 2 != 0) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "nf4: block must be positive and even");
+  if (nbytes <= 0) return B2Q_OK;
+  if ((2 * nbytes) % block != 0) B2Q_FAIL(h, B2Q_ERR_DIMENSION_MISMATCH, "nf4_decode: packed length inconsistent with block");
+  if (!packed || !absmaxs || !out || (reinterpret_cast<uintptr_t>(out) & 7)) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "nf4_decode: bad pointer");
+  nf4_decode_kernel<<<grid_for(h, nbytes, kThreads), kThreads, 0, h->stream>>>(packed, nbytes, block, absmaxs, out);
+  B2Q_LAUNCH_CHECK(h, "nf4_decode_kernel");
+  return B2Q_OK;
+}
+
+int32_t b2q_nf4_encode_f32(b2q_handle h, const float* x, int64_t n, int block, uint8_t* packed, float* absmaxs) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (n <= 0) B2Q_FAIL(h, B2Q_ERR_EMPTY_INPUT, "Nf4Quantizer::encode: empty input");
+  if (block <= 0 || block % 2 != 0) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "nf4: block must be positive and even");
+  if (n % block != 0) B2Q_FAIL(h, B2Q_ERR_GROUP_SIZE_MISMATCH, "nf4_encode: len %lld not divisible by group %d", (long long)n, block);
+  if (!x || !packed || !absmaxs) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "nf4_encode: null pointer");
+  int64_t nblocks = n / block;
+  nf4_encode_kernel<<<grid_for(h, nblocks, kThreads / 32), kThreads, 0, h->stream>>>(x, nblocks, block, packed, absmaxs);
+  B2Q_LAUNCH_CHECK(h, "nf4_encode_kernel");
+  return B2Q_OK;
+}
+
+int32_t b2q_int8_quant_f32(b2q_handle h, const float* x, int64_t n, float scale, int8_t* out) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (n <= 0) return B2Q_OK;
+  if (!(scale > 0.0f) || !isfinite(scale)) B2Q_FAIL(h, B2Q_ERR_INVALID_SCALE, "int8_quant: scale %g", (double)scale);
+  if (!x || !out) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "int8_quant: null pointer");
+  int8_quant_kernel<<<grid_for(h, n, kThreads), kThreads, 0, h->stream>>>(x, n, scale, out);
+  B2Q_LAUNCH_CHECK(h, "int8_quant_kernel");
+  return B2Q_OK;
+}
+int32_t b2q_int8_dequant_f32(b2q_handle h, const int8_t* q, int64_t n, float scale, float* out) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (n <= 0) return B2Q_OK;
+  if (!q || !out) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "int8_dequant: null pointer");
+  int8_dequant_kernel<<<grid_for(h, n, kThreads), kThreads, 0, h->stream>>>(q, n, scale, out);
+  B2Q_LAUNCH_CHECK(h, "int8_dequant_kernel");
+  return B2Q_OK;
+}
+
+int32_t b2q_distfp8_quantize_block_f32(b2q_handle h, const float* x, int64_t n, int64_t block, uint8_t* q, float* absmaxs) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (n <= 0) return B2Q_OK;
+  if (!x || !q || !absmaxs) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "distfp8_quantize: null pointer");
+  if (block < 1) block = 1;
+  if (block > n) block = n;
+  if (n % block != 0) B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "distfp8_quantize: device path needs n %% block == 0");
+  StatArgs a{kAbsmaxOnly, 0, 0, 0.0f, absmaxs, nullptr, h->d_status, 0};
+  int32_t st = launch_row_stats<float>(h, x, n / block, block, a);
+  if (st != B2Q_OK) return st;
+  distfp8_quantize_kernel<<<grid_for(h, n, kThreads), kThreads, 0, h->stream>>>(x, n, block, absmaxs, q);
+  B2Q_LAUNCH_CHECK(h, "distfp8_quantize_kernel");
+  return B2Q_OK;
+}
+int32_t b2q_distfp8_dequantize_block_f32(b2q_handle h, const uint8_t* q, int64_t n, int64_t block, const float* absmaxs, float* out) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (n <= 0) return B2Q_OK;
+  if (!q || !absmaxs || !out) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "distfp8_dequantize: null pointer");
+  if (block < 1) block = 1;
+  if (block > n) block = n;
+  distfp8_dequantize_kernel<<<grid_for(h, n, kThreads), kThreads, 0, h->stream>>>(q, n, block, absmaxs, out);
+  B2Q_LAUNCH_CHECK(h, "distfp8_dequantize_kernel");
+  return B2Q_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,151 @@
+"""Writes tests/golden/reference_kat.json: the known-answer vectors that the
+reference's own unit tests hold for the quantized-linear path.
+
+The reference is a Rust workspace and no Rust toolchain exists where this
+repository is built, so the reference cannot be executed to produce fixtures.
+Every entry below is transcribed from an assertion of a reference test (the
+`src` field gives file:line inside the reference repository); the oracle
+(oracle/oracle.cpp) and the CUDA path are both checked against this file.
+Inputs produced by a helper of the reference's tests (the LCG of
+crates/oxicuda-quant/src/scheme/llm_int8.rs:320-332) are regenerated here with
+the same integer recurrence.
+
+Run:  python tests/golden/make_reference_kat.py
+"""
+from __future__ import annotations
+
+import json
+from pathlib import Path
+
+import numpy as np
+
+
+def lcg(n: int, seed: int, scale: float):
+    """crates/oxicuda-quant/src/scheme/llm_int8.rs:320-332 (u64 wrapping LCG, top 32 bits -> [-scale, scale])."""
+    state = seed
+    out = []
+    for _ in range(n):
+        state = (state * 6364136223846793005 + 1442695040888963407) & 0xFFFFFFFFFFFFFFFF
+        bits = np.uint32(state >> 32)
+        f = np.float32(bits) / np.float32(np.uint32(0xFFFFFFFF))       # (bits as f32) / (u32::MAX as f32)
+        out.append(float((f * np.float32(2.0) - np.float32(1.0)) * np.float32(scale)))
+    return out
+
+
+KAT = {
+    "minmax": {
+        "symmetric_calibrate_scale": {"src": "crates/oxicuda-quant/src/scheme/minmax.rs:341-348",
+                                      "x": [-2.0, -1.0, 0.5, 2.0], "bits": 8, "scheme": 0,
+                                      "scale": 2.0 / 127.0, "eps": 1e-6, "zp": 0},
+        "asymmetric_calibrate_scale_zp": {"src": "crates/oxicuda-quant/src/scheme/minmax.rs:351-359",
+                                          "x": [0.0, 1.0, 2.0, 3.0], "bits": 8, "scheme": 1,
+                                          "scale": 3.0 / 255.0, "eps": 1e-5, "zp": 0},
+        "per_group_calibrate": {"src": "crates/oxicuda-quant/src/scheme/minmax.rs:362-367",
+                                "x": [-1.0, 0.0, 0.5, 1.0, -2.0, 0.0, 1.0, 2.0], "bits": 4, "group": 4, "n_scales": 2},
+        "symmetric_round_trip_low_error": {"src": "crates/oxicuda-quant/src/scheme/minmax.rs:370-384",
+                                           "n": 128, "bits": 8, "max_err": 0.02},
+        "grouped_round_trip": {"src": "crates/oxicuda-quant/src/scheme/minmax.rs:387-403",
+                               "n": 64, "step": 0.1, "bits": 4, "group": 16, "max_err": 0.5},
+        "q_max_q_min_int8": {"src": "crates/oxicuda-quant/src/scheme/minmax.rs:423-428", "q_max": 127.0, "q_min": -128.0},
+        "calibrate_2d_per_row": {"src": "crates/oxicuda-quant/src/scheme/minmax.rs:431-443",
+                                 "x": [0.0, 1.0, -1.0, 0.5, 0.0, 2.0, -2.0, 1.5], "rows": 2, "cols": 4},
+    },
+    "fp8_codec": {
+        "e4m3_zero": {"src": "crates/oxicuda-quant/src/scheme/fp8.rs:288-292", "x": [0.0, -0.0], "codes": [0x00, 0x80]},
+        "e4m3_round_trip_basic": {"src": "crates/oxicuda-quant/src/scheme/fp8.rs:295-303",
+                                  "x": [1.0, -1.0, 2.0, 0.5, 0.25, -0.25], "rel_err": 0.15},
+        "e5m2_round_trip_basic": {"src": "crates/oxicuda-quant/src/scheme/fp8.rs:306-314",
+                                  "x": [1.0, -1.0, 4.0, 16.0, -8.0], "rel_err": 0.25},
+        "e4m3_saturates_large_values": {"src": "crates/oxicuda-quant/src/scheme/fp8.rs:317-324", "x": 1000.0, "max": 449.0},
+        "nan_input_errors": {"src": "crates/oxicuda-quant/src/scheme/fp8.rs:327-340", "x": ["nan", "inf"]},
+        "mse_within_tolerance": {"src": "crates/oxicuda-quant/src/scheme/fp8.rs:343-350", "n": 256, "mse": 0.01},
+        "type_decode": {"src": "crates/oxicuda-blas/src/types.rs:792-816",
+                        "e4m3": {"0x38": 1.0, "0x40": 2.0, "0x00": 0.0}, "e5m2": {"0x3C": 1.0, "0x40": 2.0, "0x00": 0.0}},
+    },
+    "fp8_rne": {
+        "e4m3_encode_known_patterns": {"src": "crates/oxicuda-dnn/src/quantize/fp8_quantize.rs:996-1010",
+                                       "x": [1.0, 2.0, 0.5, -1.0, 448.0, 0.0, 1.75],
+                                       "codes": [0x38, 0x40, 0x30, 0xB8, 0x7E, 0x00, 0x3E]},
+        "e4m3_subnormal_boundary": {"src": "crates/oxicuda-dnn/src/quantize/fp8_quantize.rs:1098-1111",
+                                    "x": [7.5 / 512.0], "codes_low7": [0x08]},
+        "e4m3_flush_to_zero": {"src": "crates/oxicuda-dnn/src/quantize/fp8_quantize.rs:1114-1121",
+                               "x": [2.0 ** -11, 1e-10, -1e-10], "codes": [0x00, 0x00, 0x80]},
+        "e4m3_saturation": {"src": "crates/oxicuda-dnn/src/quantize/fp8_quantize.rs:1124-1140",
+                            "x": [448.0, -448.0], "codes": [0x7E, 0xFE], "decode_0x7E": 448.0},
+        "e4m3_round_to_nearest_even": {"src": "crates/oxicuda-dnn/src/quantize/fp8_quantize.rs:1143-1160",
+                                       "x": [1.0 + 0.5 / 8.0, 1.0 + 1.5 / 8.0], "mantissa": [0, 2]},
+    },
+    "fp4": {
+        "packed_fp4_roundtrip": {"src": "crates/oxicuda-blas/src/precision/fp4_fp6_ops/tests.rs:28-43", "pair": [0, 15]},
+        "packed_fp4_overflow_rejected": {"src": "crates/oxicuda-blas/src/precision/fp4_fp6_ops/tests.rs:46-49",
+                                         "bad": [[16, 0], [0, 16]]},
+        "fp4_e2m1_roundtrip_accuracy": {"src": "crates/oxicuda-blas/src/precision/fp4_fp6_ops/tests.rs:95-111",
+                                        "x": [0.0, 1.0, -1.0, 2.0, -2.0, 4.0, -4.0, 6.0], "tol_rel": 0.6, "tol_abs": 0.01},
+        "fp4_int4_roundtrip": {"src": "crates/oxicuda-blas/src/precision/fp4_fp6_ops/tests.rs:114-128",
+                               "x": [0.0, 1.0, -1.0, 7.0, -8.0, 3.0, -5.0, 2.0], "tol_abs": 0.5},
+        "block_size_validation": {"src": "crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:205-214", "valid": [32, 64, 128],
+                                  "invalid": [0, 16, 48, 256]},
+        "block_scale_rules": {"src": "crates/oxicuda-dnn/src/quantize/block_scale.rs:528-582",
+                              "cases": [{"fill": 0.0, "scale": 1.0}, {"fill": 6.0, "scale": 1.0}, {"fill": 12.0, "scale": 2.0}],
+                              "num_scales": {"32": 1, "96": 3, "33": 2}},
+    },
+    "tiles": {
+        "classify_workload": {"src": "crates/oxicuda-blas/src/precision/fp8_ops.rs:462-529",
+                              "cases": [[64, 64, 256, "SmallSquare"], [32, 128, 512, "SmallSquare"],
+                                        [1024, 1024, 512, "LargeSquare"], [4096, 4096, 4096, "LargeSquare"],
+                                        [64, 512, 256, "SkinnyM"], [512, 64, 256, "SkinnyN"], [256, 256, 32, "SkinnyK"],
+                                        [256, 512, 128, "General"], [1, 1, 1, "SmallSquare"], [1, 16384, 256, "SkinnyM"],
+                                        [16384, 1, 256, "SkinnyN"]]},
+        "fp8_blackwell_large_square": {"src": "crates/oxicuda-blas/src/precision/fp8_ops.rs:563-568",
+                                       "mnk": [2048, 2048, 2048], "tile_m": 256, "tile_n": 256, "stages": 4},
+        "fp8_blackwell_skinny_m": {"src": "crates/oxicuda-blas/src/precision/fp8_ops.rs:595-599",
+                                   "mnk": [1, 16384, 256], "tile_m": 64, "tile_n": 256},
+        "fp4_tile_blackwell_skinny_m": {"src": "crates/oxicuda-blas/src/precision/fp4_fp6_ops/tests.rs:186-191",
+                                        "mnk": [64, 512, 256], "tile_m": 64, "tile_n": 256},
+        "fp4_tile_blackwell_large": {"src": "crates/oxicuda-blas/src/precision/fp4_fp6_ops/tests.rs:194-200",
+                                     "mnk": [4096, 4096, 4096], "tile_m": 256, "tile_n": 256, "tile_k": 128},
+        "int8_tile_hopper_plus": {"src": "crates/oxicuda-blas/src/precision/int_ops.rs:861-874", "tile_k": 64, "stages": 4},
+        "int8_k_multiple_of_4": {"src": "crates/oxicuda-blas/src/precision/int_ops.rs:814-827", "bad_k": 33},
+    },
+    "llm_int8": {
+        "detects_outlier_column": {"src": "crates/oxicuda-quant/src/scheme/llm_int8.rs:364-371",
+                                   "x": None, "samples": 4, "cols": 5, "outliers": [2]},
+        "no_outliers_when_below_threshold": {"src": "crates/oxicuda-quant/src/scheme/llm_int8.rs:374-379",
+                                             "x": lcg(20, 2, 1.0), "samples": 4, "cols": 5, "outliers": []},
+        "matmul_matches_fp32_when_no_outliers": {"src": "crates/oxicuda-quant/src/scheme/llm_int8.rs:393-408",
+                                                 "x": lcg(6 * 8, 10, 1.0), "w": lcg(4 * 8, 20, 0.5),
+                                                 "samples": 6, "rows": 4, "cols": 8, "rmse_frac": 0.05},
+        "outlier_fraction_reported": {"src": "crates/oxicuda-quant/src/scheme/llm_int8.rs:461-472",
+                                      "x": None, "w": lcg(3 * 10, 60, 0.5), "samples": 4, "rows": 3, "cols": 10,
+                                      "fraction": 0.2},
+        "config_validation": {"src": "crates/oxicuda-quant/src/scheme/llm_int8.rs:353-359", "bad": [-1.0, 0.0, "nan"], "ok": [6.0]},
+    },
+    "distfp8": {
+        "zero_quantizes_to_zero": {"src": "crates/oxicuda-dist-infer/src/quantisation/fp8_infer.rs:201-207", "x": [0.0], "q": [0]},
+        "block_scales_shape": {"src": "crates/oxicuda-dist-infer/src/quantisation/fp8_infer.rs:210-216", "n": 8, "block": 4, "n_scales": 2},
+        "max_quantized_value_is_127": {"src": "crates/oxicuda-dist-infer/src/quantisation/fp8_infer.rs:246-253", "x": [1000.0], "q": [127]},
+        "negative_packs_as_twos_complement": {"src": "crates/oxicuda-dist-infer/src/quantisation/fp8_infer.rs:256-264", "x": [-1.0], "q": [0x81]},
+        "block_all_zeros_scale_is_zero": {"src": "crates/oxicuda-dist-infer/src/quantisation/fp8_infer.rs:266-273",
+                                          "x": [0.0, 0.0, 0.0, 0.0, 1.0, -1.0, 0.5, -0.5], "block": 4},
+    },
+    "tensor_parallel": {
+        "ring_all_reduce_sum": {"src": "crates/oxicuda-dist-infer/src/lib.rs:368-389",
+                                "ranks": [[1.0, 2.0, 3.0, 4.0], [10.0, 20.0, 30.0, 40.0], [100.0, 200.0, 300.0, 400.0],
+                                          [1000.0, 2000.0, 3000.0, 4000.0]], "sum": [1111.0, 2222.0, 3333.0, 4444.0]},
+    },
+}
+
+# inputs that the reference tests build by patching the LCG stream
+_x = lcg(4 * 5, 1, 1.0)
+_x[2] = 9.0
+KAT["llm_int8"]["detects_outlier_column"]["x"] = _x
+_x = lcg(4 * 10, 50, 1.0)
+_x[1] = 20.0
+_x[5] = 20.0
+KAT["llm_int8"]["outlier_fraction_reported"]["x"] = _x
+
+
+if __name__ == "__main__":
+    out = Path(__file__).resolve().parent / "reference_kat.json"
+    out.write_text(json.dumps(KAT, indent=1))
+    print(f"wrote {out} ({out.stat().st_size} bytes)")
