@@ -1,0 +1,371 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-linear hot path on B200.
+
+Headline workload (N=1): FP8 E4M3 GEMM M=N=K=4096, per-tensor scales, fp32 accumulate, bf16 out — the
+configuration the metric "quantized GEMM TFLOPS ... % roofline" is quoted on.  With N>1 ranks every rank
+owns a 4096-row column-parallel shard of the weight (out_features = 4096*N, activations replicated), so
+per-GPU work is fixed ("weak") and the path needs no collective.
+
+One "step" = one pass of the GEMM over one batch of activations.  Prints ONE JSON line (rank 0).
+`--impl reference` times the CPU restatement of the reference's own arithmetic (oracle/) instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+M = N = K = 4096
+FLOP_PER_STEP = 2.0 * M * N * K
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.t = threading.Thread(target=self._read, daemon=True)
+            self.t.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for nm, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def cpu_sample(threads: int | None = None, size: int = 1024, repeats: int = 1):
+    """Times the oracle's FP8 GEMM (Fp8Codec decode + k-ascending fp32 FMA, the reference's arithmetic)
+    on a size^3 sub-problem of the workload; returns (TFLOP/s, cores, description)."""
+    import numpy as np
+    from oracle import api
+    if threads:
+        api.set_threads(threads)
+    cores = api.num_threads()
+    rng = np.random.default_rng(1)
+    a = rng.integers(0, 0x7E, (size, size)).astype(np.uint8)
+    w = rng.integers(0, 0x7E, (size, size)).astype(np.uint8)
+    one = np.ones(1, np.float32)
+    api.gemm_fp8(a[:64], w[:64], one, one, 0, 0, "bf16")          # page in, spin up the thread pool
+    t0 = time.perf_counter()
+    for _ in range(repeats):
+        api.gemm_fp8(a, w, one, one, 0, 0, "bf16")
+    dt = (time.perf_counter() - t0) / repeats
+    return 2.0 * size ** 3 / dt / 1e12, cores, f"{size}x{size}x{size} sub-problem of the 4096^3 GEMM, {repeats} pass(es), {dt:.2f} s each"
+
+
+def run_reference(args, rank: int):
+    """CPU arm: the reference's own arithmetic for this path on the host cores (rank 0 only)."""
+    if rank != 0:
+        return
+    vals = []
+    desc = ""
+    for _ in range(args.warmup if args.warmup < 2 else 1):
+        cpu_sample(size=512)
+    t_start = time.perf_counter()
+    steps = 0
+    for _ in range(args.steps):
+        v, cores, desc = cpu_sample(size=1024)
+        vals.append(v)
+        steps += 1
+        if time.perf_counter() - t_start > 150:            # keep the whole arm within a few minutes
+            break
+    value = statistics.median(vals)
+    line = {
+        "impl": "reference", "metric": "fp8_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": steps, "warmup": args.warmup, "ms_per_step": FLOP_PER_STEP / (value * 1e12) * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+        "config": {"workload": "fp8_e4m3_gemm_m4096_n4096_k4096_bf16out", "m": M, "n": N, "k": K,
+                   "note": "CPU restatement of the reference's arithmetic (Fp8Codec decode + k-ascending fp32 FMA); "
+                           "ms_per_step is the full 4096^3 step extrapolated from the timed sample"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b2q", choices=["b2q", "reference"])
+    ap.add_argument("--rounding", default="rne", choices=["rne", "ref"], help="E4M3 encoder used to make the operands")
+    ap.add_argument("--no-extras", action="store_true", help="skip the GEMV / INT8 side measurements")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch
+    import torch.distributed as dist
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the CUDA kernels have no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    from oxicuda_b200 import _build
+    if rank == 0:
+        _build.build()
+    if world > 1:
+        dist.barrier()
+    from oxicuda_b200.blas import gemm_fp8, select_tile
+    from oxicuda_b200.quant import Fp8Codec
+
+    peaks = load_peaks()
+    warmup = max(args.warmup, 3)
+    codec = Fp8Codec.e4m3(args.rounding)
+
+    # ---- operands: SETS rotating (A, W shard, C) triples so that successive steps do not hit in L2 ----
+    SETS = 4                                              # 4 x 64 MiB = 256 MiB > 126 MB L2
+    g = torch.Generator(device=dev).manual_seed(0xB2000001 + rank)
+    sets = []
+    for _ in range(SETS):
+        a = torch.randn(M, K, device=dev, generator=g)
+        w = torch.randn(N, K, device=dev, generator=g) * 0.02      # this rank's 4096 output rows of W[4096*world x 4096]
+        ac, sa = codec.quantize_rows(a, 1, M * K)
+        wc, sw = codec.quantize_rows(w, 1, N * K)
+        sets.append((ac.view(M, K), wc.view(N, K), sa, sw, torch.empty(M, N, dtype=torch.bfloat16, device=dev)))
+        del a, w
+    torch.cuda.synchronize()
+
+    def step(i):
+        ac, wc, sa, sw, out = sets[i % SETS]
+        gemm_fp8(ac, wc, sa, sw, out=out)
+
+    for i in range(warmup):
+        step(i)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.25)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    ms_per_step = ms / args.steps
+    value = FLOP_PER_STEP * world / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end to end through the public call with HOST buffers: H2D activations, GEMM, D2H result ----
+    ac, wc, sa, sw, out = sets[0]
+    h_a = torch.empty(M, K, dtype=torch.uint8).pin_memory()
+    h_a.copy_(ac.cpu())
+    h_sa = sa.cpu().pin_memory()
+    h_out = torch.empty(M, N, dtype=torch.bfloat16).pin_memory()
+    d_a = torch.empty_like(ac)
+    d_sa = torch.empty_like(sa)
+    e2e_steps = max(3, min(args.steps, 20))
+
+    def e2e_step():
+        d_a.copy_(h_a, non_blocking=True)
+        d_sa.copy_(h_sa, non_blocking=True)
+        gemm_fp8(d_a, wc, d_sa, sw, out=out)
+        h_out.copy_(out, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = FLOP_PER_STEP * world / (e2e_ms / e2e_steps * 1e-3) / 1e12
+    clocks = sampler.stop() if rank == 0 else None
+
+    extras = {}
+    if rank == 0 and not args.no_extras:
+        try:
+            extras = side_measurements(dev, peaks)
+        except Exception as exc:                       # side numbers never block the headline line
+            extras = {"error": repr(exc)}
+
+    if rank == 0:
+        tile, kid = select_tile("fp8", M, N, K)
+        kernel_tflops = FLOP_PER_STEP / (ms_per_step * 1e-3) / 1e12
+        fp8_peak = 2.0 * peaks["bf16_tflops"]
+        cpu = None
+        if world == 1:
+            v, cores, desc = cpu_sample(size=1024, repeats=1)
+            cpu = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc}
+        prof = ROOT / "profiles" / "gemm_tc_fp8_4096_traffic.json"
+        traffic = json.loads(prof.read_text()).get("dram_bytes_per_launch") if prof.exists() else None
+        line = {
+            "metric": "fp8_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic",
+            "config": {"workload": "fp8_e4m3_gemm_m4096_n4096_k4096_bf16out", "m": M, "n": N, "k": K,
+                       "scales": "per-tensor absmax/448", "encoder": args.rounding, "accumulate": "fp32 (TMEM)",
+                       "sharding": f"column-parallel, {N} output rows per rank, out_features={N * world}, no collective",
+                       "l2": f"rotating {SETS} operand sets ({SETS * 64} MiB) so inputs exceed the 126 MB L2",
+                       "tile": f"{tile.tile_m}x{tile.tile_n}x{tile.tile_k}", "kernel_id": kid},
+            "roofline": {"bound": "tensor", "achieved": kernel_tflops, "peak": fp8_peak, "unit": "TFLOP/s",
+                         "frac": kernel_tflops / fp8_peak, "traffic": traffic,
+                         "peak_source": f"2 x bf16_tflops of MEASURED_PEAKS.json ({peaks['source']}): dense FP8 issues at twice the bf16 rate",
+                         "frac_of_nominal_4500": kernel_tflops / 4500.0,
+                         "frac_of_measured_bf16": kernel_tflops / peaks["bf16_tflops"]},
+            "cpu_baseline": cpu,
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": M * K + 4, "d2h_bytes_per_step": M * N * 2,
+                    "steps": e2e_steps},
+            "gpu_launches": args.steps,
+            "clocks": clocks,
+            "extras": extras,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def _time_calls(fn, iters, warm=5):
+    import torch
+    for i in range(warm):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e-3
+
+
+def _time_graph(fn, calls_per_graph, replays=20):
+    """Seconds per call with the calls captured in a CUDA graph and replayed: removes the host launch cost
+    (a decode step launches these kernels back to back from a graph)."""
+    import torch
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        for i in range(3):
+            fn(i)
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g):
+        for i in range(calls_per_graph):
+            fn(i)
+    for _ in range(3):
+        g.replay()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(replays):
+        g.replay()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / (replays * calls_per_graph) * 1e-3
+
+
+def side_measurements(dev, peaks):
+    """Decode GEMV (HBM GB/s) on the four Llama-3-8B-shaped projections and the INT8 W8A8 linear, rank 0 only."""
+    import torch
+    from oxicuda_b200.blas import MicroScalingConfig, MicroScalingQuantizer, ScalingFormat, gemv_fp4_wo
+    from oxicuda_b200.quant import LlmInt8Config, LlmInt8Quantizer
+    res = {"gemv_fp4_e8m0": {"timing": "CUDA-graph replay of back-to-back launches over rotating weight copies (> L2)"}}
+    msq = MicroScalingQuantizer(MicroScalingConfig(32, ScalingFormat.E8M0))
+    for (Kd, Nd) in ((4096, 4096), (4096, 1024), (4096, 14336), (14336, 4096)):
+        copies = max(4, int(300e6 // (Nd * Kd // 2)) + 1)         # rotate weight copies: > 126 MB L2 in total
+        ws = []
+        for c in range(copies):
+            w = torch.randn(Nd * Kd, device=dev) * 0.02
+            ws.append(msq.quantize_fp4(w))
+            del w
+        for tokens in (1, 4, 16, 32):
+            x = torch.randn(tokens, Kd, device=dev).to(torch.bfloat16)
+            out = torch.empty(tokens, Nd, dtype=torch.bfloat16, device=dev)
+            call = lambda i: gemv_fp4_wo(ws[i % copies][0], ws[i % copies][1], x, Nd, Kd, out=out)
+            sec = _time_graph(call, 4 * copies)
+            sec_eager = _time_calls(call, 100, 10)
+            nbytes = Nd * Kd // 2 + Nd * Kd // 32 + 2 * tokens * Kd + 2 * tokens * Nd
+            res["gemv_fp4_e8m0"][f"k{Kd}_n{Nd}_m{tokens}"] = {
+                "us": sec * 1e6, "us_eager_launch": sec_eager * 1e6, "gbs": nbytes / sec / 1e9,
+                "frac_of_measured_hbm": nbytes / sec / 1e9 / peaks["hbm_gbs"]}
+        del ws
+    x = torch.randn(8, 1024, device=dev)
+    w = torch.randn(1024, 1024, device=dev) * 0.02
+    q = LlmInt8Quantizer(LlmInt8Config(1e30, True))
+    sec = _time_calls(lambda i: q.matmul(x, w, 8, 1024, 1024), 50, 5)
+    res["int8_w8a8_linear_8x1024x1024"] = {"us": sec * 1e6, "note": "quantizes W and X on every call, as the reference entry point does"}
+    return res
+
+
+if __name__ == "__main__":
+    main()

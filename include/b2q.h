@@ -94,6 +94,11 @@ int32_t b2q_fp8_encode_f32(b2q_handle h, const float* x, int64_t n, int fmt, int
 /* decode (:140-142).  rounding=B2Q_ROUND_REF decodes as the reference codec does (:210-261);
  * B2Q_ROUND_RNE decodes IEEE-style (true subnormals), which is what the tensor core computes with. */
 int32_t b2q_fp8_decode_f32(b2q_handle h, const uint8_t* codes, int64_t n, int fmt, int rounding, float* out);
+/* In place: rewrites each subnormal code (exponent field 0, mantissa m != 0) as exponent field 1 with the same
+ * mantissa.  Fp8Codec::fp8_to_fp32 (fp8.rs:242-254) decodes a subnormal code as 2^(1-bias)*(1+m/2^mb), which is the
+ * IEEE value of the rewritten code; b2q_gemm_fp8 over rewritten codes therefore multiplies exactly the values the
+ * reference's decode -> f32 matmul composition multiplies. */
+int32_t b2q_fp8_remap_ref_subnormals(b2q_handle h, uint8_t* codes, int64_t n, int fmt);
 /* Absmax-scaled quantization of `rows` slices: scale = absmax/max_val (1.0 for an all-zero slice),
  * code = encode(x/scale).  The per-tensor rule of crates/oxicuda-dnn/src/quantize/fp8_quantize.rs:28-34
  * composed with the codec; rows=1 is per-tensor, rows>1 per-row (per-token / per-output-channel). */

@@ -76,16 +76,16 @@ def minmax_calibrate(x, rows, cols, bits=8, scheme=0):
 def minmax_quantize(x, rows, cols, scales, zps, bits=8, scheme=0):
     x = _f32(x).reshape(-1)
     codes = np.zeros(rows * cols, np.int32)
-    lib().orc_minmax_quantize(_p(x), _i64(rows), _i64(cols), _p(_f32(scales)), _p(np.ascontiguousarray(zps, np.int32)),
-                              bits, scheme, _p(codes))
+    scales, zps = _f32(scales), np.ascontiguousarray(zps, np.int32)    # locals keep converted copies alive
+    lib().orc_minmax_quantize(_p(x), _i64(rows), _i64(cols), _p(scales), _p(zps), bits, scheme, _p(codes))
     return codes
 
 
 def minmax_dequantize(codes, rows, cols, scales, zps):
     codes = np.ascontiguousarray(codes, np.int32).reshape(-1)
     out = np.zeros(rows * cols, np.float32)
-    lib().orc_minmax_dequantize(_p(codes), _i64(rows), _i64(cols), _p(_f32(scales)),
-                                _p(np.ascontiguousarray(zps, np.int32)), _p(out))
+    scales, zps = _f32(scales), np.ascontiguousarray(zps, np.int32)
+    lib().orc_minmax_dequantize(_p(codes), _i64(rows), _i64(cols), _p(scales), _p(zps), _p(out))
     return out
 
 
@@ -180,7 +180,8 @@ def nf4_encode(x, block=64):
 def nf4_decode(packed, absmaxs, block=64):
     packed = np.ascontiguousarray(packed, np.uint8).reshape(-1)
     out = np.zeros(packed.size * 2, np.float32)
-    lib().orc_nf4_decode(_p(packed), _i64(packed.size), block, _p(_f32(absmaxs)), _p(out))
+    absmaxs = _f32(absmaxs)
+    lib().orc_nf4_decode(_p(packed), _i64(packed.size), block, _p(absmaxs), _p(out))
     return out
 
 
@@ -197,7 +198,8 @@ def distfp8_quantize_block(x, block):
 def distfp8_dequantize_block(q, absmaxs, block):
     q = np.ascontiguousarray(q, np.uint8).reshape(-1)
     out = np.zeros(q.size, np.float32)
-    lib().orc_distfp8_dequantize_block(_p(q), _i64(q.size), _i64(max(1, int(block))), _p(_f32(absmaxs)), _p(out))
+    absmaxs = _f32(absmaxs)
+    lib().orc_distfp8_dequantize_block(_p(q), _i64(q.size), _i64(max(1, int(block))), _p(absmaxs), _p(out))
     return out
 
 
@@ -268,16 +270,18 @@ def gemv_fp4(codes, scales, x_bf16_bits, M, N, K, block=32, want="bf16"):
 
 # ---- tensor parallel ----
 def column_linear(x, w, bias, batch, in_f, out_f, tp):
+    x, w = _f32(x).reshape(-1), _f32(w).reshape(-1)          # keep the (possibly copied) arrays alive over the call
+    b = None if bias is None else _f32(bias)
     out = np.zeros(batch * out_f, np.float32)
-    lib().orc_column_linear(_p(_f32(x).reshape(-1)), _p(_f32(w).reshape(-1)), _p(None if bias is None else _f32(bias)),
-                            _i64(batch), _i64(in_f), _i64(out_f), tp, _p(out))
+    lib().orc_column_linear(_p(x), _p(w), _p(b), _i64(batch), _i64(in_f), _i64(out_f), tp, _p(out))
     return out.reshape(batch, out_f)
 
 
 def row_linear(x, w, bias, batch, in_f, out_f, tp):
+    x, w = _f32(x).reshape(-1), _f32(w).reshape(-1)
+    b = None if bias is None else _f32(bias)
     out = np.zeros(batch * out_f, np.float32)
-    lib().orc_row_linear(_p(_f32(x).reshape(-1)), _p(_f32(w).reshape(-1)), _p(None if bias is None else _f32(bias)),
-                         _i64(batch), _i64(in_f), _i64(out_f), tp, _p(out))
+    lib().orc_row_linear(_p(x), _p(w), _p(b), _i64(batch), _i64(in_f), _i64(out_f), tp, _p(out))
     return out.reshape(batch, out_f)
 
 

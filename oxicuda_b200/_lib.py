@@ -95,6 +95,7 @@ SIGNATURES = {
     "b2q_fake_quant_inplace_f32": (C.c_int32, [_H, _P, _I64, _F, _F, _F, _F]),
     "b2q_fp8_encode_f32": (C.c_int32, [_H, _P, _I64, _I, _I, _P]),
     "b2q_fp8_decode_f32": (C.c_int32, [_H, _P, _I64, _I, _I, _P]),
+    "b2q_fp8_remap_ref_subnormals": (C.c_int32, [_H, _P, _I64, _I]),
     "b2q_fp8_quantize_rows_f32": (C.c_int32, [_H, _P, _I64, _I64, _I, _I, _P, _P]),
     "b2q_fp8_quantize_rows_bf16": (C.c_int32, [_H, _P, _I64, _I64, _I, _I, _P, _P]),
     "b2q_fp4_block_quantize_f32": (C.c_int32, [_H, _P, _I64, _I, _I, _I, _P, _P]),

@@ -24,8 +24,12 @@ struct b2q_handle_s {
   // allocates): [0] status word, [1..] reduction keys.
   int32_t* d_status;         // 1 x i32
   uint32_t* d_scratch;       // kScratchWords x u32
+  void* ws;                  // grow-only workspace for calls that need temporaries (kept so steady-state calls never allocate)
+  size_t ws_bytes;
   char err[512];
 };
+// Returns a workspace of at least `bytes` (256-byte aligned); grows it when needed (synchronises the stream first).
+int32_t b2q_workspace(b2q_handle h, size_t bytes, void** out);
 static const size_t kScratchWords = 1 << 16;   // 256 KiB of reduction keys / counters
 
 #define B2Q_FAIL(h, code, ...)                                   \

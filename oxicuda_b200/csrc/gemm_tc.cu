@@ -14,6 +14,7 @@
 // B2Q_ERR_TIMEOUT in the status word, drains what it issued, frees TMEM and returns.
 #include "common.cuh"
 #include <cuda.h>
+#include <stdlib.h>
 
 namespace tc {
 
@@ -267,6 +268,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll 1
       for (int c = 0; c < BN; c += 32) {
         uint32_t r[32];
+        __syncwarp();                       // tcgen05.ld is warp-collective: reconverge after the guarded stores
         tmem_ld32(tmem_base + buf * BN + c + ((uint32_t)(q * 32) << 16), r);
         tmem_ld_wait();
         const int64_t n = n0 + c;
@@ -428,6 +430,11 @@ extern "C" int32_t b2q_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w
   if (st != B2Q_OK) return st;
   b2q_tile_config t; int kid = 0;
   b2q_select_tile(0, (uint32_t)M, (uint32_t)N, (uint32_t)K, &t, &kid);
+  if (kid != 0) {   // experiment switch: B2Q_FORCE_TILE_N=128|256 overrides the static table
+    const char* force = getenv("B2Q_FORCE_TILE_N");
+    if (force && force[0] == '1') kid = 2;
+    if (force && force[0] == '2') kid = 1;
+  }
   const bool tma_ok = K % 16 == 0 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
   if (kid == 0 || !tma_ok)
     return b2q_gemm_fp8_simt(h, a, w, M, N, K, fmt, /*IEEE decode, as the tensor core*/ 1, scale_a, scale_a_kind, scale_w,

@@ -5,17 +5,19 @@
 //   * a CTA owns R = 16 * WARPS consecutive weight rows and one K slice; a thread-block
 //     cluster of `split_k` CTAs covers the whole K of those rows and reduces the
 //     partial sums through distributed shared memory (no global scratch, no atomics);
-//   * a warp owns 16 weight rows.  Per 128-wide K step every lane issues two 128-bit
-//     streaming loads (row g and row g+8, 32 codes = one scale block each), so a warp
-//     instruction covers 8 rows x 64 contiguous bytes;
-//   * codes are expanded in registers: cvt.rn.f16x2.e2m1x2 (one instruction per byte)
-//     and one HMUL2 by the block scale, which directly yields the A fragments of
-//     mma.sync.m16n8k16 (the K order inside an MMA is permuted consistently for A and B);
+//   * a warp owns 16 weight rows and walks K in steps of 128 (four scale blocks).  For
+//     each block the four lanes of a quad load 4 bytes each of row g and of row g+8, so
+//     one warp instruction covers 8 rows x 16 contiguous bytes and the four instructions
+//     of a step cover 64 contiguous bytes per row (both 32-byte sectors fully used);
+//   * codes are expanded in registers with cvt.rn.f16x2.e2m1x2 (one instruction per
+//     byte, exact) and are directly the A fragments of mma.sync.m16n8k16: every MMA spans
+//     16 codes of ONE scale block, so the block scale is applied to the fp32 result of
+//     the two MMAs of a block (exact for f32 and for E8M0 scales alike);
 //   * activations are converted bf16 -> f16 once per 512-wide K chunk and staged in
 //     shared memory in fragment order, so B fragments are conflict-free 128-bit loads;
-//   * fp32 accumulation in the MMA; bf16 (RNE) or f32 store.
-// f16 is used because E2M1 -> f16x2 is a single hardware conversion; activations
-// beyond +-65504 saturate and block scales outside [2^-24, 2^15] are not representable.
+//   * fp32 accumulation; bf16 (RNE) or f32 store.
+// f16 operands are used because E2M1 -> f16x2 is a single hardware conversion and every
+// E2M1 value is exact in f16; activations beyond +-65504 saturate.
 #include "common.cuh"
 #include <cooperative_groups.h>
 
@@ -25,10 +27,9 @@ namespace gemv {
 
 constexpr int KC = 512;   // K elements per staged activation chunk (4 steps of 128)
 
-__device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
-  uint4 r;
-  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+__device__ __forceinline__ uint32_t ld_stream_u32(const void* p) {
+  uint32_t r;
+  asm volatile("ld.global.nc.u32 %0, [%1];" : "=r"(r) : "l"(p));
   return r;
 }
 
@@ -43,10 +44,11 @@ __device__ __forceinline__ void cvt_e2m1x8(uint32_t w, uint32_t (&h)[4]) {
       "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
       : "=r"(h[0]), "=r"(h[1]), "=r"(h[2]), "=r"(h[3]) : "r"(w));
 }
-__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
+// d = a * b (+ 0): first MMA of a scale block
+__device__ __forceinline__ void mma_f16_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
 }
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile(
@@ -60,22 +62,37 @@ __device__ __forceinline__ uint32_t bf16x2_to_f16x2_sat(uint32_t v) {
   __half2 h = __floats2half2_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&h);
 }
-__device__ __forceinline__ uint32_t scale_to_h2(float s) {
-  __half2 h = __float2half2_rn(s);
-  return *reinterpret_cast<uint32_t*>(&h);
-}
+
+// Scales of the four blocks of one 128-wide step of one row, kept as loaded (E8M0: one word,
+// f32: four floats) and decoded at the point of use.
+template <bool E8> struct Scales4;
+template <> struct Scales4<true> {
+  uint32_t w;
+  __device__ __forceinline__ void load(const void* base, int64_t idx) {            // idx is a multiple of 4
+    w = __ldg(reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(base) + idx));
+  }
+  __device__ __forceinline__ void clear() { w = 0; }
+  __device__ __forceinline__ float get(int j) const { return e8m0_to_f32_dev((w >> (8 * j)) & 0xFF); }
+};
+template <> struct Scales4<false> {
+  float4 v;
+  __device__ __forceinline__ void load(const void* base, int64_t idx) {
+    v = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + idx));
+  }
+  __device__ __forceinline__ void clear() { v = make_float4(0.f, 0.f, 0.f, 0.f); }
+  __device__ __forceinline__ float get(int j) const { return j == 0 ? v.x : j == 1 ? v.y : j == 2 ? v.z : v.w; }
+};
 
 // MT: token tiles of 8 (tokens padded to 8*MT).  WARPS: warps per CTA (16 rows each).
-template <int MT, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32) gemv_fp4_kernel(const uint8_t* __restrict__ codes, const float* __restrict__ scales_f32,
-                                                              const uint8_t* __restrict__ scales_e8m0,
+template <int MT, int WARPS, bool E8>
+__global__ void __launch_bounds__(WARPS * 32) gemv_fp4_kernel(const uint8_t* __restrict__ codes, const void* __restrict__ scales,
                                                               const __nv_bfloat16* __restrict__ x, int tokens, int64_t N, int64_t K,
                                                               void* out, int out_type, int split_k) {
   constexpr int MPAD = 8 * MT;
   constexpr int R = 16 * WARPS;
   constexpr int NT = WARPS * 32;
   extern __shared__ __align__(16) uint8_t smem[];        // activation chunk, later the partial sums
-  uint4* xs = reinterpret_cast<uint4*>(smem);            // [step 4][jj 4][MPAD][tig 4] x 16 bytes
+  uint4* xs = reinterpret_cast<uint4*>(smem);            // [block-of-32 (16 per chunk)][MPAD][quad lane 4] x 16 bytes
   float* red = reinterpret_cast<float*>(smem);           // [MPAD][R]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -86,8 +103,8 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_fp4_kernel(const uint8_t* __r
   // clamp so that loads stay in bounds; rows >= N are dropped at the store
   const int64_t r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);
   const int64_t kblocks = K >> 5;                        // scale blocks per row
-  const uint8_t* w0 = codes + r0 * (K >> 1);
-  const uint8_t* w1 = codes + r1 * (K >> 1);
+  const uint8_t* w0 = codes + r0 * (K >> 1) + tig * 4;   // this lane's 4 bytes inside every 16-byte block
+  const uint8_t* w1 = codes + r1 * (K >> 1) + tig * 4;
 
   const int chunks_total = (int)((K + KC - 1) / KC);
   const int cpc = (chunks_total + split_k - 1) / split_k;
@@ -100,65 +117,58 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_fp4_kernel(const uint8_t* __r
   for (int c = c_begin; c < c_end; ++c) {
     const int64_t k0 = (int64_t)c * KC;
     // ---- issue this chunk's weight and scale loads first (they are the long-latency HBM stream) ----
-    uint4 wa[4], wb[4];
-    uint32_t sa[4], sb[4];
+    uint32_t wa[4][4], wb[4][4];
+    Scales4<E8> sa[4], sb[4];
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
-      const int64_t k = k0 + s * 128 + tig * 32;
+      const int64_t k = k0 + s * 128;
       if (k < K) {
-        wa[s] = ld_stream_v4(w0 + (k >> 1));
-        wb[s] = ld_stream_v4(w1 + (k >> 1));
-        const int64_t kb = k >> 5;
-        float fa, fb;
-        if (scales_e8m0) {
-          fa = e8m0_to_f32_dev(__ldg(scales_e8m0 + r0 * kblocks + kb));
-          fb = e8m0_to_f32_dev(__ldg(scales_e8m0 + r1 * kblocks + kb));
-        } else {
-          fa = __ldg(scales_f32 + r0 * kblocks + kb);
-          fb = __ldg(scales_f32 + r1 * kblocks + kb);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          wa[s][j] = ld_stream_u32(w0 + ((k + j * 32) >> 1));
+          wb[s][j] = ld_stream_u32(w1 + ((k + j * 32) >> 1));
         }
-        sa[s] = scale_to_h2(fa);
-        sb[s] = scale_to_h2(fb);
+        sa[s].load(scales, r0 * kblocks + (k >> 5));
+        sb[s].load(scales, r1 * kblocks + (k >> 5));
       } else {
-        wa[s] = make_uint4(0, 0, 0, 0);
-        wb[s] = make_uint4(0, 0, 0, 0);
-        sa[s] = sb[s] = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) { wa[s][j] = 0; wb[s][j] = 0; }
+        sa[s].clear();
+        sb[s].clear();
       }
     }
     // ---- stage activations of this chunk: bf16 -> f16, fragment order ----
     __syncthreads();                                     // previous chunk's readers are done
-    for (int i = threadIdx.x; i < 16 * MPAD; i += NT) {
-      const int ttig = i & 3, tok = (i >> 2) % MPAD, step = i / (4 * MPAD);
-      const int64_t k = k0 + step * 128 + ttig * 32;
-      const bool live = tok < tokens && k < K;
-      const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)tok * K + k);
-#pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {
-        uint4 v = live ? __ldg(src + jj) : make_uint4(0, 0, 0, 0);
-        uint4 h;
-        h.x = bf16x2_to_f16x2_sat(v.x); h.y = bf16x2_to_f16x2_sat(v.y);
-        h.z = bf16x2_to_f16x2_sat(v.z); h.w = bf16x2_to_f16x2_sat(v.w);
-        xs[((step * 4 + jj) * MPAD + tok) * 4 + ttig] = h;
-      }
+    for (int i = threadIdx.x; i < 64 * MPAD; i += NT) {
+      const int ttig = i & 3, tok = (i >> 2) % MPAD, blk = i / (4 * MPAD);
+      const int64_t k = k0 + blk * 32 + ttig * 8;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (tok < tokens && k < K) v = __ldg(reinterpret_cast<const uint4*>(x + (int64_t)tok * K + k));
+      uint4 h;
+      h.x = bf16x2_to_f16x2_sat(v.x); h.y = bf16x2_to_f16x2_sat(v.y);
+      h.z = bf16x2_to_f16x2_sat(v.z); h.w = bf16x2_to_f16x2_sat(v.w);
+      xs[i] = h;                                         // == xs[(blk * MPAD + tok) * 4 + ttig]
     }
     __syncthreads();
-    // ---- expand codes and multiply ----
+    // ---- expand codes, multiply, scale in fp32 ----
 #pragma unroll
     for (int s = 0; s < 4; ++s) {
-      const uint32_t wav[4] = {wa[s].x, wa[s].y, wa[s].z, wa[s].w};
-      const uint32_t wbv[4] = {wb[s].x, wb[s].y, wb[s].z, wb[s].w};
 #pragma unroll
-      for (int jj = 0; jj < 4; ++jj) {                   // 8 codes per row = two MMA k-steps
+      for (int j = 0; j < 4; ++j) {                      // one scale block: 8 codes per lane and row, two MMA k-steps
         uint32_t ha[4], hb[4];
-        cvt_e2m1x8(wav[jj], ha);
-        cvt_e2m1x8(wbv[jj], hb);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { ha[i] = hmul2_u32(ha[i], sa[s]); hb[i] = hmul2_u32(hb[i], sb[s]); }
+        cvt_e2m1x8(wa[s][j], ha);
+        cvt_e2m1x8(wb[s][j], hb);
+        const float fa = sa[s].get(j), fb = sb[s].get(j);
 #pragma unroll
         for (int t = 0; t < MT; ++t) {
-          const uint4 xv = xs[((s * 4 + jj) * MPAD + (t * 8 + g)) * 4 + tig];
-          mma_f16(acc[t], ha[0], hb[0], ha[1], hb[1], xv.x, xv.y);
-          mma_f16(acc[t], ha[2], hb[2], ha[3], hb[3], xv.z, xv.w);
+          const uint4 xv = xs[((s * 4 + j) * MPAD + (t * 8 + g)) * 4 + tig];
+          float d[4];
+          mma_f16_zero(d, ha[0], hb[0], ha[1], hb[1], xv.x, xv.y);
+          mma_f16(d, ha[2], hb[2], ha[3], hb[3], xv.z, xv.w);
+          acc[t][0] = fmaf(fa, d[0], acc[t][0]);
+          acc[t][1] = fmaf(fa, d[1], acc[t][1]);
+          acc[t][2] = fmaf(fb, d[2], acc[t][2]);
+          acc[t][3] = fmaf(fb, d[3], acc[t][3]);
         }
       }
     }
@@ -197,20 +207,20 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_fp4_kernel(const uint8_t* __r
   if (split_k > 1) cluster.sync();                       // peers may still be reading this CTA's partials
 }
 
-template <int MT, int WARPS>
-int32_t launch(b2q_handle h, const uint8_t* codes, const void* scales, int scale_format, const void* x, int tokens, int64_t N,
-               int64_t K, void* out, int out_type) {
+template <int MT, int WARPS, bool E8>
+int32_t launch_fmt(b2q_handle h, const uint8_t* codes, const void* scales, const void* x, int tokens, int64_t N, int64_t K,
+                   void* out, int out_type) {
   constexpr int R = 16 * WARPS;
   const int64_t row_tiles = ceil_div64(N, R);
   const int chunks = (int)ceil_div64(K, KC);
-  // K split: enough CTAs for ~2 per SM, a divisor-friendly cluster size of at most 8
+  // K split = cluster size (<= 8, a divisor of the chunk count): the smallest one that gives about 1.5 CTAs
+  // per SM, else the largest available.
   int split = 1;
-  while (split < 8 && row_tiles * split < 2 * (int64_t)h->sm_count && split * 2 <= chunks) split *= 2;
-  if (chunks % split != 0) {                             // prefer an even split when one exists nearby
-    for (int s = split; s >= 1; --s) if (chunks % s == 0 && s * 2 > split) { split = s; break; }
-    if (chunks == 28 && row_tiles * 7 >= (int64_t)h->sm_count) split = 7;
+  for (int s = 1; s <= 8 && s <= chunks; ++s) {
+    if (chunks % s != 0) continue;
+    split = s;
+    if (row_tiles * s >= (3 * (int64_t)h->sm_count) / 2) break;
   }
-  if (chunks % 7 == 0 && split == 4 && row_tiles * 7 <= 3 * (int64_t)h->sm_count) split = 7;
   const size_t smem = (size_t)1024 * 8 * MT > (size_t)8 * MT * R * 4 ? (size_t)1024 * 8 * MT : (size_t)8 * MT * R * 4;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(row_tiles * split));
@@ -224,11 +234,16 @@ int32_t launch(b2q_handle h, const uint8_t* codes, const void* scales, int scale
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  const float* sf = scale_format == B2Q_SCALE_F32 ? (const float*)scales : nullptr;
-  const uint8_t* se = scale_format == B2Q_SCALE_E8M0 ? (const uint8_t*)scales : nullptr;
-  B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, gemv_fp4_kernel<MT, WARPS>, codes, sf, se, (const __nv_bfloat16*)x, tokens, N, K, out,
+  B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, gemv_fp4_kernel<MT, WARPS, E8>, codes, scales, (const __nv_bfloat16*)x, tokens, N, K, out,
                                  out_type, split));
   return B2Q_OK;
+}
+
+template <int MT, int WARPS>
+int32_t launch(b2q_handle h, const uint8_t* codes, const void* scales, int scale_format, const void* x, int tokens, int64_t N,
+               int64_t K, void* out, int out_type) {
+  return scale_format == B2Q_SCALE_E8M0 ? launch_fmt<MT, WARPS, true>(h, codes, scales, x, tokens, N, K, out, out_type)
+                                        : launch_fmt<MT, WARPS, false>(h, codes, scales, x, tokens, N, K, out, out_type);
 }
 
 }  // namespace gemv
@@ -248,6 +263,8 @@ extern "C" int32_t b2q_gemv_fp4_wo(b2q_handle h, const uint8_t* codes, const voi
     B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemv_fp4_wo: bad argument");
   if (((reinterpret_cast<uintptr_t>(codes) | reinterpret_cast<uintptr_t>(x_bf16)) & 15) != 0)
     B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemv_fp4_wo: codes and activations must be 16-byte aligned");
+  if ((reinterpret_cast<uintptr_t>(scales) & (scale_format == B2Q_SCALE_E8M0 ? 3 : 15)) != 0)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemv_fp4_wo: scales must be 4-byte (E8M0) or 16-byte (f32) aligned");
   const int t = (int)tokens;
   const bool small_n = N <= 2048;
   if (t <= 8) return small_n ? gemv::launch<1, 4>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type)

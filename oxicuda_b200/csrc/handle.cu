@@ -1,6 +1,20 @@
 // Handle lifetime, status word and the host-side tile heuristics of libb2q.
 #include "common.cuh"
 
+int32_t b2q_workspace(b2q_handle h, size_t bytes, void** out) {
+  if (bytes > h->ws_bytes) {
+    B2Q_CUDA(h, cudaStreamSynchronize(h->stream));       // earlier calls may still be using the old buffer
+    if (h->ws) cudaFree(h->ws);
+    h->ws = nullptr;
+    h->ws_bytes = 0;
+    size_t want = bytes + bytes / 4;
+    B2Q_CUDA(h, cudaMalloc(&h->ws, want));
+    h->ws_bytes = want;
+  }
+  *out = h->ws;
+  return B2Q_OK;
+}
+
 extern "C" {
 
 int32_t b2q_create(b2q_handle* out, int device) {
@@ -42,6 +56,7 @@ int32_t b2q_destroy(b2q_handle h) {
   cudaSetDevice(h->device);
   cudaFree(h->d_status);
   cudaFree(h->d_scratch);
+  if (h->ws) cudaFree(h->ws);
   delete h;
   return B2Q_OK;
 }

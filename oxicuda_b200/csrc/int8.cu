@@ -38,7 +38,7 @@ __global__ void masked_absmax_kernel(const float* x, int64_t n, int64_t cols, co
 // One block per row: scale = amax/127 over the regular columns (1.0 when amax == 0),
 // code = clamp(round(v * (1/scale)), +-127) (round half away from zero), outlier
 // columns get code 0.  `global_amax_bits` (optional) replaces the per-row absmax.
-__global__ void __launch_bounds__(kThreads) int8_row_quant_kernel(const float* x, int64_t cols, const uint8_t* is_out,
+__global__ void __launch_bounds__(kThreads) int8_row_quant_kernel(const float* x, int64_t cols, int64_t ld, const uint8_t* is_out,
                                                                   const uint32_t* global_amax_bits, int8_t* q, float* scales) {
   const int64_t r = blockIdx.x;
   const float* row = x + r * cols;
@@ -74,8 +74,9 @@ __global__ void __launch_bounds__(kThreads) int8_row_quant_kernel(const float* x
       t = t < -127.0f ? -127.0f : (t > 127.0f ? 127.0f : t);
       code = isnan(t) ? (int8_t)0 : (int8_t)(int)t;
     }
-    q[r * cols + c] = code;
+    q[r * ld + c] = code;
   }
+  for (int64_t c = cols + threadIdx.x; c < ld; c += kThreads) q[r * ld + c] = 0;   // padding columns contribute nothing
 }
 
 // Small-M INT8 GEMM: C[m,n] = sum_k A[m,k] * B[n,k].  A (all M rows) is staged in
@@ -87,7 +88,7 @@ __global__ void __launch_bounds__(kThreads) gemm_i8_small_m_kernel(
     const int8_t* __restrict__ a, const int8_t* __restrict__ b, int M, int64_t N, int64_t K, int32_t* c_s32,
     float* c_f32, const float* sa, const float* sb,
     // outlier side path (LLM.int8): fp32 operands and the mask; all null/0 when unused
-    const float* xf, const float* wf, const uint8_t* is_out, const int32_t* n_out) {
+    const float* xf, const float* wf, const uint8_t* is_out, const int32_t* n_out, int64_t Kf) {
   extern __shared__ __align__(16) int8_t sa_tile[];          // [M][K]
   const int64_t total = (int64_t)M * K;
   for (int64_t i = (int64_t)threadIdx.x * 16; i < total; i += (int64_t)kThreads * 16)
@@ -135,8 +136,8 @@ __global__ void __launch_bounds__(kThreads) gemm_i8_small_m_kernel(
           if (side) {
             // acc_fp += x[m,c]*w[n,c] over outlier columns in ascending order, unfused
             float fp = 0.0f;
-            for (int64_t c = 0; c < K; ++c)
-              if (is_out[c]) fp = __fadd_rn(fp, __fmul_rn(xf[(int64_t)m * K + c], wf[n * K + c]));
+            for (int64_t c = 0; c < Kf; ++c)
+              if (is_out[c]) fp = __fadd_rn(fp, __fmul_rn(xf[(int64_t)m * Kf + c], wf[n * Kf + c]));
             o = __fadd_rn(o, fp);
           }
           c_f32[(int64_t)m * N + n] = o;
@@ -214,7 +215,7 @@ __global__ void outlier_side_kernel(const float* xf, const float* wf, const uint
 
 int32_t launch_gemm_i8(b2q_handle h, const int8_t* a, const int8_t* b, int64_t M, int64_t N, int64_t K, int32_t* c_s32,
                        float* c_f32, const float* sa, const float* sb, const float* xf, const float* wf,
-                       const uint8_t* is_out, const int32_t* n_out) {
+                       const uint8_t* is_out, const int32_t* n_out, int64_t Kf) {
   const bool aligned = ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) == 0 && K % 16 == 0;
   const size_t smem = (size_t)M * K;
   if (aligned && M <= 64 && smem <= 96 * 1024) {
@@ -223,7 +224,7 @@ int32_t launch_gemm_i8(b2q_handle h, const int8_t* a, const int8_t* b, int64_t M
     auto kern = M <= 8 ? gemm_i8_small_m_kernel<8> : gemm_i8_small_m_kernel<4>;
     if (smem > 48 * 1024)
       B2Q_CUDA(h, cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    kern<<<grid, kThreads, smem, h->stream>>>(a, b, (int)M, N, K, c_s32, c_f32, sa, sb, xf, wf, is_out, n_out);
+    kern<<<grid, kThreads, smem, h->stream>>>(a, b, (int)M, N, K, c_s32, c_f32, sa, sb, xf, wf, is_out, n_out, Kf);
     B2Q_LAUNCH_CHECK(h, "gemm_i8_small_m_kernel");
     return B2Q_OK;
   }
@@ -231,7 +232,7 @@ int32_t launch_gemm_i8(b2q_handle h, const int8_t* a, const int8_t* b, int64_t M
   gemm_i8_tiled_kernel<<<grid, 256, 0, h->stream>>>(a, b, M, N, K, c_s32, c_f32, sa, sb);
   B2Q_LAUNCH_CHECK(h, "gemm_i8_tiled_kernel");
   if (c_f32 && n_out) {
-    outlier_side_kernel<<<(int)ceil_div64(M * N, 256), 256, 0, h->stream>>>(xf, wf, is_out, n_out, M, N, K, c_f32);
+    outlier_side_kernel<<<(int)ceil_div64(M * N, 256), 256, 0, h->stream>>>(xf, wf, is_out, n_out, M, N, Kf, c_f32);
     B2Q_LAUNCH_CHECK(h, "outlier_side_kernel");
   }
   return B2Q_OK;
@@ -261,7 +262,7 @@ int32_t b2q_gemm_i8(b2q_handle h, const int8_t* a, const int8_t* b, int64_t M, i
     if (st != B2Q_ERR_UNSUPPORTED) return st;
     h->err[0] = 0;
   }
-  return launch_gemm_i8(h, a, b, M, N, K, c_s32, c_f32, scale_a, scale_b, nullptr, nullptr, nullptr, nullptr);
+  return launch_gemm_i8(h, a, b, M, N, K, c_s32, c_f32, scale_a, scale_b, nullptr, nullptr, nullptr, nullptr, K);
 }
 
 int32_t b2q_llm_int8_linear_f32(b2q_handle h, const float* x, const float* w, int64_t samples, int64_t rows, int64_t cols,
@@ -272,36 +273,40 @@ int32_t b2q_llm_int8_linear_f32(b2q_handle h, const float* x, const float* w, in
   if (!isfinite(threshold) || threshold <= 0.0f)
     B2Q_FAIL(h, B2Q_ERR_INVALID_CONFIG, "LLM.int8 threshold must be finite and positive, got %g", (double)threshold);
   if (!x || !w || !out) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "llm_int8_linear: null pointer");
-  if (cols % 4 != 0) B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "llm_int8_linear: cols must be a multiple of 4, got %lld", (long long)cols);
-  // Workspace inside the caller-provided dumps when given, otherwise one stream-ordered allocation.
-  const size_t need_wq = wq ? 0 : (size_t)(rows * cols), need_xq = xq ? 0 : (size_t)(samples * cols);
-  const size_t need_sw = sw ? 0 : sizeof(float) * (size_t)rows, need_sx = sx ? 0 : sizeof(float) * (size_t)samples;
+  // Codes are kept with the row length padded to 16 so that every row starts 16-byte aligned; the padding is zero.
+  // Caller-provided dumps are used in place when no padding is needed, otherwise filled by a strided copy.
+  const int64_t ld = (cols + 15) & ~(int64_t)15;
+  const bool padded = ld != cols;
+  int8_t* wq_user = wq; int8_t* xq_user = xq;
   auto al = [](size_t v) { return (v + 255) & ~(size_t)255; };
+  const size_t need_wq = (wq && !padded) ? 0 : (size_t)(rows * ld), need_xq = (xq && !padded) ? 0 : (size_t)(samples * ld);
+  const size_t need_sw = sw ? 0 : sizeof(float) * (size_t)rows, need_sx = sx ? 0 : sizeof(float) * (size_t)samples;
   const size_t total = al(need_wq) + al(need_xq) + al(need_sw) + al(need_sx) + al((size_t)cols) + 256;
-  uint8_t* ws = nullptr;
-  B2Q_CUDA(h, cudaMallocAsync((void**)&ws, total, h->stream));
-  uint8_t* p = ws;
-  if (!wq) { wq = (int8_t*)p; p += al(need_wq); }
-  if (!xq) { xq = (int8_t*)p; p += al(need_xq); }
+  uint8_t* p = nullptr;
+  int32_t wst = b2q_workspace(h, total, (void**)&p);
+  if (wst != B2Q_OK) return wst;
+  if (need_wq) { wq = (int8_t*)p; p += al(need_wq); }
+  if (need_xq) { xq = (int8_t*)p; p += al(need_xq); }
   if (!sw) { sw = (float*)p; p += al(need_sw); }
   if (!sx) { sx = (float*)p; p += al(need_sx); }
   uint8_t* is_out = p; p += al((size_t)cols);
   int32_t* n_out = (int32_t*)p;            // [0] count, [1] global absmax bits
   uint32_t* gmax = (uint32_t*)(n_out + 1);
-  cudaMemsetAsync(n_out, 0, 8, h->stream);
+  B2Q_CUDA(h, cudaMemsetAsync(n_out, 0, 8, h->stream));
 
   outlier_mask_kernel<<<(int)ceil_div64(cols, 256), 256, 0, h->stream>>>(x, samples, cols, threshold, is_out, n_out);
-  int8_row_quant_kernel<<<(int)rows, kThreads, 0, h->stream>>>(w, cols, is_out, nullptr, wq, sw);
+  int8_row_quant_kernel<<<(int)rows, kThreads, 0, h->stream>>>(w, cols, ld, is_out, nullptr, wq, sw);
   if (!row_wise) {
     int g = (int)ceil_div64(samples * cols, 256);
     if (g > h->sm_count * 8) g = h->sm_count * 8;
     masked_absmax_kernel<<<g, 256, 0, h->stream>>>(x, samples * cols, cols, is_out, gmax);
   }
-  int8_row_quant_kernel<<<(int)samples, kThreads, 0, h->stream>>>(x, cols, is_out, row_wise ? nullptr : gmax, xq, sx);
+  int8_row_quant_kernel<<<(int)samples, kThreads, 0, h->stream>>>(x, cols, ld, is_out, row_wise ? nullptr : gmax, xq, sx);
   B2Q_LAUNCH_CHECK(h, "llm_int8 quantize kernels");
-  int32_t st = launch_gemm_i8(h, xq, wq, samples, rows, cols, acc, out, sx, sw, x, w, is_out, n_out);
-  if (n_outliers) cudaMemcpyAsync(n_outliers, n_out, sizeof(int32_t), cudaMemcpyDeviceToDevice, h->stream);
-  cudaFreeAsync(ws, h->stream);
+  int32_t st = launch_gemm_i8(h, xq, wq, samples, rows, ld, acc, out, sx, sw, x, w, is_out, n_out, cols);
+  if (padded && wq_user) B2Q_CUDA(h, cudaMemcpy2DAsync(wq_user, (size_t)cols, wq, (size_t)ld, (size_t)cols, (size_t)rows, cudaMemcpyDeviceToDevice, h->stream));
+  if (padded && xq_user) B2Q_CUDA(h, cudaMemcpy2DAsync(xq_user, (size_t)cols, xq, (size_t)ld, (size_t)cols, (size_t)samples, cudaMemcpyDeviceToDevice, h->stream));
+  if (n_outliers) B2Q_CUDA(h, cudaMemcpyAsync(n_outliers, n_out, sizeof(int32_t), cudaMemcpyDeviceToDevice, h->stream));
   return st;
 }
 

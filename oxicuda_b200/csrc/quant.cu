@@ -296,6 +296,19 @@ __global__ void __launch_bounds__(kThreads) fp8_decode_kernel(const uint8_t* cod
   }
 }
 
+// Rewrites the subnormal codes (exponent field 0, mantissa m != 0) to exponent field 1 with the same
+// mantissa.  The reference decoder reads a subnormal code as 2^(1-bias) * (1 + m/2^mb), which is exactly
+// the IEEE value of that rewritten code, so a tensor-core GEMM over rewritten codes multiplies the very
+// values the reference's decode -> f32 matmul composition multiplies.
+__global__ void __launch_bounds__(kThreads) fp8_remap_ref_subnormals_kernel(uint8_t* codes, int64_t n, int fmt) {
+  const uint32_t mb = fmt == 0 ? 3u : 2u;
+  const uint32_t exp_mask = fmt == 0 ? 0x78u : 0x7Cu, man_mask = (1u << mb) - 1u;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+    uint32_t c = codes[i];
+    if ((c & exp_mask) == 0 && (c & man_mask) != 0) codes[i] = (uint8_t)(c | (1u << mb));
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Block-scaled FP4.  block/4 lanes cooperate on one block: each lane loads one
 // float4, the absmax is reduced with xor-shuffles inside the lane group, and each
@@ -534,6 +547,15 @@ int32_t b2q_fp8_decode_f32(b2q_handle h, const uint8_t* codes, int64_t n, int fm
     B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "fp8_decode: bad argument");
   fp8_decode_kernel<<<grid_for(h, n, kThreads * 4), kThreads, 0, h->stream>>>(codes, n, fmt, rounding, out);
   B2Q_LAUNCH_CHECK(h, "fp8_decode_kernel");
+  return B2Q_OK;
+}
+
+int32_t b2q_fp8_remap_ref_subnormals(b2q_handle h, uint8_t* codes, int64_t n, int fmt) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (n == 0) return B2Q_OK;
+  if (n < 0 || !codes || fmt < 0 || fmt > 1) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "fp8_remap_ref_subnormals: bad argument");
+  fp8_remap_ref_subnormals_kernel<<<grid_for(h, n, kThreads), kThreads, 0, h->stream>>>(codes, n, fmt);
+  B2Q_LAUNCH_CHECK(h, "fp8_remap_ref_subnormals_kernel");
   return B2Q_OK;
 }
 

@@ -204,6 +204,15 @@ class Fp8Codec:
         default_handle().call("b2q_fp8_decode_f32", ptr(c), c.numel(), self.format.value, self.rounding, ptr(out))
         return _back(out, was_host)
 
+    def to_reference_decode_codes(self, codes: torch.Tensor) -> torch.Tensor:
+        """Copy of `codes` whose IEEE values equal the reference decoder's reading of `codes`
+        (fp8.rs:242-254 reads subnormal codes as 2^(1-bias)*(1+m/2^mb)); feed it to gemm_fp8 to reproduce
+        the reference's decode -> f32 matmul composition on the tensor cores."""
+        c, was_host = _dev(codes.reshape(-1), torch.uint8)
+        c = c.clone()
+        default_handle().call("b2q_fp8_remap_ref_subnormals", ptr(c), c.numel(), self.format.value)
+        return _back(c, was_host).view(codes.shape)
+
     def quantization_mse(self, data: torch.Tensor) -> float:
         """fp8.rs:149-159"""
         dec = self.decode(self.encode(data))

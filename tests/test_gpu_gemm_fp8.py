@@ -1,0 +1,146 @@
+"""GPU: FP8 GEMM through the C ABI.  Small and ragged shapes against the CPU oracle (same codes in), the
+full 4096^3 configuration against the order-exact SIMT kernel and size-independent properties.
+
+Tolerance (stated by the task): max relative error <= 1e-2 after dequantization, bf16 output.  Relative
+error is |got - ref| / max(|ref|, tau) with tau = 1e-3 * rms(ref), so that near-zero outputs do not divide
+by zero; the un-floored count is asserted too."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def _t(a, dev):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+
+def rel_err(got, ref):
+    got = np.asarray(got, np.float64)
+    ref = np.asarray(ref, np.float64)
+    tau = 1e-3 * np.sqrt((ref ** 2).mean()) + 1e-30
+    return float((np.abs(got - ref) / np.maximum(np.abs(ref), tau)).max())
+
+
+def _quantize(oracle, x, rows, cols, mode):
+    codes, scales, bad = oracle.fp8_quantize_rows(x, rows, cols, 0, mode)
+    assert bad == -1
+    return codes.reshape(rows, cols), scales
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 128), (128, 128, 256), (256, 512, 1024), (64, 64, 64), (100, 200, 304),
+                                   (129, 257, 144), (384, 1000, 512), (1000, 136, 2048), (8, 512, 256), (300, 300, 100)])
+def test_gemm_fp8_vs_oracle(cuda, oracle, M, N, K):
+    from oxicuda_b200.blas import gemm_fp8
+    rng = np.random.default_rng(M * 7 + N * 3 + K)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    for mode in (0, 1):                           # reference codec codes, RNE codes
+        ac, sa = _quantize(oracle, a, 1, M * K, mode)       # per-tensor scales (config 2)
+        wc, sw = _quantize(oracle, w, 1, N * K, mode)
+        ac, wc = ac.reshape(M, K), wc.reshape(N, K)
+        # the tensor core decodes IEEE-style; the oracle in decode mode 1 does the same
+        ref = oracle.gemm_fp8(ac, wc, sa, sw, 0, 1, "bf16")
+        got = gemm_fp8(_t(ac, cuda), _t(wc, cuda), _t(sa, cuda), _t(sw, cuda)).float().cpu().numpy()
+        assert rel_err(got, ref) <= TOL, (M, N, K, mode)
+        if mode == 0:
+            # the reference's own composition (its codec's encode AND decode, then the f32 matmul): its decoder
+            # reads subnormal codes as 2^-6*(1+m/8), which the code rewrite reproduces on the tensor core
+            from oxicuda_b200.quant import Fp8Codec
+            codec = Fp8Codec.e4m3("ref")
+            ref0 = oracle.gemm_fp8(ac, wc, sa, sw, 0, 0, "bf16")
+            got0 = gemm_fp8(codec.to_reference_decode_codes(_t(ac, cuda)), codec.to_reference_decode_codes(_t(wc, cuda)),
+                            _t(sa, cuda), _t(sw, cuda)).float().cpu().numpy()
+            assert rel_err(got0, ref0) <= TOL, (M, N, K, mode)
+        # f32 output, per-row (per-token x per-channel) scales
+        sa_r = (rng.random(M).astype(np.float32) + 0.5) * sa[0]
+        sw_r = (rng.random(N).astype(np.float32) + 0.5) * sw[0]
+        ref = oracle.gemm_fp8(ac, wc, sa_r, sw_r, 0, 1, "f32")
+        got = gemm_fp8(_t(ac, cuda), _t(wc, cuda), _t(sa_r, cuda), _t(sw_r, cuda), out_dtype=torch.float32).cpu().numpy()
+        assert rel_err(got, ref) <= 1e-3, (M, N, K, mode)   # fp32 out: only the tensor core's accumulation differs
+
+
+def test_simt_kernel_reproduces_oracle_order(cuda, oracle):
+    """The checker kernel (software decode, k-ascending fp32 FMA) equals the oracle to the last bit."""
+    from oxicuda_b200.blas import gemm_fp8
+    rng = np.random.default_rng(31)
+    M, N, K = 96, 80, 520
+    ac = rng.integers(0, 256, (M, K)).astype(np.uint8)
+    wc = rng.integers(0, 256, (N, K)).astype(np.uint8)
+    ac[(ac & 0x7F) == 0x7F] = 0x3C
+    wc[(wc & 0x7F) == 0x7F] = 0x3C                # no NaN codes
+    sa = np.array([0.013], np.float32)
+    sw = rng.random(N).astype(np.float32)
+    for decode, mode in (("ref", 0), ("ieee", 1)):
+        ref = oracle.gemm_fp8(ac, wc, sa, sw, 0, mode, "f32")
+        got = gemm_fp8(_t(ac, cuda), _t(wc, cuda), _t(sa, cuda), _t(sw, cuda), out_dtype=torch.float32, simt_decode=decode)
+        assert np.array_equal(got.cpu().numpy().view(np.uint32), ref.view(np.uint32)), decode
+
+
+def test_every_code_pair_is_exact_on_the_tensor_core(cuda, oracle):
+    """One product per output: A holds every E4M3 code on the diagonal positions, so out[m,n] = a_m * w_n
+    exactly (a single non-zero term); all 254x254 finite pairs must match the IEEE decode product."""
+    from oxicuda_b200.blas import gemm_fp8
+    codes = np.array([c for c in range(256) if (c & 0x7F) != 0x7F], np.uint8)     # 254 finite codes
+    n = codes.size
+    K = 256
+    a = np.zeros((n, K), np.uint8)
+    w = np.zeros((n, K), np.uint8)
+    a[:, 5] = codes
+    w[:, 5] = codes
+    one = np.ones(1, np.float32)
+    got = gemm_fp8(_t(a, cuda), _t(w, cuda), _t(one, cuda), _t(one, cuda), out_dtype=torch.float32).cpu().numpy()
+    vals = oracle.fp8_decode(codes, 0, 1).astype(np.float32)
+    assert np.array_equal(got, np.outer(vals, vals).astype(np.float32))
+
+
+def test_config2_full_size_4096(cuda, oracle):
+    """A ~N(0,1), B ~N(0,0.02) at 4096^3, per-tensor absmax scales, bf16 out."""
+    from oxicuda_b200.blas import gemm_fp8
+    from oxicuda_b200.quant import Fp8Codec
+    M = N = K = 4096
+    g = torch.Generator(device=cuda).manual_seed(0xB2000001)
+    a = torch.randn(M, K, device=cuda, generator=g)
+    w = torch.randn(N, K, device=cuda, generator=g) * 0.02
+    for rounding, mode in (("ref", 0), ("rne", 1)):
+        codec = Fp8Codec.e4m3(rounding)
+        ac, sa = codec.quantize_rows(a, 1, M * K)
+        wc, sw = codec.quantize_rows(w, 1, N * K)
+        ac, wc = ac.view(M, K), wc.view(N, K)
+        out = gemm_fp8(ac, wc, sa, sw)
+        # (1) codes and scales are bit-exact with the oracle on a slice the CPU finishes quickly
+        sl = slice(0, 64)
+        c_ref, s_ref, _ = oracle.fp8_quantize_rows(a.cpu().numpy(), 1, M * K, 0, mode)
+        assert np.array_equal(sa.cpu().numpy(), s_ref) and np.array_equal(ac.cpu().numpy().reshape(-1), c_ref)
+        # (2) rows/columns sampled across all tiles against the oracle GEMM on the same codes
+        rows = np.r_[0:16, 2040:2056, 4080:4096]
+        ref = oracle.gemm_fp8(ac[rows].cpu().numpy(), wc.cpu().numpy(), sa.cpu().numpy(), sw.cpu().numpy(), 0, 1, "bf16")
+        assert rel_err(out[rows].float().cpu().numpy(), ref) <= TOL
+        # (3) whole output against the order-exact SIMT kernel
+        chk = gemm_fp8(ac, wc, sa, sw, simt_decode="ieee")
+        tau = 1e-3 * chk.float().pow(2).mean().sqrt()
+        err = ((out.float() - chk.float()).abs() / chk.float().abs().clamp_min(tau)).max().item()
+        assert err <= TOL, err
+        # (4) linearity in the scales: doubling a scale doubles every output exactly (power of two)
+        out2 = gemm_fp8(ac, wc, sa * 2, sw)
+        assert torch.equal(out2.float(), out.float() * 2)
+        # (5) row permutation of A permutes the rows of the output bit for bit
+        perm = torch.randperm(M, device=cuda, generator=g)
+        assert torch.equal(gemm_fp8(ac[perm].contiguous(), wc, sa, sw), out[perm])
+
+
+def test_gemm_fp8_validation_order(cuda):
+    from oxicuda_b200 import _lib
+    from oxicuda_b200.blas import gemm_fp8
+    one = torch.ones(1, device=cuda)
+    z = lambda *s: torch.zeros(*s, dtype=torch.uint8, device=cuda)
+    with pytest.raises(_lib.InvalidDimension):                       # zero dims first (gemm_api.rs:142-146)
+        gemm_fp8(z(0, 64), z(64, 64), one, one)
+    with pytest.raises(_lib.DimensionMismatch):                      # inner mismatch (gemm_api.rs:149-153)
+        gemm_fp8(z(64, 64), z(64, 128), one, one)
+    buf = z(64 * 64 * 4)
+    with pytest.raises(_lib.InvalidArgument):                        # C overlaps A (gemm_api.rs:189-195)
+        gemm_fp8(buf[:4096].view(64, 64), z(64, 64), one, one, out=buf[:8192].view(torch.bfloat16).view(64, 64))
+    with pytest.raises(_lib.DimensionMismatch):
+        gemm_fp8(z(64, 64), z(64, 64), torch.ones(3, device=cuda), one)

@@ -1,0 +1,82 @@
+"""GPU: block-scaled FP4 weight-only decode GEMV through the C ABI against the CPU oracle
+(dequantize_fp4 followed by an f32 dot product), bf16 out, max relative error <= 1e-2."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+TOL = 1e-2
+
+
+def _t(a, dev):
+    return torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+
+
+def rel_err(got, ref):
+    got = np.asarray(got, np.float64)
+    ref = np.asarray(ref, np.float64)
+    tau = 1e-3 * np.sqrt((ref ** 2).mean()) + 1e-30
+    return float((np.abs(got - ref) / np.maximum(np.abs(ref), tau)).max())
+
+
+def _case(cuda, oracle, tokens, N, K, scale_mode, seed, out_dtype=torch.bfloat16):
+    from oxicuda_b200.blas import gemv_fp4_wo
+    rng = np.random.default_rng(seed)
+    w = (rng.standard_normal(N * K) * 0.02).astype(np.float32)
+    codes, scales = oracle.fp4_block_quantize(w, 32, 0, scale_mode)
+    x = torch.from_numpy(rng.standard_normal((tokens, K)).astype(np.float32)).to(torch.bfloat16)
+    xb = x.view(torch.int16).numpy().view(np.uint16)
+    ref = oracle.gemv_fp4(codes, scales, xb, tokens, N, K, 32, "bf16" if out_dtype == torch.bfloat16 else "f32")
+    got = gemv_fp4_wo(_t(codes, cuda), _t(scales, cuda), x.to(cuda), N, K, out_dtype=out_dtype)
+    return rel_err(got.float().cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("tokens", [1, 4, 16, 32])
+@pytest.mark.parametrize("N,K", [(4096, 4096), (1024, 4096), (14336, 4096), (4096, 14336)])
+def test_llama3_8b_projections(cuda, oracle, tokens, N, K):
+    for scale_mode in (1, 0):                       # E8M0 (the configuration's wording) and f32 (reference) scales
+        assert _case(cuda, oracle, tokens, N, K, scale_mode, N + K + tokens) <= TOL
+
+
+@pytest.mark.parametrize("tokens,N,K", [(1, 16, 128), (3, 100, 256), (7, 17, 640), (9, 2050, 1152), (31, 130, 128), (32, 64, 8192)])
+def test_ragged_shapes(cuda, oracle, tokens, N, K):
+    for scale_mode in (1, 0):
+        assert _case(cuda, oracle, tokens, N, K, scale_mode, 5, torch.float32) <= 2e-3
+
+
+def test_codes_map_exactly(cuda, oracle):
+    """x = one-hot rows picks single weights: every E2M1 code times a power-of-two scale is exact."""
+    from oxicuda_b200.blas import gemv_fp4_wo
+    N, K = 16, 128
+    codes = np.zeros((N, K // 2), np.uint8)
+    for n in range(N):
+        codes[n, :] = n | (n << 4)                  # row n holds code n everywhere
+    scales = np.full((N, K // 32), 127 + 3, np.uint8)   # 2^3
+    for pos in (0, 1, 37, 127):
+        x = torch.zeros(1, K, dtype=torch.bfloat16)
+        x[0, pos] = 1.0
+        got = gemv_fp4_wo(_t(codes, cuda), _t(scales, cuda), x.to(cuda), N, K, out_dtype=torch.float32).cpu().numpy()[0]
+        want = np.array([oracle.fp4_dequantize_one(n, 0) * 8.0 for n in range(N)], np.float32)
+        assert np.array_equal(got, want), pos
+
+
+def test_linearity_and_validation(cuda, oracle):
+    from oxicuda_b200 import _lib
+    from oxicuda_b200.blas import gemv_fp4_wo
+    rng = np.random.default_rng(8)
+    N, K = 512, 1024
+    w = (rng.standard_normal(N * K) * 0.02).astype(np.float32)
+    codes, scales = oracle.fp4_block_quantize(w, 32, 0, 1)
+    cd, sd = _t(codes, cuda), _t(scales, cuda)
+    x = torch.randn(4, K, device=cuda).to(torch.bfloat16)
+    y = gemv_fp4_wo(cd, sd, x, N, K, out_dtype=torch.float32)
+    y2 = gemv_fp4_wo(cd, sd, (x.float() * 2).to(torch.bfloat16), N, K, out_dtype=torch.float32)
+    assert torch.equal(y2, y * 2)                   # scaling activations by 2 is exact
+    y1 = gemv_fp4_wo(cd, sd, x[:1].contiguous(), N, K, out_dtype=torch.float32)
+    assert torch.allclose(y1, y[:1], rtol=1e-5, atol=1e-6)     # a token's result does not depend on its batch
+    with pytest.raises(_lib.UnsupportedOperation):
+        gemv_fp4_wo(cd, sd, torch.zeros(33, K, device=cuda, dtype=torch.bfloat16), N, K)
+    with pytest.raises(_lib.InvalidDimension):
+        gemv_fp4_wo(cd, sd, x, N, 1000)
+    with pytest.raises(_lib.InvalidArgument):
+        gemv_fp4_wo(cd, sd, x, N, K, block=48)

@@ -1,0 +1,142 @@
+"""CPU: the C-ABI library loads without a GPU, exports every symbol the header declares, and the
+host-side logic (tile heuristics, argument validation, error mapping) behaves like the reference."""
+import ctypes as C
+import re
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+CLASS_NAMES = ["SmallSquare", "LargeSquare", "SkinnyM", "SkinnyN", "SkinnyK", "General"]
+
+
+def _header_symbols():
+    text = (ROOT / "include" / "b2q.h").read_text()
+    return sorted(set(re.findall(r"\b(b2q_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol(libb2q):
+    from oxicuda_b200 import _lib
+    names = _header_symbols()
+    assert len(names) >= 30
+    for n in names:
+        assert hasattr(libb2q, n), f"{n} is declared in include/b2q.h but missing from libb2q.so"
+    assert set(names) == set(_lib.SIGNATURES), "ctypes signature table and header disagree"
+
+
+def test_no_cpu_fallback_without_device(libb2q):
+    import torch
+    from oxicuda_b200 import _lib
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    with pytest.raises(_lib.B2qError):
+        _lib.Handle(0)
+
+
+def test_null_handle_is_rejected(libb2q):
+    assert libb2q.b2q_check(None) == 8
+    assert libb2q.b2q_gemm_fp8(None, None, None, 1, 1, 16, 0, None, 0, None, 0, None, 0) == 8
+    assert libb2q.b2q_last_error(None) == b"null handle"
+
+
+def test_tile_heuristics_match_reference_pins(libb2q, kat, oracle):
+    from oxicuda_b200 import blas
+    k = kat["tiles"]
+    for m, n, kk, name in k["classify_workload"]["cases"]:
+        assert blas.classify_workload(m, n, kk).name == name
+    c = k["fp8_blackwell_large_square"]
+    t = blas.Fp8Config.tile_config(*c["mnk"])
+    assert (t.tile_m, t.tile_n, t.stages) == (c["tile_m"], c["tile_n"], c["stages"])
+    c = k["fp8_blackwell_skinny_m"]
+    t = blas.Fp8Config.tile_config(*c["mnk"])
+    assert (t.tile_m, t.tile_n) == (c["tile_m"], c["tile_n"])
+    c = k["fp4_tile_blackwell_skinny_m"]
+    t = blas.select_fp4_tile(*c["mnk"])
+    assert (t.tile_m, t.tile_n) == (c["tile_m"], c["tile_n"])
+    c = k["fp4_tile_blackwell_large"]
+    t = blas.select_fp4_tile(*c["mnk"])
+    assert (t.tile_m, t.tile_n, t.tile_k) == (c["tile_m"], c["tile_n"], c["tile_k"])
+    t = blas.int8_tile_config(512, 512, 512)
+    assert (t.tile_k, t.stages) == (k["int8_tile_hopper_plus"]["tile_k"], k["int8_tile_hopper_plus"]["stages"])
+    # the library and the oracle agree on a sweep of shapes
+    for dtype in (0, 1, 2):
+        for m in (1, 8, 64, 127, 128, 1024, 4096):
+            for n in (1, 64, 128, 1000, 4096, 14336):
+                for kk in (1, 32, 63, 64, 4096, 40000):
+                    t = blas._ref_tile(dtype, m, n, kk)
+                    assert t.as_tuple() == oracle.tile_config(dtype, m, n, kk), (dtype, m, n, kk)
+                    assert blas.classify_workload(m, n, kk).value == oracle.classify_workload(m, n, kk)
+                    assert blas.Fp8Config.compute_split_k(m, n, kk) == oracle.fp8_split_k(m, n, kk)
+
+
+def test_zero_dimension_is_invalid_dimension(libb2q):
+    from oxicuda_b200 import _lib, blas
+    with pytest.raises(_lib.InvalidDimension):
+        blas.Fp8Config.tile_config(0, 4, 4)
+    with pytest.raises(_lib.InvalidDimension):
+        blas.select_tile("fp8", 4, 0, 4)
+
+
+def test_static_tile_table(libb2q):
+    from oxicuda_b200 import blas
+    t, kid = blas.select_tile("fp8", 4096, 4096, 4096)
+    assert kid in (1, 2) and t.tile_m == 128 and t.tile_n in (128, 256) and t.tile_k == 128
+    t, kid = blas.select_tile("fp8", 8, 4096, 4096)
+    assert kid == 0                                   # decode-sized: SIMT path
+    t, kid = blas.select_tile("fp8", 4096, 4096, 4100)
+    assert kid == 0                                   # row pitch TMA cannot take
+    t, kid = blas.select_tile("fp4", 1, 4096, 4096)
+    assert kid == 3 and t.tile_m == 8 and t.tile_n == 128
+    t, kid = blas.select_tile("fp4", 32, 1024, 4096)
+    assert kid == 3 and t.tile_m == 32 and t.tile_n == 64
+
+
+def test_python_side_validation_mirrors_reference_errors(libb2q, kat):
+    import torch
+    from oxicuda_b200 import _lib, blas, quant
+    q = quant.MinMaxQuantizer.int8_symmetric()
+    with pytest.raises(_lib.EmptyInput):
+        q.calibrate(torch.empty(0))
+    with pytest.raises(_lib.EmptyInput):
+        q.calibrate_2d(torch.empty(0), 0, 4)
+    with pytest.raises(_lib.DimensionMismatch):
+        q.calibrate_2d(torch.empty(0), 2, 0)
+    for bad in kat["llm_int8"]["config_validation"]["bad"]:
+        with pytest.raises(_lib.InvalidConfig):
+            quant.LlmInt8Config.new(float(bad), True)
+    assert quant.LlmInt8Config.new(6.0, True).threshold == 6.0
+    cfg = quant.LlmInt8Config()
+    assert cfg.threshold == 6.0 and cfg.row_wise_activations
+    lq = quant.LlmInt8Quantizer()
+    with pytest.raises(_lib.EmptyInput):
+        lq.matmul(torch.empty(0), torch.ones(4), 1, 1, 4)
+    with pytest.raises(_lib.DimensionMismatch):
+        lq.matmul(torch.ones(10), torch.ones(4), 3, 1, 4)
+    for a, b in kat["fp4"]["packed_fp4_overflow_rejected"]["bad"]:
+        with pytest.raises(_lib.InvalidArgument):
+            blas.PackedFp4.pack(a, b)
+    for a in range(16):
+        for b in range(16):
+            assert blas.PackedFp4.unpack(blas.PackedFp4.pack(a, b)) == (a, b)
+    for bs in kat["fp4"]["block_size_validation"]["invalid"]:
+        with pytest.raises(_lib.InvalidArgument):
+            blas.MicroScalingConfig(block_size=bs).validate()
+    for bs in kat["fp4"]["block_size_validation"]["valid"]:
+        blas.MicroScalingConfig(block_size=bs).validate()
+    p = quant.QuantParams(torch.ones(1), torch.zeros(1, dtype=torch.int32), 8, quant.QuantScheme.Symmetric)
+    assert (p.q_max(), p.q_min()) == (kat["minmax"]["q_max_q_min_int8"]["q_max"], kat["minmax"]["q_max_q_min_int8"]["q_min"])
+
+
+def test_rank_coordinates_and_shard_ranges(libb2q):
+    from oxicuda_b200 import _lib
+    from oxicuda_b200.dist_infer import DistInferHandle, ParallelismConfig, column_shard_rows, row_shard_cols
+    cfg = ParallelismConfig(tp=2, sp=2, ep=2)
+    assert cfg.world_size() == 8
+    h = DistInferHandle(5, cfg)          # crates/oxicuda-dist-infer/src/handle.rs: tp=g%tp, sp=(g/tp)%sp, ep=g/(tp*sp)
+    assert (h.tp_rank(), h.sp_rank(), h.ep_rank()) == (1, 0, 1)
+    with pytest.raises(_lib.InvalidArgument):
+        DistInferHandle(8, cfg)
+    assert column_shard_rows(28672, 8, 3) == (3 * 3584, 4 * 3584)
+    assert row_shard_cols(28672, 4, 1) == (7168, 14336)
+    with pytest.raises(_lib.InvalidDimension):
+        column_shard_rows(10, 3, 0)
