@@ -143,7 +143,13 @@ def main():
     ap.add_argument("--impl", default="b2q", choices=["b2q", "reference"])
     ap.add_argument("--rounding", default="rne", choices=["rne", "ref"], help="E4M3 encoder used to make the operands")
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMV / INT8 side measurements")
+    ap.add_argument("--case", default=None,
+                    help="run ONE kernel case a few times and exit (for ncu captures): gemm_fp8:M:N:K | gemv_fp4:K:N:tokens")
+    ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args()
+    if args.case:
+        run_case(args.case, args.iters)
+        return
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -293,6 +299,46 @@ def main():
         dist.destroy_process_group()
 
 
+def run_case(case: str, iters: int):
+    """One kernel on synthetic operands, `iters` launches, CUDA-event time of the last ones printed."""
+    import torch
+    from oxicuda_b200.blas import MicroScalingConfig, MicroScalingQuantizer, ScalingFormat, gemm_fp8, gemv_fp4_wo
+    from oxicuda_b200.quant import Fp8Codec
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    kind, *dims = case.split(":")
+    d = [int(v) for v in dims]
+    if kind == "gemm_fp8":
+        m, n, k = d
+        codec = Fp8Codec.e4m3("rne")
+        ac, sa = codec.quantize_rows(torch.randn(m, k, device=dev), 1, m * k)
+        wc, sw = codec.quantize_rows(torch.randn(n, k, device=dev) * 0.02, 1, n * k)
+        out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        fn = lambda: gemm_fp8(ac.view(m, k), wc.view(n, k), sa, sw, out=out)
+        work, unit = 2.0 * m * n * k / 1e12, "TFLOP/s"
+    elif kind == "gemv_fp4":
+        k, n, tokens = d
+        codes, scales = MicroScalingQuantizer(MicroScalingConfig(32, ScalingFormat.E8M0)).quantize_fp4(torch.randn(n * k, device=dev) * 0.02)
+        x = torch.randn(tokens, k, device=dev).to(torch.bfloat16)
+        out = torch.empty(tokens, n, dtype=torch.bfloat16, device=dev)
+        fn = lambda: gemv_fp4_wo(codes, scales, x, n, k, out=out)
+        work, unit = (n * k // 2 + n * k // 32 + 2 * tokens * k + 2 * tokens * n) / 1e9, "GB/s"
+    else:
+        raise SystemExit(f"unknown case {case}")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    times = []
+    for _ in range(iters):
+        flush.zero_()                                  # evict the operands from L2 between launches
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e-3)
+    best = min(times)
+    print(json.dumps({"case": case, "iters": iters, "best_us": best * 1e6, "rate": work / best, "unit": unit}))
+
+
 def _time_calls(fn, iters, warm=5):
     import torch
     for i in range(warm):
@@ -352,10 +398,15 @@ def side_measurements(dev, peaks):
             x = torch.randn(tokens, Kd, device=dev).to(torch.bfloat16)
             out = torch.empty(tokens, Nd, dtype=torch.bfloat16, device=dev)
             call = lambda i: gemv_fp4_wo(ws[i % copies][0], ws[i % copies][1], x, Nd, Kd, out=out)
-            sec = _time_graph(call, 4 * copies)
-            sec_eager = _time_calls(call, 100, 10)
+            key = f"k{Kd}_n{Nd}_m{tokens}"
+            try:
+                sec = _time_graph(call, 4 * copies)
+                sec_eager = _time_calls(call, 100, 10)
+            except Exception as exc:
+                res["gemv_fp4_e8m0"][key] = {"error": repr(exc)}
+                continue
             nbytes = Nd * Kd // 2 + Nd * Kd // 32 + 2 * tokens * Kd + 2 * tokens * Nd
-            res["gemv_fp4_e8m0"][f"k{Kd}_n{Nd}_m{tokens}"] = {
+            res["gemv_fp4_e8m0"][key] = {
                 "us": sec * 1e6, "us_eager_launch": sec_eager * 1e6, "gbs": nbytes / sec / 1e9,
                 "frac_of_measured_hbm": nbytes / sec / 1e9 / peaks["hbm_gbs"]}
         del ws

@@ -149,6 +149,68 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   nb = in_group / gm;
 }
 
+// Scales, converts and stores 32 consecutive accumulator columns of one output row.
+template <int KIND>
+__device__ __forceinline__ void store_chunk(const Params& p, const uint32_t (&r)[32], int64_t m, int64_t n, float sa, float sw0) {
+  const bool full = n + 32 <= p.N;
+  if constexpr (KIND == kF8) {
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) {
+      const float sw = p.scale_w_rows ? (n + j < p.N ? __ldg(p.scale_w + n + j) : 0.0f) : sw0;
+      v[j] = __uint_as_float(r[j]) * (sa * sw);
+    }
+    if (p.out_type == B2Q_OUT_BF16) {
+      __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + m * p.N + n;
+      if (full && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          uint4 pk;
+          __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]), h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+          __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+          pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+          pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+          *reinterpret_cast<uint4*>(o + j) = pk;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (n + j < p.N) o[j] = __float2bfloat16_rn(v[j]);
+      }
+    } else {
+      float* o = reinterpret_cast<float*>(p.out) + m * p.N + n;
+      if (full && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (n + j < p.N) o[j] = v[j];
+      }
+    }
+  } else {
+    if (p.c_s32) {
+      int32_t* o = p.c_s32 + m * p.N + n;
+      if (full && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) if (n + j < p.N) o[j] = (int32_t)r[j];
+      }
+    }
+    if (p.c_f32) {
+      float* o = p.c_f32 + m * p.N + n;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        if (n + j < p.N) {
+          float f = __int2float_rn((int32_t)r[j]);
+          if (p.scale_a) f = __fmul_rn(f, __fmul_rn(sa, p.scale_w[n + j]));
+          o[j] = f;
+        }
+      }
+    }
+  }
+}
+
 template <int BN, int KIND>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const Params p) {
@@ -273,63 +335,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         tmem_ld_wait();
         const int64_t n = n0 + c;
         if (!row_ok || n >= p.N) continue;
-        const bool full = n + 32 <= p.N;
-        if constexpr (KIND == kF8) {
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const float sw = p.scale_w_rows ? (n + j < p.N ? __ldg(p.scale_w + n + j) : 0.0f) : sw0;
-            v[j] = __uint_as_float(r[j]) * (sa * sw);
-          }
-          if (p.out_type == B2Q_OUT_BF16) {
-            __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + m * p.N + n;
-            if (full && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 pk;
-                __nv_bfloat162 h0 = __floats2bfloat162_rn(v[j], v[j + 1]), h1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                __nv_bfloat162 h2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), h3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
-                pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
-                *reinterpret_cast<uint4*>(o + j) = pk;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) if (n + j < p.N) o[j] = __float2bfloat16_rn(v[j]);
-            }
-          } else {
-            float* o = reinterpret_cast<float*>(p.out) + m * p.N + n;
-            if (full && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) if (n + j < p.N) o[j] = v[j];
-            }
-          }
-        } else {
-          if (p.c_s32) {
-            int32_t* o = p.c_s32 + m * p.N + n;
-            if (full && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) if (n + j < p.N) o[j] = (int32_t)r[j];
-            }
-          }
-          if (p.c_f32) {
-            float* o = p.c_f32 + m * p.N + n;
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (n + j < p.N) {
-                float f = __int2float_rn((int32_t)r[j]);
-                if (p.scale_a) f = __fmul_rn(f, __fmul_rn(sa, p.scale_w[n + j]));
-                o[j] = f;
-              }
-            }
-          }
-        }
+        store_chunk<KIND>(p, r, m, n, sa, sw0);
       }
       tc_fence_before();
       __syncwarp();
@@ -346,6 +352,214 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   }
   if (threadIdx.x == 0 && s_abort) atomicCAS(p.status, 0, (int)B2Q_ERR_TIMEOUT);
 }
+
+
+// =============================================================================
+// Two-CTA variant (cta_group::2): a cluster of two CTAs on one TPC computes a
+// 256 x 256 output tile.  Each CTA stages its own 128 rows of A and its own 128
+// rows of W per K block (32 KiB per stage instead of 48 KiB), the leader CTA
+// issues one tcgen05.mma.cta_group::2 per 32-wide K step that reads both CTAs'
+// shared memory, and each CTA's TMEM receives its 128 accumulator rows.  Shared
+// memory traffic per SM drops from 192 to 128 bytes per MMA-clock, which is what
+// bounds the one-CTA kernel.  No TMA multicast: each CTA loads its own halves and
+// signals the leader's "full" barrier; stage release and accumulator hand-off use
+// tcgen05.commit with a two-CTA mask.
+// =============================================================================
+namespace two {
+
+constexpr int BN2 = 256;                 // output columns of the pair tile
+constexpr int kStages = 6;
+constexpr int kBytesA = BM * BK;         // this CTA's 128 rows of A
+constexpr int kBytesB = (BN2 / 2) * BK;  // this CTA's 128 rows of W
+constexpr int kStageBytes = kBytesA + kBytesB;
+constexpr int kTmemCols = 2 * BN2;
+constexpr int kSmem = kStages * kStageBytes + 1024 + 256;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load into THIS CTA's shared memory; the byte count is credited to `bar`, a shared::cluster address
+// (the leader CTA's barrier).  No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// arrive on the barrier at this shared-memory offset in both CTAs of the pair once the MMAs issued so far are done
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+template <int KIND>
+__device__ __forceinline__ void umma2(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  if constexpr (KIND == kF8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  }
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const Params p) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = base + kStages * kStageBytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 2 + b); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * kStages + 4);
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0 = leader (issues the MMAs), 1 = peer
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int total_tiles = p.tiles_m * p.tiles_n;    // tiles of 256 x 256
+  const int num_kb = (int)((p.K + BK - 1) / BK);
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 1); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 8); }   // 4 epilogue warps x 2 CTAs
+    mbar_init(drain_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
+  }
+  if (warp == 1) tmem_alloc2(smem_u32(&s_tmem_base), kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                               // both CTAs' barriers exist before anyone signals across
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  volatile int* abort_flag = &s_abort;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
+        int mb, nb;
+        tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag)) { ok = false; break; }
+          const uint32_t sa = base + s * kStageBytes, sb = sa + kBytesA;
+          const uint32_t leader_full = mapa_u32(full_bar(s), 0);
+          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * kStageBytes);   // both CTAs' bytes land on the leader's barrier
+          tma_load_2d_pair(sa, &map_a, leader_full, kb * BK, mb * 256 + (int)rank * BM);
+          tma_load_2d_pair(sb, &map_w, leader_full, kb * BK, nb * BN2 + (int)rank * (BN2 / 2));
+        }
+      }
+      if (!ok) {   // give copies already issued time to land before shared memory is released
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 1000000ull) {}
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (leader CTA only) ----------------
+    if (lane == 0 && rank == 0) {
+      uint32_t it = 0, tile_it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++tile_it) {
+        const uint32_t buf = tile_it & 1, aph = (tile_it >> 1) & 1;
+        if (!mbar_wait(tempty_bar(buf), aph ^ 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * BN2;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = base + s * kStageBytes, sb = sa + kBytesA;
+          const uint64_t adesc = make_smem_desc(sa), bdesc = make_smem_desc(sb);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            umma2<KIND>(tmem_d, adesc + (uint64_t)(k * (UMMA_K >> 4)), bdesc + (uint64_t)(k * (UMMA_K >> 4)), p.idesc,
+                        (uint32_t)((kb | k) != 0));
+          tc_commit_pair(empty_bar(s));
+        }
+        if (ok) tc_commit_pair(tfull_bar(buf));
+      }
+      if (!ok) {
+        tc_commit(drain_bar);
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(drain_bar, 0))
+          if (globaltimer_ns() - t0 > 100000000ull) break;
+      }
+    }
+  } else {
+    // ---------------- epilogue (4 warps in each CTA) ----------------
+    const int q = warp & 3;
+    uint32_t tile_it = 0;
+    bool ok = true;
+    for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++tile_it) {
+      int mb, nb;
+      tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
+      const uint32_t buf = tile_it & 1, aph = (tile_it >> 1) & 1;
+      if (!mbar_wait(tfull_bar(buf), aph, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int64_t m = (int64_t)mb * 256 + rank * BM + q * 32 + lane;
+      const int64_t n0 = (int64_t)nb * BN2;
+      const bool row_ok = m < p.M;
+      const float sa = row_ok && p.scale_a ? (p.scale_a_rows ? p.scale_a[m] : p.scale_a[0]) : 1.0f;
+      const float sw0 = p.scale_w && !p.scale_w_rows ? p.scale_w[0] : 1.0f;
+#pragma unroll 1
+      for (int c = 0; c < BN2; c += 32) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld32(tmem_base + buf * BN2 + c + ((uint32_t)(q * 32) << 16), r);
+        tmem_ld_wait();
+        const int64_t n = n0 + c;
+        if (!row_ok || n >= p.N) continue;
+        store_chunk<KIND>(p, r, m, n, sa, sw0);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(tempty_bar(buf), 0));   // the leader's MMA thread waits for both CTAs
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                               // the peer's TMEM and barriers stay valid until both CTAs are done
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc2(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && s_abort) atomicCAS(p.status, 0, (int)B2Q_ERR_TIMEOUT);
+}
+
+}  // namespace two
 
 // ---- host side --------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -404,6 +618,41 @@ int32_t launch(b2q_handle h, const void* a, const void* w, Params p) {
   return B2Q_OK;
 }
 
+// 256 x 256 pair tiles on clusters of two CTAs.
+template <int KIND>
+int32_t launch2(b2q_handle h, const void* a, const void* w, Params p) {
+  CUtensorMap map_a, map_w;
+  int32_t st = make_map(h, &map_a, a, p.M, p.K, BM);
+  if (st != B2Q_OK) return st;
+  st = make_map(h, &map_w, w, p.N, p.K, two::BN2 / 2);
+  if (st != B2Q_OK) return st;
+  p.tiles_m = (int)ceil_div64(p.M, 256);
+  p.tiles_n = (int)ceil_div64(p.N, two::BN2);
+  const uint32_t shape = ((uint32_t)(two::BN2 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+  p.idesc = KIND == kF8 ? (p.idesc | (1u << 4) | shape) : ((2u << 4) | (1u << 7) | (1u << 10) | shape);
+  static bool attr_set = false;
+  if (!attr_set) {
+    B2Q_CUDA(h, cudaFuncSetAttribute(two::gemm_tc2_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, two::kSmem));
+    attr_set = true;
+  }
+  const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
+  const int pairs = (int)(tiles < h->sm_count / 2 ? tiles : h->sm_count / 2);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * pairs));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = two::kSmem;
+  cfg.stream = h->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, two::gemm_tc2_kernel<KIND>, map_a, map_w, p));
+  return B2Q_OK;
+}
+
 }  // namespace tc
 
 int32_t b2q_validate_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,
@@ -419,6 +668,7 @@ int32_t b2q_gemm_i8_tc(b2q_handle h, const int8_t* a, const int8_t* b, int64_t M
   p.c_s32 = c_s32; p.c_f32 = c_f32; p.status = h->d_status;
   b2q_tile_config t; int kid = 0;
   b2q_select_tile(2, (uint32_t)M, (uint32_t)N, (uint32_t)K, &t, &kid);
+  if (kid == 4) return tc::launch2<tc::kI8>(h, a, b, p);
   return kid == 1 ? tc::launch<256, tc::kI8>(h, a, b, p) : tc::launch<128, tc::kI8>(h, a, b, p);
 }
 
@@ -434,6 +684,7 @@ extern "C" int32_t b2q_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w
     const char* force = getenv("B2Q_FORCE_TILE_N");
     if (force && force[0] == '1') kid = 2;
     if (force && force[0] == '2') kid = 1;
+    if (force && force[0] == 'p') kid = 4;     // "pair": the two-CTA kernel
   }
   const bool tma_ok = K % 16 == 0 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
   if (kid == 0 || !tma_ok)
@@ -444,5 +695,6 @@ extern "C" int32_t b2q_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w
   p.scale_a = scale_a; p.scale_a_rows = scale_a_kind; p.scale_w = scale_w; p.scale_w_rows = scale_w_kind;
   p.out = out; p.out_type = out_type; p.status = h->d_status;
   p.idesc = ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10);   // A/B format: 0 = E4M3, 1 = E5M2
+  if (kid == 4) return tc::launch2<tc::kF8>(h, a, w, p);
   return kid == 1 ? tc::launch<256, tc::kF8>(h, a, w, p) : tc::launch<128, tc::kF8>(h, a, w, p);
 }

@@ -20,6 +20,7 @@
 // E2M1 value is exact in f16; activations beyond +-65504 saturate.
 #include "common.cuh"
 #include <cooperative_groups.h>
+#include <stdlib.h>
 
 namespace cg = cooperative_groups;
 
@@ -246,6 +247,162 @@ int32_t launch(b2q_handle h, const uint8_t* codes, const void* scales, int scale
                                         : launch_fmt<MT, WARPS, false>(h, codes, scales, x, tokens, N, K, out, out_type);
 }
 
+// ---------------------------------------------------------------------------
+// Decode kernel for tokens <= 8 (the bandwidth-bound regime).  No clusters and no CTA-wide
+// barrier in the main loop:
+//   * a CTA owns 16 weight rows; its WK warps split K into contiguous slices of 512-wide chunks;
+//   * a warp prefetches the codes and scales of its NEXT chunk into a second register set before it
+//     multiplies the current one, so HBM loads stay in flight while the tensor core works;
+//   * each warp stages only its own slice of the activations (warp-private shared memory, __syncwarp);
+//   * one __syncthreads at the end to add the WK partial sums.
+// ---------------------------------------------------------------------------
+template <bool E8> struct ChunkRegs {
+  uint32_t wa[4][4], wb[4][4];
+  Scales4<E8> sa[4], sb[4];
+};
+
+template <bool E8>
+__device__ __forceinline__ void load_chunk(ChunkRegs<E8>& r, const uint8_t* w0, const uint8_t* w1, const void* scales,
+                                           int64_t s0, int64_t s1, int64_t k0, int64_t K) {
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    const int64_t k = k0 + s * 128;
+    if (k < K) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        r.wa[s][j] = ld_stream_u32(w0 + ((k + j * 32) >> 1));
+        r.wb[s][j] = ld_stream_u32(w1 + ((k + j * 32) >> 1));
+      }
+      r.sa[s].load(scales, s0 + (k >> 5));
+      r.sb[s].load(scales, s1 + (k >> 5));
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { r.wa[s][j] = 0; r.wb[s][j] = 0; }
+      r.sa[s].clear();
+      r.sb[s].clear();
+    }
+  }
+}
+
+template <bool E8>
+__device__ __forceinline__ void mul_chunk(const ChunkRegs<E8>& r, const uint4* xs, int g, int tig, float (&acc)[4]) {
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t ha[4], hb[4];
+      cvt_e2m1x8(r.wa[s][j], ha);
+      cvt_e2m1x8(r.wb[s][j], hb);
+      const uint4 xv = xs[((s * 4 + j) * 8 + g) * 4 + tig];
+      float d[4];
+      mma_f16_zero(d, ha[0], hb[0], ha[1], hb[1], xv.x, xv.y);
+      mma_f16(d, ha[2], hb[2], ha[3], hb[3], xv.z, xv.w);
+      const float fa = r.sa[s].get(j), fb = r.sb[s].get(j);
+      acc[0] = fmaf(fa, d[0], acc[0]);
+      acc[1] = fmaf(fa, d[1], acc[1]);
+      acc[2] = fmaf(fb, d[2], acc[2]);
+      acc[3] = fmaf(fb, d[3], acc[3]);
+    }
+  }
+}
+
+// Stages activations [tokens x 512] of chunk k0 into this warp's buffer (f16, fragment order).
+__device__ __forceinline__ void stage_x_warp(uint4* xs, const __nv_bfloat16* x, int tokens, int64_t K, int64_t k0, int lane) {
+  __syncwarp();                                          // the previous chunk's fragment reads are done
+  const int pieces = 64 * tokens;                        // 16 blocks x tokens x 4 quad lanes
+  for (int p = lane; p < pieces; p += 32) {
+    const int ttig = p & 3, tok = (p >> 2) % tokens, blk = (p >> 2) / tokens;
+    const int64_t k = k0 + blk * 32 + ttig * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (k < K) v = __ldg(reinterpret_cast<const uint4*>(x + (int64_t)tok * K + k));
+    uint4 h;
+    h.x = bf16x2_to_f16x2_sat(v.x); h.y = bf16x2_to_f16x2_sat(v.y);
+    h.z = bf16x2_to_f16x2_sat(v.z); h.w = bf16x2_to_f16x2_sat(v.w);
+    xs[(blk * 8 + tok) * 4 + ttig] = h;
+  }
+  __syncwarp();
+}
+
+template <bool E8, int WK>
+__global__ void __launch_bounds__(WK * 32) gemv_fp4_small_kernel(const uint8_t* __restrict__ codes, const void* __restrict__ scales,
+                                                                 const __nv_bfloat16* __restrict__ x, int tokens, int64_t N, int64_t K,
+                                                                 void* out, int out_type) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, tig = lane & 3;
+  uint4* xs = reinterpret_cast<uint4*>(smem) + warp * 512;        // [16 blocks][8 tokens][4] x 16 bytes = 8 KiB per warp
+  float* red = reinterpret_cast<float*>(smem);                    // [WK][16 rows][8 tokens], reused after the main loop
+
+  const int64_t n0 = (int64_t)blockIdx.x * 16;
+  const int64_t r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);
+  const int64_t kblocks = K >> 5;
+  const uint8_t* w0 = codes + r0 * (K >> 1) + tig * 4;
+  const uint8_t* w1 = codes + r1 * (K >> 1) + tig * 4;
+  const int64_t s0 = r0 * kblocks, s1 = r1 * kblocks;
+
+  const int chunks_total = (int)((K + KC - 1) / KC);
+  const int cpw = (chunks_total + WK - 1) / WK;
+  int c = warp * cpw;
+  const int c_end = min(c + cpw, chunks_total);
+
+  ChunkRegs<E8> A, B;
+  if (c < c_end) load_chunk<E8>(A, w0, w1, scales, s0, s1, (int64_t)c * KC, K);
+  // rows of the fragment buffer that belong to no token stay zero for the whole kernel
+  for (int p = lane; p < 512; p += 32) xs[p] = make_uint4(0, 0, 0, 0);
+
+  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  while (c < c_end) {
+    if (c + 1 < c_end) load_chunk<E8>(B, w0, w1, scales, s0, s1, (int64_t)(c + 1) * KC, K);
+    stage_x_warp(xs, x, tokens, K, (int64_t)c * KC, lane);
+    mul_chunk<E8>(A, xs, g, tig, acc);
+    if (++c >= c_end) break;
+    if (c + 1 < c_end) load_chunk<E8>(A, w0, w1, scales, s0, s1, (int64_t)(c + 1) * KC, K);
+    stage_x_warp(xs, x, tokens, K, (int64_t)c * KC, lane);
+    mul_chunk<E8>(B, xs, g, tig, acc);
+    ++c;
+  }
+
+  __syncthreads();                                       // every warp is done with its activation buffer
+  // acc[0],acc[1]: row g, tokens 2*tig, 2*tig+1;  acc[2],acc[3]: row g+8
+  red[(warp * 16 + g) * 8 + tig * 2 + 0] = acc[0];
+  red[(warp * 16 + g) * 8 + tig * 2 + 1] = acc[1];
+  red[(warp * 16 + g + 8) * 8 + tig * 2 + 0] = acc[2];
+  red[(warp * 16 + g + 8) * 8 + tig * 2 + 1] = acc[3];
+  __syncthreads();
+  for (int e = threadIdx.x; e < 16 * tokens; e += WK * 32) {
+    const int tok = e >> 4, row = e & 15;               // consecutive threads -> consecutive output rows
+    float v = 0.0f;
+#pragma unroll
+    for (int w = 0; w < WK; ++w) v += red[(w * 16 + row) * 8 + tok];
+    const int64_t n = n0 + row;
+    if (n < N) {
+      if (out_type == B2Q_OUT_BF16) reinterpret_cast<__nv_bfloat16*>(out)[(int64_t)tok * N + n] = __float2bfloat16_rn(v);
+      else reinterpret_cast<float*>(out)[(int64_t)tok * N + n] = v;
+    }
+  }
+}
+
+template <int WK>
+int32_t launch_small(b2q_handle h, const uint8_t* codes, const void* scales, int scale_format, const void* x, int tokens, int64_t N,
+                     int64_t K, void* out, int out_type) {
+  const unsigned grid = (unsigned)ceil_div64(N, 16);
+  const size_t smem = (size_t)WK * 8192;
+  if (smem > 48 * 1024) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      B2Q_CUDA(h, cudaFuncSetAttribute(gemv_fp4_small_kernel<true, WK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      B2Q_CUDA(h, cudaFuncSetAttribute(gemv_fp4_small_kernel<false, WK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      attr_set = true;
+    }
+  }
+  if (scale_format == B2Q_SCALE_E8M0)
+    gemv_fp4_small_kernel<true, WK><<<grid, WK * 32, smem, h->stream>>>(codes, scales, (const __nv_bfloat16*)x, tokens, N, K, out, out_type);
+  else
+    gemv_fp4_small_kernel<false, WK><<<grid, WK * 32, smem, h->stream>>>(codes, scales, (const __nv_bfloat16*)x, tokens, N, K, out, out_type);
+  B2Q_LAUNCH_CHECK(h, "gemv_fp4_small_kernel");
+  return B2Q_OK;
+}
+
 }  // namespace gemv
 
 extern "C" int32_t b2q_gemv_fp4_wo(b2q_handle h, const uint8_t* codes, const void* scales, int scale_format, int block,
@@ -267,8 +424,15 @@ extern "C" int32_t b2q_gemv_fp4_wo(b2q_handle h, const uint8_t* codes, const voi
     B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemv_fp4_wo: scales must be 4-byte (E8M0) or 16-byte (f32) aligned");
   const int t = (int)tokens;
   const bool small_n = N <= 2048;
-  if (t <= 8) return small_n ? gemv::launch<1, 4>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type)
-                             : gemv::launch<1, 8>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type);
+  if (t <= 8) {
+    // experiment switch: B2Q_GEMV_CLUSTER=1 takes the cluster split-K kernel for small token counts too
+    const char* force = getenv("B2Q_GEMV_CLUSTER");
+    if (force && force[0] == '1')
+      return small_n ? gemv::launch<1, 4>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type)
+                     : gemv::launch<1, 8>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type);
+    return K >= 8192 ? gemv::launch_small<8>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type)
+                     : gemv::launch_small<4>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type);
+  }
   if (t <= 16) return small_n ? gemv::launch<2, 4>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type)
                               : gemv::launch<2, 8>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type);
   return small_n ? gemv::launch<4, 4>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type)

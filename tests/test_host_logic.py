@@ -80,7 +80,9 @@ def test_zero_dimension_is_invalid_dimension(libb2q):
 def test_static_tile_table(libb2q):
     from oxicuda_b200 import blas
     t, kid = blas.select_tile("fp8", 4096, 4096, 4096)
-    assert kid in (1, 2) and t.tile_m == 128 and t.tile_n in (128, 256) and t.tile_k == 128
+    assert kid == 4 and (t.tile_m, t.tile_n, t.tile_k) == (256, 256, 128)      # two-CTA pair tiles
+    t, kid = blas.select_tile("fp8", 128, 4096, 4096)
+    assert kid in (1, 2) and t.tile_m == 128 and t.tile_n in (128, 256)
     t, kid = blas.select_tile("fp8", 8, 4096, 4096)
     assert kid == 0                                   # decode-sized: SIMT path
     t, kid = blas.select_tile("fp8", 4096, 4096, 4100)
