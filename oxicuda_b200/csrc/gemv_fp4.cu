@@ -35,8 +35,11 @@ __device__ __forceinline__ uint32_t ld_stream_u32(const void* p) {
 }
 
 // Four bytes (eight E2M1 codes) -> four f16x2 registers; low nibble is the low half.
+// (Plain asm, not volatile: these are pure functions, and the scheduler must be free to interleave the
+// conversions, MMAs and FMAs of different scale blocks — in program order the chain cvt -> mma -> mma -> fma
+// leaves the pipes idle.)
 __device__ __forceinline__ void cvt_e2m1x8(uint32_t w, uint32_t (&h)[4]) {
-  asm volatile(
+  asm(
       "{\n\t.reg .b8 b0, b1, b2, b3;\n\t"
       "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
       "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
@@ -47,12 +50,12 @@ __device__ __forceinline__ void cvt_e2m1x8(uint32_t w, uint32_t (&h)[4]) {
 }
 // d = a * b (+ 0): first MMA of a scale block
 __device__ __forceinline__ void mma_f16_zero(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%10, %10, %10, %10};"
       : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.0f));
 }
 __device__ __forceinline__ void mma_f16(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
       : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -248,33 +251,63 @@ int32_t launch(b2q_handle h, const uint8_t* codes, const void* scales, int scale
 }
 
 // ---------------------------------------------------------------------------
-// Decode kernel for tokens <= 8 (the bandwidth-bound regime).  No clusters and no CTA-wide
-// barrier in the main loop:
+// Decode kernel for tokens <= 8 (the bandwidth-bound regime).  The kernel is bound by instruction issue
+// long before HBM, so the inner loop is kept to the conversions, two MMAs and four FMAs per scale block:
 //   * a CTA owns 16 weight rows; its WK warps split K into contiguous slices of 512-wide chunks;
 //   * a warp prefetches the codes and scales of its NEXT chunk into a second register set before it
 //     multiplies the current one, so HBM loads stay in flight while the tensor core works;
-//   * each warp stages only its own slice of the activations (warp-private shared memory, __syncwarp);
+//   * each warp stages only its own slice of the activations (warp-private shared memory, __syncwarp),
+//     TOK = 1, 2, 4 or 8 token rows so that all index arithmetic is shifts;
 //   * one __syncthreads at the end to add the WK partial sums.
 // ---------------------------------------------------------------------------
-template <bool E8> struct ChunkRegs {
-  uint32_t wa[4][4], wb[4][4];
-  Scales4<E8> sa[4], sb[4];
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2_satfinite(uint32_t v) {
+  uint32_t r;
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(__uint_as_float(v & 0xFFFF0000u)), "f"(__uint_as_float(v << 16)));
+  return r;
+}
+
+// E8M0 byte j of a packed word -> 2^(b-127) as fp32 bits (b == 0, i.e. 2^-127, reads as 0)
+__device__ __forceinline__ float e8m0_word_get(uint32_t w, int j) {
+  return __uint_as_float(j == 3 ? ((w >> 1) & 0x7F800000u) : ((w << (23 - 8 * j)) & 0x7F800000u));
+}
+
+template <bool E8> struct StepScales;
+template <> struct StepScales<true> {
+  uint32_t w;
+  __device__ __forceinline__ void load(const void* base, int64_t idx) {
+    w = __ldg(reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(base) + idx));
+  }
+  __device__ __forceinline__ void clear() { w = 0; }
+  __device__ __forceinline__ float get(int j) const { return e8m0_word_get(w, j); }
+};
+template <> struct StepScales<false> {
+  float4 v;
+  __device__ __forceinline__ void load(const void* base, int64_t idx) {
+    v = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(base) + idx));
+  }
+  __device__ __forceinline__ void clear() { v = make_float4(0.f, 0.f, 0.f, 0.f); }
+  __device__ __forceinline__ float get(int j) const { return j == 0 ? v.x : j == 1 ? v.y : j == 2 ? v.z : v.w; }
 };
 
+template <bool E8> struct ChunkRegs {
+  uint32_t wa[4][4], wb[4][4];
+  StepScales<E8> sa[4], sb[4];
+};
+
+// w0/w1: this lane's byte inside the chunk's first block of row g / g+8; s0/s1: scale index of that block
 template <bool E8>
 __device__ __forceinline__ void load_chunk(ChunkRegs<E8>& r, const uint8_t* w0, const uint8_t* w1, const void* scales,
-                                           int64_t s0, int64_t s1, int64_t k0, int64_t K) {
+                                           int64_t s0, int64_t s1, int steps) {
 #pragma unroll
   for (int s = 0; s < 4; ++s) {
-    const int64_t k = k0 + s * 128;
-    if (k < K) {
+    if (s < steps) {
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        r.wa[s][j] = ld_stream_u32(w0 + ((k + j * 32) >> 1));
-        r.wb[s][j] = ld_stream_u32(w1 + ((k + j * 32) >> 1));
+        r.wa[s][j] = ld_stream_u32(w0 + s * 64 + j * 16);
+        r.wb[s][j] = ld_stream_u32(w1 + s * 64 + j * 16);
       }
-      r.sa[s].load(scales, s0 + (k >> 5));
-      r.sb[s].load(scales, s1 + (k >> 5));
+      r.sa[s].load(scales, s0 + s * 4);
+      r.sb[s].load(scales, s1 + s * 4);
     } else {
 #pragma unroll
       for (int j = 0; j < 4; ++j) { r.wa[s][j] = 0; r.wb[s][j] = 0; }
@@ -285,7 +318,7 @@ __device__ __forceinline__ void load_chunk(ChunkRegs<E8>& r, const uint8_t* w0, 
 }
 
 template <bool E8>
-__device__ __forceinline__ void mul_chunk(const ChunkRegs<E8>& r, const uint4* xs, int g, int tig, float (&acc)[4]) {
+__device__ __forceinline__ void mul_chunk(const ChunkRegs<E8>& r, const uint4* xs_lane, float (&acc)[4]) {
 #pragma unroll
   for (int s = 0; s < 4; ++s) {
 #pragma unroll
@@ -293,7 +326,7 @@ __device__ __forceinline__ void mul_chunk(const ChunkRegs<E8>& r, const uint4* x
       uint32_t ha[4], hb[4];
       cvt_e2m1x8(r.wa[s][j], ha);
       cvt_e2m1x8(r.wb[s][j], hb);
-      const uint4 xv = xs[((s * 4 + j) * 8 + g) * 4 + tig];
+      const uint4 xv = xs_lane[(s * 4 + j) * 32];          // [block][8 token rows][4 quad lanes]
       float d[4];
       mma_f16_zero(d, ha[0], hb[0], ha[1], hb[1], xv.x, xv.y);
       mma_f16(d, ha[2], hb[2], ha[3], hb[3], xv.z, xv.w);
@@ -306,25 +339,28 @@ __device__ __forceinline__ void mul_chunk(const ChunkRegs<E8>& r, const uint4* x
   }
 }
 
-// Stages activations [tokens x 512] of chunk k0 into this warp's buffer (f16, fragment order).
-__device__ __forceinline__ void stage_x_warp(uint4* xs, const __nv_bfloat16* x, int tokens, int64_t K, int64_t k0, int lane) {
+// Stages activations [tokens x 512] of one chunk into this warp's buffer (f16, fragment order).
+// TOK (power of two >= tokens) rows are written; rows TOK..7 of the buffer stay zero.
+template <int TOK>
+__device__ __forceinline__ void stage_x_warp(uint4* xs, const __nv_bfloat16* xk, int tokens, int64_t K, int k_left, int lane) {
   __syncwarp();                                          // the previous chunk's fragment reads are done
-  const int pieces = 64 * tokens;                        // 16 blocks x tokens x 4 quad lanes
-  for (int p = lane; p < pieces; p += 32) {
-    const int ttig = p & 3, tok = (p >> 2) % tokens, blk = (p >> 2) / tokens;
-    const int64_t k = k0 + blk * 32 + ttig * 8;
+#pragma unroll
+  for (int i = 0; i < 2 * TOK; ++i) {
+    const int p = lane + 32 * i;                         // 64 * TOK pieces of 8 activations
+    const int ttig = p & 3, tok = (p >> 2) & (TOK - 1), blk = p / (4 * TOK);
+    const int k = blk * 32 + ttig * 8;
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (k < K) v = __ldg(reinterpret_cast<const uint4*>(x + (int64_t)tok * K + k));
+    if (tok < tokens && k < k_left) v = __ldg(reinterpret_cast<const uint4*>(xk + (int64_t)tok * K + k));
     uint4 h;
-    h.x = bf16x2_to_f16x2_sat(v.x); h.y = bf16x2_to_f16x2_sat(v.y);
-    h.z = bf16x2_to_f16x2_sat(v.z); h.w = bf16x2_to_f16x2_sat(v.w);
+    h.x = bf16x2_to_f16x2_satfinite(v.x); h.y = bf16x2_to_f16x2_satfinite(v.y);
+    h.z = bf16x2_to_f16x2_satfinite(v.z); h.w = bf16x2_to_f16x2_satfinite(v.w);
     xs[(blk * 8 + tok) * 4 + ttig] = h;
   }
   __syncwarp();
 }
 
-template <bool E8, int WK>
-__global__ void __launch_bounds__(WK * 32) gemv_fp4_small_kernel(const uint8_t* __restrict__ codes, const void* __restrict__ scales,
+template <bool E8, int WK, int TOK>
+__global__ void __launch_bounds__(WK * 32, 512 / (WK * 32)) gemv_fp4_small_kernel(const uint8_t* __restrict__ codes, const void* __restrict__ scales,
                                                                  const __nv_bfloat16* __restrict__ x, int tokens, int64_t N, int64_t K,
                                                                  void* out, int out_type) {
   extern __shared__ __align__(16) uint8_t smem[];
@@ -336,30 +372,36 @@ __global__ void __launch_bounds__(WK * 32) gemv_fp4_small_kernel(const uint8_t* 
   const int64_t n0 = (int64_t)blockIdx.x * 16;
   const int64_t r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);
   const int64_t kblocks = K >> 5;
-  const uint8_t* w0 = codes + r0 * (K >> 1) + tig * 4;
-  const uint8_t* w1 = codes + r1 * (K >> 1) + tig * 4;
-  const int64_t s0 = r0 * kblocks, s1 = r1 * kblocks;
 
   const int chunks_total = (int)((K + KC - 1) / KC);
   const int cpw = (chunks_total + WK - 1) / WK;
   int c = warp * cpw;
   const int c_end = min(c + cpw, chunks_total);
+  const int total_steps = (int)(K >> 7);                          // 128-wide steps in a row
+
+  const uint8_t* w0 = codes + r0 * (K >> 1) + tig * 4 + (int64_t)c * (KC / 2);
+  const uint8_t* w1 = codes + r1 * (K >> 1) + tig * 4 + (int64_t)c * (KC / 2);
+  int64_t s0 = r0 * kblocks + (int64_t)c * (KC / 32), s1 = r1 * kblocks + (int64_t)c * (KC / 32);
+  const __nv_bfloat16* xk = x + (int64_t)c * KC;
 
   ChunkRegs<E8> A, B;
-  if (c < c_end) load_chunk<E8>(A, w0, w1, scales, s0, s1, (int64_t)c * KC, K);
+  if (c < c_end) load_chunk<E8>(A, w0, w1, scales, s0, s1, min(4, total_steps - c * 4));
   // rows of the fragment buffer that belong to no token stay zero for the whole kernel
-  for (int p = lane; p < 512; p += 32) xs[p] = make_uint4(0, 0, 0, 0);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) xs[lane + 32 * i] = make_uint4(0, 0, 0, 0);
+  const uint4* xs_lane = xs + g * 4 + tig;
 
   float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
   while (c < c_end) {
-    if (c + 1 < c_end) load_chunk<E8>(B, w0, w1, scales, s0, s1, (int64_t)(c + 1) * KC, K);
-    stage_x_warp(xs, x, tokens, K, (int64_t)c * KC, lane);
-    mul_chunk<E8>(A, xs, g, tig, acc);
-    if (++c >= c_end) break;
-    if (c + 1 < c_end) load_chunk<E8>(A, w0, w1, scales, s0, s1, (int64_t)(c + 1) * KC, K);
-    stage_x_warp(xs, x, tokens, K, (int64_t)c * KC, lane);
-    mul_chunk<E8>(B, xs, g, tig, acc);
-    ++c;
+    if (c + 1 < c_end) load_chunk<E8>(B, w0 + KC / 2, w1 + KC / 2, scales, s0 + KC / 32, s1 + KC / 32, min(4, total_steps - (c + 1) * 4));
+    stage_x_warp<TOK>(xs, xk, tokens, K, (int)min((int64_t)KC, K - (int64_t)c * KC), lane);
+    mul_chunk<E8>(A, xs_lane, acc);
+    ++c; w0 += KC / 2; w1 += KC / 2; s0 += KC / 32; s1 += KC / 32; xk += KC;
+    if (c >= c_end) break;
+    if (c + 1 < c_end) load_chunk<E8>(A, w0 + KC / 2, w1 + KC / 2, scales, s0 + KC / 32, s1 + KC / 32, min(4, total_steps - (c + 1) * 4));
+    stage_x_warp<TOK>(xs, xk, tokens, K, (int)min((int64_t)KC, K - (int64_t)c * KC), lane);
+    mul_chunk<E8>(B, xs_lane, acc);
+    ++c; w0 += KC / 2; w1 += KC / 2; s0 += KC / 32; s1 += KC / 32; xk += KC;
   }
 
   __syncthreads();                                       // every warp is done with its activation buffer
@@ -382,25 +424,31 @@ __global__ void __launch_bounds__(WK * 32) gemv_fp4_small_kernel(const uint8_t* 
   }
 }
 
-template <int WK>
-int32_t launch_small(b2q_handle h, const uint8_t* codes, const void* scales, int scale_format, const void* x, int tokens, int64_t N,
-                     int64_t K, void* out, int out_type) {
+template <bool E8, int WK, int TOK>
+int32_t launch_small_t(b2q_handle h, const uint8_t* codes, const void* scales, const void* x, int tokens, int64_t N, int64_t K,
+                       void* out, int out_type) {
   const unsigned grid = (unsigned)ceil_div64(N, 16);
   const size_t smem = (size_t)WK * 8192;
   if (smem > 48 * 1024) {
     static bool attr_set = false;
     if (!attr_set) {
-      B2Q_CUDA(h, cudaFuncSetAttribute(gemv_fp4_small_kernel<true, WK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      B2Q_CUDA(h, cudaFuncSetAttribute(gemv_fp4_small_kernel<false, WK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      B2Q_CUDA(h, cudaFuncSetAttribute(gemv_fp4_small_kernel<E8, WK, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
       attr_set = true;
     }
   }
-  if (scale_format == B2Q_SCALE_E8M0)
-    gemv_fp4_small_kernel<true, WK><<<grid, WK * 32, smem, h->stream>>>(codes, scales, (const __nv_bfloat16*)x, tokens, N, K, out, out_type);
-  else
-    gemv_fp4_small_kernel<false, WK><<<grid, WK * 32, smem, h->stream>>>(codes, scales, (const __nv_bfloat16*)x, tokens, N, K, out, out_type);
+  gemv_fp4_small_kernel<E8, WK, TOK><<<grid, WK * 32, smem, h->stream>>>(codes, scales, (const __nv_bfloat16*)x, tokens, N, K, out, out_type);
   B2Q_LAUNCH_CHECK(h, "gemv_fp4_small_kernel");
   return B2Q_OK;
+}
+
+template <int WK>
+int32_t launch_small(b2q_handle h, const uint8_t* codes, const void* scales, int scale_format, const void* x, int tokens, int64_t N,
+                     int64_t K, void* out, int out_type) {
+#define B2Q_SMALL(E8, TOK) launch_small_t<E8, WK, TOK>(h, codes, scales, x, tokens, N, K, out, out_type)
+  if (scale_format == B2Q_SCALE_E8M0)
+    return tokens == 1 ? B2Q_SMALL(true, 1) : tokens == 2 ? B2Q_SMALL(true, 2) : tokens <= 4 ? B2Q_SMALL(true, 4) : B2Q_SMALL(true, 8);
+  return tokens == 1 ? B2Q_SMALL(false, 1) : tokens == 2 ? B2Q_SMALL(false, 2) : tokens <= 4 ? B2Q_SMALL(false, 4) : B2Q_SMALL(false, 8);
+#undef B2Q_SMALL
 }
 
 }  // namespace gemv
