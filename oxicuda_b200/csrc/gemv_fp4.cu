@@ -441,6 +441,202 @@ int32_t launch_small_t(b2q_handle h, const uint8_t* codes, const void* scales, c
   return B2Q_OK;
 }
 
+// ---------------------------------------------------------------------------
+// E8M0 decode kernel for tokens <= 8: 128-bit weight loads.
+// The exact kernel above needs four 4-byte loads per row and 128-wide step so that one MMA stays inside
+// one scale block; each of those warp instructions touches 8 cache lines, and the L1 wavefront rate
+// (measured 84 % of peak) bounds it.  With power-of-two scales the block scale can instead be multiplied
+// into the f16 codes before the MMA without rounding (code * 2^e is exact in f16 for -23 <= e <= 13), so a
+// lane may own a whole 32-code block: ONE 16-byte load per row and step, a quarter of the wavefronts.
+// A scale exponent outside [-23, 13] records B2Q_ERR_UNSUPPORTED in the status word (such a tensor must
+// use f32 scales, which take the exact kernel).
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
+  uint4 r;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(p));
+  return r;
+}
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+// E8M0 byte -> 2^(b-127) as f16x2 (both halves); subnormal f16 below 2^-14.  `bad` collects range violations.
+__device__ __forceinline__ uint32_t e8m0_to_h2(uint32_t b, uint32_t& bad) {
+  bad |= (b - 104u) > 36u ? 1u : 0u;                     // exponent outside [-23, 13]
+  const int ee = (int)b - 112;                           // f16 exponent field
+  const uint32_t h = ee > 0 ? ((uint32_t)min(ee, 30) << 10) : (ee > -10 ? (0x0400u >> (1 - ee)) : 0u);
+  return h * 0x00010001u;
+}
+
+struct ChunkRegsE8 {
+  uint4 wa[4], wb[4];      // one 32-code block per step for row g and row g+8
+  uint4 sa, sb;            // the 16 scale bytes of the chunk for both rows
+};
+
+__device__ __forceinline__ void load_chunk_e8(ChunkRegsE8& r, const uint8_t* w0, const uint8_t* w1, const uint8_t* s0,
+                                              const uint8_t* s1, int steps) {
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    if (s < steps) {
+      r.wa[s] = ld_stream_v4(w0 + s * 64);
+      r.wb[s] = ld_stream_v4(w1 + s * 64);
+    } else {
+      r.wa[s] = make_uint4(0, 0, 0, 0);
+      r.wb[s] = make_uint4(0, 0, 0, 0);
+    }
+  }
+  if (steps == 4 && ((reinterpret_cast<uintptr_t>(s0) | reinterpret_cast<uintptr_t>(s1)) & 15) == 0) {
+    r.sa = __ldg(reinterpret_cast<const uint4*>(s0));
+    r.sb = __ldg(reinterpret_cast<const uint4*>(s1));
+  } else {                                               // ragged tail or K % 512 != 0: word loads stay aligned and inside the row
+    uint32_t a[4] = {0, 0, 0, 0}, b[4] = {0, 0, 0, 0};
+    for (int s = 0; s < steps; ++s) {
+      a[s] = __ldg(reinterpret_cast<const uint32_t*>(s0) + s);
+      b[s] = __ldg(reinterpret_cast<const uint32_t*>(s1) + s);
+    }
+    r.sa = make_uint4(a[0], a[1], a[2], a[3]);
+    r.sb = make_uint4(b[0], b[1], b[2], b[3]);
+  }
+}
+
+__device__ __forceinline__ void mul_chunk_e8(const ChunkRegsE8& r, const uint4* xs_lane, int tig, float (&acc0)[4],
+                                             float (&acc1)[4], uint32_t& bad) {
+  const uint32_t saw[4] = {r.sa.x, r.sa.y, r.sa.z, r.sa.w};
+  const uint32_t sbw[4] = {r.sb.x, r.sb.y, r.sb.z, r.sb.w};
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    const uint32_t ha2 = e8m0_to_h2((saw[s] >> (8 * tig)) & 0xFFu, bad);
+    const uint32_t hb2 = e8m0_to_h2((sbw[s] >> (8 * tig)) & 0xFFu, bad);
+    const uint32_t wav[4] = {r.wa[s].x, r.wa[s].y, r.wa[s].z, r.wa[s].w};
+    const uint32_t wbv[4] = {r.wb[s].x, r.wb[s].y, r.wb[s].z, r.wb[s].w};
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {                     // 8 codes per row: two MMA k-steps
+      uint32_t ha[4], hb[4];
+      cvt_e2m1x8(wav[jj], ha);
+      cvt_e2m1x8(wbv[jj], hb);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { ha[i] = hmul2_u32(ha[i], ha2); hb[i] = hmul2_u32(hb[i], hb2); }
+      const uint4 xv = xs_lane[(s * 4 + jj) * 32];        // [step][jj][8 token rows][4 quad lanes]
+      mma_f16(acc0, ha[0], hb[0], ha[1], hb[1], xv.x, xv.y);
+      mma_f16(acc1, ha[2], hb[2], ha[3], hb[3], xv.z, xv.w);
+    }
+  }
+}
+
+// Activations of one chunk for the block-per-lane mapping: piece (step, jj, token, quad lane) holds
+// x[token][step*128 + lane*32 + jj*8 .. +8).
+template <int TOK>
+__device__ __forceinline__ void stage_x_warp_e8(uint4* xs, const __nv_bfloat16* xk, int tokens, int64_t K, int k_left, int lane) {
+  __syncwarp();
+#pragma unroll
+  for (int i = 0; i < 2 * TOK; ++i) {
+    const int p = lane + 32 * i;
+    const int ttig = p & 3, tok = (p >> 2) & (TOK - 1), sjj = p / (4 * TOK);
+    const int k = (sjj >> 2) * 128 + ttig * 32 + (sjj & 3) * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (tok < tokens && k < k_left) v = __ldg(reinterpret_cast<const uint4*>(xk + (int64_t)tok * K + k));
+    uint4 h;
+    h.x = bf16x2_to_f16x2_satfinite(v.x); h.y = bf16x2_to_f16x2_satfinite(v.y);
+    h.z = bf16x2_to_f16x2_satfinite(v.z); h.w = bf16x2_to_f16x2_satfinite(v.w);
+    xs[(sjj * 8 + tok) * 4 + ttig] = h;
+  }
+  __syncwarp();
+}
+
+template <int WK, int TOK>
+__global__ void __launch_bounds__(WK * 32, 512 / (WK * 32)) gemv_fp4_e8_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,
+                                                                               const __nv_bfloat16* __restrict__ x, int tokens, int64_t N, int64_t K,
+                                                                               void* out, int out_type, int32_t* status) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, tig = lane & 3;
+  uint4* xs = reinterpret_cast<uint4*>(smem) + warp * 512;
+  float* red = reinterpret_cast<float*>(smem);
+
+  const int64_t n0 = (int64_t)blockIdx.x * 16;
+  const int64_t r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);
+  const int64_t kblocks = K >> 5;
+  const int chunks_total = (int)((K + KC - 1) / KC);
+  const int cpw = (chunks_total + WK - 1) / WK;
+  int c = warp * cpw;
+  const int c_end = min(c + cpw, chunks_total);
+  const int total_steps = (int)(K >> 7);
+
+  const uint8_t* w0 = codes + r0 * (K >> 1) + tig * 16 + (int64_t)c * (KC / 2);     // this lane's block inside each step
+  const uint8_t* w1 = codes + r1 * (K >> 1) + tig * 16 + (int64_t)c * (KC / 2);
+  const uint8_t* s0 = scales + r0 * kblocks + (int64_t)c * (KC / 32);
+  const uint8_t* s1 = scales + r1 * kblocks + (int64_t)c * (KC / 32);
+  const __nv_bfloat16* xk = x + (int64_t)c * KC;
+
+  ChunkRegsE8 A, B;
+  if (c < c_end) load_chunk_e8(A, w0, w1, s0, s1, min(4, total_steps - c * 4));
+#pragma unroll
+  for (int i = 0; i < 16; ++i) xs[lane + 32 * i] = make_uint4(0, 0, 0, 0);
+  const uint4* xs_lane = xs + g * 4 + tig;
+
+  float acc0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, acc1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  uint32_t bad = 0;
+  while (c < c_end) {
+    if (c + 1 < c_end) load_chunk_e8(B, w0 + KC / 2, w1 + KC / 2, s0 + KC / 32, s1 + KC / 32, min(4, total_steps - (c + 1) * 4));
+    stage_x_warp_e8<TOK>(xs, xk, tokens, K, (int)min((int64_t)KC, K - (int64_t)c * KC), lane);
+    mul_chunk_e8(A, xs_lane, tig, acc0, acc1, bad);
+    ++c; w0 += KC / 2; w1 += KC / 2; s0 += KC / 32; s1 += KC / 32; xk += KC;
+    if (c >= c_end) break;
+    if (c + 1 < c_end) load_chunk_e8(A, w0 + KC / 2, w1 + KC / 2, s0 + KC / 32, s1 + KC / 32, min(4, total_steps - (c + 1) * 4));
+    stage_x_warp_e8<TOK>(xs, xk, tokens, K, (int)min((int64_t)KC, K - (int64_t)c * KC), lane);
+    mul_chunk_e8(B, xs_lane, tig, acc0, acc1, bad);
+    ++c; w0 += KC / 2; w1 += KC / 2; s0 += KC / 32; s1 += KC / 32; xk += KC;
+  }
+  if (bad) atomicCAS(status, 0, (int)B2Q_ERR_UNSUPPORTED);
+
+  __syncthreads();
+  red[(warp * 16 + g) * 8 + tig * 2 + 0] = acc0[0] + acc1[0];
+  red[(warp * 16 + g) * 8 + tig * 2 + 1] = acc0[1] + acc1[1];
+  red[(warp * 16 + g + 8) * 8 + tig * 2 + 0] = acc0[2] + acc1[2];
+  red[(warp * 16 + g + 8) * 8 + tig * 2 + 1] = acc0[3] + acc1[3];
+  __syncthreads();
+  for (int e = threadIdx.x; e < 16 * tokens; e += WK * 32) {
+    const int tok = e >> 4, row = e & 15;
+    float v = 0.0f;
+#pragma unroll
+    for (int w = 0; w < WK; ++w) v += red[(w * 16 + row) * 8 + tok];
+    const int64_t n = n0 + row;
+    if (n < N) {
+      if (out_type == B2Q_OUT_BF16) reinterpret_cast<__nv_bfloat16*>(out)[(int64_t)tok * N + n] = __float2bfloat16_rn(v);
+      else reinterpret_cast<float*>(out)[(int64_t)tok * N + n] = v;
+    }
+  }
+}
+
+template <int WK, int TOK>
+int32_t launch_e8_t(b2q_handle h, const uint8_t* codes, const void* scales, const void* x, int tokens, int64_t N, int64_t K,
+                    void* out, int out_type) {
+  const unsigned grid = (unsigned)ceil_div64(N, 16);
+  const size_t smem = (size_t)WK * 8192;
+  if (smem > 48 * 1024) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      B2Q_CUDA(h, cudaFuncSetAttribute(gemv_fp4_e8_kernel<WK, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      attr_set = true;
+    }
+  }
+  gemv_fp4_e8_kernel<WK, TOK><<<grid, WK * 32, smem, h->stream>>>(codes, (const uint8_t*)scales, (const __nv_bfloat16*)x, tokens, N, K,
+                                                                   out, out_type, h->d_status);
+  B2Q_LAUNCH_CHECK(h, "gemv_fp4_e8_kernel");
+  return B2Q_OK;
+}
+
+template <int WK>
+int32_t launch_e8(b2q_handle h, const uint8_t* codes, const void* scales, const void* x, int tokens, int64_t N, int64_t K, void* out,
+                  int out_type) {
+  return tokens == 1 ? launch_e8_t<WK, 1>(h, codes, scales, x, tokens, N, K, out, out_type)
+       : tokens == 2 ? launch_e8_t<WK, 2>(h, codes, scales, x, tokens, N, K, out, out_type)
+       : tokens <= 4 ? launch_e8_t<WK, 4>(h, codes, scales, x, tokens, N, K, out, out_type)
+                     : launch_e8_t<WK, 8>(h, codes, scales, x, tokens, N, K, out, out_type);
+}
+
 template <int WK>
 int32_t launch_small(b2q_handle h, const uint8_t* codes, const void* scales, int scale_format, const void* x, int tokens, int64_t N,
                      int64_t K, void* out, int out_type) {
@@ -478,6 +674,13 @@ extern "C" int32_t b2q_gemv_fp4_wo(b2q_handle h, const uint8_t* codes, const voi
     if (force && force[0] == '1')
       return small_n ? gemv::launch<1, 4>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type)
                      : gemv::launch<1, 8>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type);
+    // E8M0 scales: 128-bit-load kernel (scale folded into the f16 codes, exact for powers of two) unless
+    // B2Q_GEMV_EXACT=1 asks for the fp32-scaled kernel; f32 scales always take the fp32-scaled kernel.
+    const char* exact = getenv("B2Q_GEMV_EXACT");
+    const bool scales16 = (reinterpret_cast<uintptr_t>(scales) & 15) == 0;
+    if (scale_format == B2Q_SCALE_E8M0 && scales16 && !(exact && exact[0] == '1'))
+      return K >= 8192 ? gemv::launch_e8<8>(h, codes, scales, x_bf16, t, N, K, out, out_type)
+                       : gemv::launch_e8<4>(h, codes, scales, x_bf16, t, N, K, out, out_type);
     return K >= 8192 ? gemv::launch_small<8>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type)
                      : gemv::launch_small<4>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type);
   }
