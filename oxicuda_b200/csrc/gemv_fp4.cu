@@ -491,7 +491,8 @@ __device__ __forceinline__ void load_chunk_e8(ChunkRegsE8& r, const uint8_t* w0,
     r.sa = __ldg(reinterpret_cast<const uint4*>(s0));
     r.sb = __ldg(reinterpret_cast<const uint4*>(s1));
   } else {                                               // ragged tail or K % 512 != 0: word loads stay aligned and inside the row
-    uint32_t a[4] = {0, 0, 0, 0}, b[4] = {0, 0, 0, 0};
+    // steps past the end of the row get scale 2^0 (their codes are zero), which keeps the range check quiet
+    uint32_t a[4] = {0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu}, b[4] = {0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu, 0x7F7F7F7Fu};
     for (int s = 0; s < steps; ++s) {
       a[s] = __ldg(reinterpret_cast<const uint32_t*>(s0) + s);
       b[s] = __ldg(reinterpret_cast<const uint32_t*>(s1) + s);
