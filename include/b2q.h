@@ -108,6 +108,20 @@ int32_t b2q_fp8_quantize_rows_f32(b2q_handle h, const float* x, int64_t rows, in
 int32_t b2q_fp8_quantize_rows_bf16(b2q_handle h, const void* x_bf16, int64_t rows, int64_t cols, int fmt,
                                    int rounding, float* scales, uint8_t* codes);
 
+/* No counterpart in the reference.  The same quantizer for callers that cannot allocate device memory: a plugin
+ * living inside a host process that has handed out all of its memory budget, or code in a region where the allocator
+ * must not be touched.  It needs no handle (creating one allocates) and calls neither cudaMalloc nor cudaFree: the
+ * reduction scratch is a fixed array inside the library (16.25 KiB per GPU for the life of the process), which limits
+ * `rows` to 1024 slices per call (B2Q_ERR_BUFFER_TOO_SMALL beyond that, with the reason written to `err`).
+ * The first call on each device looks up the array's address; make that call outside stream capture.  All calls on a
+ * device share the array, so calls that may overlap on the GPU must be ordered by the caller.  `stream` is a
+ * cudaStream_t; `device_status` (optional, 1 x int32 on the device, zeroed by the caller) receives
+ * B2Q_ERR_NON_FINITE_FP8 if the input holds NaN/Inf; `err`/`err_len` (optional) receive a message on failure.
+ * Same results as b2q_fp8_quantize_rows_f32. */
+int32_t b2q_fp8_quantize_rows_f32_noalloc(const float* x, int64_t rows, int64_t cols, int fmt, int rounding,
+                                          float* scales, uint8_t* codes, void* stream, int32_t* device_status,
+                                          char* err, size_t err_len);
+
 /* ---- MicroScalingQuantizer / Fp4Quantizer / PackedFp4: crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs ---- */
 /* quantize_fp4 (:849-876): blocks of `block` in {32,64,128} over the flat array (validate :205-214),
  * two codes per byte, element 2i in the low nibble (PackedFp4::pack :465-472).  n must be a multiple of

@@ -671,3 +671,85 @@ int32_t b2q_distfp8_dequantize_block_f32(b2q_handle h, const uint8_t* q, int64_t
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of the absmax-scaled FP8 quantizer.
+//
+// Some callers may not allocate device memory at all: code running under a memory budget it
+// does not own (a plugin inside a serving process whose allocator hands out every byte up
+// front), code that must not touch the allocator between two points in time (a latency-critical
+// region, a region that another component is capturing or replaying), or a host that simply has
+// no handle yet.  b2q_create allocates (status word, scratch, later the workspace), so this
+// entry point takes no handle: the reduction keys and the status word that the handle's scratch
+// normally provides live in the file-scope array below, which every device that loads this
+// library carries until the process exits (kNoAllocWords * 4 bytes = 16.25 KiB).
+//
+// The array's name is only a host-side stand-in for the device object: its device address is
+// obtained once per device, with that device current, through cudaGetSymbolAddress.  That set-up
+// happens in the first call made on a device, so make the first call outside any stream capture.
+// All calls on a device share the array and it keeps the previous call's contents: each call
+// re-initialises the keys it is going to use on the stream before using them, and two calls
+// whose kernels may overlap on the GPU (different streams, no dependency) race on it.
+// ---------------------------------------------------------------------------
+namespace {
+constexpr int kNoAllocMaxRows = 1024;                         // slices per call
+constexpr int kNoAllocWords = 4 * kNoAllocMaxRows + 64;       // 4 keys per slice + the status word (own 256-byte line)
+}  // namespace
+static __device__ __align__(256) uint32_t g_noalloc_scratch[kNoAllocWords];
+
+namespace {
+struct NoAllocDevice { uint32_t* ptr; int sm_count; bool ready; };
+NoAllocDevice g_noalloc_dev[64];
+
+void noalloc_msg(char* err, size_t err_len, const char* fmt, long long a, long long b) {
+  if (err && err_len) snprintf(err, err_len, fmt, a, b);
+}
+}  // namespace
+
+extern "C" int32_t b2q_fp8_quantize_rows_f32_noalloc(const float* x, int64_t rows, int64_t cols, int fmt, int rounding,
+                                                     float* scales, uint8_t* codes, void* stream, int32_t* device_status,
+                                                     char* err, size_t err_len) {
+  if (err && err_len) err[0] = 0;
+  if (rows <= 0 || cols <= 0) { noalloc_msg(err, err_len, "empty input: rows=%lld cols=%lld", rows, cols); return B2Q_ERR_EMPTY_INPUT; }
+  if (rows > kNoAllocMaxRows) {
+    noalloc_msg(err, err_len, "rows=%lld exceeds the %lld slices the built-in scratch holds; use b2q_fp8_quantize_rows_f32", rows, kNoAllocMaxRows);
+    return B2Q_ERR_BUFFER_TOO_SMALL;
+  }
+  if (!x || !scales || !codes || fmt < 0 || fmt > 1 || rounding < 0 || rounding > 1) {
+    noalloc_msg(err, err_len, "null pointer or bad format/rounding (fmt=%lld rounding=%lld)", fmt, rounding);
+    return B2Q_ERR_INVALID_ARGUMENT;
+  }
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { noalloc_msg(err, err_len, "no current CUDA device (%lld, %lld)", dev, 0); return B2Q_ERR_CUDA; }
+  NoAllocDevice& d = g_noalloc_dev[dev];
+  if (!d.ready) {                                             // once per device, with that device current
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || !p) { noalloc_msg(err, err_len, "cudaGetSymbolAddress failed with CUDA error %lld on device %lld", (int)e, dev); return B2Q_ERR_CUDA; }
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 128;
+    d.ptr = (uint32_t*)p;
+    d.sm_count = sms;
+    d.ready = true;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  uint32_t* keys = d.ptr;
+  int32_t* status = device_status ? device_status : (int32_t*)(d.ptr + 4 * kNoAllocMaxRows);
+  // same arithmetic as b2q_fp8_quantize_rows_f32: per-slice absmax through ordered-key atomics, scale, encode
+  int64_t bpr = ceil_div64((int64_t)d.sm_count * 8, rows);
+  int64_t seg = ceil_div64(cols, bpr);
+  seg = ceil_div64(seg, 4 * kThreads) * 4 * kThreads;
+  bpr = ceil_div64(cols, seg);
+  StatArgs a{kFp8Scale, 0, 0, fp8_fmt(fmt).max_val, scales, nullptr, status, 1};
+  stat_keys_init_kernel<<<(int)ceil_div64(rows, 256), 256, 0, st>>>(keys, rows);            // clears what must start clean
+  row_stat_split_kernel<float><<<dim3((unsigned)bpr, (unsigned)rows), kThreads, 0, st>>>(x, cols, seg, keys);
+  stat_keys_finish_kernel<<<(int)ceil_div64(rows, 256), 256, 0, st>>>(keys, rows, a);
+  const int64_t n = rows * cols;
+  const int vec_ok = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((reinterpret_cast<uintptr_t>(codes) & 3) == 0);
+  int64_t g = ceil_div64(n, (int64_t)kThreads * 4);
+  if (g > (int64_t)d.sm_count * 16) g = (int64_t)d.sm_count * 16;
+  fp8_encode_kernel<float, true><<<(int)g, kThreads, 0, st>>>(x, n, cols, scales, fmt, rounding, codes, status, vec_ok);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) { noalloc_msg(err, err_len, "kernel launch failed with CUDA error %lld (%lld)", (int)e, 0); return B2Q_ERR_LAUNCH_FAILED; }
+  return B2Q_OK;
+}
