@@ -271,8 +271,12 @@ def main():
         if world == 1:
             v, cores, desc = cpu_sample(size=1024, repeats=1)
             cpu = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc}
-        prof = ROOT / "profiles" / "gemm_tc_fp8_4096_traffic.json"
-        traffic = json.loads(prof.read_text()).get("dram_bytes_per_launch") if prof.exists() else None
+        traffic = None                                  # dram read + write bytes of one launch, from the committed ncu summary
+        prof = ROOT / "profiles" / "gemm_tc2_fp8_4096.md"
+        if prof.exists():
+            import re
+            mt = re.search(r"dram_bytes_per_launch:\s*(\d+)", prof.read_text())
+            traffic = int(mt.group(1)) if mt else None
         line = {
             "metric": "fp8_gemm_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
