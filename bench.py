@@ -89,8 +89,8 @@ def cpu_sample(threads: int | None = None, size: int = 1024, repeats: int = 1):
     on a size^3 sub-problem of the workload; returns (TFLOP/s, cores, description)."""
     import numpy as np
     from oracle import api
-    if threads:
-        api.set_threads(threads)
+    # all host cores this process may use (a launcher may have exported OMP_NUM_THREADS=1 for its workers)
+    api.set_threads(threads or len(os.sched_getaffinity(0)))
     cores = api.num_threads()
     rng = np.random.default_rng(1)
     a = rng.integers(0, 0x7E, (size, size)).astype(np.uint8)

@@ -108,6 +108,14 @@ int32_t b2q_fp8_quantize_rows_f32(b2q_handle h, const float* x, int64_t rows, in
 int32_t b2q_fp8_quantize_rows_bf16(b2q_handle h, const void* x_bf16, int64_t rows, int64_t cols, int fmt,
                                    int rounding, float* scales, uint8_t* codes);
 
+/* SwiGLU between the gate/up and down projections, fused with the per-token re-quantization of its result:
+ * h = silu(gate) * up in fp32, silu(x) = x / (1 + exp(-x)) (crates/oxicuda-lm/src/layer/ffn.rs:25-27,
+ * SwiGluExpert::forward crates/oxicuda-moe/src/expert/ffn.rs:208-243), then scale = absmax(h)/max_val per row and
+ * code = encode(h/scale).  gate/up: bf16 [rows x cols] with leading dimension ld (they may be the two halves of one
+ * [rows x 2*cols] GEMM output). */
+int32_t b2q_swiglu_quantize_rows_bf16(b2q_handle h, const void* gate, const void* up, int64_t rows, int64_t cols,
+                                      int64_t ld, int fmt, int rounding, float* scales, uint8_t* codes);
+
 /* No counterpart in the reference.  The same quantizer for callers that cannot allocate device memory: a plugin
  * living inside a host process that has handed out all of its memory budget, or code in a region where the allocator
  * must not be touched.  It needs no handle (creating one allocates) and calls neither cudaMalloc nor cudaFree: the

@@ -98,6 +98,7 @@ SIGNATURES = {
     "b2q_fp8_remap_ref_subnormals": (C.c_int32, [_H, _P, _I64, _I]),
     "b2q_fp8_quantize_rows_f32": (C.c_int32, [_H, _P, _I64, _I64, _I, _I, _P, _P]),
     "b2q_fp8_quantize_rows_bf16": (C.c_int32, [_H, _P, _I64, _I64, _I, _I, _P, _P]),
+    "b2q_swiglu_quantize_rows_bf16": (C.c_int32, [_H, _P, _P, _I64, _I64, _I64, _I, _I, _P, _P]),
     "b2q_fp8_quantize_rows_f32_noalloc": (C.c_int32, [_P, _I64, _I64, _I, _I, _P, _P, _P, _P, C.c_char_p, C.c_size_t]),
     "b2q_fp4_block_quantize_f32": (C.c_int32, [_H, _P, _I64, _I, _I, _I, _P, _P]),
     "b2q_fp4_block_dequantize_f32": (C.c_int32, [_H, _P, _I64, _I, _I, _I, _P, _P]),

@@ -3,7 +3,7 @@
 // A [M x K] and W [N x K] are 8-bit codes (E4M3/E5M2, or INT8), both K-major.
 //
 // One persistent CTA per SM, 6 warps:
-//   warp 0      TMA producer: cp.async.bulk.tensor (no multicast) into a ring of
+//   warp 0      TMA producer: cp.async.bulk.tensor (each CTA issues its own copies) into a ring of
 //               128-byte-swizzled shared-memory stages, completion on mbarriers;
 //   warp 1      allocates TMEM and issues tcgen05.mma (one elected thread), the
 //               accumulator (128 lanes x BN fp32/s32 columns) lives in TMEM and is
@@ -361,7 +361,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // issues one tcgen05.mma.cta_group::2 per 32-wide K step that reads both CTAs'
 // shared memory, and each CTA's TMEM receives its 128 accumulator rows.  Shared
 // memory traffic per SM drops from 192 to 128 bytes per MMA-clock, which is what
-// bounds the one-CTA kernel.  No TMA multicast: each CTA loads its own halves and
+// bounds the one-CTA kernel.  Every CTA issues its own TMA copies: it loads its own halves and
 // signals the leader's "full" barrier; stage release and accumulator hand-off use
 // tcgen05.commit with a two-CTA mask.
 // =============================================================================
@@ -389,7 +389,7 @@ __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 // TMA load into THIS CTA's shared memory; the byte count is credited to `bar`, a shared::cluster address
-// (the leader CTA's barrier).  No multicast.
+// (the leader CTA's barrier)..
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"

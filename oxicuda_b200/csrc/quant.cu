@@ -753,3 +753,84 @@ extern "C" int32_t b2q_fp8_quantize_rows_f32_noalloc(const float* x, int64_t row
   if (e != cudaSuccess) { noalloc_msg(err, err_len, "kernel launch failed with CUDA error %lld (%lld)", (int)e, 0); return B2Q_ERR_LAUNCH_FAILED; }
   return B2Q_OK;
 }
+
+// ---------------------------------------------------------------------------
+// SwiGLU + per-token FP8 re-quantization between the column-parallel gate/up projections and the
+// row-parallel down projection: h = silu(gate) * up in fp32 (silu(x) = x / (1 + exp(-x))), scale = absmax(h)/max,
+// code = encode(h / scale).  One CTA per token row; h is recomputed in the second pass instead of being stored.
+// ---------------------------------------------------------------------------
+namespace {
+__device__ __forceinline__ float swiglu_f32(float g, float u) { return __fdiv_rn(g, 1.0f + expf(-g)) * u; }
+
+__global__ void __launch_bounds__(kThreads) swiglu_quantize_rows_kernel(const __nv_bfloat16* __restrict__ gate,
+                                                                        const __nv_bfloat16* __restrict__ up, int64_t ld,
+                                                                        int64_t cols, int fmt, int rounding, float* scales,
+                                                                        uint8_t* codes) {
+  const int64_t r = blockIdx.x;
+  const __nv_bfloat16* g = gate + r * ld;
+  const __nv_bfloat16* u = up + r * ld;
+  const Fp8Fmt F = fp8_fmt(fmt);
+  __shared__ float sh[kThreads / 32];
+  float amax = 0.0f;
+  const bool vec = (cols % 8 == 0) && (ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up)) & 15) == 0;
+  if (vec) {
+    for (int64_t c = (int64_t)threadIdx.x * 8; c < cols; c += (int64_t)kThreads * 8) {
+      const uint4 gv = *reinterpret_cast<const uint4*>(g + c), uv = *reinterpret_cast<const uint4*>(u + c);
+      const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        amax = fmaxf(amax, fabsf(swiglu_f32(__uint_as_float(gw[j] << 16), __uint_as_float(uw[j] << 16))));
+        amax = fmaxf(amax, fabsf(swiglu_f32(__uint_as_float(gw[j] & 0xFFFF0000u), __uint_as_float(uw[j] & 0xFFFF0000u))));
+      }
+    }
+  } else {
+    for (int64_t c = threadIdx.x; c < cols; c += kThreads)
+      amax = fmaxf(amax, fabsf(swiglu_f32(__bfloat162float(g[c]), __bfloat162float(u[c]))));
+  }
+  amax = warp_max(amax);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = amax;
+  __syncthreads();
+  amax = sh[0];
+#pragma unroll
+  for (int w = 1; w < kThreads / 32; ++w) amax = fmaxf(amax, sh[w]);
+  const float scale = amax > 0.0f ? __fdiv_rn(amax, F.max_val) : 1.0f;
+  if (threadIdx.x == 0) scales[r] = scale;
+  auto enc = [&](float h) -> uint32_t {
+    float v = __fdiv_rn(h, scale);
+    v = v < -F.max_val ? -F.max_val : (v > F.max_val ? F.max_val : v);
+    return rounding == 0 ? fp8_encode_ref_dev(v, F) : fp8_encode_rne_dev(v, fmt);
+  };
+  uint8_t* out = codes + r * cols;
+  if (vec) {
+    for (int64_t c = (int64_t)threadIdx.x * 8; c < cols; c += (int64_t)kThreads * 8) {
+      const uint4 gv = *reinterpret_cast<const uint4*>(g + c), uv = *reinterpret_cast<const uint4*>(u + c);
+      const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint32_t c0 = enc(swiglu_f32(__uint_as_float(gw[j] << 16), __uint_as_float(uw[j] << 16)));
+        const uint32_t c1 = enc(swiglu_f32(__uint_as_float(gw[j] & 0xFFFF0000u), __uint_as_float(uw[j] & 0xFFFF0000u)));
+        const uint32_t pair = c0 | (c1 << 8);
+        if (j < 2) lo |= pair << (16 * j); else hi |= pair << (16 * (j - 2));
+      }
+      *reinterpret_cast<uint2*>(out + c) = make_uint2(lo, hi);
+    }
+  } else {
+    for (int64_t c = threadIdx.x; c < cols; c += kThreads)
+      out[c] = (uint8_t)enc(swiglu_f32(__bfloat162float(g[c]), __bfloat162float(u[c])));
+  }
+}
+}  // namespace
+
+extern "C" int32_t b2q_swiglu_quantize_rows_bf16(b2q_handle h, const void* gate, const void* up, int64_t rows, int64_t cols,
+                                                 int64_t ld, int fmt, int rounding, float* scales, uint8_t* codes) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (rows <= 0 || cols <= 0) B2Q_FAIL(h, B2Q_ERR_EMPTY_INPUT, "swiglu_quantize_rows: empty input");
+  if (!gate || !up || !scales || !codes || ld < cols || fmt < 0 || fmt > 1 || rounding < 0 || rounding > 1)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "swiglu_quantize_rows: bad argument");
+  if (rows > 0x7FFFFFFF) B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "swiglu_quantize_rows: too many rows");
+  swiglu_quantize_rows_kernel<<<(unsigned)rows, kThreads, 0, h->stream>>>((const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, ld,
+                                                                          cols, fmt, rounding, scales, codes);
+  B2Q_LAUNCH_CHECK(h, "swiglu_quantize_rows_kernel");
+  return B2Q_OK;
+}

@@ -122,3 +122,44 @@ class RowLinear:
         if self.handle.config.tp > 1:
             dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.handle.group)
         return partial
+
+
+class TpFp8Mlp:
+    """Tensor-parallel SwiGLU MLP with FP8 weights: gate and up column-parallel (fused into one GEMM over the
+    concatenated shard), down row-parallel, one all-reduce after the down projection.
+
+    Semantics: SwiGluExpert::forward (crates/oxicuda-moe/src/expert/ffn.rs:208-243) with the linears sharded as
+    ColumnLinear / RowLinear do (crates/oxicuda-dist-infer/src/tensor_parallel/*.rs).  Activations are quantized
+    per token (absmax/448), weights per output row; the SwiGLU result is re-quantized per token over this rank's
+    columns before the down projection."""
+
+    def __init__(self, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, handle: DistInferHandle,
+                 rounding: str = "rne"):
+        self.handle = handle
+        tp, r = handle.config.tp, handle.tp_rank()
+        ffn, hidden = w_gate.shape
+        r0, r1 = column_shard_rows(ffn, tp, r)
+        c0, c1 = row_shard_cols(ffn, tp, r)
+        self.local_ffn, self.hidden = r1 - r0, hidden
+        self.gate_up = Fp8Linear(torch.cat([w_gate[r0:r1], w_up[r0:r1]], dim=0), rounding)   # [2*ffn/tp x hidden]
+        self.down = Fp8Linear(w_down[:, c0:c1].contiguous(), rounding)                          # [hidden x ffn/tp]
+        self.codec = Fp8Codec.e4m3(rounding)
+
+    def forward_partial(self, x: torch.Tensor) -> torch.Tensor:
+        """x bf16 [tokens x hidden] (replicated) -> this rank's partial of the output, bf16 [tokens x hidden]."""
+        from ._lib import default_handle, ptr
+        tokens = x.shape[0]
+        xc, xs = self.codec.quantize_rows(x, tokens, self.hidden)
+        gu = self.gate_up.forward(xc.view(tokens, self.hidden), xs)              # bf16 [tokens x 2F]: gate | up
+        F = self.local_ffn
+        hc = torch.empty(tokens, F, dtype=torch.uint8, device=x.device)
+        hs = torch.empty(tokens, dtype=torch.float32, device=x.device)
+        default_handle().call("b2q_swiglu_quantize_rows_bf16", ptr(gu), ptr(gu[:, F:]), tokens, F, 2 * F,
+                              L.FP8_E4M3, self.codec.rounding, ptr(hs), ptr(hc))
+        return self.down.forward(hc, hs)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        y = self.forward_partial(x)
+        if self.handle.config.tp > 1:
+            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.handle.group)
+        return y
