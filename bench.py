@@ -84,24 +84,23 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def cpu_sample(threads: int | None = None, size: int = 1024, repeats: int = 1):
-    """Times the oracle's FP8 GEMM (Fp8Codec decode + k-ascending fp32 FMA, the reference's arithmetic)
-    on a size^3 sub-problem of the workload; returns (TFLOP/s, cores, description)."""
+def cpu_sample(threads: int | None = None, rows: int = 2048, k: int = K):
+    """Times the oracle's FP8 GEMM (Fp8Codec decode + k-ascending fp32 FMA, the reference's arithmetic) on a
+    rows x rows x k slice of the workload (full K, a block of the output); returns (TFLOP/s, cores, description)."""
     import numpy as np
     from oracle import api
     # all host cores this process may use (a launcher may have exported OMP_NUM_THREADS=1 for its workers)
     api.set_threads(threads or len(os.sched_getaffinity(0)))
     cores = api.num_threads()
     rng = np.random.default_rng(1)
-    a = rng.integers(0, 0x7E, (size, size)).astype(np.uint8)
-    w = rng.integers(0, 0x7E, (size, size)).astype(np.uint8)
+    a = rng.integers(0, 0x7E, (rows, k)).astype(np.uint8)
+    w = rng.integers(0, 0x7E, (rows, k)).astype(np.uint8)
     one = np.ones(1, np.float32)
     api.gemm_fp8(a[:64], w[:64], one, one, 0, 0, "bf16")          # page in, spin up the thread pool
     t0 = time.perf_counter()
-    for _ in range(repeats):
-        api.gemm_fp8(a, w, one, one, 0, 0, "bf16")
-    dt = (time.perf_counter() - t0) / repeats
-    return 2.0 * size ** 3 / dt / 1e12, cores, f"{size}x{size}x{size} sub-problem of the 4096^3 GEMM, {repeats} pass(es), {dt:.2f} s each"
+    api.gemm_fp8(a, w, one, one, 0, 0, "bf16")
+    dt = time.perf_counter() - t0
+    return 2.0 * rows * rows * k / dt / 1e12, cores, f"{rows}x{rows} output block x K={k} of the 4096^3 GEMM ({rows * rows * 100 // (M * N)} % of the step), {dt:.2f} s"
 
 
 def run_reference(args, rank: int):
@@ -111,11 +110,11 @@ def run_reference(args, rank: int):
     vals = []
     desc = ""
     for _ in range(args.warmup if args.warmup < 2 else 1):
-        cpu_sample(size=512)
+        cpu_sample(rows=512)
     t_start = time.perf_counter()
     steps = 0
     for _ in range(args.steps):
-        v, cores, desc = cpu_sample(size=1024)
+        v, cores, desc = cpu_sample(rows=2048)
         vals.append(v)
         steps += 1
         if time.perf_counter() - t_start > 150:            # keep the whole arm within a few minutes
@@ -257,11 +256,21 @@ def main():
     clocks = sampler.stop() if rank == 0 else None
 
     extras = {}
-    if rank == 0 and not args.no_extras:
+    if not args.no_extras:
+        for s_ in sets:                                # free the GEMM operands before the side measurements
+            del s_
+        sets.clear()
+        torch.cuda.empty_cache()
         try:
-            extras = side_measurements(dev, peaks)
-        except Exception as exc:                       # side numbers never block the headline line
-            extras = {"error": repr(exc)}
+            tp = tp_mlp_measurements(dev, rank, world)     # every rank takes part (all-reduce)
+        except Exception as exc:
+            tp = {"error": repr(exc)}
+        if rank == 0:
+            try:
+                extras = side_measurements(dev, peaks)
+            except Exception as exc:                   # side numbers never block the headline line
+                extras = {"error": repr(exc)}
+            extras["tp_fp8_mlp_8192_28672"] = tp
 
     if rank == 0:
         tile, kid = select_tile("fp8", M, N, K)
@@ -269,7 +278,7 @@ def main():
         fp8_peak = 2.0 * peaks["bf16_tflops"]
         cpu = None
         if world == 1:
-            v, cores, desc = cpu_sample(size=1024, repeats=1)
+            v, cores, desc = cpu_sample(rows=2048)
             cpu = {"value": v, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": desc}
         traffic = None                                  # dram read + write bytes of one launch, from the committed ncu summary
         prof = ROOT / "profiles" / "gemm_tc2_fp8_4096.md"
@@ -382,6 +391,32 @@ def _time_graph(fn, calls_per_graph, replays=20):
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) / (replays * calls_per_graph) * 1e-3
+
+
+def tp_mlp_measurements(dev, rank, world):
+    """Tensor-parallel FP8 SwiGLU MLP of a 70B-shaped layer (hidden 8192, FFN 28672): gate/up column-parallel,
+    down row-parallel, NCCL all-reduce after the down projection; tokens in {1, 64, 4096}; tp = number of ranks."""
+    import torch
+    from oxicuda_b200.dist_infer import DistInferHandle, ParallelismConfig, TpFp8Mlp
+    hidden, ffn = 8192, 28672
+    F = ffn // world
+    g = torch.Generator(device=dev).manual_seed(0xB2000003 + rank)
+    mk = lambda r, c: torch.randn(r, c, device=dev, generator=g) * 0.01
+    mlp = TpFp8Mlp.from_shards(mk(F, hidden), mk(F, hidden), mk(hidden, F), DistInferHandle(rank, ParallelismConfig(tp=world)))
+    torch.cuda.empty_cache()
+    res = {"tp": world, "weights_bytes_per_gpu": 3 * hidden * F}
+    for tokens in (1, 64, 4096):
+        x = torch.randn(tokens, hidden, device=dev, generator=g).to(torch.bfloat16)
+        sec = _time_calls(lambda i: mlp.forward(x), 20 if tokens < 4096 else 10, 3)
+        t = torch.tensor([sec], device=dev)
+        if world > 1:
+            import torch.distributed as dist
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        sec = float(t.item())
+        flops = 6.0 * tokens * hidden * ffn
+        res[f"m{tokens}"] = {"us": sec * 1e6, "tflops_all_gpus": flops / sec / 1e12,
+                             "weight_gbs_per_gpu": 3 * hidden * F / sec / 1e9}
+    return res
 
 
 def side_measurements(dev, peaks):

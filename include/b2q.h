@@ -192,6 +192,26 @@ int32_t b2q_gemm_fp8_simt(b2q_handle h, const uint8_t* a, const uint8_t* w, int6
                           int decode_mode, const float* scale_a, int scale_a_kind, const float* scale_w,
                           int scale_w_kind, void* out, int out_type);
 
+/* ---- grouped GEMM: grouped_gemm / GroupedGemmProblem crates/oxicuda-blas/src/batched/grouped_gemm.rs:46-78 ----
+ * One FP8 GEMM per entry of a host-side problem table (an expert and the tokens routed to it); entries with m == 0 are
+ * skipped.  Problems are issued back to back on the handle's stream (the reference launches them one by one up to four
+ * problems and uses a table-driven kernel beyond). */
+typedef struct {
+  const uint8_t* a; const uint8_t* w; int64_t m, n, k;
+  const float* scale_a; int32_t scale_a_kind; const float* scale_w; int32_t scale_w_kind; void* out;
+} b2q_gemm_fp8_problem;
+int32_t b2q_grouped_gemm_fp8(b2q_handle h, const b2q_gemm_fp8_problem* problems, int count, int fmt, int out_type);
+
+/* ---- expert dispatch: ep_token_scatter / ep_token_gather crates/oxicuda-dist-infer/src/ptx_kernels.rs:46-469,
+ *      ExpertDispatcher::{scatter,gather} crates/oxicuda-dist-infer/src/expert_parallel/dispatch.rs:99-219 ----
+ * scatter: expert_buf[slot[i]] = in[token[i]] for each routed pair i (rows of row_bytes bytes, a multiple of 16);
+ * gather: out[t] = sum_j weight[t*top_k+j] * expert_out[slot[t*top_k+j]] in fp32, j ascending, bf16 in and out;
+ * a negative slot marks a pair served by another rank and contributes nothing. */
+int32_t b2q_ep_token_scatter(b2q_handle h, const void* in, const int32_t* token, const int32_t* slot, int64_t pairs,
+                             int64_t row_bytes, void* expert_buf);
+int32_t b2q_ep_token_gather_bf16(b2q_handle h, const void* expert_out, const int32_t* slot, const float* weight,
+                                 int64_t tokens, int top_k, int64_t hidden, void* out);
+
 /* ---- FP4 weight-only decode GEMV: Fp4GemmConfig / generate_fp4_gemm_ptx
  *      crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:337-395, :1237-1362; semantics = dequantize_fp4 (:879-897)
  *      followed by a dot product.  The reference's M (quantized rows) is `N` here, its N (columns of dense B) is
@@ -215,7 +235,7 @@ uint32_t b2q_fp8_compute_split_k(uint32_t m, uint32_t n, uint32_t k);
 /* The static per-shape table this library actually dispatches with (replaces the autotuner role,
  * crates/oxicuda-autotune/src/dispatch.rs:36-196): the CTA tile, pipeline depth and kernel family chosen for
  * (dtype, m, n, k).  kernel_id: 0 simt, 1 tcgen05 128x256, 2 tcgen05 128x128, 3 warp gemv,
- * 4 tcgen05 two-CTA 256x256. */
+ * 4 tcgen05 two-CTA 256x256, 5 fp8 decode gemv. */
 int32_t b2q_select_tile(int dtype, uint32_t m, uint32_t n, uint32_t k, b2q_tile_config* out, int* kernel_id);
 
 #ifdef __cplusplus

@@ -64,6 +64,13 @@ _ERRORS = {
 }
 
 
+class GemmFp8Problem(C.Structure):
+    """b2q_gemm_fp8_problem (include/b2q.h): one entry of a grouped-GEMM problem table."""
+    _fields_ = [("a", C.c_void_p), ("w", C.c_void_p), ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64),
+                ("scale_a", C.c_void_p), ("scale_a_kind", C.c_int32), ("scale_w", C.c_void_p), ("scale_w_kind", C.c_int32),
+                ("out", C.c_void_p)]
+
+
 class TileConfig(C.Structure):
     """TileConfig, crates/oxicuda-blas/src/level3/gemm/dispatch.rs:57-107."""
     _fields_ = [(n, C.c_uint32) for n in
@@ -112,6 +119,9 @@ SIGNATURES = {
     "b2q_gemm_i8": (C.c_int32, [_H, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P]),
     "b2q_gemm_fp8": (C.c_int32, [_H, _P, _P, _I64, _I64, _I64, _I, _P, _I, _P, _I, _P, _I]),
     "b2q_gemm_fp8_simt": (C.c_int32, [_H, _P, _P, _I64, _I64, _I64, _I, _I, _P, _I, _P, _I, _P, _I]),
+    "b2q_grouped_gemm_fp8": (C.c_int32, [_H, _P, _I, _I, _I]),
+    "b2q_ep_token_scatter": (C.c_int32, [_H, _P, _P, _P, _I64, _I64, _P]),
+    "b2q_ep_token_gather_bf16": (C.c_int32, [_H, _P, _P, _P, _I64, _I, _I64, _P]),
     "b2q_gemv_fp4_wo": (C.c_int32, [_H, _P, _P, _I, _I, _P, _I64, _I64, _I64, _P, _I]),
     "b2q_classify_workload": (C.c_int32, [_U32, _U32, _U32]),
     "b2q_ref_tile_config": (C.c_int32, [_I, _U32, _U32, _U32, C.POINTER(TileConfig)]),

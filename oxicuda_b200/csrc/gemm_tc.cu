@@ -658,6 +658,9 @@ int32_t launch2(b2q_handle h, const void* a, const void* w, Params p) {
 int32_t b2q_validate_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,
                               const float* scale_a, int ka, const float* scale_w, int kw, void* out, int out_type);
 
+int32_t b2q_gemv_fp8_dispatch(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,
+                              const float* scale_a, int ka, const float* scale_w, int kw, void* out, int out_type);
+
 int32_t b2q_gemm_i8_tc(b2q_handle h, const int8_t* a, const int8_t* b, int64_t M, int64_t N, int64_t K, int32_t* c_s32,
                        float* c_f32, const float* sa, const float* sb) {
   if (K % 16 != 0 || ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b)) & 15) != 0 || N < 64)
@@ -685,6 +688,11 @@ extern "C" int32_t b2q_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w
     if (force && force[0] == '1') kid = 2;
     if (force && force[0] == '2') kid = 1;
     if (force && force[0] == 'p') kid = 4;     // "pair": the two-CTA kernel
+  }
+  if (kid == 5) {   // decode-sized: tensor-core GEMV over the codes
+    int32_t gst = b2q_gemv_fp8_dispatch(h, a, w, M, N, K, fmt, scale_a, scale_a_kind, scale_w, scale_w_kind, out, out_type);
+    if (gst != B2Q_ERR_UNSUPPORTED) return gst;
+    kid = 0;
   }
   const bool tma_ok = K % 16 == 0 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
   if (kid == 0 || !tma_ok)

@@ -154,7 +154,12 @@ int32_t b2q_select_tile(int dtype, uint32_t m, uint32_t n, uint32_t k, b2q_tile_
     *kernel_id = 3;
     return B2Q_OK;
   }
-  if (m < 64 || k % 16 != 0) {  // decode-sized or TMA-incompatible pitch: SIMT path
+  if (dtype == 0 && m <= 32 && k % 64 == 0) {  // FP8 decode: 16 weight rows per CTA, mma.sync.m16n8k32 over the codes
+    *out = b2q_tile_config{m <= 8 ? 8u : (m <= 16 ? 16u : 32u), 16, 256, 8, 16, 2, 1, 1};
+    *kernel_id = 5;
+    return B2Q_OK;
+  }
+  if (m < 64 || k % 16 != 0) {  // TMA-incompatible pitch or too few rows for a tensor-core tile: SIMT path
     *out = b2q_tile_config{16, 16, 16, 16, 16, 1, 0, 1};
     *kernel_id = 0;
     return B2Q_OK;

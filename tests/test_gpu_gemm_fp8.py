@@ -30,7 +30,8 @@ def _quantize(oracle, x, rows, cols, mode):
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 256, 128), (128, 128, 256), (256, 512, 1024), (64, 64, 64), (100, 200, 304),
-                                   (129, 257, 144), (384, 1000, 512), (1000, 136, 2048), (8, 512, 256), (300, 300, 100)])
+                                   (129, 257, 144), (384, 1000, 512), (1000, 136, 2048), (8, 512, 256), (300, 300, 100),
+                                   (1, 4096, 4096), (3, 130, 192), (17, 1000, 8192), (32, 256, 320), (12, 64, 64), (40, 200, 128)])
 def test_gemm_fp8_vs_oracle(cuda, oracle, M, N, K):
     from oxicuda_b200.blas import gemm_fp8
     rng = np.random.default_rng(M * 7 + N * 3 + K)

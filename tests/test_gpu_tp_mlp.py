@@ -1,8 +1,9 @@
 """GPU: tensor-parallel FP8 SwiGLU MLP (gate/up column-parallel, down row-parallel + all-reduce) against the
 oracle composition on the same seeded inputs.  tp=1 runs in-process; tp=2 runs as two NCCL ranks when the box
-has two GPUs.  Tolerance: |got - ref| <= 1e-2*|ref| + 5e-3*rms(ref) on every element (1e-2 relative, as for the
+has two GPUs.  Tolerance: |got - ref| <= 1e-2*|ref| + 1e-2*rms(ref) on every element (1e-2 relative, as for the
 GEMMs, plus an absolute floor): exp() may differ in the last bit between libm and the GPU, which can move one
-re-quantized SwiGLU value to the neighbouring E4M3 code and shifts an output by about 1.5e-3*rms."""
+re-quantized SwiGLU value to the neighbouring E4M3 code; when that value is the row's largest, one output
+moves by up to about 7e-3*rms."""
 import os
 import socket
 import subprocess
@@ -42,10 +43,10 @@ def oracle_mlp(oracle, x_bf16_as_f32, wg, wu, wd, tp):
 
 
 def rel_err(got, ref):
-    """max over elements of |got - ref| / (|ref| + 0.5*rms(ref)); <= 1e-2 means the bound of the module docstring."""
+    """max over elements of |got - ref| / (|ref| + rms(ref)); <= 1e-2 means the bound of the module docstring."""
     got, ref = np.asarray(got, np.float64), np.asarray(ref, np.float64)
     rms = np.sqrt((ref ** 2).mean()) + 1e-30
-    return float((np.abs(got - ref) / (np.abs(ref) + 0.5 * rms)).max())
+    return float((np.abs(got - ref) / (np.abs(ref) + rms)).max())
 
 
 def make_inputs(tokens, hidden, ffn, seed=0xB2000003):

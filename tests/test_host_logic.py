@@ -84,7 +84,9 @@ def test_static_tile_table(libb2q):
     t, kid = blas.select_tile("fp8", 128, 4096, 4096)
     assert kid in (1, 2) and t.tile_m == 128 and t.tile_n in (128, 256)
     t, kid = blas.select_tile("fp8", 8, 4096, 4096)
-    assert kid == 0                                   # decode-sized: SIMT path
+    assert kid == 5 and t.tile_n == 16                # decode-sized: tensor-core GEMV over the codes
+    t, kid = blas.select_tile("fp8", 40, 4096, 4096)
+    assert kid == 0                                   # between the GEMV and a 128-row tile: SIMT path
     t, kid = blas.select_tile("fp8", 4096, 4096, 4100)
     assert kid == 0                                   # row pitch TMA cannot take
     t, kid = blas.select_tile("fp4", 1, 4096, 4096)
