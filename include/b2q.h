@@ -221,6 +221,14 @@ int32_t b2q_ep_token_gather_bf16(b2q_handle h, const void* expert_out, const int
 int32_t b2q_gemv_fp4_wo(b2q_handle h, const uint8_t* codes, const void* scales, int scale_format, int block,
                         const void* x_bf16, int64_t tokens, int64_t N, int64_t K, void* out, int out_type);
 
+/* Weight-only FP4 GEMM for any token count (prefill): same operands and semantics as b2q_gemv_fp4_wo plus `format`
+ * (B2Q_FP4_E2M1 or B2Q_FP4_INT4) and blocks of 32, 64 or 128.  32 tokens or fewer go to the decode GEMV; above that the
+ * weights are expanded to bf16 in the handle's workspace (N*K*2 bytes, kept for later calls) and multiplied on tcgen05
+ * (kind::f16, fp32 accumulation).  Fp4GemmConfig::validate order: zero dims, odd K, block size
+ * (crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:354-376). */
+int32_t b2q_gemm_fp4_wo(b2q_handle h, const uint8_t* codes, const void* scales, int scale_format, int block, int format,
+                        const void* x_bf16, int64_t tokens, int64_t N, int64_t K, void* out, int out_type);
+
 /* ---- tile heuristics: classify_workload / Fp8TileHeuristic::select crates/oxicuda-blas/src/precision/fp8_ops.rs:67-107,
  *      :239-304; select_fp4_tile fp4_fp6_ops.rs:996-1075; Int8GemmConfig::tile_config int_ops.rs:141-176 ---- */
 typedef struct {

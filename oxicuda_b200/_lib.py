@@ -123,6 +123,7 @@ SIGNATURES = {
     "b2q_ep_token_scatter": (C.c_int32, [_H, _P, _P, _P, _I64, _I64, _P]),
     "b2q_ep_token_gather_bf16": (C.c_int32, [_H, _P, _P, _P, _I64, _I, _I64, _P]),
     "b2q_gemv_fp4_wo": (C.c_int32, [_H, _P, _P, _I, _I, _P, _I64, _I64, _I64, _P, _I]),
+    "b2q_gemm_fp4_wo": (C.c_int32, [_H, _P, _P, _I, _I, _I, _P, _I64, _I64, _I64, _P, _I]),
     "b2q_classify_workload": (C.c_int32, [_U32, _U32, _U32]),
     "b2q_ref_tile_config": (C.c_int32, [_I, _U32, _U32, _U32, C.POINTER(TileConfig)]),
     "b2q_fp8_compute_split_k": (_U32, [_U32, _U32, _U32]),

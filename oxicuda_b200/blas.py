@@ -208,3 +208,16 @@ def gemv_fp4_wo(codes: torch.Tensor, scales: torch.Tensor, x: torch.Tensor, N: i
     ot = L.OUT_BF16 if out.dtype == torch.bfloat16 else L.OUT_F32
     default_handle().call("b2q_gemv_fp4_wo", ptr(codes), ptr(scales), sf, block, ptr(x), tokens, N, K, ptr(out), ot)
     return out
+
+
+def gemm_fp4_wo(codes: torch.Tensor, scales: torch.Tensor, x: torch.Tensor, N: int, K: int, out: torch.Tensor = None,
+                out_dtype=torch.bfloat16, block: int = 32, format: Fp4Format = Fp4Format.E2M1) -> torch.Tensor:
+    """Weight-only FP4 GEMM for any token count: decode GEMV at 32 tokens or fewer, bf16 expansion + tcgen05 above
+    (Fp4GemmConfig, crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:337-395)."""
+    tokens = x.shape[0]
+    if out is None:
+        out = torch.empty(tokens, N, dtype=out_dtype, device=x.device)
+    sf = L.SCALE_E8M0 if scales.dtype == torch.uint8 else L.SCALE_F32
+    ot = L.OUT_BF16 if out.dtype == torch.bfloat16 else L.OUT_F32
+    default_handle().call("b2q_gemm_fp4_wo", ptr(codes), ptr(scales), sf, block, format.value, ptr(x), tokens, N, K, ptr(out), ot)
+    return out

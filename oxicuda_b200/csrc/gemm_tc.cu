@@ -25,7 +25,7 @@ constexpr int kThreads = 192;
 constexpr int GROUP_M = 8;     // tile rasterisation: 8 row-blocks share each W panel in L2
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
-enum Kind { kF8 = 0, kI8 = 1 };
+enum Kind { kF8 = 0, kI8 = 1, kBF16 = 2 };   // kBF16: 16-bit operands, K counted in BYTES by the kernels (BK = 64 elements)
 
 template <int BN> struct Cfg {
   static constexpr int kStages = BN == 256 ? 4 : 6;
@@ -106,10 +106,15 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-  } else {
+  } else if constexpr (KIND == kI8) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
   }
 }
@@ -153,7 +158,7 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 template <int KIND>
 __device__ __forceinline__ void store_chunk(const Params& p, const uint32_t (&r)[32], int64_t m, int64_t n, float sa, float sw0) {
   const bool full = n + 32 <= p.N;
-  if constexpr (KIND == kF8) {
+  if constexpr (KIND != kI8) {
     float v[32];
 #pragma unroll
     for (int j = 0; j < 32; ++j) {
@@ -414,10 +419,15 @@ __device__ __forceinline__ void umma2(uint32_t tmem_d, uint64_t adesc, uint64_t 
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-  } else {
+  } else if constexpr (KIND == kI8) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
   }
 }
@@ -605,7 +615,9 @@ int32_t launch(b2q_handle h, const void* a, const void* w, Params p) {
   p.tiles_n = (int)ceil_div64(p.N, BN);
   // instruction descriptor: dense, D format, A/B formats, both K-major, N>>3 at bit 17, M>>4 at bit 24
   const uint32_t shape = ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
-  p.idesc = KIND == kF8 ? (p.idesc | (1u << 4) | shape) : ((2u << 4) | (1u << 7) | (1u << 10) | shape);
+  p.idesc = KIND == kF8 ? (p.idesc | (1u << 4) | shape)                                   // fp32 accumulate, E4M3/E5M2 per p.idesc
+          : KIND == kI8 ? ((2u << 4) | (1u << 7) | (1u << 10) | shape)                    // s32 accumulate, signed 8-bit A and B
+                        : ((1u << 4) | (1u << 7) | (1u << 10) | shape);                   // fp32 accumulate, bf16 A and B
   static bool attr_set = false;
   if (!attr_set) {
     B2Q_CUDA(h, cudaFuncSetAttribute(gemm_tc_kernel<BN, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
@@ -629,7 +641,9 @@ int32_t launch2(b2q_handle h, const void* a, const void* w, Params p) {
   p.tiles_m = (int)ceil_div64(p.M, 256);
   p.tiles_n = (int)ceil_div64(p.N, two::BN2);
   const uint32_t shape = ((uint32_t)(two::BN2 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
-  p.idesc = KIND == kF8 ? (p.idesc | (1u << 4) | shape) : ((2u << 4) | (1u << 7) | (1u << 10) | shape);
+  p.idesc = KIND == kF8 ? (p.idesc | (1u << 4) | shape)                                   // fp32 accumulate, E4M3/E5M2 per p.idesc
+          : KIND == kI8 ? ((2u << 4) | (1u << 7) | (1u << 10) | shape)                    // s32 accumulate, signed 8-bit A and B
+                        : ((1u << 4) | (1u << 7) | (1u << 10) | shape);                   // fp32 accumulate, bf16 A and B
   static bool attr_set = false;
   if (!attr_set) {
     B2Q_CUDA(h, cudaFuncSetAttribute(two::gemm_tc2_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, two::kSmem));
@@ -673,6 +687,17 @@ int32_t b2q_gemm_i8_tc(b2q_handle h, const int8_t* a, const int8_t* b, int64_t M
   b2q_select_tile(2, (uint32_t)M, (uint32_t)N, (uint32_t)K, &t, &kid);
   if (kid == 4) return tc::launch2<tc::kI8>(h, a, b, p);
   return kid == 1 ? tc::launch<256, tc::kI8>(h, a, b, p) : tc::launch<128, tc::kI8>(h, a, b, p);
+}
+
+// bf16 x bf16 -> bf16/f32 on the same pipeline (tcgen05 kind::f16); a [M x K], w [N x K], both K-major.
+// Used by the weight-only FP4 prefill GEMM after the weights are expanded to bf16.
+int32_t b2q_gemm_bf16_tc(b2q_handle h, const void* a, const void* w, int64_t M, int64_t N, int64_t K, void* out, int out_type) {
+  if (K % 8 != 0 || ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) != 0) return B2Q_ERR_UNSUPPORTED;
+  tc::Params p{};
+  p.M = M; p.N = N; p.K = 2 * K;                        // bytes
+  p.out = out; p.out_type = out_type; p.status = h->d_status;
+  if (M > 128 && N > 128) return tc::launch2<tc::kBF16>(h, a, w, p);
+  return N >= 256 ? tc::launch<256, tc::kBF16>(h, a, w, p) : tc::launch<128, tc::kBF16>(h, a, w, p);
 }
 
 extern "C" int32_t b2q_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,

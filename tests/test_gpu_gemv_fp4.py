@@ -80,3 +80,33 @@ def test_linearity_and_validation(cuda, oracle):
         gemv_fp4_wo(cd, sd, x, N, 1000)
     with pytest.raises(_lib.InvalidArgument):
         gemv_fp4_wo(cd, sd, x, N, K, block=48)
+
+
+@pytest.mark.parametrize("tokens,N,K,block", [(64, 512, 1024, 32), (300, 1000, 256, 64), (1000, 136, 2048, 128), (33, 64, 128, 32),
+                                              (4096, 1024, 4096, 32)])
+def test_prefill_fp4_weight_only_gemm(cuda, oracle, tokens, N, K, block):
+    """Token counts above the decode range: weights expanded to bf16, product on tcgen05 (kind::f16)."""
+    from oxicuda_b200.blas import Fp4Format, gemm_fp4_wo
+    rng = np.random.default_rng(tokens + N + K)
+    w = (rng.standard_normal(N * K) * 0.02).astype(np.float32)
+    x = torch.from_numpy(rng.standard_normal((tokens, K)).astype(np.float32)).to(torch.bfloat16)
+    xb = x.view(torch.int16).numpy().view(np.uint16)
+    for scale_mode in (1, 0):
+        codes, scales = oracle.fp4_block_quantize(w, block, 0, scale_mode)
+        ref = oracle.gemv_fp4(codes, scales, xb, tokens, N, K, block, "bf16")
+        got = gemm_fp4_wo(_t(codes, cuda), _t(scales, cuda), x.to(cuda), N, K, block=block).float().cpu().numpy()
+        if scale_mode == 1 or tokens <= 32:
+            assert rel_err(got, ref) <= TOL, (scale_mode, block)          # power-of-two scales expand to bf16 exactly
+        else:
+            # an f32 scale times a code is rounded to bf16 (8 significant bits) before the tensor-core product: each
+            # weight is off by up to 2^-9 relative, which moves an output by about 1e-3 of the output rms whatever its
+            # own size; the bound is therefore 1e-2 relative plus 1e-2 of the rms
+            rms = np.sqrt((ref.astype(np.float64) ** 2).mean())
+            assert float((np.abs(got - ref) / (np.abs(ref) + rms)).max()) <= TOL, (scale_mode, block)
+    if tokens <= 300:                                     # INT4 codes share the kernel
+        codes, scales = oracle.fp4_block_quantize(w, block, 1, 0)
+        deq = oracle.fp4_block_dequantize(codes, scales, N * K, block, 1).reshape(N, K).astype(np.float64)
+        ref = x.float().numpy().astype(np.float64) @ deq.T
+        got = gemm_fp4_wo(_t(codes, cuda), _t(scales, cuda), x.to(cuda), N, K, block=block, format=Fp4Format.Int4, out_dtype=torch.float32)
+        rms = np.sqrt((ref ** 2).mean())
+        assert float((np.abs(got.cpu().numpy() - ref) / (np.abs(ref) + rms)).max()) <= TOL
