@@ -45,6 +45,9 @@ struct Params {
   void* out; int out_type;          // kF8: bf16 / f32 scaled
   int32_t* c_s32; float* c_f32;     // kI8: raw accumulators and/or scaled f32
   int32_t* status;
+  // pair kernel only: units [0, full_units) are whole 256x256 tiles, units beyond are 256x128 halves of the last tiles
+  int full_units, total_units;
+  uint32_t idesc_half;
 };
 
 // ---- PTX wrappers ----------------------------------------------------------
@@ -434,7 +437,8 @@ __device__ __forceinline__ void umma2(uint32_t tmem_d, uint64_t adesc, uint64_t 
 
 template <int KIND>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const Params p) {
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                const __grid_constant__ CUtensorMap map_w_half, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bar_base = base + kStages * kStageBytes;
@@ -449,7 +453,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();          // 0 = leader (issues the MMAs), 1 = peer
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  const int total_tiles = p.tiles_m * p.tiles_n;    // tiles of 256 x 256
+  // Work units: whole 256 x 256 tiles first; when the last wave would leave more than half of the CTA pairs idle, its
+  // tiles are cut into two 256 x 128 halves (MMA N = 128, 64 rows of W per CTA) so that the tail takes half a wave.
+  auto unit_info = [&](int u, int& tile, int& half, int& width) {
+    if (u < p.full_units) { tile = u; half = 0; width = BN2; }
+    else { const int v = u - p.full_units; tile = p.full_units + (v >> 1); half = v & 1; width = BN2 / 2; }
+  };
   const int num_kb = (int)((p.K + BK - 1) / BK);
 
   if (threadIdx.x == 0) {
@@ -461,6 +470,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w_half)) : "memory");
   }
   if (warp == 1) tmem_alloc2(smem_u32(&s_tmem_base), kTmemCols);
   tc_fence_before();
@@ -475,18 +485,21 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs) {
-        int mb, nb;
+      for (int u = pair; u < p.total_units && ok; u += num_pairs) {
+        int tile, half, width, mb, nb;
+        unit_info(u, tile, half, width);
         tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
+        const uint32_t bytes = 2u * (uint32_t)(kBytesA + (width / 2) * BK);  // both CTAs' bytes land on the leader's barrier
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag)) { ok = false; break; }
           const uint32_t sa = base + s * kStageBytes, sb = sa + kBytesA;
           const uint32_t leader_full = mapa_u32(full_bar(s), 0);
-          if (rank == 0) mbar_expect_tx(full_bar(s), 2 * kStageBytes);   // both CTAs' bytes land on the leader's barrier
+          if (rank == 0) mbar_expect_tx(full_bar(s), bytes);
           tma_load_2d_pair(sa, &map_a, leader_full, kb * BK, mb * 256 + (int)rank * BM);
-          tma_load_2d_pair(sb, &map_w, leader_full, kb * BK, nb * BN2 + (int)rank * (BN2 / 2));
+          if (width == BN2) tma_load_2d_pair(sb, &map_w, leader_full, kb * BK, nb * BN2 + (int)rank * (BN2 / 2));
+          else tma_load_2d_pair(sb, &map_w_half, leader_full, kb * BK, nb * BN2 + half * (BN2 / 2) + (int)rank * (BN2 / 4));
         }
       }
       if (!ok) {   // give copies already issued time to land before shared memory is released
@@ -499,7 +512,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (lane == 0 && rank == 0) {
       uint32_t it = 0, tile_it = 0;
       bool ok = true;
-      for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++tile_it) {
+      for (int u = pair; u < p.total_units && ok; u += num_pairs, ++tile_it) {
+        const uint32_t idesc = u < p.full_units ? p.idesc : p.idesc_half;
         const uint32_t buf = tile_it & 1, aph = (tile_it >> 1) & 1;
         if (!mbar_wait(tempty_bar(buf), aph ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
@@ -513,7 +527,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const uint64_t adesc = make_smem_desc(sa), bdesc = make_smem_desc(sb);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
-            umma2<KIND>(tmem_d, adesc + (uint64_t)(k * (UMMA_K >> 4)), bdesc + (uint64_t)(k * (UMMA_K >> 4)), p.idesc,
+            umma2<KIND>(tmem_d, adesc + (uint64_t)(k * (UMMA_K >> 4)), bdesc + (uint64_t)(k * (UMMA_K >> 4)), idesc,
                         (uint32_t)((kb | k) != 0));
           tc_commit_pair(empty_bar(s));
         }
@@ -531,19 +545,20 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int q = warp & 3;
     uint32_t tile_it = 0;
     bool ok = true;
-    for (int tile = pair; tile < total_tiles && ok; tile += num_pairs, ++tile_it) {
-      int mb, nb;
+    for (int u = pair; u < p.total_units && ok; u += num_pairs, ++tile_it) {
+      int tile, half, width, mb, nb;
+      unit_info(u, tile, half, width);
       tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
       const uint32_t buf = tile_it & 1, aph = (tile_it >> 1) & 1;
       if (!mbar_wait(tfull_bar(buf), aph, abort_flag)) { ok = false; break; }
       tc_fence_after();
       const int64_t m = (int64_t)mb * 256 + rank * BM + q * 32 + lane;
-      const int64_t n0 = (int64_t)nb * BN2;
+      const int64_t n0 = (int64_t)nb * BN2 + half * (BN2 / 2);
       const bool row_ok = m < p.M;
       const float sa = row_ok && p.scale_a ? (p.scale_a_rows ? p.scale_a[m] : p.scale_a[0]) : 1.0f;
       const float sw0 = p.scale_w && !p.scale_w_rows ? p.scale_w[0] : 1.0f;
 #pragma unroll 1
-      for (int c = 0; c < BN2; c += 32) {
+      for (int c = 0; c < width; c += 32) {
         uint32_t r[32];
         __syncwarp();
         tmem_ld32(tmem_base + buf * BN2 + c + ((uint32_t)(q * 32) << 16), r);
@@ -638,9 +653,17 @@ int32_t launch2(b2q_handle h, const void* a, const void* w, Params p) {
   if (st != B2Q_OK) return st;
   st = make_map(h, &map_w, w, p.N, p.K, two::BN2 / 2);
   if (st != B2Q_OK) return st;
+  CUtensorMap map_w_half;
+  st = make_map(h, &map_w_half, w, p.N, p.K, two::BN2 / 4);
+  if (st != B2Q_OK) return st;
   p.tiles_m = (int)ceil_div64(p.M, 256);
   p.tiles_n = (int)ceil_div64(p.N, two::BN2);
-  const uint32_t shape = ((uint32_t)(two::BN2 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+  const uint32_t idesc_fmt = p.idesc;
+  uint32_t shape = ((uint32_t)((two::BN2 / 2) >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+  p.idesc_half = KIND == kF8 ? (idesc_fmt | (1u << 4) | shape)
+               : KIND == kI8 ? ((2u << 4) | (1u << 7) | (1u << 10) | shape)
+                             : ((1u << 4) | (1u << 7) | (1u << 10) | shape);
+  shape = ((uint32_t)(two::BN2 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
   p.idesc = KIND == kF8 ? (p.idesc | (1u << 4) | shape)                                   // fp32 accumulate, E4M3/E5M2 per p.idesc
           : KIND == kI8 ? ((2u << 4) | (1u << 7) | (1u << 10) | shape)                    // s32 accumulate, signed 8-bit A and B
                         : ((1u << 4) | (1u << 7) | (1u << 10) | shape);                   // fp32 accumulate, bf16 A and B
@@ -650,7 +673,13 @@ int32_t launch2(b2q_handle h, const void* a, const void* w, Params p) {
     attr_set = true;
   }
   const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
-  const int pairs = (int)(tiles < h->sm_count / 2 ? tiles : h->sm_count / 2);
+  const int max_pairs = h->sm_count / 2;
+  // tail split: when the last wave fills at most half of the pairs, its tiles become two half-width units each
+  const int rem = (int)(tiles % max_pairs);
+  const bool split = tiles > max_pairs && rem > 0 && 2 * rem <= max_pairs && getenv("B2Q_NO_TAIL_SPLIT") == nullptr;
+  p.full_units = split ? (int)(tiles - rem) : (int)tiles;
+  p.total_units = split ? (int)(tiles + rem) : (int)tiles;
+  const int pairs = (int)(p.total_units < max_pairs ? p.total_units : max_pairs);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(2 * pairs));
   cfg.blockDim = dim3(kThreads);
@@ -663,7 +692,7 @@ int32_t launch2(b2q_handle h, const void* a, const void* w, Params p) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, two::gemm_tc2_kernel<KIND>, map_a, map_w, p));
+  B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, two::gemm_tc2_kernel<KIND>, map_a, map_w, map_w_half, p));
   return B2Q_OK;
 }
 
