@@ -24,6 +24,7 @@ struct b2q_handle_s {
   // allocates): [0] status word, [1..] reduction keys.
   int32_t* d_status;         // 1 x i32
   uint32_t* d_scratch;       // kScratchWords x u32
+  int32_t* d_tile_counters;  // kTileCounters x i32, all zero between launches (split-K arrival counts; the last arriver resets its entry)
   void* ws;                  // grow-only workspace for calls that need temporaries (kept so steady-state calls never allocate)
   size_t ws_bytes;
   char err[512];
@@ -31,6 +32,7 @@ struct b2q_handle_s {
 // Returns a workspace of at least `bytes` (256-byte aligned); grows it when needed (synchronises the stream first).
 int32_t b2q_workspace(b2q_handle h, size_t bytes, void** out);
 static const size_t kScratchWords = 1 << 16;   // 256 KiB of reduction keys / counters
+static const size_t kTileCounters = 1 << 14;
 
 #define B2Q_FAIL(h, code, ...)                                   \
   do {                                                           \

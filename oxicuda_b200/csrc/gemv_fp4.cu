@@ -638,6 +638,192 @@ int32_t launch_e8(b2q_handle h, const uint8_t* codes, const void* scales, const 
                      : launch_e8_t<WK, 8>(h, codes, scales, x, tokens, N, K, out, out_type);
 }
 
+// ---------------------------------------------------------------------------
+// E8M0 kernel for 9..32 tokens: the 128-bit-load inner loop above over MT token tiles.  The activation
+// chunk (8*MT tokens x 512 K values as f16) is too large to stage per warp, so the CTA's WARPS warps own
+// 16 rows each and share one staged chunk; K is split across the CTAs of a cluster and the partial sums
+// are added through distributed shared memory, as in gemv_fp4_kernel.
+// ---------------------------------------------------------------------------
+template <int MT>
+__device__ __forceinline__ void mul_chunk_e8c(const ChunkRegsE8& r, const uint4* xs_lane, int tig, float (&acc0)[MT][4],
+                                              float (&acc1)[MT][4], uint32_t& bad) {
+  constexpr int MPAD = 8 * MT;
+  const uint32_t saw[4] = {r.sa.x, r.sa.y, r.sa.z, r.sa.w};
+  const uint32_t sbw[4] = {r.sb.x, r.sb.y, r.sb.z, r.sb.w};
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    const uint32_t ha2 = e8m0_to_h2((saw[s] >> (8 * tig)) & 0xFFu, bad);
+    const uint32_t hb2 = e8m0_to_h2((sbw[s] >> (8 * tig)) & 0xFFu, bad);
+    const uint32_t wav[4] = {r.wa[s].x, r.wa[s].y, r.wa[s].z, r.wa[s].w};
+    const uint32_t wbv[4] = {r.wb[s].x, r.wb[s].y, r.wb[s].z, r.wb[s].w};
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      uint32_t ha[4], hb[4];
+      cvt_e2m1x8(wav[jj], ha);
+      cvt_e2m1x8(wbv[jj], hb);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { ha[i] = hmul2_u32(ha[i], ha2); hb[i] = hmul2_u32(hb[i], hb2); }
+#pragma unroll
+      for (int t = 0; t < MT; ++t) {
+        const uint4 xv = xs_lane[((s * 4 + jj) * MPAD + t * 8) * 4];   // [step][jj][token][quad lane]
+        mma_f16(acc0[t], ha[0], hb[0], ha[1], hb[1], xv.x, xv.y);
+        mma_f16(acc1[t], ha[2], hb[2], ha[3], hb[3], xv.z, xv.w);
+      }
+    }
+  }
+}
+
+template <int MT, int WARPS, bool DB>
+__global__ void __launch_bounds__(WARPS * 32, DB ? 1 : 512 / (WARPS * 32)) gemv_fp4_e8c_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,
+                                                                  const __nv_bfloat16* __restrict__ x, int tokens, int64_t N, int64_t K,
+                                                                  void* out, int out_type, int split_k, int32_t* status) {
+  constexpr int MPAD = 8 * MT;
+  constexpr int R = 16 * WARPS;
+  constexpr int NT = WARPS * 32;
+  extern __shared__ __align__(16) uint8_t smem[];        // activation chunk, later the partial sums
+  uint4* xs = reinterpret_cast<uint4*>(smem);            // [step 4][jj 4][MPAD][quad lane 4] x 16 bytes
+  float* red = reinterpret_cast<float*>(smem);           // [MPAD][R]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, tig = lane & 3;
+  const int ks = blockIdx.x % split_k;
+  const int64_t row_tile = blockIdx.x / split_k;
+  const int64_t n0 = row_tile * R + warp * 16;
+  const int64_t r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);
+  const int64_t kblocks = K >> 5;
+  const int chunks_total = (int)((K + KC - 1) / KC);
+  const int cpc = (chunks_total + split_k - 1) / split_k;
+  int c = ks * cpc;
+  const int c_end = min(c + cpc, chunks_total);
+  const int total_steps = (int)(K >> 7);
+
+  const uint8_t* w0 = codes + r0 * (K >> 1) + tig * 16 + (int64_t)c * (KC / 2);
+  const uint8_t* w1 = codes + r1 * (K >> 1) + tig * 16 + (int64_t)c * (KC / 2);
+  const uint8_t* s0 = scales + r0 * kblocks + (int64_t)c * (KC / 32);
+  const uint8_t* s1 = scales + r1 * kblocks + (int64_t)c * (KC / 32);
+  const uint4* xs_lane = xs + g * 4 + tig;
+
+  float acc0[MT][4], acc1[MT][4];
+#pragma unroll
+  for (int t = 0; t < MT; ++t) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { acc0[t][i] = 0.0f; acc1[t][i] = 0.0f; }
+  }
+  uint32_t bad = 0;
+
+  // activations of chunk cc for the whole CTA: piece (step, jj, token, quad lane) = x[token][step*128 + lane*32 + jj*8 .. +8)
+  auto stage = [&](int cc) {
+    const int64_t k0 = (int64_t)cc * KC;
+    __syncthreads();                                     // the previous chunk's readers are done
+    for (int i = threadIdx.x; i < 64 * MPAD; i += NT) {
+      const int ttig = i & 3, tok = (i >> 2) % MPAD, sjj = i / (4 * MPAD);
+      const int64_t k = k0 + (sjj >> 2) * 128 + ttig * 32 + (sjj & 3) * 8;
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (tok < tokens && k < K) v = __ldg(reinterpret_cast<const uint4*>(x + (int64_t)tok * K + k));
+      uint4 hv;
+      hv.x = bf16x2_to_f16x2_satfinite(v.x); hv.y = bf16x2_to_f16x2_satfinite(v.y);
+      hv.z = bf16x2_to_f16x2_satfinite(v.z); hv.w = bf16x2_to_f16x2_satfinite(v.w);
+      xs[i] = hv;                                        // == xs[(sjj * MPAD + tok) * 4 + ttig]
+    }
+    __syncthreads();
+  };
+
+  // every warp of the CTA walks the same chunks, so the barriers inside stage() are uniform
+  if constexpr (DB) {                                    // next chunk's weights in a second register set; one CTA per SM
+    ChunkRegsE8 A, B;
+    if (c < c_end) load_chunk_e8(A, w0, w1, s0, s1, min(4, total_steps - c * 4));
+    while (c < c_end) {
+      if (c + 1 < c_end) load_chunk_e8(B, w0 + KC / 2, w1 + KC / 2, s0 + KC / 32, s1 + KC / 32, min(4, total_steps - (c + 1) * 4));
+      stage(c);
+      mul_chunk_e8c<MT>(A, xs_lane, tig, acc0, acc1, bad);
+      ++c; w0 += KC / 2; w1 += KC / 2; s0 += KC / 32; s1 += KC / 32;
+      if (c >= c_end) break;
+      if (c + 1 < c_end) load_chunk_e8(A, w0 + KC / 2, w1 + KC / 2, s0 + KC / 32, s1 + KC / 32, min(4, total_steps - (c + 1) * 4));
+      stage(c);
+      mul_chunk_e8c<MT>(B, xs_lane, tig, acc0, acc1, bad);
+      ++c; w0 += KC / 2; w1 += KC / 2; s0 += KC / 32; s1 += KC / 32;
+    }
+  } else {                                               // one register set, two CTAs per SM hide the load latency
+    for (; c < c_end; ++c) {
+      ChunkRegsE8 A;
+      load_chunk_e8(A, w0, w1, s0, s1, min(4, total_steps - c * 4));
+      stage(c);
+      mul_chunk_e8c<MT>(A, xs_lane, tig, acc0, acc1, bad);
+      w0 += KC / 2; w1 += KC / 2; s0 += KC / 32; s1 += KC / 32;
+    }
+  }
+  if (bad) atomicCAS(status, 0, (int)B2Q_ERR_UNSUPPORTED);
+
+  // ---- partial sums to shared memory: red[token][row within the CTA] ----
+  __syncthreads();
+#pragma unroll
+  for (int t = 0; t < MT; ++t) {
+    const int tok = t * 8 + tig * 2;
+    red[(tok + 0) * R + warp * 16 + g] = acc0[t][0] + acc1[t][0];
+    red[(tok + 1) * R + warp * 16 + g] = acc0[t][1] + acc1[t][1];
+    red[(tok + 0) * R + warp * 16 + g + 8] = acc0[t][2] + acc1[t][2];
+    red[(tok + 1) * R + warp * 16 + g + 8] = acc0[t][3] + acc1[t][3];
+  }
+  cg::cluster_group cluster = cg::this_cluster();
+  if (split_k > 1) cluster.sync(); else __syncthreads();
+  const int E = MPAD * R;
+  const int per = (E + split_k - 1) / split_k;
+  const int e_begin = ks * per, e_end = min(e_begin + per, E);
+  for (int e = e_begin + threadIdx.x; e < e_end; e += NT) {
+    float v = 0.0f;
+    if (split_k > 1) {
+      for (int pr = 0; pr < split_k; ++pr) v += cluster.map_shared_rank(red, pr)[e];
+    } else {
+      v = red[e];
+    }
+    const int tok = e / R;
+    const int64_t n = row_tile * R + (e % R);
+    if (tok < tokens && n < N) {
+      if (out_type == B2Q_OUT_BF16) reinterpret_cast<__nv_bfloat16*>(out)[(int64_t)tok * N + n] = __float2bfloat16_rn(v);
+      else reinterpret_cast<float*>(out)[(int64_t)tok * N + n] = v;
+    }
+  }
+  if (split_k > 1) cluster.sync();                       // peers may still be reading this CTA's partials
+}
+
+template <int MT, int WARPS, bool DB>
+int32_t launch_e8c_t(b2q_handle h, const uint8_t* codes, const void* scales, const void* x, int tokens, int64_t N, int64_t K,
+                   void* out, int out_type) {
+  constexpr int R = 16 * WARPS;
+  const int64_t row_tiles = ceil_div64(N, R);
+  const int chunks = (int)ceil_div64(K, KC);
+  int split = 1;                                         // cluster size: smallest divisor of the chunk count giving ~2 CTAs per SM
+  for (int s = 1; s <= 8 && s <= chunks; ++s) {
+    if (chunks % s != 0) continue;
+    split = s;
+    if (row_tiles * s >= 2 * (int64_t)h->sm_count) break;
+  }
+  const size_t smem = (size_t)1024 * 8 * MT > (size_t)8 * MT * R * 4 ? (size_t)1024 * 8 * MT : (size_t)8 * MT * R * 4;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(row_tiles * split));
+  cfg.blockDim = dim3(WARPS * 32);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = h->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)split;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, gemv_fp4_e8c_kernel<MT, WARPS, DB>, codes, (const uint8_t*)scales, (const __nv_bfloat16*)x, tokens,
+                                 N, K, out, out_type, split, h->d_status));
+  return B2Q_OK;
+}
+
+template <int MT, int WARPS>
+int32_t launch_e8c(b2q_handle h, const uint8_t* codes, const void* scales, const void* x, int tokens, int64_t N, int64_t K,
+                   void* out, int out_type) {
+  const char* db = getenv("B2Q_GEMV_E8C_DB");           // experiment switch: 1 = double-buffered weights, one CTA per SM
+  if (db && db[0] == '1') return launch_e8c_t<MT, WARPS, true>(h, codes, scales, x, tokens, N, K, out, out_type);
+  return launch_e8c_t<MT, WARPS, false>(h, codes, scales, x, tokens, N, K, out, out_type);
+}
+
 template <int WK>
 int32_t launch_small(b2q_handle h, const uint8_t* codes, const void* scales, int scale_format, const void* x, int tokens, int64_t N,
                      int64_t K, void* out, int out_type) {
@@ -649,6 +835,9 @@ int32_t launch_small(b2q_handle h, const uint8_t* codes, const void* scales, int
 }
 
 }  // namespace gemv
+
+int32_t b2q_gemv_fp4_mx_dispatch(b2q_handle h, const uint8_t* codes, const void* scales, const void* x, int tokens, int64_t N, int64_t K,
+                                 void* out, int out_type);
 
 extern "C" int32_t b2q_gemv_fp4_wo(b2q_handle h, const uint8_t* codes, const void* scales, int scale_format, int block,
                                    const void* x_bf16, int64_t tokens, int64_t N, int64_t K, void* out, int out_type) {
@@ -669,6 +858,17 @@ extern "C" int32_t b2q_gemv_fp4_wo(b2q_handle h, const uint8_t* codes, const voi
     B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemv_fp4_wo: scales must be 4-byte (E8M0) or 16-byte (f32) aligned");
   const int t = (int)tokens;
   const bool small_n = N <= 2048;
+  {
+    // E8M0 scales: the tcgen05 block-scaled kernel (weights never touch a CUDA core) where its fixed cost of
+    // about 7 us pays: 16 MiB of codes with 4 tokens or more, 64 MiB with fewer.  B2Q_GEMV_MX=1 / 0 forces it on / off.
+    const char* mxe = getenv("B2Q_GEMV_MX");
+    const int64_t code_bytes = N * (K / 2);
+    const bool mx_pays = code_bytes >= ((int64_t)64 << 20) || (t >= 4 && code_bytes >= ((int64_t)16 << 20));
+    if (scale_format == B2Q_SCALE_E8M0 && (mxe ? mxe[0] == '1' : mx_pays)) {
+      const int32_t st = b2q_gemv_fp4_mx_dispatch(h, codes, scales, x_bf16, t, N, K, out, out_type);
+      if (st != B2Q_ERR_UNSUPPORTED) return st;
+    }
+  }
   if (t <= 8) {
     // experiment switch: B2Q_GEMV_CLUSTER=1 takes the cluster split-K kernel for small token counts too
     const char* force = getenv("B2Q_GEMV_CLUSTER");
@@ -684,6 +884,15 @@ extern "C" int32_t b2q_gemv_fp4_wo(b2q_handle h, const uint8_t* codes, const voi
                        : gemv::launch_e8<4>(h, codes, scales, x_bf16, t, N, K, out, out_type);
     return K >= 8192 ? gemv::launch_small<8>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type)
                      : gemv::launch_small<4>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type);
+  }
+  {
+    const char* exact = getenv("B2Q_GEMV_EXACT");
+    if (scale_format == B2Q_SCALE_E8M0 && !(exact && exact[0] == '1')) {
+      if (t <= 16) return small_n ? gemv::launch_e8c<2, 4>(h, codes, scales, x_bf16, t, N, K, out, out_type)
+                                  : gemv::launch_e8c<2, 8>(h, codes, scales, x_bf16, t, N, K, out, out_type);
+      return small_n ? gemv::launch_e8c<4, 4>(h, codes, scales, x_bf16, t, N, K, out, out_type)
+                     : gemv::launch_e8c<4, 8>(h, codes, scales, x_bf16, t, N, K, out, out_type);
+    }
   }
   if (t <= 16) return small_n ? gemv::launch<2, 4>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type)
                               : gemv::launch<2, 8>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type);

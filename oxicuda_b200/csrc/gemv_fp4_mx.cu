@@ -1,0 +1,592 @@
+// Block-scaled FP4 (E2M1 codes, E8M0 scale per 32) weight-only decode GEMV on the 5th-generation tensor
+// cores: tcgen05.mma kind::mxf8f6f4.block_scale consumes the 4-bit codes and their block scales directly,
+// so no CUDA core touches a weight.
+//   out[t, n] = sum_k x[t, k] * decode(codes[n, k]) * 2^(scale[n, k / 32] - 127)          tokens <= 32
+// (Fp4GemmConfig / MicroScalingQuantizer semantics, crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:337-395,
+//  :879-897, with the weight-only bf16-activation contract of the decode GEMV.)
+//
+// Activations: the instruction takes 8-bit floats, so a small pre-pass writes every bf16 activation as the
+// sum of TWO E4M3 codes under an E8M0 scale per (token, 32-block):  x = 2^e * (c1 + c2),  c1 = rn(x / 2^e),
+// c2 = rn(x / 2^e - c1).  c2 is exact whenever |x| >= 2^-11 of its block's maximum (bf16 has 8 significant
+// bits, c1 keeps 4 and the remainder fits in 4), below that the absolute error is < 2^-18 of the block maximum.
+// The two codes are two accumulator columns of the same MMA (N = 2 * padded tokens) added in the epilogue.
+//
+// Main kernel, persistent, two CTAs per SM (one CTA alone leaves the memory pipe half empty), 7 warps:
+//   warp 0      weight producer: per 128-wide K stage one TMA copy of 128 weight rows (4-bit data expanded by
+//               the TMA unit to the 16-byte-aligned layout the MMA reads, 128-byte swizzle);
+//   warp 6      scale + activation producer: the weight scales of the stage (read with 16-byte loads three
+//               512-wide chunks ahead, written in the 32 x 16-byte scale-factor atom layout) and one bulk copy
+//               of the activation codes + their scale atom;
+//   warp 1      one thread: tcgen05.cp of both scale atoms into TMEM, four tcgen05.mma (K = 32 = one scale
+//               block each), tcgen05.commit to release the stage / publish the accumulator;
+//   warps 2..5  epilogue: tcgen05.ld of the 128 x N accumulator, add the two activation terms, store.
+// The main grid is launched as a programmatic dependent of the pre-pass: its prologue, weight copies and scale
+// loads overlap the pre-pass, only the activation copies wait for it (griddepcontrol.wait).
+// Work units are (128-row tile, K stage) pairs split evenly over the CTAs (stream-K), so every SM streams the
+// same number of bytes whatever N is.  A CTA that owns only part of a tile's K range writes its partial sums
+// to a workspace; the last CTA to arrive at the tile (a counter per tile) adds the partials in CTA order and
+// stores, so results do not depend on arrival order.  Every mbarrier wait is bounded.
+#include "common.cuh"
+#include <cuda.h>
+#include <stdlib.h>
+
+namespace mx {
+
+constexpr int TILE_ROWS = 128;   // weight rows per tile = TMEM lanes
+constexpr int BK = 128;          // K per stage
+constexpr int kTmemCols = 256;   // 2 x 64 accumulator columns + one 8-column scale slot per stage (two CTAs share the 512 columns of an SM)
+constexpr int kSfCol = 128;
+constexpr uint64_t kWaitLimitNs = 500000000ull;
+
+template <int MT> struct Cfg {
+  static constexpr int MPAD = 8 * MT;
+  static constexpr int NB = 2 * MPAD;                          // accumulator columns
+  static constexpr int kBytesW = TILE_ROWS * 128;              // in shared memory (half of it crosses HBM)
+  static constexpr int kBytesX = NB * 128 + 512;               // activation codes + activation scale atom
+  static constexpr int kStageBytes = kBytesW + kBytesX + 512;  // + weight scale atom
+  static constexpr int kStages = MT == 4 ? 4 : 5;               // two CTAs per SM: about 100 KiB each
+  static constexpr int kThreads = 224;
+  static constexpr int kSmem = kStages * kStageBytes + 1024 + 256;
+};
+
+struct Params {
+  const uint8_t* scales;      // [N][K/32] E8M0
+  const uint8_t* xq;          // per K stage: NB x 128 swizzled code bytes, then the 512-byte scale atom (pre-pass output)
+  float* partials;            // [tile][slot][MPAD][128]
+  int32_t* counters;          // [tile], zero on entry and on exit
+  void* out;
+  int out_type;
+  int tokens;
+  int64_t N, K;
+  int stages_per_tile;        // K / 128
+  int units, per;             // work units in total and per CTA
+  int max_slots;
+  uint32_t idesc;
+  int debug;                  // report which wait expired (status 400 + role) instead of B2Q_ERR_TIMEOUT
+  int32_t* status;
+};
+
+// ---- PTX wrappers ----------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint64_t globaltimer_ns() { uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
+// Bounded wait: false when the limit expired or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where = 1) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if (((++spins) & 0x3F) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) { *abort_flag = where; return false; }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+// 32 rows x 16 bytes of shared memory -> 4 TMEM columns, replicated into the four 32-lane quarters
+__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+__device__ __forceinline__ void umma_mx(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t tsfa, uint32_t tsfb,
+                                        uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb) : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// K-major tile of 128-byte rows with the 128-byte swizzle: 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Scale-factor atom: 32 rows of 16 bytes, unswizzled, 8-row groups 128 bytes apart.
+__device__ __forceinline__ uint64_t make_desc_sf(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(128 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  return d;
+}
+
+// ---------------------------------------------------------------------------
+// Activation pre-pass: bf16 [tokens x K] -> per K stage of 128 a block of NB rows x 128 bytes of E4M3 codes
+// (rows 0..MPAD-1 first term, rows MPAD..2*MPAD-1 residual term; 16-byte units XOR-swizzled by row & 7, the
+// layout tcgen05.mma reads with the 128-byte swizzle) followed by the 512-byte E8M0 scale atom
+// (scale of row n, block j at byte (n % 32) * 16 + (n / 32) * 4 + j).  One CTA per stage, 16 threads per
+// token row, 8 values per thread.
+// ---------------------------------------------------------------------------
+// Eight bf16 activations (one quarter of a 32-block; the four lanes of a block are consecutive) -> eight
+// first-term and eight residual E4M3 codes; returns the block exponent e (scale byte e + 127).
+// Warp-collective (two shuffles).
+__device__ __forceinline__ int quant_piece(const uint4& v, uint32_t (&c1)[2], uint32_t (&c2)[2]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+  float f[8];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    f[2 * j] = __uint_as_float(w[j] << 16);
+    f[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+  }
+  float amax = 0.0f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(f[j]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 1));
+  amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, 2));   // the four threads of one 32-block
+  // block exponent e: the smallest one with amax / 2^e <= 448 (= 1.75 * 2^8)
+  const uint32_t ab = __float_as_uint(amax);
+  int e = (int)((ab >> 23) & 0xFF) - 127 - 8 + ((ab & 0x007FFFFFu) > 0x00600000u ? 1 : 0);
+  if (amax == 0.0f || !(amax <= 3.0e38f)) e = 0;               // empty block; inf/nan blocks keep scale 1
+  e = max(e, -127);
+  const float inv = __uint_as_float((uint32_t)(127 - e) << 23);  // 2^-e, exponent field in [7, 254]
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float q0 = f[2 * j] * inv, q1 = f[2 * j + 1] * inv;  // exact (power-of-two scaling)
+    const __nv_fp8x2_storage_t a = __nv_cvt_float2_to_fp8x2(make_float2(q0, q1), __NV_SATFINITE, __NV_E4M3);
+    const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(a, __NV_E4M3);
+    const float2 back = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+    const __nv_fp8x2_storage_t b = __nv_cvt_float2_to_fp8x2(make_float2(q0 - back.x, q1 - back.y), __NV_SATFINITE, __NV_E4M3);
+    if (j & 1) { c1[j >> 1] |= (uint32_t)a << 16; c2[j >> 1] |= (uint32_t)b << 16; }
+    else       { c1[j >> 1] = (uint32_t)a;        c2[j >> 1] = (uint32_t)b; }
+  }
+  return e;
+}
+
+template <int MT>
+__global__ void __launch_bounds__(128 * MT) x_quant_mx_kernel(const __nv_bfloat16* __restrict__ x, int tokens, int64_t K, uint8_t* __restrict__ xq) {
+  using C = Cfg<MT>;
+  __shared__ uint32_t sf[128];
+  const int tid = threadIdx.x;
+  const int i = tid & 15, t = tid >> 4;                        // 16-byte piece of the stage, token row
+  const int64_t kb = blockIdx.x;
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the dependent grid only waits where it reads this grid's output
+  if (tid < 128) sf[tid] = 0;
+  __syncthreads();
+
+  uint4 v = make_uint4(0, 0, 0, 0);
+  if (t < tokens) v = __ldg(reinterpret_cast<const uint4*>(x + (int64_t)t * K + kb * BK + i * 8));
+  uint32_t c1[2], c2[2];
+  const int e = quant_piece(v, c1, c2);
+  uint8_t* blk = xq + kb * C::kBytesX;
+  const int n1 = t, n2 = C::MPAD + t;
+  *reinterpret_cast<uint2*>(blk + n1 * 128 + (((i >> 1) ^ (n1 & 7)) << 4) + (i & 1) * 8) = make_uint2(c1[0], c1[1]);
+  *reinterpret_cast<uint2*>(blk + n2 * 128 + (((i >> 1) ^ (n2 & 7)) << 4) + (i & 1) * 8) = make_uint2(c2[0], c2[1]);
+  if ((i & 3) == 0) {
+    uint8_t* sfb = reinterpret_cast<uint8_t*>(sf);
+    const uint8_t sb = (uint8_t)(e + 127);
+    sfb[(n1 & 31) * 16 + (n1 >> 5) * 4 + (i >> 2)] = sb;
+    sfb[(n2 & 31) * 16 + (n2 >> 5) * 4 + (i >> 2)] = sb;
+  }
+  __syncthreads();
+  if (tid < 128) reinterpret_cast<uint32_t*>(blk + C::NB * 128)[tid] = sf[tid];
+}
+
+// ---------------------------------------------------------------------------
+// Main kernel
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t pick_word(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
+
+template <int MT>
+__global__ void __launch_bounds__(Cfg<MT>::kThreads, 2) gemv_fp4_mx_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
+  using C = Cfg<MT>;
+  constexpr int kStages = C::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+  const uint32_t bar_base = base + kStages * C::kStageBytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * kStages + 2 + b); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * kStages + 4);
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+  __shared__ int s_last;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int S = p.stages_per_tile;
+  const int u0 = blockIdx.x * p.per, u1 = min(u0 + p.per, p.units);
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    // a stage is full after two arrivals: the weight copy was issued, and the scale atom is written + the activation copy issued
+    for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 2); mbar_init(empty_bar(s), 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
+    mbar_init(drain_bar, 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
+    // the first round of weight copies needs nothing but the barriers: start the HBM stream before the rest of the prologue
+    for (int it = 0; it < kStages && u0 + it < u1; ++it) {
+      const int u = u0 + it, tile = u / S, j = u - tile * S;
+      mbar_expect_tx(full_bar(it), C::kBytesW / 2);
+      tma_load_2d(base + it * C::kStageBytes, &map_w, full_bar(it), j * BK, tile * TILE_ROWS);
+    }
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&s_tmem_base), kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = s_tmem_base;
+  volatile int* abort_flag = &s_abort;
+
+  if (warp == 0) {
+    // ---------------- weight producer: one TMA copy per stage ----------------
+    if (lane == 0) {
+      uint32_t it = (uint32_t)min(kStages, u1 - u0);           // the first round was issued in the prologue
+      bool ok = true;
+      for (int u = u0 + (int)it; u < u1; ++u, ++it) {
+        const int tile = u / S, j = u - tile * S;
+        const int s = it % kStages;
+        const uint32_t ph = (it / kStages) & 1;
+        if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, 1)) { ok = false; break; }
+        // the mbarrier counts the packed bytes read from global memory (64 per row), not the padded bytes written
+        mbar_expect_tx(full_bar(s), C::kBytesW / 2);
+        tma_load_2d(base + s * C::kStageBytes, &map_w, full_bar(s), j * BK, tile * TILE_ROWS);
+      }
+      if (!ok) {
+        // give every copy already issued a bounded chance to land before shared memory is released
+        const uint32_t issued = it < (uint32_t)kStages ? it : (uint32_t)kStages;
+        for (uint32_t q = 0; q < issued; ++q) {
+          const uint32_t w = it - 1 - q;
+          const uint64_t t0 = globaltimer_ns();
+          while (!mbar_try_wait(full_bar(w % kStages), (w / kStages) & 1))
+            if (globaltimer_ns() - t0 > 100000000ull) break;
+        }
+      }
+    }
+  } else if (warp == 6) {
+    // ---------------- scale + activation producer (whole warp: every lane owns one 16-byte line of the weight scale atom) ----------------
+    const int64_t kblocks = p.K >> 5;
+    // scale words are prefetched kAhead chunks (of 4 stages) ahead of use: they come from HBM like the codes
+    constexpr int kAhead = 3;
+    uint4 q[kAhead + 1][4];
+    int key_cur = u0 >> 2;
+    // scale bytes of the 512-wide chunk `key` (4 stages) for rows lane, lane+32, lane+64, lane+96 of its tile
+    auto load_scales = [&](int key, uint4 (&dst)[4]) {
+      const int tile = (key * 4) / S, chunk = ((key * 4) % S) >> 2;
+#pragma unroll
+      for (int r1 = 0; r1 < 4; ++r1) {
+        const int64_t row = min((int64_t)tile * TILE_ROWS + lane + 32 * r1, p.N - 1);
+        dst[r1] = __ldg(reinterpret_cast<const uint4*>(p.scales + row * kblocks + chunk * 16));
+      }
+    };
+#pragma unroll
+    for (int a = 0; a <= kAhead; ++a)
+      if ((key_cur + a) * 4 < u1) load_scales(key_cur + a, q[a]);
+    // the activation codes come from the pre-pass kernel, which this grid may overlap (programmatic dependent
+    // launch): nothing of it is read before this point
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    uint32_t it = 0;
+    for (int u = u0; u < u1; ++u, ++it) {
+      const int j = u % S;
+      const int key = u >> 2;
+      if (key != key_cur) {                                    // the keys of a CTA are consecutive
+#pragma unroll
+        for (int a = 0; a < kAhead; ++a) {
+#pragma unroll
+          for (int r1 = 0; r1 < 4; ++r1) q[a][r1] = q[a + 1][r1];
+        }
+        key_cur = key;
+        if ((key + kAhead) * 4 < u1) load_scales(key + kAhead, q[kAhead]);
+      }
+      const int s = it % kStages;
+      const uint32_t ph = (it / kStages) & 1;
+      if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, 5)) break;
+      uint4 line;
+      line.x = pick_word(q[0][0], u & 3); line.y = pick_word(q[0][1], u & 3);
+      line.z = pick_word(q[0][2], u & 3); line.w = pick_word(q[0][3], u & 3);
+      *reinterpret_cast<uint4*>(base_ptr + s * C::kStageBytes + C::kBytesW + C::kBytesX + lane * 16) = line;
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the scale atom is read by tcgen05.cp
+      __syncwarp();
+      if (lane == 0) {
+        mbar_expect_tx(full_bar(s), C::kBytesX);
+        bulk_load(base + s * C::kStageBytes + C::kBytesW, p.xq + (int64_t)j * C::kBytesX, C::kBytesX, full_bar(s));
+      }
+    }
+    // on a failed wait the copies of this warp are covered by the weight producer's drain (same barriers)
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      uint32_t it = 0, seg_it = 0;
+      bool ok = true;
+      for (int u = u0; u < u1 && ok; ++seg_it) {
+        const int tile = u / S, j0 = u - tile * S;
+        const int n = min(u1 - u, S - j0);
+        const uint32_t buf = seg_it & 1, aph = (seg_it >> 1) & 1;
+        if (!mbar_wait(tempty_bar(buf), aph ^ 1, abort_flag, 2)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + buf * 64;
+        for (int jj = 0; jj < n; ++jj, ++it) {
+          const int s = it % kStages;
+          const uint32_t ph = (it / kStages) & 1;
+          if (!mbar_wait(full_bar(s), ph, abort_flag, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sw = base + s * C::kStageBytes, sx = sw + C::kBytesW;
+          const uint32_t tsfa = tmem_base + kSfCol + s * 8, tsfb = tsfa + 4;
+          tmem_cp_sf(tsfa, make_desc_sf(sx + C::kBytesX));
+          tmem_cp_sf(tsfb, make_desc_sf(sx + C::NB * 128));
+          const uint64_t adesc = make_desc_sw128(sw), bdesc = make_desc_sw128(sx);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            // K advance inside the swizzle atom: +32 bytes; scale byte k of the atom's columns
+            umma_mx(tmem_d, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), p.idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4),
+                    tsfa, tsfb, (uint32_t)((jj | k) != 0));
+          }
+          tc_commit(empty_bar(s));
+        }
+        if (ok) tc_commit(tfull_bar(buf));
+        u += n;
+      }
+      if (!ok) {
+        tc_commit(drain_bar);
+        const uint64_t t0 = globaltimer_ns();
+        while (!mbar_try_wait(drain_bar, 0))
+          if (globaltimer_ns() - t0 > 100000000ull) break;
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int q = warp & 3;                                   // TMEM lane quarter this warp may access
+    const int row_local = q * 32 + lane;
+    uint32_t seg_it = 0;
+    bool ok = true;
+    for (int u = u0; u < u1 && ok; ++seg_it) {
+      const int tile = u / S, j0 = u - tile * S;
+      const int n = min(u1 - u, S - j0);
+      u += n;
+      const uint32_t buf = seg_it & 1, aph = (seg_it >> 1) & 1;
+      if (!mbar_wait(tfull_bar(buf), aph, abort_flag, 4)) { ok = false; break; }
+      tc_fence_after();
+      float v[C::MPAD];
+#pragma unroll
+      for (int c = 0; c < C::NB; c += 16) {
+        uint32_t r[16];
+        tmem_ld16(tmem_base + buf * 64 + c + ((uint32_t)(q * 32) << 16), r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const int col = c + i;                              // compile-time after unrolling
+          if (col < C::MPAD) v[col] = __uint_as_float(r[i]);
+          else v[col - C::MPAD] += __uint_as_float(r[i]);     // residual term of the same token
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tempty_bar(buf));            // accumulator is in registers now
+      const int64_t row = (int64_t)tile * TILE_ROWS + row_local;
+      auto store_out = [&](int t, float val) {
+        if (row < p.N) {
+          if (p.out_type == B2Q_OUT_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[(int64_t)t * p.N + row] = __float2bfloat16_rn(val);
+          else reinterpret_cast<float*>(p.out)[(int64_t)t * p.N + row] = val;
+        }
+      };
+      if (n == S) {                                           // this CTA owns the tile's whole K range
+#pragma unroll
+        for (int t = 0; t < C::MPAD; ++t) if (t < p.tokens) store_out(t, v[t]);
+      } else {
+        const int first = (tile * S) / p.per, last = (tile * S + S - 1) / p.per;
+        const int nc = last - first + 1, slot = (int)blockIdx.x - first;
+        float* mine = p.partials + ((int64_t)tile * p.max_slots + slot) * (C::MPAD * TILE_ROWS);
+#pragma unroll
+        for (int t = 0; t < C::MPAD; ++t) if (t < p.tokens) mine[t * TILE_ROWS + row_local] = v[t];
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (warp == 2 && lane == 0) {
+          const int old = atomicAdd(p.counters + tile, 1);
+          s_last = (old == nc - 1);
+          if (old == nc - 1) p.counters[tile] = 0;            // every contributor has arrived: leave the counter zero
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (s_last) {
+          __threadfence();
+          const float* all = p.partials + (int64_t)tile * p.max_slots * (C::MPAD * TILE_ROWS);
+          float sum[C::MPAD];
+#pragma unroll
+          for (int t = 0; t < C::MPAD; ++t) sum[t] = 0.0f;
+          for (int c = 0; c < nc; ++c) {                      // contributors in CTA order; the loads of one contributor are independent
+            float part[C::MPAD];
+#pragma unroll
+            for (int t = 0; t < C::MPAD; ++t)
+              part[t] = t < p.tokens ? __ldcg(all + (int64_t)c * (C::MPAD * TILE_ROWS) + t * TILE_ROWS + row_local) : 0.0f;
+#pragma unroll
+            for (int t = 0; t < C::MPAD; ++t) sum[t] += part[t];
+          }
+#pragma unroll
+          for (int t = 0; t < C::MPAD; ++t) if (t < p.tokens) store_out(t, sum[t]);
+        }
+      }
+    }
+  }
+
+  // ---------------- teardown ----------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+  if (threadIdx.x == 0 && s_abort) atomicCAS(p.status, 0, p.debug ? 400 + s_abort : (int)B2Q_ERR_TIMEOUT);
+}
+
+// ---- host side --------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)sym;
+  }
+  return fn;
+}
+
+static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+template <int MT>
+int32_t launch(b2q_handle h, const uint8_t* codes, const uint8_t* scales, const void* x, int tokens, int64_t N, int64_t K, void* out,
+               int out_type) {
+  using C = Cfg<MT>;
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) B2Q_FAIL(h, B2Q_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  // weight codes as a [N][K] tensor of 4-bit elements; a box is 128 codes x 128 rows and lands in shared memory
+  // as 128-byte rows (8 data bytes + 8 pad bytes per 16 codes), 128-byte swizzle, zero fill past row N
+  CUtensorMap map_w;
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)N};
+  cuuint64_t strides[1] = {(cuuint64_t)(K / 2)};
+  cuuint32_t box[2] = {128, (cuuint32_t)TILE_ROWS};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(&map_w, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN16B, 2, const_cast<uint8_t*>(codes), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) B2Q_FAIL(h, B2Q_ERR_CUDA, "cuTensorMapEncodeTiled (4-bit weights) failed with CUresult %d", (int)r);
+
+  Params p = {};
+  const int S = (int)(K / BK);
+  const int64_t tiles = ceil_div64(N, TILE_ROWS);
+  const int64_t units = tiles * S;
+  const int64_t slots = 2 * (int64_t)h->sm_count;              // two CTAs per SM: one CTA alone cannot keep the memory pipe full
+  int grid = (int)(units < slots ? units : slots);
+  const int per = (int)ceil_div64(units, grid);
+  grid = (int)ceil_div64(units, per);
+  p.max_slots = (S + per - 1) / per + 1;
+  const size_t xq_bytes = align256((size_t)S * C::kBytesX);
+  const size_t part_bytes = (size_t)tiles * p.max_slots * C::MPAD * TILE_ROWS * sizeof(float);
+  void* ws = nullptr;
+  int32_t st = b2q_workspace(h, xq_bytes + part_bytes, &ws);
+  if (st != B2Q_OK) return st;
+  p.scales = scales;
+  p.xq = reinterpret_cast<const uint8_t*>(ws);
+  p.partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + xq_bytes);
+  p.counters = h->d_tile_counters;
+  p.out = out;
+  p.out_type = out_type;
+  p.tokens = tokens;
+  p.N = N;
+  p.K = K;
+  p.stages_per_tile = S;
+  p.units = (int)units;
+  p.per = per;
+  // block-scaled instruction descriptor: A = E2M1 (5), B = E4M3 (0), both K-major, N = NB, E8M0 scales, M = 128
+  p.idesc = (5u << 7) | (0u << 10) | ((uint32_t)(C::NB >> 3) << 17) | (1u << 23) | ((uint32_t)(TILE_ROWS >> 4) << 24);
+  if (const char* e = getenv("B2Q_MX_DEBUG")) p.debug = atoi(e);   // 1: report which wait expired as status 400 + role
+  p.status = h->d_status;
+
+  const char* skip_pre = getenv("B2Q_MX_SKIP_PRE");   // timing experiment: reuse the activation codes of the previous call
+  if (!(skip_pre && skip_pre[0] == '1'))
+  x_quant_mx_kernel<MT><<<S, 128 * MT, 0, h->stream>>>((const __nv_bfloat16*)x, tokens, K, reinterpret_cast<uint8_t*>(ws));
+  B2Q_LAUNCH_CHECK(h, "x_quant_mx_kernel");
+  static bool attr_set = false;
+  if (!attr_set) {
+    B2Q_CUDA(h, cudaFuncSetAttribute(gemv_fp4_mx_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
+    attr_set = true;
+  }
+  // programmatic dependent launch: this grid may start while the pre-pass runs; its activation loads wait for it
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(C::kThreads);
+  cfg.dynamicSmemBytes = C::kSmem;
+  cfg.stream = h->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  const char* pdl = getenv("B2Q_MX_PDL");
+  cfg.attrs = attr;
+  cfg.numAttrs = (pdl && pdl[0] == '0') ? 0 : 1;
+  B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, gemv_fp4_mx_kernel<MT>, map_w, p));
+  return B2Q_OK;
+}
+
+}  // namespace mx
+
+// Tensor-core FP4 decode GEMV for E8M0 scales; B2Q_ERR_UNSUPPORTED (nothing launched) when the shape or the
+// alignment does not fit: K % 512, codes 32-byte aligned, scales 16-byte aligned, tokens <= 32.
+int32_t b2q_gemv_fp4_mx_dispatch(b2q_handle h, const uint8_t* codes, const void* scales, const void* x, int tokens, int64_t N, int64_t K,
+                                 void* out, int out_type) {
+  if (tokens < 1 || tokens > 32 || K % 512 != 0 || N < 1) return B2Q_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(codes) & 31) != 0 || (reinterpret_cast<uintptr_t>(scales) & 15) != 0 ||
+      (reinterpret_cast<uintptr_t>(x) & 15) != 0)
+    return B2Q_ERR_UNSUPPORTED;
+  if (ceil_div64(N, mx::TILE_ROWS) > (int64_t)kTileCounters || ceil_div64(N, mx::TILE_ROWS) * (K / mx::BK) > 0x7FFFFFFF)
+    return B2Q_ERR_UNSUPPORTED;
+  if (tokens <= 8) return mx::launch<1>(h, codes, (const uint8_t*)scales, x, tokens, N, K, out, out_type);
+  if (tokens <= 16) return mx::launch<2>(h, codes, (const uint8_t*)scales, x, tokens, N, K, out, out_type);
+  return mx::launch<4>(h, codes, (const uint8_t*)scales, x, tokens, N, K, out, out_type);
+}

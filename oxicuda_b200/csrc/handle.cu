@@ -39,10 +39,13 @@ int32_t b2q_create(b2q_handle* out, int device) {
   }
   if (cudaMalloc(&h->d_status, sizeof(int32_t)) != cudaSuccess ||
       cudaMalloc(&h->d_scratch, kScratchWords * sizeof(uint32_t)) != cudaSuccess ||
+      cudaMalloc(&h->d_tile_counters, kTileCounters * sizeof(int32_t)) != cudaSuccess ||
+      cudaMemset(h->d_tile_counters, 0, kTileCounters * sizeof(int32_t)) != cudaSuccess ||
       cudaMemset(h->d_status, 0, sizeof(int32_t)) != cudaSuccess ||
       cudaMemset(h->d_scratch, 0, kScratchWords * sizeof(uint32_t)) != cudaSuccess) {
     cudaFree(h->d_status);
     cudaFree(h->d_scratch);
+    cudaFree(h->d_tile_counters);
     delete h;
     return B2Q_ERR_CUDA;
   }
@@ -56,6 +59,7 @@ int32_t b2q_destroy(b2q_handle h) {
   cudaSetDevice(h->device);
   cudaFree(h->d_status);
   cudaFree(h->d_scratch);
+  cudaFree(h->d_tile_counters);
   if (h->ws) cudaFree(h->ws);
   delete h;
   return B2Q_OK;
