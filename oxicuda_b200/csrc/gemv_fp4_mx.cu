@@ -34,8 +34,6 @@ namespace mx {
 
 constexpr int TILE_ROWS = 128;   // weight rows per tile = TMEM lanes
 constexpr int BK = 128;          // K per stage
-constexpr int kTmemCols = 256;   // 2 x 64 accumulator columns + one 8-column scale slot per stage (two CTAs share the 512 columns of an SM)
-constexpr int kSfCol = 128;
 constexpr uint64_t kWaitLimitNs = 500000000ull;
 
 template <int MT> struct Cfg {
@@ -44,7 +42,12 @@ template <int MT> struct Cfg {
   static constexpr int kBytesW = TILE_ROWS * 128;              // in shared memory (half of it crosses HBM)
   static constexpr int kBytesX = NB * 128 + 512;               // activation codes + activation scale atom
   static constexpr int kStageBytes = kBytesW + kBytesX + 512;  // + weight scale atom
-  static constexpr int kStages = MT == 4 ? 4 : 5;               // two CTAs per SM: about 100 KiB each
+  // One CTA sustains about one stage per 440 ns whatever its pipeline depth, so the SM is shared by several CTAs:
+  // three (3 stages, 64 TMEM columns each) up to 8 tokens, two above.
+  static constexpr int kCtasPerSm = MT == 1 ? 3 : 2;
+  static constexpr int kStages = MT == 1 ? 3 : (MT == 2 ? 5 : 4);
+  static constexpr int kSfCol = 2 * NB;                         // TMEM: two accumulators of NB columns, then an 8-column scale slot per stage
+  static constexpr int kTmemCols = MT == 1 ? 64 : (MT == 2 ? 128 : 256);
   static constexpr int kThreads = 224;
   static constexpr int kSmem = kStages * kStageBytes + 1024 + 256;
 };
@@ -211,7 +214,12 @@ __global__ void __launch_bounds__(128 * MT) x_quant_mx_kernel(const __nv_bfloat1
   const int tid = threadIdx.x;
   const int i = tid & 15, t = tid >> 4;                        // 16-byte piece of the stage, token row
   const int64_t kb = blockIdx.x;
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");   // the dependent grid only waits where it reads this grid's output
+  // Programmatic dependent launch on both sides: the main kernel may start now (it waits for this grid only
+  // where it reads the codes written here), and this grid may itself have started before the previous kernel
+  // of the stream finished, so it waits for that kernel before it reads the activations or overwrites the
+  // code buffer the previous GEMV may still be reading.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (tid < 128) sf[tid] = 0;
   __syncthreads();
 
@@ -239,7 +247,7 @@ __global__ void __launch_bounds__(128 * MT) x_quant_mx_kernel(const __nv_bfloat1
 __device__ __forceinline__ uint32_t pick_word(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 
 template <int MT>
-__global__ void __launch_bounds__(Cfg<MT>::kThreads, 2) gemv_fp4_mx_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
+__global__ void __launch_bounds__(Cfg<MT>::kThreads, Cfg<MT>::kCtasPerSm) gemv_fp4_mx_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
   using C = Cfg<MT>;
   constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -275,12 +283,15 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, 2) gemv_fp4_mx_kernel(const
       tma_load_2d(base + it * C::kStageBytes, &map_w, full_bar(it), j * BK, tile * TILE_ROWS);
     }
   }
-  if (warp == 1) tmem_alloc(smem_u32(&s_tmem_base), kTmemCols);
+  if (warp == 1) tmem_alloc(smem_u32(&s_tmem_base), C::kTmemCols);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = s_tmem_base;
   volatile int* abort_flag = &s_abort;
+  // the next kernel of the stream may be scheduled as SMs free up; whatever it reads of this grid's output it reads
+  // after its own griddepcontrol.wait, i.e. after this grid has completed
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp == 0) {
     // ---------------- weight producer: one TMA copy per stage ----------------
@@ -368,14 +379,14 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, 2) gemv_fp4_mx_kernel(const
         const uint32_t buf = seg_it & 1, aph = (seg_it >> 1) & 1;
         if (!mbar_wait(tempty_bar(buf), aph ^ 1, abort_flag, 2)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + buf * 64;
+        const uint32_t tmem_d = tmem_base + buf * C::NB;
         for (int jj = 0; jj < n; ++jj, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (it / kStages) & 1;
           if (!mbar_wait(full_bar(s), ph, abort_flag, 3)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sw = base + s * C::kStageBytes, sx = sw + C::kBytesW;
-          const uint32_t tsfa = tmem_base + kSfCol + s * 8, tsfb = tsfa + 4;
+          const uint32_t tsfa = tmem_base + C::kSfCol + s * 8, tsfb = tsfa + 4;
           tmem_cp_sf(tsfa, make_desc_sf(sx + C::kBytesX));
           tmem_cp_sf(tsfb, make_desc_sf(sx + C::NB * 128));
           const uint64_t adesc = make_desc_sw128(sw), bdesc = make_desc_sw128(sx);
@@ -414,7 +425,7 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, 2) gemv_fp4_mx_kernel(const
 #pragma unroll
       for (int c = 0; c < C::NB; c += 16) {
         uint32_t r[16];
-        tmem_ld16(tmem_base + buf * 64 + c + ((uint32_t)(q * 32) << 16), r);
+        tmem_ld16(tmem_base + buf * C::NB + c + ((uint32_t)(q * 32) << 16), r);
         tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
@@ -476,7 +487,7 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, 2) gemv_fp4_mx_kernel(const
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc(tmem_base, C::kTmemCols);
   }
   if (threadIdx.x == 0 && s_abort) atomicCAS(p.status, 0, p.debug ? 400 + s_abort : (int)B2Q_ERR_TIMEOUT);
 }
@@ -522,7 +533,7 @@ int32_t launch(b2q_handle h, const uint8_t* codes, const uint8_t* scales, const 
   const int S = (int)(K / BK);
   const int64_t tiles = ceil_div64(N, TILE_ROWS);
   const int64_t units = tiles * S;
-  const int64_t slots = 2 * (int64_t)h->sm_count;              // two CTAs per SM: one CTA alone cannot keep the memory pipe full
+  const int64_t slots = (int64_t)C::kCtasPerSm * h->sm_count;
   int grid = (int)(units < slots ? units : slots);
   const int per = (int)ceil_div64(units, grid);
   grid = (int)ceil_div64(units, per);
@@ -550,9 +561,20 @@ int32_t launch(b2q_handle h, const uint8_t* codes, const uint8_t* scales, const 
   p.status = h->d_status;
 
   const char* skip_pre = getenv("B2Q_MX_SKIP_PRE");   // timing experiment: reuse the activation codes of the previous call
-  if (!(skip_pre && skip_pre[0] == '1'))
-  x_quant_mx_kernel<MT><<<S, 128 * MT, 0, h->stream>>>((const __nv_bfloat16*)x, tokens, K, reinterpret_cast<uint8_t*>(ws));
-  B2Q_LAUNCH_CHECK(h, "x_quant_mx_kernel");
+  const char* pdl = getenv("B2Q_MX_PDL");                      // 0: plain stream-ordered launches
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  const int num_attrs = (pdl && pdl[0] == '0') ? 0 : 1;
+  if (!(skip_pre && skip_pre[0] == '1')) {
+    cudaLaunchConfig_t pre = {};
+    pre.gridDim = dim3((unsigned)S);
+    pre.blockDim = dim3(128 * MT);
+    pre.stream = h->stream;
+    pre.attrs = attr;
+    pre.numAttrs = num_attrs;
+    B2Q_CUDA(h, cudaLaunchKernelEx(&pre, x_quant_mx_kernel<MT>, (const __nv_bfloat16*)x, tokens, K, reinterpret_cast<uint8_t*>(ws)));
+  }
   static bool attr_set = false;
   if (!attr_set) {
     B2Q_CUDA(h, cudaFuncSetAttribute(gemv_fp4_mx_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
@@ -564,12 +586,8 @@ int32_t launch(b2q_handle h, const uint8_t* codes, const uint8_t* scales, const 
   cfg.blockDim = dim3(C::kThreads);
   cfg.dynamicSmemBytes = C::kSmem;
   cfg.stream = h->stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  const char* pdl = getenv("B2Q_MX_PDL");
   cfg.attrs = attr;
-  cfg.numAttrs = (pdl && pdl[0] == '0') ? 0 : 1;
+  cfg.numAttrs = num_attrs;
   B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, gemv_fp4_mx_kernel<MT>, map_w, p));
   return B2Q_OK;
 }
