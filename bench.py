@@ -442,9 +442,12 @@ def side_measurements(dev, peaks):
     import torch
     from oxicuda_b200.blas import MicroScalingConfig, MicroScalingQuantizer, ScalingFormat, gemv_fp4_wo
     from oxicuda_b200.quant import LlmInt8Config, LlmInt8Quantizer
-    res = {"gemv_fp4_e8m0": {"timing": "CUDA-graph replay of back-to-back launches over rotating weight copies (> L2)"}}
+    res = {"gemv_fp4_e8m0": {"timing": "CUDA-graph replay of back-to-back launches over rotating weight copies (> L2); "
+                                       "consecutive launches of the tcgen05 kernel overlap their prologue with the previous tail "
+                                       "(programmatic dependent launch), as they do in a decode step"}}
     msq = MicroScalingQuantizer(MicroScalingConfig(32, ScalingFormat.E8M0))
-    for (Kd, Nd) in ((4096, 4096), (4096, 1024), (4096, 14336), (14336, 4096)):
+    # the four Llama-3-8B-shaped projections of the configuration, and the 70B-shaped FFN projection
+    for (Kd, Nd) in ((4096, 4096), (4096, 1024), (4096, 14336), (14336, 4096), (8192, 28672)):
         copies = max(4, int(300e6 // (Nd * Kd // 2)) + 1)         # rotate weight copies: > 126 MB L2 in total
         ws = []
         for c in range(copies):

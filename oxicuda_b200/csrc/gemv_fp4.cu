@@ -859,11 +859,12 @@ extern "C" int32_t b2q_gemv_fp4_wo(b2q_handle h, const uint8_t* codes, const voi
   const int t = (int)tokens;
   const bool small_n = N <= 2048;
   {
-    // E8M0 scales: the tcgen05 block-scaled kernel (weights never touch a CUDA core) where its fixed cost of
-    // about 7 us pays: 16 MiB of codes with 4 tokens or more, 40 MiB with fewer.  B2Q_GEMV_MX=1 / 0 forces it on / off.
+    // E8M0 scales: the tcgen05 block-scaled kernel (weights never touch a CUDA core) where its fixed cost pays:
+    // from 16 MiB of codes with 4 tokens or more or with enough rows for one tile per SM (no partial sums to
+    // exchange), from 40 MiB otherwise.  B2Q_GEMV_MX=1 / 0 forces it on / off.
     const char* mxe = getenv("B2Q_GEMV_MX");
     const int64_t code_bytes = N * (K / 2);
-    const bool mx_pays = code_bytes >= ((int64_t)40 << 20) || (t >= 4 && code_bytes >= ((int64_t)16 << 20));
+    const bool mx_pays = code_bytes >= ((int64_t)40 << 20) || (code_bytes >= ((int64_t)16 << 20) && (t >= 4 || N >= 13312));
     if (scale_format == B2Q_SCALE_E8M0 && (mxe ? mxe[0] == '1' : mx_pays)) {
       const int32_t st = b2q_gemv_fp4_mx_dispatch(h, codes, scales, x_bf16, t, N, K, out, out_type);
       if (st != B2Q_ERR_UNSUPPORTED) return st;

@@ -42,13 +42,23 @@ template <int MT> struct Cfg {
   static constexpr int kBytesW = TILE_ROWS * 128;              // in shared memory (half of it crosses HBM)
   static constexpr int kBytesX = NB * 128 + 512;               // activation codes + activation scale atom
   static constexpr int kStageBytes = kBytesW + kBytesX + 512;  // + weight scale atom
-  // One CTA sustains about one stage per 440 ns whatever its pipeline depth, so the SM is shared by several CTAs:
-  // three (3 stages, 64 TMEM columns each) up to 8 tokens, two above.
-  static constexpr int kCtasPerSm = MT == 1 ? 3 : 2;
-  static constexpr int kStages = MT == 1 ? 3 : (MT == 2 ? 5 : 4);
-  static constexpr int kSfCol = 2 * NB;                         // TMEM: two accumulators of NB columns, then an 8-column scale slot per stage
-  static constexpr int kTmemCols = MT == 1 ? 64 : (MT == 2 ? 128 : 256);
-  static constexpr int kThreads = 224;
+  // One thread sustains about one asynchronous copy per 250 ns (measured: wait on the stage, expect_tx, issue), far
+  // less than one SM's share of the HBM stream, so the copies of consecutive stages are issued by kWWarps weight
+  // warps and kXWarps scale/activation warps in turn; with that one CTA per SM keeps the memory pipe full.
+  // The stage count is a multiple of every role's warp count, so a stage is always filled and consumed by the same
+  // warps: the parity waits on its barriers then never see a party more than one phase away (with a round-robin
+  // that walks the ring, a warp running ahead of its siblings could mistake phase r-2 for phase r).
+  static constexpr int kWWarps = 4;
+  static constexpr int kXWarps = 4;
+  static constexpr int kStages = 8;
+  // Likewise one thread needs about 270 ns to issue the two tcgen05.cp, four tcgen05.mma and the commit of a stage, so
+  // kMmaWarps threads issue the stages in turn, each into an accumulator of its own (added in the epilogue).
+  static constexpr int kMmaWarps = MT == 4 ? 2 : 4;
+  static constexpr int kSfCol = 2 * kMmaWarps * NB;             // TMEM: two buffers x kMmaWarps accumulators of NB columns, then an 8-column scale slot per stage
+  static constexpr int kTmemCols = MT == 1 ? 256 : 512;
+  // warp 0 (weights) + warp 1 (MMA) + 4 epilogue + scale/activation warps + extra weight warps + extra MMA warps
+  static constexpr int kThreads = 32 * (6 + kXWarps + (kWWarps - 1) + (kMmaWarps - 1));
+  static_assert(kStages % kWWarps == 0 && kStages % kXWarps == 0 && kStages % kMmaWarps == 0, "a stage must belong to one warp of each role");
   static constexpr int kSmem = kStages * kStageBytes + 1024 + 256;
 };
 
@@ -247,7 +257,7 @@ __global__ void __launch_bounds__(128 * MT) x_quant_mx_kernel(const __nv_bfloat1
 __device__ __forceinline__ uint32_t pick_word(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 
 template <int MT>
-__global__ void __launch_bounds__(Cfg<MT>::kThreads, Cfg<MT>::kCtasPerSm) gemv_fp4_mx_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
+__global__ void __launch_bounds__(Cfg<MT>::kThreads, 1) gemv_fp4_mx_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
   using C = Cfg<MT>;
   constexpr int kStages = C::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -271,7 +281,7 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, Cfg<MT>::kCtasPerSm) gemv_f
     s_abort = 0;
     // a stage is full after two arrivals: the weight copy was issued, and the scale atom is written + the activation copy issued
     for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 2); mbar_init(empty_bar(s), 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), 1); mbar_init(tempty_bar(b), 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), C::kMmaWarps); mbar_init(tempty_bar(b), 4); }
     mbar_init(drain_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -293,33 +303,33 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, Cfg<MT>::kCtasPerSm) gemv_f
   // after its own griddepcontrol.wait, i.e. after this grid has completed
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
-  if (warp == 0) {
-    // ---------------- weight producer: one TMA copy per stage ----------------
+  const int w_idx = warp == 0 ? 0 : warp - (6 + C::kXWarps) + 1;   // weight warps: warp 0 and the warps after the scale/activation warps
+  const int m_idx = warp == 1 ? 0 : warp - (6 + C::kXWarps + C::kWWarps - 1) + 1;   // MMA warps: warp 1 and the last warps
+  if (warp == 0 || (warp >= 6 + C::kXWarps && warp < 6 + C::kXWarps + C::kWWarps - 1)) {
+    // ---------------- weight producers: one TMA copy per stage, stages dealt round-robin to the weight warps ----------------
     if (lane == 0) {
-      uint32_t it = (uint32_t)min(kStages, u1 - u0);           // the first round was issued in the prologue
       bool ok = true;
-      for (int u = u0 + (int)it; u < u1; ++u, ++it) {
-        const int tile = u / S, j = u - tile * S;
+      const int total = u1 - u0;
+      // the first round (kStages copies) was issued in the prologue by thread 0
+      for (int it = kStages + ((w_idx - kStages % C::kWWarps + C::kWWarps) % C::kWWarps); it < total; it += C::kWWarps) {
+        const int u = u0 + it, tile = u / S, j = u - tile * S;
         const int s = it % kStages;
-        const uint32_t ph = (it / kStages) & 1;
+        const uint32_t ph = (uint32_t)(it / kStages) & 1;
         if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, 1)) { ok = false; break; }
         // the mbarrier counts the packed bytes read from global memory (64 per row), not the padded bytes written
         mbar_expect_tx(full_bar(s), C::kBytesW / 2);
         tma_load_2d(base + s * C::kStageBytes, &map_w, full_bar(s), j * BK, tile * TILE_ROWS);
       }
-      if (!ok) {
-        // give every copy already issued a bounded chance to land before shared memory is released
-        const uint32_t issued = it < (uint32_t)kStages ? it : (uint32_t)kStages;
-        for (uint32_t q = 0; q < issued; ++q) {
-          const uint32_t w = it - 1 - q;
-          const uint64_t t0 = globaltimer_ns();
-          while (!mbar_try_wait(full_bar(w % kStages), (w / kStages) & 1))
-            if (globaltimer_ns() - t0 > 100000000ull) break;
-        }
+      if (!ok || *abort_flag) {
+        // a wait expired somewhere: give the copies in flight time to land before shared memory is released
+        const uint64_t t0 = globaltimer_ns();
+        while (globaltimer_ns() - t0 < 2000000ull) {}
       }
     }
-  } else if (warp == 6) {
-    // ---------------- scale + activation producer (whole warp: every lane owns one 16-byte line of the weight scale atom) ----------------
+  } else if (warp >= 6 && warp < 6 + C::kXWarps) {
+    // ---------------- scale + activation producers (whole warps: every lane owns one 16-byte line of the weight scale atom),
+    // stages dealt round-robin to the kXWarps warps ----------------
+    const int x_idx = warp - 6;
     const int64_t kblocks = p.K >> 5;
     // scale words are prefetched kAhead chunks (of 4 stages) ahead of use: they come from HBM like the codes
     constexpr int kAhead = 3;
@@ -340,11 +350,11 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, Cfg<MT>::kCtasPerSm) gemv_f
     // the activation codes come from the pre-pass kernel, which this grid may overlap (programmatic dependent
     // launch): nothing of it is read before this point
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    uint32_t it = 0;
-    for (int u = u0; u < u1; ++u, ++it) {
+    for (int it = x_idx; it < u1 - u0; it += C::kXWarps) {
+      const int u = u0 + it;
       const int j = u % S;
       const int key = u >> 2;
-      if (key != key_cur) {                                    // the keys of a CTA are consecutive
+      if (key != key_cur) {                                    // consecutive units of a warp are kXWarps <= 4 apart: the key grows by at most one
 #pragma unroll
         for (int a = 0; a < kAhead; ++a) {
 #pragma unroll
@@ -354,7 +364,7 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, Cfg<MT>::kCtasPerSm) gemv_f
         if ((key + kAhead) * 4 < u1) load_scales(key + kAhead, q[kAhead]);
       }
       const int s = it % kStages;
-      const uint32_t ph = (it / kStages) & 1;
+      const uint32_t ph = (uint32_t)(it / kStages) & 1;
       if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, 5)) break;
       uint4 line;
       line.x = pick_word(q[0][0], u & 3); line.y = pick_word(q[0][1], u & 3);
@@ -367,11 +377,12 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, Cfg<MT>::kCtasPerSm) gemv_f
         bulk_load(base + s * C::kStageBytes + C::kBytesW, p.xq + (int64_t)j * C::kBytesX, C::kBytesX, full_bar(s));
       }
     }
-    // on a failed wait the copies of this warp are covered by the weight producer's drain (same barriers)
-  } else if (warp == 1) {
-    // ---------------- MMA issuer ----------------
+    // on a failed wait the weight warps hold the CTA until the copies in flight have landed
+  } else if (warp == 1 || warp >= 6 + C::kXWarps + C::kWWarps - 1) {
+    // ---------------- MMA issuers: thread m_idx takes the stages with ring position % kMmaWarps == m_idx ----------------
     if (lane == 0) {
-      uint32_t it = 0, seg_it = 0;
+      int it0 = 0;                                             // ring position of the segment's first stage
+      uint32_t seg_it = 0;
       bool ok = true;
       for (int u = u0; u < u1 && ok; ++seg_it) {
         const int tile = u / S, j0 = u - tile * S;
@@ -379,10 +390,11 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, Cfg<MT>::kCtasPerSm) gemv_f
         const uint32_t buf = seg_it & 1, aph = (seg_it >> 1) & 1;
         if (!mbar_wait(tempty_bar(buf), aph ^ 1, abort_flag, 2)) { ok = false; break; }
         tc_fence_after();
-        const uint32_t tmem_d = tmem_base + buf * C::NB;
-        for (int jj = 0; jj < n; ++jj, ++it) {
+        const uint32_t tmem_d = tmem_base + (buf * C::kMmaWarps + m_idx) * C::NB;
+        bool first = true;
+        for (int it = it0 + ((m_idx - it0 % C::kMmaWarps + C::kMmaWarps) % C::kMmaWarps); it < it0 + n; it += C::kMmaWarps) {
           const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
+          const uint32_t ph = (uint32_t)(it / kStages) & 1;
           if (!mbar_wait(full_bar(s), ph, abort_flag, 3)) { ok = false; break; }
           tc_fence_after();
           const uint32_t sw = base + s * C::kStageBytes, sx = sw + C::kBytesW;
@@ -394,14 +406,16 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, Cfg<MT>::kCtasPerSm) gemv_f
           for (int k = 0; k < 4; ++k) {
             // K advance inside the swizzle atom: +32 bytes; scale byte k of the atom's columns
             umma_mx(tmem_d, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), p.idesc | ((uint32_t)k << 29) | ((uint32_t)k << 4),
-                    tsfa, tsfb, (uint32_t)((jj | k) != 0));
+                    tsfa, tsfb, (uint32_t)(!first || k != 0));
           }
+          first = false;
           tc_commit(empty_bar(s));
         }
-        if (ok) tc_commit(tfull_bar(buf));
+        if (ok) tc_commit(tfull_bar(buf));                     // arrives once this thread's MMAs of the segment are complete (at once if it had none)
         u += n;
+        it0 += n;
       }
-      if (!ok) {
+      if (!ok && m_idx == 0) {
         tc_commit(drain_bar);
         const uint64_t t0 = globaltimer_ns();
         while (!mbar_try_wait(drain_bar, 0))
@@ -412,6 +426,7 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, Cfg<MT>::kCtasPerSm) gemv_f
     // ---------------- epilogue (warps 2..5) ----------------
     const int q = warp & 3;                                   // TMEM lane quarter this warp may access
     const int row_local = q * 32 + lane;
+    int it0 = 0;
     uint32_t seg_it = 0;
     bool ok = true;
     for (int u = u0; u < u1 && ok; ++seg_it) {
@@ -423,20 +438,26 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, Cfg<MT>::kCtasPerSm) gemv_f
       tc_fence_after();
       float v[C::MPAD];
 #pragma unroll
-      for (int c = 0; c < C::NB; c += 16) {
-        uint32_t r[16];
-        tmem_ld16(tmem_base + buf * C::NB + c + ((uint32_t)(q * 32) << 16), r);
-        tmem_ld_wait();
+      for (int t = 0; t < C::MPAD; ++t) v[t] = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int col = c + i;                              // compile-time after unrolling
-          if (col < C::MPAD) v[col] = __uint_as_float(r[i]);
-          else v[col - C::MPAD] += __uint_as_float(r[i]);     // residual term of the same token
+      for (int g = 0; g < C::kMmaWarps; ++g) {
+        // accumulator g holds something only if MMA thread g had a stage in this segment
+        const bool used = n >= C::kMmaWarps || ((g - it0 % C::kMmaWarps + C::kMmaWarps) % C::kMmaWarps) < n;
+        if (used) {                                           // uniform over the warp
+#pragma unroll
+          for (int c = 0; c < C::NB; c += 16) {
+            uint32_t r[16];
+            tmem_ld16(tmem_base + (buf * C::kMmaWarps + g) * C::NB + c + ((uint32_t)(q * 32) << 16), r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) v[(c + i) % C::MPAD] += __uint_as_float(r[i]);   // first term and residual term of a token
+          }
         }
       }
+      it0 += n;
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(buf));            // accumulator is in registers now
+      if (lane == 0) mbar_arrive(tempty_bar(buf));            // accumulators are in registers now
       const int64_t row = (int64_t)tile * TILE_ROWS + row_local;
       auto store_out = [&](int t, float val) {
         if (row < p.N) {
@@ -533,10 +554,20 @@ int32_t launch(b2q_handle h, const uint8_t* codes, const uint8_t* scales, const 
   const int S = (int)(K / BK);
   const int64_t tiles = ceil_div64(N, TILE_ROWS);
   const int64_t units = tiles * S;
-  const int64_t slots = (int64_t)C::kCtasPerSm * h->sm_count;
-  int grid = (int)(units < slots ? units : slots);
-  const int per = (int)ceil_div64(units, grid);
-  grid = (int)ceil_div64(units, per);
+  const int64_t slots = h->sm_count;                            // one CTA per SM
+  int grid, per;
+  if (tiles * 10 >= slots * 7) {
+    // enough tiles to occupy most SMs: every CTA owns whole tiles, no partial sums to exchange
+    per = S * (int)ceil_div64(tiles, slots);
+    grid = (int)ceil_div64(units, per);
+  } else {
+    grid = (int)(units < slots ? units : slots);
+    per = (int)ceil_div64(units, grid);
+    grid = (int)ceil_div64(units, per);
+  }
+  if (const char* e = getenv("B2Q_MX_STREAMK")) {               // experiment switch: 1 forces the even split over all SMs
+    if (e[0] == '1') { grid = (int)(units < slots ? units : slots); per = (int)ceil_div64(units, grid); grid = (int)ceil_div64(units, per); }
+  }
   p.max_slots = (S + per - 1) / per + 1;
   const size_t xq_bytes = align256((size_t)S * C::kBytesX);
   const size_t part_bytes = (size_t)tiles * p.max_slots * C::MPAD * TILE_ROWS * sizeof(float);

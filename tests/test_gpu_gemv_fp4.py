@@ -44,6 +44,40 @@ def test_ragged_shapes(cuda, oracle, tokens, N, K):
         assert _case(cuda, oracle, tokens, N, K, scale_mode, 5, torch.float32) <= 2e-3
 
 
+@pytest.mark.parametrize("tokens,N,K", [(4, 38400, 1024), (1, 28672, 4096), (32, 14336, 4096), (8, 4096, 14336), (5, 13400, 2560)])
+def test_tensor_core_block_scaled_path(cuda, oracle, tokens, N, K, monkeypatch):
+    """The tcgen05 kind::mxf8f6f4 kernel, forced on: several whole tiles per CTA (38400 rows = 300 tiles), one tile
+    per CTA, the even split with partial sums (4096 rows), a ragged last tile (13400 rows)."""
+    monkeypatch.setenv("B2Q_GEMV_MX", "1")
+    assert _case(cuda, oracle, tokens, N, K, 1, 11 * tokens + N, torch.float32) <= 2e-3
+    assert _case(cuda, oracle, tokens, N, K, 1, 13 * tokens + N, torch.bfloat16) <= TOL
+
+
+def test_back_to_back_calls_with_different_operands(cuda, oracle, monkeypatch):
+    """Consecutive launches overlap their tails (programmatic dependent launch): every call must still see its own
+    activations, scales and partial sums."""
+    from oxicuda_b200.blas import gemv_fp4_wo
+    from oxicuda_b200._lib import default_handle
+    monkeypatch.setenv("B2Q_GEMV_MX", "1")
+    rng = np.random.default_rng(7)
+    N, K = 4096, 4096
+    sets = []
+    for tokens in (1, 8, 32):
+        w = (rng.standard_normal(N * K) * 0.02).astype(np.float32)
+        codes, scales = oracle.fp4_block_quantize(w, 32, 0, 1)
+        x = torch.from_numpy(rng.standard_normal((tokens, K)).astype(np.float32)).to(torch.bfloat16)
+        xb = x.view(torch.int16).numpy().view(np.uint16)
+        ref = np.asarray(oracle.gemv_fp4(codes, scales, xb, tokens, N, K, 32, "f32")).reshape(tokens, N)
+        sets.append((_t(codes, cuda), _t(scales, cuda), x.to(cuda), ref))
+    outs = []
+    for rep in range(30):
+        c, s, x, _ = sets[rep % 3]
+        outs.append((rep % 3, gemv_fp4_wo(c, s, x, N, K, out_dtype=torch.float32)))
+    default_handle().check()
+    for i, o in outs:
+        assert rel_err(o.cpu().numpy(), sets[i][3]) <= 2e-3
+
+
 def test_codes_map_exactly(cuda, oracle):
     """x = one-hot rows picks single weights: every E2M1 code times a power-of-two scale is exact."""
     from oxicuda_b200.blas import gemv_fp4_wo
