@@ -217,7 +217,12 @@ int32_t b2q_ep_token_gather_bf16(b2q_handle h, const void* expert_out, const int
  *      followed by a dot product.  The reference's M (quantized rows) is `N` here, its N (columns of dense B) is
  *      `tokens`; activations are taken token-major [tokens x K] bf16 instead of [K x tokens] f32.
  * codes [N x K/2] (E2M1, low nibble first), scales [N x K/32] f32 or E8M0 bytes, x [tokens x K] bf16,
- * out [tokens x N] bf16 or f32.  tokens <= 32, K % 128 == 0, block == 32. */
+ * out [tokens x N] bf16 or f32.  tokens <= 32, K % 128 == 0, block == 32.
+ * With E8M0 scales, K % 512 == 0, codes 32-byte aligned and scales 16-byte aligned, matrices from 16 MiB of codes run on
+ * the block-scaled tensor-core kernel (weights and scales as stored; each bf16 activation enters as the sum of two E4M3
+ * terms under a power-of-two scale per 32 values, absolute error below 2^-18 of the largest of the 32); it uses the
+ * handle's workspace, and consecutive calls on the stream overlap (programmatic dependent launch).  Everything else
+ * runs kernels that use the activations exactly. */
 int32_t b2q_gemv_fp4_wo(b2q_handle h, const uint8_t* codes, const void* scales, int scale_format, int block,
                         const void* x_bf16, int64_t tokens, int64_t N, int64_t K, void* out, int out_type);
 

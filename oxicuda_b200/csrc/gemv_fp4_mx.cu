@@ -11,20 +11,24 @@
 // bits, c1 keeps 4 and the remainder fits in 4), below that the absolute error is < 2^-18 of the block maximum.
 // The two codes are two accumulator columns of the same MMA (N = 2 * padded tokens) added in the epilogue.
 //
-// Main kernel, persistent, two CTAs per SM (one CTA alone leaves the memory pipe half empty), 7 warps:
-//   warp 0      weight producer: per 128-wide K stage one TMA copy of 128 weight rows (4-bit data expanded by
-//               the TMA unit to the 16-byte-aligned layout the MMA reads, 128-byte swizzle);
-//   warp 6      scale + activation producer: the weight scales of the stage (read with 16-byte loads three
-//               512-wide chunks ahead, written in the 32 x 16-byte scale-factor atom layout) and one bulk copy
-//               of the activation codes + their scale atom;
-//   warp 1      one thread: tcgen05.cp of both scale atoms into TMEM, four tcgen05.mma (K = 32 = one scale
-//               block each), tcgen05.commit to release the stage / publish the accumulator;
-//   warps 2..5  epilogue: tcgen05.ld of the 128 x N accumulator, add the two activation terms, store.
-// The main grid is launched as a programmatic dependent of the pre-pass: its prologue, weight copies and scale
-// loads overlap the pre-pass, only the activation copies wait for it (griddepcontrol.wait).
-// Work units are (128-row tile, K stage) pairs split evenly over the CTAs (stream-K), so every SM streams the
-// same number of bytes whatever N is.  A CTA that owns only part of a tile's K range writes its partial sums
-// to a workspace; the last CTA to arrive at the tile (a counter per tile) adds the partials in CTA order and
+// Main kernel: one persistent CTA per SM, a ring of 8 stages (128 weight rows x 128 K each).  A single thread can
+// issue only one asynchronous copy per ~250 ns and one stage of tcgen05 work per ~270 ns (measured), far below an
+// SM's share of the HBM stream, so every role is spread over several warps, and stage s always belongs to warp
+// s % 4 of each role (fixed owners keep the parity waits on the stage barriers one phase apart at most):
+//   weight warps (4)             per stage one TMA copy of 128 weight rows (4-bit data expanded by the TMA unit to the
+//                                16-byte-aligned layout the MMA reads, 128-byte swizzle);
+//   scale/activation warps (4)   the weight scales of the stage (16-byte loads, a register ring four stages ahead,
+//                                written in the 32 x 16-byte scale-factor atom layout) and one bulk copy of the
+//                                activation codes + their scale atom;
+//   MMA threads (4; 2 above 16 tokens)  tcgen05.cp of both scale atoms into TMEM, four tcgen05.mma (K = 32 = one
+//                                scale block each) into the thread's own accumulator, tcgen05.commit to release the stage;
+//   epilogue warps (4)           tcgen05.ld of the accumulators, add them and the two activation terms, store.
+// Pre-pass and main grid are chained by programmatic dependent launch: a grid's prologue, weight copies and scale
+// loads overlap the previous grid's tail, only the activation copies wait for the pre-pass (griddepcontrol.wait),
+// and the pre-pass waits for the previous main grid before it touches the shared code buffer.
+// Work units are (128-row tile, K stage) pairs.  With at least 0.7 tiles per SM every CTA owns whole tiles; otherwise
+// the units are split evenly over the SMs (stream-K): a CTA that owns only part of a tile's K range writes its partial
+// sums to a workspace and the last CTA to arrive at the tile (a counter per tile) adds the partials in CTA order and
 // stores, so results do not depend on arrival order.  Every mbarrier wait is bounded.
 #include "common.cuh"
 #include <cuda.h>
@@ -279,8 +283,8 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, 1) gemv_fp4_mx_kernel(const
 
   if (threadIdx.x == 0) {
     s_abort = 0;
-    // a stage is full after two arrivals: the weight copy was issued, and the scale atom is written + the activation copy issued
-    for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 2); mbar_init(empty_bar(s), 1); }
+    // a stage is full after three arrivals: weight copy issued, activation copy issued, weight scale atom written
+    for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 3); mbar_init(empty_bar(s), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), C::kMmaWarps); mbar_init(tempty_bar(b), 4); }
     mbar_init(drain_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -331,13 +335,16 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, 1) gemv_fp4_mx_kernel(const
     // stages dealt round-robin to the kXWarps warps ----------------
     const int x_idx = warp - 6;
     const int64_t kblocks = p.K >> 5;
-    // scale words are prefetched kAhead chunks (of 4 stages) ahead of use: they come from HBM like the codes
-    constexpr int kAhead = 3;
-    uint4 q[kAhead + 1][4];
-    int key_cur = u0 >> 2;
-    // scale bytes of the 512-wide chunk `key` (4 stages) for rows lane, lane+32, lane+64, lane+96 of its tile
-    auto load_scales = [&](int key, uint4 (&dst)[4]) {
-      const int tile = (key * 4) / S, chunk = ((key * 4) % S) >> 2;
+    // A warp takes every fourth stage, so every stage it takes lies in a new 512-wide chunk of scale bytes.  The
+    // chunks are read kRing stages of this warp ahead into a register ring with compile-time slot indices (a ring
+    // that shifts its registers would wait for the newest load at every shift).
+    static_assert(C::kXWarps == 4, "one chunk of scale bytes per stage of a warp");
+    constexpr int kRing = 4;
+    uint4 q[kRing][4];
+    const int total = u1 - u0;
+    // scale bytes of the chunk that holds unit u (4 stages), for rows lane, lane+32, lane+64, lane+96 of its tile
+    auto load_scales = [&](int u, uint4 (&dst)[4]) {
+      const int tile = u / S, chunk = (u - tile * S) >> 2;
 #pragma unroll
       for (int r1 = 0; r1 < 4; ++r1) {
         const int64_t row = min((int64_t)tile * TILE_ROWS + lane + 32 * r1, p.N - 1);
@@ -345,36 +352,34 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, 1) gemv_fp4_mx_kernel(const
       }
     };
 #pragma unroll
-    for (int a = 0; a <= kAhead; ++a)
-      if ((key_cur + a) * 4 < u1) load_scales(key_cur + a, q[a]);
+    for (int r = 0; r < kRing; ++r)
+      if (x_idx + 4 * r < total) load_scales(u0 + x_idx + 4 * r, q[r]);
     // the activation codes come from the pre-pass kernel, which this grid may overlap (programmatic dependent
     // launch): nothing of it is read before this point
     asm volatile("griddepcontrol.wait;" ::: "memory");
-    for (int it = x_idx; it < u1 - u0; it += C::kXWarps) {
-      const int u = u0 + it;
-      const int j = u % S;
-      const int key = u >> 2;
-      if (key != key_cur) {                                    // consecutive units of a warp are kXWarps <= 4 apart: the key grows by at most one
+    bool ok = true;
+    for (int it0 = x_idx; it0 < total && ok; it0 += 4 * kRing) {
 #pragma unroll
-        for (int a = 0; a < kAhead; ++a) {
-#pragma unroll
-          for (int r1 = 0; r1 < 4; ++r1) q[a][r1] = q[a + 1][r1];
+      for (int r = 0; r < kRing; ++r) {
+        const int it = it0 + 4 * r;
+        if (it >= total) break;
+        const int u = u0 + it;
+        const int j = u % S;
+        const int s = it % kStages;
+        const uint32_t ph = (uint32_t)(it / kStages) & 1;
+        if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, 5)) { ok = false; break; }
+        if (lane == 0) {                                       // the copy is in flight while the warp writes the scale atom
+          mbar_expect_tx(full_bar(s), C::kBytesX);
+          bulk_load(base + s * C::kStageBytes + C::kBytesW, p.xq + (int64_t)j * C::kBytesX, C::kBytesX, full_bar(s));
         }
-        key_cur = key;
-        if ((key + kAhead) * 4 < u1) load_scales(key + kAhead, q[kAhead]);
-      }
-      const int s = it % kStages;
-      const uint32_t ph = (uint32_t)(it / kStages) & 1;
-      if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, 5)) break;
-      uint4 line;
-      line.x = pick_word(q[0][0], u & 3); line.y = pick_word(q[0][1], u & 3);
-      line.z = pick_word(q[0][2], u & 3); line.w = pick_word(q[0][3], u & 3);
-      *reinterpret_cast<uint4*>(base_ptr + s * C::kStageBytes + C::kBytesW + C::kBytesX + lane * 16) = line;
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the scale atom is read by tcgen05.cp
-      __syncwarp();
-      if (lane == 0) {
-        mbar_expect_tx(full_bar(s), C::kBytesX);
-        bulk_load(base + s * C::kStageBytes + C::kBytesW, p.xq + (int64_t)j * C::kBytesX, C::kBytesX, full_bar(s));
+        uint4 line;
+        line.x = pick_word(q[r][0], u & 3); line.y = pick_word(q[r][1], u & 3);
+        line.z = pick_word(q[r][2], u & 3); line.w = pick_word(q[r][3], u & 3);
+        *reinterpret_cast<uint4*>(base_ptr + s * C::kStageBytes + C::kBytesW + C::kBytesX + lane * 16) = line;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the scale atom is read by tcgen05.cp
+        __syncwarp();
+        if (lane == 0) mbar_arrive(full_bar(s));
+        if (it + 4 * kRing < total) load_scales(u + 4 * kRing, q[r]);  // this slot's next use
       }
     }
     // on a failed wait the weight warps hold the CTA until the copies in flight have landed
@@ -591,13 +596,12 @@ int32_t launch(b2q_handle h, const uint8_t* codes, const uint8_t* scales, const 
   if (const char* e = getenv("B2Q_MX_DEBUG")) p.debug = atoi(e);   // 1: report which wait expired as status 400 + role
   p.status = h->d_status;
 
-  const char* skip_pre = getenv("B2Q_MX_SKIP_PRE");   // timing experiment: reuse the activation codes of the previous call
   const char* pdl = getenv("B2Q_MX_PDL");                      // 0: plain stream-ordered launches
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   const int num_attrs = (pdl && pdl[0] == '0') ? 0 : 1;
-  if (!(skip_pre && skip_pre[0] == '1')) {
+  {
     cudaLaunchConfig_t pre = {};
     pre.gridDim = dim3((unsigned)S);
     pre.blockDim = dim3(128 * MT);
