@@ -69,6 +69,7 @@ template <int MT> struct Cfg {
 struct Params {
   const uint8_t* scales;      // [N][K/32] E8M0
   const uint8_t* xq;          // per K stage: NB x 128 swizzled code bytes, then the 512-byte scale atom (pre-pass output)
+  const __nv_bfloat16* x;     // [tokens][K] activations (read by the main kernel when it quantizes them itself)
   float* partials;            // [tile][slot][MPAD][128]
   int32_t* counters;          // [tile], zero on entry and on exit
   void* out;
@@ -258,9 +259,9 @@ __global__ void __launch_bounds__(128 * MT) x_quant_mx_kernel(const __nv_bfloat1
 // ---------------------------------------------------------------------------
 // Main kernel
 // ---------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t pick_word(const uint4& v, int i) { return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w; }
 
-template <int MT>
+// INL (up to 4 tokens): the scale/activation warps quantize the activations of each stage themselves, no pre-pass.
+template <int MT, bool INL>
 __global__ void __launch_bounds__(Cfg<MT>::kThreads, 1) gemv_fp4_mx_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
   using C = Cfg<MT>;
   constexpr int kStages = C::kStages;
@@ -283,8 +284,8 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, 1) gemv_fp4_mx_kernel(const
 
   if (threadIdx.x == 0) {
     s_abort = 0;
-    // a stage is full after three arrivals: weight copy issued, activation copy issued, weight scale atom written
-    for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 3); mbar_init(empty_bar(s), 1); }
+    // a stage is full after: weight copy issued, (activation copy issued,) weight scale atom (and activation codes) written
+    for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), INL ? 2 : 3); mbar_init(empty_bar(s), 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(tfull_bar(b), C::kMmaWarps); mbar_init(tempty_bar(b), 4); }
     mbar_init(drain_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -340,23 +341,47 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, 1) gemv_fp4_mx_kernel(const
     // that shifts its registers would wait for the newest load at every shift).
     static_assert(C::kXWarps == 4, "one chunk of scale bytes per stage of a warp");
     constexpr int kRing = 4;
-    uint4 q[kRing][4];
+    uint32_t q[kRing][4];                                      // the stage's scale word (4 blocks) of rows lane, lane+32, lane+64, lane+96
     const int total = u1 - u0;
-    // scale bytes of the chunk that holds unit u (4 stages), for rows lane, lane+32, lane+64, lane+96 of its tile
-    auto load_scales = [&](int u, uint4 (&dst)[4]) {
-      const int tile = u / S, chunk = (u - tile * S) >> 2;
+    auto load_scales = [&](int u, uint32_t (&dst)[4]) {
+      const int tile = u / S, j = u - tile * S;
 #pragma unroll
       for (int r1 = 0; r1 < 4; ++r1) {
         const int64_t row = min((int64_t)tile * TILE_ROWS + lane + 32 * r1, p.N - 1);
-        dst[r1] = __ldg(reinterpret_cast<const uint4*>(p.scales + row * kblocks + chunk * 16));
+        dst[r1] = __ldg(reinterpret_cast<const uint32_t*>(p.scales + row * kblocks + j * 4));
       }
     };
 #pragma unroll
     for (int r = 0; r < kRing; ++r)
       if (x_idx + 4 * r < total) load_scales(u0 + x_idx + 4 * r, q[r]);
-    // the activation codes come from the pre-pass kernel, which this grid may overlap (programmatic dependent
-    // launch): nothing of it is read before this point
+    // inline quantization: lane -> 16-byte piece i of the stage and token tb (+2 for the second piece)
+    constexpr int kPieces = 2;                                 // tokens <= 4
+    const int pi = lane & 15, tb = lane >> 4;
+    uint4 xr[kRing][kPieces];
+    auto load_x = [&](int u, uint4 (&dst)[kPieces]) {
+      const int j = u % S;
+#pragma unroll
+      for (int r = 0; r < kPieces; ++r) {
+        const int t = tb + 2 * r;
+        dst[r] = t < p.tokens ? __ldg(reinterpret_cast<const uint4*>(p.x + (int64_t)t * p.K + (int64_t)j * BK + pi * 8)) : make_uint4(0, 0, 0, 0);
+      }
+    };
+    if constexpr (INL) {
+      // rows of the activation tile that belong to no token, and the unused part of its scale atom, stay zero: clear
+      // this warp's stages once (a stage keeps its owner)
+      for (int s = x_idx; s < kStages; s += C::kXWarps) {
+        uint4* xz = reinterpret_cast<uint4*>(base_ptr + s * C::kStageBytes + C::kBytesW);
+        for (int k = lane; k < C::kBytesX / 16; k += 32) xz[k] = make_uint4(0, 0, 0, 0);
+      }
+    }
+    // the activations come from the previous kernel of the stream (the pre-pass, or whatever produced x), which this
+    // grid may overlap (programmatic dependent launch): nothing of them is read before this point
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    if constexpr (INL) {
+#pragma unroll
+      for (int r = 0; r < kRing; ++r)
+        if (x_idx + 4 * r < total) load_x(u0 + x_idx + 4 * r, xr[r]);
+    }
     bool ok = true;
     for (int it0 = x_idx; it0 < total && ok; it0 += 4 * kRing) {
 #pragma unroll
@@ -368,18 +393,34 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, 1) gemv_fp4_mx_kernel(const
         const int s = it % kStages;
         const uint32_t ph = (uint32_t)(it / kStages) & 1;
         if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, 5)) { ok = false; break; }
-        if (lane == 0) {                                       // the copy is in flight while the warp writes the scale atom
+        uint8_t* xs = base_ptr + s * C::kStageBytes + C::kBytesW;
+        if constexpr (INL) {
+#pragma unroll
+          for (int k = 0; k < kPieces; ++k) {
+            uint32_t c1[2], c2[2];
+            const int e = quant_piece(xr[r][k], c1, c2);
+            const int n1 = tb + 2 * k, n2 = C::MPAD + n1;
+            if (n1 < p.tokens) {
+              *reinterpret_cast<uint2*>(xs + n1 * 128 + (((pi >> 1) ^ (n1 & 7)) << 4) + (pi & 1) * 8) = make_uint2(c1[0], c1[1]);
+              *reinterpret_cast<uint2*>(xs + n2 * 128 + (((pi >> 1) ^ (n2 & 7)) << 4) + (pi & 1) * 8) = make_uint2(c2[0], c2[1]);
+              if ((pi & 3) == 0) {
+                xs[C::NB * 128 + n1 * 16 + (pi >> 2)] = (uint8_t)(e + 127);
+                xs[C::NB * 128 + n2 * 16 + (pi >> 2)] = (uint8_t)(e + 127);
+              }
+            }
+          }
+        } else if (lane == 0) {                                // the copy is in flight while the warp writes the scale atom
           mbar_expect_tx(full_bar(s), C::kBytesX);
           bulk_load(base + s * C::kStageBytes + C::kBytesW, p.xq + (int64_t)j * C::kBytesX, C::kBytesX, full_bar(s));
         }
-        uint4 line;
-        line.x = pick_word(q[r][0], u & 3); line.y = pick_word(q[r][1], u & 3);
-        line.z = pick_word(q[r][2], u & 3); line.w = pick_word(q[r][3], u & 3);
-        *reinterpret_cast<uint4*>(base_ptr + s * C::kStageBytes + C::kBytesW + C::kBytesX + lane * 16) = line;
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // the scale atom is read by tcgen05.cp
+        *reinterpret_cast<uint4*>(xs + C::kBytesX + lane * 16) = make_uint4(q[r][0], q[r][1], q[r][2], q[r][3]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // read by tcgen05.cp / tcgen05.mma
         __syncwarp();
         if (lane == 0) mbar_arrive(full_bar(s));
-        if (it + 4 * kRing < total) load_scales(u + 4 * kRing, q[r]);  // this slot's next use
+        if (it + 4 * kRing < total) {                          // this slot's next use
+          load_scales(u + 4 * kRing, q[r]);
+          if constexpr (INL) load_x(u + 4 * kRing, xr[r]);
+        }
       }
     }
     // on a failed wait the weight warps hold the CTA until the copies in flight have landed
@@ -479,9 +520,9 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, 1) gemv_fp4_mx_kernel(const
         float* mine = p.partials + ((int64_t)tile * p.max_slots + slot) * (C::MPAD * TILE_ROWS);
 #pragma unroll
         for (int t = 0; t < C::MPAD; ++t) if (t < p.tokens) mine[t * TILE_ROWS + row_local] = v[t];
-        __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (warp == 2 && lane == 0) {
+          __threadfence();                                    // cumulative: the partial sums of all 128 threads (ordered by the barrier) before the arrival
           const int old = atomicAdd(p.counters + tile, 1);
           s_last = (old == nc - 1);
           if (old == nc - 1) p.counters[tile] = 0;            // every contributor has arrived: leave the counter zero
@@ -537,7 +578,7 @@ static EncodeTiledFn get_encode_fn() {
 
 static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
-template <int MT>
+template <int MT, bool INL>
 int32_t launch(b2q_handle h, const uint8_t* codes, const uint8_t* scales, const void* x, int tokens, int64_t N, int64_t K, void* out,
                int out_type) {
   using C = Cfg<MT>;
@@ -581,6 +622,7 @@ int32_t launch(b2q_handle h, const uint8_t* codes, const uint8_t* scales, const 
   if (st != B2Q_OK) return st;
   p.scales = scales;
   p.xq = reinterpret_cast<const uint8_t*>(ws);
+  p.x = reinterpret_cast<const __nv_bfloat16*>(x);
   p.partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + xq_bytes);
   p.counters = h->d_tile_counters;
   p.out = out;
@@ -601,7 +643,7 @@ int32_t launch(b2q_handle h, const uint8_t* codes, const uint8_t* scales, const 
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   const int num_attrs = (pdl && pdl[0] == '0') ? 0 : 1;
-  {
+  if (!INL) {
     cudaLaunchConfig_t pre = {};
     pre.gridDim = dim3((unsigned)S);
     pre.blockDim = dim3(128 * MT);
@@ -612,7 +654,7 @@ int32_t launch(b2q_handle h, const uint8_t* codes, const uint8_t* scales, const 
   }
   static bool attr_set = false;
   if (!attr_set) {
-    B2Q_CUDA(h, cudaFuncSetAttribute(gemv_fp4_mx_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
+    B2Q_CUDA(h, cudaFuncSetAttribute(gemv_fp4_mx_kernel<MT, INL>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
     attr_set = true;
   }
   // programmatic dependent launch: this grid may start while the pre-pass runs; its activation loads wait for it
@@ -623,7 +665,7 @@ int32_t launch(b2q_handle h, const uint8_t* codes, const uint8_t* scales, const 
   cfg.stream = h->stream;
   cfg.attrs = attr;
   cfg.numAttrs = num_attrs;
-  B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, gemv_fp4_mx_kernel<MT>, map_w, p));
+  B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, gemv_fp4_mx_kernel<MT, INL>, map_w, p));
   return B2Q_OK;
 }
 
@@ -639,7 +681,9 @@ int32_t b2q_gemv_fp4_mx_dispatch(b2q_handle h, const uint8_t* codes, const void*
     return B2Q_ERR_UNSUPPORTED;
   if (ceil_div64(N, mx::TILE_ROWS) > (int64_t)kTileCounters || ceil_div64(N, mx::TILE_ROWS) * (K / mx::BK) > 0x7FFFFFFF)
     return B2Q_ERR_UNSUPPORTED;
-  if (tokens <= 8) return mx::launch<1>(h, codes, (const uint8_t*)scales, x, tokens, N, K, out, out_type);
-  if (tokens <= 16) return mx::launch<2>(h, codes, (const uint8_t*)scales, x, tokens, N, K, out, out_type);
-  return mx::launch<4>(h, codes, (const uint8_t*)scales, x, tokens, N, K, out, out_type);
+  const char* inl = getenv("B2Q_MX_INLINE");                   // experiment switch: 0 keeps the pre-pass for every token count
+  if (tokens <= 4 && !(inl && inl[0] == '0')) return mx::launch<1, true>(h, codes, (const uint8_t*)scales, x, tokens, N, K, out, out_type);
+  if (tokens <= 8) return mx::launch<1, false>(h, codes, (const uint8_t*)scales, x, tokens, N, K, out, out_type);
+  if (tokens <= 16) return mx::launch<2, false>(h, codes, (const uint8_t*)scales, x, tokens, N, K, out, out_type);
+  return mx::launch<4, false>(h, codes, (const uint8_t*)scales, x, tokens, N, K, out, out_type);
 }
