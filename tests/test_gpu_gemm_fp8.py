@@ -62,6 +62,32 @@ def test_gemm_fp8_vs_oracle(cuda, oracle, M, N, K):
         assert rel_err(got, ref) <= 1e-3, (M, N, K, mode)   # fp32 out: only the tensor core's accumulation differs
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 256, 128), (7, 1000, 1024), (16, 4096, 4096), (17, 300, 256), (33, 640, 2048),
+                                   (64, 2304, 1024), (100, 520, 384), (128, 1024, 512), (4, 19000, 256), (2, 40000, 128)])
+def test_weight_stationary_tcgen05_kernel(cuda, oracle, M, N, K, monkeypatch):
+    """The few-token kernel (weights as the M = 128 operand), forced on: one tile per CTA, several tiles per CTA
+    (19000 and 40000 rows), the even split with partial sums (few rows, long K), ragged last tiles, every token padding."""
+    from oxicuda_b200.blas import gemm_fp8
+    monkeypatch.setenv("B2Q_FP8_SKINNY", "1")
+    rng = np.random.default_rng(M * 11 + N * 5 + K)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    ac, sa = _quantize(oracle, a, 1, M * K, 1)
+    wc, sw = _quantize(oracle, w, 1, N * K, 1)
+    ac, wc = ac.reshape(M, K), wc.reshape(N, K)
+    ref = oracle.gemm_fp8(ac, wc, sa, sw, 0, 1, "bf16")
+    got = gemm_fp8(_t(ac, cuda), _t(wc, cuda), _t(sa, cuda), _t(sw, cuda)).float().cpu().numpy()
+    assert rel_err(got, ref) <= TOL
+    sa_r = (rng.random(M).astype(np.float32) + 0.5) * sa[0]
+    sw_r = (rng.random(N).astype(np.float32) + 0.5) * sw[0]
+    ref = oracle.gemm_fp8(ac, wc, sa_r, sw_r, 0, 1, "f32")
+    for _ in range(3):                                # back to back: launches overlap their tails
+        got = gemm_fp8(_t(ac, cuda), _t(wc, cuda), _t(sa_r, cuda), _t(sw_r, cuda), out_dtype=torch.float32)
+    from oxicuda_b200._lib import default_handle
+    default_handle().check()
+    assert rel_err(got.cpu().numpy(), ref) <= 1e-3
+
+
 def test_simt_kernel_reproduces_oracle_order(cuda, oracle):
     """The checker kernel (software decode, k-ascending fp32 FMA) equals the oracle to the last bit."""
     from oxicuda_b200.blas import gemm_fp8
