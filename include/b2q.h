@@ -248,7 +248,8 @@ uint32_t b2q_fp8_compute_split_k(uint32_t m, uint32_t n, uint32_t k);
 /* The static per-shape table this library actually dispatches with (replaces the autotuner role,
  * crates/oxicuda-autotune/src/dispatch.rs:36-196): the CTA tile, pipeline depth and kernel family chosen for
  * (dtype, m, n, k).  kernel_id: 0 simt, 1 tcgen05 128x256, 2 tcgen05 128x128, 3 warp gemv,
- * 4 tcgen05 two-CTA 256x256, 5 fp8 decode gemv. */
+ * 4 tcgen05 two-CTA 256x256, 5 fp8 decode gemv (mma.sync), 6 fp8 few-token weight-stationary tcgen05,
+ * 7 fp4 block-scaled tcgen05 gemv (E8M0 scales; f32 scales take 3). */
 int32_t b2q_select_tile(int dtype, uint32_t m, uint32_t n, uint32_t k, b2q_tile_config* out, int* kernel_id);
 
 #ifdef __cplusplus

@@ -31,6 +31,8 @@ struct b2q_handle_s {
 };
 // Returns a workspace of at least `bytes` (256-byte aligned); grows it when needed (synchronises the stream first).
 int32_t b2q_workspace(b2q_handle h, size_t bytes, void** out);
+// b2q_select_tile with a switch that leaves the few-token tcgen05 kernels out of the table
+int32_t b2q_select_tile_ex(int dtype, uint32_t m, uint32_t n, uint32_t k, b2q_tile_config* out, int* kernel_id, int few_token_kernels);
 static const size_t kScratchWords = 1 << 16;   // 256 KiB of reduction keys / counters
 static const size_t kTileCounters = 1 << 14;
 

@@ -746,16 +746,14 @@ extern "C" int32_t b2q_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w
     if (force && force[0] == 'p') kid = 4;     // "pair": the two-CTA kernel
   }
   {
-    // few tokens against a large weight matrix: the weight-stationary tcgen05 kernel streams W at HBM rate
-    // (B2Q_FP8_SKINNY=0 / 1 forces it off / on)
+    // few tokens against a large weight matrix (kernel 6 of the static table): the weight-stationary tcgen05 kernel
+    // streams W at HBM rate (B2Q_FP8_SKINNY=0 / 1 forces it off / on)
     const char* sk = getenv("B2Q_FP8_SKINNY");
-    // measured crossover against the mma.sync GEMV (M <= 32) and the prefill kernels: 32 MiB of weights up to 64 tokens,
-    // 16 MiB between 9 and 32 tokens
-    const bool pays = (M <= 64 && N * K >= ((int64_t)32 << 20)) || (M > 8 && M <= 32 && N * K >= ((int64_t)16 << 20));
-    if (M <= 128 && (sk ? sk[0] == '1' : pays)) {
+    if (M <= 128 && (sk ? sk[0] == '1' : kid == 6)) {
       int32_t sst = b2q_gemm_fp8_skinny_dispatch(h, a, w, M, N, K, fmt, scale_a, scale_a_kind, scale_w, scale_w_kind, out, out_type);
       if (sst != B2Q_ERR_UNSUPPORTED) return sst;
     }
+    if (kid == 6) b2q_select_tile_ex(0, (uint32_t)M, (uint32_t)N, (uint32_t)K, &t, &kid, 0);   // not taken (alignment, switch)
   }
   if (kid == 5) {   // decode-sized: tensor-core GEMV over the codes
     int32_t gst = b2q_gemv_fp8_dispatch(h, a, w, M, N, K, fmt, scale_a, scale_a_kind, scale_w, scale_w_kind, out, out_type);

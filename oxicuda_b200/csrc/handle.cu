@@ -150,12 +150,36 @@ uint32_t b2q_fp8_compute_split_k(uint32_t m, uint32_t n, uint32_t k) {
 // The static per-shape table: which kernel family and CTA tile each (dtype, shape)
 // dispatches to.  dtype 0 fp8, 1 fp4 (weight-only), 2 int8.
 int32_t b2q_select_tile(int dtype, uint32_t m, uint32_t n, uint32_t k, b2q_tile_config* out, int* kernel_id) {
+  return b2q_select_tile_ex(dtype, m, n, k, out, kernel_id, 1);
+}
+
+}  // extern "C"
+
+// few_token_kernels = 0 leaves the weight-stationary tcgen05 kernels (ids 6 and 7) out: what a call falls back to when
+// its operands do not meet their alignment rules.
+int32_t b2q_select_tile_ex(int dtype, uint32_t m, uint32_t n, uint32_t k, b2q_tile_config* out, int* kernel_id, int few_token_kernels) {
   if (!out || !kernel_id || dtype < 0 || dtype > 2) return B2Q_ERR_INVALID_ARGUMENT;
   if (m == 0 || n == 0 || k == 0) return B2Q_ERR_INVALID_DIMENSION;
-  if (dtype == 1) {  // FP4 weight-only: warp-level mma GEMV, 16 output rows per warp
+  if (dtype == 1) {
+    const uint64_t code_bytes = (uint64_t)n * (k / 2);
+    if (few_token_kernels && m <= 32 && k % 512 == 0 && (code_bytes >= (40ull << 20) || (code_bytes >= (16ull << 20) && (m >= 4 || n >= 13312)))) {
+      // FP4 weight-only with E8M0 scales, large matrix: tcgen05 block-scaled MMA, 128 weight rows x 128 K per stage
+      *out = b2q_tile_config{m <= 8 ? 16u : (m <= 16 ? 32u : 64u), 128, 128, 128, m <= 8 ? 16u : (m <= 16 ? 32u : 64u), 8, 1, 1};
+      *kernel_id = 7;
+      return B2Q_OK;
+    }
+    // FP4 weight-only: warp-level mma GEMV, 16 output rows per warp
     uint32_t rows = n <= 2048 ? 64u : 128u;
     *out = b2q_tile_config{m <= 8 ? 8u : (m <= 16 ? 16u : 32u), rows, 512, 8, 16, 1, 1, 1};
     *kernel_id = 3;
+    return B2Q_OK;
+  }
+  if (few_token_kernels && dtype == 0 && k % 128 == 0 &&
+      ((m <= 64 && (uint64_t)n * k >= (32ull << 20)) || (m > 8 && m <= 32 && (uint64_t)n * k >= (16ull << 20)))) {
+    // FP8, few tokens against a large weight matrix: weight-stationary tcgen05 kernel (weights are the M = 128 operand)
+    const uint32_t nb = m <= 16 ? 16u : (m <= 32 ? 32u : 64u);
+    *out = b2q_tile_config{nb, 128, 128, 128, nb, 8, 1, 1};
+    *kernel_id = 6;
     return B2Q_OK;
   }
   if (dtype == 0 && m <= 32 && k % 64 == 0) {  // FP8 decode: 16 weight rows per CTA, mma.sync.m16n8k32 over the codes
@@ -186,5 +210,3 @@ int32_t b2q_select_tile(int dtype, uint32_t m, uint32_t n, uint32_t k, b2q_tile_
   *kernel_id = wide ? 1 : 2;
   return B2Q_OK;
 }
-
-}  // extern "C"
