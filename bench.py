@@ -426,13 +426,23 @@ def tp_mlp_measurements(dev, rank, world):
     for tokens in (1, 64, 4096):
         x = torch.randn(tokens, hidden, device=dev, generator=g).to(torch.bfloat16)
         sec = _time_calls(lambda i: mlp.forward(x), 20 if tokens < 4096 else 10, 3)
+        timing = "eager launches"
+        if tokens < 4096 and world == 1:
+            # decode-sized steps are launch-bound from Python: replay them from a CUDA graph, as a serving loop does
+            # (single rank only: a capture that one rank refuses must not leave the others waiting in a collective)
+            try:
+                sec_graph = _time_graph(lambda i: mlp.forward(x), 4, 10)
+                if sec_graph < sec:
+                    sec, timing = sec_graph, "CUDA-graph replay"
+            except Exception:
+                pass
         t = torch.tensor([sec], device=dev)
         if world > 1:
             import torch.distributed as dist
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         sec = float(t.item())
         flops = 6.0 * tokens * hidden * ffn
-        res[f"m{tokens}"] = {"us": sec * 1e6, "tflops_all_gpus": flops / sec / 1e12,
+        res[f"m{tokens}"] = {"us": sec * 1e6, "timing": timing, "tflops_all_gpus": flops / sec / 1e12,
                              "weight_gbs_per_gpu": 3 * hidden * F / sec / 1e9}
     return res
 
@@ -470,6 +480,31 @@ def side_measurements(dev, peaks):
                 "us": sec * 1e6, "us_eager_launch": sec_eager * 1e6, "gbs": nbytes / sec / 1e9,
                 "frac_of_measured_hbm": nbytes / sec / 1e9 / peaks["hbm_gbs"]}
         del ws
+    # FP8 W8A8 with few tokens (decode / small batch) on the 70B-shaped FFN projection: HBM-bound, GB/s of algorithmic bytes
+    from oxicuda_b200.blas import gemm_fp8
+    from oxicuda_b200.quant import Fp8Codec
+    codec = Fp8Codec.e4m3("rne")
+    Kd, Nd = 8192, 28672
+    fw = []
+    for c in range(3):                                             # 3 x 235 MB > L2
+        wc, sw = codec.quantize_rows(torch.randn(Nd, Kd, device=dev) * 0.02, Nd, Kd)
+        fw.append((wc.view(Nd, Kd), sw))
+    res["gemm_fp8_few_tokens_k8192_n28672"] = {"timing": res["gemv_fp4_e8m0"]["timing"]}
+    for tokens in (1, 16, 32, 64):
+        ac, sa = codec.quantize_rows(torch.randn(tokens, Kd, device=dev), tokens, Kd)
+        ac = ac.view(tokens, Kd)
+        out = torch.empty(tokens, Nd, dtype=torch.bfloat16, device=dev)
+        call = lambda i: gemm_fp8(ac, fw[i % 3][0], sa, fw[i % 3][1], out=out)
+        try:
+            sec = _time_graph(call, 12)
+        except Exception as exc:
+            res["gemm_fp8_few_tokens_k8192_n28672"][f"m{tokens}"] = {"error": repr(exc)}
+            continue
+        nbytes = Nd * Kd + tokens * Kd + 2 * tokens * Nd
+        res["gemm_fp8_few_tokens_k8192_n28672"][f"m{tokens}"] = {
+            "us": sec * 1e6, "gbs": nbytes / sec / 1e9, "frac_of_measured_hbm": nbytes / sec / 1e9 / peaks["hbm_gbs"],
+            "tflops": 2.0 * tokens * Nd * Kd / sec / 1e12}
+    del fw
     x = torch.randn(8, 1024, device=dev)
     w = torch.randn(1024, 1024, device=dev) * 0.02
     q = LlmInt8Quantizer(LlmInt8Config(1e30, True))

@@ -63,6 +63,13 @@ int32_t b2q_create(b2q_handle* out, int device);
 int32_t b2q_destroy(b2q_handle h);
 /* stream is a cudaStream_t passed as void*; NULL = the legacy default stream */
 int32_t b2q_set_stream(b2q_handle h, void* stream);
+/* The few-token tensor-core kernels (FP4 decode GEMV, FP8 GEMM with up to 64 tokens) are launched as programmatic
+ * dependents of the previous kernel of the stream: they start while it drains and read everything it may have produced
+ * only after it has completed.  With static_weights = 1 (the default: inference weights are written once) the weight
+ * codes and weight scales are excepted: they are fetched before that point, which hides the first memory round trip.
+ * Pass 0 when a call's weight operand may be written by the kernel that precedes it on the stream; the kernels then
+ * read nothing before the previous kernel has completed.  No counterpart in the reference (it has no stream overlap). */
+int32_t b2q_set_static_weights(b2q_handle h, int static_weights);
 int32_t b2q_get_sm(b2q_handle h, int* sm);              /* 100 on a B200 */
 int32_t b2q_get_sm_count(b2q_handle h, int* count);
 const char* b2q_last_error(b2q_handle h);

@@ -92,6 +92,7 @@ SIGNATURES = {
     "b2q_create": (C.c_int32, [C.POINTER(_H), _I]),
     "b2q_destroy": (C.c_int32, [_H]),
     "b2q_set_stream": (C.c_int32, [_H, _P]),
+    "b2q_set_static_weights": (C.c_int32, [_H, C.c_int]),
     "b2q_get_sm": (C.c_int32, [_H, C.POINTER(_I)]),
     "b2q_get_sm_count": (C.c_int32, [_H, C.POINTER(_I)]),
     "b2q_last_error": (C.c_char_p, [_H]),
@@ -188,6 +189,10 @@ class Handle:
 
     def set_stream(self, stream_ptr: int):
         self.call("b2q_set_stream", C.c_void_p(stream_ptr))
+
+    def set_static_weights(self, static_weights: bool):
+        """False: weight operands may be produced by the kernel right before a call (see include/b2q.h)."""
+        self.call("b2q_set_static_weights", 1 if static_weights else 0)
 
     def sm_version(self) -> int:
         v = _I()

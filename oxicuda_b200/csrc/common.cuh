@@ -27,6 +27,7 @@ struct b2q_handle_s {
   int32_t* d_tile_counters;  // kTileCounters x i32, all zero between launches (split-K arrival counts; the last arriver resets its entry)
   void* ws;                  // grow-only workspace for calls that need temporaries (kept so steady-state calls never allocate)
   size_t ws_bytes;
+  int dynamic_weights;       // 1: weight operands may be written by the previous kernel of the stream (no early weight fetch)
   char err[512];
 };
 // Returns a workspace of at least `bytes` (256-byte aligned); grows it when needed (synchronises the stream first).

@@ -46,6 +46,7 @@ struct Params {
   int64_t N, K;
   int stages_per_tile, units, per, max_slots;
   uint32_t idesc;
+  int wait_first;             // 1: read nothing before the previous kernel of the stream has completed
   int32_t* status;
 };
 
@@ -146,6 +147,7 @@ gemm_fp8_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
   const int u0 = blockIdx.x * p.per, u1 = min(u0 + p.per, p.units);
   const int total = u1 - u0;
 
+  if (p.wait_first) asm volatile("griddepcontrol.wait;" ::: "memory");
   if (threadIdx.x == 0) {
     s_abort = 0;
     // a stage is full after two arrivals (weight copy issued, activation copy issued) and their bytes
@@ -399,6 +401,7 @@ int32_t launch(b2q_handle h, const uint8_t* a, const uint8_t* w, int tokens, int
   p.per = per;
   // instruction descriptor (kind::f8f6f4): fp32 accumulate, A = weights and B = activations in `fmt`, both K-major, N = NB, M = 128
   p.idesc = (1u << 4) | ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10) | ((uint32_t)(NB >> 3) << 17) | ((uint32_t)(TILE_ROWS >> 4) << 24);
+  p.wait_first = h->dynamic_weights;
   p.status = h->d_status;
 
   static bool attr_set = false;

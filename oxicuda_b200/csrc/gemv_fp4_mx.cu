@@ -80,6 +80,7 @@ struct Params {
   int units, per;             // work units in total and per CTA
   int max_slots;
   uint32_t idesc;
+  int wait_first;             // 1: read nothing before the previous kernel of the stream has completed
   int debug;                  // report which wait expired (status 400 + role) instead of B2Q_ERR_TIMEOUT
   int32_t* status;
 };
@@ -282,6 +283,7 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, 1) gemv_fp4_mx_kernel(const
   const int S = p.stages_per_tile;
   const int u0 = blockIdx.x * p.per, u1 = min(u0 + p.per, p.units);
 
+  if (p.wait_first) asm volatile("griddepcontrol.wait;" ::: "memory");
   if (threadIdx.x == 0) {
     s_abort = 0;
     // a stage is full after: weight copy issued, (activation copy issued,) weight scale atom (and activation codes) written
@@ -635,6 +637,7 @@ int32_t launch(b2q_handle h, const uint8_t* codes, const uint8_t* scales, const 
   p.per = per;
   // block-scaled instruction descriptor: A = E2M1 (5), B = E4M3 (0), both K-major, N = NB, E8M0 scales, M = 128
   p.idesc = (5u << 7) | (0u << 10) | ((uint32_t)(C::NB >> 3) << 17) | (1u << 23) | ((uint32_t)(TILE_ROWS >> 4) << 24);
+  p.wait_first = h->dynamic_weights;
   if (const char* e = getenv("B2Q_MX_DEBUG")) p.debug = atoi(e);   // 1: report which wait expired as status 400 + role
   p.status = h->d_status;
 

@@ -65,6 +65,12 @@ int32_t b2q_destroy(b2q_handle h) {
   return B2Q_OK;
 }
 
+int32_t b2q_set_static_weights(b2q_handle h, int static_weights) {
+  B2Q_REQUIRE_HANDLE(h);
+  h->dynamic_weights = static_weights ? 0 : 1;
+  return B2Q_OK;
+}
+
 int32_t b2q_set_stream(b2q_handle h, void* stream) {
   B2Q_REQUIRE_HANDLE(h);
   h->stream = (cudaStream_t)stream;

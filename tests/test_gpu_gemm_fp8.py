@@ -88,6 +88,31 @@ def test_weight_stationary_tcgen05_kernel(cuda, oracle, M, N, K, monkeypatch):
     assert rel_err(got.cpu().numpy(), ref) <= 1e-3
 
 
+def test_weights_written_right_before_the_call(cuda, oracle, monkeypatch):
+    """With static_weights off the few-token kernel reads nothing before the previous kernel of the stream (here the
+    one that produces the weight codes) has completed."""
+    from oxicuda_b200.blas import gemm_fp8
+    from oxicuda_b200.quant import Fp8Codec
+    from oxicuda_b200._lib import default_handle
+    monkeypatch.setenv("B2Q_FP8_SKINNY", "1")
+    h = default_handle()
+    h.set_static_weights(False)
+    try:
+        M, N, K = 8, 8192, 4096
+        codec = Fp8Codec.e4m3("rne")
+        g = torch.Generator(device=cuda).manual_seed(5)
+        a = torch.randn(M, K, device=cuda, generator=g)
+        ac, sa = codec.quantize_rows(a, 1, M * K)
+        for rep in range(5):
+            w = torch.randn(N, K, device=cuda, generator=g) * 0.02
+            wc, sw = codec.quantize_rows(w, 1, N * K)            # kernels on the same stream, no synchronisation
+            got = gemm_fp8(ac.view(M, K), wc.view(N, K), sa, sw, out_dtype=torch.float32)
+            ref = oracle.gemm_fp8(ac.view(M, K).cpu().numpy(), wc.view(N, K).cpu().numpy(), sa.cpu().numpy(), sw.cpu().numpy(), 0, 1, "f32")
+            assert rel_err(got.cpu().numpy(), ref) <= 1e-3, rep
+    finally:
+        h.set_static_weights(True)
+
+
 def test_simt_kernel_reproduces_oracle_order(cuda, oracle):
     """The checker kernel (software decode, k-ascending fp32 FMA) equals the oracle to the last bit."""
     from oxicuda_b200.blas import gemm_fp8
