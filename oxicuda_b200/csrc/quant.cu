@@ -461,6 +461,38 @@ __global__ void __launch_bounds__(kThreads) distfp8_dequantize_kernel(const uint
     out[i] = __fmul_rn((float)(int8_t)q[i], __fdiv_rn(absmaxs[i / block], 127.0f));
 }
 
+// Few long rows (per-token quantization of a decode step): one CTA of 1024 threads per row does the statistics and the
+// encoding in one launch, with the arithmetic of the two-kernel path (finish_row, then divide, clamp, encode).
+template <typename T>
+__global__ void __launch_bounds__(1024) fp8_quantize_rows_fused_kernel(const T* x, int64_t cols, StatArgs a, int fmt, int rounding,
+                                                                       uint8_t* codes) {
+  __shared__ RowStat sh[32];
+  __shared__ float s_scale;
+  const int64_t r = blockIdx.x;
+  const T* row = x + r * cols;
+  RowStat s = scan_segment<T>(row, 0, cols, (int)threadIdx.x, (int)blockDim.x);
+  s = warp_reduce_stat(s);
+  if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = s;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    RowStat t = threadIdx.x < (blockDim.x >> 5) ? sh[threadIdx.x] : RowStat{__uint_as_float(0x7F800000u), __uint_as_float(0xFF800000u), 0.0f, 0};
+    t = warp_reduce_stat(t);
+    if (threadIdx.x == 0) {
+      finish_row(a, r, t);
+      s_scale = a.scales[r];
+    }
+  }
+  __syncthreads();
+  const float scale = s_scale;
+  const Fp8Fmt F = fp8_fmt(fmt);
+  uint8_t* out = codes + r * cols;
+  for (int64_t i = threadIdx.x; i < cols; i += blockDim.x) {
+    float v = __fdiv_rn(load_as_f32<T>(row, i), scale);
+    v = v < -F.max_val ? -F.max_val : (v > F.max_val ? F.max_val : v);
+    out[i] = (uint8_t)(rounding == 0 ? fp8_encode_ref_dev(v, F) : fp8_encode_rne_dev(v, fmt));
+  }
+}
+
 template <typename T>
 int32_t fp8_quantize_rows_impl(b2q_handle h, const T* x, int64_t rows, int64_t cols, int fmt, int rounding,
                                float* scales, uint8_t* codes) {
@@ -468,6 +500,11 @@ int32_t fp8_quantize_rows_impl(b2q_handle h, const T* x, int64_t rows, int64_t c
   if (!x || !scales || !codes) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "fp8_quantize_rows: null pointer");
   if (fmt < 0 || fmt > 1 || rounding < 0 || rounding > 1) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "fp8_quantize_rows: bad format/rounding");
   StatArgs a{kFp8Scale, 0, 0, fp8_fmt(fmt).max_val, scales, nullptr, h->d_status, 1};
+  if (rows <= 128 && cols >= 2048 && cols <= (1 << 20)) {
+    fp8_quantize_rows_fused_kernel<T><<<(unsigned)rows, 1024, 0, h->stream>>>(x, cols, a, fmt, rounding, codes);
+    B2Q_LAUNCH_CHECK(h, "fp8_quantize_rows_fused_kernel");
+    return B2Q_OK;
+  }
   int32_t st = launch_row_stats<T>(h, x, rows, cols, a);
   if (st != B2Q_OK) return st;
   const int64_t n = rows * cols;
@@ -762,7 +799,7 @@ extern "C" int32_t b2q_fp8_quantize_rows_f32_noalloc(const float* x, int64_t row
 namespace {
 __device__ __forceinline__ float swiglu_f32(float g, float u) { return __fdiv_rn(g, 1.0f + expf(-g)) * u; }
 
-__global__ void __launch_bounds__(kThreads) swiglu_quantize_rows_kernel(const __nv_bfloat16* __restrict__ gate,
+__global__ void __launch_bounds__(1024) swiglu_quantize_rows_kernel(const __nv_bfloat16* __restrict__ gate,
                                                                         const __nv_bfloat16* __restrict__ up, int64_t ld,
                                                                         int64_t cols, int fmt, int rounding, float* scales,
                                                                         uint8_t* codes) {
@@ -770,11 +807,12 @@ __global__ void __launch_bounds__(kThreads) swiglu_quantize_rows_kernel(const __
   const __nv_bfloat16* g = gate + r * ld;
   const __nv_bfloat16* u = up + r * ld;
   const Fp8Fmt F = fp8_fmt(fmt);
-  __shared__ float sh[kThreads / 32];
+  __shared__ float sh[32];
+  const int nthreads = (int)blockDim.x;                      // kThreads, or 1024 when there are few rows
   float amax = 0.0f;
   const bool vec = (cols % 8 == 0) && (ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up)) & 15) == 0;
   if (vec) {
-    for (int64_t c = (int64_t)threadIdx.x * 8; c < cols; c += (int64_t)kThreads * 8) {
+    for (int64_t c = (int64_t)threadIdx.x * 8; c < cols; c += (int64_t)nthreads * 8) {
       const uint4 gv = *reinterpret_cast<const uint4*>(g + c), uv = *reinterpret_cast<const uint4*>(u + c);
       const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
 #pragma unroll
@@ -784,15 +822,14 @@ __global__ void __launch_bounds__(kThreads) swiglu_quantize_rows_kernel(const __
       }
     }
   } else {
-    for (int64_t c = threadIdx.x; c < cols; c += kThreads)
+    for (int64_t c = threadIdx.x; c < cols; c += nthreads)
       amax = fmaxf(amax, fabsf(swiglu_f32(__bfloat162float(g[c]), __bfloat162float(u[c]))));
   }
   amax = warp_max(amax);
   if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = amax;
   __syncthreads();
   amax = sh[0];
-#pragma unroll
-  for (int w = 1; w < kThreads / 32; ++w) amax = fmaxf(amax, sh[w]);
+  for (int w = 1; w < nthreads / 32; ++w) amax = fmaxf(amax, sh[w]);
   const float scale = amax > 0.0f ? __fdiv_rn(amax, F.max_val) : 1.0f;
   if (threadIdx.x == 0) scales[r] = scale;
   auto enc = [&](float h) -> uint32_t {
@@ -802,7 +839,7 @@ __global__ void __launch_bounds__(kThreads) swiglu_quantize_rows_kernel(const __
   };
   uint8_t* out = codes + r * cols;
   if (vec) {
-    for (int64_t c = (int64_t)threadIdx.x * 8; c < cols; c += (int64_t)kThreads * 8) {
+    for (int64_t c = (int64_t)threadIdx.x * 8; c < cols; c += (int64_t)nthreads * 8) {
       const uint4 gv = *reinterpret_cast<const uint4*>(g + c), uv = *reinterpret_cast<const uint4*>(u + c);
       const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
       uint32_t lo = 0, hi = 0;
@@ -816,7 +853,7 @@ __global__ void __launch_bounds__(kThreads) swiglu_quantize_rows_kernel(const __
       *reinterpret_cast<uint2*>(out + c) = make_uint2(lo, hi);
     }
   } else {
-    for (int64_t c = threadIdx.x; c < cols; c += kThreads)
+    for (int64_t c = threadIdx.x; c < cols; c += nthreads)
       out[c] = (uint8_t)enc(swiglu_f32(__bfloat162float(g[c]), __bfloat162float(u[c])));
   }
 }
@@ -829,7 +866,7 @@ extern "C" int32_t b2q_swiglu_quantize_rows_bf16(b2q_handle h, const void* gate,
   if (!gate || !up || !scales || !codes || ld < cols || fmt < 0 || fmt > 1 || rounding < 0 || rounding > 1)
     B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "swiglu_quantize_rows: bad argument");
   if (rows > 0x7FFFFFFF) B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "swiglu_quantize_rows: too many rows");
-  swiglu_quantize_rows_kernel<<<(unsigned)rows, kThreads, 0, h->stream>>>((const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, ld,
+  swiglu_quantize_rows_kernel<<<(unsigned)rows, rows <= 2 * h->sm_count ? 1024 : kThreads, 0, h->stream>>>((const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, ld,
                                                                           cols, fmt, rounding, scales, codes);
   B2Q_LAUNCH_CHECK(h, "swiglu_quantize_rows_kernel");
   return B2Q_OK;
