@@ -3,6 +3,8 @@
 // dist-infer INT8-in-u8 flavour.  All kernels are grid-stride, 128-bit vectorised
 // where the pointers allow it, and launched on the handle's stream.
 #include "common.cuh"
+#include <cooperative_groups.h>
+namespace cg = cooperative_groups;
 
 namespace {
 
@@ -799,18 +801,25 @@ extern "C" int32_t b2q_fp8_quantize_rows_f32_noalloc(const float* x, int64_t row
 namespace {
 __device__ __forceinline__ float swiglu_f32(float g, float u) { return __fdiv_rn(g, 1.0f + expf(-g)) * u; }
 
+// `split` > 1: a thread-block cluster of `split` CTAs shares a row (few rows, long rows: the decode step); each CTA
+// takes a contiguous slice of the columns and the slices' maxima are exchanged through distributed shared memory.
 __global__ void __launch_bounds__(1024) swiglu_quantize_rows_kernel(const __nv_bfloat16* __restrict__ gate,
                                                                         const __nv_bfloat16* __restrict__ up, int64_t ld,
-                                                                        int64_t cols, int fmt, int rounding, float* scales,
-                                                                        uint8_t* codes) {
-  const int64_t r = blockIdx.x;
-  const __nv_bfloat16* g = gate + r * ld;
-  const __nv_bfloat16* u = up + r * ld;
+                                                                        int64_t cols_all, int fmt, int rounding, float* scales,
+                                                                        uint8_t* codes, int split) {
+  const int64_t r = blockIdx.x / split;
+  const int part = (int)(blockIdx.x % split);
+  // slices are multiples of 8 columns so that the vector path keeps its alignment
+  const int64_t slice = ((cols_all + split - 1) / split + 7) & ~(int64_t)7;
+  const int64_t c_begin = min((int64_t)part * slice, cols_all), c_end = min(c_begin + slice, cols_all);
+  const int64_t cols = c_end - c_begin;
+  const __nv_bfloat16* g = gate + r * ld + c_begin;
+  const __nv_bfloat16* u = up + r * ld + c_begin;
   const Fp8Fmt F = fp8_fmt(fmt);
   __shared__ float sh[32];
   const int nthreads = (int)blockDim.x;                      // kThreads, or 1024 when there are few rows
   float amax = 0.0f;
-  const bool vec = (cols % 8 == 0) && (ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up)) & 15) == 0;
+  const bool vec = (cols % 8 == 0) && (cols_all % 8 == 0) && (ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up)) & 15) == 0;
   if (vec) {
     for (int64_t c = (int64_t)threadIdx.x * 8; c < cols; c += (int64_t)nthreads * 8) {
       const uint4 gv = *reinterpret_cast<const uint4*>(g + c), uv = *reinterpret_cast<const uint4*>(u + c);
@@ -830,14 +839,22 @@ __global__ void __launch_bounds__(1024) swiglu_quantize_rows_kernel(const __nv_b
   __syncthreads();
   amax = sh[0];
   for (int w = 1; w < nthreads / 32; ++w) amax = fmaxf(amax, sh[w]);
+  if (split > 1) {
+    __shared__ float s_part;
+    cg::cluster_group cluster = cg::this_cluster();
+    if (threadIdx.x == 0) s_part = amax;
+    cluster.sync();
+    for (int q = 0; q < split; ++q) amax = fmaxf(amax, *cluster.map_shared_rank(&s_part, q));
+    cluster.sync();                                          // peers may still be reading this CTA's maximum
+  }
   const float scale = amax > 0.0f ? __fdiv_rn(amax, F.max_val) : 1.0f;
-  if (threadIdx.x == 0) scales[r] = scale;
+  if (threadIdx.x == 0 && part == 0) scales[r] = scale;
   auto enc = [&](float h) -> uint32_t {
     float v = __fdiv_rn(h, scale);
     v = v < -F.max_val ? -F.max_val : (v > F.max_val ? F.max_val : v);
     return rounding == 0 ? fp8_encode_ref_dev(v, F) : fp8_encode_rne_dev(v, fmt);
   };
-  uint8_t* out = codes + r * cols;
+  uint8_t* out = codes + r * cols_all + c_begin;
   if (vec) {
     for (int64_t c = (int64_t)threadIdx.x * 8; c < cols; c += (int64_t)nthreads * 8) {
       const uint4 gv = *reinterpret_cast<const uint4*>(g + c), uv = *reinterpret_cast<const uint4*>(u + c);
@@ -866,8 +883,21 @@ extern "C" int32_t b2q_swiglu_quantize_rows_bf16(b2q_handle h, const void* gate,
   if (!gate || !up || !scales || !codes || ld < cols || fmt < 0 || fmt > 1 || rounding < 0 || rounding > 1)
     B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "swiglu_quantize_rows: bad argument");
   if (rows > 0x7FFFFFFF) B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "swiglu_quantize_rows: too many rows");
-  swiglu_quantize_rows_kernel<<<(unsigned)rows, rows <= 2 * h->sm_count ? 1024 : kThreads, 0, h->stream>>>((const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, ld,
-                                                                          cols, fmt, rounding, scales, codes);
-  B2Q_LAUNCH_CHECK(h, "swiglu_quantize_rows_kernel");
+  // few rows: 1024 threads per CTA, and for long rows a cluster of 8 CTAs per row
+  const int threads = rows <= 2 * h->sm_count ? 1024 : kThreads;
+  const int split = (rows * 8 <= h->sm_count && cols >= 8192) ? 8 : 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(rows * split));
+  cfg.blockDim = dim3((unsigned)threads);
+  cfg.stream = h->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)split;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, swiglu_quantize_rows_kernel, (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, ld, cols, fmt,
+                                 rounding, scales, codes, split));
   return B2Q_OK;
 }
