@@ -156,7 +156,7 @@ def main():
     ap.add_argument("--rounding", default="rne", choices=["rne", "ref"], help="E4M3 encoder used to make the operands")
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMV / INT8 side measurements")
     ap.add_argument("--case", default=None,
-                    help="run ONE kernel case a few times and exit (for ncu captures): gemm_fp8:M:N:K | gemv_fp4:K:N:tokens")
+                    help="run ONE kernel case a few times and exit (for ncu captures): gemm_fp8:M:N:K | gemv_fp4:K:N:tokens | kv_quant:tokens:head_dim:axis:bf16 | rms_quant:rows:cols:residual")
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args()
     if args.case:
@@ -354,6 +354,25 @@ def run_case(case: str, iters: int):
         out = torch.empty(tokens, n, dtype=torch.bfloat16, device=dev)
         fn = lambda: gemv_fp4_wo(codes, scales, x, n, k, out=out)
         work, unit = (n * k // 2 + n * k // 32 + 2 * tokens * k + 2 * tokens * n) / 1e9, "GB/s"
+    elif kind == "kv_quant":        # kv_quant:n_tokens:head_dim:axis:bf16  (KvCacheQuantizer, 8 bits)
+        from oxicuda_b200._lib import default_handle, ptr
+        tokens, hd, axis, bf16 = d
+        x = torch.randn(tokens, hd, device=dev)
+        x = x.to(torch.bfloat16) if bf16 else x
+        groups = tokens if axis == 0 else hd
+        codes = torch.empty(tokens * hd, dtype=torch.uint8, device=dev)
+        sc, zp = torch.empty(groups, device=dev), torch.empty(groups, device=dev)
+        name = "b2q_kv_cache_quantize_bf16" if bf16 else "b2q_kv_cache_quantize_f32"
+        fn = lambda: default_handle().call(name, ptr(x), tokens, hd, 8, axis, ptr(codes), ptr(sc), ptr(zp))
+        work, unit = (tokens * hd * (x.element_size() + 1) + 8 * groups) / 1e9, "GB/s"
+    elif kind == "rms_quant":       # rms_quant:rows:cols:residual
+        from oxicuda_b200.kv_cache import rms_norm_quantize_fp8
+        rows, cols, with_res = d
+        x = torch.randn(rows, cols, device=dev).to(torch.bfloat16)
+        gamma = torch.ones(cols, device=dev, dtype=torch.bfloat16)
+        res = torch.zeros(rows, cols, device=dev, dtype=torch.bfloat16) if with_res else None
+        fn = lambda: rms_norm_quantize_fp8(x, gamma, 1e-6, residual=res)
+        work, unit = (rows * cols * (3 + (4 if with_res else 0)) + 2 * cols + 4 * rows) / 1e9, "GB/s"
     else:
         raise SystemExit(f"unknown case {case}")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)

@@ -40,7 +40,8 @@ typedef enum {
   B2Q_ERR_GROUP_SIZE_MISMATCH = 21,  /* QuantError::GroupSizeMismatch */
   B2Q_ERR_INVALID_SCALE = 22,        /* QuantError::InvalidScale */
   B2Q_ERR_NON_FINITE_FP8 = 23,       /* QuantError::NonFiniteFp8 */
-  B2Q_ERR_INVALID_CONFIG = 24,       /* QuantError::InvalidConfig */
+  B2Q_ERR_INVALID_CONFIG = 24,       /* QuantError::InvalidConfig / InferError::InvalidConfig */
+  B2Q_ERR_INVALID_BIT_WIDTH = 25,    /* QuantError::InvalidBitWidth */
   B2Q_ERR_TIMEOUT = 40               /* a bounded device-side wait gave up */
 } b2q_status;
 
@@ -165,6 +166,46 @@ int32_t b2q_distfp8_quantize_block_f32(b2q_handle h, const float* x, int64_t n, 
                                        float* absmaxs);
 int32_t b2q_distfp8_dequantize_block_f32(b2q_handle h, const uint8_t* q, int64_t n, int64_t block,
                                          const float* absmaxs, float* out);
+
+/* ---- RMSNorm fused with the per-token FP8 quantizer of the next linear ----
+ * y = x / sqrt(mean(x^2) + eps) * gamma per row (rms_norm, crates/oxicuda-dnn/src/norm/rms_norm.rs:29-33, CPU statement
+ * :566-574), then scale = absmax(y)/max_val per row and code = encode(y/scale) exactly as b2q_fp8_quantize_rows_bf16
+ * would compute them from y in f32.  x, gamma: bf16.  residual (optional, bf16 [rows x cols], updated in place) selects
+ * fused_add_rms_norm (rms_norm.rs:98-103): residual = bf16(residual + x) and the norm is taken of the stored sum.
+ * y_out (optional, bf16) also receives the normalised activations.  The f32 sum of squares is a tree sum, so y can
+ * differ from the reference's sequential sum in the last bits (the reference's own GPU kernel uses rsqrt.approx). */
+int32_t b2q_rms_norm_quantize_fp8_bf16(b2q_handle h, const void* x_bf16, void* residual_bf16, const void* gamma_bf16,
+                                       int64_t rows, int64_t cols, float eps, int fmt, int rounding, float* scales,
+                                       uint8_t* codes, void* y_out_bf16);
+
+/* ---- KvCacheQuantizer: crates/oxicuda-quant/src/scheme/kv_cache.rs ---- */
+typedef enum { B2Q_KV_PER_TOKEN = 0, B2Q_KV_PER_CHANNEL = 1 } b2q_kv_axis;  /* KvAxis, kv_cache.rs:33-38 */
+/* quantize (:146-221): x is [n_tokens x head_dim] row-major; codes (one per byte, as the reference's Vec<u8>) lie in
+ * [0, 2^bits-1], bits in [2, 8] (KvCacheConfig::new :59-64, else B2Q_ERR_INVALID_BIT_WIDTH); scales / zero_points hold
+ * one f32 per group: n_tokens of them for B2Q_KV_PER_TOKEN, head_dim for B2Q_KV_PER_CHANNEL.  Bit-exact.
+ * append_token (:254-282) is this call with n_tokens = 1 and the output pointers advanced to the new row. */
+int32_t b2q_kv_cache_quantize_f32(b2q_handle h, const float* x, int64_t n_tokens, int64_t head_dim, int bits, int axis,
+                                  uint8_t* codes, float* scales, float* zero_points);
+int32_t b2q_kv_cache_quantize_bf16(b2q_handle h, const void* x_bf16, int64_t n_tokens, int64_t head_dim, int bits,
+                                   int axis, uint8_t* codes, float* scales, float* zero_points);
+/* dequantize (:224-238): code * scale + zero_point, unfused.  The bf16 form rounds that f32 value to nearest even. */
+int32_t b2q_kv_cache_dequantize_f32(b2q_handle h, const uint8_t* codes, int64_t n_tokens, int64_t head_dim, int axis,
+                                    const float* scales, const float* zero_points, float* out);
+int32_t b2q_kv_cache_dequantize_bf16(b2q_handle h, const uint8_t* codes, int64_t n_tokens, int64_t head_dim, int axis,
+                                     const float* scales, const float* zero_points, void* out_bf16);
+/* ---- quantize_token: crates/oxicuda-infer/src/cache/kv_quant.rs:112-154, for n_tokens vectors of d channels ----
+ * bits is 4 or 8 (KvQuantConfig::new :48-53, else B2Q_ERR_INVALID_CONFIG); symmetric codes lie in
+ * [-(2^(bits-1)-1), 2^(bits-1)-1] and are stored as int8, asymmetric ones in [0, 2^bits-1] as uint8 (the reference
+ * holds them as Vec<i32>; q_range :69-76).  An empty input is B2Q_ERR_INVALID_CONFIG as in the reference (:113-115). */
+int32_t b2q_kv_quantize_tokens_f32(b2q_handle h, const float* x, int64_t n_tokens, int64_t d, int bits, int symmetric,
+                                   uint8_t* codes, float* scales, float* zero_points);
+int32_t b2q_kv_quantize_tokens_bf16(b2q_handle h, const void* x_bf16, int64_t n_tokens, int64_t d, int bits,
+                                    int symmetric, uint8_t* codes, float* scales, float* zero_points);
+/* QuantizedToken::dequantize (:94-100): scale * code + zero_point. */
+int32_t b2q_kv_dequantize_tokens_f32(b2q_handle h, const uint8_t* codes, int64_t n_tokens, int64_t d, int symmetric,
+                                     const float* scales, const float* zero_points, float* out);
+int32_t b2q_kv_dequantize_tokens_bf16(b2q_handle h, const uint8_t* codes, int64_t n_tokens, int64_t d, int symmetric,
+                                      const float* scales, const float* zero_points, void* out_bf16);
 
 /* ---- LlmInt8Quantizer::matmul: crates/oxicuda-quant/src/scheme/llm_int8.rs:175-288 ----
  * x [samples x cols] f32, w [rows x cols] f32 -> out [samples x rows] f32.  Per-row INT8 of W and per-token

@@ -294,6 +294,54 @@ def swiglu(gate, up):
 
 
 # ---- heuristics ----
+# ---- KV cache / RMSNorm ----
+def kv_cache_quantize(x, n_tokens, head_dim, bits=8, axis=0):
+    """axis 0 = PerToken, 1 = PerChannel.  Returns (codes u8, scales, zero_points)."""
+    x = _f32(x).reshape(-1)
+    groups = n_tokens if axis == 0 else head_dim
+    codes = np.zeros(n_tokens * head_dim, np.uint8)
+    scales = np.zeros(groups, np.float32)
+    zps = np.zeros(groups, np.float32)
+    lib().orc_kv_cache_quantize(_p(x), _i64(n_tokens), _i64(head_dim), bits, axis, _p(codes), _p(scales), _p(zps))
+    return codes, scales, zps
+
+
+def kv_cache_dequantize(codes, n_tokens, head_dim, axis, scales, zps):
+    codes = np.ascontiguousarray(codes, np.uint8).reshape(-1)
+    scales, zps = _f32(scales), _f32(zps)
+    out = np.zeros(n_tokens * head_dim, np.float32)
+    lib().orc_kv_cache_dequantize(_p(codes), _i64(n_tokens), _i64(head_dim), axis, _p(scales), _p(zps), _p(out))
+    return out
+
+
+def kv_quantize_tokens(x, n_tokens, d, bits=8, symmetric=False):
+    """Returns (codes i32, scales, zero_points), one (scale, zero point) per token."""
+    x = _f32(x).reshape(-1)
+    codes = np.zeros(n_tokens * d, np.int32)
+    scales = np.zeros(n_tokens, np.float32)
+    zps = np.zeros(n_tokens, np.float32)
+    lib().orc_kv_quantize_tokens(_p(x), _i64(n_tokens), _i64(d), bits, int(bool(symmetric)), _p(codes), _p(scales), _p(zps))
+    return codes, scales, zps
+
+
+def kv_dequantize_tokens(codes, n_tokens, d, scales, zps):
+    codes = np.ascontiguousarray(codes, np.int32).reshape(-1)
+    scales, zps = _f32(scales), _f32(zps)
+    out = np.zeros(n_tokens * d, np.float32)
+    lib().orc_kv_dequantize_tokens(_p(codes), _i64(n_tokens), _i64(d), _p(scales), _p(zps), _p(out))
+    return out
+
+
+def rms_norm(x, gamma, rows, cols, eps, residual=None):
+    """Returns y (and the updated residual when one is given)."""
+    x = _f32(x).reshape(-1)
+    gamma = _f32(gamma).reshape(-1)
+    y = np.zeros(rows * cols, np.float32)
+    res = None if residual is None else _f32(residual).reshape(-1).copy()
+    lib().orc_rms_norm(_p(x), _p(res), _p(gamma), _i64(rows), _i64(cols), C.c_float(eps), _p(y))
+    return y if residual is None else (y, res)
+
+
 def classify_workload(m, n, k):
     return int(lib().orc_classify_workload(C.c_uint32(m), C.c_uint32(n), C.c_uint32(k)))
 

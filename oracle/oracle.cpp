@@ -685,6 +685,99 @@ void orc_swiglu(const float* gate, const float* up, int64_t n, float* h) {
 }
 
 // ---------------------------------------------------------------------------
+// KvCacheQuantizer — crates/oxicuda-quant/src/scheme/kv_cache.rs
+// ---------------------------------------------------------------------------
+// quantize (:146-221): asymmetric affine codes in [0, 2^bits-1] with one (scale, min) per group;
+// axis 0 = KvAxis::PerToken (one group per row), 1 = KvAxis::PerChannel (one group per column).
+// append_token (:254-282) is the per-token rule on a single row, so it is this function with n_tokens = 1.
+void orc_kv_cache_quantize(const float* x, int64_t n_tokens, int64_t head_dim, int bits, int axis,
+                           uint8_t* codes, float* scales, float* zero_points) {
+  const float q_max = (float)((1u << bits) - 1u);
+  const int64_t n_groups = axis == 0 ? n_tokens : head_dim;
+  std::vector<float> gmin((size_t)n_groups, INFINITY), gmax((size_t)n_groups, -INFINITY);
+  for (int64_t t = 0; t < n_tokens; ++t)
+    for (int64_t c = 0; c < head_dim; ++c) {
+      const float v = x[t * head_dim + c];
+      const int64_t g = axis == 0 ? t : c;
+      if (v < gmin[g]) gmin[g] = v;
+      if (v > gmax[g]) gmax[g] = v;
+    }
+  for (int64_t g = 0; g < n_groups; ++g) {
+    const float range = rmax(gmax[g] - gmin[g], 1e-8f);
+    scales[g] = range / q_max;
+    zero_points[g] = gmin[g];
+  }
+  for (int64_t t = 0; t < n_tokens; ++t)
+    for (int64_t c = 0; c < head_dim; ++c) {
+      const int64_t g = axis == 0 ? t : c;
+      const float q = rclamp(std::round((x[t * head_dim + c] - zero_points[g]) / scales[g]), 0.0f, q_max);
+      codes[t * head_dim + c] = (uint8_t)f32_as_i32(q != q ? 0.0f : q);   // `NaN as u8` is 0; q is already within [0, 255]
+    }
+}
+// dequantize (:224-238): q * scale + zero_point, unfused.
+void orc_kv_cache_dequantize(const uint8_t* codes, int64_t n_tokens, int64_t head_dim, int axis,
+                             const float* scales, const float* zero_points, float* out) {
+  for (int64_t t = 0; t < n_tokens; ++t)
+    for (int64_t c = 0; c < head_dim; ++c) {
+      const int64_t g = axis == 0 ? t : c;
+      out[t * head_dim + c] = (float)codes[t * head_dim + c] * scales[g] + zero_points[g];
+    }
+}
+
+// quantize_token — crates/oxicuda-infer/src/cache/kv_quant.rs:112-154, applied to each of `n_tokens` rows of `d`
+// channels.  q_range (:69-76): symmetric [-(2^(bits-1)-1), 2^(bits-1)-1], asymmetric [0, 2^bits-1].
+void orc_kv_quantize_tokens(const float* x, int64_t n_tokens, int64_t d, int bits, int symmetric,
+                            int32_t* codes, float* scales, float* zero_points) {
+  const int32_t qmin = symmetric ? -((1 << (bits - 1)) - 1) : 0;
+  const int32_t qmax = symmetric ? (1 << (bits - 1)) - 1 : (1 << bits) - 1;
+  const float qmin_f = (float)qmin, qmax_f = (float)qmax;
+  for (int64_t t = 0; t < n_tokens; ++t) {
+    const float* row = x + t * d;
+    float x_min = INFINITY, x_max = -INFINITY;
+    for (int64_t i = 0; i < d; ++i) { x_min = rmin(x_min, row[i]); x_max = rmax(x_max, row[i]); }
+    float scale, zp;
+    if (symmetric) {
+      const float amax = rmax(std::fabs(x_min), std::fabs(x_max));
+      scale = amax > 0.0f ? amax / qmax_f : 1.0f;
+      zp = 0.0f;
+    } else {
+      const float range = x_max - x_min;
+      scale = range > 0.0f ? range / (qmax_f - qmin_f) : 1.0f;
+      zp = x_min - qmin_f * scale;
+    }
+    for (int64_t i = 0; i < d; ++i) {
+      const int32_t q = f32_as_i32(std::round((row[i] - zp) / scale));
+      codes[t * d + i] = q < qmin ? qmin : (q > qmax ? qmax : q);
+    }
+    scales[t] = scale; zero_points[t] = zp;
+  }
+}
+// QuantizedToken::dequantize (:94-100): scale * code + zero_point, unfused.
+void orc_kv_dequantize_tokens(const int32_t* codes, int64_t n_tokens, int64_t d, const float* scales,
+                              const float* zero_points, float* out) {
+  for (int64_t t = 0; t < n_tokens; ++t)
+    for (int64_t i = 0; i < d; ++i) out[t * d + i] = scales[t] * (float)codes[t * d + i] + zero_points[t];
+}
+
+// RMSNorm — crates/oxicuda-dnn/src/norm/rms_norm.rs:29-33 (definition), :566-574 (CPU statement of the same):
+// y = x / sqrt(mean(x^2) + eps) * gamma per row, sequential f32 sum.  With `residual` non-null the fused form of
+// fused_add_rms_norm (:98-103): residual += x first, and the norm is taken of the updated residual.
+void orc_rms_norm(const float* x, float* residual, const float* gamma, int64_t rows, int64_t cols, float eps, float* y) {
+  for (int64_t r = 0; r < rows; ++r) {
+    const float* row = x + r * cols;
+    if (residual) {
+      float* res = residual + r * cols;
+      for (int64_t i = 0; i < cols; ++i) res[i] = res[i] + row[i];
+      row = res;
+    }
+    float sum = 0.0f;
+    for (int64_t i = 0; i < cols; ++i) sum += row[i] * row[i];
+    const float rms = std::sqrt(sum / (float)cols + eps);
+    for (int64_t i = 0; i < cols; ++i) y[r * cols + i] = row[i] / rms * gamma[i];
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Tile heuristics — crates/oxicuda-blas/src/precision/fp8_ops.rs:67-87 (classify),
 // :239-304 (Blackwell table), :389-396 (split-K); fp4_fp6_ops.rs:996-1075;
 // int_ops.rs:141-176.  Class ids: 0 SmallSquare, 1 LargeSquare, 2 SkinnyM,

@@ -19,6 +19,7 @@ OK = 0
 ERR_CUDA, ERR_INVALID_DIMENSION, ERR_BUFFER_TOO_SMALL, ERR_DIMENSION_MISMATCH = 1, 2, 3, 4
 ERR_UNSUPPORTED, ERR_LAUNCH_FAILED, ERR_INVALID_ARGUMENT = 5, 7, 8
 ERR_EMPTY_INPUT, ERR_GROUP_SIZE_MISMATCH, ERR_INVALID_SCALE, ERR_NON_FINITE_FP8, ERR_INVALID_CONFIG = 20, 21, 22, 23, 24
+ERR_INVALID_BIT_WIDTH = 25
 ERR_TIMEOUT = 40
 
 FP8_E4M3, FP8_E5M2 = 0, 1
@@ -52,6 +53,7 @@ class GroupSizeMismatch(B2qError): pass
 class InvalidScale(B2qError): pass
 class NonFiniteFp8(B2qError): pass
 class InvalidConfig(B2qError): pass
+class InvalidBitWidth(B2qError): pass
 class DeviceTimeout(B2qError): pass
 
 
@@ -60,7 +62,7 @@ _ERRORS = {
     ERR_DIMENSION_MISMATCH: DimensionMismatch, ERR_UNSUPPORTED: UnsupportedOperation, ERR_LAUNCH_FAILED: LaunchFailed,
     ERR_INVALID_ARGUMENT: InvalidArgument, ERR_EMPTY_INPUT: EmptyInput, ERR_GROUP_SIZE_MISMATCH: GroupSizeMismatch,
     ERR_INVALID_SCALE: InvalidScale, ERR_NON_FINITE_FP8: NonFiniteFp8, ERR_INVALID_CONFIG: InvalidConfig,
-    ERR_TIMEOUT: DeviceTimeout,
+    ERR_INVALID_BIT_WIDTH: InvalidBitWidth, ERR_TIMEOUT: DeviceTimeout,
 }
 
 
@@ -107,6 +109,15 @@ SIGNATURES = {
     "b2q_fp8_quantize_rows_f32": (C.c_int32, [_H, _P, _I64, _I64, _I, _I, _P, _P]),
     "b2q_fp8_quantize_rows_bf16": (C.c_int32, [_H, _P, _I64, _I64, _I, _I, _P, _P]),
     "b2q_swiglu_quantize_rows_bf16": (C.c_int32, [_H, _P, _P, _I64, _I64, _I64, _I, _I, _P, _P]),
+    "b2q_rms_norm_quantize_fp8_bf16": (C.c_int32, [_H, _P, _P, _P, _I64, _I64, _F, _I, _I, _P, _P, _P]),
+    "b2q_kv_cache_quantize_f32": (C.c_int32, [_H, _P, _I64, _I64, _I, _I, _P, _P, _P]),
+    "b2q_kv_cache_quantize_bf16": (C.c_int32, [_H, _P, _I64, _I64, _I, _I, _P, _P, _P]),
+    "b2q_kv_cache_dequantize_f32": (C.c_int32, [_H, _P, _I64, _I64, _I, _P, _P, _P]),
+    "b2q_kv_cache_dequantize_bf16": (C.c_int32, [_H, _P, _I64, _I64, _I, _P, _P, _P]),
+    "b2q_kv_quantize_tokens_f32": (C.c_int32, [_H, _P, _I64, _I64, _I, _I, _P, _P, _P]),
+    "b2q_kv_quantize_tokens_bf16": (C.c_int32, [_H, _P, _I64, _I64, _I, _I, _P, _P, _P]),
+    "b2q_kv_dequantize_tokens_f32": (C.c_int32, [_H, _P, _I64, _I64, _I, _P, _P, _P]),
+    "b2q_kv_dequantize_tokens_bf16": (C.c_int32, [_H, _P, _I64, _I64, _I, _P, _P, _P]),
     "b2q_fp8_quantize_rows_f32_noalloc": (C.c_int32, [_P, _I64, _I64, _I, _I, _P, _P, _P, _P, C.c_char_p, C.c_size_t]),
     "b2q_fp4_block_quantize_f32": (C.c_int32, [_H, _P, _I64, _I, _I, _I, _P, _P]),
     "b2q_fp4_block_dequantize_f32": (C.c_int32, [_H, _P, _I64, _I, _I, _I, _P, _P]),

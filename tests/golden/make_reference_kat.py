@@ -133,6 +133,45 @@ KAT = {
                                 "ranks": [[1.0, 2.0, 3.0, 4.0], [10.0, 20.0, 30.0, 40.0], [100.0, 200.0, 300.0, 400.0],
                                           [1000.0, 2000.0, 3000.0, 4000.0]], "sum": [1111.0, 2222.0, 3333.0, 4444.0]},
     },
+    "kv_cache": {
+        "int8_per_token_round_trip": {"src": "crates/oxicuda-quant/src/scheme/kv_cache.rs:333-343",
+                                      "n_tokens": 12, "head_dim": 16, "seed": 1, "amp": 3.0, "bits": 8, "axis": 0,
+                                      "n_groups": 12, "rel_err": 0.01},
+        "int8_per_channel_round_trip": {"src": "crates/oxicuda-quant/src/scheme/kv_cache.rs:346-356",
+                                        "n_tokens": 16, "head_dim": 8, "seed": 2, "amp": 3.0, "bits": 8, "axis": 1,
+                                        "n_groups": 8, "rel_err": 0.01},
+        "int4_round_trip_coarser_but_bounded": {"src": "crates/oxicuda-quant/src/scheme/kv_cache.rs:359-369",
+                                                "n_tokens": 10, "head_dim": 12, "seed": 3, "amp": 2.0, "bits": 4, "axis": 0,
+                                                "n_groups": 10, "rel_err": 0.1},
+        "per_channel_beats_per_token_on_key_outliers": {"src": "crates/oxicuda-quant/src/scheme/kv_cache.rs:374-397",
+                                                        "n_tokens": 20, "head_dim": 8, "seed": 4, "amp": 1.0,
+                                                        "outlier_col": 3, "outlier_base": 50.0, "outlier_step": 0.1},
+        "append_token_grows_cache": {"src": "crates/oxicuda-quant/src/scheme/kv_cache.rs:402-419",
+                                     "n_tokens": 4, "head_dim": 6, "seed": 5, "amp": 2.0, "row_seed": 99, "rel_err": 0.01},
+        "packed_bytes_reflects_bit_width": {"src": "crates/oxicuda-quant/src/scheme/kv_cache.rs:448-459",
+                                            "n": 32, "bits4_bytes": 16, "bits8_bytes": 32},
+        "config_validates_bits": {"src": "crates/oxicuda-quant/src/scheme/kv_cache.rs:312-323", "ok": [8, 4], "bad": [1, 16]},
+    },
+    "kv_quant": {
+        "q_range_signed_and_unsigned": {"src": "crates/oxicuda-infer/src/cache/kv_quant.rs:195-203",
+                                        "asym8": [0, 255], "sym8": [-127, 127], "asym4": [0, 15]},
+        "asymmetric_endpoints_exact": {"src": "crates/oxicuda-infer/src/cache/kv_quant.rs:211-221",
+                                       "x": [-1.0, 0.0, 1.0, 2.0], "zero_point": -1.0, "tol": 1e-4},
+        "symmetric_zero_point_is_zero": {"src": "crates/oxicuda-infer/src/cache/kv_quant.rs:224-232",
+                                         "x": [-2.0, -1.0, 1.0, 2.0], "zero_point": 0.0, "mse": 1e-3},
+        "constant_vector_zero_error": {"src": "crates/oxicuda-infer/src/cache/kv_quant.rs:253-262",
+                                       "x": [3.5] * 8, "tol": 1e-5},
+        "dequantize_matches_round_trip_helper": {"src": "crates/oxicuda-infer/src/cache/kv_quant.rs:275-281",
+                                                 "x": [0.1, -0.4, 2.2, -1.7, 0.0]},
+        "mse_decreases_with_precision_on_smooth_signal": {"src": "crates/oxicuda-infer/src/cache/kv_quant.rs:284-290",
+                                                          "n": 64, "step": 0.1, "mse8": 1e-3},
+    },
+    "rms_norm": {
+        "formula": {"src": "crates/oxicuda-dnn/src/norm/rms_norm.rs:577-603", "x": [1.0, 2.0, 3.0, 4.0], "eps": 1e-5,
+                    "approx": [0.365, 0.730, 1.095, 1.461], "tol": 0.001},
+        "uniform_input": {"src": "crates/oxicuda-dnn/src/norm/rms_norm.rs:649-665", "x": [3.0] * 8, "eps": 1e-8,
+                          "y": 1.0, "tol": 1e-5},
+    },
 }
 
 # inputs that the reference tests build by patching the LCG stream

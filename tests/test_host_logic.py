@@ -131,6 +131,42 @@ def test_python_side_validation_mirrors_reference_errors(libb2q, kat):
     assert (p.q_max(), p.q_min()) == (kat["minmax"]["q_max_q_min_int8"]["q_max"], kat["minmax"]["q_max_q_min_int8"]["q_min"])
 
 
+def test_kv_cache_host_side_validation(libb2q, kat):
+    """Config and shape checks of the KV-cache mirrors fail before anything touches a device, with the reference's errors."""
+    import torch
+    from oxicuda_b200 import _lib
+    from oxicuda_b200.kv_cache import (KvAxis, KvCacheConfig, KvCacheQuantizer, KvQuantConfig, QuantizedKvCache, quantize_tokens)
+    c = kat["kv_cache"]["config_validates_bits"]
+    for bits in c["ok"]:
+        KvCacheConfig.new(bits, KvAxis.PerToken)
+    for bits in c["bad"]:
+        with pytest.raises(_lib.InvalidBitWidth):
+            KvCacheConfig.new(bits, KvAxis.PerToken)
+    assert KvCacheConfig.keys_int8().axis == KvAxis.PerChannel and KvCacheConfig.values_int8().axis == KvAxis.PerToken
+    q = KvCacheQuantizer(KvCacheConfig.values_int8())
+    with pytest.raises(_lib.EmptyInput):
+        q.quantize(torch.empty(0), 0, 0)
+    with pytest.raises(_lib.DimensionMismatch):
+        q.quantize(torch.ones(10), 3, 4)
+    cache = QuantizedKvCache(torch.zeros(32, dtype=torch.uint8), torch.ones(4), torch.zeros(4), 4, 8, 4, KvAxis.PerToken)
+    c = kat["kv_cache"]["packed_bytes_reflects_bit_width"]
+    assert cache.packed_bytes() == c["bits4_bytes"] and cache.n_groups() == 4
+    cache.bits = 8
+    assert cache.packed_bytes() == c["bits8_bytes"]
+    with pytest.raises(_lib.DimensionMismatch):
+        q.append_token(cache, torch.ones(5))
+    cache.axis = KvAxis.PerChannel
+    with pytest.raises(_lib.InvalidConfig):
+        q.append_token(cache, torch.ones(8))
+    r = kat["kv_quant"]["q_range_signed_and_unsigned"]
+    assert list(KvQuantConfig.new(8, False).q_range()) == r["asym8"] and list(KvQuantConfig.new(8, True).q_range()) == r["sym8"]
+    assert list(KvQuantConfig.new(4, False).q_range()) == r["asym4"] and KvQuantConfig.int8() == KvQuantConfig(8, False)
+    with pytest.raises(_lib.InvalidConfig):
+        KvQuantConfig.new(3, False)
+    with pytest.raises(_lib.InvalidConfig):
+        quantize_tokens(torch.empty(0, 4), KvQuantConfig.int8())
+
+
 def test_rank_coordinates_and_shard_ranges(libb2q):
     from oxicuda_b200 import _lib
     from oxicuda_b200.dist_infer import DistInferHandle, ParallelismConfig, column_shard_rows, row_shard_cols

@@ -230,3 +230,82 @@ def test_nf4_round_trip(oracle):
     assert np.abs(dec - x).max() <= np.abs(x).max() * 0.16
     lut_hit = oracle.nf4_decode(oracle.nf4_encode(np.array([1.0, -1.0] * 32, np.float32), 64)[0], np.ones(1, np.float32), 64)
     assert np.array_equal(lut_hit, np.array([1.0, -1.0] * 32, np.float32))
+
+
+def _kv_lcg(n, seed, amp):
+    from tests.golden.make_reference_kat import lcg
+    return np.array(lcg(n, seed, amp), np.float32)
+
+
+def _kv_rel_err(a, b):
+    """rel_err of crates/oxicuda-quant/src/scheme/kv_cache.rs:298-306"""
+    return float(np.abs(a - b).sum() / max(np.abs(a).sum(), 1e-8))
+
+
+def test_kv_cache_pins(oracle, kat):
+    k = kat["kv_cache"]
+    for name in ("int8_per_token_round_trip", "int8_per_channel_round_trip", "int4_round_trip_coarser_but_bounded"):
+        c = k[name]
+        x = _kv_lcg(c["n_tokens"] * c["head_dim"], c["seed"], c["amp"])
+        codes, s, z = oracle.kv_cache_quantize(x, c["n_tokens"], c["head_dim"], c["bits"], c["axis"])
+        assert len(s) == len(z) == c["n_groups"] and int(codes.max()) <= (1 << c["bits"]) - 1
+        deq = oracle.kv_cache_dequantize(codes, c["n_tokens"], c["head_dim"], c["axis"], s, z)
+        assert _kv_rel_err(x, deq) < c["rel_err"], name
+    c = k["per_channel_beats_per_token_on_key_outliers"]
+    x = _kv_lcg(c["n_tokens"] * c["head_dim"], c["seed"], c["amp"]).reshape(c["n_tokens"], c["head_dim"])
+    x[:, c["outlier_col"]] = np.float32(c["outlier_base"]) + np.arange(c["n_tokens"], dtype=np.float32) * np.float32(c["outlier_step"])
+    errs = []
+    for axis in (1, 0):
+        codes, s, z = oracle.kv_cache_quantize(x, c["n_tokens"], c["head_dim"], 8, axis)
+        errs.append(_kv_rel_err(x.reshape(-1), oracle.kv_cache_dequantize(codes, c["n_tokens"], c["head_dim"], axis, s, z)))
+    assert errs[0] < errs[1]
+    c = k["append_token_grows_cache"]           # append_token == the per-token rule on one more row
+    x = _kv_lcg(c["n_tokens"] * c["head_dim"], c["seed"], c["amp"])
+    row = _kv_lcg(c["head_dim"], c["row_seed"], c["amp"])
+    codes, s, z = oracle.kv_cache_quantize(x, c["n_tokens"], c["head_dim"], 8, 0)
+    rc, rs, rz = oracle.kv_cache_quantize(row, 1, c["head_dim"], 8, 0)
+    both = oracle.kv_cache_quantize(np.concatenate([x, row]), c["n_tokens"] + 1, c["head_dim"], 8, 0)
+    assert np.array_equal(np.concatenate([codes, rc]), both[0]) and np.array_equal(np.concatenate([s, rs]), both[1])
+    assert _kv_rel_err(row, oracle.kv_cache_dequantize(rc, 1, c["head_dim"], 0, rs, rz)) < c["rel_err"]
+
+
+def test_kv_quant_token_pins(oracle, kat):
+    k = kat["kv_quant"]
+    c = k["asymmetric_endpoints_exact"]
+    x = np.array(c["x"], np.float32)
+    codes, s, z = oracle.kv_quantize_tokens(x, 1, x.size, 8, False)
+    r = oracle.kv_dequantize_tokens(codes, 1, x.size, s, z)
+    assert z[0] == c["zero_point"] and abs(r[0] - x[0]) < c["tol"] and abs(r[-1] - x[-1]) < c["tol"]
+    assert codes.min() == k["q_range_signed_and_unsigned"]["asym8"][0] and codes.max() == k["q_range_signed_and_unsigned"]["asym8"][1]
+    c = k["symmetric_zero_point_is_zero"]
+    x = np.array(c["x"], np.float32)
+    codes, s, z = oracle.kv_quantize_tokens(x, 1, x.size, 8, True)
+    r = oracle.kv_dequantize_tokens(codes, 1, x.size, s, z)
+    assert z[0] == c["zero_point"] and float(((x - r).astype(np.float64) ** 2).mean()) < c["mse"]
+    assert [int(codes.min()), int(codes.max())] == k["q_range_signed_and_unsigned"]["sym8"]
+    c = k["constant_vector_zero_error"]
+    x = np.array(c["x"], np.float32)
+    codes, s, z = oracle.kv_quantize_tokens(x, 1, x.size, 8, False)
+    assert np.abs(oracle.kv_dequantize_tokens(codes, 1, x.size, s, z) - x).max() < c["tol"]
+    c = k["mse_decreases_with_precision_on_smooth_signal"]
+    x = np.cos(np.arange(c["n"], dtype=np.float32) * np.float32(c["step"])).astype(np.float32)
+    mse = []
+    for bits in (4, 8):
+        codes, s, z = oracle.kv_quantize_tokens(x, 1, x.size, bits, False)
+        assert codes.max() <= (1 << bits) - 1 and codes.min() >= 0
+        mse.append(float(((x - oracle.kv_dequantize_tokens(codes, 1, x.size, s, z)).astype(np.float64) ** 2).mean()))
+    assert mse[1] <= mse[0] and mse[1] < c["mse8"]
+
+
+def test_rms_norm_pins(oracle, kat):
+    c = kat["rms_norm"]["formula"]
+    y = oracle.rms_norm(c["x"], np.ones(len(c["x"]), np.float32), 1, len(c["x"]), c["eps"])
+    assert np.abs(y - np.array(c["approx"], np.float32)).max() < c["tol"]
+    c = kat["rms_norm"]["uniform_input"]
+    y = oracle.rms_norm(c["x"], np.ones(len(c["x"]), np.float32), 1, len(c["x"]), c["eps"])
+    assert np.abs(y - c["y"]).max() < c["tol"]
+    # fused residual form: the norm of (residual + x), residual updated in place
+    x = np.array([1.0, -2.0, 0.5, 4.0], np.float32); res = np.array([0.5, 0.5, -1.0, 2.0], np.float32)
+    g = np.array([1.0, 2.0, 0.5, 1.5], np.float32)
+    y, new_res = oracle.rms_norm(x, g, 1, 4, 1e-6, residual=res)
+    assert np.array_equal(new_res, x + res) and np.array_equal(y, oracle.rms_norm(x + res, g, 1, 4, 1e-6))
