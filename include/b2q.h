@@ -169,11 +169,13 @@ int32_t b2q_distfp8_dequantize_block_f32(b2q_handle h, const uint8_t* q, int64_t
 
 /* ---- RMSNorm fused with the per-token FP8 quantizer of the next linear ----
  * y = x / sqrt(mean(x^2) + eps) * gamma per row (rms_norm, crates/oxicuda-dnn/src/norm/rms_norm.rs:29-33, CPU statement
- * :566-574), then scale = absmax(y)/max_val per row and code = encode(y/scale) exactly as b2q_fp8_quantize_rows_bf16
- * would compute them from y in f32.  x, gamma: bf16.  residual (optional, bf16 [rows x cols], updated in place) selects
+ * :566-574), then the per-token rule of b2q_fp8_quantize_rows_bf16 on y in f32: scale = absmax(y)/max_val per row,
+ * code = encode(y/scale).  x, gamma: bf16.  residual (optional, bf16 [rows x cols], updated in place) selects
  * fused_add_rms_norm (rms_norm.rs:98-103): residual = bf16(residual + x) and the norm is taken of the stored sum.
- * y_out (optional, bf16) also receives the normalised activations.  The f32 sum of squares is a tree sum, so y can
- * differ from the reference's sequential sum in the last bits (the reference's own GPU kernel uses rsqrt.approx). */
+ * y_out (optional, bf16) also receives the normalised activations.  Floating-point path, not bit-exact: the f32 sum
+ * of squares is a tree sum and the two divisions are multiplications by correctly rounded reciprocals (the
+ * reference's own GPU kernel uses rsqrt.approx), so y is within a few f32 ulp of the CPU statement and a code can
+ * differ from the two-kernel composition where y/scale falls on an FP8 rounding boundary. */
 int32_t b2q_rms_norm_quantize_fp8_bf16(b2q_handle h, const void* x_bf16, void* residual_bf16, const void* gamma_bf16,
                                        int64_t rows, int64_t cols, float eps, int fmt, int rounding, float* scales,
                                        uint8_t* codes, void* y_out_bf16);

@@ -53,17 +53,107 @@ __device__ __forceinline__ KvParams kv_params(int rule, float mn, float mx, floa
 }
 
 // One code: round((v - zp) / scale) half away from zero, clamped to [qmin, qmax]; NaN gives 0 before the clamp
-// (Rust's saturating `as` casts), so the byte is the low 8 bits of the clamped integer.
-__device__ __forceinline__ uint32_t kv_code(float v, KvParams p, int qmin, int qmax) {
-  const float q = roundf(__fdiv_rn(__fsub_rn(v, p.zp), p.scale));
-  int qi = __float2int_rz(q);          // q is integral; saturates, NaN -> 0
+// (Rust's saturating `as` casts), so the byte is the low 8 bits of the clamped integer.  The exact statement is
+//   qi = __float2int_rz(roundf(__fdiv_rn(__fsub_rn(v, zp), scale)))   (integral value; the cast saturates, NaN -> 0);
+// the code below reaches the same integer with one multiplication instead of the IEEE division where that is provable.
+// inv = RN(1 / scale) (or NaN when the scale is outside [1e-30, 1e30]), so a * inv lies within 2 ulp of RN(a / scale).
+// When that product is further than 3e-4 (> 4 ulp below 1024) from every half-integer, it and the exact quotient
+// lie strictly between the same two half-integers and round to the same integer under any tie rule.  Everything
+// else (near ties, |q| >= 1024, NaN, unusable reciprocal) takes the exact path.
+__device__ __forceinline__ float kv_inv_scale(float scale) {
+  return (scale > 1e-30f && scale < 1e30f) ? __frcp_rn(scale) : __uint_as_float(0x7FC00000u);
+}
+__device__ __forceinline__ uint32_t kv_code_exact(float v, float scale, float zp, int qmin, int qmax) {
+  int qi = __float2int_rz(roundf(__fdiv_rn(__fsub_rn(v, zp), scale)));
   qi = qi < qmin ? qmin : (qi > qmax ? qmax : qi);
   return (uint32_t)qi & 0xFFu;
 }
+__device__ __forceinline__ uint32_t kv_code_fast(float v, KvParams p, float inv, int qmin, int qmax) {
+  const float a = __fsub_rn(v, p.zp);
+  const float q = __fmul_rn(a, inv);
+  int qi = __float2int_rn(q);
+  const float d = __fsub_rn(q, (float)qi);
+  if (!(fabsf(d) < 0.4997f && fabsf(q) < 1024.0f)) return kv_code_exact(v, p.scale, p.zp, qmin, qmax);
+  qi = qi < qmin ? qmin : (qi > qmax ? qmax : qi);
+  return (uint32_t)qi & 0xFFu;
+}
+// Four codes packed into a word, all on full-rate pipes.  q is clamped to [qmin, qmax] as a float, then
+// t = clamp + 1.5 * 2^23 holds round-to-nearest(clamp) in its low mantissa bits (the low byte of t is the code, in
+// two's complement for negative ones).  The distance d = q - (t - 1.5 * 2^23) is measured from the unclamped q, so a
+// quotient outside the range, next to a tie, NaN or infinite fails |d| < 0.4997 and sends the four elements down the
+// exact path.
+__device__ __forceinline__ uint32_t kv_codes4(const float (&v)[4], const float (&scale)[4], const float (&zp)[4], const float (&inv)[4],
+                                              int qmin, int qmax) {
+  const float magic = 12582912.0f, lo = (float)qmin, hi = (float)qmax;
+  uint32_t t[4];
+  bool ok = true;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const float q = __fmul_rn(__fsub_rn(v[e], zp[e]), inv[e]);
+    const float tf = __fadd_rn(fminf(fmaxf(q, lo), hi), magic);
+    ok = ok && (fabsf(__fsub_rn(q, __fsub_rn(tf, magic))) < 0.4997f);
+    t[e] = __float_as_uint(tf);
+  }
+  if (ok) return __byte_perm(__byte_perm(t[0], t[1], 0x0040), __byte_perm(t[2], t[3], 0x0040), 0x5410);
+  return kv_code_exact(v[0], scale[0], zp[0], qmin, qmax) | (kv_code_exact(v[1], scale[1], zp[1], qmin, qmax) << 8) |
+         (kv_code_exact(v[2], scale[2], zp[2], qmin, qmax) << 16) | (kv_code_exact(v[3], scale[3], zp[3], qmin, qmax) << 24);
+}
+__device__ __forceinline__ uint32_t kv_codes4(const float (&v)[4], KvParams p, float inv, int qmin, int qmax) {
+  const float s[4] = {p.scale, p.scale, p.scale, p.scale}, z[4] = {p.zp, p.zp, p.zp, p.zp}, n[4] = {inv, inv, inv, inv};
+  return kv_codes4(v, s, z, n, qmin, qmax);
+}
 
 // ---------------------------------------------------------------------------
-// One group per token: a warp per row, statistics and codes in one launch.  The second pass re-reads the row from
-// L1/L2 (a row is at most a few KB), so DRAM sees each input byte once.
+// One group per token, rows of at most 1024 elements (every head dimension in use).  G lanes share a row, so a warp
+// works on 32 / G rows at a time; a lane keeps NV chunks of 4 elements (chunk lane_in_group + G * k) in registers, so
+// each input byte is read once, NV 16-byte loads are in flight per lane, the reduction takes log2(G) shuffle rounds
+// and the parameters are derived once per 4 * NV elements of a lane.
+// ---------------------------------------------------------------------------
+template <typename T, int G, int NV>
+__global__ void __launch_bounds__(kThreads) kv_quantize_per_token_reg_kernel(const T* __restrict__ x, int64_t rows, int64_t cols, int rule,
+                                                                             int qmin, int qmax, uint8_t* __restrict__ codes,
+                                                                             float* __restrict__ scales, float* __restrict__ zps) {
+  constexpr int kRowsPerWarp = 32 / G;
+  const int lane = threadIdx.x & 31, sub = lane % G, grp = lane / G;
+  const float qmin_f = (float)qmin, qmax_f = (float)qmax;
+  const float nan = __uint_as_float(0x7FC00000u);   // never wins fminf / fmaxf
+  const int64_t warp = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+  for (int64_t r0 = warp * kRowsPerWarp; r0 < rows; r0 += (int64_t)gridDim.x * kWarpsPerBlock * kRowsPerWarp) {
+    const int64_t r = r0 + grp;
+    const bool live = r < rows;
+    float v[NV][4];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t c = (int64_t)(sub + G * k) * 4;
+      if (live && c < cols) ld4<T>(x + r * cols, c, v[k]);
+      else v[k][0] = v[k][1] = v[k][2] = v[k][3] = nan;
+    }
+    float mn = __uint_as_float(0x7F800000u), mx = __uint_as_float(0xFF800000u);
+#pragma unroll
+    for (int k = 0; k < NV; ++k)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) { mn = fminf(mn, v[k][e]); mx = fmaxf(mx, v[k][e]); }
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) {
+      mn = fminf(mn, __shfl_xor_sync(0xffffffffu, mn, o));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    }
+    if (!live) continue;
+    const KvParams p = kv_params(rule, mn, mx, qmin_f, qmax_f);
+    const float inv = kv_inv_scale(p.scale);
+    if (sub == 0) { scales[r] = p.scale; zps[r] = p.zp; }
+    uint8_t* out = codes + r * cols;
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t c = (int64_t)(sub + G * k) * 4;
+      if (c < cols) *reinterpret_cast<uint32_t*>(out + c) = kv_codes4(v[k], p, inv, qmin, qmax);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// One group per token, any row length and alignment: a warp per row, statistics and codes in one launch.  The second
+// pass re-reads the row from L1/L2, so DRAM sees each input byte once.
 // ---------------------------------------------------------------------------
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(kThreads) kv_quantize_per_token_kernel(const T* __restrict__ x, int64_t rows, int64_t cols, int rule,
@@ -79,26 +169,25 @@ __global__ void __launch_bounds__(kThreads) kv_quantize_per_token_kernel(const T
         float v[4];
         ld4<T>(row, i, v);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) { if (v[j] < mn) mn = v[j]; if (v[j] > mx) mx = v[j]; }
+        for (int j = 0; j < 4; ++j) { mn = fminf(mn, v[j]); mx = fmaxf(mx, v[j]); }
       }
     } else {
-      for (int64_t i = lane; i < cols; i += 32) { const float v = ld1<T>(row, i); if (v < mn) mn = v; if (v > mx) mx = v; }
+      for (int64_t i = lane; i < cols; i += 32) { const float v = ld1<T>(row, i); mn = fminf(mn, v); mx = fmaxf(mx, v); }
     }
     mn = warp_min(mn);
     mx = warp_max(mx);
     const KvParams p = kv_params(rule, mn, mx, qmin_f, qmax_f);
+    const float inv = kv_inv_scale(p.scale);
     if (lane == 0) { scales[r] = p.scale; zps[r] = p.zp; }
     uint8_t* out = codes + r * cols;
     if (VEC) {
       for (int64_t i = (int64_t)lane * 4; i < cols; i += 128) {
         float v[4];
         ld4<T>(row, i, v);
-        const uint32_t w = kv_code(v[0], p, qmin, qmax) | (kv_code(v[1], p, qmin, qmax) << 8) | (kv_code(v[2], p, qmin, qmax) << 16) |
-                           (kv_code(v[3], p, qmin, qmax) << 24);
-        *reinterpret_cast<uint32_t*>(out + i) = w;
+        *reinterpret_cast<uint32_t*>(out + i) = kv_codes4(v, p, inv, qmin, qmax);
       }
     } else {
-      for (int64_t i = lane; i < cols; i += 32) out[i] = (uint8_t)kv_code(ld1<T>(row, i), p, qmin, qmax);
+      for (int64_t i = lane; i < cols; i += 32) out[i] = (uint8_t)kv_code_fast(ld1<T>(row, i), p, inv, qmin, qmax);
     }
   }
 }
@@ -133,9 +222,9 @@ __global__ void __launch_bounds__(kThreads) kv_channel_stats_kernel(const T* __r
 #pragma unroll
       for (int j = 0; j < 4; ++j) v[j] = ld1<T>(x, (r + j * kWarpsPerBlock) * cols + c);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) { if (v[j] < mn) mn = v[j]; if (v[j] > mx) mx = v[j]; }
+      for (int j = 0; j < 4; ++j) { mn = fminf(mn, v[j]); mx = fmaxf(mx, v[j]); }
     }
-    for (; r < r1; r += kWarpsPerBlock) { const float v = ld1<T>(x, r * cols + c); if (v < mn) mn = v; if (v > mx) mx = v; }
+    for (; r < r1; r += kWarpsPerBlock) { const float v = ld1<T>(x, r * cols + c); mn = fminf(mn, v); mx = fmaxf(mx, v); }
   }
   s_mn[warp][lane] = mn;
   s_mx[warp][lane] = mx;
@@ -148,19 +237,20 @@ __global__ void __launch_bounds__(kThreads) kv_channel_stats_kernel(const T* __r
   }
 }
 
-__global__ void kv_channel_params_kernel(const uint32_t* keys, int64_t head_dim, float qmax_f, float* scales, float* zps) {
+__global__ void kv_channel_params_kernel(const uint32_t* keys, int64_t head_dim, float qmax_f, float* scales, float* zps, float* inv_scales) {
   const int64_t c = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (c < head_dim) {
     const KvParams p = kv_params(kRuleCache, float_from_order_key(keys[c]), float_from_order_key(keys[head_dim + c]), 0.0f, qmax_f);
     scales[c] = p.scale;
     zps[c] = p.zp;
+    inv_scales[c] = kv_inv_scale(p.scale);
   }
 }
 
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(kThreads) kv_quantize_per_channel_kernel(const T* __restrict__ x, int64_t n, int64_t cols, int qmax,
                                                                            const float* __restrict__ scales, const float* __restrict__ zps,
-                                                                           uint8_t* __restrict__ codes) {
+                                                                           const float* __restrict__ inv_scales, uint8_t* __restrict__ codes) {
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   if (VEC) {   // cols % 4 == 0: four consecutive elements share a row and are four consecutive channels
     for (int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n; i += stride * 4) {
@@ -169,29 +259,57 @@ __global__ void __launch_bounds__(kThreads) kv_quantize_per_channel_kernel(const
       ld4<T>(x, i, v);
       const float4 s = *reinterpret_cast<const float4*>(scales + c);
       const float4 z = *reinterpret_cast<const float4*>(zps + c);
-      const uint32_t w = kv_code(v[0], KvParams{s.x, z.x}, 0, qmax) | (kv_code(v[1], KvParams{s.y, z.y}, 0, qmax) << 8) |
-                         (kv_code(v[2], KvParams{s.z, z.z}, 0, qmax) << 16) | (kv_code(v[3], KvParams{s.w, z.w}, 0, qmax) << 24);
-      *reinterpret_cast<uint32_t*>(codes + i) = w;
+      const float4 n = *reinterpret_cast<const float4*>(inv_scales + c);
+      const float sc[4] = {s.x, s.y, s.z, s.w}, zp[4] = {z.x, z.y, z.z, z.w}, nv[4] = {n.x, n.y, n.z, n.w};
+      *reinterpret_cast<uint32_t*>(codes + i) = kv_codes4(v, sc, zp, nv, 0, qmax);
     }
   } else {
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
       const int64_t c = i % cols;
-      codes[i] = (uint8_t)kv_code(ld1<T>(x, i), KvParams{scales[c], zps[c]}, 0, qmax);
+      codes[i] = (uint8_t)kv_code_fast(ld1<T>(x, i), KvParams{scales[c], zps[c]}, inv_scales[c], 0, qmax);
     }
   }
 }
 
 // code * scale + zero point, unfused (kv_cache.rs:224-238, kv_quant.rs:94-100).  axis 0: group = row, 1: group = column.
+// n = rows * cols.
 template <typename T>
 __global__ void __launch_bounds__(kThreads) kv_dequantize_kernel(const uint8_t* __restrict__ codes, int64_t n, int64_t cols, int axis,
                                                                  int signed_codes, const float* __restrict__ scales,
                                                                  const float* __restrict__ zps, T* __restrict__ out) {
-  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
-    const int64_t g = axis == 0 ? i / cols : i % cols;
-    const uint32_t b = codes[i];
-    const float q = signed_codes ? (float)(int)(int8_t)b : (float)b;
-    st1<T>(out, i, __fadd_rn(__fmul_rn(q, scales[g]), zps[g]));
+  // a warp per row (grid-stride), four codes per lane and step when the rows allow 32-bit code loads
+  const int lane = threadIdx.x & 31;
+  const int64_t rows = n / cols;
+  const bool vec = (cols & 3) == 0 && (reinterpret_cast<uintptr_t>(codes) & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & (4 * sizeof(T) - 1)) == 0;
+  for (int64_t r = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5); r < rows; r += (int64_t)gridDim.x * kWarpsPerBlock) {
+    const uint8_t* crow = codes + r * cols;
+    T* orow = out + r * cols;
+    const float s_row = axis == 0 ? scales[r] : 0.0f, z_row = axis == 0 ? zps[r] : 0.0f;
+    if (vec) {
+      for (int64_t c = (int64_t)lane * 4; c < cols; c += 128) {
+        const uint32_t w = *reinterpret_cast<const uint32_t*>(crow + c);
+        float o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const uint32_t b = (w >> (8 * e)) & 0xFFu;
+          const float q = signed_codes ? (float)(int)(int8_t)b : (float)b;
+          o[e] = __fadd_rn(__fmul_rn(q, axis == 0 ? s_row : scales[c + e]), axis == 0 ? z_row : zps[c + e]);
+        }
+        if constexpr (sizeof(T) == 4) {
+          *reinterpret_cast<float4*>(orow + c) = make_float4(o[0], o[1], o[2], o[3]);
+        } else {
+          const uint32_t lo = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(o[0])) | ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(o[1])) << 16);
+          const uint32_t hi = (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(o[2])) | ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(o[3])) << 16);
+          *reinterpret_cast<uint2*>(orow + c) = make_uint2(lo, hi);
+        }
+      }
+    } else {
+      for (int64_t c = lane; c < cols; c += 32) {
+        const uint32_t b = crow[c];
+        const float q = signed_codes ? (float)(int)(int8_t)b : (float)b;
+        st1<T>(orow, c, __fadd_rn(__fmul_rn(q, axis == 0 ? s_row : scales[c]), axis == 0 ? z_row : zps[c]));
+      }
+    }
   }
 }
 
@@ -204,6 +322,20 @@ template <typename T>
 int32_t kv_quantize_rows(b2q_handle h, const T* x, int64_t rows, int64_t cols, int rule, int qmin, int qmax, uint8_t* codes,
                          float* scales, float* zps) {
   const bool vec = cols % 4 == 0 && (reinterpret_cast<uintptr_t>(x) % (4 * sizeof(T))) == 0 && (reinterpret_cast<uintptr_t>(codes) & 3) == 0;
+  if (vec && cols <= 1024) {
+#define KV_REG_LAUNCH(G, NV)                                                                                                              \
+  kv_quantize_per_token_reg_kernel<T, G, NV><<<grid_cap(h, ceil_div64(rows, kWarpsPerBlock * (32 / G))), kThreads, 0, h->stream>>>(x, rows, cols, rule, \
+                                                                                                                                qmin, qmax, codes, scales, zps)
+    if (cols <= 32) KV_REG_LAUNCH(4, 2);          // G lanes x NV chunks x 4 elements cover the row
+    else if (cols <= 64) KV_REG_LAUNCH(4, 4);
+    else if (cols <= 128) KV_REG_LAUNCH(8, 4);
+    else if (cols <= 256) KV_REG_LAUNCH(16, 4);
+    else if (cols <= 512) KV_REG_LAUNCH(32, 4);
+    else KV_REG_LAUNCH(32, 8);
+#undef KV_REG_LAUNCH
+    B2Q_LAUNCH_CHECK(h, "kv_quantize_per_token_reg_kernel");
+    return B2Q_OK;
+  }
   const int grid = grid_cap(h, ceil_div64(rows, kWarpsPerBlock));
   if (vec) kv_quantize_per_token_kernel<T, true><<<grid, kThreads, 0, h->stream>>>(x, rows, cols, rule, qmin, qmax, codes, scales, zps);
   else kv_quantize_per_token_kernel<T, false><<<grid, kThreads, 0, h->stream>>>(x, rows, cols, rule, qmin, qmax, codes, scales, zps);
@@ -213,8 +345,10 @@ int32_t kv_quantize_rows(b2q_handle h, const T* x, int64_t rows, int64_t cols, i
 
 template <typename T>
 int32_t kv_quantize_channels(b2q_handle h, const T* x, int64_t rows, int64_t cols, int qmax, uint8_t* codes, float* scales, float* zps) {
-  if ((size_t)cols * 2 > kScratchWords) B2Q_FAIL(h, B2Q_ERR_UNSUPPORTED, "kv_cache_quantize: per-channel head_dim %lld above %zu", (long long)cols, kScratchWords / 2);
+  const int64_t cols_pad = (cols + 3) & ~(int64_t)3;   // keeps the reciprocals 16-byte aligned
+  if ((size_t)(2 * cols_pad + cols) > kScratchWords) B2Q_FAIL(h, B2Q_ERR_UNSUPPORTED, "kv_cache_quantize: per-channel head_dim %lld above %zu", (long long)cols, kScratchWords / 3 - 4);
   uint32_t* keys = h->d_scratch;
+  float* inv_scales = reinterpret_cast<float*>(h->d_scratch + 2 * cols_pad);
   kv_channel_keys_init_kernel<<<(unsigned)ceil_div64(cols, kThreads), kThreads, 0, h->stream>>>(keys, cols);
   const int64_t col_blocks = ceil_div64(cols, 32);
   // about 8 blocks per SM over the whole grid, at least 64 rows per block
@@ -224,12 +358,12 @@ int32_t kv_quantize_channels(b2q_handle h, const T* x, int64_t rows, int64_t col
   row_blocks = ceil_div64(rows, rows_per_block);
   if (row_blocks > 65535) { row_blocks = 65535; rows_per_block = ceil_div64(rows, row_blocks); row_blocks = ceil_div64(rows, rows_per_block); }
   kv_channel_stats_kernel<T><<<dim3((unsigned)col_blocks, (unsigned)row_blocks), kThreads, 0, h->stream>>>(x, rows, cols, rows_per_block, keys);
-  kv_channel_params_kernel<<<(unsigned)ceil_div64(cols, kThreads), kThreads, 0, h->stream>>>(keys, cols, (float)qmax, scales, zps);
+  kv_channel_params_kernel<<<(unsigned)ceil_div64(cols, kThreads), kThreads, 0, h->stream>>>(keys, cols, (float)qmax, scales, zps, inv_scales);
   const int64_t n = rows * cols;
   const bool vec = cols % 4 == 0 && (reinterpret_cast<uintptr_t>(x) % (4 * sizeof(T))) == 0 && (reinterpret_cast<uintptr_t>(codes) & 3) == 0 &&
                    (reinterpret_cast<uintptr_t>(scales) & 15) == 0 && (reinterpret_cast<uintptr_t>(zps) & 15) == 0;
-  if (vec) kv_quantize_per_channel_kernel<T, true><<<grid_cap(h, ceil_div64(n, kThreads * 4)), kThreads, 0, h->stream>>>(x, n, cols, qmax, scales, zps, codes);
-  else kv_quantize_per_channel_kernel<T, false><<<grid_cap(h, ceil_div64(n, kThreads)), kThreads, 0, h->stream>>>(x, n, cols, qmax, scales, zps, codes);
+  if (vec) kv_quantize_per_channel_kernel<T, true><<<grid_cap(h, ceil_div64(n, kThreads * 4)), kThreads, 0, h->stream>>>(x, n, cols, qmax, scales, zps, inv_scales, codes);
+  else kv_quantize_per_channel_kernel<T, false><<<grid_cap(h, ceil_div64(n, kThreads)), kThreads, 0, h->stream>>>(x, n, cols, qmax, scales, zps, inv_scales, codes);
   B2Q_LAUNCH_CHECK(h, "kv_quantize_per_channel");
   return B2Q_OK;
 }
@@ -264,7 +398,7 @@ int32_t kv_dequantize_impl(b2q_handle h, const uint8_t* codes, int64_t n_tokens,
   if (axis < 0 || axis > 1) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "kv_cache_dequantize: axis %d", axis);
   if (!codes || !scales || !zps || !out) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "kv_cache_dequantize: null pointer");
   const int64_t n = n_tokens * head_dim;
-  kv_dequantize_kernel<T><<<grid_cap(h, ceil_div64(n, kThreads * 4)), kThreads, 0, h->stream>>>(codes, n, head_dim, axis, signed_codes, scales, zps, out);
+  kv_dequantize_kernel<T><<<grid_cap(h, ceil_div64(n_tokens, kWarpsPerBlock)), kThreads, 0, h->stream>>>(codes, n, head_dim, axis, signed_codes, scales, zps, out);
   B2Q_LAUNCH_CHECK(h, "kv_dequantize_kernel");
   return B2Q_OK;
 }

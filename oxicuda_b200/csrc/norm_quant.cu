@@ -74,7 +74,10 @@ __global__ void __launch_bounds__(1024) rms_norm_quantize_fp8_kernel(const __nv_
     }
   }
   ss = block_reduce(ss, false, sh);
-  const float rms = sqrtf(__fadd_rn(__fdiv_rn(ss, (float)cols), eps));
+  // x * (1 / rms) * gamma and y * (1 / scale): one rounding more than the divisions of the CPU statement (the
+  // reference's own kernel multiplies by rsqrt.approx); an IEEE division per element would make the kernel
+  // instruction-bound instead of HBM-bound.
+  const float inv_rms = __frcp_rn(sqrtf(__fadd_rn(__fdiv_rn(ss, (float)cols), eps)));
   const uint4* gr = reinterpret_cast<const uint4*>(gamma);
   float amax = 0.0f;
 #pragma unroll
@@ -85,7 +88,7 @@ __global__ void __launch_bounds__(1024) rms_norm_quantize_fp8_kernel(const __nv_
       unpack8(gr[c], g);
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        v[k][j] = __fmul_rn(__fdiv_rn(v[k][j], rms), g[j]);
+        v[k][j] = __fmul_rn(__fmul_rn(v[k][j], inv_rms), g[j]);
         amax = fmaxf(amax, fabsf(v[k][j]));
       }
     }
@@ -93,6 +96,7 @@ __global__ void __launch_bounds__(1024) rms_norm_quantize_fp8_kernel(const __nv_
   amax = block_reduce(amax, true, sh);
   const Fp8Fmt F = fp8_fmt(fmt);
   const float scale = amax > 0.0f ? __fdiv_rn(amax, F.max_val) : 1.0f;
+  const float inv_scale = __frcp_rn(scale);
   if (threadIdx.x == 0) scales[r] = scale;
   uint2* cr = reinterpret_cast<uint2*>(codes + r * cols);
   uint4* yr = y_out ? reinterpret_cast<uint4*>(y_out + r * cols) : nullptr;
@@ -101,12 +105,21 @@ __global__ void __launch_bounds__(1024) rms_norm_quantize_fp8_kernel(const __nv_
     const int c = (int)threadIdx.x + k * (int)blockDim.x;
     if (c < chunks) {
       uint32_t lo = 0, hi = 0;
+      if (rounding == 1) {     // the conversion saturates to +-max_val by itself
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        float q = __fdiv_rn(v[k][j], scale);
-        q = q < -F.max_val ? -F.max_val : (q > F.max_val ? F.max_val : q);
-        const uint32_t b = rounding == 0 ? fp8_encode_ref_dev(q, F) : fp8_encode_rne_dev(q, fmt);
-        if (j < 4) lo |= b << (8 * j); else hi |= b << (8 * (j - 4));
+        for (int j = 0; j < 8; j += 2) {
+          const uint32_t b = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(v[k][j], inv_scale), __fmul_rn(v[k][j + 1], inv_scale)),
+                                                                __NV_SATFINITE, fmt == 0 ? __NV_E4M3 : __NV_E5M2);
+          if (j < 4) lo |= b << (8 * j); else hi |= b << (8 * (j - 4));
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float q = __fmul_rn(v[k][j], inv_scale);
+          q = q < -F.max_val ? -F.max_val : (q > F.max_val ? F.max_val : q);
+          const uint32_t b = fp8_encode_ref_dev(q, F);
+          if (j < 4) lo |= b << (8 * j); else hi |= b << (8 * (j - 4));
+        }
       }
       cr[c] = make_uint2(lo, hi);
       if (yr) {
@@ -139,18 +152,19 @@ __global__ void __launch_bounds__(256) rms_norm_quantize_fp8_generic_kernel(cons
     ss = fmaf(v, v, ss);
   }
   ss = block_reduce(ss, false, sh);
-  const float rms = sqrtf(__fadd_rn(__fdiv_rn(ss, (float)cols), eps));
+  const float inv_rms = __frcp_rn(sqrtf(__fadd_rn(__fdiv_rn(ss, (float)cols), eps)));   // same arithmetic as the register kernel
   const __nv_bfloat16* src = res ? res : row;
   float amax = 0.0f;
   for (int64_t i = threadIdx.x; i < cols; i += blockDim.x)
-    amax = fmaxf(amax, fabsf(__fmul_rn(__fdiv_rn(__bfloat162float(src[i]), rms), __bfloat162float(gamma[i]))));
+    amax = fmaxf(amax, fabsf(__fmul_rn(__fmul_rn(__bfloat162float(src[i]), inv_rms), __bfloat162float(gamma[i]))));
   amax = block_reduce(amax, true, sh);
   const Fp8Fmt F = fp8_fmt(fmt);
   const float scale = amax > 0.0f ? __fdiv_rn(amax, F.max_val) : 1.0f;
+  const float inv_scale = __frcp_rn(scale);
   if (threadIdx.x == 0) scales[r] = scale;
   for (int64_t i = threadIdx.x; i < cols; i += blockDim.x) {
-    const float y = __fmul_rn(__fdiv_rn(__bfloat162float(src[i]), rms), __bfloat162float(gamma[i]));
-    float q = __fdiv_rn(y, scale);
+    const float y = __fmul_rn(__fmul_rn(__bfloat162float(src[i]), inv_rms), __bfloat162float(gamma[i]));
+    float q = __fmul_rn(y, inv_scale);
     q = q < -F.max_val ? -F.max_val : (q > F.max_val ? F.max_val : q);
     codes[r * cols + i] = (uint8_t)(rounding == 0 ? fp8_encode_ref_dev(q, F) : fp8_encode_rne_dev(q, fmt));
     if (y_out) y_out[r * cols + i] = __float2bfloat16_rn(y);
