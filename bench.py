@@ -286,6 +286,10 @@ def main():
         if rank == 0:
             try:
                 extras = side_measurements(dev, peaks)
+                try:
+                    extras["quantizers"] = quantizer_measurements(dev, peaks)
+                except Exception as exc:  # noqa: BLE001 - side numbers must never kill the headline line
+                    extras["quantizers"] = {"error": repr(exc)}
             except Exception as exc:                   # side numbers never block the headline line
                 extras = {"error": repr(exc)}
             extras["tp_fp8_mlp_8192_28672"] = tp
@@ -338,6 +342,9 @@ def run_case(case: str, iters: int):
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     kind, *dims = case.split(":")
+    if kind == "quantizers":        # the quantizer table of the extras, alone
+        print(json.dumps(quantizer_measurements(dev, load_peaks()), indent=1))
+        return
     d = [int(v) for v in dims]
     if kind == "gemm_fp8":
         m, n, k = d
@@ -463,6 +470,63 @@ def tp_mlp_measurements(dev, rank, world):
         flops = 6.0 * tokens * hidden * ffn
         res[f"m{tokens}"] = {"us": sec * 1e6, "timing": timing, "tflops_all_gpus": flops / sec / 1e12,
                              "weight_gbs_per_gpu": 3 * hidden * F / sec / 1e9}
+    return res
+
+
+def quantizer_measurements(dev, peaks):
+    """HBM-bound quantize / dequantize entry points on inputs far larger than L2: µs per call, algorithmic GB/s (input
+    bytes + output bytes + parameters, each counted once) and the fraction of the measured copy peak."""
+    import torch
+    from oxicuda_b200._lib import default_handle, ptr
+    h = default_handle()
+    res = {"timing": "CUDA events around 10 back-to-back calls through the C ABI after 3 warm-up calls; operands of 128-512 MiB"}
+    g = torch.Generator(device=dev).manual_seed(0xB2000007)
+    n = 64 << 20
+    x32 = torch.randn(n, device=dev, generator=g)
+    x16 = x32.to(torch.bfloat16)
+    u8 = torch.empty(n, dtype=torch.uint8, device=dev)
+    i32 = torch.empty(n, dtype=torch.int32, device=dev)
+    f32o = torch.empty(n, dtype=torch.float32, device=dev)
+
+    def run(name, nbytes, fn):
+        try:
+            sec = _time_calls(lambda i: fn(), 10, 3)
+            h.check()
+            res[name] = {"us": sec * 1e6, "gbs": nbytes / sec / 1e9, "frac_of_measured_hbm": nbytes / sec / 1e9 / peaks["hbm_gbs"]}
+        except Exception as exc:  # noqa: BLE001 - keep the remaining rows
+            res[name] = {"error": repr(exc)}
+
+    rows, cols = 8192, 8192
+    sc = torch.empty(1 << 21, device=dev)
+    zp = torch.empty(1 << 21, dtype=torch.int32, device=dev)
+    zpf = torch.empty(1 << 21, device=dev)
+    run("fp8_quantize_rows_bf16_8192x8192", n * 3, lambda: h.call("b2q_fp8_quantize_rows_bf16", ptr(x16), rows, cols, 0, 1, ptr(sc), ptr(u8)))
+    run("fp8_quantize_rows_f32_8192x8192", n * 5, lambda: h.call("b2q_fp8_quantize_rows_f32", ptr(x32), rows, cols, 0, 1, ptr(sc), ptr(u8)))
+    run("fp8_quantize_per_tensor_f32_64M_ref_rounding", n * 5, lambda: h.call("b2q_fp8_quantize_rows_f32", ptr(x32), 1, n, 0, 0, ptr(sc), ptr(u8)))
+    run("fp8_encode_f32_64M", n * 5, lambda: h.call("b2q_fp8_encode_f32", ptr(x32), n, 0, 0, ptr(u8)))
+    run("fp8_decode_f32_64M", n * 5, lambda: h.call("b2q_fp8_decode_f32", ptr(u8), n, 0, 0, ptr(f32o)))
+    h.call("b2q_minmax_calibrate_f32", ptr(x32), n // 128, 128, 8, 0, ptr(sc), ptr(zp))
+    run("minmax_calibrate_f32_group128", n * 4 + n // 16, lambda: h.call("b2q_minmax_calibrate_f32", ptr(x32), n // 128, 128, 8, 0, ptr(sc), ptr(zp)))
+    run("minmax_quantize_f32_group128", n * 8 + n // 16, lambda: h.call("b2q_minmax_quantize_f32", ptr(x32), n // 128, 128, ptr(sc), ptr(zp), 8, 0, ptr(i32)))
+    run("minmax_dequantize_f32_group128", n * 8 + n // 16, lambda: h.call("b2q_minmax_dequantize_f32", ptr(i32), n // 128, 128, ptr(sc), ptr(zp), ptr(f32o)))
+    run("fp4_block_quantize_f32_e8m0", n * 4 + n // 2 + n // 32, lambda: h.call("b2q_fp4_block_quantize_f32", ptr(x32), n, 32, 0, 1, ptr(u8), ptr(sc)))
+    run("fp4_block_quantize_f32_f32scales", n * 4 + n // 2 + n // 8, lambda: h.call("b2q_fp4_block_quantize_f32", ptr(x32), n, 32, 0, 0, ptr(u8), ptr(sc)))
+    run("fp4_block_dequantize_f32_f32scales", n * 4 + n // 2 + n // 8, lambda: h.call("b2q_fp4_block_dequantize_f32", ptr(u8), n, 32, 0, 0, ptr(sc), ptr(f32o)))
+    run("nf4_encode_f32_block64", n * 4 + n // 2 + n // 16, lambda: h.call("b2q_nf4_encode_f32", ptr(x32), n, 64, ptr(u8), ptr(sc)))
+    run("nf4_decode_f32_block64", n * 4 + n // 2 + n // 16, lambda: h.call("b2q_nf4_decode_f32", ptr(u8), n // 2, 64, ptr(sc), ptr(f32o)))
+    run("int8_quant_f32", n * 5, lambda: h.call("b2q_int8_quant_f32", ptr(x32), n, 0.03, ptr(u8)))
+    run("int8_dequant_f32", n * 5, lambda: h.call("b2q_int8_dequant_f32", ptr(u8), n, 0.03, ptr(f32o)))
+    run("distfp8_quantize_block_f32_block128", n * 5 + n // 32, lambda: h.call("b2q_distfp8_quantize_block_f32", ptr(x32), n, 128, ptr(u8), ptr(sc)))
+    run("fake_quant_inplace_f32", n * 8, lambda: h.call("b2q_fake_quant_inplace_f32", ptr(f32o), n, 0.03, 0.0, -128.0, 127.0))
+    tokens, hd = n // 128, 128
+    run("kv_cache_quantize_per_token_bf16_d128", n * 3 + tokens * 8, lambda: h.call("b2q_kv_cache_quantize_bf16", ptr(x16), tokens, hd, 8, 0, ptr(u8), ptr(sc), ptr(zpf)))
+    run("kv_cache_quantize_per_token_f32_d128", n * 5 + tokens * 8, lambda: h.call("b2q_kv_cache_quantize_f32", ptr(x32), tokens, hd, 8, 0, ptr(u8), ptr(sc), ptr(zpf)))
+    run("kv_cache_quantize_per_channel_bf16_d128", n * 3, lambda: h.call("b2q_kv_cache_quantize_bf16", ptr(x16), tokens, hd, 8, 1, ptr(u8), ptr(sc), ptr(zpf)))
+    run("kv_cache_dequantize_per_token_bf16_d128", n * 3 + tokens * 8, lambda: h.call("b2q_kv_cache_dequantize_bf16", ptr(u8), tokens, hd, 0, ptr(sc), ptr(zpf), ptr(x16)))
+    gamma = torch.ones(cols, dtype=torch.bfloat16, device=dev)
+    res16 = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+    run("rms_norm_quantize_fp8_bf16_8192x8192", n * 3, lambda: h.call("b2q_rms_norm_quantize_fp8_bf16", ptr(x16), None, ptr(gamma), rows, cols, 1e-6, 0, 1, ptr(sc), ptr(u8), None))
+    run("rms_norm_quantize_fp8_bf16_residual_8192x8192", n * 7, lambda: h.call("b2q_rms_norm_quantize_fp8_bf16", ptr(x16), ptr(res16), ptr(gamma), rows, cols, 1e-6, 0, 1, ptr(sc), ptr(u8), None))
     return res
 
 
