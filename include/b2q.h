@@ -209,6 +209,31 @@ int32_t b2q_kv_dequantize_tokens_f32(b2q_handle h, const uint8_t* codes, int64_t
 int32_t b2q_kv_dequantize_tokens_bf16(b2q_handle h, const uint8_t* codes, int64_t n_tokens, int64_t d, int symmetric,
                                       const float* scales, const float* zero_points, void* out_bf16);
 
+/* ---- oxicuda-dnn quantize: crates/oxicuda-dnn/src/quantize/ (the statements its GPU tests check bit for bit,
+ * crates/oxicuda-dnn/src/gpu_tests/quantize.rs:184-325, :503-554) ---- */
+/* quantize_to_fp8 (fp8_quantize.rs:45-122): scale[0] = max(absmax / 448, 1e-12); code = E4M3(clamp(x / scale, +-448))
+ * with ties to even and saturation to 0x7E.  n = 0 is a no-op, as in the reference. */
+int32_t b2q_dnn_quantize_to_fp8_f32(b2q_handle h, const float* x, int64_t n, uint8_t* codes, float* scale);
+/* dequantize_from_fp8 (:125-170): out = e4m3(code) * scale[0]; subnormal codes are m / 512. */
+int32_t b2q_dnn_dequantize_from_fp8_f32(b2q_handle h, const uint8_t* codes, const float* scale, int64_t n, float* out);
+/* quantize_to_int8 (int8_quantize.rs:31-102): scale[0] = max(absmax / 127, 1e-12); q = rne(clamp(x / scale, +-127)). */
+int32_t b2q_dnn_quantize_to_int8_f32(b2q_handle h, const float* x, int64_t n, int8_t* q, float* scale);
+/* dequantize_from_int8 (:105-160): out = q * scale[0]. */
+int32_t b2q_dnn_dequantize_from_int8_f32(b2q_handle h, const int8_t* q, const float* scale, int64_t n, float* out);
+/* quantize_block_scaled (block_scale.rs:51-150): per block of block_size (a power of two >= 16, else
+ * B2Q_ERR_INVALID_ARGUMENT) scale = max(absmax / 6, 1e-12); byte = clamp(rne(clamp(x / scale, +-6)) + 6, 0, 255);
+ * ceil(n / block_size) scales. */
+int32_t b2q_dnn_quantize_block_scaled_f32(b2q_handle h, const float* x, int64_t n, uint32_t block_size, uint8_t* out,
+                                          float* scales);
+/* BlockQuantizedInt8::{quantize,dequantize} (int8_quantize.rs:427-470): scale = absmax / 127 (1 for a zero block),
+ * q = round_half_away(x / scale) clamped to [-128, 127]; the last block may be short. */
+int32_t b2q_block_int8_quantize_f32(b2q_handle h, const float* x, int64_t n, int64_t block_size, int8_t* q, float* scales);
+int32_t b2q_block_int8_dequantize_f32(b2q_handle h, const int8_t* q, const float* scales, int64_t n, int64_t block_size,
+                                      float* out);
+/* Fp4BlockQuantizer::compute_scale (block_scale.rs:437-444) for every block: absmax / max_val, 1 for a zero block. */
+int32_t b2q_block_absmax_scale_f32(b2q_handle h, const float* x, int64_t n, int64_t block_size, float max_val,
+                                   float* scales);
+
 /* ---- LlmInt8Quantizer::matmul: crates/oxicuda-quant/src/scheme/llm_int8.rs:175-288 ----
  * x [samples x cols] f32, w [rows x cols] f32 -> out [samples x rows] f32.  Per-row INT8 of W and per-token
  * (row_wise != 0) or per-tensor INT8 of X over the non-outlier columns, exact integer accumulation,

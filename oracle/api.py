@@ -342,6 +342,64 @@ def rms_norm(x, gamma, rows, cols, eps, residual=None):
     return y if residual is None else (y, res)
 
 
+# ---- oxicuda-dnn quantize ----
+def dnn_quantize_to_fp8(x):
+    x = _f32(x).reshape(-1)
+    codes, scale = np.zeros(x.size, np.uint8), np.zeros(1, np.float32)
+    lib().orc_dnn_quantize_to_fp8(_p(x), _i64(x.size), _p(codes), _p(scale))
+    return codes, scale
+
+
+def dnn_dequantize_from_fp8(codes, scale):
+    codes = np.ascontiguousarray(codes, np.uint8).reshape(-1)
+    out = np.zeros(codes.size, np.float32)
+    lib().orc_dnn_dequantize_from_fp8(_p(codes), C.c_float(float(scale)), _i64(codes.size), _p(out))
+    return out
+
+
+def dnn_quantize_to_int8(x):
+    x = _f32(x).reshape(-1)
+    q, scale = np.zeros(x.size, np.int8), np.zeros(1, np.float32)
+    lib().orc_dnn_quantize_to_int8(_p(x), _i64(x.size), _p(q), _p(scale))
+    return q, scale
+
+
+def dnn_dequantize_from_int8(q, scale):
+    q = np.ascontiguousarray(q, np.int8).reshape(-1)
+    out = np.zeros(q.size, np.float32)
+    lib().orc_dnn_dequantize_from_int8(_p(q), C.c_float(float(scale)), _i64(q.size), _p(out))
+    return out
+
+
+def dnn_quantize_block_scaled(x, block):
+    x = _f32(x).reshape(-1)
+    out, scales = np.zeros(x.size, np.uint8), np.zeros(-(-x.size // block), np.float32)
+    lib().orc_dnn_quantize_block_scaled(_p(x), _i64(x.size), _i64(block), _p(out), _p(scales))
+    return out, scales
+
+
+def block_int8_quantize(x, block):
+    x = _f32(x).reshape(-1)
+    q, scales = np.zeros(x.size, np.int8), np.zeros(-(-x.size // block), np.float32)
+    lib().orc_block_int8_quantize(_p(x), _i64(x.size), _i64(block), _p(q), _p(scales))
+    return q, scales
+
+
+def block_int8_dequantize(q, scales, block):
+    q = np.ascontiguousarray(q, np.int8).reshape(-1)
+    scales = _f32(scales)
+    out = np.zeros(q.size, np.float32)
+    lib().orc_block_int8_dequantize(_p(q), _p(scales), _i64(q.size), _i64(block), _p(out))
+    return out
+
+
+def block_absmax_scale(x, block, max_val=6.0):
+    x = _f32(x).reshape(-1)
+    scales = np.zeros(-(-x.size // block), np.float32)
+    lib().orc_block_absmax_scale(_p(x), _i64(x.size), _i64(block), C.c_float(max_val), _p(scales))
+    return scales
+
+
 def classify_workload(m, n, k):
     return int(lib().orc_classify_workload(C.c_uint32(m), C.c_uint32(n), C.c_uint32(k)))
 

@@ -778,6 +778,92 @@ void orc_rms_norm(const float* x, float* residual, const float* gamma, int64_t r
 }
 
 // ---------------------------------------------------------------------------
+// oxicuda-dnn quantize — crates/oxicuda-dnn/src/quantize/{fp8_quantize,int8_quantize,block_scale}.rs, in the form the
+// reference's GPU tests state them (crates/oxicuda-dnn/src/gpu_tests/quantize.rs).
+// ---------------------------------------------------------------------------
+// rne (gpu_tests/quantize.rs:47-60): round to nearest, ties to even; NaN comes back as NaN.
+static float dnn_rne(float x) {
+  const float f = std::floor(x), diff = x - f;
+  if (diff < 0.5f) return f;
+  if (diff > 0.5f) return f + 1.0f;
+  // ties (and NaN, whose `f as i64` is 0): even stays
+  const long long fi = std::isnan(f) ? 0 : (long long)f;
+  return fi % 2 == 0 ? f : f + 1.0f;
+}
+// cpu_e4m3_encode (gpu_tests/quantize.rs:64-109): sign | 0x7E from 448 up (NaN included: its bits compare above), zero
+// below 2^-20, otherwise ties-to-even onto the E4M3 grid, which is fp8_encode_rne for finite input.
+static uint8_t dnn_e4m3_encode(float v) {
+  const uint32_t bits = f2u(v);
+  if ((bits & 0x7fffffffu) >= 0x43E00000u) return (uint8_t)(((bits >> 24) & 0x80u) | 0x7Eu);
+  return fp8_encode_rne(v, Fp8Fmt{4, 3, 7, 448.0f, 0x7E});
+}
+// cpu_e4m3_decode (gpu_tests/quantize.rs:112-125)
+static float dnn_e4m3_decode(uint8_t b) {
+  const uint32_t e = (b >> 3) & 0xF, m = b & 7;
+  const float sign = (b & 0x80) ? -1.0f : 1.0f;
+  if (e == 0) return sign * (float)m * (1.0f / 512.0f);
+  return sign * u2f(((e + 120u) << 23) | (m << 20));
+}
+static float dnn_absmax(const float* x, int64_t n) {
+  float m = 0.0f;
+  for (int64_t i = 0; i < n; ++i) m = rmax(m, std::fabs(x[i]));
+  return m;
+}
+// quantize_to_fp8 (fp8_quantize.rs:45-122; checked at gpu_tests/quantize.rs:279-293)
+void orc_dnn_quantize_to_fp8(const float* x, int64_t n, uint8_t* codes, float* scale) {
+  if (n == 0) return;
+  const float s = rmax(dnn_absmax(x, n) / 448.0f, 1e-12f);
+  *scale = s;
+  for (int64_t i = 0; i < n; ++i) codes[i] = dnn_e4m3_encode(rclamp(x[i] / s, -448.0f, 448.0f));
+}
+// dequantize_from_fp8 (fp8_quantize.rs:125-170; gpu_tests/quantize.rs:319-320)
+void orc_dnn_dequantize_from_fp8(const uint8_t* codes, float scale, int64_t n, float* out) {
+  for (int64_t i = 0; i < n; ++i) out[i] = dnn_e4m3_decode(codes[i]) * scale;
+}
+// quantize_to_int8 (int8_quantize.rs:31-102; gpu_tests/quantize.rs:206-219)
+void orc_dnn_quantize_to_int8(const float* x, int64_t n, int8_t* q, float* scale) {
+  if (n == 0) return;
+  const float s = rmax(dnn_absmax(x, n) / 127.0f, 1e-12f);
+  *scale = s;
+  for (int64_t i = 0; i < n; ++i) q[i] = (int8_t)f32_as_i32(dnn_rne(rclamp(x[i] / s, -127.0f, 127.0f)));
+}
+void orc_dnn_dequantize_from_int8(const int8_t* q, float scale, int64_t n, float* out) {
+  for (int64_t i = 0; i < n; ++i) out[i] = (float)q[i] * scale;
+}
+// quantize_block_scaled (block_scale.rs:51-150; gpu_tests/quantize.rs:527-553)
+void orc_dnn_quantize_block_scaled(const float* x, int64_t n, int64_t block, uint8_t* out, float* scales) {
+  for (int64_t b = 0; b * block < n; ++b) {
+    const int64_t lo = b * block, hi = std::min(n, lo + block);
+    const float s = rmax(dnn_absmax(x + lo, hi - lo) / 6.0f, 1e-12f);
+    scales[b] = s;
+    for (int64_t i = lo; i < hi; ++i) {
+      const int32_t q = f32_as_i32(dnn_rne(rclamp(x[i] / s, -6.0f, 6.0f))) + 6;
+      out[i] = (uint8_t)std::min(255, std::max(0, q));
+    }
+  }
+}
+// BlockQuantizedInt8::quantize / dequantize (int8_quantize.rs:427-470)
+void orc_block_int8_quantize(const float* x, int64_t n, int64_t block, int8_t* q, float* scales) {
+  for (int64_t b = 0; b * block < n; ++b) {
+    const int64_t lo = b * block, hi = std::min(n, lo + block);
+    const float m = dnn_absmax(x + lo, hi - lo);
+    const float s = m > 0.0f ? m / 127.0f : 1.0f;
+    scales[b] = s;
+    for (int64_t i = lo; i < hi; ++i) q[i] = (int8_t)f32_as_i32(rclamp(std::round(x[i] / s), -128.0f, 127.0f));
+  }
+}
+void orc_block_int8_dequantize(const int8_t* q, const float* scales, int64_t n, int64_t block, float* out) {
+  for (int64_t i = 0; i < n; ++i) out[i] = (float)q[i] * scales[i / block];
+}
+// Fp4BlockQuantizer::compute_scale (block_scale.rs:437-444) for every block
+void orc_block_absmax_scale(const float* x, int64_t n, int64_t block, float max_val, float* scales) {
+  for (int64_t b = 0; b * block < n; ++b) {
+    const float m = dnn_absmax(x + b * block, std::min(block, n - b * block));
+    scales[b] = m == 0.0f ? 1.0f : m / max_val;
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Tile heuristics — crates/oxicuda-blas/src/precision/fp8_ops.rs:67-87 (classify),
 // :239-304 (Blackwell table), :389-396 (split-K); fp4_fp6_ops.rs:996-1075;
 // int_ops.rs:141-176.  Class ids: 0 SmallSquare, 1 LargeSquare, 2 SkinnyM,

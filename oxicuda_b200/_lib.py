@@ -118,6 +118,14 @@ SIGNATURES = {
     "b2q_kv_quantize_tokens_bf16": (C.c_int32, [_H, _P, _I64, _I64, _I, _I, _P, _P, _P]),
     "b2q_kv_dequantize_tokens_f32": (C.c_int32, [_H, _P, _I64, _I64, _I, _P, _P, _P]),
     "b2q_kv_dequantize_tokens_bf16": (C.c_int32, [_H, _P, _I64, _I64, _I, _P, _P, _P]),
+    "b2q_dnn_quantize_to_fp8_f32": (C.c_int32, [_H, _P, _I64, _P, _P]),
+    "b2q_dnn_dequantize_from_fp8_f32": (C.c_int32, [_H, _P, _P, _I64, _P]),
+    "b2q_dnn_quantize_to_int8_f32": (C.c_int32, [_H, _P, _I64, _P, _P]),
+    "b2q_dnn_dequantize_from_int8_f32": (C.c_int32, [_H, _P, _P, _I64, _P]),
+    "b2q_dnn_quantize_block_scaled_f32": (C.c_int32, [_H, _P, _I64, _U32, _P, _P]),
+    "b2q_block_int8_quantize_f32": (C.c_int32, [_H, _P, _I64, _I64, _P, _P]),
+    "b2q_block_int8_dequantize_f32": (C.c_int32, [_H, _P, _P, _I64, _I64, _P]),
+    "b2q_block_absmax_scale_f32": (C.c_int32, [_H, _P, _I64, _I64, _F, _P]),
     "b2q_fp8_quantize_rows_f32_noalloc": (C.c_int32, [_P, _I64, _I64, _I, _I, _P, _P, _P, _P, C.c_char_p, C.c_size_t]),
     "b2q_fp4_block_quantize_f32": (C.c_int32, [_H, _P, _I64, _I, _I, _I, _P, _P]),
     "b2q_fp4_block_dequantize_f32": (C.c_int32, [_H, _P, _I64, _I, _I, _I, _P, _P]),

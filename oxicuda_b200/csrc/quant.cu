@@ -210,19 +210,49 @@ int32_t launch_row_stats(b2q_handle h, const T* x, int64_t rows, int64_t cols, c
 // ---------------------------------------------------------------------------
 // MinMax quantize / dequantize / fake-quant
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads) minmax_quantize_kernel(const float* x, int64_t n, int64_t cols,
-                                                                   const float* scales, const int32_t* zps,
-                                                                   float q_min, float q_max, int32_t* codes) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    int64_t r = i / cols;
-    float t = roundf(__fadd_rn(__fdiv_rn(x[i], scales[r]), (float)zps[r]));
-    t = t < q_min ? q_min : (t > q_max ? q_max : t);
-    codes[i] = isnan(t) ? 0 : (int32_t)t;
+__device__ __forceinline__ int32_t minmax_code(float v, float scale, float zp, float q_min, float q_max) {
+  float t = roundf(__fadd_rn(__fdiv_rn(v, scale), zp));
+  t = t < q_min ? q_min : (t > q_max ? q_max : t);
+  return isnan(t) ? 0 : (int32_t)t;
+}
+// vec_ok: cols % 4 == 0 and 16-byte aligned pointers, so four consecutive elements share a row
+__global__ void __launch_bounds__(kThreads) minmax_quantize_kernel(const float* __restrict__ x, int64_t n, int64_t cols,
+                                                                   const float* __restrict__ scales, const int32_t* __restrict__ zps,
+                                                                   float q_min, float q_max, int32_t* __restrict__ codes, int vec_ok) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (int64_t)gridDim.x * blockDim.x;
+  if (vec_ok) {
+    const int64_t c4 = cols >> 2;
+    for (int64_t i = tid; i < (n >> 2); i += nth) {
+      const int64_t r = c4 == (n >> 2) ? 0 : i / c4;
+      const float s = scales[r], z = (float)zps[r];
+      const float4 q = reinterpret_cast<const float4*>(x)[i];
+      reinterpret_cast<int4*>(codes)[i] = make_int4(minmax_code(q.x, s, z, q_min, q_max), minmax_code(q.y, s, z, q_min, q_max),
+                                                    minmax_code(q.z, s, z, q_min, q_max), minmax_code(q.w, s, z, q_min, q_max));
+    }
+    return;
+  }
+  for (int64_t i = tid; i < n; i += nth) {
+    const int64_t r = i / cols;
+    codes[i] = minmax_code(x[i], scales[r], (float)zps[r], q_min, q_max);
   }
 }
-__global__ void __launch_bounds__(kThreads) minmax_dequantize_kernel(const int32_t* codes, int64_t n, int64_t cols,
-                                                                     const float* scales, const int32_t* zps, float* out) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+__global__ void __launch_bounds__(kThreads) minmax_dequantize_kernel(const int32_t* __restrict__ codes, int64_t n, int64_t cols,
+                                                                     const float* __restrict__ scales, const int32_t* __restrict__ zps,
+                                                                     float* __restrict__ out, int vec_ok) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (int64_t)gridDim.x * blockDim.x;
+  if (vec_ok) {
+    const int64_t c4 = cols >> 2;
+    for (int64_t i = tid; i < (n >> 2); i += nth) {
+      const int64_t r = c4 == (n >> 2) ? 0 : i / c4;
+      const float s = scales[r];
+      const uint32_t z = (uint32_t)zps[r];
+      const int4 c = reinterpret_cast<const int4*>(codes)[i];
+      reinterpret_cast<float4*>(out)[i] = make_float4(__fmul_rn((float)(int32_t)((uint32_t)c.x - z), s), __fmul_rn((float)(int32_t)((uint32_t)c.y - z), s),
+                                                      __fmul_rn((float)(int32_t)((uint32_t)c.z - z), s), __fmul_rn((float)(int32_t)((uint32_t)c.w - z), s));
+    }
+    return;
+  }
+  for (int64_t i = tid; i < n; i += nth) {
     int64_t r = i / cols;
     int32_t d = (int32_t)((uint32_t)codes[i] - (uint32_t)zps[r]);
     out[i] = __fmul_rn((float)d, scales[r]);
@@ -245,9 +275,11 @@ __global__ void __launch_bounds__(kThreads) fp8_encode_kernel(const T* x, int64_
                                                               int fmt, int rounding, uint8_t* codes, int32_t* status,
                                                               int vec_ok) {
   const Fp8Fmt F = fp8_fmt(fmt);
+  const bool one_slice = cols >= n;               // per-tensor: no row index to derive
+  const float scale0 = SCALED ? scales[0] : 1.0f;
   auto enc1 = [&](float v, int64_t idx) -> uint32_t {
     if (!isfinite(v)) { atomicCAS(status, 0, (int)B2Q_ERR_NON_FINITE_FP8); }
-    if (SCALED) v = __fdiv_rn(v, scales[idx / cols]);
+    if (SCALED) v = __fdiv_rn(v, one_slice ? scale0 : scales[idx / cols]);
     v = v < -F.max_val ? -F.max_val : (v > F.max_val ? F.max_val : v);
     return rounding == 0 ? fp8_encode_ref_dev(v, F) : fp8_encode_rne_dev(v, fmt);
   };
@@ -430,16 +462,30 @@ __global__ void __launch_bounds__(kThreads) nf4_encode_kernel(const float* x, in
 // ---------------------------------------------------------------------------
 // INT8 with a scalar scale (quant: ties-to-even as cvt.rni, clamp +-127)
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads) int8_quant_kernel(const float* x, int64_t n, float scale, int8_t* out) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    float t = rintf(__fdiv_rn(x[i], scale));
-    t = fminf(fmaxf(t, -127.0f), 127.0f);
-    out[i] = (int8_t)(int)t;
-  }
+__device__ __forceinline__ uint32_t int8_quant_one(float v, float scale) {
+  float t = rintf(__fdiv_rn(v, scale));
+  t = fminf(fmaxf(t, -127.0f), 127.0f);
+  return (uint32_t)(int)t & 0xFFu;
 }
-__global__ void __launch_bounds__(kThreads) int8_dequant_kernel(const int8_t* q, int64_t n, float scale, float* out) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
-    out[i] = __fmul_rn((float)q[i], scale);
+__global__ void __launch_bounds__(kThreads) int8_quant_kernel(const float* __restrict__ x, int64_t n, float scale, int8_t* __restrict__ out, int vec_ok) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (int64_t)gridDim.x * blockDim.x;
+  const int64_t n4 = vec_ok ? n >> 2 : 0;
+  for (int64_t i = tid; i < n4; i += nth) {
+    const float4 q = reinterpret_cast<const float4*>(x)[i];
+    reinterpret_cast<uint32_t*>(out)[i] = int8_quant_one(q.x, scale) | (int8_quant_one(q.y, scale) << 8) | (int8_quant_one(q.z, scale) << 16) |
+                                          (int8_quant_one(q.w, scale) << 24);
+  }
+  for (int64_t i = (n4 << 2) + tid; i < n; i += nth) out[i] = (int8_t)int8_quant_one(x[i], scale);
+}
+__global__ void __launch_bounds__(kThreads) int8_dequant_kernel(const int8_t* __restrict__ q, int64_t n, float scale, float* __restrict__ out, int vec_ok) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (int64_t)gridDim.x * blockDim.x;
+  const int64_t n4 = vec_ok ? n >> 2 : 0;
+  for (int64_t i = tid; i < n4; i += nth) {
+    const uint32_t w = reinterpret_cast<const uint32_t*>(q)[i];
+    reinterpret_cast<float4*>(out)[i] = make_float4(__fmul_rn((float)(int8_t)(w & 0xFF), scale), __fmul_rn((float)(int8_t)((w >> 8) & 0xFF), scale),
+                                                    __fmul_rn((float)(int8_t)((w >> 16) & 0xFF), scale), __fmul_rn((float)(int8_t)(w >> 24), scale));
+  }
+  for (int64_t i = (n4 << 2) + tid; i < n; i += nth) out[i] = __fmul_rn((float)q[i], scale);
 }
 
 // ---------------------------------------------------------------------------
@@ -495,6 +541,80 @@ __global__ void __launch_bounds__(1024) fp8_quantize_rows_fused_kernel(const T* 
   }
 }
 
+// Many rows of up to 16384 elements (per-token quantization of a prefill batch): one CTA per row keeps the row in
+// registers (thread t holds chunks t, t + blockDim, ... of 8 elements), so the input is read once and nothing is
+// divided per element but the value itself.  Same arithmetic as the two-kernel path (finish_row, divide, clamp, encode).
+template <typename T> __device__ __forceinline__ void load_chunk8(const T* row, int c, float (&v)[8]);
+template <> __device__ __forceinline__ void load_chunk8<float>(const float* row, int c, float (&v)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(row)[2 * c], b = reinterpret_cast<const float4*>(row)[2 * c + 1];
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void load_chunk8<__nv_bfloat16>(const __nv_bfloat16* row, int c, float (&v)[8]) {
+  const uint4 q = reinterpret_cast<const uint4*>(row)[c];
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { v[2 * j] = __uint_as_float(w[j] << 16); v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u); }
+}
+
+template <typename T, int NCH>
+__global__ void __launch_bounds__(1024) fp8_quantize_rows_reg_kernel(const T* __restrict__ x, int64_t cols, StatArgs a, int fmt, int rounding,
+                                                                     uint8_t* __restrict__ codes) {
+  __shared__ float sh_amax[32];
+  __shared__ int sh_bad[32];
+  const int64_t r = blockIdx.x;
+  const T* row = x + r * cols;
+  const int chunks = (int)(cols >> 3);
+  float v[NCH][8];
+  float amax = 0.0f;
+  int bad = 0;
+#pragma unroll
+  for (int k = 0; k < NCH; ++k) {
+    const int c = (int)threadIdx.x + k * (int)blockDim.x;
+    if (c < chunks) {
+      load_chunk8<T>(row, c, v[k]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { amax = fmaxf(amax, fabsf(v[k][j])); bad |= !isfinite(v[k][j]); }
+    }
+  }
+  amax = warp_max(amax);
+  bad = __any_sync(0xffffffffu, bad);
+  if ((threadIdx.x & 31) == 0) { sh_amax[threadIdx.x >> 5] = amax; sh_bad[threadIdx.x >> 5] = bad; }
+  __syncthreads();
+  const int nw = blockDim.x >> 5;
+  amax = (int)(threadIdx.x & 31) < nw ? sh_amax[threadIdx.x & 31] : 0.0f;
+  bad = (int)(threadIdx.x & 31) < nw ? sh_bad[threadIdx.x & 31] : 0;
+  amax = warp_max(amax);
+  bad = __any_sync(0xffffffffu, bad);
+  if (threadIdx.x == 0) finish_row(a, r, RowStat{0.0f, 0.0f, amax, bad});   // kFp8Scale reads amax and bad only
+  const Fp8Fmt F = fp8_fmt(fmt);
+  const float scale = amax > 0.0f ? __fdiv_rn(amax, F.max_val) : 1.0f;      // finish_row's value
+  uint2* out = reinterpret_cast<uint2*>(codes + r * cols);
+#pragma unroll
+  for (int k = 0; k < NCH; ++k) {
+    const int c = (int)threadIdx.x + k * (int)blockDim.x;
+    if (c < chunks) {
+      uint32_t lo = 0, hi = 0;
+      if (rounding == 1) {   // the conversion saturates at +-max_val, which is what the clamp of the other path does
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          const uint32_t b = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v[k][j], scale), __fdiv_rn(v[k][j + 1], scale)),
+                                                                __NV_SATFINITE, fmt == 0 ? __NV_E4M3 : __NV_E5M2);
+          if (j < 4) lo |= b << (8 * j); else hi |= b << (8 * (j - 4));
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float q = __fdiv_rn(v[k][j], scale);
+          q = q < -F.max_val ? -F.max_val : (q > F.max_val ? F.max_val : q);
+          const uint32_t b = fp8_encode_ref_dev(q, F);
+          if (j < 4) lo |= b << (8 * j); else hi |= b << (8 * (j - 4));
+        }
+      }
+      out[c] = make_uint2(lo, hi);
+    }
+  }
+}
+
 template <typename T>
 int32_t fp8_quantize_rows_impl(b2q_handle h, const T* x, int64_t rows, int64_t cols, int fmt, int rounding,
                                float* scales, uint8_t* codes) {
@@ -502,6 +622,18 @@ int32_t fp8_quantize_rows_impl(b2q_handle h, const T* x, int64_t rows, int64_t c
   if (!x || !scales || !codes) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "fp8_quantize_rows: null pointer");
   if (fmt < 0 || fmt > 1 || rounding < 0 || rounding > 1) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "fp8_quantize_rows: bad format/rounding");
   StatArgs a{kFp8Scale, 0, 0, fp8_fmt(fmt).max_val, scales, nullptr, h->d_status, 1};
+  if (cols % 8 == 0 && cols >= 256 && cols <= 16384 && rows <= 0x7FFFFFFF && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+      (reinterpret_cast<uintptr_t>(codes) & 7) == 0 && (rows >= 64 || cols <= 2048)) {
+    const int64_t chunks = cols >> 3;
+    // 1, 2 or 4 chunks of 8 elements per thread; many rows prefer small CTAs (several per SM)
+    const int nch = chunks <= 128 ? 1 : (chunks <= 512 ? 2 : 4);
+    const int threads = (int)((ceil_div64(chunks, nch) + 31) / 32 * 32);
+    if (nch == 1) fp8_quantize_rows_reg_kernel<T, 1><<<(unsigned)rows, threads, 0, h->stream>>>(x, cols, a, fmt, rounding, codes);
+    else if (nch == 2) fp8_quantize_rows_reg_kernel<T, 2><<<(unsigned)rows, threads, 0, h->stream>>>(x, cols, a, fmt, rounding, codes);
+    else fp8_quantize_rows_reg_kernel<T, 4><<<(unsigned)rows, threads, 0, h->stream>>>(x, cols, a, fmt, rounding, codes);
+    B2Q_LAUNCH_CHECK(h, "fp8_quantize_rows_reg_kernel");
+    return B2Q_OK;
+  }
   if (rows <= 128 && cols >= 2048 && cols <= (1 << 20)) {
     fp8_quantize_rows_fused_kernel<T><<<(unsigned)rows, 1024, 0, h->stream>>>(x, cols, a, fmt, rounding, codes);
     B2Q_LAUNCH_CHECK(h, "fp8_quantize_rows_fused_kernel");
@@ -541,7 +673,9 @@ int32_t b2q_minmax_quantize_f32(b2q_handle h, const float* x, int64_t rows, int6
   float q_max = scheme == 0 ? (float)(1 << (bits - 1)) - 1.0f : (float)(1 << bits) - 1.0f;
   float q_min = scheme == 0 ? -(float)(1 << (bits - 1)) : 0.0f;
   int64_t n = rows * cols;
-  minmax_quantize_kernel<<<grid_for(h, n, kThreads), kThreads, 0, h->stream>>>(x, n, cols, scales, zero_points, q_min, q_max, codes);
+  const int vec_ok = cols % 4 == 0 && ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(codes)) & 15) == 0;
+  minmax_quantize_kernel<<<grid_for(h, n, kThreads * (vec_ok ? 4 : 1)), kThreads, 0, h->stream>>>(x, n, cols, scales, zero_points, q_min, q_max,
+                                                                                               codes, vec_ok);
   B2Q_LAUNCH_CHECK(h, "minmax_quantize_kernel");
   return B2Q_OK;
 }
@@ -552,7 +686,8 @@ int32_t b2q_minmax_dequantize_f32(b2q_handle h, const int32_t* codes, int64_t ro
   if (rows <= 0 || cols <= 0) B2Q_FAIL(h, B2Q_ERR_EMPTY_INPUT, "minmax_dequantize: empty input");
   if (!codes || !scales || !zero_points || !out) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "minmax_dequantize: null pointer");
   int64_t n = rows * cols;
-  minmax_dequantize_kernel<<<grid_for(h, n, kThreads), kThreads, 0, h->stream>>>(codes, n, cols, scales, zero_points, out);
+  const int vec_ok = cols % 4 == 0 && ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(codes)) & 15) == 0;
+  minmax_dequantize_kernel<<<grid_for(h, n, kThreads * (vec_ok ? 4 : 1)), kThreads, 0, h->stream>>>(codes, n, cols, scales, zero_points, out, vec_ok);
   B2Q_LAUNCH_CHECK(h, "minmax_dequantize_kernel");
   return B2Q_OK;
 }
@@ -671,7 +806,8 @@ int32_t b2q_int8_quant_f32(b2q_handle h, const float* x, int64_t n, float scale,
   if (n <= 0) return B2Q_OK;
   if (!(scale > 0.0f) || !isfinite(scale)) B2Q_FAIL(h, B2Q_ERR_INVALID_SCALE, "int8_quant: scale %g", (double)scale);
   if (!x || !out) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "int8_quant: null pointer");
-  int8_quant_kernel<<<grid_for(h, n, kThreads), kThreads, 0, h->stream>>>(x, n, scale, out);
+  const int vec_ok = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) && ((reinterpret_cast<uintptr_t>(out) & 3) == 0);
+  int8_quant_kernel<<<grid_for(h, n, kThreads * 4), kThreads, 0, h->stream>>>(x, n, scale, out, vec_ok);
   B2Q_LAUNCH_CHECK(h, "int8_quant_kernel");
   return B2Q_OK;
 }
@@ -679,7 +815,8 @@ int32_t b2q_int8_dequant_f32(b2q_handle h, const int8_t* q, int64_t n, float sca
   B2Q_REQUIRE_HANDLE(h);
   if (n <= 0) return B2Q_OK;
   if (!q || !out) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "int8_dequant: null pointer");
-  int8_dequant_kernel<<<grid_for(h, n, kThreads), kThreads, 0, h->stream>>>(q, n, scale, out);
+  const int vec_ok = ((reinterpret_cast<uintptr_t>(out) & 15) == 0) && ((reinterpret_cast<uintptr_t>(q) & 3) == 0);
+  int8_dequant_kernel<<<grid_for(h, n, kThreads * 4), kThreads, 0, h->stream>>>(q, n, scale, out, vec_ok);
   B2Q_LAUNCH_CHECK(h, "int8_dequant_kernel");
   return B2Q_OK;
 }

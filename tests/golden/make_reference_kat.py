@@ -166,6 +166,39 @@ KAT = {
         "mse_decreases_with_precision_on_smooth_signal": {"src": "crates/oxicuda-infer/src/cache/kv_quant.rs:284-290",
                                                           "n": 64, "step": 0.1, "mse8": 1e-3},
     },
+    "dnn_quantize": {
+        "lcg": {"src": "crates/oxicuda-dnn/src/gpu_tests/mod.rs:169-189",
+                "rule": "state = state * 6364136223846793005 + 1442695040888963407 (u64); next_u32 = state >> 32; "
+                        "range_f32(lo, hi) = (lo + (hi - lo) * next_u32 / 2^32) as f32"},
+        "int8_quantize_numeric": {"src": "crates/oxicuda-dnn/src/gpu_tests/quantize.rs:184-220",
+                                  "n": 300, "seed": 0x12345678, "lo": -4.0, "hi": 4.0, "qmax": 127.0, "scale_floor": 1e-12,
+                                  "scale_rel": 1e-5, "scale_abs": 1e-9},
+        "int8_dequantize_numeric": {"src": "crates/oxicuda-dnn/src/gpu_tests/quantize.rs:223-250",
+                                    "n": 192, "seed": 0xC0FFEE01, "scale": 0.0375, "rel": 1e-6, "abs": 1e-9},
+        "fp8_quantize_numeric": {"src": "crates/oxicuda-dnn/src/gpu_tests/quantize.rs:256-293",
+                                 "n": 257, "seed": 0xBEEF0042, "lo": -6.0, "hi": 6.0, "qmax": 448.0, "scale_floor": 1e-12,
+                                 "scale_rel": 1e-5, "scale_abs": 1e-9},
+        "fp8_dequantize_numeric": {"src": "crates/oxicuda-dnn/src/gpu_tests/quantize.rs:296-321",
+                                   "scale": 0.031, "rel": 1e-6, "abs": 1e-7},
+        "block_quantize_numeric": {"src": "crates/oxicuda-dnn/src/gpu_tests/quantize.rs:503-554",
+                                   "n": 128, "block": 32, "seed": 0x77772222, "lo": -5.0, "hi": 5.0, "qmax": 6.0,
+                                   "scale_floor": 1e-12, "scale_rel": 1e-5, "scale_abs": 1e-9},
+        "block_size_validation": {"src": "crates/oxicuda-dnn/src/quantize/block_scale.rs:63-73", "bad": [0, 24, 8], "ok": [16, 32, 128]},
+        "block_int8_gptq_dequant_precision": {"src": "crates/oxicuda-dnn/src/quantize/int8_quantize.rs:639-660",
+                                              "data": [-128, 0, 127], "scale": 0.1, "expected": [-12.8, 0.0, 12.7], "tol": 1e-4},
+        "block_int8_round_trip": {"src": "crates/oxicuda-dnn/src/quantize/int8_quantize.rs:525-543",
+                                  "n": 256, "offset": 128.0, "div": 10.0, "block": 64, "tol": 0.05},
+        "block_int8_non_multiple_len": {"src": "crates/oxicuda-dnn/src/quantize/int8_quantize.rs:591-598",
+                                        "n": 100, "block": 64, "num_blocks": 2},
+        "block_int8_max_value_saturation": {"src": "crates/oxicuda-dnn/src/quantize/int8_quantize.rs:601-612",
+                                            "x": [1e30, -1e30, 0.0, 1e30], "block": 4},
+        "block_int8_block_size_100_round_trip": {"src": "crates/oxicuda-dnn/src/quantize/int8_quantize.rs:702-722",
+                                                 "n": 300, "offset": 150.0, "div": 5.0, "block": 100, "num_blocks": 3},
+        "block_int8_zero_input": {"src": "crates/oxicuda-dnn/src/quantize/int8_quantize.rs:571-579", "n": 64, "block": 64},
+        "fp4_block_quantizer": {"src": "crates/oxicuda-dnn/src/quantize/block_scale.rs:497-622",
+                                "ok": [32], "bad": [16, 64], "zeros_scale": 1.0, "six_scale": 1.0, "twelve_scale": 2.0,
+                                "num_scales": [[32, 1], [96, 3], [33, 2], [0, 0]], "max_value": 6.0},
+    },
     "rms_norm": {
         "formula": {"src": "crates/oxicuda-dnn/src/norm/rms_norm.rs:577-603", "x": [1.0, 2.0, 3.0, 4.0], "eps": 1e-5,
                     "approx": [0.365, 0.730, 1.095, 1.461], "tol": 0.001},

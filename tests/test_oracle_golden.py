@@ -309,3 +309,62 @@ def test_rms_norm_pins(oracle, kat):
     g = np.array([1.0, 2.0, 0.5, 1.5], np.float32)
     y, new_res = oracle.rms_norm(x, g, 1, 4, 1e-6, residual=res)
     assert np.array_equal(new_res, x + res) and np.array_equal(y, oracle.rms_norm(x + res, g, 1, 4, 1e-6))
+
+
+class DnnLcg:
+    """Lcg of crates/oxicuda-dnn/src/gpu_tests/mod.rs:169-189."""
+
+    def __init__(self, seed):
+        self.s = seed
+
+    def next_u32(self):
+        self.s = (self.s * 6364136223846793005 + 1442695040888963407) & 0xFFFFFFFFFFFFFFFF
+        return self.s >> 32
+
+    def range_f32(self, lo, hi):
+        return np.float32(lo + (hi - lo) * (self.next_u32() / 4294967296.0))
+
+
+def test_dnn_quantize_pins(oracle, kat):
+    """The oracle run through the assertions of the reference's GPU tests (gpu_tests/quantize.rs:184-325, :503-554)."""
+    import torch
+    k = kat["dnn_quantize"]
+    c = k["int8_quantize_numeric"]
+    lcg = DnnLcg(c["seed"])
+    data = np.array([lcg.range_f32(c["lo"], c["hi"]) for _ in range(c["n"])], np.float32)
+    q, s = oracle.dnn_quantize_to_int8(data)
+    assert s[0] == max(np.float32(np.abs(data).max()) / np.float32(127.0), np.float32(1e-12))
+    assert np.array_equal(q, np.rint(np.clip(data / s[0], -127.0, 127.0)).astype(np.int8))
+    c = k["fp8_quantize_numeric"]
+    lcg = DnnLcg(c["seed"])
+    data = np.array([lcg.range_f32(c["lo"], c["hi"]) for _ in range(c["n"])], np.float32)
+    codes, s = oracle.dnn_quantize_to_fp8(data)
+    assert s[0] == max(np.float32(np.abs(data).max()) / np.float32(448.0), np.float32(1e-12))
+    scaled = torch.from_numpy(np.clip(data / s[0], -448.0, 448.0).astype(np.float32))
+    assert np.array_equal(codes, scaled.to(torch.float8_e4m3fn).view(torch.uint8).numpy())
+    c = k["fp8_dequantize_numeric"]
+    b = np.arange(256, dtype=np.uint8)
+    ref = torch.from_numpy(b).view(torch.float8_e4m3fn).to(torch.float32).numpy()
+    ref[0x7F], ref[0xFF] = 480.0, -480.0
+    assert np.array_equal(oracle.dnn_dequantize_from_fp8(b, c["scale"]), ref * np.float32(c["scale"]))
+    c = k["block_quantize_numeric"]
+    lcg = DnnLcg(c["seed"])
+    data = np.array([lcg.range_f32(c["lo"], c["hi"]) for _ in range(c["n"])], np.float32)
+    out, sc = oracle.dnn_quantize_block_scaled(data, c["block"])
+    assert np.array_equal(sc, np.maximum(np.abs(data).reshape(-1, c["block"]).max(axis=1) / np.float32(6.0), np.float32(1e-12)))
+    assert np.array_equal(out, np.clip(np.rint(np.clip(data / np.repeat(sc, c["block"]), -6.0, 6.0)).astype(np.int32) + 6, 0, 255))
+    c = k["block_int8_gptq_dequant_precision"]
+    deq = oracle.block_int8_dequantize(np.array(c["data"], np.int8), [c["scale"]], 3)
+    assert np.abs(deq - np.array(c["expected"], np.float32)).max() < c["tol"]
+    c = k["block_int8_round_trip"]
+    x = ((np.arange(c["n"], dtype=np.float32) - np.float32(c["offset"])) / np.float32(c["div"])).astype(np.float32)
+    q, sc = oracle.block_int8_quantize(x, c["block"])
+    assert np.abs(oracle.block_int8_dequantize(q, sc, c["block"]) - x).max() < c["tol"] and len(sc) == 4
+    c = k["block_int8_non_multiple_len"]
+    q, sc = oracle.block_int8_quantize(np.arange(c["n"], dtype=np.float32), c["block"])
+    assert len(sc) == c["num_blocks"] and len(q) == c["n"]
+    c = k["fp4_block_quantizer"]
+    assert oracle.block_absmax_scale(np.zeros(32, np.float32), 32)[0] == c["zeros_scale"]
+    assert oracle.block_absmax_scale(np.full(32, 12.0, np.float32), 32)[0] == c["twelve_scale"]
+    for n, want in c["num_scales"]:
+        assert len(oracle.block_absmax_scale(np.ones(n, np.float32), 32)) == want
