@@ -156,7 +156,7 @@ def main():
     ap.add_argument("--rounding", default="rne", choices=["rne", "ref"], help="E4M3 encoder used to make the operands")
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMV / INT8 side measurements")
     ap.add_argument("--case", default=None,
-                    help="run ONE kernel case a few times and exit (for ncu captures): gemm_fp8:M:N:K | gemv_fp4:K:N:tokens | kv_quant:tokens:head_dim:axis:bf16 | rms_quant:rows:cols:residual")
+                    help="run ONE kernel case a few times and exit (for ncu captures): gemm_fp8:M:N:K | gemv_fp4:K:N:tokens | gemv_int4:K:N:tokens:group | kv_quant:tokens:head_dim:axis:bf16 | rms_quant:rows:cols:residual")
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args()
     if args.case:
@@ -361,6 +361,15 @@ def run_case(case: str, iters: int):
         out = torch.empty(tokens, n, dtype=torch.bfloat16, device=dev)
         fn = lambda: gemv_fp4_wo(codes, scales, x, n, k, out=out)
         work, unit = (n * k // 2 + n * k // 32 + 2 * tokens * k + 2 * tokens * n) / 1e9, "GB/s"
+    elif kind == "gemv_int4":       # gemv_int4:K:N:tokens:group
+        from oxicuda_b200.blas import gemv_int4_wo
+        k, n, tokens, group = d
+        packed = torch.randint(-2**31, 2**31 - 1, (n * k // 8,), dtype=torch.int32, device=dev)
+        scales = (torch.rand(n * k // group, device=dev) * 0.01).to(torch.float16)
+        x = torch.randn(tokens, k, device=dev).to(torch.bfloat16)
+        out = torch.empty(tokens, n, dtype=torch.bfloat16, device=dev)
+        fn = lambda: gemv_int4_wo(packed, scales, group, x, n, k, out=out)
+        work, unit = (n * k // 2 + 2 * n * k // group + 2 * tokens * k + 2 * tokens * n) / 1e9, "GB/s"
     elif kind == "kv_quant":        # kv_quant:n_tokens:head_dim:axis:bf16  (KvCacheQuantizer, 8 bits)
         from oxicuda_b200._lib import default_handle, ptr
         tokens, hd, axis, bf16 = d

@@ -234,6 +234,25 @@ int32_t b2q_block_int8_dequantize_f32(b2q_handle h, const int8_t* q, const float
 int32_t b2q_block_absmax_scale_f32(b2q_handle h, const float* x, int64_t n, int64_t block_size, float max_val,
                                    float* scales);
 
+/* ---- INT4 group-scaled weight-only linear: crates/oxicuda-blas/src/precision/int_ops.rs ---- */
+/* pack_int4 (:375-403): eight two's-complement nibbles per u32, value j in bits [4j, 4j+4).  n must be a multiple of 8
+ * (B2Q_ERR_INVALID_ARGUMENT); a value outside [-8, 7] records B2Q_ERR_INVALID_ARGUMENT in the device status word
+ * (read it with b2q_check).  values: int8 on the device, 8-byte aligned. */
+int32_t b2q_pack_int4(b2q_handle h, const int8_t* values, int64_t n, uint32_t* packed);
+/* unpack_int4 (:415-429) for `words` packed words -> 8 * words sign-extended int8. */
+int32_t b2q_unpack_int4(b2q_handle h, const uint32_t* packed, int64_t words, int8_t* out);
+/* The kernel of generate_int4_gemm_ptx (:602-757) with its own operand layout and summation order:
+ * C[m x n] (f32) = dequant(A) * B, A packed [m x k/8] u32, scales f16 [m x k/group_size], B f32 [k x n] row-major;
+ * acc = fma(float(int4) * scale, B[k, col], acc) for k ascending.  Bit-exact against that statement.
+ * Validation as Int4GemmConfig::validate (:250-283). */
+int32_t b2q_gemm_int4_f32(b2q_handle h, const uint32_t* a_packed, const void* scales_f16, const float* b, float* c,
+                          int64_t m, int64_t n, int64_t k, int64_t group_size);
+/* The decode form of the same linear: out[tokens x n] = x[tokens x k] (bf16) * dequant(W)^T, W packed [n x k/8],
+ * scales f16 [n x k/group_size]; tokens <= 32, k % 128 == 0, group_size >= 32 (else B2Q_ERR_UNSUPPORTED).
+ * Activations enter the tensor core as f16 (saturating at +-65504), fp32 accumulation. */
+int32_t b2q_gemv_int4_wo(b2q_handle h, const uint32_t* packed, const void* scales_f16, int64_t group_size,
+                         const void* x_bf16, int64_t tokens, int64_t n, int64_t k, void* out, int out_type);
+
 /* ---- LlmInt8Quantizer::matmul: crates/oxicuda-quant/src/scheme/llm_int8.rs:175-288 ----
  * x [samples x cols] f32, w [rows x cols] f32 -> out [samples x rows] f32.  Per-row INT8 of W and per-token
  * (row_wise != 0) or per-tensor INT8 of X over the non-outlier columns, exact integer accumulation,

@@ -400,6 +400,33 @@ def block_absmax_scale(x, block, max_val=6.0):
     return scales
 
 
+# ---- INT4 group-scaled weight-only GEMM ----
+def pack_int4(values):
+    """Returns (packed u32 array, status): 0 ok, 1 length not a multiple of 8, 2 + i first value out of [-8, 7]."""
+    v = np.ascontiguousarray(values, np.int8).reshape(-1)
+    packed = np.zeros(v.size // 8, np.uint32)
+    lib().orc_pack_int4.restype = C.c_int64
+    st = lib().orc_pack_int4(_p(v), _i64(v.size), _p(packed))
+    return packed, int(st)
+
+
+def unpack_int4(packed):
+    p = np.ascontiguousarray(packed, np.uint32).reshape(-1)
+    out = np.zeros(p.size * 8, np.int8)
+    lib().orc_unpack_int4(_p(p), _i64(p.size), _p(out))
+    return out
+
+
+def gemm_int4(a_packed, scales_f16, b, M, N, K, group):
+    """a_packed u32 [M, K/8], scales float16 [M, K/group], b f32 [K, N] -> c f32 [M, N] in the reference kernel's order."""
+    a = np.ascontiguousarray(a_packed, np.uint32).reshape(-1)
+    sc = np.ascontiguousarray(scales_f16, np.float16).reshape(-1).view(np.uint16)
+    b = _f32(b).reshape(-1)
+    c = np.zeros(M * N, np.float32)
+    lib().orc_gemm_int4(_p(a), _p(sc), _p(b), _p(c), _i64(M), _i64(N), _i64(K), _i64(group))
+    return c.reshape(M, N)
+
+
 def classify_workload(m, n, k):
     return int(lib().orc_classify_workload(C.c_uint32(m), C.c_uint32(n), C.c_uint32(k)))
 

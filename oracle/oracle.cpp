@@ -864,6 +864,59 @@ void orc_block_absmax_scale(const float* x, int64_t n, int64_t block, float max_
 }
 
 // ---------------------------------------------------------------------------
+// INT4 group-scaled weight-only GEMM — crates/oxicuda-blas/src/precision/int_ops.rs
+// ---------------------------------------------------------------------------
+// pack_int4 (:375-403): eight two's-complement nibbles per u32, value j in bits [4j, 4j+4).  Returns 0, 1 when the
+// length is not a multiple of 8, or 2 + index of the first value outside [-8, 7].
+int64_t orc_pack_int4(const int8_t* values, int64_t n, uint32_t* packed) {
+  if (n % 8 != 0) return 1;
+  for (int64_t i = 0; i < n; ++i) if (values[i] < -8 || values[i] > 7) return 2 + i;
+  for (int64_t w = 0; w < n / 8; ++w) {
+    uint32_t p = 0;
+    for (int j = 0; j < 8; ++j) p |= (uint32_t)((uint8_t)values[w * 8 + j] & 0x0F) << (j * 4);
+    packed[w] = p;
+  }
+  return 0;
+}
+// unpack_int4 (:415-429)
+void orc_unpack_int4(const uint32_t* packed, int64_t words, int8_t* out) {
+  for (int64_t w = 0; w < words; ++w)
+    for (int j = 0; j < 8; ++j) {
+      const uint8_t nib = (packed[w] >> (j * 4)) & 0x0F;
+      out[w * 8 + j] = (nib & 0x08) ? (int8_t)(0xF0u | nib) : (int8_t)nib;
+    }
+}
+static float f16_bits_to_f32(uint16_t h) {
+  const uint32_t sign = (uint32_t)(h & 0x8000) << 16, e = (h >> 10) & 0x1F, m = h & 0x3FF;
+  if (e == 0) return u2f(sign) * 0.0f + (sign ? -1.0f : 1.0f) * (float)m * 5.9604644775390625e-8f;   // m * 2^-24
+  if (e == 31) return u2f(sign | 0x7F800000u | (m << 13));
+  return u2f(sign | ((e + 112) << 23) | (m << 13));
+}
+// The kernel of generate_int4_gemm_ptx (:602-757): C[row, col] = sum over k ascending of
+// fma(float(int4[row, k]) * f32(scale_f16[row, k / group]), B[k, col], acc); A packed [M x K/8] u32, scales f16
+// [M x K/group], B f32 [K x N] row-major, C f32 [M x N].
+void orc_gemm_int4(const uint32_t* a_packed, const uint16_t* scales_f16, const float* b, float* c, int64_t M, int64_t N,
+                   int64_t K, int64_t group) {
+  const int64_t groups = K / group, kw = K / 8;
+#pragma omp parallel for schedule(static)
+  for (int64_t row = 0; row < M; ++row)
+    for (int64_t col = 0; col < N; ++col) {
+      float acc = 0.0f;
+      for (int64_t k = 0; k < K; k += 8) {
+        const float scale = f16_bits_to_f32(scales_f16[row * groups + k / group]);
+        const uint32_t w = a_packed[row * kw + k / 8];
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t nib = (w >> (4 * j)) & 0xF;
+          const int32_t v = (nib & 8) ? (int32_t)(nib | 0xFFFFFFF0u) : (int32_t)nib;
+          const float dq = (float)v * scale;
+          acc = std::fmaf(dq, b[(k + j) * N + col], acc);
+        }
+      }
+      c[row * N + col] = acc;
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Tile heuristics — crates/oxicuda-blas/src/precision/fp8_ops.rs:67-87 (classify),
 // :239-304 (Blackwell table), :389-396 (split-K); fp4_fp6_ops.rs:996-1075;
 // int_ops.rs:141-176.  Class ids: 0 SmallSquare, 1 LargeSquare, 2 SkinnyM,

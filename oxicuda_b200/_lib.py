@@ -126,6 +126,10 @@ SIGNATURES = {
     "b2q_block_int8_quantize_f32": (C.c_int32, [_H, _P, _I64, _I64, _P, _P]),
     "b2q_block_int8_dequantize_f32": (C.c_int32, [_H, _P, _P, _I64, _I64, _P]),
     "b2q_block_absmax_scale_f32": (C.c_int32, [_H, _P, _I64, _I64, _F, _P]),
+    "b2q_pack_int4": (C.c_int32, [_H, _P, _I64, _P]),
+    "b2q_unpack_int4": (C.c_int32, [_H, _P, _I64, _P]),
+    "b2q_gemm_int4_f32": (C.c_int32, [_H, _P, _P, _P, _P, _I64, _I64, _I64, _I64]),
+    "b2q_gemv_int4_wo": (C.c_int32, [_H, _P, _P, _I64, _P, _I64, _I64, _I64, _P, _I]),
     "b2q_fp8_quantize_rows_f32_noalloc": (C.c_int32, [_P, _I64, _I64, _I, _I, _P, _P, _P, _P, C.c_char_p, C.c_size_t]),
     "b2q_fp4_block_quantize_f32": (C.c_int32, [_H, _P, _I64, _I, _I, _I, _P, _P]),
     "b2q_fp4_block_dequantize_f32": (C.c_int32, [_H, _P, _I64, _I, _I, _I, _P, _P]),

@@ -221,3 +221,88 @@ def gemm_fp4_wo(codes: torch.Tensor, scales: torch.Tensor, x: torch.Tensor, N: i
     ot = L.OUT_BF16 if out.dtype == torch.bfloat16 else L.OUT_F32
     default_handle().call("b2q_gemm_fp4_wo", ptr(codes), ptr(scales), sf, block, format.value, ptr(x), tokens, N, K, ptr(out), ot)
     return out
+
+
+# ---- INT4 group-scaled weight-only linear: crates/oxicuda-blas/src/precision/int_ops.rs:196-429, :602-757 ----
+@dataclass
+class Int4GemmConfig:
+    """int_ops.rs:215-356"""
+    m: int
+    n: int
+    k: int
+    layout_a: str = "RowMajor"
+    layout_b: str = "RowMajor"
+    group_size: int = 128
+
+    PACKED_ELEMENT_BYTES = 4
+    VALUES_PER_U32 = 8
+    VALID_GROUP_SIZES = (32, 64, 128, 256)
+
+    def validate(self) -> None:
+        """int_ops.rs:250-283 (the architecture check always passes on sm_100)."""
+        if self.m == 0 or self.n == 0 or self.k == 0:
+            raise L.InvalidDimension(L.ERR_INVALID_DIMENSION, f"INT4 GEMM dimensions must be non-zero: m={self.m}, n={self.n}, k={self.k}")
+        if self.k % 8 != 0:
+            raise L.InvalidDimension(L.ERR_INVALID_DIMENSION, f"INT4 GEMM K dimension must be a multiple of 8 for packing, got k={self.k}")
+        if self.group_size == 0 or self.group_size & (self.group_size - 1):
+            raise L.InvalidArgument(L.ERR_INVALID_ARGUMENT, f"INT4 group_size must be a positive power of 2, got {self.group_size}")
+        if self.k % self.group_size != 0:
+            raise L.InvalidArgument(L.ERR_INVALID_ARGUMENT, f"INT4 group_size ({self.group_size}) must divide K ({self.k}) evenly")
+
+    def tile_config(self) -> tuple:
+        """int_ops.rs:296-309, the Hopper/Blackwell row: (tile_m, tile_n, tile_k, warp_m, warp_n, stages, tensor core, split_k)."""
+        return (128, 128, 128, 64, 64, 4, 1, 1)
+
+    def kernel_name(self) -> str:
+        short = {"RowMajor": "r", "ColMajor": "c"}
+        return f"int4_gemm_{self.m}x{self.n}x{self.k}_{short[self.layout_a]}{short[self.layout_b]}_f32_gs{self.group_size}"
+
+    def num_groups(self) -> int:
+        return self.k // self.group_size
+
+    def packed_k(self) -> int:
+        return self.k // self.VALUES_PER_U32
+
+
+def pack_int4(values: torch.Tensor) -> torch.Tensor:
+    """int_ops.rs:375-403: int8 values in [-8, 7], a multiple of 8 of them -> u32 words (as int32 tensors hold them)."""
+    n = values.numel()
+    if n % 8 != 0:
+        raise L.InvalidArgument(L.ERR_INVALID_ARGUMENT, f"pack_int4 requires input length to be a multiple of 8, got {n}")
+    v, was_host = _dev(values.reshape(-1), torch.int8)
+    packed = torch.empty(n // 8, dtype=torch.int32, device=v.device)
+    h = default_handle()
+    h.call("b2q_pack_int4", ptr(v), n, ptr(packed))
+    h.check()                       # a value outside [-8, 7] is detected on the device
+    return _back(packed, was_host)
+
+
+def unpack_int4(packed) -> torch.Tensor:
+    """int_ops.rs:415-429 for one word (an int) or a tensor of words -> int8 values."""
+    if isinstance(packed, int):
+        packed = torch.tensor([packed if packed < (1 << 31) else packed - (1 << 32)], dtype=torch.int32)
+    p, was_host = _dev(packed.reshape(-1), torch.int32)
+    out = torch.empty(p.numel() * 8, dtype=torch.int8, device=p.device)
+    default_handle().call("b2q_unpack_int4", ptr(p), p.numel(), ptr(out))
+    return _back(out, was_host)
+
+
+def gemm_int4(a_packed: torch.Tensor, scales: torch.Tensor, b: torch.Tensor, config: Int4GemmConfig) -> torch.Tensor:
+    """The kernel of generate_int4_gemm_ptx (int_ops.rs:602-757): C[m, n] f32 = dequant(A packed [m, k/8], scales f16
+    [m, k/group]) @ B f32 [k, n], summed over k ascending exactly as the reference kernel does."""
+    config.validate()
+    c = torch.empty(config.m, config.n, dtype=torch.float32, device=a_packed.device)
+    default_handle().call("b2q_gemm_int4_f32", ptr(a_packed), ptr(scales), ptr(b.contiguous()), ptr(c), config.m, config.n, config.k,
+                          config.group_size)
+    return c
+
+
+def gemv_int4_wo(packed: torch.Tensor, scales: torch.Tensor, group_size: int, x: torch.Tensor, N: int, K: int, out: torch.Tensor = None,
+                 out_dtype=torch.bfloat16) -> torch.Tensor:
+    """Decode form: out[tokens, N] = x[tokens, K] (bf16) @ dequant(W[N, K])^T; tokens <= 32, K % 128 == 0, group_size >= 32."""
+    tokens = x.shape[0]
+    if out is None:
+        out = torch.empty(tokens, N, dtype=out_dtype, device=x.device)
+    ot = L.OUT_BF16 if out.dtype == torch.bfloat16 else L.OUT_F32
+    default_handle().call("b2q_gemv_int4_wo", ptr(packed), ptr(scales), group_size, ptr(x.contiguous()), tokens, N, K, ptr(out), ot)
+    return out

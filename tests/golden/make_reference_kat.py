@@ -199,6 +199,23 @@ KAT = {
                                 "ok": [32], "bad": [16, 64], "zeros_scale": 1.0, "six_scale": 1.0, "twelve_scale": 2.0,
                                 "num_scales": [[32, 1], [96, 3], [33, 2], [0, 0]], "max_value": 6.0},
     },
+    "int4": {
+        "pack_unpack_roundtrip": {"src": "crates/oxicuda-blas/src/precision/int_ops.rs:1008-1017",
+                                  "values": [0, 1, -1, 7, -8, 3, -5, 2]},
+        "pack_wrong_length": {"src": "crates/oxicuda-blas/src/precision/int_ops.rs:1020-1023", "values": [0, 1, 2]},
+        "pack_out_of_range": {"src": "crates/oxicuda-blas/src/precision/int_ops.rs:1026-1029", "values": [0, 1, 2, 3, 4, 5, 6, 10]},
+        "unpack_words": {"src": "crates/oxicuda-blas/src/precision/int_ops.rs:1032-1053",
+                         "cases": [[0x00000000, [0] * 8], [0xFFFFFFFF, [-1] * 8], [0x87878787, [7, -8, 7, -8, 7, -8, 7, -8]]]},
+        "config_validation": {"src": "crates/oxicuda-blas/src/precision/int_ops.rs:879-943",
+                              "ok": [[128, 128, 128, 32]],
+                              "bad": [[128, 0, 128, 32], [128, 128, 100, 32], [128, 128, 128, 3], [128, 128, 48, 32]]},
+        "helpers": {"src": "crates/oxicuda-blas/src/precision/int_ops.rs:1065-1088",
+                    "num_groups": [256, 64, 4], "packed_k": [256, 32]},
+        "kernel_name": {"src": "crates/oxicuda-blas/src/precision/int_ops.rs:1110-1123",
+                        "config": [256, 128, 64, "ColMajor", "RowMajor", 32], "contains": ["int4_gemm", "cr", "gs32"]},
+        "tile_config_sm100": {"src": "crates/oxicuda-blas/src/precision/int_ops.rs:296-309",
+                              "tile": [128, 128, 128, 64, 64, 4, 1, 1]},
+    },
     "rms_norm": {
         "formula": {"src": "crates/oxicuda-dnn/src/norm/rms_norm.rs:577-603", "x": [1.0, 2.0, 3.0, 4.0], "eps": 1e-5,
                     "approx": [0.365, 0.730, 1.095, 1.461], "tol": 0.001},

@@ -368,3 +368,24 @@ def test_dnn_quantize_pins(oracle, kat):
     assert oracle.block_absmax_scale(np.full(32, 12.0, np.float32), 32)[0] == c["twelve_scale"]
     for n, want in c["num_scales"]:
         assert len(oracle.block_absmax_scale(np.ones(n, np.float32), 32)) == want
+
+
+def test_int4_pins(oracle, kat):
+    k = kat["int4"]
+    v = k["pack_unpack_roundtrip"]["values"]
+    packed, st = oracle.pack_int4(v)
+    assert st == 0 and packed.size == 1 and list(oracle.unpack_int4(packed)) == v
+    assert oracle.pack_int4(k["pack_wrong_length"]["values"])[1] == 1
+    assert oracle.pack_int4(k["pack_out_of_range"]["values"])[1] == 2 + 7
+    for word, vals in k["unpack_words"]["cases"]:
+        assert list(oracle.unpack_int4([word])) == vals
+    # the GEMM against a float64 statement of dequantize-then-multiply on a small case
+    rng = np.random.default_rng(41)
+    M, N, K, group = 5, 3, 64, 32
+    vals = rng.integers(-8, 8, (M, K)).astype(np.int8)
+    packed, _ = oracle.pack_int4(vals)
+    scales = (rng.uniform(0.01, 0.1, (M, K // group))).astype(np.float16)
+    b = rng.standard_normal((K, N)).astype(np.float32)
+    c = oracle.gemm_int4(packed, scales, b, M, N, K, group)
+    w = vals.astype(np.float64) * np.repeat(scales.astype(np.float64), group, axis=1)
+    assert np.allclose(c, w @ b.astype(np.float64), rtol=1e-5, atol=1e-5)
