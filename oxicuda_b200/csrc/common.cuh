@@ -140,8 +140,11 @@ __device__ __forceinline__ uint32_t e2m1_encode_ref_dev(float value) {
   if (value == 0.0f) return 0;
   uint32_t sign = value < 0.0f ? 8u : 0u;
   float a = fminf(fabsf(value), 6.0f);          // NaN.min(6) == 6, as in the reference
-  uint32_t mag = a < 0.75f ? 0u : a < 1.0f ? 1u : a < 1.5f ? 2u : a < 2.0f ? 3u
-               : a < 3.0f ? 4u : a < 4.0f ? 5u : a < 6.0f ? 6u : 7u;
+  // thresholds 0.75, 1, 1.5, 2, 3, 4, 6: from 1 up they are the floats with one mantissa bit, so truncating the
+  // float to that bit (bits >> 22) counts them: 1.0 -> 254 -> code 2, ..., 6.0 -> 259 -> code 7 (same codes as the
+  // comparison chain for every float; NaN, which fminf turned into 6, ends at 7 either way)
+  const uint32_t top = (__float_as_uint(a) >> 22) - 252u;
+  uint32_t mag = a < 0.75f ? 0u : a < 1.0f ? 1u : (top < 7u ? top : 7u);
   return sign | mag;
 }
 __device__ __forceinline__ uint32_t int4_encode_ref_dev(float value) {

@@ -9,6 +9,7 @@
 //     weights, so the group scale is applied to its fp32 result.
 #include "common.cuh"
 #include <cooperative_groups.h>
+#include <stdlib.h>
 
 namespace cg = cooperative_groups;
 
@@ -111,26 +112,33 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
 
 // The f16 scales of the four blocks of 32 of one 128-wide step of one row: 4, 2 or 1 distinct values for a group size
 // of 32, 64 or >= 128 (gsh = log2 of the group size).
-struct StepScales {
+template <bool WIDE> struct StepScales;          // WIDE: group size 32 (four scales per step); else 64 and up (two or one)
+template <> struct StepScales<true> {
   uint32_t a, b;
-  __device__ __forceinline__ void load(const __half* row_scales, int64_t k, int gsh) {
-    const __half* p = row_scales + (k >> gsh);
-    a = b = 0;
-    if (gsh == 5) { const uint2 v = __ldg(reinterpret_cast<const uint2*>(p)); a = v.x; b = v.y; }
-    else if (gsh == 6) a = __ldg(reinterpret_cast<const uint32_t*>(p));
-    else a = (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(p));
+  __device__ __forceinline__ void load(const __half* row_scales, int64_t k, int) {
+    const uint2 v = __ldg(reinterpret_cast<const uint2*>(row_scales + (k >> 5)));
+    a = v.x; b = v.y;
   }
   __device__ __forceinline__ void clear() { a = b = 0; }
+  __device__ __forceinline__ float get(int j, int) const {
+    return __half2float(__ushort_as_half((unsigned short)(((j < 2 ? a : b) >> (16 * (j & 1))) & 0xFFFFu)));
+  }
+};
+template <> struct StepScales<false> {
+  uint32_t a;
+  __device__ __forceinline__ void load(const __half* row_scales, int64_t k, int gsh) {
+    const __half* p = row_scales + (k >> gsh);
+    a = gsh == 6 ? __ldg(reinterpret_cast<const uint32_t*>(p)) : (uint32_t)__ldg(reinterpret_cast<const unsigned short*>(p));
+  }
+  __device__ __forceinline__ void clear() { a = 0; }
   __device__ __forceinline__ float get(int j, int gsh) const {
-    const int i = gsh == 5 ? j : (gsh == 6 ? j >> 1 : 0);
-    const uint32_t w = i < 2 ? a : b;
-    return __half2float(__ushort_as_half((unsigned short)((w >> (16 * (i & 1))) & 0xFFFFu)));
+    return __half2float(__ushort_as_half((unsigned short)((gsh == 6 && j >= 2 ? a >> 16 : a) & 0xFFFFu)));
   }
 };
 
 // MT: token tiles of 8.  WARPS: warps per CTA, 16 weight rows each.  A cluster of split_k CTAs covers K and adds
 // the partial sums through distributed shared memory.
-template <int MT, int WARPS>
+template <int MT, int WARPS, bool WIDE>
 __global__ void __launch_bounds__(WARPS * 32) gemv_int4_kernel(const uint32_t* __restrict__ packed, const __half* __restrict__ scales, int gsh,
                                                                const __nv_bfloat16* __restrict__ x, int tokens, int64_t N, int64_t K,
                                                                void* out, int out_type, int split_k) {
@@ -156,7 +164,7 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_int4_kernel(const uint32_t* _
   for (int c = c_begin; c < c_end; ++c) {
     const int64_t k0 = (int64_t)c * KC;
     uint32_t wa[4][4], wb[4][4];
-    StepScales sa[4], sb[4];
+    StepScales<WIDE> sa[4], sb[4];
 #pragma unroll
     for (int s = 0; s < 4; ++s) {                        // the HBM stream first
       const int64_t k = k0 + s * 128;
@@ -238,6 +246,167 @@ __global__ void __launch_bounds__(WARPS * 32) gemv_int4_kernel(const uint32_t* _
   if (split_k > 1) cluster.sync();                       // peers may still be reading this CTA's partial sums
 }
 
+// ---------------------------------------------------------------------------
+// Decode kernel for up to 8 tokens.  Instruction issue binds long before HBM, so: a CTA owns 16 weight rows and its WK
+// warps split K into contiguous slices of 512-wide chunks; a warp loads the words and scales of its NEXT chunk into a
+// second register set before it multiplies the current one (HBM loads stay in flight under the MMAs); every warp stages
+// only its own slice of the activations (warp-private shared memory, __syncwarp); one __syncthreads at the end adds the
+// WK partial sums.
+// ---------------------------------------------------------------------------
+template <bool WIDE> struct ChunkRegs {
+  uint32_t wa[4][4], wb[4][4];
+  StepScales<WIDE> sa[4], sb[4];
+};
+// w0 / w1: this lane's word of the chunk's first block of row g / g + 8; k: first K index of the chunk
+template <bool WIDE>
+__device__ __forceinline__ void load_chunk(ChunkRegs<WIDE>& r, const uint8_t* w0, const uint8_t* w1, const __half* s0, const __half* s1, int64_t k,
+                                           int gsh, int steps) {
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+    if (s < steps) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        r.wa[s][j] = ld_stream_u32(w0 + s * 64 + j * 16);
+        r.wb[s][j] = ld_stream_u32(w1 + s * 64 + j * 16);
+      }
+      r.sa[s].load(s0, k + s * 128, gsh);
+      r.sb[s].load(s1, k + s * 128, gsh);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) { r.wa[s][j] = 0; r.wb[s][j] = 0; }
+      r.sa[s].clear();
+      r.sb[s].clear();
+    }
+  }
+}
+template <bool WIDE>
+__device__ __forceinline__ void mul_chunk(const ChunkRegs<WIDE>& r, const uint4* xs_lane, int gsh, float (&acc)[4]) {
+#pragma unroll
+  for (int s = 0; s < 4; ++s) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      uint32_t ha[4], hb[4];
+      cvt_int4x8(r.wa[s][j], ha);
+      cvt_int4x8(r.wb[s][j], hb);
+      const uint4 xv = xs_lane[(s * 4 + j) * 32];          // [block][8 token rows][4 quad lanes]
+      float d[4];
+      mma_f16_zero(d, ha[0], hb[0], ha[1], hb[1], xv.x, xv.y);
+      mma_f16(d, ha[2], hb[2], ha[3], hb[3], xv.z, xv.w);
+      const float fa = r.sa[s].get(j, gsh), fb = r.sb[s].get(j, gsh);
+      acc[0] = fmaf(fa, d[0], acc[0]);
+      acc[1] = fmaf(fa, d[1], acc[1]);
+      acc[2] = fmaf(fb, d[2], acc[2]);
+      acc[3] = fmaf(fb, d[3], acc[3]);
+    }
+  }
+}
+// Activations [tokens x 512] of one chunk into this warp's buffer: f16, in the pair order of cvt_int4x8.
+template <int TOK>
+__device__ __forceinline__ void stage_x_warp(uint4* xs, const __nv_bfloat16* xk, int tokens, int64_t K, int k_left, int lane) {
+  __syncwarp();                                          // the previous chunk's fragment reads are done
+#pragma unroll
+  for (int i = 0; i < 2 * TOK; ++i) {
+    const int p = lane + 32 * i;                         // 64 * TOK pieces of 8 activations
+    const int ttig = p & 3, tok = (p >> 2) & (TOK - 1), blk = p / (4 * TOK);
+    const int k = blk * 32 + ttig * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (tok < tokens && k < k_left) v = __ldg(reinterpret_cast<const uint4*>(xk + (int64_t)tok * K + k));
+    uint4 h;
+    h.x = pack_f16x2(bf16_lo(v.x), bf16_lo(v.z));
+    h.y = pack_f16x2(bf16_hi(v.x), bf16_hi(v.z));
+    h.z = pack_f16x2(bf16_lo(v.y), bf16_lo(v.w));
+    h.w = pack_f16x2(bf16_hi(v.y), bf16_hi(v.w));
+    xs[(blk * 8 + tok) * 4 + ttig] = h;
+  }
+  __syncwarp();
+}
+
+template <int WK, int TOK, bool WIDE>
+__global__ void __launch_bounds__(WK * 32, 512 / (WK * 32)) gemv_int4_small_kernel(const uint32_t* __restrict__ packed, const __half* __restrict__ scales,
+                                                                                   int gsh, const __nv_bfloat16* __restrict__ x, int tokens, int64_t N,
+                                                                                   int64_t K, void* out, int out_type) {
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tig = lane & 3;
+  uint4* xs = reinterpret_cast<uint4*>(smem) + warp * 512;        // [16 blocks][8 tokens][4] x 16 bytes = 8 KiB per warp
+  float* red = reinterpret_cast<float*>(smem);                    // [WK][16 rows][8 tokens], reused after the main loop
+  const int64_t n0 = (int64_t)blockIdx.x * 16;
+  const int64_t r0 = min(n0 + g, N - 1), r1 = min(n0 + g + 8, N - 1);
+  const int chunks_total = (int)((K + KC - 1) / KC), cpw = (chunks_total + WK - 1) / WK;
+  int c = warp * cpw;
+  const int c_end = min(c + cpw, chunks_total);
+  const int total_steps = (int)(K >> 7);
+  const uint8_t* w0 = reinterpret_cast<const uint8_t*>(packed) + r0 * (K >> 1) + tig * 4 + (int64_t)c * (KC / 2);
+  const uint8_t* w1 = reinterpret_cast<const uint8_t*>(packed) + r1 * (K >> 1) + tig * 4 + (int64_t)c * (KC / 2);
+  const __half* s0 = scales + r0 * (K >> gsh);
+  const __half* s1 = scales + r1 * (K >> gsh);
+  const __nv_bfloat16* xk = x + (int64_t)c * KC;
+  int64_t k = (int64_t)c * KC;
+
+  ChunkRegs<WIDE> A, B;
+  if (c < c_end) load_chunk(A, w0, w1, s0, s1, k, gsh, min(4, total_steps - c * 4));
+#pragma unroll
+  for (int i = 0; i < 16; ++i) xs[lane + 32 * i] = make_uint4(0, 0, 0, 0);   // rows of no token stay zero
+  const uint4* xs_lane = xs + g * 4 + tig;
+  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  while (c < c_end) {
+    if (c + 1 < c_end) load_chunk(B, w0 + KC / 2, w1 + KC / 2, s0, s1, k + KC, gsh, min(4, total_steps - (c + 1) * 4));
+    stage_x_warp<TOK>(xs, xk, tokens, K, (int)min((int64_t)KC, K - k), lane);
+    mul_chunk(A, xs_lane, gsh, acc);
+    ++c; w0 += KC / 2; w1 += KC / 2; xk += KC; k += KC;
+    if (c >= c_end) break;
+    if (c + 1 < c_end) load_chunk(A, w0 + KC / 2, w1 + KC / 2, s0, s1, k + KC, gsh, min(4, total_steps - (c + 1) * 4));
+    stage_x_warp<TOK>(xs, xk, tokens, K, (int)min((int64_t)KC, K - k), lane);
+    mul_chunk(B, xs_lane, gsh, acc);
+    ++c; w0 += KC / 2; w1 += KC / 2; xk += KC; k += KC;
+  }
+  __syncthreads();                                       // every warp is done with its activation buffer
+  red[(warp * 16 + g) * 8 + tig * 2 + 0] = acc[0];
+  red[(warp * 16 + g) * 8 + tig * 2 + 1] = acc[1];
+  red[(warp * 16 + g + 8) * 8 + tig * 2 + 0] = acc[2];
+  red[(warp * 16 + g + 8) * 8 + tig * 2 + 1] = acc[3];
+  __syncthreads();
+  for (int e = threadIdx.x; e < 16 * tokens; e += WK * 32) {
+    const int tok = e >> 4, row = e & 15;
+    float v = 0.0f;
+#pragma unroll
+    for (int w = 0; w < WK; ++w) v += red[(w * 16 + row) * 8 + tok];
+    const int64_t n = n0 + row;
+    if (n < N) {
+      if (out_type == B2Q_OUT_BF16) reinterpret_cast<__nv_bfloat16*>(out)[(int64_t)tok * N + n] = __float2bfloat16_rn(v);
+      else reinterpret_cast<float*>(out)[(int64_t)tok * N + n] = v;
+    }
+  }
+}
+
+template <int WK, int TOK, bool WIDE>
+int32_t launch_small_t(b2q_handle h, const uint32_t* packed, const __half* scales, int gsh, const void* x, int tokens, int64_t N, int64_t K,
+                       void* out, int out_type) {
+  const size_t smem = (size_t)WK * 8192;
+  if (smem > 48 * 1024) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      B2Q_CUDA(h, cudaFuncSetAttribute(gemv_int4_small_kernel<WK, TOK, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      attr_set = true;
+    }
+  }
+  gemv_int4_small_kernel<WK, TOK, WIDE><<<(unsigned)ceil_div64(N, 16), WK * 32, smem, h->stream>>>(packed, scales, gsh, (const __nv_bfloat16*)x, tokens,
+                                                                                             N, K, out, out_type);
+  B2Q_LAUNCH_CHECK(h, "gemv_int4_small_kernel");
+  return B2Q_OK;
+}
+template <int WK>
+int32_t launch_small(b2q_handle h, const uint32_t* packed, const __half* scales, int gsh, const void* x, int tokens, int64_t N, int64_t K,
+                     void* out, int out_type) {
+#define I4_SMALL(TOK)                                                                                              \
+  return gsh == 5 ? launch_small_t<WK, TOK, true>(h, packed, scales, gsh, x, tokens, N, K, out, out_type)          \
+                  : launch_small_t<WK, TOK, false>(h, packed, scales, gsh, x, tokens, N, K, out, out_type)
+  if (tokens <= 1) { I4_SMALL(1); }
+  if (tokens <= 2) { I4_SMALL(2); }
+  if (tokens <= 4) { I4_SMALL(4); }
+  I4_SMALL(8);
+#undef I4_SMALL
+}
+
 template <int MT, int WARPS>
 int32_t launch(b2q_handle h, const uint32_t* packed, const __half* scales, int gsh, const void* x, int tokens, int64_t N, int64_t K,
                void* out, int out_type) {
@@ -263,7 +432,8 @@ int32_t launch(b2q_handle h, const uint32_t* packed, const __half* scales, int g
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, gemv_int4_kernel<MT, WARPS>, packed, scales, gsh, (const __nv_bfloat16*)x, tokens, N, K, out, out_type, split));
+  if (gsh == 5) B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, gemv_int4_kernel<MT, WARPS, true>, packed, scales, gsh, (const __nv_bfloat16*)x, tokens, N, K, out, out_type, split));
+  else B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, gemv_int4_kernel<MT, WARPS, false>, packed, scales, gsh, (const __nv_bfloat16*)x, tokens, N, K, out, out_type, split));
   return B2Q_OK;
 }
 
@@ -334,6 +504,14 @@ int32_t b2q_gemv_int4_wo(b2q_handle h, const uint32_t* packed, const void* scale
   const __half* sc = static_cast<const __half*>(scales_f16);
   const int t = (int)tokens;
   const bool small_n = n <= 8192;   // few row tiles: 4 warps (64 rows) per CTA give more CTAs
+  // One or two tokens with groups of 64 and up: the prefetching kernel (measured 65.5 against 71.6 us on 8192 x 28672);
+  // with more tokens or groups of 32 its registers spill and the cluster kernel is faster (73.7 against 102 us at 4 tokens).
+  // B2Q_INT4_SMALL=1 / 0 forces the choice.
+  const char* force_small = getenv("B2Q_INT4_SMALL");
+  if (force_small ? (force_small[0] == '1' && t <= 8) : (t <= 2 && gsh >= 6)) {
+    return k >= 8192 ? i4w::launch_small<8>(h, packed, sc, gsh, x_bf16, t, n, k, out, out_type)
+                     : i4w::launch_small<4>(h, packed, sc, gsh, x_bf16, t, n, k, out, out_type);
+  }
   if (t <= 8) return small_n ? i4w::launch<1, 4>(h, packed, sc, gsh, x_bf16, t, n, k, out, out_type) : i4w::launch<1, 8>(h, packed, sc, gsh, x_bf16, t, n, k, out, out_type);
   if (t <= 16) return small_n ? i4w::launch<2, 4>(h, packed, sc, gsh, x_bf16, t, n, k, out, out_type) : i4w::launch<2, 8>(h, packed, sc, gsh, x_bf16, t, n, k, out, out_type);
   return small_n ? i4w::launch<4, 4>(h, packed, sc, gsh, x_bf16, t, n, k, out, out_type) : i4w::launch<4, 8>(h, packed, sc, gsh, x_bf16, t, n, k, out, out_type);

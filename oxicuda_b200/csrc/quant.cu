@@ -364,14 +364,15 @@ __global__ void __launch_bounds__(kThreads) fp4_block_quantize_kernel(const floa
     for (int o = lanes >> 1; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
     float scale;
     uint32_t eb = 127;
+    float inv_pow2 = 0.0f;   // E8M0: dividing by 2^e is multiplying by 2^-e, exactly (both are representable for every scale byte)
     if (scale_format == 0) scale = amax == 0.0f ? 1.0f : __fdiv_rn(amax, target);
-    else { eb = e8m0_from_absmax_dev(amax); scale = e8m0_to_f32_dev(eb); }
+    else { eb = e8m0_from_absmax_dev(amax); scale = e8m0_to_f32_dev(eb); inv_pow2 = e8m0_to_f32_dev(254u - eb); }
     if (live) {
       float v[4] = {q.x, q.y, q.z, q.w};
       uint32_t c[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        float s = __fdiv_rn(v[j], scale);
+        float s = scale_format == 0 ? __fdiv_rn(v[j], scale) : __fmul_rn(v[j], inv_pow2);
         c[j] = format == 0 ? e2m1_encode_ref_dev(s) : int4_encode_ref_dev(s);
       }
       reinterpret_cast<uint16_t*>(packed)[i] = (uint16_t)(c[0] | (c[1] << 4) | (c[2] << 8) | (c[3] << 12));
