@@ -415,7 +415,19 @@ __global__ void __launch_bounds__(kThreads) nf4_decode_kernel(const uint8_t* pac
   __shared__ float lut[16];
   if (threadIdx.x < 16) lut[threadIdx.x] = kNf4Lut[threadIdx.x];
   __syncthreads();
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < nbytes; i += (int64_t)gridDim.x * blockDim.x) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (int64_t)gridDim.x * blockDim.x;
+  // four bytes (eight values of one block) per thread when the block size and the pointers allow it
+  const bool vec = block % 8 == 0 && (reinterpret_cast<uintptr_t>(packed) & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+  const int64_t n4 = vec ? nbytes >> 2 : 0;
+  for (int64_t i = tid; i < n4; i += nth) {
+    const uint32_t w = reinterpret_cast<const uint32_t*>(packed)[i];
+    const float amax = absmaxs[(8 * i) / block];
+    reinterpret_cast<float4*>(out)[2 * i] = make_float4(__fmul_rn(lut[w & 0xF], amax), __fmul_rn(lut[(w >> 4) & 0xF], amax),
+                                                        __fmul_rn(lut[(w >> 8) & 0xF], amax), __fmul_rn(lut[(w >> 12) & 0xF], amax));
+    reinterpret_cast<float4*>(out)[2 * i + 1] = make_float4(__fmul_rn(lut[(w >> 16) & 0xF], amax), __fmul_rn(lut[(w >> 20) & 0xF], amax),
+                                                            __fmul_rn(lut[(w >> 24) & 0xF], amax), __fmul_rn(lut[w >> 28], amax));
+  }
+  for (int64_t i = (n4 << 2) + tid; i < nbytes; i += nth) {
     uint32_t b = packed[i];
     float amax = absmaxs[(2 * i) / block];
     reinterpret_cast<float2*>(out)[i] = make_float2(__fmul_rn(lut[b & 0xF], amax), __fmul_rn(lut[b >> 4], amax));
@@ -492,16 +504,29 @@ __global__ void __launch_bounds__(kThreads) int8_dequant_kernel(const int8_t* __
 // ---------------------------------------------------------------------------
 // dist-infer INT8-in-u8 ("fp8_infer"): q = round(clamp(v*(127/absmax), +-127)) as i8 as u8
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(kThreads) distfp8_quantize_kernel(const float* x, int64_t n, int64_t block,
-                                                                    const float* absmaxs, uint8_t* q) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    float amax = absmaxs[i / block];
-    if (amax == 0.0f) { q[i] = 0; continue; }
-    float scale = __fdiv_rn(127.0f, amax);
-    float t = __fmul_rn(x[i], scale);
-    t = t < -127.0f ? -127.0f : (t > 127.0f ? 127.0f : t);
-    t = roundf(t);
-    q[i] = (uint8_t)(int8_t)(isnan(t) ? 0 : (int)t);
+__device__ __forceinline__ uint32_t distfp8_code(float v, float amax, float scale) {
+  if (amax == 0.0f) return 0u;
+  float t = __fmul_rn(v, scale);
+  t = t < -127.0f ? -127.0f : (t > 127.0f ? 127.0f : t);
+  t = roundf(t);
+  return (uint32_t)(isnan(t) ? 0 : (int)t) & 0xFFu;
+}
+// vec_ok: block % 4 == 0 and aligned pointers, so four consecutive elements share a block (one index division and one
+// scale division per four elements)
+__global__ void __launch_bounds__(kThreads) distfp8_quantize_kernel(const float* __restrict__ x, int64_t n, int64_t block,
+                                                                    const float* __restrict__ absmaxs, uint8_t* __restrict__ q, int vec_ok) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (int64_t)gridDim.x * blockDim.x;
+  const int64_t n4 = vec_ok ? n >> 2 : 0;
+  for (int64_t i = tid; i < n4; i += nth) {
+    const float amax = absmaxs[(4 * i) / block];
+    const float scale = __fdiv_rn(127.0f, amax);
+    const float4 v = reinterpret_cast<const float4*>(x)[i];
+    reinterpret_cast<uint32_t*>(q)[i] = distfp8_code(v.x, amax, scale) | (distfp8_code(v.y, amax, scale) << 8) |
+                                        (distfp8_code(v.z, amax, scale) << 16) | (distfp8_code(v.w, amax, scale) << 24);
+  }
+  for (int64_t i = (n4 << 2) + tid; i < n; i += nth) {
+    const float amax = absmaxs[i / block];
+    q[i] = (uint8_t)distfp8_code(x[i], amax, __fdiv_rn(127.0f, amax));
   }
 }
 __global__ void __launch_bounds__(kThreads) distfp8_dequantize_kernel(const uint8_t* q, int64_t n, int64_t block,
@@ -832,7 +857,8 @@ int32_t b2q_distfp8_quantize_block_f32(b2q_handle h, const float* x, int64_t n, 
   StatArgs a{kAbsmaxOnly, 0, 0, 0.0f, absmaxs, nullptr, h->d_status, 0};
   int32_t st = launch_row_stats<float>(h, x, n / block, block, a);
   if (st != B2Q_OK) return st;
-  distfp8_quantize_kernel<<<grid_for(h, n, kThreads), kThreads, 0, h->stream>>>(x, n, block, absmaxs, q);
+  const int vec_ok = block % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(q) & 3) == 0;
+  distfp8_quantize_kernel<<<grid_for(h, n, kThreads * (vec_ok ? 4 : 1)), kThreads, 0, h->stream>>>(x, n, block, absmaxs, q, vec_ok);
   B2Q_LAUNCH_CHECK(h, "distfp8_quantize_kernel");
   return B2Q_OK;
 }
