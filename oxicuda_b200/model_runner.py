@@ -105,6 +105,7 @@ class QuantizedLlamaRunner:
         self.g_final = (1.0 + 0.05 * torch.randn(cfg.hidden, device=device, generator=gen)).to(torch.bfloat16)
         self.lm_head = Fp8Linear(torch.randn(cfg.vocab_size, cfg.hidden, device=device, generator=gen) * (1.0 / math.sqrt(cfg.hidden)))
         self.codec = Fp8Codec.e4m3("rne")
+        self.trace = None          # a list here collects every stage's tensors per layer (tests check each stage on its own inputs)
         half = cfg.head_dim // 2
         self.inv_freq = 1.0 / (cfg.rope_theta ** (torch.arange(0, half, device=device, dtype=torch.float32) / half))
 
@@ -174,7 +175,9 @@ class QuantizedLlamaRunner:
         res = torch.zeros(tokens, cfg.hidden, dtype=torch.bfloat16, device=self.dev)
         nq, nkv, d = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
         for layer in self.layers:
+            x_in = delta
             xc, xs = rms_norm_quantize_fp8(delta, layer.g_attn, cfg.eps, residual=res)
+            res_attn = res.clone() if self.trace is not None else None
             qkv = layer.qkv.forward(xc, xs)                                    # bf16 [tokens, (nq + 2 nkv) d]
             q = self._rope(qkv[:, : nq * d].reshape(tokens, nq, d), positions)
             k = self._rope(qkv[:, nq * d: (nq + nkv) * d].reshape(tokens, nkv, d), positions)
@@ -188,7 +191,7 @@ class QuantizedLlamaRunner:
                 attn[r0:r1] = self._attend(q[r0:r1], self._kv_load(layer.k_codes, layer.k_par, all_slots),
                                            self._kv_load(layer.v_codes, layer.v_par, all_slots), p0)
             ac, as_ = self.codec.quantize_rows(attn.view(tokens, nq * d), tokens, nq * d)
-            delta = layer.o.forward(ac.view(tokens, nq * d), as_)
+            delta = o_out = layer.o.forward(ac.view(tokens, nq * d), as_)
             xc, xs = rms_norm_quantize_fp8(delta, layer.g_mlp, cfg.eps, residual=res)
             gu = layer.gate_up.forward(xc, xs)                                 # gate | up
             hc = torch.empty(tokens, cfg.ffn, dtype=torch.uint8, device=self.dev)
@@ -196,6 +199,9 @@ class QuantizedLlamaRunner:
             default_handle().call("b2q_swiglu_quantize_rows_bf16", ptr(gu), ptr(gu[:, cfg.ffn:]), tokens, cfg.ffn, 2 * cfg.ffn,
                                   L.FP8_E4M3, L.ROUND_RNE, ptr(hs), ptr(hc))
             delta = layer.down.forward(hc, hs)
+            if self.trace is not None:
+                self.trace.append(dict(x_in=x_in, res_attn=res_attn, qkv=qkv, attn=attn.clone(), o_out=o_out, res_mlp=res.clone(), gu=gu,
+                                       mlp_out=delta))
         xc, xs = rms_norm_quantize_fp8(delta, self.g_final, cfg.eps, residual=res)
         return xc, xs
 

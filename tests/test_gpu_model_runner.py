@@ -13,10 +13,27 @@ def _dense(lin):
     return lin.codes.view(torch.float8_e4m3fn).to(torch.float32) * lin.scales[:, None]
 
 
-def _reference_logits(runner, token_ids, positions, seqs_rows):
-    """fp32 forward over full sequences: token_ids [tokens], positions [tokens], seqs_rows = [(r0, r1)] causal blocks."""
+def _reference_logits(runner, token_ids, positions, seqs_rows, quant=False):
+    """Forward over full sequences in torch: token_ids [tokens], positions [tokens], seqs_rows = [(r0, r1)] causal blocks.
+    quant=False: plain fp32.  quant=True: the same quantization points as the runner, restated with torch operations
+    (per-token FP8 E4M3 activations, per-(token, head) INT8 keys and values, bf16 GEMM outputs and residual stream)."""
     cfg = runner.cfg
     nq, nkv, d = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+    bf = (lambda t: t.to(torch.bfloat16).to(torch.float32)) if quant else (lambda t: t)
+
+    def q8(t):        # per-token absmax / 448 scale, E4M3 round to nearest even
+        if not quant:
+            return t
+        s = t.abs().amax(dim=-1, keepdim=True) / 448.0
+        s = torch.where(s > 0, s, torch.ones_like(s))
+        return (t / s).to(torch.float8_e4m3fn).to(torch.float32) * s
+
+    def kv8(t):       # [tokens, heads, d]: asymmetric 8-bit per (token, head)
+        if not quant:
+            return t
+        mn, mx = t.amin(dim=-1, keepdim=True), t.amax(dim=-1, keepdim=True)
+        s = torch.where(mx > mn, (mx - mn) / 255.0, torch.ones_like(mx))
+        return bf(torch.clamp(torch.round((t - mn) / s), 0, 255) * s + mn)
 
     def rms(x, g):
         return x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + cfg.eps) * g.to(torch.float32)
@@ -30,11 +47,11 @@ def _reference_logits(runner, token_ids, positions, seqs_rows):
     res = runner.embed[token_ids.long()].to(torch.float32)
     tokens = res.shape[0]
     for layer in runner.layers:
-        h = rms(res, layer.g_attn)
-        qkv = h @ _dense(layer.qkv).T
-        q = rope(qkv[:, : nq * d].reshape(tokens, nq, d))
-        k = rope(qkv[:, nq * d: (nq + nkv) * d].reshape(tokens, nkv, d))
-        v = qkv[:, (nq + nkv) * d:].reshape(tokens, nkv, d)
+        h = q8(rms(res, layer.g_attn))
+        qkv = bf(h @ _dense(layer.qkv).T)
+        q = bf(rope(qkv[:, : nq * d].reshape(tokens, nq, d)))
+        k = kv8(bf(rope(qkv[:, nq * d: (nq + nkv) * d].reshape(tokens, nkv, d))))
+        v = kv8(qkv[:, (nq + nkv) * d:].reshape(tokens, nkv, d))
         attn = torch.empty(tokens, nq, d, device=res.device)
         for r0, r1 in seqs_rows:
             kf = k[r0:r1].repeat_interleave(nq // nkv, dim=1)
@@ -43,12 +60,12 @@ def _reference_logits(runner, token_ids, positions, seqs_rows):
             n = r1 - r0
             s = s.masked_fill(torch.triu(torch.ones(n, n, dtype=torch.bool, device=res.device), 1)[None], float("-inf"))
             attn[r0:r1] = torch.einsum("hqk,khd->qhd", torch.softmax(s, dim=-1), vf)
-        res = res + attn.reshape(tokens, nq * d) @ _dense(layer.o).T
-        h = rms(res, layer.g_mlp)
-        gu = h @ _dense(layer.gate_up).T
+        res = bf(res + bf(q8(bf(attn.reshape(tokens, nq * d))) @ _dense(layer.o).T))
+        h = q8(rms(res, layer.g_mlp))
+        gu = bf(h @ _dense(layer.gate_up).T)
         g, u = gu[:, : cfg.ffn], gu[:, cfg.ffn:]
-        res = res + (g / (1.0 + torch.exp(-g)) * u) @ _dense(layer.down).T
-    return rms(res, runner.g_final) @ _dense(runner.lm_head).T
+        res = bf(res + bf(q8(g / (1.0 + torch.exp(-g)) * u) @ _dense(layer.down).T))
+    return q8(rms(res, runner.g_final)) @ _dense(runner.lm_head).T
 
 
 def _rel_rms(got, ref):
@@ -56,7 +73,65 @@ def _rel_rms(got, ref):
     return float(np.sqrt(((got - ref) ** 2).mean()) / np.sqrt((ref ** 2).mean()))
 
 
-def test_prefill_and_decode_against_fp32_statement(cuda):
+def _stage_checks(runner, trace, positions, rows, prev_res):
+    """Every stage of every layer recomputed in torch FROM THE RUNNER'S OWN INPUTS of that stage.  (Whole-pipeline
+    agreement cannot be tight: a 0.5 % perturbation ahead of an E4M3 quantizer re-rolls the rounding of several percent
+    of the elements, so two correct pipelines drift apart by the size of the quantization noise itself.)"""
+    cfg = runner.cfg
+    nq, nkv, d = cfg.n_heads, cfg.n_kv_heads, cfg.head_dim
+    bf = lambda t: t.to(torch.bfloat16).to(torch.float32)
+
+    def q8(t):
+        s = t.abs().amax(dim=-1, keepdim=True) / 448.0
+        s = torch.where(s > 0, s, torch.ones_like(s))
+        return (t / s).to(torch.float8_e4m3fn).to(torch.float32) * s
+
+    def rms(x, g):
+        return x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + cfg.eps) * g.to(torch.float32)
+
+    def rope(t):
+        ang = positions.to(torch.float32)[:, None] * runner.inv_freq[None, :]
+        cos, sin = ang.cos()[:, None, :], ang.sin()[:, None, :]
+        a, b = t[..., : d // 2], t[..., d // 2:]
+        return torch.cat([a * cos - b * sin, a * sin + b * cos], dim=-1)
+
+    def kv8(t):
+        mn, mx = t.amin(dim=-1, keepdim=True), t.amax(dim=-1, keepdim=True)
+        s = torch.where(mx > mn, (mx - mn) / 255.0, torch.ones_like(mx))
+        return bf(torch.clamp(torch.round((t - mn) / s), 0, 255) * s + mn)
+
+    def rel(a, b):
+        return float(((a.double() - b.double()) ** 2).mean().sqrt() / (b.double() ** 2).mean().sqrt())
+
+    res = prev_res
+    for layer, t in zip(runner.layers, trace):
+        tokens = t["qkv"].shape[0]
+        res = bf(res + t["x_in"].float())
+        assert torch.equal(t["res_attn"].float(), res)                                   # residual add, exact
+        assert rel(t["qkv"].float(), bf(q8(rms(res, layer.g_attn)) @ _dense(layer.qkv).T)) <= 2e-3
+        qkv = t["qkv"].float()
+        q = bf(rope(qkv[:, : nq * d].reshape(tokens, nq, d)))
+        k = kv8(bf(rope(qkv[:, nq * d: (nq + nkv) * d].reshape(tokens, nkv, d))))
+        v = kv8(qkv[:, (nq + nkv) * d:].reshape(tokens, nkv, d))
+        attn = torch.empty(tokens, nq, d, device=res.device)
+        for r0, r1 in rows:
+            kf = k[r0:r1].repeat_interleave(nq // nkv, dim=1)
+            vf = v[r0:r1].repeat_interleave(nq // nkv, dim=1)
+            s = torch.einsum("qhd,khd->hqk", q[r0:r1], kf) / math.sqrt(d)
+            n = r1 - r0
+            s = s.masked_fill(torch.triu(torch.ones(n, n, dtype=torch.bool, device=res.device), 1)[None], float("-inf"))
+            attn[r0:r1] = torch.einsum("hqk,khd->qhd", torch.softmax(s, dim=-1), vf)
+        assert rel(t["attn"].float(), bf(attn)) <= 5e-3                                   # INT8 pages, tie rule of round()
+        # bf16 inputs sit on exact E4M3 ties about once per row, and torch divides by 448 through a reciprocal: 4e-3 measured
+        assert rel(t["o_out"].float(), bf(q8(t["attn"].float().reshape(tokens, nq * d)) @ _dense(layer.o).T)) <= 1e-2
+        res = bf(res + t["o_out"].float())
+        assert torch.equal(t["res_mlp"].float(), res)
+        assert rel(t["gu"].float(), bf(q8(rms(res, layer.g_mlp)) @ _dense(layer.gate_up).T)) <= 2e-3
+        g, u = t["gu"].float()[:, : cfg.ffn], t["gu"].float()[:, cfg.ffn:]
+        assert rel(t["mlp_out"].float(), bf(q8(g / (1.0 + torch.exp(-g)) * u) @ _dense(layer.down).T)) <= 2e-3
+
+
+def test_prefill_and_decode_against_torch_statements(cuda):
     from oxicuda_b200.model_runner import LlamaConfig, QuantizedLlamaRunner
     cfg = LlamaConfig()
     runner = QuantizedLlamaRunner(cfg, cuda, seed=7)
@@ -68,15 +143,20 @@ def test_prefill_and_decode_against_fp32_statement(cuda):
     for n in lens:
         starts.append(starts[-1] + n)
     flat = [t for p in prompts for t in p]
+    runner.trace = []
     logits = runner.prefill(flat, starts, tables)
     assert len(logits) == 3 and len(logits[0]) == cfg.vocab_size
     ids = torch.tensor(flat, device=cuda)
     pos = torch.cat([torch.arange(n, device=cuda) for n in lens])
-    ref = _reference_logits(runner, ids, pos, [(starts[i], starts[i + 1]) for i in range(3)])
-    ref_last = ref[[s - 1 for s in starts[1:]]].cpu().numpy()
-    # FP8 (3 mantissa bits) activations per token, FP8 weights shared with the reference, INT8 KV: a few percent
-    assert _rel_rms(logits, ref_last) <= 5e-2
-    # two decode steps: the cache written by prefill and by the first step is what the next step attends to
+    rows = [(starts[i], starts[i + 1]) for i in range(3)]
+    _stage_checks(runner, runner.trace, pos, rows, torch.zeros(len(flat), cfg.hidden, device=cuda))
+    runner.trace = None
+    # end to end against plain fp32: every per-token E4M3 quantization (3 mantissa bits, about 3.6 % rms) adds its noise
+    # to the residual stream; eleven such steps in two layers and the head measured 7 %
+    last = [s - 1 for s in starts[1:]]
+    ref = _reference_logits(runner, ids, pos, rows)[last].cpu().numpy()
+    assert _rel_rms(logits, ref) <= 0.12
+    # two decode steps: the pages written by prefill and by the first step are what the next step attends to
     seq_lens = list(lens)
     for step in range(2):
         nxt = [int(np.argmax(row)) for row in logits]
@@ -91,10 +171,11 @@ def test_prefill_and_decode_against_fp32_statement(cuda):
         ids = torch.tensor(flat, device=cuda)
         pos = torch.cat([torch.arange(n, device=cuda) for n in seq_lens])
         ref = _reference_logits(runner, ids, pos, [(st[i], st[i + 1]) for i in range(3)])
-        assert _rel_rms(logits, ref[[s - 1 for s in st[1:]]].cpu().numpy()) <= 5e-2, step
-    # a prefill of the extended prompts into fresh pages agrees with prefill + decode (same kernels, other batch shapes)
+        assert _rel_rms(logits, ref[[s - 1 for s in st[1:]]].cpu().numpy()) <= 0.12, step
+    # a prefill of the extended prompts into fresh pages against prefill + decode: other batch shapes, other GEMM
+    # kernels, same noise level
     fresh = runner.prefill(flat, st, [[10, 11], [12, 13, 14], [15, 16]])
-    assert _rel_rms(fresh, logits) <= 3e-2
+    assert _rel_rms(fresh, logits) <= 0.12
 
 
 def test_model_runner_contract(cuda):
