@@ -37,7 +37,8 @@ __device__ __forceinline__ void unpack8(const uint4 q, float (&v)[8]) {
 __device__ __forceinline__ uint32_t bf16_bits(float f) { return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(f)); }
 
 // One CTA per token; thread t keeps chunks t, t + blockDim, ... (8 elements each, NCH at most) of the row in registers.
-template <int NCH>
+// FULL: every thread has all NCH chunks (cols == 8 * NCH * blockDim), so the bounds predicates drop out.
+template <int NCH, bool FULL>
 __global__ void __launch_bounds__(1024) rms_norm_quantize_fp8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* residual,
                                                                      const __nv_bfloat16* __restrict__ gamma, int64_t cols, float eps, int fmt,
                                                                      int rounding, float* __restrict__ scales, uint8_t* __restrict__ codes,
@@ -52,7 +53,7 @@ __global__ void __launch_bounds__(1024) rms_norm_quantize_fp8_kernel(const __nv_
 #pragma unroll
   for (int k = 0; k < NCH; ++k) {
     const int c = (int)threadIdx.x + k * (int)blockDim.x;
-    if (c < chunks) {
+    if (FULL || c < chunks) {
       unpack8(xr[c], v[k]);
       if (rr) {
         float res[8];
@@ -83,7 +84,7 @@ __global__ void __launch_bounds__(1024) rms_norm_quantize_fp8_kernel(const __nv_
 #pragma unroll
   for (int k = 0; k < NCH; ++k) {
     const int c = (int)threadIdx.x + k * (int)blockDim.x;
-    if (c < chunks) {
+    if (FULL || c < chunks) {
       float g[8];
       unpack8(gr[c], g);
 #pragma unroll
@@ -103,15 +104,16 @@ __global__ void __launch_bounds__(1024) rms_norm_quantize_fp8_kernel(const __nv_
 #pragma unroll
   for (int k = 0; k < NCH; ++k) {
     const int c = (int)threadIdx.x + k * (int)blockDim.x;
-    if (c < chunks) {
+    if (FULL || c < chunks) {
       uint32_t lo = 0, hi = 0;
       if (rounding == 1) {     // the conversion saturates to +-max_val by itself
+        uint32_t p[4];
 #pragma unroll
-        for (int j = 0; j < 8; j += 2) {
-          const uint32_t b = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(v[k][j], inv_scale), __fmul_rn(v[k][j + 1], inv_scale)),
-                                                                __NV_SATFINITE, fmt == 0 ? __NV_E4M3 : __NV_E5M2);
-          if (j < 4) lo |= b << (8 * j); else hi |= b << (8 * (j - 4));
-        }
+        for (int j = 0; j < 4; ++j)
+          p[j] = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(v[k][2 * j], inv_scale), __fmul_rn(v[k][2 * j + 1], inv_scale)),
+                                                    __NV_SATFINITE, fmt == 0 ? __NV_E4M3 : __NV_E5M2);
+        lo = __byte_perm(p[0], p[1], 0x5410);
+        hi = __byte_perm(p[2], p[3], 0x5410);
       } else {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -193,9 +195,12 @@ extern "C" int32_t b2q_rms_norm_quantize_fp8_bf16(b2q_handle h, const void* x, v
     if (chunks <= 1024 && chunks > 256 && rows >= 4 * (int64_t)h->sm_count) nch = chunks <= 512 ? 2 : 4;   // many rows: smaller CTAs, more of them per SM
     int threads = (int)((ceil_div64(chunks, nch) + 31) / 32 * 32);
     if (threads < 32) threads = 32;
-    if (nch == 1) rms_norm_quantize_fp8_kernel<1><<<(unsigned)rows, threads, 0, h->stream>>>(xp, rp, gp, cols, eps, fmt, rounding, scales, codes, yp);
-    else if (nch == 2) rms_norm_quantize_fp8_kernel<2><<<(unsigned)rows, threads, 0, h->stream>>>(xp, rp, gp, cols, eps, fmt, rounding, scales, codes, yp);
-    else rms_norm_quantize_fp8_kernel<4><<<(unsigned)rows, threads, 0, h->stream>>>(xp, rp, gp, cols, eps, fmt, rounding, scales, codes, yp);
+    const bool full = chunks == (int64_t)nch * threads;
+#define RMS_LAUNCH(N, F) rms_norm_quantize_fp8_kernel<N, F><<<(unsigned)rows, threads, 0, h->stream>>>(xp, rp, gp, cols, eps, fmt, rounding, scales, codes, yp)
+    if (nch == 1) { if (full) RMS_LAUNCH(1, true); else RMS_LAUNCH(1, false); }
+    else if (nch == 2) { if (full) RMS_LAUNCH(2, true); else RMS_LAUNCH(2, false); }
+    else { if (full) RMS_LAUNCH(4, true); else RMS_LAUNCH(4, false); }
+#undef RMS_LAUNCH
     B2Q_LAUNCH_CHECK(h, "rms_norm_quantize_fp8_kernel");
     return B2Q_OK;
   }
