@@ -582,7 +582,8 @@ template <> __device__ __forceinline__ void load_chunk8<__nv_bfloat16>(const __n
   for (int j = 0; j < 4; ++j) { v[2 * j] = __uint_as_float(w[j] << 16); v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u); }
 }
 
-template <typename T, int NCH>
+// FULL: every thread has all NCH chunks (cols == 8 * NCH * blockDim), so the bounds predicates drop out.
+template <typename T, int NCH, bool FULL>
 __global__ void __launch_bounds__(1024) fp8_quantize_rows_reg_kernel(const T* __restrict__ x, int64_t cols, StatArgs a, int fmt, int rounding,
                                                                      uint8_t* __restrict__ codes) {
   __shared__ float sh_amax[32];
@@ -596,7 +597,7 @@ __global__ void __launch_bounds__(1024) fp8_quantize_rows_reg_kernel(const T* __
 #pragma unroll
   for (int k = 0; k < NCH; ++k) {
     const int c = (int)threadIdx.x + k * (int)blockDim.x;
-    if (c < chunks) {
+    if (FULL || c < chunks) {
       load_chunk8<T>(row, c, v[k]);
 #pragma unroll
       for (int j = 0; j < 8; ++j) { amax = fmaxf(amax, fabsf(v[k][j])); bad |= !isfinite(v[k][j]); }
@@ -618,15 +619,16 @@ __global__ void __launch_bounds__(1024) fp8_quantize_rows_reg_kernel(const T* __
 #pragma unroll
   for (int k = 0; k < NCH; ++k) {
     const int c = (int)threadIdx.x + k * (int)blockDim.x;
-    if (c < chunks) {
+    if (FULL || c < chunks) {
       uint32_t lo = 0, hi = 0;
       if (rounding == 1) {   // the conversion saturates at +-max_val, which is what the clamp of the other path does
+        uint32_t p[4];
 #pragma unroll
-        for (int j = 0; j < 8; j += 2) {
-          const uint32_t b = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v[k][j], scale), __fdiv_rn(v[k][j + 1], scale)),
-                                                                __NV_SATFINITE, fmt == 0 ? __NV_E4M3 : __NV_E5M2);
-          if (j < 4) lo |= b << (8 * j); else hi |= b << (8 * (j - 4));
-        }
+        for (int j = 0; j < 4; ++j)
+          p[j] = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v[k][2 * j], scale), __fdiv_rn(v[k][2 * j + 1], scale)),
+                                                    __NV_SATFINITE, fmt == 0 ? __NV_E4M3 : __NV_E5M2);
+        lo = __byte_perm(p[0], p[1], 0x5410);
+        hi = __byte_perm(p[2], p[3], 0x5410);
       } else {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -654,9 +656,12 @@ int32_t fp8_quantize_rows_impl(b2q_handle h, const T* x, int64_t rows, int64_t c
     // 1, 2 or 4 chunks of 8 elements per thread; many rows prefer small CTAs (several per SM)
     const int nch = chunks <= 128 ? 1 : (chunks <= 512 ? 2 : 4);
     const int threads = (int)((ceil_div64(chunks, nch) + 31) / 32 * 32);
-    if (nch == 1) fp8_quantize_rows_reg_kernel<T, 1><<<(unsigned)rows, threads, 0, h->stream>>>(x, cols, a, fmt, rounding, codes);
-    else if (nch == 2) fp8_quantize_rows_reg_kernel<T, 2><<<(unsigned)rows, threads, 0, h->stream>>>(x, cols, a, fmt, rounding, codes);
-    else fp8_quantize_rows_reg_kernel<T, 4><<<(unsigned)rows, threads, 0, h->stream>>>(x, cols, a, fmt, rounding, codes);
+    const bool full = chunks == (int64_t)nch * threads;
+#define ROWS_LAUNCH(N, F) fp8_quantize_rows_reg_kernel<T, N, F><<<(unsigned)rows, threads, 0, h->stream>>>(x, cols, a, fmt, rounding, codes)
+    if (nch == 1) { if (full) ROWS_LAUNCH(1, true); else ROWS_LAUNCH(1, false); }
+    else if (nch == 2) { if (full) ROWS_LAUNCH(2, true); else ROWS_LAUNCH(2, false); }
+    else { if (full) ROWS_LAUNCH(4, true); else ROWS_LAUNCH(4, false); }
+#undef ROWS_LAUNCH
     B2Q_LAUNCH_CHECK(h, "fp8_quantize_rows_reg_kernel");
     return B2Q_OK;
   }

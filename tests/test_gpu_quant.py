@@ -121,6 +121,34 @@ def test_fp8_quantize_rows_bit_exact(cuda, oracle):
     assert np.array_equal(codes.cpu().numpy(), c_ref) and np.array_equal(scales.cpu().numpy(), s_ref)
 
 
+@pytest.mark.parametrize("bf16", [False, True])
+def test_fp8_quantize_rows_register_kernel_bit_exact(cuda, oracle, bf16):
+    """Many rows of 256..16384 elements (a multiple of 8) take the kernel that keeps a row in registers: 1, 2 or 4 chunks
+    per thread, rows that fill every thread and rows that do not, both roundings, a zero row and (f32) a NaN element."""
+    from oxicuda_b200 import _lib
+    from oxicuda_b200._lib import default_handle
+    from oxicuda_b200.quant import Fp8Codec
+    rng = _rng(14)
+    for rows, cols in ((44, 256), (200, 1024), (64, 4096), (70, 8192), (3, 2048), (65, 1000), (130, 16384), (64, 4104)):
+        x = torch.from_numpy((rng.standard_normal((rows, cols)) * rng.uniform(0.01, 3.0, (rows, 1))).astype(np.float32))
+        x[1, :] = 0.0
+        if bf16:
+            x = x.to(torch.bfloat16)
+        xf = x.float().numpy().reshape(-1)
+        for mode, name in ((0, "ref"), (1, "rne")):
+            codes, scales = Fp8Codec.e4m3(name).quantize_rows(x.to(cuda), rows, cols)
+            c_ref, s_ref, bad = oracle.fp8_quantize_rows(xf, rows, cols, 0, mode)
+            assert bad == -1
+            assert np.array_equal(scales.cpu().numpy().view(np.uint32), s_ref.view(np.uint32)), (rows, cols, name)
+            assert np.array_equal(codes.cpu().numpy(), c_ref), (rows, cols, name)
+    if not bf16:
+        x = torch.ones(64, 512)
+        x[5, 17] = float("nan")
+        Fp8Codec.e4m3("rne").quantize_rows(x.to(cuda), 64, 512)
+        with pytest.raises(_lib.NonFiniteFp8):
+            default_handle().check()
+
+
 def test_fp4_block_quantize_bit_exact(cuda, oracle, kat):
     from oxicuda_b200.blas import Fp4Format, MicroScalingConfig, MicroScalingQuantizer, ScalingFormat
     rng = _rng(14)
