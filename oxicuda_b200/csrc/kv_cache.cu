@@ -109,7 +109,8 @@ __device__ __forceinline__ uint32_t kv_codes4(const float (&v)[4], KvParams p, f
 // each input byte is read once, NV 16-byte loads are in flight per lane, the reduction takes log2(G) shuffle rounds
 // and the parameters are derived once per 4 * NV elements of a lane.
 // ---------------------------------------------------------------------------
-template <typename T, int G, int NV>
+// FULL: cols == G * NV * 4, every lane has all its chunks and the column predicates drop out.
+template <typename T, int G, int NV, bool FULL>
 __global__ void __launch_bounds__(kThreads) kv_quantize_per_token_reg_kernel(const T* __restrict__ x, int64_t rows, int64_t cols, int rule,
                                                                              int qmin, int qmax, uint8_t* __restrict__ codes,
                                                                              float* __restrict__ scales, float* __restrict__ zps) {
@@ -125,7 +126,7 @@ __global__ void __launch_bounds__(kThreads) kv_quantize_per_token_reg_kernel(con
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int64_t c = (int64_t)(sub + G * k) * 4;
-      if (live && c < cols) ld4<T>(x + r * cols, c, v[k]);
+      if (live && (FULL || c < cols)) ld4<T>(x + r * cols, c, v[k]);
       else v[k][0] = v[k][1] = v[k][2] = v[k][3] = nan;
     }
     float mn = __uint_as_float(0x7F800000u), mx = __uint_as_float(0xFF800000u);
@@ -146,7 +147,7 @@ __global__ void __launch_bounds__(kThreads) kv_quantize_per_token_reg_kernel(con
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int64_t c = (int64_t)(sub + G * k) * 4;
-      if (c < cols) *reinterpret_cast<uint32_t*>(out + c) = kv_codes4(v[k], p, inv, qmin, qmax);
+      if (FULL || c < cols) *reinterpret_cast<uint32_t*>(out + c) = kv_codes4(v[k], p, inv, qmin, qmax);
     }
   }
 }
@@ -323,9 +324,14 @@ int32_t kv_quantize_rows(b2q_handle h, const T* x, int64_t rows, int64_t cols, i
                          float* scales, float* zps) {
   const bool vec = cols % 4 == 0 && (reinterpret_cast<uintptr_t>(x) % (4 * sizeof(T))) == 0 && (reinterpret_cast<uintptr_t>(codes) & 3) == 0;
   if (vec && cols <= 1024) {
-#define KV_REG_LAUNCH(G, NV)                                                                                                              \
-  kv_quantize_per_token_reg_kernel<T, G, NV><<<grid_cap(h, ceil_div64(rows, kWarpsPerBlock * (32 / G))), kThreads, 0, h->stream>>>(x, rows, cols, rule, \
-                                                                                                                                qmin, qmax, codes, scales, zps)
+#define KV_REG_LAUNCH(G, NV)                                                                                                                \
+  do {                                                                                                                                      \
+    const int grid_ = grid_cap(h, ceil_div64(rows, kWarpsPerBlock * (32 / G)));                                                             \
+    if (cols == G * NV * 4)                                                                                                                 \
+      kv_quantize_per_token_reg_kernel<T, G, NV, true><<<grid_, kThreads, 0, h->stream>>>(x, rows, cols, rule, qmin, qmax, codes, scales, zps); \
+    else                                                                                                                                    \
+      kv_quantize_per_token_reg_kernel<T, G, NV, false><<<grid_, kThreads, 0, h->stream>>>(x, rows, cols, rule, qmin, qmax, codes, scales, zps); \
+  } while (0)
     if (cols <= 32) KV_REG_LAUNCH(4, 2);          // G lanes x NV chunks x 4 elements cover the row
     else if (cols <= 64) KV_REG_LAUNCH(4, 4);
     else if (cols <= 128) KV_REG_LAUNCH(8, 4);
