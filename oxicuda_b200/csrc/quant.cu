@@ -137,6 +137,50 @@ __global__ void __launch_bounds__(kThreads) row_stat_warp_kernel(const T* x, int
   }
 }
 
+// Short f32 rows (groups of up to 1024 elements, a multiple of 4, 16-byte aligned): G lanes share a row, so a warp
+// works on 32 / G rows at a time with NV 16-byte loads in flight per lane and log2(G) shuffle rounds per row.
+template <int G, int NV>
+__global__ void __launch_bounds__(kThreads) row_stat_subwarp_kernel(const float* __restrict__ x, int64_t rows, int64_t cols, StatArgs a) {
+  constexpr int kRowsPerWarp = 32 / G;
+  const int lane = threadIdx.x & 31, sub = lane % G, grp = lane / G;
+  const int64_t warp = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  for (int64_t r0 = warp * kRowsPerWarp; r0 < rows; r0 += (int64_t)gridDim.x * (kThreads / 32) * kRowsPerWarp) {
+    const int64_t r = r0 + grp;
+    const bool live = r < rows;
+    RowStat s{__uint_as_float(0x7F800000u), __uint_as_float(0xFF800000u), 0.0f, 0};
+    float4 q[NV];
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t c = (int64_t)(sub + G * k) * 4;
+      if (live && c < cols) q[k] = *reinterpret_cast<const float4*>(x + r * cols + c);
+      else q[k] = make_float4(__uint_as_float(0x7FC00000u), __uint_as_float(0x7FC00000u), __uint_as_float(0x7FC00000u), __uint_as_float(0x7FC00000u));
+    }
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int64_t c = (int64_t)(sub + G * k) * 4;
+      if (live && c < cols) {
+        const float vv[4] = {q[k].x, q[k].y, q[k].z, q[k].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float v = vv[j];
+          s.fmin = fminf(s.fmin, v);          // NaN never wins, like the `<` / `>` scan
+          s.fmax = fmaxf(s.fmax, v);
+          s.amax = fmaxf(s.amax, fabsf(v));
+          s.bad |= !isfinite(v);
+        }
+      }
+    }
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) {
+      s.fmin = fminf(s.fmin, __shfl_xor_sync(0xffffffffu, s.fmin, o));
+      s.fmax = fmaxf(s.fmax, __shfl_xor_sync(0xffffffffu, s.fmax, o));
+      s.amax = fmaxf(s.amax, __shfl_xor_sync(0xffffffffu, s.amax, o));
+      s.bad |= __shfl_xor_sync(0xffffffffu, s.bad, o);
+    }
+    if (live && sub == 0) finish_row(a, r, s);
+  }
+}
+
 // keys: [rows][4] = {min key, max key, absmax bits, bad flag}
 __global__ void stat_keys_init_kernel(uint32_t* keys, int64_t rows) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -188,6 +232,22 @@ __global__ void stat_keys_finish_kernel(const uint32_t* keys, int64_t rows, Stat
 
 template <typename T>
 int32_t launch_row_stats(b2q_handle h, const T* x, int64_t rows, int64_t cols, const StatArgs& a) {
+  if constexpr (sizeof(T) == 4) {
+    if (cols % 4 == 0 && cols <= 1024 && rows >= 256 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+      const float* xf = reinterpret_cast<const float*>(x);
+#define STAT_SUBWARP(G, NV) \
+  row_stat_subwarp_kernel<G, NV><<<grid_for(h, rows, (kThreads / 32) * (32 / G)), kThreads, 0, h->stream>>>(xf, rows, cols, a)
+      if (cols <= 32) STAT_SUBWARP(4, 2);
+      else if (cols <= 64) STAT_SUBWARP(4, 4);
+      else if (cols <= 128) STAT_SUBWARP(8, 4);
+      else if (cols <= 256) STAT_SUBWARP(16, 4);
+      else if (cols <= 512) STAT_SUBWARP(32, 4);
+      else STAT_SUBWARP(32, 8);
+#undef STAT_SUBWARP
+      B2Q_LAUNCH_CHECK(h, "row_stat_subwarp_kernel");
+      return B2Q_OK;
+    }
+  }
   const bool split = cols >= (1 << 15) && rows * 4 <= (int64_t)kScratchWords && rows <= 65535;
   if (!split) {
     int grid = grid_for(h, rows, kThreads / 32);
