@@ -436,8 +436,8 @@ __global__ void __launch_bounds__(kThreads) fp4_block_quantize_kernel(const floa
         c[j] = format == 0 ? e2m1_encode_ref_dev(s) : int4_encode_ref_dev(s);
       }
       reinterpret_cast<uint16_t*>(packed)[i] = (uint16_t)(c[0] | (c[1] << 4) | (c[2] << 8) | (c[3] << 12));
-      if ((i % lanes) == 0) {
-        int64_t b = i / lanes;
+      if ((i & (lanes - 1)) == 0) {                       // lanes is 8, 16 or 32
+        int64_t b = i >> (lanes == 8 ? 3 : (lanes == 16 ? 4 : 5));
         if (scale_format == 0) scales_f32[b] = scale; else scales_e8m0[b] = (uint8_t)eb;
       }
     }
@@ -451,7 +451,7 @@ __global__ void __launch_bounds__(kThreads) fp4_block_dequantize_kernel(const ui
   const int64_t n4 = n >> 2;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
     uint32_t w = reinterpret_cast<const uint16_t*>(packed)[i];
-    int64_t b = (4 * i) / block;
+    int64_t b = (block & (block - 1)) == 0 ? (4 * i) >> (31 - __clz(block)) : (4 * i) / block;
     float scale = scale_format == 0 ? scales_f32[b] : e8m0_to_f32_dev(scales_e8m0[b]);
     float r[4];
 #pragma unroll
