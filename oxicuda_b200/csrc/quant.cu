@@ -479,9 +479,11 @@ __global__ void __launch_bounds__(kThreads) nf4_decode_kernel(const uint8_t* pac
   // four bytes (eight values of one block) per thread when the block size and the pointers allow it
   const bool vec = block % 8 == 0 && (reinterpret_cast<uintptr_t>(packed) & 3) == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
   const int64_t n4 = vec ? nbytes >> 2 : 0;
+  const bool pow2 = (block & (block - 1)) == 0;          // block index by a shift where the block size allows it
+  const int bsh = 31 - __clz(block);
   for (int64_t i = tid; i < n4; i += nth) {
     const uint32_t w = reinterpret_cast<const uint32_t*>(packed)[i];
-    const float amax = absmaxs[(8 * i) / block];
+    const float amax = absmaxs[pow2 ? (8 * i) >> bsh : (8 * i) / block];
     reinterpret_cast<float4*>(out)[2 * i] = make_float4(__fmul_rn(lut[w & 0xF], amax), __fmul_rn(lut[(w >> 4) & 0xF], amax),
                                                         __fmul_rn(lut[(w >> 8) & 0xF], amax), __fmul_rn(lut[(w >> 12) & 0xF], amax));
     reinterpret_cast<float4*>(out)[2 * i + 1] = make_float4(__fmul_rn(lut[(w >> 16) & 0xF], amax), __fmul_rn(lut[(w >> 20) & 0xF], amax),
