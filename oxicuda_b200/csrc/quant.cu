@@ -509,6 +509,46 @@ __device__ __forceinline__ uint32_t nearest_nf4_dev(const float* lut, float v) {
   return d_lo <= d_hi ? lo - 1 : lo;
 }
 
+// Blocks of 32, 64, 128 or 256 elements, 16-byte aligned input: G = block / 8 lanes share a block, eight elements (two
+// 16-byte loads) and one 4-byte store per lane, log2(G) shuffle rounds for the block maximum.  Same arithmetic as the
+// warp-per-block kernel below.
+template <int G>
+__global__ void __launch_bounds__(kThreads) nf4_encode_subwarp_kernel(const float* __restrict__ x, int64_t nblocks, uint8_t* __restrict__ packed,
+                                                                      float* __restrict__ absmaxs) {
+  __shared__ float lut[16];
+  if (threadIdx.x < 16) lut[threadIdx.x] = kNf4Lut[threadIdx.x];
+  __syncthreads();
+  constexpr int kPerWarp = 32 / G;
+  const int lane = threadIdx.x & 31, sub = lane % G, grp = lane / G;
+  const int64_t warp = (int64_t)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  for (int64_t b0 = warp * kPerWarp; b0 < nblocks; b0 += (int64_t)gridDim.x * (kThreads / 32) * kPerWarp) {
+    const int64_t b = b0 + grp;
+    const bool live = b < nblocks;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (live) {
+      const float4* p = reinterpret_cast<const float4*>(x + b * (G * 8) + sub * 8);
+      const float4 q0 = p[0], q1 = p[1];
+      v[0] = q0.x; v[1] = q0.y; v[2] = q0.z; v[3] = q0.w; v[4] = q1.x; v[5] = q1.y; v[6] = q1.z; v[7] = q1.w;
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(v[j]));
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (amax < 1e-8f) amax = 1e-8f;
+    if (!live) continue;
+    if (sub == 0) absmaxs[b] = amax;
+    uint32_t w = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float a = __fdiv_rn(v[j], amax);
+      a = a < -1.0f ? -1.0f : (a > 1.0f ? 1.0f : a);
+      w |= nearest_nf4_dev(lut, a) << (4 * j);
+    }
+    reinterpret_cast<uint32_t*>(packed)[b * G + sub] = w;
+  }
+}
+
 // one warp per block of `block` (even) elements
 __global__ void __launch_bounds__(kThreads) nf4_encode_kernel(const float* x, int64_t nblocks, int block, uint8_t* packed,
                                                               float* absmaxs) {
@@ -889,6 +929,17 @@ int32_t b2q_nf4_encode_f32(b2q_handle h, const float* x, int64_t n, int block, u
   if (n % block != 0) B2Q_FAIL(h, B2Q_ERR_GROUP_SIZE_MISMATCH, "nf4_encode: len %lld not divisible by group %d", (long long)n, block);
   if (!x || !packed || !absmaxs) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "nf4_encode: null pointer");
   int64_t nblocks = n / block;
+  const bool aligned = (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(packed) & 3) == 0;
+  if (aligned && (block == 32 || block == 64 || block == 128 || block == 256)) {
+#define NF4_SUBWARP(G) nf4_encode_subwarp_kernel<G><<<grid_for(h, nblocks, (kThreads / 32) * (32 / G)), kThreads, 0, h->stream>>>(x, nblocks, packed, absmaxs)
+    if (block == 32) NF4_SUBWARP(4);
+    else if (block == 64) NF4_SUBWARP(8);
+    else if (block == 128) NF4_SUBWARP(16);
+    else NF4_SUBWARP(32);
+#undef NF4_SUBWARP
+    B2Q_LAUNCH_CHECK(h, "nf4_encode_subwarp_kernel");
+    return B2Q_OK;
+  }
   nf4_encode_kernel<<<grid_for(h, nblocks, kThreads / 32), kThreads, 0, h->stream>>>(x, nblocks, block, packed, absmaxs);
   B2Q_LAUNCH_CHECK(h, "nf4_encode_kernel");
   return B2Q_OK;

@@ -186,7 +186,7 @@ def test_nf4_bit_exact(cuda, oracle):
     from oxicuda_b200 import _lib
     from oxicuda_b200.quant import Nf4Quantizer
     rng = _rng(15)
-    for block in (64, 32, 2):
+    for block in (64, 32, 2, 128, 256, 24):          # 32..256: eight elements per lane; others: a warp per block
         x = rng.standard_normal(block * 513).astype(np.float32)
         x[:block] = 0.0
         q = Nf4Quantizer(block)
