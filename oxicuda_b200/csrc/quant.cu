@@ -318,12 +318,23 @@ __global__ void __launch_bounds__(kThreads) minmax_dequantize_kernel(const int32
     out[i] = __fmul_rn((float)d, scales[r]);
   }
 }
+__device__ __forceinline__ float fake_quant_one(float v, float scale, float zp, float qmin, float qmax) {
+  float q = roundf(__fadd_rn(__fdiv_rn(v, scale), zp));
+  q = q < qmin ? qmin : (q > qmax ? qmax : q);
+  return __fmul_rn(__fsub_rn(q, zp), scale);
+}
 __global__ void __launch_bounds__(kThreads) fake_quant_kernel(float* x, int64_t n, float scale, float zp, float qmin, float qmax) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-    float q = roundf(__fadd_rn(__fdiv_rn(x[i], scale), zp));
-    q = q < qmin ? qmin : (q > qmax ? qmax : q);
-    x[i] = __fmul_rn(__fsub_rn(q, zp), scale);
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (int64_t)gridDim.x * blockDim.x;
+  const int64_t n4 = (reinterpret_cast<uintptr_t>(x) & 15) == 0 ? n >> 2 : 0;
+  for (int64_t i = tid; i < n4; i += nth) {
+    float4 v = reinterpret_cast<float4*>(x)[i];
+    v.x = fake_quant_one(v.x, scale, zp, qmin, qmax);
+    v.y = fake_quant_one(v.y, scale, zp, qmin, qmax);
+    v.z = fake_quant_one(v.z, scale, zp, qmin, qmax);
+    v.w = fake_quant_one(v.w, scale, zp, qmin, qmax);
+    reinterpret_cast<float4*>(x)[i] = v;
   }
+  for (int64_t i = (n4 << 2) + tid; i < n; i += nth) x[i] = fake_quant_one(x[i], scale, zp, qmin, qmax);
 }
 
 // ---------------------------------------------------------------------------
