@@ -642,9 +642,17 @@ __global__ void __launch_bounds__(kThreads) distfp8_quantize_kernel(const float*
     q[i] = (uint8_t)distfp8_code(x[i], amax, __fdiv_rn(127.0f, amax));
   }
 }
-__global__ void __launch_bounds__(kThreads) distfp8_dequantize_kernel(const uint8_t* q, int64_t n, int64_t block,
-                                                                      const float* absmaxs, float* out) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+__global__ void __launch_bounds__(kThreads) distfp8_dequantize_kernel(const uint8_t* __restrict__ q, int64_t n, int64_t block,
+                                                                      const float* __restrict__ absmaxs, float* __restrict__ out, int vec_ok) {
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, nth = (int64_t)gridDim.x * blockDim.x;
+  const int64_t n4 = vec_ok ? n >> 2 : 0;      // block % 4 == 0: four consecutive elements share a block
+  for (int64_t i = tid; i < n4; i += nth) {
+    const float s = __fdiv_rn(absmaxs[(4 * i) / block], 127.0f);
+    const uint32_t w = reinterpret_cast<const uint32_t*>(q)[i];
+    reinterpret_cast<float4*>(out)[i] = make_float4(__fmul_rn((float)(int8_t)(w & 0xFF), s), __fmul_rn((float)(int8_t)((w >> 8) & 0xFF), s),
+                                                    __fmul_rn((float)(int8_t)((w >> 16) & 0xFF), s), __fmul_rn((float)(int8_t)(w >> 24), s));
+  }
+  for (int64_t i = (n4 << 2) + tid; i < n; i += nth)
     out[i] = __fmul_rn((float)(int8_t)q[i], __fdiv_rn(absmaxs[i / block], 127.0f));
 }
 
@@ -997,7 +1005,8 @@ int32_t b2q_distfp8_dequantize_block_f32(b2q_handle h, const uint8_t* q, int64_t
   if (!q || !absmaxs || !out) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "distfp8_dequantize: null pointer");
   if (block < 1) block = 1;
   if (block > n) block = n;
-  distfp8_dequantize_kernel<<<grid_for(h, n, kThreads), kThreads, 0, h->stream>>>(q, n, block, absmaxs, out);
+  const int vec_ok = block % 4 == 0 && (reinterpret_cast<uintptr_t>(out) & 15) == 0 && (reinterpret_cast<uintptr_t>(q) & 3) == 0;
+  distfp8_dequantize_kernel<<<grid_for(h, n, kThreads * (vec_ok ? 4 : 1)), kThreads, 0, h->stream>>>(q, n, block, absmaxs, out, vec_ok);
   B2Q_LAUNCH_CHECK(h, "distfp8_dequantize_kernel");
   return B2Q_OK;
 }
