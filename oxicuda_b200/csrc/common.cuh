@@ -9,6 +9,7 @@
 #include <stdint.h>
 #include <stdio.h>
 #include <string.h>
+#include <atomic>
 
 #include "../../include/b2q.h"
 
@@ -28,6 +29,11 @@ struct b2q_handle_s {
   void* ws;                  // grow-only workspace for calls that need temporaries (kept so steady-state calls never allocate)
   size_t ws_bytes;
   int dynamic_weights;       // 1: weight operands may be written by the previous kernel of the stream (no early weight fetch)
+  // Experiment switches (environment variables B2Q_*), read once when the handle is created: -1 = not set.
+  struct Switches {
+    int no_tail_split, force_tile, fp8_skinny, skinny_pdl, mx_streamk, mx_debug, mx_pdl, mx_inline, e8c_db, gemv_mx, gemv_cluster,
+        gemv_exact, int4_small, gemv_stream;
+  } sw;
   char err[512];
 };
 // Returns a workspace of at least `bytes` (256-byte aligned); grows it when needed (synchronises the stream first).
@@ -55,8 +61,27 @@ static const size_t kTileCounters = 1 << 14;
     if (_e != cudaSuccess) B2Q_FAIL(h, B2Q_ERR_LAUNCH_FAILED, "%s: %s", what, cudaGetErrorString(_e)); \
   } while (0)
 
-#define B2Q_REQUIRE_HANDLE(h) \
-  do { if (!(h)) return (int32_t)B2Q_ERR_INVALID_ARGUMENT; (h)->err[0] = 0; } while (0)
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to the current device only: remember per kernel (one
+// static mask per expansion site) which devices have been configured.  The handle's device must be current.
+#define B2Q_SMEM_ATTR(h, kernel, bytes)                                                               \
+  do {                                                                                                \
+    static std::atomic<unsigned long long> _done{0};                                                  \
+    const unsigned long long _bit = 1ull << ((h)->device & 63);                                       \
+    if (!(_done.load(std::memory_order_acquire) & _bit)) {                                            \
+      B2Q_CUDA(h, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)(bytes))); \
+      _done.fetch_or(_bit, std::memory_order_release);                                                \
+    }                                                                                                 \
+  } while (0)
+
+// Every entry point launches on the CURRENT device: a handle used while another device is current is refused.
+#define B2Q_REQUIRE_HANDLE(h)                                                                          \
+  do {                                                                                                 \
+    if (!(h)) return (int32_t)B2Q_ERR_INVALID_ARGUMENT;                                                \
+    (h)->err[0] = 0;                                                                                   \
+    int _dev = -1;                                                                                     \
+    if (cudaGetDevice(&_dev) != cudaSuccess || _dev != (h)->device)                                    \
+      B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "the handle belongs to device %d but device %d is current", (h)->device, _dev); \
+  } while (0)
 
 static inline int64_t ceil_div64(int64_t a, int64_t b) { return (a + b - 1) / b; }
 

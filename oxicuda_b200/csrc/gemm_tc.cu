@@ -12,8 +12,7 @@
 //               bf16/f32 (or raw s32), vectorised global stores.
 // Every mbarrier wait is bounded (wall-clock limit); on expiry the kernel records
 // B2Q_ERR_TIMEOUT in the status word, drains what it issued, frees TMEM and returns.
-#include "common.cuh"
-#include <cuda.h>
+#include "tc_common.cuh"
 #include <stdlib.h>
 
 namespace tc {
@@ -50,57 +49,9 @@ struct Params {
   uint32_t idesc_half;
 };
 
-// ---- PTX wrappers ----------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ uint64_t globaltimer_ns() { uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok;
-}
-// Bounded wait: false when the limit expired or another role already gave up.
+using namespace tcx;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
-  uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if (((++spins) & 0x3F) == 0) {
-      if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; return false; }
-    }
-  }
-  return true;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+  return mbar_wait_bounded(bar, parity, abort_flag, kWaitLimitNs, 1);
 }
 template <int KIND>
 __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
@@ -121,31 +72,7 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
   }
 }
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// Shared-memory matrix descriptor for a K-major tile stored as rows of 128 bytes
-// with the 128-byte swizzle (what TMA SWIZZLE_128B writes): 8-row groups are
-// 1024 bytes apart (stride byte offset), descriptor version 1, layout type 2.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-  d |= (uint64_t)1 << 16;                     // leading byte offset (unused for swizzled K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;           // stride byte offset
-  d |= (uint64_t)1 << 46;                     // descriptor version (sm_100)
-  d |= (uint64_t)2 << 61;                     // SWIZZLE_128B
-  return d;
-}
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) { return make_desc_sw128(smem_addr); }
 
 __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& mb, int& nb) {
   const int group_size = GROUP_M * tiles_n;
@@ -587,22 +514,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 }  // namespace two
 
 // ---- host side --------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)sym;
-  }
-  return fn;
-}
-
 // rows x K bytes, K-major; box = 128 bytes x box_rows, 128-byte swizzle, zero fill out of bounds.
 int32_t make_map(b2q_handle h, CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int box_rows) {
   EncodeTiledFn enc = get_encode_fn();
@@ -633,11 +544,7 @@ int32_t launch(b2q_handle h, const void* a, const void* w, Params p) {
   p.idesc = KIND == kF8 ? (p.idesc | (1u << 4) | shape)                                   // fp32 accumulate, E4M3/E5M2 per p.idesc
           : KIND == kI8 ? ((2u << 4) | (1u << 7) | (1u << 10) | shape)                    // s32 accumulate, signed 8-bit A and B
                         : ((1u << 4) | (1u << 7) | (1u << 10) | shape);                   // fp32 accumulate, bf16 A and B
-  static bool attr_set = false;
-  if (!attr_set) {
-    B2Q_CUDA(h, cudaFuncSetAttribute(gemm_tc_kernel<BN, KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
-    attr_set = true;
-  }
+  B2Q_SMEM_ATTR(h, (gemm_tc_kernel<BN, KIND>), C::kSmem);
   int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
   int grid = (int)(tiles < h->sm_count ? tiles : h->sm_count);
   gemm_tc_kernel<BN, KIND><<<grid, kThreads, C::kSmem, h->stream>>>(map_a, map_w, p);
@@ -667,16 +574,12 @@ int32_t launch2(b2q_handle h, const void* a, const void* w, Params p) {
   p.idesc = KIND == kF8 ? (p.idesc | (1u << 4) | shape)                                   // fp32 accumulate, E4M3/E5M2 per p.idesc
           : KIND == kI8 ? ((2u << 4) | (1u << 7) | (1u << 10) | shape)                    // s32 accumulate, signed 8-bit A and B
                         : ((1u << 4) | (1u << 7) | (1u << 10) | shape);                   // fp32 accumulate, bf16 A and B
-  static bool attr_set = false;
-  if (!attr_set) {
-    B2Q_CUDA(h, cudaFuncSetAttribute(two::gemm_tc2_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, two::kSmem));
-    attr_set = true;
-  }
+  B2Q_SMEM_ATTR(h, (two::gemm_tc2_kernel<KIND>), two::kSmem);
   const int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
   const int max_pairs = h->sm_count / 2;
   // tail split: when the last wave fills at most half of the pairs, its tiles become two half-width units each
   const int rem = (int)(tiles % max_pairs);
-  const bool split = tiles > max_pairs && rem > 0 && 2 * rem <= max_pairs && getenv("B2Q_NO_TAIL_SPLIT") == nullptr;
+  const bool split = tiles > max_pairs && rem > 0 && 2 * rem <= max_pairs && h->sw.no_tail_split < 0;
   p.full_units = split ? (int)(tiles - rem) : (int)tiles;
   p.total_units = split ? (int)(tiles + rem) : (int)tiles;
   const int pairs = (int)(p.total_units < max_pairs ? p.total_units : max_pairs);
@@ -740,16 +643,14 @@ extern "C" int32_t b2q_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w
   b2q_tile_config t; int kid = 0;
   b2q_select_tile(0, (uint32_t)M, (uint32_t)N, (uint32_t)K, &t, &kid);
   if (kid != 0) {   // experiment switch: B2Q_FORCE_TILE_N=128|256 overrides the static table
-    const char* force = getenv("B2Q_FORCE_TILE_N");
-    if (force && force[0] == '1') kid = 2;
-    if (force && force[0] == '2') kid = 1;
-    if (force && force[0] == 'p') kid = 4;     // "pair": the two-CTA kernel
+    if (h->sw.force_tile == 128) kid = 2;
+    if (h->sw.force_tile == 256) kid = 1;
+    if (h->sw.force_tile == 9) kid = 4;        // "p(air)": the two-CTA kernel
   }
   {
     // few tokens against a large weight matrix (kernel 6 of the static table): the weight-stationary tcgen05 kernel
     // streams W at HBM rate (B2Q_FP8_SKINNY=0 / 1 forces it off / on)
-    const char* sk = getenv("B2Q_FP8_SKINNY");
-    if (M <= 128 && (sk ? sk[0] == '1' : kid == 6)) {
+    if (M <= 128 && (h->sw.fp8_skinny >= 0 ? h->sw.fp8_skinny == 1 : kid == 6)) {
       int32_t sst = b2q_gemm_fp8_skinny_dispatch(h, a, w, M, N, K, fmt, scale_a, scale_a_kind, scale_w, scale_w_kind, out, out_type);
       if (sst != B2Q_ERR_UNSUPPORTED) return sst;
     }

@@ -430,11 +430,7 @@ int32_t launch_small_t(b2q_handle h, const uint8_t* codes, const void* scales, c
   const unsigned grid = (unsigned)ceil_div64(N, 16);
   const size_t smem = (size_t)WK * 8192;
   if (smem > 48 * 1024) {
-    static bool attr_set = false;
-    if (!attr_set) {
-      B2Q_CUDA(h, cudaFuncSetAttribute(gemv_fp4_small_kernel<E8, WK, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      attr_set = true;
-    }
+    B2Q_SMEM_ATTR(h, (gemv_fp4_small_kernel<E8, WK, TOK>), (int)smem);
   }
   gemv_fp4_small_kernel<E8, WK, TOK><<<grid, WK * 32, smem, h->stream>>>(codes, scales, (const __nv_bfloat16*)x, tokens, N, K, out, out_type);
   B2Q_LAUNCH_CHECK(h, "gemv_fp4_small_kernel");
@@ -448,8 +444,9 @@ int32_t launch_small_t(b2q_handle h, const uint8_t* codes, const void* scales, c
 // (measured 84 % of peak) bounds it.  With power-of-two scales the block scale can instead be multiplied
 // into the f16 codes before the MMA without rounding (code * 2^e is exact in f16 for -23 <= e <= 13), so a
 // lane may own a whole 32-code block: ONE 16-byte load per row and step, a quarter of the wavefronts.
-// A scale exponent outside [-23, 13] records B2Q_ERR_UNSUPPORTED in the status word (such a tensor must
-// use f32 scales, which take the exact kernel).
+// Exponents below -23 lose at most 2^-24 per code (flushed towards zero in f16).  An exponent above 13 would
+// overflow f16: a warp that meets one in a 512-wide chunk computes that chunk with exact_chunk_e8 instead
+// (fp32 scale, fp32 FMA, k ascending), so every legal E8M0 tensor gives the defined result.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ uint4 ld_stream_v4(const void* p) {
   uint4 r;
@@ -462,9 +459,8 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
   asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
   return d;
 }
-// E8M0 byte -> 2^(b-127) as f16x2 (both halves); subnormal f16 below 2^-14.  `bad` collects range violations.
-__device__ __forceinline__ uint32_t e8m0_to_h2(uint32_t b, uint32_t& bad) {
-  bad |= (b - 104u) > 36u ? 1u : 0u;                     // exponent outside [-23, 13]
+// E8M0 byte -> 2^(b-127) as f16x2 (both halves); subnormal f16 below 2^-14, zero below 2^-24.
+__device__ __forceinline__ uint32_t e8m0_to_h2(uint32_t b) {
   const int ee = (int)b - 112;                           // f16 exponent field
   const uint32_t h = ee > 0 ? ((uint32_t)min(ee, 30) << 10) : (ee > -10 ? (0x0400u >> (1 - ee)) : 0u);
   return h * 0x00010001u;
@@ -502,14 +498,55 @@ __device__ __forceinline__ void load_chunk_e8(ChunkRegsE8& r, const uint8_t* w0,
   }
 }
 
+// True when one of this lane's scale bytes of the chunk is an exponent above 13 (byte > 140).
+__device__ __forceinline__ bool chunk_overflows_f16(const ChunkRegsE8& r, int tig) {
+  const uint32_t w[8] = {r.sa.x, r.sa.y, r.sa.z, r.sa.w, r.sb.x, r.sb.y, r.sb.z, r.sb.w};
+  bool bad = false;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) bad |= ((w[i] >> (8 * tig)) & 0xFFu) > 140u;
+  return bad;
+}
+
+// The defined arithmetic (dequantize_fp4, then an fp32 dot product with k ascending) for one chunk of `klen` K
+// values starting at k0 and the four outputs a lane holds in one MMA accumulator: rows ra, rb x tokens t0, t0 + 1.
+// Reads global memory directly; only runs for chunks that hold a block exponent f16 cannot carry.
+__device__ __noinline__ void exact_chunk_e8(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ scales,
+                                            const __nv_bfloat16* __restrict__ x, int64_t K, int64_t ra, int64_t rb, int64_t k0,
+                                            int klen, int t0, int tokens, float (&add)[4]) {
+  for (int ri = 0; ri < 2; ++ri) {
+    const int64_t row = ri ? rb : ra;
+    const uint8_t* cw = codes + row * (K >> 1) + (k0 >> 1);
+    const uint8_t* sc = scales + row * (K >> 5) + (k0 >> 5);
+    float s0 = 0.0f, s1 = 0.0f;
+    for (int b = 0; b < (klen >> 5); ++b) {
+      const float scale = e8m0_to_f32_dev(sc[b]);
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t byte = cw[b * 16 + i];
+        const float wl = e2m1_decode_dev(byte & 15u) * scale, wh = e2m1_decode_dev(byte >> 4) * scale;
+        const int64_t k = k0 + b * 32 + 2 * i;
+        if (t0 < tokens) {
+          s0 = fmaf(wl, __bfloat162float(x[(int64_t)t0 * K + k]), s0);
+          s0 = fmaf(wh, __bfloat162float(x[(int64_t)t0 * K + k + 1]), s0);
+        }
+        if (t0 + 1 < tokens) {
+          s1 = fmaf(wl, __bfloat162float(x[(int64_t)(t0 + 1) * K + k]), s1);
+          s1 = fmaf(wh, __bfloat162float(x[(int64_t)(t0 + 1) * K + k + 1]), s1);
+        }
+      }
+    }
+    add[2 * ri] += s0;
+    add[2 * ri + 1] += s1;
+  }
+}
+
 __device__ __forceinline__ void mul_chunk_e8(const ChunkRegsE8& r, const uint4* xs_lane, int tig, float (&acc0)[4],
-                                             float (&acc1)[4], uint32_t& bad) {
+                                             float (&acc1)[4]) {
   const uint32_t saw[4] = {r.sa.x, r.sa.y, r.sa.z, r.sa.w};
   const uint32_t sbw[4] = {r.sb.x, r.sb.y, r.sb.z, r.sb.w};
 #pragma unroll
   for (int s = 0; s < 4; ++s) {
-    const uint32_t ha2 = e8m0_to_h2((saw[s] >> (8 * tig)) & 0xFFu, bad);
-    const uint32_t hb2 = e8m0_to_h2((sbw[s] >> (8 * tig)) & 0xFFu, bad);
+    const uint32_t ha2 = e8m0_to_h2((saw[s] >> (8 * tig)) & 0xFFu);
+    const uint32_t hb2 = e8m0_to_h2((sbw[s] >> (8 * tig)) & 0xFFu);
     const uint32_t wav[4] = {r.wa[s].x, r.wa[s].y, r.wa[s].z, r.wa[s].w};
     const uint32_t wbv[4] = {r.wb[s].x, r.wb[s].y, r.wb[s].z, r.wb[s].w};
 #pragma unroll
@@ -578,19 +615,23 @@ __global__ void __launch_bounds__(WK * 32, 512 / (WK * 32)) gemv_fp4_e8_kernel(c
   const uint4* xs_lane = xs + g * 4 + tig;
 
   float acc0[4] = {0.0f, 0.0f, 0.0f, 0.0f}, acc1[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-  uint32_t bad = 0;
+  auto consume = [&](const ChunkRegsE8& R) {
+    const int klen = (int)min((int64_t)KC, K - (int64_t)c * KC);
+    if (__any_sync(0xFFFFFFFFu, chunk_overflows_f16(R, tig))) {      // warp-uniform; never taken for ordinary weights
+      exact_chunk_e8(codes, scales, x, K, r0, r1, (int64_t)c * KC, klen, 2 * tig, tokens, acc0);
+    } else {
+      stage_x_warp_e8<TOK>(xs, xk, tokens, K, klen, lane);
+      mul_chunk_e8(R, xs_lane, tig, acc0, acc1);
+    }
+    ++c; w0 += KC / 2; w1 += KC / 2; s0 += KC / 32; s1 += KC / 32; xk += KC;
+  };
   while (c < c_end) {
     if (c + 1 < c_end) load_chunk_e8(B, w0 + KC / 2, w1 + KC / 2, s0 + KC / 32, s1 + KC / 32, min(4, total_steps - (c + 1) * 4));
-    stage_x_warp_e8<TOK>(xs, xk, tokens, K, (int)min((int64_t)KC, K - (int64_t)c * KC), lane);
-    mul_chunk_e8(A, xs_lane, tig, acc0, acc1, bad);
-    ++c; w0 += KC / 2; w1 += KC / 2; s0 += KC / 32; s1 += KC / 32; xk += KC;
+    consume(A);
     if (c >= c_end) break;
     if (c + 1 < c_end) load_chunk_e8(A, w0 + KC / 2, w1 + KC / 2, s0 + KC / 32, s1 + KC / 32, min(4, total_steps - (c + 1) * 4));
-    stage_x_warp_e8<TOK>(xs, xk, tokens, K, (int)min((int64_t)KC, K - (int64_t)c * KC), lane);
-    mul_chunk_e8(B, xs_lane, tig, acc0, acc1, bad);
-    ++c; w0 += KC / 2; w1 += KC / 2; s0 += KC / 32; s1 += KC / 32; xk += KC;
+    consume(B);
   }
-  if (bad) atomicCAS(status, 0, (int)B2Q_ERR_UNSUPPORTED);
 
   __syncthreads();
   red[(warp * 16 + g) * 8 + tig * 2 + 0] = acc0[0] + acc1[0];
@@ -617,11 +658,7 @@ int32_t launch_e8_t(b2q_handle h, const uint8_t* codes, const void* scales, cons
   const unsigned grid = (unsigned)ceil_div64(N, 16);
   const size_t smem = (size_t)WK * 8192;
   if (smem > 48 * 1024) {
-    static bool attr_set = false;
-    if (!attr_set) {
-      B2Q_CUDA(h, cudaFuncSetAttribute(gemv_fp4_e8_kernel<WK, TOK>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      attr_set = true;
-    }
+    B2Q_SMEM_ATTR(h, (gemv_fp4_e8_kernel<WK, TOK>), (int)smem);
   }
   gemv_fp4_e8_kernel<WK, TOK><<<grid, WK * 32, smem, h->stream>>>(codes, (const uint8_t*)scales, (const __nv_bfloat16*)x, tokens, N, K,
                                                                    out, out_type, h->d_status);
@@ -646,14 +683,14 @@ int32_t launch_e8(b2q_handle h, const uint8_t* codes, const void* scales, const 
 // ---------------------------------------------------------------------------
 template <int MT>
 __device__ __forceinline__ void mul_chunk_e8c(const ChunkRegsE8& r, const uint4* xs_lane, int tig, float (&acc0)[MT][4],
-                                              float (&acc1)[MT][4], uint32_t& bad) {
+                                              float (&acc1)[MT][4]) {
   constexpr int MPAD = 8 * MT;
   const uint32_t saw[4] = {r.sa.x, r.sa.y, r.sa.z, r.sa.w};
   const uint32_t sbw[4] = {r.sb.x, r.sb.y, r.sb.z, r.sb.w};
 #pragma unroll
   for (int s = 0; s < 4; ++s) {
-    const uint32_t ha2 = e8m0_to_h2((saw[s] >> (8 * tig)) & 0xFFu, bad);
-    const uint32_t hb2 = e8m0_to_h2((sbw[s] >> (8 * tig)) & 0xFFu, bad);
+    const uint32_t ha2 = e8m0_to_h2((saw[s] >> (8 * tig)) & 0xFFu);
+    const uint32_t hb2 = e8m0_to_h2((sbw[s] >> (8 * tig)) & 0xFFu);
     const uint32_t wav[4] = {r.wa[s].x, r.wa[s].y, r.wa[s].z, r.wa[s].w};
     const uint32_t wbv[4] = {r.wb[s].x, r.wb[s].y, r.wb[s].z, r.wb[s].w};
 #pragma unroll
@@ -709,7 +746,16 @@ __global__ void __launch_bounds__(WARPS * 32, DB ? 1 : 512 / (WARPS * 32)) gemv_
 #pragma unroll
     for (int i = 0; i < 4; ++i) { acc0[t][i] = 0.0f; acc1[t][i] = 0.0f; }
   }
-  uint32_t bad = 0;
+  // one chunk of this warp's rows: tensor-core path, or the exact fp32 statement when a block exponent exceeds f16
+  auto consume = [&](const ChunkRegsE8& R, int cc) {
+    if (__any_sync(0xFFFFFFFFu, chunk_overflows_f16(R, tig))) {
+      const int klen = (int)min((int64_t)KC, K - (int64_t)cc * KC);
+#pragma unroll
+      for (int t = 0; t < MT; ++t) exact_chunk_e8(codes, scales, x, K, r0, r1, (int64_t)cc * KC, klen, t * 8 + 2 * tig, tokens, acc0[t]);
+    } else {
+      mul_chunk_e8c<MT>(R, xs_lane, tig, acc0, acc1);
+    }
+  };
 
   // activations of chunk cc for the whole CTA: piece (step, jj, token, quad lane) = x[token][step*128 + lane*32 + jj*8 .. +8)
   auto stage = [&](int cc) {
@@ -735,12 +781,12 @@ __global__ void __launch_bounds__(WARPS * 32, DB ? 1 : 512 / (WARPS * 32)) gemv_
     while (c < c_end) {
       if (c + 1 < c_end) load_chunk_e8(B, w0 + KC / 2, w1 + KC / 2, s0 + KC / 32, s1 + KC / 32, min(4, total_steps - (c + 1) * 4));
       stage(c);
-      mul_chunk_e8c<MT>(A, xs_lane, tig, acc0, acc1, bad);
+      consume(A, c);
       ++c; w0 += KC / 2; w1 += KC / 2; s0 += KC / 32; s1 += KC / 32;
       if (c >= c_end) break;
       if (c + 1 < c_end) load_chunk_e8(A, w0 + KC / 2, w1 + KC / 2, s0 + KC / 32, s1 + KC / 32, min(4, total_steps - (c + 1) * 4));
       stage(c);
-      mul_chunk_e8c<MT>(B, xs_lane, tig, acc0, acc1, bad);
+      consume(B, c);
       ++c; w0 += KC / 2; w1 += KC / 2; s0 += KC / 32; s1 += KC / 32;
     }
   } else {                                               // one register set, two CTAs per SM hide the load latency
@@ -748,11 +794,10 @@ __global__ void __launch_bounds__(WARPS * 32, DB ? 1 : 512 / (WARPS * 32)) gemv_
       ChunkRegsE8 A;
       load_chunk_e8(A, w0, w1, s0, s1, min(4, total_steps - c * 4));
       stage(c);
-      mul_chunk_e8c<MT>(A, xs_lane, tig, acc0, acc1, bad);
+      consume(A, c);
       w0 += KC / 2; w1 += KC / 2; s0 += KC / 32; s1 += KC / 32;
     }
   }
-  if (bad) atomicCAS(status, 0, (int)B2Q_ERR_UNSUPPORTED);
 
   // ---- partial sums to shared memory: red[token][row within the CTA] ----
   __syncthreads();
@@ -819,8 +864,8 @@ int32_t launch_e8c_t(b2q_handle h, const uint8_t* codes, const void* scales, con
 template <int MT, int WARPS>
 int32_t launch_e8c(b2q_handle h, const uint8_t* codes, const void* scales, const void* x, int tokens, int64_t N, int64_t K,
                    void* out, int out_type) {
-  const char* db = getenv("B2Q_GEMV_E8C_DB");           // experiment switch: 1 = double-buffered weights, one CTA per SM
-  if (db && db[0] == '1') return launch_e8c_t<MT, WARPS, true>(h, codes, scales, x, tokens, N, K, out, out_type);
+  if (h->sw.e8c_db == 1)                                // experiment switch: double-buffered weights, one CTA per SM
+    return launch_e8c_t<MT, WARPS, true>(h, codes, scales, x, tokens, N, K, out, out_type);
   return launch_e8c_t<MT, WARPS, false>(h, codes, scales, x, tokens, N, K, out, out_type);
 }
 
@@ -862,33 +907,29 @@ extern "C" int32_t b2q_gemv_fp4_wo(b2q_handle h, const uint8_t* codes, const voi
     // E8M0 scales: the tcgen05 block-scaled kernel (weights never touch a CUDA core) where its fixed cost pays:
     // from 16 MiB of codes with 4 tokens or more or with enough rows for one tile per SM (no partial sums to
     // exchange), from 40 MiB otherwise.  B2Q_GEMV_MX=1 / 0 forces it on / off.
-    const char* mxe = getenv("B2Q_GEMV_MX");
     const int64_t code_bytes = N * (K / 2);
     const bool mx_pays = code_bytes >= ((int64_t)40 << 20) || (code_bytes >= ((int64_t)16 << 20) && (t >= 4 || N >= 13312));
-    if (scale_format == B2Q_SCALE_E8M0 && (mxe ? mxe[0] == '1' : mx_pays)) {
+    if (scale_format == B2Q_SCALE_E8M0 && (h->sw.gemv_mx >= 0 ? h->sw.gemv_mx == 1 : mx_pays)) {
       const int32_t st = b2q_gemv_fp4_mx_dispatch(h, codes, scales, x_bf16, t, N, K, out, out_type);
       if (st != B2Q_ERR_UNSUPPORTED) return st;
     }
   }
   if (t <= 8) {
     // experiment switch: B2Q_GEMV_CLUSTER=1 takes the cluster split-K kernel for small token counts too
-    const char* force = getenv("B2Q_GEMV_CLUSTER");
-    if (force && force[0] == '1')
+    if (h->sw.gemv_cluster == 1)
       return small_n ? gemv::launch<1, 4>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type)
                      : gemv::launch<1, 8>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type);
     // E8M0 scales: 128-bit-load kernel (scale folded into the f16 codes, exact for powers of two) unless
     // B2Q_GEMV_EXACT=1 asks for the fp32-scaled kernel; f32 scales always take the fp32-scaled kernel.
-    const char* exact = getenv("B2Q_GEMV_EXACT");
     const bool scales16 = (reinterpret_cast<uintptr_t>(scales) & 15) == 0;
-    if (scale_format == B2Q_SCALE_E8M0 && scales16 && !(exact && exact[0] == '1'))
+    if (scale_format == B2Q_SCALE_E8M0 && scales16 && h->sw.gemv_exact != 1)
       return K >= 8192 ? gemv::launch_e8<8>(h, codes, scales, x_bf16, t, N, K, out, out_type)
                        : gemv::launch_e8<4>(h, codes, scales, x_bf16, t, N, K, out, out_type);
     return K >= 8192 ? gemv::launch_small<8>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type)
                      : gemv::launch_small<4>(h, codes, scales, scale_format, x_bf16, t, N, K, out, out_type);
   }
   {
-    const char* exact = getenv("B2Q_GEMV_EXACT");
-    if (scale_format == B2Q_SCALE_E8M0 && !(exact && exact[0] == '1')) {
+    if (scale_format == B2Q_SCALE_E8M0 && h->sw.gemv_exact != 1) {
       if (t <= 16) return small_n ? gemv::launch_e8c<2, 4>(h, codes, scales, x_bf16, t, N, K, out, out_type)
                                   : gemv::launch_e8c<2, 8>(h, codes, scales, x_bf16, t, N, K, out, out_type);
       return small_n ? gemv::launch_e8c<4, 4>(h, codes, scales, x_bf16, t, N, K, out, out_type)

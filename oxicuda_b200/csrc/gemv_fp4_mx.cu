@@ -30,8 +30,7 @@
 // the units are split evenly over the SMs (stream-K): a CTA that owns only part of a tile's K range writes its partial
 // sums to a workspace and the last CTA to arrive at the tile (a counter per tile) adds the partials in CTA order and
 // stores, so results do not depend on arrival order.  Every mbarrier wait is bounded.
-#include "common.cuh"
-#include <cuda.h>
+#include "tc_common.cuh"
 #include <stdlib.h>
 
 namespace mx {
@@ -85,64 +84,9 @@ struct Params {
   int32_t* status;
 };
 
-// ---- PTX wrappers ----------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ uint64_t globaltimer_ns() { uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-  return ok;
-}
-// Bounded wait: false when the limit expired or another role already gave up.
+using namespace tcx;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where = 1) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
-  uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if (((++spins) & 0x3F) == 0) {
-      if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) { *abort_flag = where; return false; }
-    }
-  }
-  return true;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
-  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
-  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t cols) {
-  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-// 32 rows x 16 bytes of shared memory -> 4 TMEM columns, replicated into the four 32-lane quarters
-__device__ __forceinline__ void tmem_cp_sf(uint32_t taddr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+  return mbar_wait_bounded(bar, parity, abort_flag, kWaitLimitNs, where);
 }
 __device__ __forceinline__ void umma_mx(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t tsfa, uint32_t tsfb,
                                         uint32_t accumulate) {
@@ -151,36 +95,6 @@ __device__ __forceinline__ void umma_mx(uint32_t tmem_d, uint64_t adesc, uint64_
       "tcgen05.mma.cta_group::1.kind::mxf8f6f4.block_scale [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(tsfa), "r"(tsfb) : "memory");
 }
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr) : "memory");
-}
-__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
-// K-major tile of 128-byte rows with the 128-byte swizzle: 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-  d |= (uint64_t)1 << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-// Scale-factor atom: 32 rows of 16 bytes, unswizzled, 8-row groups 128 bytes apart.
-__device__ __forceinline__ uint64_t make_desc_sf(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-  d |= (uint64_t)1 << 16;
-  d |= (uint64_t)(128 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  return d;
-}
-
 // ---------------------------------------------------------------------------
 // Activation pre-pass: bf16 [tokens x K] -> per K stage of 128 a block of NB rows x 128 bytes of E4M3 codes
 // (rows 0..MPAD-1 first term, rows MPAD..2*MPAD-1 residual term; 16-byte units XOR-swizzled by row & 7, the
@@ -562,22 +476,6 @@ __global__ void __launch_bounds__(Cfg<MT>::kThreads, 1) gemv_fp4_mx_kernel(const
 }
 
 // ---- host side --------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)sym;
-  }
-  return fn;
-}
-
 static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
 template <int MT, bool INL>
@@ -613,8 +511,8 @@ int32_t launch(b2q_handle h, const uint8_t* codes, const uint8_t* scales, const 
     per = (int)ceil_div64(units, grid);
     grid = (int)ceil_div64(units, per);
   }
-  if (const char* e = getenv("B2Q_MX_STREAMK")) {               // experiment switch: 1 forces the even split over all SMs
-    if (e[0] == '1') { grid = (int)(units < slots ? units : slots); per = (int)ceil_div64(units, grid); grid = (int)ceil_div64(units, per); }
+  if (h->sw.mx_streamk == 1) {                                  // experiment switch: 1 forces the even split over all SMs
+    { grid = (int)(units < slots ? units : slots); per = (int)ceil_div64(units, grid); grid = (int)ceil_div64(units, per); }
   }
   p.max_slots = (S + per - 1) / per + 1;
   const size_t xq_bytes = align256((size_t)S * C::kBytesX);
@@ -638,14 +536,13 @@ int32_t launch(b2q_handle h, const uint8_t* codes, const uint8_t* scales, const 
   // block-scaled instruction descriptor: A = E2M1 (5), B = E4M3 (0), both K-major, N = NB, E8M0 scales, M = 128
   p.idesc = (5u << 7) | (0u << 10) | ((uint32_t)(C::NB >> 3) << 17) | (1u << 23) | ((uint32_t)(TILE_ROWS >> 4) << 24);
   p.wait_first = h->dynamic_weights;
-  if (const char* e = getenv("B2Q_MX_DEBUG")) p.debug = atoi(e);   // 1: report which wait expired as status 400 + role
+  if (h->sw.mx_debug > 0) p.debug = h->sw.mx_debug;            // 1: report which wait expired as status 400 + role
   p.status = h->d_status;
 
-  const char* pdl = getenv("B2Q_MX_PDL");                      // 0: plain stream-ordered launches
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
-  const int num_attrs = (pdl && pdl[0] == '0') ? 0 : 1;
+  const int num_attrs = h->sw.mx_pdl == 0 ? 0 : 1;             // B2Q_MX_PDL=0: plain stream-ordered launches
   if (!INL) {
     cudaLaunchConfig_t pre = {};
     pre.gridDim = dim3((unsigned)S);
@@ -655,11 +552,7 @@ int32_t launch(b2q_handle h, const uint8_t* codes, const uint8_t* scales, const 
     pre.numAttrs = num_attrs;
     B2Q_CUDA(h, cudaLaunchKernelEx(&pre, x_quant_mx_kernel<MT>, (const __nv_bfloat16*)x, tokens, K, reinterpret_cast<uint8_t*>(ws)));
   }
-  static bool attr_set = false;
-  if (!attr_set) {
-    B2Q_CUDA(h, cudaFuncSetAttribute(gemv_fp4_mx_kernel<MT, INL>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem));
-    attr_set = true;
-  }
+  B2Q_SMEM_ATTR(h, (gemv_fp4_mx_kernel<MT, INL>), C::kSmem);
   // programmatic dependent launch: this grid may start while the pre-pass runs; its activation loads wait for it
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
@@ -684,8 +577,8 @@ int32_t b2q_gemv_fp4_mx_dispatch(b2q_handle h, const uint8_t* codes, const void*
     return B2Q_ERR_UNSUPPORTED;
   if (ceil_div64(N, mx::TILE_ROWS) > (int64_t)kTileCounters || ceil_div64(N, mx::TILE_ROWS) * (K / mx::BK) > 0x7FFFFFFF)
     return B2Q_ERR_UNSUPPORTED;
-  const char* inl = getenv("B2Q_MX_INLINE");                   // experiment switch: 0 keeps the pre-pass for every token count
-  if (tokens <= 4 && !(inl && inl[0] == '0')) return mx::launch<1, true>(h, codes, (const uint8_t*)scales, x, tokens, N, K, out, out_type);
+  if (tokens <= 4 && h->sw.mx_inline != 0)                     // B2Q_MX_INLINE=0 keeps the pre-pass for every token count
+    return mx::launch<1, true>(h, codes, (const uint8_t*)scales, x, tokens, N, K, out, out_type);
   if (tokens <= 8) return mx::launch<1, false>(h, codes, (const uint8_t*)scales, x, tokens, N, K, out, out_type);
   if (tokens <= 16) return mx::launch<2, false>(h, codes, (const uint8_t*)scales, x, tokens, N, K, out, out_type);
   return mx::launch<4, false>(h, codes, (const uint8_t*)scales, x, tokens, N, K, out, out_type);

@@ -383,11 +383,7 @@ int32_t launch_small_t(b2q_handle h, const uint32_t* packed, const __half* scale
                        void* out, int out_type) {
   const size_t smem = (size_t)WK * 8192;
   if (smem > 48 * 1024) {
-    static bool attr_set = false;
-    if (!attr_set) {
-      B2Q_CUDA(h, cudaFuncSetAttribute(gemv_int4_small_kernel<WK, TOK, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      attr_set = true;
-    }
+    B2Q_SMEM_ATTR(h, (gemv_int4_small_kernel<WK, TOK, WIDE>), (int)smem);
   }
   gemv_int4_small_kernel<WK, TOK, WIDE><<<(unsigned)ceil_div64(N, 16), WK * 32, smem, h->stream>>>(packed, scales, gsh, (const __nv_bfloat16*)x, tokens,
                                                                                              N, K, out, out_type);
@@ -507,8 +503,7 @@ int32_t b2q_gemv_int4_wo(b2q_handle h, const uint32_t* packed, const void* scale
   // One or two tokens with groups of 64 and up: the prefetching kernel (measured 65.5 against 71.6 us on 8192 x 28672);
   // with more tokens or groups of 32 its registers spill and the cluster kernel is faster (73.7 against 102 us at 4 tokens).
   // B2Q_INT4_SMALL=1 / 0 forces the choice.
-  const char* force_small = getenv("B2Q_INT4_SMALL");
-  if (force_small ? (force_small[0] == '1' && t <= 8) : (t <= 2 && gsh >= 6)) {
+  if (h->sw.int4_small >= 0 ? (h->sw.int4_small == 1 && t <= 8) : (t <= 2 && gsh >= 6)) {
     return k >= 8192 ? i4w::launch_small<8>(h, packed, sc, gsh, x_bf16, t, n, k, out, out_type)
                      : i4w::launch_small<4>(h, packed, sc, gsh, x_bf16, t, n, k, out, out_type);
   }

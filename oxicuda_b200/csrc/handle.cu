@@ -1,5 +1,6 @@
 // Handle lifetime, status word and the host-side tile heuristics of libb2q.
 #include "common.cuh"
+#include <stdlib.h>
 
 int32_t b2q_workspace(b2q_handle h, size_t bytes, void** out) {
   if (bytes > h->ws_bytes) {
@@ -26,6 +27,12 @@ int32_t b2q_create(b2q_handle* out, int device) {
   b2q_handle h = new b2q_handle_s();
   memset(h, 0, sizeof(*h));
   h->device = device;
+  int prev_device = -1;
+  cudaGetDevice(&prev_device);
+  struct RestoreDevice {                                 // the caller's current device is left as it was found
+    int prev;
+    ~RestoreDevice() { if (prev >= 0) cudaSetDevice(prev); }
+  } restore{prev_device};
   cudaDeviceProp prop;
   if (cudaSetDevice(device) != cudaSuccess || cudaGetDeviceProperties(&prop, device) != cudaSuccess) {
     delete h;
@@ -50,18 +57,37 @@ int32_t b2q_create(b2q_handle* out, int device) {
     return B2Q_ERR_CUDA;
   }
   h->stream = nullptr;
+  // experiment switches: read here once, never on the dispatch path
+  auto sw = [](const char* name) { const char* e = getenv(name); return e && e[0] ? (e[0] == 'p' ? 9 : atoi(e)) : -1; };
+  h->sw.no_tail_split = getenv("B2Q_NO_TAIL_SPLIT") ? 1 : -1;
+  h->sw.force_tile = sw("B2Q_FORCE_TILE_N");       // 128 | 256 | p(air)
+  h->sw.fp8_skinny = sw("B2Q_FP8_SKINNY");
+  h->sw.skinny_pdl = sw("B2Q_SKINNY_PDL");
+  h->sw.mx_streamk = sw("B2Q_MX_STREAMK");
+  h->sw.mx_debug = sw("B2Q_MX_DEBUG");
+  h->sw.mx_pdl = sw("B2Q_MX_PDL");
+  h->sw.mx_inline = sw("B2Q_MX_INLINE");
+  h->sw.e8c_db = sw("B2Q_GEMV_E8C_DB");
+  h->sw.gemv_mx = sw("B2Q_GEMV_MX");
+  h->sw.gemv_cluster = sw("B2Q_GEMV_CLUSTER");
+  h->sw.gemv_exact = sw("B2Q_GEMV_EXACT");
+  h->sw.int4_small = sw("B2Q_INT4_SMALL");
+  h->sw.gemv_stream = sw("B2Q_GEMV_STREAM");
   *out = h;
   return B2Q_OK;
 }
 
 int32_t b2q_destroy(b2q_handle h) {
   if (!h) return B2Q_OK;
+  int prev_device = -1;
+  cudaGetDevice(&prev_device);
   cudaSetDevice(h->device);
   cudaFree(h->d_status);
   cudaFree(h->d_scratch);
   cudaFree(h->d_tile_counters);
   if (h->ws) cudaFree(h->ws);
   delete h;
+  if (prev_device >= 0) cudaSetDevice(prev_device);
   return B2Q_OK;
 }
 
@@ -99,6 +125,9 @@ int32_t b2q_check(b2q_handle h) {
   B2Q_CUDA(h, cudaMemcpyAsync(&st, h->d_status, sizeof(st), cudaMemcpyDeviceToHost, h->stream));
   B2Q_CUDA(h, cudaStreamSynchronize(h->stream));
   if (st != 0) {
+    // A kernel that gave up on a bounded wait may have left split-K arrival counters non-zero (its CTAs skip the
+    // arrival): clear them with the status so that the next stream-K launch starts from a clean table.
+    B2Q_CUDA(h, cudaMemsetAsync(h->d_tile_counters, 0, kTileCounters * sizeof(int32_t), h->stream));
     B2Q_CUDA(h, cudaMemsetAsync(h->d_status, 0, sizeof(int32_t), h->stream));
     B2Q_CUDA(h, cudaStreamSynchronize(h->stream));
     B2Q_FAIL(h, st, "device-side validation recorded status %d", (int)st);
@@ -181,7 +210,8 @@ int32_t b2q_select_tile_ex(int dtype, uint32_t m, uint32_t n, uint32_t k, b2q_ti
     return B2Q_OK;
   }
   if (few_token_kernels && dtype == 0 && k % 128 == 0 &&
-      ((m <= 64 && (uint64_t)n * k >= (32ull << 20)) || (m > 8 && m <= 32 && (uint64_t)n * k >= (16ull << 20)))) {
+      ((m <= 64 && (uint64_t)n * k >= (32ull << 20)) || (m > 8 && m <= 32 && (uint64_t)n * k >= (16ull << 20)) ||
+       (m > 32 && m < 64))) {   // 33..63 tokens: too many for the mma.sync GEMV, too few for a 128-row tile
     // FP8, few tokens against a large weight matrix: weight-stationary tcgen05 kernel (weights are the M = 128 operand)
     const uint32_t nb = m <= 16 ? 16u : (m <= 32 ? 32u : 64u);
     *out = b2q_tile_config{nb, 128, 128, 128, nb, 8, 1, 1};

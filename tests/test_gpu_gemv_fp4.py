@@ -94,6 +94,34 @@ def test_codes_map_exactly(cuda, oracle):
         assert np.array_equal(got, want), pos
 
 
+@pytest.mark.parametrize("tokens", [1, 5, 16, 32])
+def test_e8m0_exponents_outside_the_f16_range(cuda, oracle, tokens):
+    """Legal MX tensors whose block exponents cannot be folded into f16 codes: 2^20 and 2^14 (code * scale overflows
+    f16) take the exact fp32 statement inside the kernel, 2^-40 flushes (at most 2^-24 per code).  No status is raised
+    and the result is the oracle's."""
+    from oxicuda_b200._lib import default_handle
+    from oxicuda_b200.blas import gemv_fp4_wo
+    rng = np.random.default_rng(21 + tokens)
+    N, K = 272, 2048
+    codes = rng.integers(0, 256, (N, K // 2)).astype(np.uint8)
+    scales = rng.integers(127 - 9, 127 - 3, (N, K // 32)).astype(np.uint8)
+    scales[3, 5] = 127 + 20
+    scales[100, 0] = 127 + 14
+    scales[271, K // 32 - 1] = 127 + 20
+    scales[7, 9] = 127 - 40
+    scales[8, :] = 127 - 40                          # a whole row of tiny blocks
+    x = torch.from_numpy(rng.standard_normal((tokens, K)).astype(np.float32)).to(torch.bfloat16)
+    xb = x.view(torch.int16).numpy().view(np.uint16)
+    ref = np.asarray(oracle.gemv_fp4(codes.reshape(-1), scales.reshape(-1), xb, tokens, N, K, 32, "f32"), np.float64).reshape(tokens, N)
+    got = gemv_fp4_wo(_t(codes.reshape(-1), cuda), _t(scales.reshape(-1), cuda), x.to(cuda), N, K, out_dtype=torch.float32)
+    default_handle().check()                         # nothing recorded
+    got = got.cpu().numpy().astype(np.float64)
+    # per row: rows with a huge block are dominated by it
+    for n in range(N):
+        scale = np.abs(ref[:, n]).max() + 1e-300
+        assert np.abs(got[:, n] - ref[:, n]).max() <= 2e-3 * scale + 1e-3, n      # flushed blocks: < 2^-24 per code
+
+
 def test_linearity_and_validation(cuda, oracle):
     from oxicuda_b200 import _lib
     from oxicuda_b200.blas import gemv_fp4_wo

@@ -86,7 +86,9 @@ def test_static_tile_table(libb2q):
     t, kid = blas.select_tile("fp8", 8, 4096, 4096)
     assert kid == 5 and t.tile_n == 16                # decode-sized: tensor-core GEMV over the codes
     t, kid = blas.select_tile("fp8", 40, 4096, 4096)
-    assert kid == 0                                   # between the GEMV and a 128-row tile: SIMT path
+    assert kid == 6                                   # between the GEMV and a 128-row tile: weight-stationary tcgen05 kernel
+    t, kid = blas.select_tile("fp8", 40, 4096, 4000)
+    assert kid == 0                                   # K not a multiple of 128 (nor of 16): SIMT path
     t, kid = blas.select_tile("fp8", 4096, 4096, 4100)
     assert kid == 0                                   # row pitch TMA cannot take
     t, kid = blas.select_tile("fp4", 1, 4096, 4096)
