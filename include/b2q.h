@@ -42,7 +42,8 @@ typedef enum {
   B2Q_ERR_NON_FINITE_FP8 = 23,       /* QuantError::NonFiniteFp8 */
   B2Q_ERR_INVALID_CONFIG = 24,       /* QuantError::InvalidConfig / InferError::InvalidConfig */
   B2Q_ERR_INVALID_BIT_WIDTH = 25,    /* QuantError::InvalidBitWidth */
-  B2Q_ERR_TIMEOUT = 40               /* a bounded device-side wait gave up */
+  B2Q_ERR_TIMEOUT = 40,              /* a bounded device-side wait gave up */
+  B2Q_ERR_NCCL = 41                  /* an NCCL call failed, or libnccl could not be resolved (DistInferError::Collective) */
 } b2q_status;
 
 typedef enum { B2Q_FP8_E4M3 = 0, B2Q_FP8_E5M2 = 1 } b2q_fp8_format;  /* Fp8Format, crates/oxicuda-quant/src/scheme/fp8.rs:32-37 */
@@ -60,6 +61,8 @@ typedef enum { B2Q_OUT_BF16 = 0, B2Q_OUT_F32 = 1 } b2q_out_type;
 typedef enum { B2Q_SCALE_SCALAR = 0, B2Q_SCALE_PER_ROW = 1 } b2q_scale_kind;
 
 /* ---- handle: BlasHandle::{new,set_stream,sm_version} crates/oxicuda-blas/src/handle.rs:80-95, :243-255 ---- */
+/* b2q_create / b2q_destroy leave the caller's current device as they found it.  Every other call launches on the
+ * CURRENT device and returns B2Q_ERR_INVALID_ARGUMENT when that is not the handle's device. */
 int32_t b2q_create(b2q_handle* out, int device);
 int32_t b2q_destroy(b2q_handle h);
 /* stream is a cudaStream_t passed as void*; NULL = the legacy default stream */
@@ -285,6 +288,58 @@ int32_t b2q_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M
 int32_t b2q_gemm_fp8_simt(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,
                           int decode_mode, const float* scale_a, int scale_a_kind, const float* scale_w,
                           int scale_w_kind, void* out, int out_type);
+
+/* ---- tensor-parallel linears: ColumnLinear / RowLinear crates/oxicuda-dist-infer/src/tensor_parallel/column_parallel.rs:103-205,
+ *      row_parallel.rs:97-224; DistInferHandle crates/oxicuda-dist-infer/src/handle.rs:62-239.  One rank per process and GPU.
+ * A b2q_tp binds a handle to an NCCL communicator of `tp` ranks (ncclComm_t passed as void*; NCCL is resolved at run
+ * time from the libnccl.so.2 already loaded in the process).  It owns a second stream for overlapped collectives,
+ * grow-only scratch (the first call with a larger shape allocates: warm up before capturing a CUDA graph) and, for
+ * tp > 1, a 36 MiB exchange buffer for the peer-memory all-reduce of few-token results. ---- */
+typedef struct b2q_tp_s* b2q_tp;
+/* Helpers for callers without an NCCL binding of their own: ncclGetUniqueId / ncclCommInitRank (on the current
+ * device) / ncclCommDestroy.  id128: 128 bytes, made on one rank and sent to the others by the caller. */
+int32_t b2q_tp_unique_id(uint8_t* id128);
+int32_t b2q_tp_comm_init(const uint8_t* id128, int tp, int rank, void** nccl_comm);
+int32_t b2q_tp_comm_destroy(void* nccl_comm);
+int32_t b2q_tp_create(b2q_handle h, void* nccl_comm, int tp, int rank, b2q_tp* out);   /* nccl_comm may be NULL for tp = 1 */
+int32_t b2q_tp_destroy(b2q_tp t);
+/* The exchange buffer of this rank: its device pointer and/or its 64-byte CUDA IPC handle.  Every rank sends its
+ * handle to the others (any host channel) and passes the tp handles, in rank order, to b2q_tp_attach_peers; ranks
+ * that share a process pass mapped pointers instead (direct_ptrs[r], peer access enabled by the caller).  Until peers
+ * are attached every row-parallel boundary goes through NCCL. */
+int32_t b2q_tp_exchange_buffer(b2q_tp t, void** ptr, uint8_t* ipc_handle64);
+int32_t b2q_tp_attach_peers(b2q_tp t, const uint8_t* ipc_handles, void* const* direct_ptrs);
+/* Token chunks of the many-token path (0 = automatic, see b2q_tp_plan). */
+int32_t b2q_tp_set_chunks(b2q_tp t, int chunks);
+/* The boundary a row-parallel result of tokens x out_features takes: mode 0 none (tp = 1); 1 one-shot and 2 two-shot
+ * peer-memory kernel (fp32 partials up to 256 KiB / 4 MiB: every rank pushes its partial into its peers' inboxes over
+ * NVLink, waits on per-CTA flags with a one-second limit (B2Q_ERR_TIMEOUT in the status word) and adds the partials in
+ * rank order in fp32, the reference's order, row_parallel.rs:202-223); 3 NCCL all-reduce of bf16 partials in `chunks`
+ * token chunks, chunk i on the second stream while the GEMMs of chunk i + 1 run.  Pure host function. */
+int32_t b2q_tp_plan(int tp, int peers_attached, int64_t tokens, int64_t out_features, int* mode, int* chunks);
+/* Sum over ranks of fp32 partials [n] -> bf16 on every rank through the peer kernel (n % (4 * tp) == 0, n * 4 <= 4 MiB,
+ * peers attached); and the in-place NCCL sum of a bf16 buffer on the handle's stream. */
+int32_t b2q_tp_all_reduce_f32_to_bf16(b2q_tp t, const float* partial, int64_t n, void* y_bf16);
+int32_t b2q_tp_all_reduce_bf16(b2q_tp t, void* y_bf16, int64_t n);
+/* ColumnLinear::forward (column_parallel.rs:168-179): y_local [tokens x out_local] bf16 = x W_s^T + bias_s over this
+ * rank's out/tp rows of W (E4M3 codes, per-token and per-row scales); bias: f32 [out_local] or NULL.  With y_gathered
+ * != NULL also ColumnLinear::all_gather (:181-204): [tokens x out_local * tp], shard r at columns [r * out_local, ...). */
+int32_t b2q_column_linear_forward(b2q_tp t, const uint8_t* x_codes, const float* x_scales, const uint8_t* w_codes,
+                                  const float* w_scales, const float* bias, int64_t tokens, int64_t in_features,
+                                  int64_t out_local, void* y_local, void* y_gathered);
+/* RowLinear::forward + all_reduce (row_parallel.rs:170-223): x_codes [tokens x in_local] is this rank's column slice of
+ * the activations, w_codes [out x in_local] its columns of W; bias (f32 [out] or NULL) is added on rank 0 only (:183-190);
+ * y [tokens x out] bf16 holds the sum over ranks on every rank. */
+int32_t b2q_row_linear_forward_allreduce(b2q_tp t, const uint8_t* x_codes, const float* x_scales, const uint8_t* w_codes,
+                                         const float* w_scales, const float* bias, int64_t tokens, int64_t in_local,
+                                         int64_t out_features, void* y);
+/* SwiGluExpert::forward (crates/oxicuda-moe/src/expert/ffn.rs:208-243) over ColumnLinear (gate | up, one GEMM over the
+ * concatenated [2 * ffn_local x hidden] shard) and RowLinear (down [hidden x ffn_local]): x bf16 [tokens x hidden] is
+ * quantized per token (absmax / 448), h = silu(gate) * up is re-quantized per token over this rank's columns,
+ * y bf16 [tokens x hidden] is the sum over ranks. */
+int32_t b2q_mlp_swiglu_fp8_forward(b2q_tp t, const void* x_bf16, const uint8_t* w_gate_up, const float* s_gate_up,
+                                   const uint8_t* w_down, const float* s_down, int64_t tokens, int64_t hidden,
+                                   int64_t ffn_local, int rounding, void* y_bf16);
 
 /* ---- grouped GEMM: grouped_gemm / GroupedGemmProblem crates/oxicuda-blas/src/batched/grouped_gemm.rs:46-78 ----
  * One FP8 GEMM per entry of a host-side problem table (an expert and the tokens routed to it); entries with m == 0 are

@@ -15,7 +15,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libb2q.so"
-SOURCES = ["handle.cu", "quant.cu", "kv_cache.cu", "norm_quant.cu", "dnn_quant.cu", "int8.cu", "gemm_fp8_simt.cu", "gemm_tc.cu", "gemv_fp4.cu", "gemv_fp4_mx.cu", "gemv_int4.cu", "gemv_fp8.cu", "gemm_fp8_skinny.cu", "moe.cu", "gemm_fp4.cu"]
+SOURCES = ["handle.cu", "quant.cu", "kv_cache.cu", "norm_quant.cu", "dnn_quant.cu", "int8.cu", "gemm_fp8_simt.cu", "gemm_tc.cu", "gemv_fp4.cu", "gemv_fp4_mx.cu", "gemv_int4.cu", "gemv_fp8.cu", "gemm_fp8_skinny.cu", "moe.cu", "gemm_fp4.cu", "tp.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",
@@ -33,7 +33,7 @@ def _stale() -> bool:
     if not LIB.exists():
         return True
     t = LIB.stat().st_mtime
-    deps = [CSRC / s for s in SOURCES] + [CSRC / "common.cuh", PKG.parent / "include" / "b2q.h"]
+    deps = [CSRC / s for s in SOURCES] + [CSRC / "common.cuh", CSRC / "tc_common.cuh", PKG.parent / "include" / "b2q.h"]
     return any(d.stat().st_mtime > t for d in deps)
 
 
@@ -58,7 +58,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
 
     with ThreadPoolExecutor(max_workers=min(8, len(SOURCES))) as ex:
         objs = list(ex.map(compile_one, SOURCES))
-    r = subprocess.run([nvcc, "-shared", "-o", str(LIB), *objs, "-cudart", "static"], capture_output=True, text=True)
+    r = subprocess.run([nvcc, "-shared", "-o", str(LIB), *objs, "-cudart", "static", "-ldl"], capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stderr}")
     return LIB

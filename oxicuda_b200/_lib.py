@@ -21,6 +21,7 @@ ERR_UNSUPPORTED, ERR_LAUNCH_FAILED, ERR_INVALID_ARGUMENT = 5, 7, 8
 ERR_EMPTY_INPUT, ERR_GROUP_SIZE_MISMATCH, ERR_INVALID_SCALE, ERR_NON_FINITE_FP8, ERR_INVALID_CONFIG = 20, 21, 22, 23, 24
 ERR_INVALID_BIT_WIDTH = 25
 ERR_TIMEOUT = 40
+ERR_NCCL = 41
 
 FP8_E4M3, FP8_E5M2 = 0, 1
 ROUND_REF, ROUND_RNE = 0, 1
@@ -55,6 +56,7 @@ class NonFiniteFp8(B2qError): pass
 class InvalidConfig(B2qError): pass
 class InvalidBitWidth(B2qError): pass
 class DeviceTimeout(B2qError): pass
+class CollectiveError(B2qError): pass
 
 
 _ERRORS = {
@@ -62,7 +64,7 @@ _ERRORS = {
     ERR_DIMENSION_MISMATCH: DimensionMismatch, ERR_UNSUPPORTED: UnsupportedOperation, ERR_LAUNCH_FAILED: LaunchFailed,
     ERR_INVALID_ARGUMENT: InvalidArgument, ERR_EMPTY_INPUT: EmptyInput, ERR_GROUP_SIZE_MISMATCH: GroupSizeMismatch,
     ERR_INVALID_SCALE: InvalidScale, ERR_NON_FINITE_FP8: NonFiniteFp8, ERR_INVALID_CONFIG: InvalidConfig,
-    ERR_INVALID_BIT_WIDTH: InvalidBitWidth, ERR_TIMEOUT: DeviceTimeout,
+    ERR_INVALID_BIT_WIDTH: InvalidBitWidth, ERR_TIMEOUT: DeviceTimeout, ERR_NCCL: CollectiveError,
 }
 
 
@@ -148,6 +150,20 @@ SIGNATURES = {
     "b2q_ep_token_gather_bf16": (C.c_int32, [_H, _P, _P, _P, _I64, _I, _I64, _P]),
     "b2q_gemv_fp4_wo": (C.c_int32, [_H, _P, _P, _I, _I, _P, _I64, _I64, _I64, _P, _I]),
     "b2q_gemm_fp4_wo": (C.c_int32, [_H, _P, _P, _I, _I, _I, _P, _I64, _I64, _I64, _P, _I]),
+    "b2q_tp_unique_id": (C.c_int32, [_P]),
+    "b2q_tp_comm_init": (C.c_int32, [_P, _I, _I, C.POINTER(_P)]),
+    "b2q_tp_comm_destroy": (C.c_int32, [_P]),
+    "b2q_tp_create": (C.c_int32, [_H, _P, _I, _I, C.POINTER(_P)]),
+    "b2q_tp_destroy": (C.c_int32, [_P]),
+    "b2q_tp_exchange_buffer": (C.c_int32, [_P, C.POINTER(_P), _P]),
+    "b2q_tp_attach_peers": (C.c_int32, [_P, _P, _P]),
+    "b2q_tp_set_chunks": (C.c_int32, [_P, _I]),
+    "b2q_tp_plan": (C.c_int32, [_I, _I, _I64, _I64, C.POINTER(_I), C.POINTER(_I)]),
+    "b2q_tp_all_reduce_f32_to_bf16": (C.c_int32, [_P, _P, _I64, _P]),
+    "b2q_tp_all_reduce_bf16": (C.c_int32, [_P, _P, _I64]),
+    "b2q_column_linear_forward": (C.c_int32, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _P]),
+    "b2q_row_linear_forward_allreduce": (C.c_int32, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P]),
+    "b2q_mlp_swiglu_fp8_forward": (C.c_int32, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I, _P]),
     "b2q_classify_workload": (C.c_int32, [_U32, _U32, _U32]),
     "b2q_ref_tile_config": (C.c_int32, [_I, _U32, _U32, _U32, C.POINTER(TileConfig)]),
     "b2q_fp8_compute_split_k": (_U32, [_U32, _U32, _U32]),

@@ -1,0 +1,549 @@
+// Tensor-parallel linears behind the C ABI: ColumnLinear / RowLinear of oxicuda-dist-infer
+// (crates/oxicuda-dist-infer/src/tensor_parallel/column_parallel.rs:103-205, row_parallel.rs:97-224) and the
+// SwiGLU MLP built from them (SwiGluExpert::forward, crates/oxicuda-moe/src/expert/ffn.rs:208-243), one rank per
+// process and GPU.  The reference sums partials in rank order on the host; here the row-parallel boundary is
+//   * for few tokens (partial sums up to 4 MiB of fp32): ONE kernel over peer-mapped memory.  Every rank pushes its
+//     fp32 partial into the other ranks' inboxes with plain NVLink stores, signals per-CTA flags, waits (bounded)
+//     for its peers and adds the inboxes IN RANK ORDER in fp32 (the reference's order, the same bits on every rank).
+//     Above 256 KiB the exchange is two-shot: each rank reduces one slice and pushes the bf16 result to all.
+//     The buffer parity and the flag epoch live in device memory, so the launch can be captured in a CUDA graph;
+//   * for many tokens: the tokens are cut into chunks, and the NCCL all-reduce of chunk i runs on a second stream
+//     while the GEMMs of chunk i + 1 run on the handle's stream.
+// NCCL is resolved at run time from the library already loaded in the process (no link-time dependency).
+#include "common.cuh"
+#include <dlfcn.h>
+#include <stdlib.h>
+
+namespace tpx {
+
+// ---- NCCL entry points (declared here: the ABI of these calls is stable across NCCL 2.x) -------------------
+typedef void* nccl_comm_t;
+struct nccl_unique_id { char internal[128]; };
+enum { kNcclUint8 = 1, kNcclFloat32 = 7, kNcclBfloat16 = 9, kNcclSum = 0 };
+struct NcclApi {
+  int (*GetUniqueId)(nccl_unique_id*);
+  int (*CommInitRank)(nccl_comm_t*, int, nccl_unique_id, int);
+  int (*CommDestroy)(nccl_comm_t);
+  int (*AllReduce)(const void*, void*, size_t, int, int, nccl_comm_t, cudaStream_t);
+  int (*AllGather)(const void*, void*, size_t, int, nccl_comm_t, cudaStream_t);
+  const char* (*GetErrorString)(int);
+  bool ok;
+};
+static NcclApi* nccl() {
+  static NcclApi api = {};
+  static bool tried = false;
+  if (!tried) {
+    tried = true;
+    void* lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);     // the copy the process already uses (torch's, the caller's)
+    if (!lib) lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+    if (!lib) lib = dlopen("libnccl.so", RTLD_NOW | RTLD_GLOBAL);
+    if (lib) {
+      api.GetUniqueId = (int (*)(nccl_unique_id*))dlsym(lib, "ncclGetUniqueId");
+      api.CommInitRank = (int (*)(nccl_comm_t*, int, nccl_unique_id, int))dlsym(lib, "ncclCommInitRank");
+      api.CommDestroy = (int (*)(nccl_comm_t))dlsym(lib, "ncclCommDestroy");
+      api.AllReduce = (int (*)(const void*, void*, size_t, int, int, nccl_comm_t, cudaStream_t))dlsym(lib, "ncclAllReduce");
+      api.AllGather = (int (*)(const void*, void*, size_t, int, nccl_comm_t, cudaStream_t))dlsym(lib, "ncclAllGather");
+      api.GetErrorString = (const char* (*)(int))dlsym(lib, "ncclGetErrorString");
+      api.ok = api.GetUniqueId && api.CommInitRank && api.CommDestroy && api.AllReduce && api.AllGather;
+    }
+  }
+  return &api;
+}
+
+// ---- exchange buffer layout (one per rank, cudaMalloc'ed, mapped into every peer) ---------------------------
+constexpr int kMaxRanks = 8;
+constexpr int kMaxCtas = 64;                                  // CTAs of the exchange kernel (same on every rank)
+constexpr size_t kFlagBytes = 8192;                           // flags[2 barriers][kMaxCtas][kMaxRanks] u32 = 4 KiB, epoch[kMaxCtas] u32
+constexpr size_t kOneShotMax = 256 << 10;                     // fp32 partial bytes up to which every rank receives every partial
+constexpr size_t kTwoShotMax = 4 << 20;                       // fp32 partial bytes up to which the peer kernel is used at all
+constexpr size_t kSlotBytes = kTwoShotMax / 2;                // inbox slot per (parity, source rank): a two-shot slice (<= 4 MiB / 2 ranks)
+constexpr size_t kInboxBytes = 2 * kMaxRanks * kSlotBytes;    // 32 MiB
+constexpr size_t kResultBytes = 2 * (kTwoShotMax / 2);        // bf16 result per parity
+constexpr size_t kXbufBytes = kFlagBytes + kInboxBytes + kResultBytes;
+constexpr uint64_t kWaitLimitNs = 1000000000ull;
+
+struct Peers { uint8_t* base[kMaxRanks]; };
+
+__device__ __forceinline__ uint64_t globaltimer_ns() { uint64_t t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) { uint32_t v; asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory"); return v; }
+
+__device__ __forceinline__ uint32_t* flag_ptr(uint8_t* base, int which, int cta, int src) {
+  return reinterpret_cast<uint32_t*>(base) + (which * kMaxCtas + cta) * kMaxRanks + src;
+}
+__device__ __forceinline__ uint32_t* epoch_ptr(uint8_t* base, int cta) { return reinterpret_cast<uint32_t*>(base + 4096) + cta; }
+__device__ __forceinline__ float4* inbox_ptr(uint8_t* base, int parity, int src) {
+  return reinterpret_cast<float4*>(base + kFlagBytes + ((size_t)parity * kMaxRanks + src) * kSlotBytes);
+}
+__device__ __forceinline__ uint2* result_ptr(uint8_t* base, int parity) {
+  return reinterpret_cast<uint2*>(base + kFlagBytes + kInboxBytes + (size_t)parity * (kTwoShotMax / 2));
+}
+
+// CTA-level barrier with the same CTA of every peer: everything this CTA stored before is visible to the peers'
+// CTA after their wait.  Returns false when a peer did not arrive within the limit.
+__device__ __forceinline__ bool peer_barrier(const Peers& peers, int tp, int rank, int which, uint32_t e, int* s_abort) {
+  __threadfence_system();
+  __syncthreads();
+  const int cta = blockIdx.x;
+  if ((int)threadIdx.x < tp) {
+    st_release_sys(flag_ptr(peers.base[threadIdx.x], which, cta, rank), e);
+    const uint32_t* mine = flag_ptr(peers.base[rank], which, cta, threadIdx.x);
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while ((int32_t)(ld_acquire_sys(mine) - e) < 0) {
+      if (((++spins) & 0xFF) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) { *s_abort = 1; break; }
+    }
+  }
+  __syncthreads();
+  return *s_abort == 0;
+}
+
+__device__ __forceinline__ uint2 pack4_bf16(float4 v) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+  return make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+}
+
+// partial: this rank's fp32 partial sums, n4 float4 elements; y: bf16 result (n4 * 4 elements).
+template <bool TWO_SHOT>
+__global__ void __launch_bounds__(512, 1) tp_allreduce_push_kernel(const Peers peers, int tp, int rank, const float4* __restrict__ partial,
+                                                                    int64_t n4, uint2* __restrict__ y, int32_t* status) {
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) s_abort = 0;
+  const int cta = blockIdx.x, G = gridDim.x;
+  uint8_t* my = peers.base[rank];
+  const uint32_t e = *epoch_ptr(my, cta) + 1;                  // written only by this CTA of the previous launch
+  const int parity = (int)(e & 1u);
+  __syncthreads();
+  bool ok = true;
+  if constexpr (!TWO_SHOT) {
+    const int64_t per = (n4 + G - 1) / G, i0 = cta * per, i1 = min(n4, i0 + per);
+    for (int r = 0; r < tp; ++r) {                             // push this CTA's range into every rank's inbox (own rank: a local copy)
+      float4* dst = inbox_ptr(peers.base[r], parity, rank);
+      for (int64_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) dst[i] = partial[i];
+    }
+    ok = peer_barrier(peers, tp, rank, 0, e, &s_abort);
+    if (ok) {
+      for (int64_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
+        float4 acc = __ldcg(inbox_ptr(my, parity, 0) + i);
+        for (int r = 1; r < tp; ++r) {                         // rank order: the reference's summation order
+          const float4 v = __ldcg(inbox_ptr(my, parity, r) + i);
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        y[i] = pack4_bf16(acc);
+      }
+    }
+  } else {
+    const int64_t slice = n4 / tp;                             // n4 is a multiple of tp (checked by the host)
+    const int64_t per = (slice + G - 1) / G, i0 = cta * per, i1 = min(slice, i0 + per);
+    for (int r = 0; r < tp; ++r) {                             // slice r of my partial -> rank r
+      float4* dst = inbox_ptr(peers.base[r], parity, rank);
+      const float4* src = partial + r * slice;
+      for (int64_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) dst[i] = src[i];
+    }
+    ok = peer_barrier(peers, tp, rank, 0, e, &s_abort);
+    if (ok) {
+      for (int64_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
+        float4 acc = __ldcg(inbox_ptr(my, parity, 0) + i);
+        for (int r = 1; r < tp; ++r) {
+          const float4 v = __ldcg(inbox_ptr(my, parity, r) + i);
+          acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        const uint2 pk = pack4_bf16(acc);
+        for (int r = 0; r < tp; ++r) result_ptr(peers.base[r], parity)[rank * slice + i] = pk;   // my slice of the result -> everyone
+      }
+      ok = peer_barrier(peers, tp, rank, 1, e, &s_abort);
+    }
+    if (ok) {
+      const uint2* res = result_ptr(my, parity);
+      for (int r = 0; r < tp; ++r)
+        for (int64_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) y[r * slice + i] = __ldcg(res + r * slice + i);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    *epoch_ptr(my, cta) = e;
+    if (!ok) atomicCAS(status, 0, (int)B2Q_ERR_TIMEOUT);
+  }
+}
+
+// y[t, c] += bias[c]  (bf16 rows, f32 bias)
+__global__ void __launch_bounds__(256) bias_add_bf16_kernel(__nv_bfloat16* __restrict__ y, const float* __restrict__ bias, int64_t rows, int64_t cols) {
+  const int64_t total = rows * cols;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x)
+    y[i] = __float2bfloat16_rn(__bfloat162float(y[i]) + bias[i % cols]);
+}
+__global__ void __launch_bounds__(256) bias_add_f32_kernel(float* __restrict__ y, const float* __restrict__ bias, int64_t rows, int64_t cols) {
+  const int64_t total = rows * cols;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) y[i] += bias[i % cols];
+}
+// gathered[t, r * local + c] = parts[r][t][c]  (16-byte pieces; local * 2 bytes is a multiple of 16)
+__global__ void __launch_bounds__(256) gather_columns_kernel(const uint4* __restrict__ parts, uint4* __restrict__ out, int tp, int64_t rows,
+                                                             int64_t local_vec) {
+  const int64_t total = (int64_t)tp * rows * local_vec;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t c = i % local_vec, t = (i / local_vec) % rows, r = i / (local_vec * rows);
+    out[(t * tp + r) * local_vec + c] = parts[i];
+  }
+}
+
+}  // namespace tpx
+
+struct b2q_tp_s {
+  b2q_handle h;
+  tpx::nccl_comm_t comm;
+  int tp, rank;
+  int chunks;                      // token chunks of the many-token path (0 = choose by size)
+  cudaStream_t comm_stream;
+  cudaEvent_t ev_ready[16], ev_done;
+  uint8_t* xbuf;                   // this rank's exchange buffer
+  tpx::Peers peers;                // every rank's exchange buffer as mapped here
+  int attached;
+  // grow-only scratch of the MLP / linears
+  void* scratch;
+  size_t scratch_bytes;
+};
+
+namespace tpx {
+
+static int32_t scratch(b2q_tp t, size_t bytes, uint8_t** out) {
+  if (bytes > t->scratch_bytes) {
+    b2q_handle h = t->h;
+    B2Q_CUDA(h, cudaStreamSynchronize(h->stream));
+    B2Q_CUDA(h, cudaStreamSynchronize(t->comm_stream));
+    if (t->scratch) cudaFree(t->scratch);
+    t->scratch = nullptr;
+    t->scratch_bytes = 0;
+    B2Q_CUDA(h, cudaMalloc(&t->scratch, bytes));
+    t->scratch_bytes = bytes;
+  }
+  *out = reinterpret_cast<uint8_t*>(t->scratch);
+  return B2Q_OK;
+}
+static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+// Sum of the ranks' fp32 partials [n floats] -> bf16 y on every rank, through the peer kernel.
+static int32_t peer_allreduce(b2q_tp t, const float* partial, int64_t n, void* y) {
+  b2q_handle h = t->h;
+  const size_t bytes = (size_t)n * 4;
+  const bool two = bytes > kOneShotMax;
+  const int64_t n4 = n / 4;
+  int grid = (int)((n4 + 511) / 512);
+  if (two) grid = (int)((n4 / t->tp + 511) / 512);
+  grid = grid < 1 ? 1 : (grid > kMaxCtas ? kMaxCtas : grid);
+  if (two)
+    tp_allreduce_push_kernel<true><<<grid, 512, 0, h->stream>>>(t->peers, t->tp, t->rank, (const float4*)partial, n4, (uint2*)y, h->d_status);
+  else
+    tp_allreduce_push_kernel<false><<<grid, 512, 0, h->stream>>>(t->peers, t->tp, t->rank, (const float4*)partial, n4, (uint2*)y, h->d_status);
+  B2Q_LAUNCH_CHECK(h, "tp_allreduce_push_kernel");
+  return B2Q_OK;
+}
+static bool peer_path_fits(b2q_tp t, int64_t n) {
+  return t->attached && n % (4 * t->tp) == 0 && (size_t)n * 4 <= kTwoShotMax && ((size_t)n * 4 / t->tp) <= kSlotBytes;
+}
+
+static int32_t add_bias(b2q_handle h, void* y, int out_type, const float* bias, int64_t rows, int64_t cols) {
+  if (!bias) return B2Q_OK;
+  const int64_t total = rows * cols;
+  int grid = (int)((total + 255) / 256);
+  if (grid > h->sm_count * 8) grid = h->sm_count * 8;
+  if (out_type == B2Q_OUT_BF16) bias_add_bf16_kernel<<<grid, 256, 0, h->stream>>>((__nv_bfloat16*)y, bias, rows, cols);
+  else bias_add_f32_kernel<<<grid, 256, 0, h->stream>>>((float*)y, bias, rows, cols);
+  B2Q_LAUNCH_CHECK(h, "bias_add_kernel");
+  return B2Q_OK;
+}
+
+}  // namespace tpx
+
+#define B2Q_REQUIRE_TP(t)                                                 \
+  do {                                                                    \
+    if (!(t) || !(t)->h) return (int32_t)B2Q_ERR_INVALID_ARGUMENT;        \
+    B2Q_REQUIRE_HANDLE((t)->h);                                           \
+  } while (0)
+#define B2Q_NCCL(h, expr)                                                                                       \
+  do {                                                                                                          \
+    int _r = (expr);                                                                                            \
+    if (_r != 0) B2Q_FAIL(h, B2Q_ERR_NCCL, "%s: %s", #expr, tpx::nccl()->GetErrorString ? tpx::nccl()->GetErrorString(_r) : "NCCL error"); \
+  } while (0)
+
+extern "C" {
+
+int32_t b2q_tp_unique_id(uint8_t* id128) {
+  if (!id128 || !tpx::nccl()->ok) return B2Q_ERR_NCCL;
+  tpx::nccl_unique_id id;
+  if (tpx::nccl()->GetUniqueId(&id) != 0) return B2Q_ERR_NCCL;
+  memcpy(id128, id.internal, 128);
+  return B2Q_OK;
+}
+
+int32_t b2q_tp_comm_init(const uint8_t* id128, int tp, int rank, void** comm) {
+  if (!id128 || !comm || tp < 1 || rank < 0 || rank >= tp || !tpx::nccl()->ok) return B2Q_ERR_NCCL;
+  tpx::nccl_unique_id id;
+  memcpy(id.internal, id128, 128);
+  tpx::nccl_comm_t c = nullptr;
+  if (tpx::nccl()->CommInitRank(&c, tp, id, rank) != 0) return B2Q_ERR_NCCL;
+  *comm = c;
+  return B2Q_OK;
+}
+
+int32_t b2q_tp_comm_destroy(void* comm) {
+  if (!comm) return B2Q_OK;
+  return tpx::nccl()->ok && tpx::nccl()->CommDestroy(comm) == 0 ? B2Q_OK : B2Q_ERR_NCCL;
+}
+
+int32_t b2q_tp_create(b2q_handle h, void* nccl_comm, int tp, int rank, b2q_tp* out) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (!out) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "tp_create: null output");
+  *out = nullptr;
+  if (tp < 1 || tp > tpx::kMaxRanks || rank < 0 || rank >= tp)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "tp_create: tp must be in [1, %d] and rank in [0, tp), got tp=%d rank=%d", tpx::kMaxRanks, tp, rank);
+  if (tp > 1 && !nccl_comm) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "tp_create: a communicator is required for tp > 1");
+  if (tp > 1 && !tpx::nccl()->ok) B2Q_FAIL(h, B2Q_ERR_NCCL, "tp_create: libnccl.so.2 could not be resolved in this process");
+  b2q_tp t = new b2q_tp_s();
+  memset(t, 0, sizeof(*t));
+  t->h = h; t->comm = nccl_comm; t->tp = tp; t->rank = rank;
+  const char* ce = getenv("B2Q_TP_CHUNKS");
+  t->chunks = ce ? atoi(ce) : 0;
+  bool ok = cudaStreamCreateWithFlags(&t->comm_stream, cudaStreamNonBlocking) == cudaSuccess;
+  for (int i = 0; i < 16 && ok; ++i) ok = cudaEventCreateWithFlags(&t->ev_ready[i], cudaEventDisableTiming) == cudaSuccess;
+  ok = ok && cudaEventCreateWithFlags(&t->ev_done, cudaEventDisableTiming) == cudaSuccess;
+  if (ok && tp > 1) {
+    ok = cudaMalloc(&t->xbuf, tpx::kXbufBytes) == cudaSuccess && cudaMemset(t->xbuf, 0, tpx::kFlagBytes) == cudaSuccess;
+    t->peers.base[rank] = t->xbuf;
+  }
+  if (!ok) {
+    b2q_tp_destroy(t);
+    B2Q_FAIL(h, B2Q_ERR_CUDA, "tp_create: stream, event or exchange-buffer creation failed: %s", cudaGetErrorString(cudaGetLastError()));
+  }
+  *out = t;
+  return B2Q_OK;
+}
+
+int32_t b2q_tp_destroy(b2q_tp t) {
+  if (!t) return B2Q_OK;
+  if (t->comm_stream) { cudaStreamSynchronize(t->comm_stream); cudaStreamDestroy(t->comm_stream); }
+  for (int i = 0; i < 16; ++i) if (t->ev_ready[i]) cudaEventDestroy(t->ev_ready[i]);
+  if (t->ev_done) cudaEventDestroy(t->ev_done);
+  if (t->attached == 1) {
+    for (int r = 0; r < t->tp; ++r) if (r != t->rank && t->peers.base[r]) cudaIpcCloseMemHandle(t->peers.base[r]);
+  }
+  if (t->xbuf) cudaFree(t->xbuf);
+  if (t->scratch) cudaFree(t->scratch);
+  delete t;
+  return B2Q_OK;
+}
+
+int32_t b2q_tp_set_chunks(b2q_tp t, int chunks) {
+  B2Q_REQUIRE_TP(t);
+  if (chunks < 0 || chunks > 16) B2Q_FAIL(t->h, B2Q_ERR_INVALID_ARGUMENT, "tp_set_chunks: 0 (automatic) to 16, got %d", chunks);
+  t->chunks = chunks;
+  return B2Q_OK;
+}
+
+int32_t b2q_tp_exchange_buffer(b2q_tp t, void** ptr, uint8_t* ipc_handle64) {
+  B2Q_REQUIRE_TP(t);
+  if (t->tp == 1) B2Q_FAIL(t->h, B2Q_ERR_UNSUPPORTED, "tp_exchange_buffer: a single rank has no exchange buffer");
+  if (ptr) *ptr = t->xbuf;
+  if (ipc_handle64) {
+    cudaIpcMemHandle_t hd;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    B2Q_CUDA(t->h, cudaIpcGetMemHandle(&hd, t->xbuf));
+    memcpy(ipc_handle64, &hd, 64);
+  }
+  return B2Q_OK;
+}
+
+int32_t b2q_tp_attach_peers(b2q_tp t, const uint8_t* ipc_handles, void* const* direct_ptrs) {
+  B2Q_REQUIRE_TP(t);
+  if (t->tp == 1) return B2Q_OK;
+  if (t->attached) B2Q_FAIL(t->h, B2Q_ERR_INVALID_ARGUMENT, "tp_attach_peers: peers are attached already");
+  if (!ipc_handles && !direct_ptrs) B2Q_FAIL(t->h, B2Q_ERR_INVALID_ARGUMENT, "tp_attach_peers: pass IPC handles or mapped pointers");
+  for (int r = 0; r < t->tp; ++r) {
+    if (r == t->rank) continue;
+    if (direct_ptrs) {
+      t->peers.base[r] = reinterpret_cast<uint8_t*>(direct_ptrs[r]);
+    } else {
+      cudaIpcMemHandle_t hd;
+      memcpy(&hd, ipc_handles + 64 * r, 64);
+      void* p = nullptr;
+      B2Q_CUDA(t->h, cudaIpcOpenMemHandle(&p, hd, cudaIpcMemLazyEnablePeerAccess));
+      t->peers.base[r] = reinterpret_cast<uint8_t*>(p);
+    }
+    if (!t->peers.base[r]) B2Q_FAIL(t->h, B2Q_ERR_INVALID_ARGUMENT, "tp_attach_peers: no mapping for rank %d", r);
+  }
+  t->attached = direct_ptrs ? 2 : 1;
+  return B2Q_OK;
+}
+
+// Which boundary a row-parallel result of `tokens` x `out_features` takes: 0 none (tp = 1), 1 one-shot peer kernel,
+// 2 two-shot peer kernel, 3 NCCL in `chunks` token chunks overlapped with the GEMMs.
+int32_t b2q_tp_plan(int tp, int peers_attached, int64_t tokens, int64_t out_features, int* mode, int* chunks) {
+  if (!mode || !chunks || tp < 1 || tokens < 1 || out_features < 1) return B2Q_ERR_INVALID_ARGUMENT;
+  *chunks = 1;
+  if (tp == 1) { *mode = 0; return B2Q_OK; }
+  const int64_t n = tokens * out_features;
+  const size_t bytes = (size_t)n * 4;
+  if (peers_attached && n % (4 * tp) == 0 && bytes <= tpx::kTwoShotMax) {
+    *mode = bytes <= tpx::kOneShotMax ? 1 : 2;
+    return B2Q_OK;
+  }
+  *mode = 3;
+  // chunks of at least 512 tokens, a multiple of 256 tokens each so that GEMM tiles stay whole; at most 8
+  int c = (int)(tokens / 1024);
+  c = c < 1 ? 1 : (c > 8 ? 8 : c);
+  while (c > 1 && (tokens % c != 0 || (tokens / c) % 256 != 0)) --c;
+  *chunks = c;
+  return B2Q_OK;
+}
+
+int32_t b2q_tp_all_reduce_f32_to_bf16(b2q_tp t, const float* partial, int64_t n, void* y_bf16) {
+  B2Q_REQUIRE_TP(t);
+  b2q_handle h = t->h;
+  if (!partial || !y_bf16 || n <= 0) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "tp_all_reduce: bad argument");
+  if (t->tp == 1 || !tpx::peer_path_fits(t, n))
+    B2Q_FAIL(h, B2Q_ERR_UNSUPPORTED, "tp_all_reduce_f32_to_bf16: needs attached peers, n %% (4 * tp) == 0 and at most %zu bytes of partials", tpx::kTwoShotMax);
+  return tpx::peer_allreduce(t, partial, n, y_bf16);
+}
+
+int32_t b2q_tp_all_reduce_bf16(b2q_tp t, void* y_bf16, int64_t n) {
+  B2Q_REQUIRE_TP(t);
+  if (t->tp == 1) return B2Q_OK;
+  if (!y_bf16 || n <= 0) B2Q_FAIL(t->h, B2Q_ERR_INVALID_ARGUMENT, "tp_all_reduce: bad argument");
+  B2Q_NCCL(t->h, tpx::nccl()->AllReduce(y_bf16, y_bf16, (size_t)n, tpx::kNcclBfloat16, tpx::kNcclSum, t->comm, t->h->stream));
+  return B2Q_OK;
+}
+
+// ColumnLinear::forward (column_parallel.rs:168-179): y_local = x W_s^T + b_s over this rank's out/tp rows of W;
+// with y_gathered != NULL also ColumnLinear::all_gather (:181-204): shard r lands at columns [r * out_local, ...).
+int32_t b2q_column_linear_forward(b2q_tp t, const uint8_t* x_codes, const float* x_scales, const uint8_t* w_codes, const float* w_scales,
+                                  const float* bias, int64_t tokens, int64_t in_features, int64_t out_local, void* y_local,
+                                  void* y_gathered) {
+  B2Q_REQUIRE_TP(t);
+  b2q_handle h = t->h;
+  int32_t st = b2q_gemm_fp8(h, x_codes, w_codes, tokens, out_local, in_features, B2Q_FP8_E4M3, x_scales, B2Q_SCALE_PER_ROW, w_scales,
+                            B2Q_SCALE_PER_ROW, y_local, B2Q_OUT_BF16);
+  if (st != B2Q_OK) return st;
+  st = tpx::add_bias(h, y_local, B2Q_OUT_BF16, bias, tokens, out_local);
+  if (st != B2Q_OK || !y_gathered) return st;
+  if (t->tp == 1) {
+    B2Q_CUDA(h, cudaMemcpyAsync(y_gathered, y_local, (size_t)tokens * out_local * 2, cudaMemcpyDeviceToDevice, h->stream));
+    return B2Q_OK;
+  }
+  if ((out_local * 2) % 16 != 0) B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "column_linear_forward: out_local must be a multiple of 8 to gather");
+  uint8_t* parts = nullptr;
+  const size_t part_bytes = (size_t)tokens * out_local * 2;
+  st = tpx::scratch(t, part_bytes * t->tp, &parts);
+  if (st != B2Q_OK) return st;
+  B2Q_NCCL(h, tpx::nccl()->AllGather(y_local, parts, part_bytes, tpx::kNcclUint8, t->comm, h->stream));
+  const int64_t total = (int64_t)t->tp * tokens * (out_local * 2 / 16);
+  int grid = (int)((total + 255) / 256);
+  if (grid > h->sm_count * 8) grid = h->sm_count * 8;
+  tpx::gather_columns_kernel<<<grid, 256, 0, h->stream>>>((const uint4*)parts, (uint4*)y_gathered, t->tp, tokens, out_local * 2 / 16);
+  B2Q_LAUNCH_CHECK(h, "gather_columns_kernel");
+  return B2Q_OK;
+}
+
+// One token range of a row-parallel linear and its boundary.  x_codes / x_scales / y point at the range.
+static int32_t row_linear_range(b2q_tp t, const uint8_t* x_codes, const float* x_scales, const uint8_t* w_codes, const float* w_scales,
+                                const float* bias, int64_t tokens, int64_t in_local, int64_t out_features, void* y, int mode,
+                                float* partial_f32) {
+  b2q_handle h = t->h;
+  const float* b = t->rank == 0 ? bias : nullptr;             // RowLinear adds the bias on rank 0 only (row_parallel.rs:183-190)
+  if (mode == 1 || mode == 2) {
+    int32_t st = b2q_gemm_fp8(h, x_codes, w_codes, tokens, out_features, in_local, B2Q_FP8_E4M3, x_scales, B2Q_SCALE_PER_ROW, w_scales,
+                              B2Q_SCALE_PER_ROW, partial_f32, B2Q_OUT_F32);
+    if (st != B2Q_OK) return st;
+    st = tpx::add_bias(h, partial_f32, B2Q_OUT_F32, b, tokens, out_features);
+    if (st != B2Q_OK) return st;
+    return tpx::peer_allreduce(t, partial_f32, tokens * out_features, y);
+  }
+  int32_t st = b2q_gemm_fp8(h, x_codes, w_codes, tokens, out_features, in_local, B2Q_FP8_E4M3, x_scales, B2Q_SCALE_PER_ROW, w_scales,
+                            B2Q_SCALE_PER_ROW, y, B2Q_OUT_BF16);
+  if (st != B2Q_OK) return st;
+  return tpx::add_bias(h, y, B2Q_OUT_BF16, b, tokens, out_features);
+}
+
+// RowLinear::forward + all_reduce (row_parallel.rs:170-223): y = sum over ranks of x_s W_s^T (+ bias once).
+int32_t b2q_row_linear_forward_allreduce(b2q_tp t, const uint8_t* x_codes, const float* x_scales, const uint8_t* w_codes,
+                                         const float* w_scales, const float* bias, int64_t tokens, int64_t in_local, int64_t out_features,
+                                         void* y) {
+  B2Q_REQUIRE_TP(t);
+  b2q_handle h = t->h;
+  if (tokens <= 0 || in_local <= 0 || out_features <= 0)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "row_linear_forward: dimensions must be non-zero: tokens=%lld, in=%lld, out=%lld", (long long)tokens,
+             (long long)in_local, (long long)out_features);
+  int mode = 0, chunks = 1;
+  b2q_tp_plan(t->tp, t->attached, tokens, out_features, &mode, &chunks);
+  if (t->chunks > 0 && mode == 3 && tokens % t->chunks == 0) chunks = t->chunks;
+  uint8_t* ws = nullptr;
+  if (mode == 1 || mode == 2) {
+    int32_t st = tpx::scratch(t, (size_t)tokens * out_features * 4, &ws);
+    if (st != B2Q_OK) return st;
+  }
+  if (mode != 3) return row_linear_range(t, x_codes, x_scales, w_codes, w_scales, bias, tokens, in_local, out_features, y, mode, (float*)ws);
+  const int64_t ct = tokens / chunks;
+  for (int c = 0; c < chunks; ++c) {
+    uint8_t* yc = reinterpret_cast<uint8_t*>(y) + (size_t)c * ct * out_features * 2;
+    int32_t st = row_linear_range(t, x_codes + (size_t)c * ct * in_local, x_scales + c * ct, w_codes, w_scales, bias, ct, in_local,
+                                  out_features, yc, 3, nullptr);
+    if (st != B2Q_OK) return st;
+    B2Q_CUDA(h, cudaEventRecord(t->ev_ready[c], h->stream));
+    B2Q_CUDA(h, cudaStreamWaitEvent(t->comm_stream, t->ev_ready[c], 0));
+    B2Q_NCCL(h, tpx::nccl()->AllReduce(yc, yc, (size_t)ct * out_features, tpx::kNcclBfloat16, tpx::kNcclSum, t->comm, t->comm_stream));
+  }
+  B2Q_CUDA(h, cudaEventRecord(t->ev_done, t->comm_stream));
+  B2Q_CUDA(h, cudaStreamWaitEvent(h->stream, t->ev_done, 0));
+  return B2Q_OK;
+}
+
+// The tensor-parallel SwiGLU MLP: per-token E4M3 quantization of x, gate|up column-parallel GEMM (one GEMM over the
+// concatenated [2 * ffn_local x hidden] shard), SwiGLU + per-token re-quantization over this rank's columns, down
+// row-parallel GEMM, sum over ranks.  y: bf16 [tokens x hidden], the same on every rank.
+int32_t b2q_mlp_swiglu_fp8_forward(b2q_tp t, const void* x_bf16, const uint8_t* w_gate_up, const float* s_gate_up, const uint8_t* w_down,
+                                   const float* s_down, int64_t tokens, int64_t hidden, int64_t ffn_local, int rounding, void* y_bf16) {
+  B2Q_REQUIRE_TP(t);
+  b2q_handle h = t->h;
+  if (tokens <= 0 || hidden <= 0 || ffn_local <= 0)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "mlp_swiglu_fp8_forward: dimensions must be non-zero: tokens=%lld, hidden=%lld, ffn=%lld",
+             (long long)tokens, (long long)hidden, (long long)ffn_local);
+  if (!x_bf16 || !w_gate_up || !s_gate_up || !w_down || !s_down || !y_bf16) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "mlp_swiglu_fp8_forward: null operand");
+  int mode = 0, chunks = 1;
+  b2q_tp_plan(t->tp, t->attached, tokens, hidden, &mode, &chunks);
+  if (t->chunks > 0 && mode == 3 && tokens % t->chunks == 0) chunks = t->chunks;
+  const int64_t ct = tokens / chunks;
+  const int64_t F = ffn_local;
+  // scratch: x codes + scales (all tokens), then per chunk: gate|up bf16, h codes + scales, fp32 partial (peer modes)
+  const size_t o_xc = 0, o_xs = o_xc + tpx::align256((size_t)tokens * hidden), o_gu = o_xs + tpx::align256((size_t)tokens * 4),
+               o_hc = o_gu + tpx::align256((size_t)ct * 2 * F * 2), o_hs = o_hc + tpx::align256((size_t)ct * F),
+               o_pf = o_hs + tpx::align256((size_t)ct * 4),
+               total = o_pf + ((mode == 1 || mode == 2) ? tpx::align256((size_t)tokens * hidden * 4) : 0);
+  uint8_t* ws = nullptr;
+  int32_t st = tpx::scratch(t, total, &ws);
+  if (st != B2Q_OK) return st;
+  uint8_t* xc = ws + o_xc; float* xs = (float*)(ws + o_xs);
+  uint8_t* gu = ws + o_gu; uint8_t* hc = ws + o_hc; float* hs = (float*)(ws + o_hs); float* pf = (float*)(ws + o_pf);
+  st = b2q_fp8_quantize_rows_bf16(h, x_bf16, tokens, hidden, B2Q_FP8_E4M3, rounding, xs, xc);
+  if (st != B2Q_OK) return st;
+  for (int c = 0; c < chunks; ++c) {
+    const uint8_t* xcc = xc + (size_t)c * ct * hidden;
+    uint8_t* yc = reinterpret_cast<uint8_t*>(y_bf16) + (size_t)c * ct * hidden * 2;
+    st = b2q_gemm_fp8(h, xcc, w_gate_up, ct, 2 * F, hidden, B2Q_FP8_E4M3, xs + c * ct, B2Q_SCALE_PER_ROW, s_gate_up, B2Q_SCALE_PER_ROW, gu,
+                      B2Q_OUT_BF16);
+    if (st != B2Q_OK) return st;
+    st = b2q_swiglu_quantize_rows_bf16(h, gu, gu + (size_t)F * 2, ct, F, 2 * F, B2Q_FP8_E4M3, rounding, hs, hc);
+    if (st != B2Q_OK) return st;
+    st = row_linear_range(t, hc, hs, w_down, s_down, nullptr, ct, F, hidden, yc, mode, pf);
+    if (st != B2Q_OK) return st;
+    if (mode == 3) {
+      B2Q_CUDA(h, cudaEventRecord(t->ev_ready[c], h->stream));
+      B2Q_CUDA(h, cudaStreamWaitEvent(t->comm_stream, t->ev_ready[c], 0));
+      B2Q_NCCL(h, tpx::nccl()->AllReduce(yc, yc, (size_t)ct * hidden, tpx::kNcclBfloat16, tpx::kNcclSum, t->comm, t->comm_stream));
+    }
+  }
+  if (mode == 3) {
+    B2Q_CUDA(h, cudaEventRecord(t->ev_done, t->comm_stream));
+    B2Q_CUDA(h, cudaStreamWaitEvent(h->stream, t->ev_done, 0));
+  }
+  return B2Q_OK;
+}
+
+}  // extern "C"

@@ -3,8 +3,8 @@
 The reference simulates ranks in one thread and its collectives are Vec sums
 (`crates/oxicuda-dist-infer/src/tensor_parallel/{column,row}_parallel.rs`); here each rank is a
 process on its own GPU, shards are quantized weights in HBM, the matmuls are the FP8 kernels of
-libb2q and the only collective is one NCCL all-reduce (row-parallel boundary) or all-gather
-(column-parallel boundary) over NVLink, issued through torch.distributed.
+libb2q and the boundary collectives run inside libb2q (b2q_tp_*, include/b2q.h): a peer-memory all-reduce kernel for few tokens,
+NCCL overlapped with the GEMMs for many; torch.distributed only carries the set-up messages.
 """
 from __future__ import annotations
 
@@ -65,6 +65,89 @@ def row_shard_cols(in_features: int, tp: int, rank: int):
     return rank * li, (rank + 1) * li
 
 
+class TpGroup:
+    """b2q_tp (include/b2q.h): the library handle bound to an NCCL communicator of the tp ranks, a second stream for
+    overlapped collectives and the peer-mapped exchange buffers of the few-token all-reduce kernel.
+
+    The communicator is created here through the library's own helpers: rank 0 of the group draws the NCCL unique
+    id, torch.distributed carries it (and the CUDA IPC handles of the exchange buffers) to the other ranks."""
+
+    def __init__(self, handle: DistInferHandle, attach_peers: bool = True):
+        import ctypes as C
+        self.handle = handle
+        self.tp, self.rank = handle.config.tp, handle.tp_rank()
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self._lib = L.lib()
+        self._h = L.default_handle()
+        self._comm = C.c_void_p(0)
+        self._t = C.c_void_p(0)
+        group = handle.group
+        if self.tp > 1:
+            src = dist.get_global_rank(group, 0) if group is not None else 0
+            ident = torch.zeros(128, dtype=torch.uint8, device=self.device)
+            if self.rank == 0:
+                buf = (C.c_uint8 * 128)()
+                self._check(self._lib.b2q_tp_unique_id(buf), "b2q_tp_unique_id")
+                ident.copy_(torch.frombuffer(bytearray(buf), dtype=torch.uint8))
+            dist.broadcast(ident, src=src, group=group)
+            idb = (C.c_uint8 * 128).from_buffer_copy(bytes(ident.cpu().numpy().tobytes()))
+            self._check(self._lib.b2q_tp_comm_init(idb, self.tp, self.rank, C.byref(self._comm)), "b2q_tp_comm_init")
+        st = self._lib.b2q_tp_create(self._h._h, self._comm, self.tp, self.rank, C.byref(self._t))
+        self._check(st, "b2q_tp_create")
+        self.peers_attached = False
+        if self.tp > 1 and attach_peers:
+            hd = (C.c_uint8 * 64)()
+            self._check(self._lib.b2q_tp_exchange_buffer(self._t, None, hd), "b2q_tp_exchange_buffer")
+            mine = torch.frombuffer(bytearray(hd), dtype=torch.uint8).to(self.device)
+            every = [torch.empty_like(mine) for _ in range(self.tp)]
+            dist.all_gather(every, mine, group=group)
+            flat = b"".join(bytes(t.cpu().numpy().tobytes()) for t in every)
+            arr = (C.c_uint8 * len(flat)).from_buffer_copy(flat)
+            self._check(self._lib.b2q_tp_attach_peers(self._t, arr, None), "b2q_tp_attach_peers")
+            self.peers_attached = True
+
+    def _check(self, st: int, what: str):
+        if st != L.OK:
+            msg = self._lib.b2q_last_error(self._h._h)
+            raise L._ERRORS.get(st, L.B2qError)(st, (msg.decode() if msg else "") or what)
+
+    def call(self, name: str, *args):
+        L.default_handle()                                   # the handle follows torch's current stream
+        self._check(getattr(self._lib, name)(self._t, *args), name)
+
+    def set_chunks(self, chunks: int):
+        self.call("b2q_tp_set_chunks", chunks)
+
+    def plan(self, tokens: int, out_features: int):
+        """(mode, chunks) of b2q_tp_plan for a row-parallel result of this shape."""
+        import ctypes as C
+        mode, chunks = C.c_int(0), C.c_int(0)
+        st = self._lib.b2q_tp_plan(self.tp, 1 if self.peers_attached else 0, tokens, out_features, C.byref(mode), C.byref(chunks))
+        self._check(st, "b2q_tp_plan")
+        return mode.value, chunks.value
+
+    def close(self):
+        if getattr(self, "_t", None) and self._t.value:
+            torch.cuda.synchronize()
+            self._lib.b2q_tp_destroy(self._t)
+            self._t.value = 0
+        if getattr(self, "_comm", None) and self._comm.value:
+            self._lib.b2q_tp_comm_destroy(self._comm)
+            self._comm.value = 0
+
+
+_groups = {}
+
+
+def tp_group(handle: DistInferHandle) -> TpGroup:
+    """One TpGroup per (process group, tp, rank, device), created on first use (a collective call when tp > 1)."""
+    key = (id(handle.group), handle.config.tp, handle.tp_rank(), torch.cuda.current_device())
+    g = _groups.get(key)
+    if g is None:
+        g = _groups[key] = TpGroup(handle)
+    return g
+
+
 class Fp8Linear:
     """One shard of a linear layer held as E4M3 codes with per-output-row scales.
     forward(x_codes, x_scales) -> bf16 [tokens x local_out]."""
@@ -82,19 +165,31 @@ class Fp8Linear:
 
 
 class ColumnLinear:
-    """ColumnLinear (column_parallel.rs:103-205): this rank owns out/tp consecutive rows of W[out x in]."""
+    """ColumnLinear (column_parallel.rs:103-205): this rank owns out/tp consecutive rows of W[out x in] and of the bias."""
 
-    def __init__(self, full_weight: torch.Tensor, handle: DistInferHandle, rounding: str = "rne"):
+    def __init__(self, full_weight: torch.Tensor, handle: DistInferHandle, rounding: str = "rne", bias: torch.Tensor = None):
         self.handle = handle
         self.total_out = full_weight.shape[0]
         r0, r1 = column_shard_rows(self.total_out, handle.config.tp, handle.tp_rank())
         self.shard = Fp8Linear(full_weight[r0:r1], rounding)
+        self.bias = None if bias is None else bias[r0:r1].float().contiguous()
+
+    def forward(self, x_codes, x_scales, gather: bool = False) -> torch.Tensor:
+        """b2q_column_linear_forward: the local output [tokens x out/tp], or with gather=True the gathered
+        [tokens x out] (column_parallel.rs:181-204: shard r lands at columns [r*out/tp, ...))."""
+        tokens = x_codes.shape[0]
+        local = torch.empty(tokens, self.shard.out_features, dtype=torch.bfloat16, device=x_codes.device)
+        full = torch.empty(tokens, self.total_out, dtype=torch.bfloat16, device=x_codes.device) if gather else None
+        tp_group(self.handle).call("b2q_column_linear_forward", L.ptr(x_codes), L.ptr(x_scales), L.ptr(self.shard.codes),
+                                   L.ptr(self.shard.scales), L.ptr(self.bias), tokens, self.shard.in_features,
+                                   self.shard.out_features, L.ptr(local), L.ptr(full))
+        return full if gather else local
 
     def local_forward(self, x_codes, x_scales) -> torch.Tensor:
-        return self.shard.forward(x_codes, x_scales)
+        return self.forward(x_codes, x_scales)
 
     def all_gather(self, local: torch.Tensor) -> torch.Tensor:
-        """column_parallel.rs:181-204: shard r lands at columns [r*out/tp, ...)."""
+        """column_parallel.rs:181-204 on an existing local result (torch.distributed)."""
         tp = self.handle.config.tp
         if tp == 1:
             return local
@@ -104,29 +199,42 @@ class ColumnLinear:
 
 
 class RowLinear:
-    """RowLinear (row_parallel.rs:97-224): this rank owns in/tp consecutive columns of every row."""
+    """RowLinear (row_parallel.rs:97-224): this rank owns in/tp consecutive columns of every row; the bias is added
+    on rank 0 only (row_parallel.rs:183-190)."""
 
-    def __init__(self, full_weight: torch.Tensor, handle: DistInferHandle, rounding: str = "rne"):
+    def __init__(self, full_weight: torch.Tensor, handle: DistInferHandle, rounding: str = "rne", bias: torch.Tensor = None):
         self.handle = handle
         self.total_in = full_weight.shape[1]
         c0, c1 = row_shard_cols(self.total_in, handle.config.tp, handle.tp_rank())
         self.cols = (c0, c1)
         self.shard = Fp8Linear(full_weight[:, c0:c1].contiguous(), rounding)
+        self.bias = None if bias is None else bias.float().contiguous()
+
+    def forward(self, x_codes, x_scales, out: torch.Tensor = None) -> torch.Tensor:
+        """b2q_row_linear_forward_allreduce: x_codes is this rank's column slice [tokens x in/tp]; returns the sum over
+        ranks [tokens x out] (peer-memory kernel for few tokens, chunked NCCL all-reduce overlapped with the GEMM
+        otherwise; neither sums in NCCL's order nor bit for bit in the host's, hence a tolerance in the tests)."""
+        tokens = x_codes.shape[0]
+        y = out if out is not None else torch.empty(tokens, self.shard.out_features, dtype=torch.bfloat16, device=x_codes.device)
+        tp_group(self.handle).call("b2q_row_linear_forward_allreduce", L.ptr(x_codes), L.ptr(x_scales), L.ptr(self.shard.codes),
+                                   L.ptr(self.shard.scales), L.ptr(self.bias), tokens, self.shard.in_features,
+                                   self.shard.out_features, L.ptr(y))
+        return y
 
     def forward_partial(self, x_codes, x_scales, out=None) -> torch.Tensor:
         return self.shard.forward(x_codes, x_scales, out=out)
 
     def all_reduce(self, partial: torch.Tensor) -> torch.Tensor:
-        """row_parallel.rs:202-223 sums partials in rank order; NCCL's order differs, so results agree
-        to a tolerance, not bit for bit."""
+        """row_parallel.rs:202-223 on an existing partial, in place (NCCL on the handle's stream)."""
         if self.handle.config.tp > 1:
-            dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.handle.group)
+            tp_group(self.handle).call("b2q_tp_all_reduce_bf16", L.ptr(partial), partial.numel())
         return partial
 
 
 class TpFp8Mlp:
     """Tensor-parallel SwiGLU MLP with FP8 weights: gate and up column-parallel (fused into one GEMM over the
-    concatenated shard), down row-parallel, one all-reduce after the down projection.
+    concatenated shard), down row-parallel, the sum over ranks after the down projection
+    (b2q_mlp_swiglu_fp8_forward).
 
     Semantics: SwiGluExpert::forward (crates/oxicuda-moe/src/expert/ffn.rs:208-243) with the linears sharded as
     ColumnLinear / RowLinear do (crates/oxicuda-dist-infer/src/tensor_parallel/*.rs).  Activations are quantized
@@ -158,7 +266,8 @@ class TpFp8Mlp:
         return self
 
     def forward_partial(self, x: torch.Tensor) -> torch.Tensor:
-        """x bf16 [tokens x hidden] (replicated) -> this rank's partial of the output, bf16 [tokens x hidden]."""
+        """x bf16 [tokens x hidden] (replicated) -> this rank's partial of the output, bf16 [tokens x hidden]
+        (separate library calls; forward() is the fused entry point)."""
         from ._lib import default_handle, ptr
         tokens = x.shape[0]
         xc, xs = self.codec.quantize_rows(x, tokens, self.hidden)
@@ -170,10 +279,12 @@ class TpFp8Mlp:
                               L.FP8_E4M3, self.codec.rounding, ptr(hs), ptr(hc))
         return self.down.forward(hc, hs)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        y = self.forward_partial(x)
-        if self.handle.config.tp > 1:
-            dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.handle.group)
+    def forward(self, x: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
+        tokens = x.shape[0]
+        y = out if out is not None else torch.empty(tokens, self.hidden, dtype=torch.bfloat16, device=x.device)
+        tp_group(self.handle).call("b2q_mlp_swiglu_fp8_forward", L.ptr(x), L.ptr(self.gate_up.codes), L.ptr(self.gate_up.scales),
+                                   L.ptr(self.down.codes), L.ptr(self.down.scales), tokens, self.hidden, self.local_ffn,
+                                   self.codec.rounding, L.ptr(y))
         return y
 
 

@@ -1,4 +1,7 @@
-"""Worker of tests/test_gpu_tp_mlp.py::test_mlp_tp2_two_ranks: one NCCL rank per GPU."""
+"""Worker of tests/test_gpu_tp_mlp.py::test_mlp_tp2_two_ranks: one NCCL rank per GPU.  Checks, against the oracle
+composition with the ranks simulated in order, the tensor-parallel MLP through b2q_mlp_swiglu_fp8_forward on every
+boundary the library has (one-shot and two-shot peer-memory kernel, chunked NCCL all-reduce overlapped with the
+GEMMs), a CUDA-graph replay of the few-token step, and ColumnLinear / RowLinear with a bias."""
 import os
 import sys
 from pathlib import Path
@@ -18,22 +21,91 @@ def main():
     dev = torch.device("cuda", int(os.environ["LOCAL_RANK"]))
     dist.init_process_group("nccl", device_id=dev)
     from oracle import api
-    from oxicuda_b200.dist_infer import DistInferHandle, ParallelismConfig, TpFp8Mlp
+    api.set_threads(max(1, len(os.sched_getaffinity(0)) // world))      # the launcher exports OMP_NUM_THREADS=1
+    from oxicuda_b200._lib import default_handle
+    from oxicuda_b200.dist_infer import ColumnLinear, DistInferHandle, ParallelismConfig, RowLinear, TpFp8Mlp, tp_group
+    from oxicuda_b200.quant import Fp8Codec
     from test_gpu_tp_mlp import make_inputs, oracle_mlp, rel_err
-    tokens, hidden, ffn = 64, 512, 2048
-    x, wg, wu, wd = make_inputs(tokens, hidden, ffn)
+    hidden, ffn = 512, 2048
+    handle = DistInferHandle(rank, ParallelismConfig(tp=world))
+    group = tp_group(handle)
     t = lambda a: torch.from_numpy(a).to(dev)
-    mlp = TpFp8Mlp(t(wg), t(wu), t(wd), DistInferHandle(rank, ParallelismConfig(tp=world)))
-    y = mlp.forward(t(x).to(torch.bfloat16)).float().cpu().numpy()
-    ref = oracle_mlp(api, x, wg, wu, wd, world)
-    err = rel_err(y, ref)
-    ok = torch.tensor([1 if err <= 1e-2 else 0], device=dev)
+    results = {}
+    modes = {}
+    for tokens in (1, 64, 200, 4096):
+        x, wg, wu, wd = make_inputs(tokens, hidden, ffn)      # the weights depend on the token count (one random stream)
+        mlp = TpFp8Mlp(t(wg), t(wu), t(wd), handle)
+        xd = t(x).to(torch.bfloat16)
+        y = mlp.forward(xd).float().cpu().numpy()
+        default_handle().check()
+        ref = oracle_mlp(api, x, wg, wu, wd, world)
+        results[f"mlp_m{tokens}"] = rel_err(y, ref)
+        modes[tokens] = group.plan(tokens, hidden)
+        if tokens == 64:                                   # the few-token step from a CUDA graph, replayed
+            out = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=dev)
+            s = torch.cuda.Stream()
+            s.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(s):
+                mlp.forward(xd, out=out)
+            torch.cuda.current_stream().wait_stream(s)
+            torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                mlp.forward(xd, out=out)
+            for _ in range(3):
+                out.zero_()
+                g.replay()
+            torch.cuda.synchronize()
+            default_handle().check()
+            results["mlp_m64_graph_replay"] = rel_err(out.float().cpu().numpy(), ref)
+    # ColumnLinear / RowLinear with a bias against the reference's f32 statement over the dequantized operands
+    rng = np.random.default_rng(5)
+    batch, in_f, out_f = 24, 512, 768
+    w = (rng.standard_normal((out_f, in_f)) * 0.05).astype(np.float32)
+    bias = rng.standard_normal(out_f).astype(np.float32)
+    xf = rng.standard_normal((batch, in_f)).astype(np.float32)
+    codec = Fp8Codec.e4m3("rne")
+    col = ColumnLinear(t(w), handle, bias=t(bias))
+    xc, xs = codec.quantize_rows(t(xf), batch, in_f)
+    y_col = col.forward(xc.view(batch, in_f), xs, gather=True).float().cpu().numpy()
+    x_deq = (api.fp8_decode(xc.cpu().numpy().reshape(-1), 0, 1).reshape(batch, in_f) * xs.cpu().numpy()[:, None]).astype(np.float32)
+    wc_full, ws_full, _ = api.fp8_quantize_rows(w, out_f, in_f, 0, 1)
+    w_deq = (api.fp8_decode(wc_full, 0, 1).reshape(out_f, in_f) * ws_full[:, None]).astype(np.float32)
+    ref_col = api.column_linear(x_deq, w_deq, bias, batch, in_f, out_f, world)
+    results["column_linear_bias_gather"] = rel_err(y_col, ref_col)
+    # row-parallel: this rank's input columns; weight scales are per output row over the LOCAL columns
+    row = RowLinear(t(w), handle, bias=t(bias))
+    c0, c1 = row.cols
+    xl = np.ascontiguousarray(xf[:, c0:c1])
+    xlc, xls = codec.quantize_rows(t(xl), batch, c1 - c0)
+    y_row = row.forward(xlc.view(batch, c1 - c0), xls).float().cpu().numpy()
+    # reference over the per-rank dequantized slices (every rank can rebuild all of them: same seed everywhere)
+    x_parts, w_parts = [], []
+    li = in_f // world
+    for r in range(world):
+        xr = np.ascontiguousarray(xf[:, r * li:(r + 1) * li])
+        c, s_, _ = api.fp8_quantize_rows(xr, batch, li, 0, 1)
+        x_parts.append(api.fp8_decode(c, 0, 1).reshape(batch, li) * s_[:, None])
+        wr = np.ascontiguousarray(w[:, r * li:(r + 1) * li])
+        c, s_, _ = api.fp8_quantize_rows(wr, out_f, li, 0, 1)
+        w_parts.append(api.fp8_decode(c, 0, 1).reshape(out_f, li) * s_[:, None])
+    ref_row = api.row_linear(np.concatenate(x_parts, 1).astype(np.float32), np.concatenate(w_parts, 1).astype(np.float32), bias, batch,
+                             in_f, out_f, world)
+    results["row_linear_bias_allreduce"] = rel_err(y_row, ref_row)
+
+    worst = max(results.values())
+    ok = torch.tensor([1 if worst <= 1e-2 else 0], device=dev)
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    expect_modes = {1: 1, 64: 1, 200: 2, 4096: 3}            # 4096 x 512 fp32 partials = 8 MiB: NCCL in 4 overlapped chunks
+    modes_ok = all(modes[k][0] == v for k, v in expect_modes.items()) and modes[4096][1] == 4
     if rank == 0:
-        print(f"rel_err {err:.3e}")
-        print("TP2 OK" if int(ok.item()) == 1 else "TP2 FAIL")
+        for k, v in results.items():
+            print(f"{k}: rel_err {v:.3e}")
+        print("boundary modes (mode, chunks):", modes)
+        print("TP2 OK" if int(ok.item()) == 1 and modes_ok else "TP2 FAIL")
+    group.close()
     dist.destroy_process_group()
-    sys.exit(0 if int(ok.item()) == 1 else 1)
+    sys.exit(0 if int(ok.item()) == 1 and modes_ok else 1)
 
 
 if __name__ == "__main__":
