@@ -237,8 +237,10 @@ def main():
     wg = torch.randn(FFN, HIDDEN, device=dev, generator=g) * 0.01
     wu = torch.randn(FFN, HIDDEN, device=dev, generator=g) * 0.01
     wd = torch.randn(HIDDEN, FFN, device=dev, generator=g) * 0.01
-    mlp = TpFp8Mlp(wg, wu, wd, handle, args.rounding)
-    mlp_full = TpFp8Mlp(wg, wu, wd, DistInferHandle(0, ParallelismConfig(tp=1)), args.rounding) if world > 1 else mlp
+    # every rank's shard, quantized exactly as that rank quantizes it: this rank's own is the layer under test, the
+    # others let it rebuild the whole sharded computation locally as the parity reference
+    shards = [TpFp8Mlp(wg, wu, wd, DistInferHandle(r, ParallelismConfig(tp=world)), args.rounding) for r in range(world)]
+    mlp = shards[rank]
     del wg, wu, wd
     torch.cuda.empty_cache()
     group = tp_group(handle)
@@ -262,6 +264,8 @@ def main():
     if rank == 0:
         sampler.start()
         time.sleep(0.25)
+    if world > 1:
+        dist.barrier()                                     # nobody enters the timed region while rank 0 starts the sampler
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
@@ -316,19 +320,23 @@ def main():
     gemm_tflops = gemm_flop / gemm_sec / 1e12
     del gu, xc, xsc
 
-    # ---- parity of the sharded result on every rank: against the un-sharded layer on the same GPU (64 and 4096 tokens)
-    # and, rank 0, against the oracle composition with the ranks simulated in order (first 8 of the 64 tokens) ----
+    # ---- parity of the sharded result, on every rank: against the same sharded computation redone locally (every
+    # rank's partial from that rank's own codes, added in rank order in fp32; 64 and 4096 tokens) and, rank 0, against
+    # the CPU oracle's composition over the same codes with the ranks simulated in order (first 8 of the 64 tokens) ----
     tp_summary = {"tp": world, "m4096_us": ms_per_step * 1e3, "timing_m4096": "CUDA events over the timed steps, max over ranks"}
     parity = {}
     x64 = xs_[2][:64].contiguous()
     y64 = mlp.forward(x64)
     y4096 = mlp.forward(xs_[2])
     if world > 1:
-        r64 = mlp_full.forward(x64)
-        r4096 = mlp_full.forward(xs_[2])
-        parity["m64_vs_unsharded"] = _rel_err(y64, r64)
-        parity["m4096_vs_unsharded"] = _rel_err(y4096, r4096)
-        del r4096
+        def local_sum(xin):
+            tot = None
+            for sh in shards:
+                part = sh.forward_partial(xin).float()
+                tot = part if tot is None else tot + part
+            return tot.to(torch.bfloat16)
+        parity["m64_vs_local_rank_order_sum"] = _rel_err(y64, local_sum(x64))
+        parity["m4096_vs_local_rank_order_sum"] = _rel_err(y4096, local_sum(xs_[2]))
     y64_host = y64.float().cpu()
     default_handle().check()
     # decode-sized steps, timed the same way at every tp: CUDA-graph replay of 4 steps (the peer-memory all-reduce is a
@@ -352,7 +360,7 @@ def main():
     tp_summary["boundary"] = {f"m{tk}": dict(zip(("mode", "chunks"), group.plan(tk, HIDDEN))) for tk in (1, 64, 4096)}
     if rank == 0:
         try:
-            parity["m64_first8_vs_oracle"] = oracle_mlp_check(mlp_full, x64[:8], y64_host[:8], world, args.rounding)
+            parity["m64_first8_vs_oracle"] = oracle_mlp_check(shards, x64[:8], y64_host[:8], args.rounding)
         except Exception as exc:                           # noqa: BLE001
             parity["oracle_error"] = repr(exc)
     worst = max([v for v in parity.values() if isinstance(v, float)] or [0.0])
@@ -369,7 +377,7 @@ def main():
     extras = {}
     roof_extra = {}
     if not args.no_extras and rank == 0:
-        del mlp_full
+        shards.clear()
         xs_.clear(); ys_.clear()
         torch.cuda.empty_cache()
         try:
@@ -420,36 +428,26 @@ def main():
         dist.destroy_process_group()
 
 
-def oracle_mlp_check(mlp_full, x_dev, y_host, tp, rounding):
-    """rel. error of y (the sharded layer's result for the tokens of x) against the oracle composition: per-token E4M3
-    quantizer, k-ascending fp32 GEMMs over the layer's own codes, SwiGLU, per-rank re-quantization, rank-ordered sum."""
+def oracle_mlp_check(shards, x_dev, y_host, rounding):
+    """rel. error of y (the sharded layer's result for the tokens of x) against the oracle composition over the ranks'
+    own codes: per-token E4M3 quantizer, k-ascending fp32 GEMMs, SwiGLU, per-rank re-quantization, rank-ordered sum."""
     import numpy as np
     import torch
     from oracle import api
+    api.set_threads(len(os.sched_getaffinity(0)))
     mode = 1 if rounding == "rne" else 0
     tokens, hidden = x_dev.shape
     x = x_dev.float().cpu().numpy()
-    wgu, sgu = mlp_full.gate_up.codes.cpu().numpy(), mlp_full.gate_up.scales.cpu().numpy()
-    wd, sd_full = mlp_full.down.codes.cpu().numpy(), None
-    ffn = wgu.shape[0] // 2
-    F = ffn // tp
     xc, xs, _ = api.fp8_quantize_rows(x, tokens, hidden, 0, mode)
-    bf = lambda a: torch.from_numpy(np.ascontiguousarray(a, np.float32)).to(torch.bfloat16).float().numpy()
     total = None
-    for r in range(tp):
-        rows = np.concatenate([np.arange(r * F, (r + 1) * F), ffn + np.arange(r * F, (r + 1) * F)])
-        gu = api.gemm_fp8(xc.reshape(tokens, hidden), np.ascontiguousarray(wgu[rows]), xs, np.ascontiguousarray(sgu[rows]), 0, 1, "bf16")
+    for sh in shards:
+        F = sh.local_ffn
+        gu = api.gemm_fp8(xc.reshape(tokens, hidden), sh.gate_up.codes.cpu().numpy(), xs, sh.gate_up.scales.cpu().numpy(), 0, 1, "bf16")
         h = api.swiglu(gu[:, :F], gu[:, F:])
         hc, hs, _ = api.fp8_quantize_rows(h, tokens, F, 0, mode)
-        # the sharded layer quantizes its down-projection columns per output row over the LOCAL columns: rebuild that
-        # from the dequantized full-width weights is not bit-identical, so the oracle re-quantizes the f32 slice the
-        # same way the layer did (decode(full codes) * full scale -> per-row absmax over the slice)
-        wslice = (api.fp8_decode(np.ascontiguousarray(wd[:, r * F:(r + 1) * F]).reshape(-1), 0, 1).reshape(hidden, F)
-                  * mlp_full.down.scales.cpu().numpy()[:, None]).astype(np.float32)
-        wdc, wds, _ = api.fp8_quantize_rows(wslice, hidden, F, 0, mode)
-        part = api.gemm_fp8(hc.reshape(tokens, F), wdc.reshape(hidden, F), hs, wds, 0, 1, "f32")
+        part = api.gemm_fp8(hc.reshape(tokens, F), sh.down.codes.cpu().numpy(), hs, sh.down.scales.cpu().numpy(), 0, 1, "f32")
         total = part if total is None else total + part
-    ref = torch.from_numpy(bf(total))
+    ref = torch.from_numpy(np.ascontiguousarray(total, np.float32)).to(torch.bfloat16).float()
     return _rel_err(y_host, ref)
 
 

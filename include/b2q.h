@@ -283,6 +283,22 @@ int32_t b2q_gemm_i8(b2q_handle h, const int8_t* a, const int8_t* b, int64_t M, i
 int32_t b2q_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,
                      const float* scale_a, int scale_a_kind, const float* scale_w, int scale_w_kind,
                      void* out, int out_type);
+/* The general form, gemm_impl of crates/oxicuda-blas/src/level3/gemm_api.rs:126-231 with an EpilogueOp
+ * (crates/oxicuda-blas/src/level3/gemm/epilogue.rs:29-120):
+ *   out = act(alpha * (A W^T) * sa * sw + beta * out + bias[col])
+ * in the reference's order (mul by alpha, fma with beta * C_old, add bias, then max(0, .) or gelu as x * sigmoid(1.702 x),
+ * epilogue.rs:99-196).  w_layout = B2Q_W_KN takes the reference's row-major [K x N] operand B (transposed into the
+ * handle's workspace on every call: hold weights as [N x K] where that matters).  The prefill tcgen05 kernels apply the
+ * epilogue in their store path; few-token shapes run their kernel into the workspace and one elementwise pass. */
+typedef enum { B2Q_EPI_LINEAR = 0, B2Q_EPI_RELU = 1, B2Q_EPI_GELU = 2, B2Q_EPI_BIAS = 3, B2Q_EPI_BIAS_RELU = 4 } b2q_epilogue_op;
+typedef enum { B2Q_W_NK = 0, B2Q_W_KN = 1 } b2q_w_layout;
+typedef struct {
+  const uint8_t* a; const uint8_t* w; int64_t m, n, k; int32_t fmt;
+  const float* scale_a; int32_t scale_a_kind; const float* scale_w; int32_t scale_w_kind;
+  void* out; int32_t out_type;
+  float alpha, beta; const float* bias; int32_t epilogue; int32_t w_layout;
+} b2q_gemm_fp8_desc;
+int32_t b2q_gemm_fp8_ex(b2q_handle h, const b2q_gemm_fp8_desc* d);
 /* Checker path on the GPU: software decode (reference or IEEE), k-ascending fp32 FMA, one thread per output
  * — the arithmetic of the reference's naive kernel (crates/oxicuda-ptx/src/templates/gemm.rs:373-447). */
 int32_t b2q_gemm_fp8_simt(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,

@@ -75,6 +75,14 @@ class GemmFp8Problem(C.Structure):
                 ("out", C.c_void_p)]
 
 
+class GemmFp8Desc(C.Structure):
+    """b2q_gemm_fp8_desc (include/b2q.h): operands, scales and the epilogue of b2q_gemm_fp8_ex."""
+    _fields_ = [("a", C.c_void_p), ("w", C.c_void_p), ("m", C.c_int64), ("n", C.c_int64), ("k", C.c_int64), ("fmt", C.c_int32),
+                ("scale_a", C.c_void_p), ("scale_a_kind", C.c_int32), ("scale_w", C.c_void_p), ("scale_w_kind", C.c_int32),
+                ("out", C.c_void_p), ("out_type", C.c_int32), ("alpha", C.c_float), ("beta", C.c_float), ("bias", C.c_void_p),
+                ("epilogue", C.c_int32), ("w_layout", C.c_int32)]
+
+
 class TileConfig(C.Structure):
     """TileConfig, crates/oxicuda-blas/src/level3/gemm/dispatch.rs:57-107."""
     _fields_ = [(n, C.c_uint32) for n in
@@ -144,6 +152,7 @@ SIGNATURES = {
     "b2q_llm_int8_linear_f32": (C.c_int32, [_H, _P, _P, _I64, _I64, _I64, _F, _I, _P, _P, _P, _P, _P, _P, _P]),
     "b2q_gemm_i8": (C.c_int32, [_H, _P, _P, _I64, _I64, _I64, _P, _P, _P, _P]),
     "b2q_gemm_fp8": (C.c_int32, [_H, _P, _P, _I64, _I64, _I64, _I, _P, _I, _P, _I, _P, _I]),
+    "b2q_gemm_fp8_ex": (C.c_int32, [_H, _P]),
     "b2q_gemm_fp8_simt": (C.c_int32, [_H, _P, _P, _I64, _I64, _I64, _I, _I, _P, _I, _P, _I, _P, _I]),
     "b2q_grouped_gemm_fp8": (C.c_int32, [_H, _P, _I, _I, _I]),
     "b2q_ep_token_scatter": (C.c_int32, [_H, _P, _P, _P, _I64, _I64, _P]),

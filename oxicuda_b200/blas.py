@@ -183,6 +183,45 @@ def gemm_fp8(a: torch.Tensor, w: torch.Tensor, scale_a: torch.Tensor, scale_w: t
     return out
 
 
+class EpilogueOp(Enum):
+    """EpilogueOp, crates/oxicuda-blas/src/level3/gemm/epilogue.rs:29-45."""
+    LinearCombination = 0
+    LinearCombinationRelu = 1
+    LinearCombinationGelu = 2
+    LinearCombinationBias = 3
+    LinearCombinationBiasRelu = 4
+
+    def needs_bias(self) -> bool:
+        return self in (EpilogueOp.LinearCombinationBias, EpilogueOp.LinearCombinationBiasRelu)
+
+
+def gemm_fp8_ex(a: torch.Tensor, w: torch.Tensor, scale_a: torch.Tensor, scale_w: torch.Tensor, out: torch.Tensor = None,
+                alpha: float = 1.0, beta: float = 0.0, bias: torch.Tensor = None, epilogue: EpilogueOp = EpilogueOp.LinearCombination,
+                w_is_kn: bool = False, out_dtype=torch.bfloat16, fmt: int = L.FP8_E4M3) -> torch.Tensor:
+    """gemm_impl with an EpilogueOp (crates/oxicuda-blas/src/level3/gemm_api.rs:126-231, gemm/epilogue.rs:99-196):
+    out = act(alpha * (A . W^T) * scale_a * scale_w + beta * out + bias[col]).  `w` is [N x K], or with w_is_kn the
+    reference's row-major [K x N] operand B.  With beta != 0 `out` must hold C on entry."""
+    import ctypes as C
+    M, K = a.shape
+    if w_is_kn:
+        K2, N = w.shape
+    else:
+        N, K2 = w.shape
+    if K != K2:
+        raise L.DimensionMismatch(L.ERR_DIMENSION_MISMATCH, f"inner dimensions differ: {K} vs {K2}")
+    if epilogue.needs_bias() and bias is None:
+        raise L.InvalidArgument(L.ERR_INVALID_ARGUMENT, f"{epilogue.name} needs a bias vector")
+    if out is None:
+        if beta != 0.0:
+            raise L.InvalidArgument(L.ERR_INVALID_ARGUMENT, "beta != 0 needs the C operand in `out`")
+        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+    d = L.GemmFp8Desc(a.data_ptr(), w.data_ptr(), M, N, K, fmt, scale_a.data_ptr(), _scale_kind(scale_a, M), scale_w.data_ptr(),
+                      _scale_kind(scale_w, N), out.data_ptr(), L.OUT_BF16 if out.dtype == torch.bfloat16 else L.OUT_F32, alpha, beta,
+                      bias.data_ptr() if bias is not None else None, epilogue.value, 1 if w_is_kn else 0)
+    default_handle().call("b2q_gemm_fp8_ex", C.byref(d))
+    return out
+
+
 def gemm_i8(a: torch.Tensor, b: torch.Tensor, scale_a: torch.Tensor = None, scale_b: torch.Tensor = None,
             want_s32: bool = True, want_f32: bool = False):
     """C[M,N] = A[M,K] . B[N,K]^T with exact s32 accumulation (Int8GemmConfig,

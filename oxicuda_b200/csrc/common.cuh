@@ -28,16 +28,23 @@ struct b2q_handle_s {
   int32_t* d_tile_counters;  // kTileCounters x i32, all zero between launches (split-K arrival counts; the last arriver resets its entry)
   void* ws;                  // grow-only workspace for calls that need temporaries (kept so steady-state calls never allocate)
   size_t ws_bytes;
+  void* ws2;                 // second grow-only buffer: operands re-laid-out for a call whose kernel uses `ws` itself
+  size_t ws2_bytes;
   int dynamic_weights;       // 1: weight operands may be written by the previous kernel of the stream (no early weight fetch)
   // Experiment switches (environment variables B2Q_*), read once when the handle is created: -1 = not set.
   struct Switches {
     int no_tail_split, force_tile, fp8_skinny, skinny_pdl, mx_streamk, mx_debug, mx_pdl, mx_inline, e8c_db, gemv_mx, gemv_cluster,
         gemv_exact, int4_small, gemv_stream;
   } sw;
+  // encoded TMA descriptors, direct-mapped by a hash of their key (128 bytes each; see b2q_tensor_map_2d)
+  struct MapEntry { uint64_t key[4]; unsigned char map[128]; int valid; };
+  MapEntry* map_cache;
   char err[512];
 };
+static const int kMapCacheEntries = 256;
 // Returns a workspace of at least `bytes` (256-byte aligned); grows it when needed (synchronises the stream first).
 int32_t b2q_workspace(b2q_handle h, size_t bytes, void** out);
+int32_t b2q_workspace2(b2q_handle h, size_t bytes, void** out);
 // b2q_select_tile with a switch that leaves the few-token tcgen05 kernels out of the table
 int32_t b2q_select_tile_ex(int dtype, uint32_t m, uint32_t n, uint32_t k, b2q_tile_config* out, int* kernel_id, int few_token_kernels);
 static const size_t kScratchWords = 1 << 16;   // 256 KiB of reduction keys / counters

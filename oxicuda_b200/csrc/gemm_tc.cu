@@ -26,13 +26,15 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 enum Kind { kF8 = 0, kI8 = 1, kBF16 = 2 };   // kBF16: 16-bit operands, K counted in BYTES by the kernels (BK = 64 elements)
 
+constexpr int kEpiBytes = 4 * 2 * 4096;   // epilogue staging: per warp two buffers of 32 rows x 128 bytes (TMA store sources)
+
 template <int BN> struct Cfg {
   static constexpr int kStages = BN == 256 ? 4 : 6;
   static constexpr int kBytesA = BM * BK;
   static constexpr int kBytesB = BN * BK;
   static constexpr int kStageBytes = kBytesA + kBytesB;
   static constexpr int kTmemCols = 2 * BN;                       // two accumulators
-  static constexpr int kSmem = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kSmem = kStages * kStageBytes + kEpiBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 struct Params {
@@ -47,6 +49,12 @@ struct Params {
   // pair kernel only: units [0, full_units) are whole 256x256 tiles, units beyond are 256x128 halves of the last tiles
   int full_units, total_units;
   uint32_t idesc_half;
+  // epilogue (EpilogueOp of the reference): out = act(alpha * acc * sa * sw + beta * out_old + bias[n])
+  int epi;                          // 0: plain scaled store; else the fields below apply
+  float alpha, beta;
+  const float* bias;                // [N] or null
+  int act;                          // 0 none, 1 relu, 2 gelu as x * sigmoid(1.702 x)
+  int tma_store;                    // 1: bf16 / f32 rows leave through shared memory and TMA stores (16-byte aligned pitch)
 };
 
 using namespace tcx;
@@ -84,6 +92,17 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   nb = in_group / gm;
 }
 
+// alpha / beta / bias / activation of the reference's EpilogueOp (crates/oxicuda-blas/src/level3/gemm/epilogue.rs:99-196):
+// result = acc * alpha; result = fma(beta, c_old, result); + bias[col]; relu or gelu (x * sigmoid(1.702 x), :153-190).
+__device__ __forceinline__ float epi_apply(const Params& p, float v, float c_old, int64_t col) {
+  v *= p.alpha;
+  if (p.beta != 0.0f) v = fmaf(p.beta, c_old, v);
+  if (p.bias) v += __ldg(p.bias + col);
+  if (p.act == 1) v = fmaxf(v, 0.0f);
+  else if (p.act == 2) v = v * __frcp_rn(1.0f + exp2f(-1.702f * 1.4426950408889634f * v));
+  return v;
+}
+
 // Scales, converts and stores 32 consecutive accumulator columns of one output row.
 template <int KIND>
 __device__ __forceinline__ void store_chunk(const Params& p, const uint32_t (&r)[32], int64_t m, int64_t n, float sa, float sw0) {
@@ -94,6 +113,12 @@ __device__ __forceinline__ void store_chunk(const Params& p, const uint32_t (&r)
     for (int j = 0; j < 32; ++j) {
       const float sw = p.scale_w_rows ? (n + j < p.N ? __ldg(p.scale_w + n + j) : 0.0f) : sw0;
       v[j] = __uint_as_float(r[j]) * (sa * sw);
+      if (p.epi && n + j < p.N) {
+        const float cold = p.beta == 0.0f ? 0.0f
+                         : (p.out_type == B2Q_OUT_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.out)[m * p.N + n + j])
+                                                       : reinterpret_cast<const float*>(p.out)[m * p.N + n + j]);
+        v[j] = epi_apply(p, v[j], cold, n + j);
+      }
     }
     if (p.out_type == B2Q_OUT_BF16) {
       __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + m * p.N + n;
@@ -146,13 +171,110 @@ __device__ __forceinline__ void store_chunk(const Params& p, const uint32_t (&r)
   }
 }
 
+// One warp's share of an output tile: its 32 accumulator rows (TMEM lane quarter) x `width` columns.
+// Fast path (bf16 / f32 with a 16-byte aligned pitch): 64 (bf16) or 32 (f32) columns at a time go through a
+// 128-byte-swizzled shared-memory buffer of 32 rows x 128 bytes and leave with one TMA store per buffer, i.e. as
+// full 128-byte row segments; two buffers per warp, so a store is in flight while the next chunk is converted.
+// TMA clips rows >= M and columns >= N.  Other outputs (INT8 accumulators, odd pitches) store from registers.
+struct EpiWarp { uint32_t smem_u; uint8_t* smem_p; uint32_t it; };
+
+template <int KIND>
+__device__ __forceinline__ void epilogue_rows(const Params& p, const CUtensorMap* map_out, EpiWarp& ew, uint32_t tmem_acc, int width,
+                                              int64_t m_warp0, int lane, int64_t n0) {
+  const int64_t m = m_warp0 + lane;
+  const bool row_ok = m < p.M;
+  const float sa = row_ok && p.scale_a ? (p.scale_a_rows ? p.scale_a[m] : p.scale_a[0]) : 1.0f;
+  const float sw0 = p.scale_w && !p.scale_w_rows ? p.scale_w[0] : 1.0f;
+  if constexpr (KIND != kI8) {
+    if (p.tma_store) {
+      const bool bf16 = p.out_type == B2Q_OUT_BF16;
+      const int CH = bf16 ? 64 : 32;
+#pragma unroll 1
+      for (int c = 0; c < width; c += CH) {
+        uint32_t r[64];
+        __syncwarp();
+        tmem_ld32(tmem_acc + c, *reinterpret_cast<uint32_t(*)[32]>(&r[0]));
+        if (bf16) tmem_ld32(tmem_acc + c + 32, *reinterpret_cast<uint32_t(*)[32]>(&r[32]));
+        tmem_ld_wait();
+        const int64_t n = n0 + c;
+        if (n >= p.N || m_warp0 >= p.M) continue;                // nothing of this chunk lies inside the output (warp-uniform)
+        const uint32_t buf = (ew.it & 1u) * 4096u;
+        if (lane == 0) tma_store_wait_read<1>();                 // the store that last read this buffer has read it
+        __syncwarp();
+        uint8_t* row = ew.smem_p + buf + lane * 128;
+        if (bf16) {
+#pragma unroll
+          for (int j = 0; j < 64; j += 8) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const float sw = p.scale_w_rows ? (n + j + i < p.N ? __ldg(p.scale_w + n + j + i) : 0.0f) : sw0;
+              v[i] = __uint_as_float(r[j + i]) * (sa * sw);
+            }
+            if (p.epi) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const bool in = row_ok && n + j + i < p.N;
+                const float cold = (p.beta != 0.0f && in) ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.out)[m * p.N + n + j + i]) : 0.0f;
+                v[i] = in ? epi_apply(p, v[i], cold, n + j + i) : 0.0f;
+              }
+            }
+            uint4 pk;
+            __nv_bfloat162 h0 = __floats2bfloat162_rn(v[0], v[1]), h1 = __floats2bfloat162_rn(v[2], v[3]);
+            __nv_bfloat162 h2 = __floats2bfloat162_rn(v[4], v[5]), h3 = __floats2bfloat162_rn(v[6], v[7]);
+            pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+            pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+            *reinterpret_cast<uint4*>(row + ((((j >> 3)) ^ (lane & 7)) << 4)) = pk;     // 128-byte swizzle: 16-byte unit ^ (row & 7)
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4) {
+            float v[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float sw = p.scale_w_rows ? (n + j + i < p.N ? __ldg(p.scale_w + n + j + i) : 0.0f) : sw0;
+              v[i] = __uint_as_float(r[j + i]) * (sa * sw);
+              if (p.epi) {
+                const bool in = row_ok && n + j + i < p.N;
+                const float cold = (p.beta != 0.0f && in) ? reinterpret_cast<const float*>(p.out)[m * p.N + n + j + i] : 0.0f;
+                v[i] = in ? epi_apply(p, v[i], cold, n + j + i) : 0.0f;
+              }
+            }
+            *reinterpret_cast<float4*>(row + ((((j >> 2)) ^ (lane & 7)) << 4)) = make_float4(v[0], v[1], v[2], v[3]);
+          }
+        }
+        fence_async_smem();                                      // the TMA unit reads what the warp just wrote
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_2d(map_out, ew.smem_u + buf, (int)n, (int)m_warp0);
+          tma_store_commit();
+        }
+        ++ew.it;
+      }
+      return;
+    }
+  }
+#pragma unroll 1
+  for (int c = 0; c < width; c += 32) {
+    uint32_t r[32];
+    __syncwarp();                           // tcgen05.ld is warp-collective: reconverge after the guarded stores
+    tmem_ld32(tmem_acc + c, r);
+    tmem_ld_wait();
+    const int64_t n = n0 + c;
+    if (!row_ok || n >= p.N) continue;
+    store_chunk<KIND>(p, r, m, n, sa, sw0);
+  }
+}
+
 template <int BN, int KIND>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w, const Params p) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+               const __grid_constant__ CUtensorMap map_out, const Params p) {
   using C = Cfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bar_base = base + C::kStages * C::kStageBytes;
+  const uint32_t epi_base = base + C::kStages * C::kStageBytes;     // 1024-byte aligned: the stage size is a multiple of 1024
+  const uint32_t bar_base = epi_base + kEpiBytes;
   // barrier layout (8 bytes each): full[stages], empty[stages], tmem_full[2], tmem_empty[2], drain
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (C::kStages + s); };
@@ -175,6 +297,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
+    if (p.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_out)) : "memory");
   }
   if (warp == 1) tmem_alloc(smem_u32(&s_tmem_base), C::kTmemCols);
   tc_fence_before();
@@ -251,31 +374,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     const int q = warp & 3;                 // TMEM lane quarter this warp may access
     uint32_t tile_it = 0;
     bool ok = true;
+    EpiWarp ew{epi_base + (uint32_t)q * 8192u, smem_raw + (epi_base - smem_u32(smem_raw)) + q * 8192, 0u};
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++tile_it) {
       int mb, nb;
       tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
       const uint32_t buf = tile_it & 1, aph = (tile_it >> 1) & 1;
       if (!mbar_wait(tfull_bar(buf), aph, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const int64_t m = (int64_t)mb * BM + q * 32 + lane;
-      const int64_t n0 = (int64_t)nb * BN;
-      const bool row_ok = m < p.M;
-      const float sa = row_ok && p.scale_a ? (p.scale_a_rows ? p.scale_a[m] : p.scale_a[0]) : 1.0f;
-      const float sw0 = p.scale_w && !p.scale_w_rows ? p.scale_w[0] : 1.0f;
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        uint32_t r[32];
-        __syncwarp();                       // tcgen05.ld is warp-collective: reconverge after the guarded stores
-        tmem_ld32(tmem_base + buf * BN + c + ((uint32_t)(q * 32) << 16), r);
-        tmem_ld_wait();
-        const int64_t n = n0 + c;
-        if (!row_ok || n >= p.N) continue;
-        store_chunk<KIND>(p, r, m, n, sa, sw0);
-      }
+      epilogue_rows<KIND>(p, &map_out, ew, tmem_base + buf * BN + ((uint32_t)(q * 32) << 16), BN, (int64_t)mb * BM + q * 32, lane,
+                          (int64_t)nb * BN);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(buf));
     }
+    if (lane == 0) tma_store_wait<0>();     // shared memory stays valid until the last store has read it
   }
 
   // ---------------- teardown ----------------
@@ -308,7 +420,7 @@ constexpr int kBytesA = BM * BK;         // this CTA's 128 rows of A
 constexpr int kBytesB = (BN2 / 2) * BK;  // this CTA's 128 rows of W
 constexpr int kStageBytes = kBytesA + kBytesB;
 constexpr int kTmemCols = 2 * BN2;
-constexpr int kSmem = kStages * kStageBytes + 1024 + 256;
+constexpr int kSmem = kStages * kStageBytes + kEpiBytes + 1024 + 256;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
 __device__ __forceinline__ uint32_t mapa_u32(uint32_t addr, uint32_t rank) {
@@ -365,10 +477,11 @@ __device__ __forceinline__ void umma2(uint32_t tmem_d, uint64_t adesc, uint64_t 
 template <int KIND>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                const __grid_constant__ CUtensorMap map_w_half, const Params p) {
+                const __grid_constant__ CUtensorMap map_w_half, const __grid_constant__ CUtensorMap map_out, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bar_base = base + kStages * kStageBytes;
+  const uint32_t epi_base = base + kStages * kStageBytes;
+  const uint32_t bar_base = epi_base + kEpiBytes;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * kStages + b); };
@@ -398,6 +511,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w_half)) : "memory");
+    if (p.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_out)) : "memory");
   }
   if (warp == 1) tmem_alloc2(smem_u32(&s_tmem_base), kTmemCols);
   tc_fence_before();
@@ -472,6 +586,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     const int q = warp & 3;
     uint32_t tile_it = 0;
     bool ok = true;
+    EpiWarp ew{epi_base + (uint32_t)q * 8192u, smem_raw + (epi_base - smem_u32(smem_raw)) + q * 8192, 0u};
     for (int u = pair; u < p.total_units && ok; u += num_pairs, ++tile_it) {
       int tile, half, width, mb, nb;
       unit_info(u, tile, half, width);
@@ -479,25 +594,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const uint32_t buf = tile_it & 1, aph = (tile_it >> 1) & 1;
       if (!mbar_wait(tfull_bar(buf), aph, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const int64_t m = (int64_t)mb * 256 + rank * BM + q * 32 + lane;
-      const int64_t n0 = (int64_t)nb * BN2 + half * (BN2 / 2);
-      const bool row_ok = m < p.M;
-      const float sa = row_ok && p.scale_a ? (p.scale_a_rows ? p.scale_a[m] : p.scale_a[0]) : 1.0f;
-      const float sw0 = p.scale_w && !p.scale_w_rows ? p.scale_w[0] : 1.0f;
-#pragma unroll 1
-      for (int c = 0; c < width; c += 32) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld32(tmem_base + buf * BN2 + c + ((uint32_t)(q * 32) << 16), r);
-        tmem_ld_wait();
-        const int64_t n = n0 + c;
-        if (!row_ok || n >= p.N) continue;
-        store_chunk<KIND>(p, r, m, n, sa, sw0);
-      }
+      epilogue_rows<KIND>(p, &map_out, ew, tmem_base + buf * BN2 + ((uint32_t)(q * 32) << 16), width,
+                          (int64_t)mb * 256 + rank * BM + q * 32, lane, (int64_t)nb * BN2 + half * (BN2 / 2));
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(tempty_bar(buf), 0));   // the leader's MMA thread waits for both CTAs
     }
+    if (lane == 0) tma_store_wait<0>();
   }
 
   // ---------------- teardown ----------------
@@ -514,28 +617,33 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 }  // namespace two
 
 // ---- host side --------------------------------------------------------------
-// rows x K bytes, K-major; box = 128 bytes x box_rows, 128-byte swizzle, zero fill out of bounds.
+// rows x K bytes, K-major; box = 128 bytes x box_rows, 128-byte swizzle, zero fill out of bounds.  Encoded maps are
+// kept in the handle (keyed by pointer, extents, box and element type), so a steady-state call encodes nothing.
 int32_t make_map(b2q_handle h, CUtensorMap* map, const void* ptr, int64_t rows, int64_t K, int box_rows) {
-  EncodeTiledFn enc = get_encode_fn();
-  if (!enc) B2Q_FAIL(h, B2Q_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)K};
-  cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) B2Q_FAIL(h, B2Q_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
-  return B2Q_OK;
+  return b2q_tensor_map_2d(h, map, ptr, /*elem_bytes=*/1, (uint64_t)K, (uint64_t)rows, (uint32_t)BK, (uint32_t)box_rows);
+}
+// The output [M x N] as a TMA store target: boxes of 32 rows x 128 bytes (64 bf16 or 32 f32 columns), 128-byte swizzle.
+// Leaves p.tma_store = 0 (register stores) when the pointer or the pitch is not 16-byte aligned.
+int32_t make_out_map(b2q_handle h, CUtensorMap* map, Params& p) {
+  memset(map, 0, sizeof(*map));
+  p.tma_store = 0;
+  if (!p.out || p.c_s32 || p.c_f32) return B2Q_OK;
+  const int es = p.out_type == B2Q_OUT_BF16 ? 2 : 4;
+  if ((reinterpret_cast<uintptr_t>(p.out) & 15) != 0 || (p.N * es) % 16 != 0) return B2Q_OK;
+  int32_t st = b2q_tensor_map_2d(h, map, p.out, es, (uint64_t)p.N, (uint64_t)p.M, (uint32_t)(128 / es), 32u);
+  if (st == B2Q_OK) p.tma_store = 1;
+  return st;
 }
 
 template <int BN, int KIND>
 int32_t launch(b2q_handle h, const void* a, const void* w, Params p) {
   using C = Cfg<BN>;
-  CUtensorMap map_a, map_w;
+  CUtensorMap map_a, map_w, map_out;
   int32_t st = make_map(h, &map_a, a, p.M, p.K, BM);
   if (st != B2Q_OK) return st;
   st = make_map(h, &map_w, w, p.N, p.K, BN);
+  if (st != B2Q_OK) return st;
+  st = make_out_map(h, &map_out, p);
   if (st != B2Q_OK) return st;
   p.tiles_m = (int)ceil_div64(p.M, BM);
   p.tiles_n = (int)ceil_div64(p.N, BN);
@@ -547,7 +655,7 @@ int32_t launch(b2q_handle h, const void* a, const void* w, Params p) {
   B2Q_SMEM_ATTR(h, (gemm_tc_kernel<BN, KIND>), C::kSmem);
   int64_t tiles = (int64_t)p.tiles_m * p.tiles_n;
   int grid = (int)(tiles < h->sm_count ? tiles : h->sm_count);
-  gemm_tc_kernel<BN, KIND><<<grid, kThreads, C::kSmem, h->stream>>>(map_a, map_w, p);
+  gemm_tc_kernel<BN, KIND><<<grid, kThreads, C::kSmem, h->stream>>>(map_a, map_w, map_out, p);
   B2Q_LAUNCH_CHECK(h, "gemm_tc_kernel");
   return B2Q_OK;
 }
@@ -560,8 +668,10 @@ int32_t launch2(b2q_handle h, const void* a, const void* w, Params p) {
   if (st != B2Q_OK) return st;
   st = make_map(h, &map_w, w, p.N, p.K, two::BN2 / 2);
   if (st != B2Q_OK) return st;
-  CUtensorMap map_w_half;
+  CUtensorMap map_w_half, map_out;
   st = make_map(h, &map_w_half, w, p.N, p.K, two::BN2 / 4);
+  if (st != B2Q_OK) return st;
+  st = make_out_map(h, &map_out, p);
   if (st != B2Q_OK) return st;
   p.tiles_m = (int)ceil_div64(p.M, 256);
   p.tiles_n = (int)ceil_div64(p.N, two::BN2);
@@ -595,7 +705,7 @@ int32_t launch2(b2q_handle h, const void* a, const void* w, Params p) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, two::gemm_tc2_kernel<KIND>, map_a, map_w, map_w_half, p));
+  B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, two::gemm_tc2_kernel<KIND>, map_a, map_w, map_w_half, map_out, p));
   return B2Q_OK;
 }
 
@@ -634,23 +744,70 @@ int32_t b2q_gemm_bf16_tc(b2q_handle h, const void* a, const void* w, int64_t M, 
   return N >= 256 ? tc::launch<256, tc::kBF16>(h, a, w, p) : tc::launch<128, tc::kBF16>(h, a, w, p);
 }
 
-extern "C" int32_t b2q_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,
-                                const float* scale_a, int scale_a_kind, const float* scale_w, int scale_w_kind, void* out,
-                                int out_type) {
-  B2Q_REQUIRE_HANDLE(h);
-  int32_t st = b2q_validate_gemm_fp8(h, a, w, M, N, K, fmt, scale_a, scale_a_kind, scale_w, scale_w_kind, out, out_type);
-  if (st != B2Q_OK) return st;
+namespace tc {
+
+struct EpiArgs { float alpha, beta; const float* bias; int act; };
+
+// out = act(alpha * plain + beta * out + bias[col]) for the kernels that have no fused epilogue (few-token and SIMT paths):
+// `plain` is their f32 result.
+__global__ void __launch_bounds__(256) epilogue_post_kernel(const float* __restrict__ plain, void* out, int out_type, int64_t M, int64_t N,
+                                                            float alpha, float beta, const float* __restrict__ bias, int act) {
+  const int64_t total = M * N;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    float v = plain[i] * alpha;
+    if (beta != 0.0f) {
+      const float cold = out_type == B2Q_OUT_BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(out)[i]) : reinterpret_cast<const float*>(out)[i];
+      v = fmaf(beta, cold, v);
+    }
+    if (bias) v += bias[i % N];
+    if (act == 1) v = fmaxf(v, 0.0f);
+    else if (act == 2) v = v * __frcp_rn(1.0f + exp2f(-1.702f * 1.4426950408889634f * v));
+    if (out_type == B2Q_OUT_BF16) reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(v);
+    else reinterpret_cast<float*>(out)[i] = v;
+  }
+}
+
+// [K x N] row-major codes -> [N x K] (the layout every kernel here reads): 32 x 32 byte tiles through shared memory.
+__global__ void __launch_bounds__(256) transpose_u8_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_t K, int64_t N) {
+  __shared__ uint8_t tile[32][33];
+  const int64_t n0 = (int64_t)blockIdx.x * 32, k0 = (int64_t)blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  for (int r = ty; r < 32; r += 8)
+    if (k0 + r < K && n0 + tx < N) tile[r][tx] = in[(k0 + r) * N + n0 + tx];
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8)
+    if (n0 + r < N && k0 + tx < K) out[(n0 + r) * K + k0 + tx] = tile[tx][r];
+}
+
+int32_t gemm_fp8_impl(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt, const float* scale_a,
+                      int scale_a_kind, const float* scale_w, int scale_w_kind, void* out, int out_type, const EpiArgs* epi) {
   b2q_tile_config t; int kid = 0;
   b2q_select_tile(0, (uint32_t)M, (uint32_t)N, (uint32_t)K, &t, &kid);
-  if (kid != 0) {   // experiment switch: B2Q_FORCE_TILE_N=128|256 overrides the static table
+  if (kid != 0) {   // experiment switch: B2Q_FORCE_TILE_N=128|256|p overrides the static table
     if (h->sw.force_tile == 128) kid = 2;
     if (h->sw.force_tile == 256) kid = 1;
     if (h->sw.force_tile == 9) kid = 4;        // "p(air)": the two-CTA kernel
   }
+  const bool tma_ok = K % 16 == 0 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
+  const bool fused = (kid == 1 || kid == 2 || kid == 4) && tma_ok;      // the prefill kernels apply the epilogue themselves
+  if (epi && !fused) {
+    // few-token / SIMT kernels: plain f32 result into the workspace, then one elementwise pass
+    void* ws = nullptr;
+    int32_t st = b2q_workspace(h, (size_t)M * N * sizeof(float), &ws);
+    if (st != B2Q_OK) return st;
+    st = gemm_fp8_impl(h, a, w, M, N, K, fmt, scale_a, scale_a_kind, scale_w, scale_w_kind, ws, B2Q_OUT_F32, nullptr);
+    if (st != B2Q_OK) return st;
+    const int64_t total = M * N;
+    int grid = (int)((total + 255) / 256);
+    if (grid > h->sm_count * 8) grid = h->sm_count * 8;
+    epilogue_post_kernel<<<grid, 256, 0, h->stream>>>((const float*)ws, out, out_type, M, N, epi->alpha, epi->beta, epi->bias, epi->act);
+    B2Q_LAUNCH_CHECK(h, "epilogue_post_kernel");
+    return B2Q_OK;
+  }
   {
     // few tokens against a large weight matrix (kernel 6 of the static table): the weight-stationary tcgen05 kernel
     // streams W at HBM rate (B2Q_FP8_SKINNY=0 / 1 forces it off / on)
-    if (M <= 128 && (h->sw.fp8_skinny >= 0 ? h->sw.fp8_skinny == 1 : kid == 6)) {
+    if (M <= 128 && !epi && (h->sw.fp8_skinny >= 0 ? h->sw.fp8_skinny == 1 : kid == 6)) {
       int32_t sst = b2q_gemm_fp8_skinny_dispatch(h, a, w, M, N, K, fmt, scale_a, scale_a_kind, scale_w, scale_w_kind, out, out_type);
       if (sst != B2Q_ERR_UNSUPPORTED) return sst;
     }
@@ -661,15 +818,57 @@ extern "C" int32_t b2q_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w
     if (gst != B2Q_ERR_UNSUPPORTED) return gst;
     kid = 0;
   }
-  const bool tma_ok = K % 16 == 0 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
   if (kid == 0 || !tma_ok)
     return b2q_gemm_fp8_simt(h, a, w, M, N, K, fmt, /*IEEE decode, as the tensor core*/ 1, scale_a, scale_a_kind, scale_w,
                              scale_w_kind, out, out_type);
-  tc::Params p{};
+  Params p{};
   p.M = M; p.N = N; p.K = K;
   p.scale_a = scale_a; p.scale_a_rows = scale_a_kind; p.scale_w = scale_w; p.scale_w_rows = scale_w_kind;
   p.out = out; p.out_type = out_type; p.status = h->d_status;
   p.idesc = ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10);   // A/B format: 0 = E4M3, 1 = E5M2
-  if (kid == 4) return tc::launch2<tc::kF8>(h, a, w, p);
-  return kid == 1 ? tc::launch<256, tc::kF8>(h, a, w, p) : tc::launch<128, tc::kF8>(h, a, w, p);
+  p.alpha = 1.0f;
+  if (epi) { p.epi = 1; p.alpha = epi->alpha; p.beta = epi->beta; p.bias = epi->bias; p.act = epi->act; }
+  if (kid == 4) return launch2<kF8>(h, a, w, p);
+  return kid == 1 ? launch<256, kF8>(h, a, w, p) : launch<128, kF8>(h, a, w, p);
+}
+
+}  // namespace tc
+
+extern "C" int32_t b2q_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,
+                                const float* scale_a, int scale_a_kind, const float* scale_w, int scale_w_kind, void* out,
+                                int out_type) {
+  B2Q_REQUIRE_HANDLE(h);
+  int32_t st = b2q_validate_gemm_fp8(h, a, w, M, N, K, fmt, scale_a, scale_a_kind, scale_w, scale_w_kind, out, out_type);
+  if (st != B2Q_OK) return st;
+  return tc::gemm_fp8_impl(h, a, w, M, N, K, fmt, scale_a, scale_a_kind, scale_w, scale_w_kind, out, out_type, nullptr);
+}
+
+extern "C" int32_t b2q_gemm_fp8_ex(b2q_handle h, const b2q_gemm_fp8_desc* d) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (!d) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemm_fp8_ex: null descriptor");
+  if (d->epilogue < 0 || d->epilogue > 4) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemm_fp8_ex: unknown epilogue %d", d->epilogue);
+  if (d->w_layout < 0 || d->w_layout > 1) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemm_fp8_ex: unknown weight layout %d", d->w_layout);
+  const bool needs_bias = d->epilogue == B2Q_EPI_BIAS || d->epilogue == B2Q_EPI_BIAS_RELU;
+  if (needs_bias && !d->bias) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemm_fp8_ex: this epilogue needs a bias vector");
+  int32_t st = b2q_validate_gemm_fp8(h, d->a, d->w, d->m, d->n, d->k, d->fmt, d->scale_a, d->scale_a_kind, d->scale_w, d->scale_w_kind,
+                                     d->out, d->out_type);
+  if (st != B2Q_OK) return st;
+  const uint8_t* w = d->w;
+  if (d->w_layout == B2Q_W_KN) {
+    // the reference's operand B is [K x N] row-major (gemm_api.rs:126-231); the kernels read [N x K]: transpose it into the
+    // workspace first (one pass over the codes; hold weights as [N x K] to avoid it)
+    void* ws = nullptr;
+    st = b2q_workspace2(h, (size_t)d->n * d->k, &ws);
+    if (st != B2Q_OK) return st;
+    uint8_t* wt = reinterpret_cast<uint8_t*>(ws);
+    dim3 grid((unsigned)ceil_div64(d->n, 32), (unsigned)ceil_div64(d->k, 32));
+    tc::transpose_u8_kernel<<<grid, 256, 0, h->stream>>>(d->w, wt, d->k, d->n);
+    B2Q_LAUNCH_CHECK(h, "transpose_u8_kernel");
+    w = wt;
+  }
+  tc::EpiArgs e{d->alpha, d->beta, needs_bias ? d->bias : nullptr,
+                (d->epilogue == B2Q_EPI_RELU || d->epilogue == B2Q_EPI_BIAS_RELU) ? 1 : (d->epilogue == B2Q_EPI_GELU ? 2 : 0)};
+  const bool plain = d->alpha == 1.0f && d->beta == 0.0f && !e.bias && e.act == 0;
+  return tc::gemm_fp8_impl(h, d->a, w, d->m, d->n, d->k, d->fmt, d->scale_a, d->scale_a_kind, d->scale_w, d->scale_w_kind, d->out,
+                           d->out_type, plain ? nullptr : &e);
 }

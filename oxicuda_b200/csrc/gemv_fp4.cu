@@ -883,6 +883,8 @@ int32_t launch_small(b2q_handle h, const uint8_t* codes, const void* scales, int
 
 int32_t b2q_gemv_fp4_mx_dispatch(b2q_handle h, const uint8_t* codes, const void* scales, const void* x, int tokens, int64_t N, int64_t K,
                                  void* out, int out_type);
+int32_t b2q_gemv_fp4_mxb_dispatch(b2q_handle h, const uint8_t* codes, const void* scales, const void* x, int tokens, int64_t N, int64_t K,
+                                  void* out, int out_type);
 
 extern "C" int32_t b2q_gemv_fp4_wo(b2q_handle h, const uint8_t* codes, const void* scales, int scale_format, int block,
                                    const void* x_bf16, int64_t tokens, int64_t N, int64_t K, void* out, int out_type) {
@@ -903,6 +905,10 @@ extern "C" int32_t b2q_gemv_fp4_wo(b2q_handle h, const uint8_t* codes, const voi
     B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemv_fp4_wo: scales must be 4-byte (E8M0) or 16-byte (f32) aligned");
   const int t = (int)tokens;
   const bool small_n = N <= 2048;
+  if (scale_format == B2Q_SCALE_E8M0 && h->sw.gemv_stream == 1) {   // B2Q_GEMV_STREAM=1: the weights-as-N tcgen05 kernel for every shape it takes
+    const int32_t st = b2q_gemv_fp4_mxb_dispatch(h, codes, scales, x_bf16, t, N, K, out, out_type);
+    if (st != B2Q_ERR_UNSUPPORTED) return st;
+  }
   {
     // E8M0 scales: the tcgen05 block-scaled kernel (weights never touch a CUDA core) where its fixed cost pays:
     // from 16 MiB of codes with 4 tokens or more or with enough rows for one tile per SM (no partial sums to

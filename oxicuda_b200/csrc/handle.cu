@@ -1,5 +1,5 @@
 // Handle lifetime, status word and the host-side tile heuristics of libb2q.
-#include "common.cuh"
+#include "tc_common.cuh"
 #include <stdlib.h>
 
 int32_t b2q_workspace(b2q_handle h, size_t bytes, void** out) {
@@ -13,6 +13,49 @@ int32_t b2q_workspace(b2q_handle h, size_t bytes, void** out) {
     h->ws_bytes = want;
   }
   *out = h->ws;
+  return B2Q_OK;
+}
+
+int32_t b2q_workspace2(b2q_handle h, size_t bytes, void** out) {
+  if (bytes > h->ws2_bytes) {
+    B2Q_CUDA(h, cudaStreamSynchronize(h->stream));
+    if (h->ws2) cudaFree(h->ws2);
+    h->ws2 = nullptr;
+    h->ws2_bytes = 0;
+    B2Q_CUDA(h, cudaMalloc(&h->ws2, bytes));
+    h->ws2_bytes = bytes;
+  }
+  *out = h->ws2;
+  return B2Q_OK;
+}
+
+int32_t b2q_tensor_map_2d(b2q_handle h, CUtensorMap* map, const void* ptr, int elem_bytes, uint64_t d0, uint64_t d1, uint32_t box0,
+                          uint32_t box1) {
+  static_assert(sizeof(CUtensorMap) == 128, "CUtensorMap size");
+  const uint64_t key[4] = {(uint64_t)reinterpret_cast<uintptr_t>(ptr), d0, d1, ((uint64_t)box0 << 40) | ((uint64_t)box1 << 8) | (uint64_t)elem_bytes};
+  uint64_t hsh = key[0] * 0x9E3779B97F4A7C15ull ^ key[1] * 0xC2B2AE3D27D4EB4Full ^ key[2] * 0x165667B19E3779F9ull ^ key[3];
+  hsh ^= hsh >> 29;
+  b2q_handle_s::MapEntry* e = h->map_cache ? &h->map_cache[hsh % kMapCacheEntries] : nullptr;
+  if (e && e->valid && e->key[0] == key[0] && e->key[1] == key[1] && e->key[2] == key[2] && e->key[3] == key[3]) {
+    memcpy(map, e->map, 128);
+    return B2Q_OK;
+  }
+  tcx::EncodeTiledFn enc = tcx::get_encode_fn();
+  if (!enc) B2Q_FAIL(h, B2Q_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t dims[2] = {(cuuint64_t)d0, (cuuint64_t)d1};
+  cuuint64_t strides[1] = {(cuuint64_t)(d0 * (uint64_t)elem_bytes)};
+  cuuint32_t box[2] = {box0, box1};
+  cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = elem_bytes == 1 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                                                                                   : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = enc(map, dt, 2, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) B2Q_FAIL(h, B2Q_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  if (e) {
+    memcpy(e->key, key, sizeof(key));
+    memcpy(e->map, map, 128);
+    e->valid = 1;
+  }
   return B2Q_OK;
 }
 
@@ -57,6 +100,7 @@ int32_t b2q_create(b2q_handle* out, int device) {
     return B2Q_ERR_CUDA;
   }
   h->stream = nullptr;
+  h->map_cache = new b2q_handle_s::MapEntry[kMapCacheEntries]();
   // experiment switches: read here once, never on the dispatch path
   auto sw = [](const char* name) { const char* e = getenv(name); return e && e[0] ? (e[0] == 'p' ? 9 : atoi(e)) : -1; };
   h->sw.no_tail_split = getenv("B2Q_NO_TAIL_SPLIT") ? 1 : -1;
@@ -86,6 +130,8 @@ int32_t b2q_destroy(b2q_handle h) {
   cudaFree(h->d_scratch);
   cudaFree(h->d_tile_counters);
   if (h->ws) cudaFree(h->ws);
+  if (h->ws2) cudaFree(h->ws2);
+  delete[] h->map_cache;
   delete h;
   if (prev_device >= 0) cudaSetDevice(prev_device);
   return B2Q_OK;

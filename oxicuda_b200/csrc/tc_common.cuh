@@ -136,3 +136,9 @@ inline EncodeTiledFn get_encode_fn() {
 }
 
 }  // namespace tcx
+
+// 2-D row-major tensor [d1 rows x d0 elements] as a tiled TMA descriptor with boxes of box0 x box1 elements, 128-byte
+// swizzle, zero fill out of bounds; 1-byte elements are UINT8, 2-byte BFLOAT16, 4-byte FLOAT32.  The encoded descriptor
+// is cached in the handle, so repeated calls on the same operands cost a lookup.
+int32_t b2q_tensor_map_2d(b2q_handle h, CUtensorMap* map, const void* ptr, int elem_bytes, uint64_t d0, uint64_t d1, uint32_t box0,
+                          uint32_t box1);

@@ -196,3 +196,49 @@ def test_gemm_fp8_validation_order(cuda):
         gemm_fp8(buf[:4096].view(64, 64), z(64, 64), one, one, out=buf[:8192].view(torch.bfloat16).view(64, 64))
     with pytest.raises(_lib.DimensionMismatch):
         gemm_fp8(z(64, 64), z(64, 64), torch.ones(3, device=cuda), one)
+
+
+@pytest.mark.parametrize("M,N,K", [(384, 512, 512), (128, 384, 256), (300, 200, 128), (8, 4096, 4096), (48, 256, 512)])
+def test_epilogue_ops_alpha_beta_bias_and_kn_layout(cuda, oracle, M, N, K):
+    """b2q_gemm_fp8_ex against the reference's epilogue statement (epilogue.rs:99-196) applied to the oracle's f32 GEMM:
+    every EpilogueOp, alpha / beta with C in place, bf16 and f32 outputs, the fused store path of the prefill kernels
+    (first three shapes), the elementwise pass behind the few-token kernels (last two), and the [K x N] operand."""
+    from oxicuda_b200.blas import EpilogueOp, gemm_fp8_ex
+    from oxicuda_b200.quant import Fp8Codec
+    rng = np.random.default_rng(M + N + K)
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    w = (rng.standard_normal((N, K)) * 0.05).astype(np.float32)
+    codec = Fp8Codec.e4m3("rne")
+    t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).to(cuda)
+    ac, sa = codec.quantize_rows(t(a), M, K)
+    wc, sw = codec.quantize_rows(t(w), N, K)
+    ac, wc = ac.view(M, K), wc.view(N, K)
+    plain = np.asarray(oracle.gemm_fp8(ac.cpu().numpy(), wc.cpu().numpy(), sa.cpu().numpy(), sw.cpu().numpy(), 0, 1, "f32"), np.float64).reshape(M, N)
+    bias = rng.standard_normal(N).astype(np.float32)
+    c0 = rng.standard_normal((M, N)).astype(np.float32)
+    gelu = lambda v: v / (1.0 + np.exp2(-1.702 * 1.4426950408889634 * v))
+
+    def check(got, ref, tol=1e-2):
+        rms = np.sqrt((ref ** 2).mean()) + 1e-30
+        assert float((np.abs(got.double().cpu().numpy() - ref) / (np.abs(ref) + rms)).max()) <= tol
+
+    cases = [(EpilogueOp.LinearCombination, 0.5, 0.0, None, lambda v: v),
+             (EpilogueOp.LinearCombination, 2.0, -0.75, None, lambda v: v),
+             (EpilogueOp.LinearCombinationRelu, 1.0, 0.0, None, lambda v: np.maximum(v, 0)),
+             (EpilogueOp.LinearCombinationGelu, 1.0, 0.0, None, gelu),
+             (EpilogueOp.LinearCombinationBias, 1.0, 0.0, bias, lambda v: v),
+             (EpilogueOp.LinearCombinationBiasRelu, 1.5, 0.25, bias, lambda v: np.maximum(v, 0))]
+    for dtype in (torch.bfloat16, torch.float32):
+        for op, alpha, beta, b, act in cases:
+            c_dev = t(c0).to(dtype)
+            c_host = c_dev.double().cpu().numpy()
+            ref = alpha * plain + beta * c_host + (b.astype(np.float64)[None, :] if b is not None else 0.0)
+            ref = act(ref)
+            got = gemm_fp8_ex(ac, wc, sa, sw, out=c_dev, alpha=alpha, beta=beta, bias=t(b) if b is not None else None, epilogue=op)
+            check(got, ref)
+    # the reference's [K x N] operand B
+    wkn = wc.t().contiguous()
+    got = gemm_fp8_ex(ac, wkn, sa, sw, w_is_kn=True, out_dtype=torch.float32)
+    check(got, plain, 2e-3)
+    with pytest.raises(Exception):
+        gemm_fp8_ex(ac, wc, sa, sw, epilogue=EpilogueOp.LinearCombinationBias)

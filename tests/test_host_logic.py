@@ -182,3 +182,20 @@ def test_rank_coordinates_and_shard_ranges(libb2q):
     assert row_shard_cols(28672, 4, 1) == (7168, 14336)
     with pytest.raises(_lib.InvalidDimension):
         column_shard_rows(10, 3, 0)
+
+
+def test_rust_bindings_cover_the_header(libb2q):
+    """rust/b2q-sys/src/lib.rs is generated from include/b2q.h: it must declare exactly the symbols the header (and
+    the ctypes table) declare, and be what the generator writes today."""
+    import re
+    import subprocess
+    import sys
+    from pathlib import Path
+    from oxicuda_b200 import _lib
+    root = Path(__file__).resolve().parent.parent
+    src = (root / "rust" / "b2q-sys" / "src" / "lib.rs").read_text()
+    names = set(re.findall(r"pub fn (b2q_[a-z0-9_]+)", src))
+    assert names == set(_lib.SIGNATURES)
+    before = src
+    subprocess.run([sys.executable, str(root / "rust" / "b2q-sys" / "gen_ffi.py")], check=True, capture_output=True)
+    assert (root / "rust" / "b2q-sys" / "src" / "lib.rs").read_text() == before
