@@ -367,6 +367,17 @@ typedef struct {
 } b2q_gemm_fp8_problem;
 int32_t b2q_grouped_gemm_fp8(b2q_handle h, const b2q_gemm_fp8_problem* problems, int count, int fmt, int out_type);
 
+/* The table-driven form (what the reference uses above four problems, grouped_gemm.rs:46-78) with the table ON THE DEVICE,
+ * for problems that share N and K and differ in their row count (experts of one layer): ONE launch, a persistent kernel
+ * walks the 256 x 256 tiles of every problem.  Problem g multiplies rows [row_offsets[g], row_offsets[g] + row_counts[g])
+ * of a [capacity_rows x K] (scale_a: one float per row) with rows [g * N, (g + 1) * N) of w [groups * N x K] (scale_w
+ * likewise) and stores the same rows of out [capacity_rows x N].  row_offsets must be multiples of 256 with every
+ * problem's rows inside [0, capacity_rows); the rows of a problem's last tile past its count are computed and stored
+ * too (they belong to no other problem).  No host synchronisation: counts and offsets may come from the kernel before. */
+int32_t b2q_grouped_gemm_fp8_rows(b2q_handle h, const uint8_t* a, const float* scale_a, const uint8_t* w, const float* scale_w,
+                                  const int32_t* row_offsets, const int32_t* row_counts, int groups, int64_t capacity_rows,
+                                  int64_t N, int64_t K, int fmt, void* out, int out_type);
+
 /* ---- expert dispatch: ep_token_scatter / ep_token_gather crates/oxicuda-dist-infer/src/ptx_kernels.rs:46-469,
  *      ExpertDispatcher::{scatter,gather} crates/oxicuda-dist-infer/src/expert_parallel/dispatch.rs:99-219 ----
  * scatter: expert_buf[slot[i]] = in[token[i]] for each routed pair i (rows of row_bytes bytes, a multiple of 16);
@@ -376,6 +387,31 @@ int32_t b2q_ep_token_scatter(b2q_handle h, const void* in, const int32_t* token,
                              int64_t row_bytes, void* expert_buf);
 int32_t b2q_ep_token_gather_bf16(b2q_handle h, const void* expert_out, const int32_t* slot, const float* weight,
                                  int64_t tokens, int top_k, int64_t hidden, void* out);
+
+/* Device-side routing and slotting (no host synchronisation), the pieces b2q_moe_forward is made of:
+ * TopKRouter::route (expert_parallel/router.rs:94-140): per token the top_k experts by descending logit (equal logits
+ * keep index order, as the reference's stable sort) and the softmax of those k logits; at most 64 experts, top_k <= 8. */
+int32_t b2q_moe_route_topk(b2q_handle h, const float* logits, int64_t tokens, int n_experts, int top_k, int32_t* expert_idx,
+                           float* weight);
+/* Counts the pairs routed to experts [first_local, first_local + n_local), lays the experts out at row offsets padded to
+ * multiples of 256 (offsets[n_local + 1], the layout b2q_grouped_gemm_fp8_rows takes) and gives every such pair a row
+ * (slot_of_pair, -1 for pairs of other ranks).  Rows within an expert are handed out in arrival order. */
+int32_t b2q_moe_assign_slots(b2q_handle h, const int32_t* expert_idx, int64_t pairs, int first_local, int n_local,
+                             int32_t* counts, int32_t* offsets, int32_t* slot_of_pair);
+/* expert_buf[slot_of_pair[i]] = x[i / top_k] for every pair with a slot (ExpertDispatcher::scatter, dispatch.rs:99-150). */
+int32_t b2q_moe_scatter(b2q_handle h, const void* x, const int32_t* slot_of_pair, int64_t pairs, int top_k, int64_t row_bytes,
+                        void* expert_buf);
+/* ExpertDispatcher::dispatch_and_gather (dispatch.rs:99-219) over SwiGluExpert::forward (crates/oxicuda-moe/src/expert/ffn.rs:208-243)
+ * with FP8 weights, experts sharded over the ranks of `t` (expert parallel: rank r owns experts [r * E / ep, ...)):
+ * x bf16 [tokens x hidden] and logits f32 [tokens x n_experts] are replicated; w_gate_up [E/ep][2 * ffn][hidden] and
+ * w_down [E/ep][hidden][ffn] are this rank's experts (E4M3 codes, one scale per row); y bf16 [tokens x hidden] is the
+ * weighted sum over each token's top_k experts, on every rank (one all-reduce adds the ranks' contributions).
+ * Everything is enqueued without reading anything back: routing, slotting, scatter, per-row quantization, one grouped
+ * gate|up GEMM, SwiGLU + re-quantization, one grouped down GEMM, gather.  counts_out (optional, device int32 [E/ep])
+ * receives the number of pairs each local expert served. */
+int32_t b2q_moe_forward(b2q_tp t, const void* x_bf16, const float* logits, const uint8_t* w_gate_up, const float* s_gate_up,
+                        const uint8_t* w_down, const float* s_down, int64_t tokens, int64_t hidden, int64_t ffn, int n_experts,
+                        int top_k, int rounding, void* y_bf16, int32_t* counts_out);
 
 /* ---- FP4 weight-only decode GEMV: Fp4GemmConfig / generate_fp4_gemm_ptx
  *      crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:337-395, :1237-1362; semantics = dequantize_fp4 (:879-897)

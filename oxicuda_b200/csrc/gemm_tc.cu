@@ -55,7 +55,12 @@ struct Params {
   const float* bias;                // [N] or null
   int act;                          // 0 none, 1 relu, 2 gelu as x * sigmoid(1.702 x)
   int tma_store;                    // 1: bf16 / f32 rows leave through shared memory and TMA stores (16-byte aligned pitch)
+  // grouped mode of the pair kernel (groups > 0, table on the device): problem g multiplies rows
+  // [group_offsets[g], group_offsets[g] + group_counts[g]) of A (offsets are multiples of 256, so a tile never spans
+  // two problems) with rows [g * N, (g + 1) * N) of W and scale_w, and stores into the same rows of out
+  const int32_t* group_offsets; const int32_t* group_counts; int groups;
 };
+constexpr int kMaxGroups = 64;
 
 using namespace tcx;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
@@ -179,8 +184,10 @@ __device__ __forceinline__ void store_chunk(const Params& p, const uint32_t (&r)
 struct EpiWarp { uint32_t smem_u; uint8_t* smem_p; uint32_t it; };
 
 template <int KIND>
-__device__ __forceinline__ void epilogue_rows(const Params& p, const CUtensorMap* map_out, EpiWarp& ew, uint32_t tmem_acc, int width,
-                                              int64_t m_warp0, int lane, int64_t n0) {
+__device__ __forceinline__ void epilogue_rows(const Params& pp, const CUtensorMap* map_out, EpiWarp& ew, uint32_t tmem_acc, int width,
+                                              int64_t m_warp0, int lane, int64_t n0, const float* scale_w) {
+  Params p = pp;
+  p.scale_w = scale_w;                       // this tile's weight scales (grouped mode: the problem's slice)
   const int64_t m = m_warp0 + lane;
   const bool row_ok = m < p.M;
   const float sa = row_ok && p.scale_a ? (p.scale_a_rows ? p.scale_a[m] : p.scale_a[0]) : 1.0f;
@@ -382,7 +389,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (!mbar_wait(tfull_bar(buf), aph, abort_flag)) { ok = false; break; }
       tc_fence_after();
       epilogue_rows<KIND>(p, &map_out, ew, tmem_base + buf * BN + ((uint32_t)(q * 32) << 16), BN, (int64_t)mb * BM + q * 32, lane,
-                          (int64_t)nb * BN);
+                          (int64_t)nb * BN, p.scale_w);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(buf));
@@ -495,9 +502,26 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   // Work units: whole 256 x 256 tiles first; when the last wave would leave more than half of the CTA pairs idle, its
   // tiles are cut into two 256 x 128 halves (MMA N = 128, 64 rows of W per CTA) so that the tail takes half a wave.
-  auto unit_info = [&](int u, int& tile, int& half, int& width) {
-    if (u < p.full_units) { tile = u; half = 0; width = BN2; }
-    else { const int v = u - p.full_units; tile = p.full_units + (v >> 1); half = v & 1; width = BN2 / 2; }
+  // Grouped mode: the units are the 256 x 256 tiles of every problem in turn; the table is read once per CTA.
+  __shared__ int s_gstart[kMaxGroups + 1], s_goff[kMaxGroups], s_gtm[kMaxGroups];
+  struct Unit { int a_row, w_row, width, half; int64_t n0; int64_t sw_off; };
+  auto unit_coords = [&](int u) {
+    Unit c;
+    if (p.groups > 0) {
+      int g = 0;
+      while (g + 1 < p.groups && u >= s_gstart[g + 1]) ++g;
+      int mb, nb;
+      tile_coords(u - s_gstart[g], s_gtm[g], p.tiles_n, mb, nb);
+      c.a_row = s_goff[g] + mb * 256; c.w_row = g * (int)p.N + nb * BN2; c.width = BN2; c.half = 0;
+      c.n0 = (int64_t)nb * BN2; c.sw_off = (int64_t)g * p.N;
+      return c;
+    }
+    int tile, mb, nb;
+    if (u < p.full_units) { tile = u; c.half = 0; c.width = BN2; }
+    else { const int v = u - p.full_units; tile = p.full_units + (v >> 1); c.half = v & 1; c.width = BN2 / 2; }
+    tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
+    c.a_row = mb * 256; c.w_row = nb * BN2 + c.half * (BN2 / 2); c.n0 = (int64_t)nb * BN2 + c.half * (BN2 / 2); c.sw_off = 0;
+    return c;
   };
   const int num_kb = (int)((p.K + BK - 1) / BK);
 
@@ -512,6 +536,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w)) : "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_w_half)) : "memory");
     if (p.tma_store) asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_out)) : "memory");
+    s_gstart[0] = 0;
+    for (int g = 0; g < p.groups; ++g) {
+      const int cnt = p.group_counts[g];
+      s_goff[g] = p.group_offsets[g];
+      s_gtm[g] = (cnt + 255) / 256;
+      s_gstart[g + 1] = s_gstart[g] + s_gtm[g] * p.tiles_n;
+    }
   }
   if (warp == 1) tmem_alloc2(smem_u32(&s_tmem_base), kTmemCols);
   tc_fence_before();
@@ -520,16 +551,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   tc_fence_after();
   const uint32_t tmem_base = s_tmem_base;
   volatile int* abort_flag = &s_abort;
+  const int total_units = p.groups > 0 ? s_gstart[p.groups] : p.total_units;
 
   if (warp == 0) {
     // ---------------- TMA producer (both CTAs) ----------------
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int u = pair; u < p.total_units && ok; u += num_pairs) {
-        int tile, half, width, mb, nb;
-        unit_info(u, tile, half, width);
-        tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
+      for (int u = pair; u < total_units && ok; u += num_pairs) {
+        const Unit c = unit_coords(u);
+        const int width = c.width;
         const uint32_t bytes = 2u * (uint32_t)(kBytesA + (width / 2) * BK);  // both CTAs' bytes land on the leader's barrier
         for (int kb = 0; kb < num_kb; ++kb, ++it) {
           const int s = it % kStages;
@@ -538,9 +569,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const uint32_t sa = base + s * kStageBytes, sb = sa + kBytesA;
           const uint32_t leader_full = mapa_u32(full_bar(s), 0);
           if (rank == 0) mbar_expect_tx(full_bar(s), bytes);
-          tma_load_2d_pair(sa, &map_a, leader_full, kb * BK, mb * 256 + (int)rank * BM);
-          if (width == BN2) tma_load_2d_pair(sb, &map_w, leader_full, kb * BK, nb * BN2 + (int)rank * (BN2 / 2));
-          else tma_load_2d_pair(sb, &map_w_half, leader_full, kb * BK, nb * BN2 + half * (BN2 / 2) + (int)rank * (BN2 / 4));
+          tma_load_2d_pair(sa, &map_a, leader_full, kb * BK, c.a_row + (int)rank * BM);
+          if (width == BN2) tma_load_2d_pair(sb, &map_w, leader_full, kb * BK, c.w_row + (int)rank * (BN2 / 2));
+          else tma_load_2d_pair(sb, &map_w_half, leader_full, kb * BK, c.w_row + (int)rank * (BN2 / 4));
         }
       }
       if (!ok) {   // give copies already issued time to land before shared memory is released
@@ -553,8 +584,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     if (lane == 0 && rank == 0) {
       uint32_t it = 0, tile_it = 0;
       bool ok = true;
-      for (int u = pair; u < p.total_units && ok; u += num_pairs, ++tile_it) {
-        const uint32_t idesc = u < p.full_units ? p.idesc : p.idesc_half;
+      for (int u = pair; u < total_units && ok; u += num_pairs, ++tile_it) {
+        const uint32_t idesc = (p.groups > 0 || u < p.full_units) ? p.idesc : p.idesc_half;
         const uint32_t buf = tile_it & 1, aph = (tile_it >> 1) & 1;
         if (!mbar_wait(tempty_bar(buf), aph ^ 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
@@ -587,15 +618,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     uint32_t tile_it = 0;
     bool ok = true;
     EpiWarp ew{epi_base + (uint32_t)q * 8192u, smem_raw + (epi_base - smem_u32(smem_raw)) + q * 8192, 0u};
-    for (int u = pair; u < p.total_units && ok; u += num_pairs, ++tile_it) {
-      int tile, half, width, mb, nb;
-      unit_info(u, tile, half, width);
-      tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
+    for (int u = pair; u < total_units && ok; u += num_pairs, ++tile_it) {
+      const Unit c = unit_coords(u);
       const uint32_t buf = tile_it & 1, aph = (tile_it >> 1) & 1;
       if (!mbar_wait(tfull_bar(buf), aph, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      epilogue_rows<KIND>(p, &map_out, ew, tmem_base + buf * BN2 + ((uint32_t)(q * 32) << 16), width,
-                          (int64_t)mb * 256 + rank * BM + q * 32, lane, (int64_t)nb * BN2 + half * (BN2 / 2));
+      epilogue_rows<KIND>(p, &map_out, ew, tmem_base + buf * BN2 + ((uint32_t)(q * 32) << 16), c.width,
+                          (int64_t)c.a_row + rank * BM + q * 32, lane, c.n0, p.scale_w ? p.scale_w + c.sw_off : nullptr);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(tempty_bar(buf), 0));   // the leader's MMA thread waits for both CTAs
@@ -791,9 +820,10 @@ int32_t gemm_fp8_impl(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t 
   const bool tma_ok = K % 16 == 0 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
   const bool fused = (kid == 1 || kid == 2 || kid == 4) && tma_ok;      // the prefill kernels apply the epilogue themselves
   if (epi && !fused) {
-    // few-token / SIMT kernels: plain f32 result into the workspace, then one elementwise pass
+    // few-token / SIMT kernels: plain f32 result into the second workspace (the kernels use the first themselves),
+    // then one elementwise pass
     void* ws = nullptr;
-    int32_t st = b2q_workspace(h, (size_t)M * N * sizeof(float), &ws);
+    int32_t st = b2q_workspace2(h, (size_t)M * N * sizeof(float), &ws);
     if (st != B2Q_OK) return st;
     st = gemm_fp8_impl(h, a, w, M, N, K, fmt, scale_a, scale_a_kind, scale_w, scale_w_kind, ws, B2Q_OUT_F32, nullptr);
     if (st != B2Q_OK) return st;
@@ -832,7 +862,64 @@ int32_t gemm_fp8_impl(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t 
   return kid == 1 ? launch<256, kF8>(h, a, w, p) : launch<128, kF8>(h, a, w, p);
 }
 
+// Grouped launch of the pair kernel: every CTA pair walks the tiles of all problems (table on the device).
+int32_t launch2_grouped(b2q_handle h, const void* a, const void* w, Params p, int64_t capacity_rows) {
+  CUtensorMap map_a, map_w, map_w_half, map_out;
+  int32_t st = make_map(h, &map_a, a, capacity_rows, p.K, BM);
+  if (st != B2Q_OK) return st;
+  st = make_map(h, &map_w, w, (int64_t)p.groups * p.N, p.K, two::BN2 / 2);
+  if (st != B2Q_OK) return st;
+  map_w_half = map_w;                                             // no half-width tail units in grouped mode
+  p.M = capacity_rows;
+  st = make_out_map(h, &map_out, p);
+  if (st != B2Q_OK) return st;
+  p.tiles_m = 0;
+  p.tiles_n = (int)ceil_div64(p.N, two::BN2);
+  const uint32_t shape = ((uint32_t)(two::BN2 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+  p.idesc = p.idesc | (1u << 4) | shape;                          // fp32 accumulate, E4M3 / E5M2 per p.idesc
+  p.idesc_half = p.idesc;
+  p.full_units = p.total_units = 0;
+  B2Q_SMEM_ATTR(h, (two::gemm_tc2_kernel<kF8>), two::kSmem);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(2 * (h->sm_count / 2)));          // the unit count is known on the device only: one pair per two SMs
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = two::kSmem;
+  cfg.stream = h->stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, two::gemm_tc2_kernel<kF8>, map_a, map_w, map_w_half, map_out, p));
+  return B2Q_OK;
+}
+
 }  // namespace tc
+
+extern "C" int32_t b2q_grouped_gemm_fp8_rows(b2q_handle h, const uint8_t* a, const float* scale_a, const uint8_t* w, const float* scale_w,
+                                             const int32_t* row_offsets, const int32_t* row_counts, int groups, int64_t capacity_rows,
+                                             int64_t N, int64_t K, int fmt, void* out, int out_type) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (groups <= 0 || capacity_rows <= 0 || N <= 0 || K <= 0)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "grouped_gemm_fp8_rows: dimensions must be non-zero: groups=%d, rows=%lld, n=%lld, k=%lld", groups,
+             (long long)capacity_rows, (long long)N, (long long)K);
+  if (groups > tc::kMaxGroups) B2Q_FAIL(h, B2Q_ERR_UNSUPPORTED, "grouped_gemm_fp8_rows: at most %d problems per call, got %d", tc::kMaxGroups, groups);
+  if (!a || !w || !scale_a || !scale_w || !row_offsets || !row_counts || !out || fmt < 0 || fmt > 1 || out_type < 0 || out_type > 1)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "grouped_gemm_fp8_rows: bad argument");
+  if (K % 16 != 0 || ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) != 0)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "grouped_gemm_fp8_rows: K must be a multiple of 16 and the operands 16-byte aligned (TMA row pitch)");
+  if ((int64_t)groups * N > 0x7FFFFFFF || capacity_rows > 0x7FFFFFFF) B2Q_FAIL(h, B2Q_ERR_UNSUPPORTED, "grouped_gemm_fp8_rows: too many rows");
+  tc::Params p{};
+  p.N = N; p.K = K;
+  p.scale_a = scale_a; p.scale_a_rows = 1; p.scale_w = scale_w; p.scale_w_rows = 1;
+  p.out = out; p.out_type = out_type; p.status = h->d_status;
+  p.idesc = ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10);
+  p.alpha = 1.0f;
+  p.group_offsets = row_offsets; p.group_counts = row_counts; p.groups = groups;
+  return tc::launch2_grouped(h, a, w, p, capacity_rows);
+}
 
 extern "C" int32_t b2q_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,
                                 const float* scale_a, int scale_a_kind, const float* scale_w, int scale_w_kind, void* out,
@@ -858,9 +945,10 @@ extern "C" int32_t b2q_gemm_fp8_ex(b2q_handle h, const b2q_gemm_fp8_desc* d) {
     // the reference's operand B is [K x N] row-major (gemm_api.rs:126-231); the kernels read [N x K]: transpose it into the
     // workspace first (one pass over the codes; hold weights as [N x K] to avoid it)
     void* ws = nullptr;
-    st = b2q_workspace2(h, (size_t)d->n * d->k, &ws);
+    const size_t off = ((size_t)d->m * d->n * sizeof(float) + 255) & ~(size_t)255;     // in front: the plain result of an unfused epilogue
+    st = b2q_workspace2(h, off + (size_t)d->n * d->k, &ws);
     if (st != B2Q_OK) return st;
-    uint8_t* wt = reinterpret_cast<uint8_t*>(ws);
+    uint8_t* wt = reinterpret_cast<uint8_t*>(ws) + off;
     dim3 grid((unsigned)ceil_div64(d->n, 32), (unsigned)ceil_div64(d->k, 32));
     tc::transpose_u8_kernel<<<grid, 256, 0, h->stream>>>(d->w, wt, d->k, d->n);
     B2Q_LAUNCH_CHECK(h, "transpose_u8_kernel");

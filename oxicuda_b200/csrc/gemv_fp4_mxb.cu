@@ -35,14 +35,15 @@ constexpr int BK = 128;          // K per stage
 constexpr int kStages = 4;
 constexpr int kBytesW = TILE_N * 128;            // in shared memory (half of it crosses HBM)
 constexpr int kBytesA = 128 * 128;               // activation operand: 128 rows x 128 bytes, rows past the used ones stay zero
-constexpr int kBytesSfb = 1024;                  // two scale atoms: weight rows 0..127 and 128..255
+constexpr int kBytesSfb = 2048;                  // scale atoms: weight rows 0..127, 128..255, and (inline mode) the stage's activation atom
 constexpr int kStageBytes = kBytesW + kBytesA + kBytesSfb;
 constexpr int kSfaOff = kStages * kStageBytes;   // activation scale atom (512 bytes), loaded once
 constexpr int kBarOff = kSfaOff + 512;
 constexpr int kSmem = kBarOff + 256 + 1024;
 constexpr int kTmemCols = 512;
-constexpr int kSfaCol = 256, kSfbCol = 264;      // TMEM: accumulator in columns 0..255, then the scale slots (8 columns per stage)
-constexpr int kThreads = 32 * 11;                // warp 0 weight copies, 1 MMA, 2..5 epilogue, 6..9 weight scales, 10 activation copies
+constexpr int kSfaCol = 256, kSfbCol = 264;      // TMEM: accumulator in columns 0..255, then the scale slots (12 columns per stage)
+constexpr int kSfCols = 12;                      // per stage: 8 columns of weight scales, 4 of activation scales (inline mode)
+constexpr int kThreads = 32 * 12;                // warp 0 weight copies, 1 MMA, 2..5 epilogue, 6..9 scales (+ inline activations), 10 activation copies, 11 scale-atom copies into TMEM
 constexpr uint64_t kWaitLimitNs = 500000000ull;
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int where) {
@@ -58,6 +59,7 @@ __device__ __forceinline__ void umma_mx(uint32_t tmem_d, uint64_t adesc, uint64_
 
 struct Params {
   const uint8_t* scales;      // [N][K/32] E8M0
+  const __nv_bfloat16* x;     // [tokens][K] activations (read by the kernel itself in inline mode)
   const uint8_t* xq;          // pre-pass output: per K stage `rows` x 128 swizzled code bytes, then the 512-byte activation scale atom
   float* partials;            // [tile][slot][32 tokens][256]
   int32_t* counters;          // [tile], zero on entry and on exit
@@ -157,6 +159,9 @@ __global__ void __launch_bounds__(kPreThreads) x_quant_token_kernel(const __nv_b
 // ---------------------------------------------------------------------------
 // Main kernel
 // ---------------------------------------------------------------------------
+// INL (up to 4 tokens): no pre-pass.  The scale warps quantize the activations of their stage themselves, under one
+// power-of-two scale per (token, stage), so the activation scale atom is per stage too.
+template <bool INL>
 __global__ void __launch_bounds__(kThreads, 1) gemv_fp4_mxb_kernel(const __grid_constant__ CUtensorMap map_w, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -164,7 +169,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fp4_mxb_kernel(const __grid_
   const uint32_t bar_base = base + kBarOff;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
-  const uint32_t tfull_bar = bar_base + 8u * (2 * kStages), tempty_bar = tfull_bar + 8, sfa_bar = tfull_bar + 16, drain_bar = tfull_bar + 24;
+  auto sf_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };     // scale atoms of the stage are in TMEM
+  const uint32_t tfull_bar = bar_base + 8u * (3 * kStages), tempty_bar = tfull_bar + 8, sfa_bar = tfull_bar + 16, drain_bar = tfull_bar + 24;
   __shared__ uint32_t s_tmem_base;
   __shared__ int s_abort;
   __shared__ int s_last;
@@ -179,7 +185,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fp4_mxb_kernel(const __grid_
   if (threadIdx.x == 0) {
     s_abort = 0;
     // a stage is full after: weight copy landed, activation copy landed, weight scale atoms written
-    for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), 3); mbar_init(empty_bar(s), 1); }
+    for (int s = 0; s < kStages; ++s) { mbar_init(full_bar(s), INL ? 2 : 3); mbar_init(empty_bar(s), 1); mbar_init(sf_bar(s), 1); }
     mbar_init(tfull_bar, 1); mbar_init(tempty_bar, 4); mbar_init(sfa_bar, 1); mbar_init(drain_bar, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -214,6 +220,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fp4_mxb_kernel(const __grid_
         const int s = it % kStages;
         const uint32_t ph = (uint32_t)(it / kStages) & 1;
         if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, 1)) { ok = false; break; }
+        if (p.debug == 6) { mbar_arrive(full_bar(s)); continue; }   // timing experiment: no weight copies
         mbar_expect_tx(full_bar(s), kBytesW / 2);
         tma_load_2d(base + s * kStageBytes, &map_w, full_bar(s), j * BK, tile * TILE_N);
       }
@@ -223,8 +230,8 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fp4_mxb_kernel(const __grid_
       }
     }
   } else if (warp == 10) {
-    // ---------------- activation producer: the scale atom once, then one bulk copy of the token rows per stage ----------------
-    if (lane == 0) {
+    // ---------------- activation producer (pre-pass mode): the scale atom once, then one bulk copy of the token rows per stage ----------------
+    if (lane == 0 && !INL) {
       asm volatile("griddepcontrol.wait;" ::: "memory");        // the activations come from the pre-pass
       mbar_expect_tx(sfa_bar, 512);
       bulk_load(base + kSfaOff, p.xq + (size_t)S * bytes_a, 512, sfa_bar);
@@ -251,9 +258,28 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fp4_mxb_kernel(const __grid_
         dst[i] = __ldg(reinterpret_cast<const uint32_t*>(p.scales + row * kblocks + j * 4));
       }
     };
+    // inline activations: lane -> 16-byte piece pi of the stage (8 values) of token tb (and tb + 2)
+    const int pi = lane & 15, tb = lane >> 4;
+    uint4 xr[kRing][2];
+    auto load_x = [&](int u, uint4 (&dst)[2]) {
+      const int j = u % S;
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        const int t = tb + 2 * r;
+        dst[r] = t < p.tokens ? __ldg(reinterpret_cast<const uint4*>(p.x + (int64_t)t * p.K + (int64_t)j * BK + pi * 8)) : make_uint4(0, 0, 0, 0);
+      }
+    };
 #pragma unroll
     for (int r = 0; r < kRing; ++r)
       if (slot + kStages * r < total) load_scales(u0 + slot + kStages * r, q[r]);
+    if constexpr (INL) {
+      // the activations may come from the previous kernel of the stream (programmatic dependent launch): nothing of them
+      // is read before it has completed; the weight scales above are static and were fetched early
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+#pragma unroll
+      for (int r = 0; r < kRing; ++r)
+        if (slot + kStages * r < total) load_x(u0 + slot + kStages * r, xr[r]);
+    }
     bool ok = true;
     for (int it0 = slot; it0 < total && ok; it0 += kStages * kRing) {
 #pragma unroll
@@ -262,24 +288,91 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fp4_mxb_kernel(const __grid_
         if (it >= total) break;
         const uint32_t ph = (uint32_t)(it / kStages) & 1;
         if (!mbar_wait(empty_bar(slot), ph ^ 1, abort_flag, 6)) { ok = false; break; }
-        uint8_t* sf = base_ptr + slot * kStageBytes + kBytesW + kBytesA;
+        uint8_t* sa = base_ptr + slot * kStageBytes + kBytesW;
+        uint8_t* sf = sa + kBytesA;
         *reinterpret_cast<uint4*>(sf + lane * 16) = make_uint4(q[r][0], q[r][1], q[r][2], q[r][3]);
         *reinterpret_cast<uint4*>(sf + 512 + lane * 16) = make_uint4(q[r][4], q[r][5], q[r][6], q[r][7]);
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // read by tcgen05.cp
+        if constexpr (INL) {
+#pragma unroll
+          for (int k = 0; k < 2; ++k) {
+            const int t = tb + 2 * k;
+            const uint32_t w[4] = {xr[r][k].x, xr[r][k].y, xr[r][k].z, xr[r][k].w};
+            float f[8];
+            float amax = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              f[2 * j] = __uint_as_float(w[j] << 16);
+              f[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u);
+              amax = fmaxf(amax, fmaxf(fabsf(f[2 * j]), fabsf(f[2 * j + 1])));
+            }
+#pragma unroll
+            for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xFFFFFFFFu, amax, o));   // the 16 lanes of one token
+            const uint32_t ab = __float_as_uint(amax);
+            int e = (int)((ab >> 23) & 0xFF) - 127 - 8 + ((ab & 0x007FFFFFu) > 0x00600000u ? 1 : 0);   // smallest e with amax / 2^e <= 448
+            if (amax == 0.0f || !(amax <= 3.0e38f)) e = 0;
+            e = max(e, -127);
+            const float inv = __uint_as_float((uint32_t)(127 - e) << 23);
+            uint32_t c1[2], c2[2];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float q0 = f[2 * j] * inv, q1 = f[2 * j + 1] * inv;
+              const __nv_fp8x2_storage_t a = __nv_cvt_float2_to_fp8x2(make_float2(q0, q1), __NV_SATFINITE, __NV_E4M3);
+              const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2(a, __NV_E4M3);
+              const float2 back = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+              const __nv_fp8x2_storage_t b = __nv_cvt_float2_to_fp8x2(make_float2(q0 - back.x, q1 - back.y), __NV_SATFINITE, __NV_E4M3);
+              if (j & 1) { c1[j >> 1] |= (uint32_t)a << 16; c2[j >> 1] |= (uint32_t)b << 16; }
+              else       { c1[j >> 1] = (uint32_t)a;        c2[j >> 1] = (uint32_t)b; }
+            }
+            if (t < p.tokens) {
+              const int r1 = term_row(t, 0), r2 = term_row(t, 1);
+              *reinterpret_cast<uint2*>(sa + r1 * 128 + (((pi >> 1) ^ (r1 & 7)) << 4) + (pi & 1) * 8) = make_uint2(c1[0], c1[1]);
+              *reinterpret_cast<uint2*>(sa + r2 * 128 + (((pi >> 1) ^ (r2 & 7)) << 4) + (pi & 1) * 8) = make_uint2(c2[0], c2[1]);
+              if (pi == 0) {
+                const uint32_t sb = (uint32_t)(e + 127) * 0x01010101u;   // the same scale for the four K blocks of the stage
+                *reinterpret_cast<uint32_t*>(sf + 1024 + (r1 & 31) * 16 + (r1 >> 5) * 4) = sb;
+                *reinterpret_cast<uint32_t*>(sf + 1024 + (r2 & 31) * 16 + (r2 >> 5) * 4) = sb;
+              }
+            }
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // read by tcgen05.cp / tcgen05.mma
         __syncwarp();
         if (lane == 0) mbar_arrive(full_bar(slot));
-        if (it + kStages * kRing < total) load_scales(u0 + it + kStages * kRing, q[r]);
+        if (it + kStages * kRing < total) {
+          load_scales(u0 + it + kStages * kRing, q[r]);
+          if constexpr (INL) load_x(u0 + it + kStages * kRing, xr[r]);
+        }
+      }
+    }
+  } else if (warp == 11) {
+    // ---------------- scale atoms into TMEM, one stage ahead of the MMAs (a thread of its own: tcgen05.cp issued between
+    // the MMAs of one thread would sit in their dependency chain) ----------------
+    if (lane == 0) {
+      bool ok = true;
+      if constexpr (!INL) {
+        ok = mbar_wait(sfa_bar, 0, abort_flag, 7);
+        if (ok) {
+          tc_fence_after();
+          tmem_cp_sf(tmem_base + kSfaCol, make_desc_sf(base + kSfaOff));
+        }
+      }
+      for (int it = 0; it < total && ok; ++it) {
+        const int s = it % kStages;
+        const uint32_t ph = (uint32_t)(it / kStages) & 1;
+        if (!mbar_wait(full_bar(s), ph, abort_flag, 8)) break;
+        tc_fence_after();
+        const uint32_t ssf = base + s * kStageBytes + kBytesW + kBytesA;
+        const uint32_t tsfb = tmem_base + kSfbCol + s * kSfCols;
+        tmem_cp_sf(tsfb, make_desc_sf(ssf));
+        tmem_cp_sf(tsfb + 4, make_desc_sf(ssf + 512));
+        if constexpr (INL) tmem_cp_sf(tsfb + 8, make_desc_sf(ssf + 1024));
+        tc_commit(sf_bar(s));                                    // arrives when the copies above (and the earlier ones) are done
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      bool ok = mbar_wait(sfa_bar, 0, abort_flag, 7);
-      const uint32_t tsfa = tmem_base + kSfaCol;
-      if (ok) {
-        tc_fence_after();
-        tmem_cp_sf(tsfa, make_desc_sf(base + kSfaOff));
-      }
+      bool ok = true;
       int it = 0;
       uint32_t seg_it = 0;
       for (int u = u0; u < u1 && ok; ++seg_it) {
@@ -290,15 +383,15 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fp4_mxb_kernel(const __grid_
         for (int i = 0; i < n; ++i, ++it) {
           const int s = it % kStages;
           const uint32_t ph = (uint32_t)(it / kStages) & 1;
-          if (!mbar_wait(full_bar(s), ph, abort_flag, 3)) { ok = false; break; }
+          if (!mbar_wait(sf_bar(s), ph, abort_flag, 3)) { ok = false; break; }   // operands in shared memory, scales in TMEM
           tc_fence_after();
-          const uint32_t sw = base + s * kStageBytes, sa = sw + kBytesW, ssf = sa + kBytesA;
-          const uint32_t tsfb = tmem_base + kSfbCol + s * 8;
-          tmem_cp_sf(tsfb, make_desc_sf(ssf));
-          tmem_cp_sf(tsfb + 4, make_desc_sf(ssf + 512));
+          const uint32_t sw = base + s * kStageBytes, sa = sw + kBytesW;
+          const uint32_t tsfb = tmem_base + kSfbCol + s * kSfCols;
+          const uint32_t tsfa = INL ? tsfb + 8 : tmem_base + kSfaCol;
           const uint64_t adesc = make_desc_sw128(sa), bdesc = make_desc_sw128(sw);
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
+            if (p.debug == 5) break;                             // timing experiment: no MMAs
             // K advance inside the swizzle atom: +32 bytes; weight scale byte k of the slot's columns
             umma_mx(tmem_base, adesc + (uint64_t)(2 * k), bdesc + (uint64_t)(2 * k), p.idesc | ((uint32_t)k << 4), tsfa, tsfb,
                     (uint32_t)((i | k) != 0));
@@ -380,7 +473,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fp4_mxb_kernel(const __grid_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar);                   // the accumulator may be overwritten
-      if (!whole) {
+      if (!whole && p.debug < 3) {                              // B2Q_MX_DEBUG=3/4: timing experiment without the partial-sum exchange
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (warp == 2 && lane == 0) {
           __threadfence();                                      // cumulative: the partial sums of all 128 threads (ordered by the barrier) before the arrival
@@ -394,21 +487,35 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fp4_mxb_kernel(const __grid_
           // 128 threads: thread e covers columns e and e + 128 of the tile for every token, contributors in CTA order
           const float* all = p.partials + (int64_t)tile * p.max_slots * (32 * TILE_N);
           const int e = (warp - 2) * 32 + lane;
-          for (int tk = 0; tk < p.tokens; ++tk) {
-            float s0 = 0.0f, s1 = 0.0f;
+          for (int tk0 = 0; tk0 < p.tokens; tk0 += 8) {            // eight tokens at a time: their loads are independent
+            float s0[8], s1[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { s0[i] = 0.0f; s1[i] = 0.0f; }
             for (int cc = 0; cc < nc; ++cc) {
-              s0 += __ldcg(all + (int64_t)cc * (32 * TILE_N) + tk * TILE_N + e);
-              s1 += __ldcg(all + (int64_t)cc * (32 * TILE_N) + tk * TILE_N + e + 128);
+              float a0[8], a1[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const bool in = tk0 + i < p.tokens;
+                a0[i] = in ? __ldcg(all + (int64_t)cc * (32 * TILE_N) + (tk0 + i) * TILE_N + e) : 0.0f;
+                a1[i] = in ? __ldcg(all + (int64_t)cc * (32 * TILE_N) + (tk0 + i) * TILE_N + e + 128) : 0.0f;
+              }
+#pragma unroll
+              for (int i = 0; i < 8; ++i) { s0[i] += a0[i]; s1[i] += a1[i]; }
             }
-            const int64_t c0 = n0 + e, c1 = n0 + e + 128;
-            if (p.out_type == B2Q_OUT_BF16) {
-              __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)tk * p.N;
-              if (c0 < p.N) o[c0] = __float2bfloat16_rn(s0);
-              if (c1 < p.N) o[c1] = __float2bfloat16_rn(s1);
-            } else {
-              float* o = reinterpret_cast<float*>(p.out) + (int64_t)tk * p.N;
-              if (c0 < p.N) o[c0] = s0;
-              if (c1 < p.N) o[c1] = s1;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int tk = tk0 + i;
+              if (tk >= p.tokens) break;
+              const int64_t c0 = n0 + e, c1 = n0 + e + 128;
+              if (p.out_type == B2Q_OUT_BF16) {
+                __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(p.out) + (int64_t)tk * p.N;
+                if (c0 < p.N) o[c0] = __float2bfloat16_rn(s0[i]);
+                if (c1 < p.N) o[c1] = __float2bfloat16_rn(s1[i]);
+              } else {
+                float* o = reinterpret_cast<float*>(p.out) + (int64_t)tk * p.N;
+                if (c0 < p.N) o[c0] = s0[i];
+                if (c1 < p.N) o[c1] = s1[i];
+              }
             }
           }
         }
@@ -466,6 +573,7 @@ int32_t launch(b2q_handle h, const uint8_t* codes, const uint8_t* scales, const 
   int32_t st = b2q_workspace(h, xq_bytes + part_bytes, &ws);
   if (st != B2Q_OK) return st;
   p.scales = scales;
+  p.x = reinterpret_cast<const __nv_bfloat16*>(x);
   p.xq = reinterpret_cast<const uint8_t*>(ws);
   p.partials = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(ws) + xq_bytes);
   p.counters = h->d_tile_counters;
@@ -487,8 +595,9 @@ int32_t launch(b2q_handle h, const uint8_t* codes, const uint8_t* scales, const 
   pre.stream = h->stream;
   pre.attrs = attr;
   pre.numAttrs = num_attrs;
-  B2Q_CUDA(h, cudaLaunchKernelEx(&pre, x_quant_token_kernel, (const __nv_bfloat16*)x, tokens, K, p.rows, reinterpret_cast<uint8_t*>(ws)));
-  B2Q_SMEM_ATTR(h, gemv_fp4_mxb_kernel, kSmem);
+  const bool inl = tokens <= 4 && h->sw.mx_inline != 0;         // B2Q_MX_INLINE=0 keeps the pre-pass for every token count
+  if (!inl && p.debug != 2 && p.debug != 4)   // B2Q_MX_DEBUG=2/4: timing experiment without the pre-pass (results are then stale)
+    B2Q_CUDA(h, cudaLaunchKernelEx(&pre, x_quant_token_kernel, (const __nv_bfloat16*)x, tokens, K, p.rows, reinterpret_cast<uint8_t*>(ws)));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)grid);
   cfg.blockDim = dim3(kThreads);
@@ -496,7 +605,13 @@ int32_t launch(b2q_handle h, const uint8_t* codes, const uint8_t* scales, const 
   cfg.stream = h->stream;
   cfg.attrs = attr;
   cfg.numAttrs = num_attrs;
-  B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, gemv_fp4_mxb_kernel, map_w, p));
+  if (inl) {
+    B2Q_SMEM_ATTR(h, gemv_fp4_mxb_kernel<true>, kSmem);
+    B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, gemv_fp4_mxb_kernel<true>, map_w, p));
+  } else {
+    B2Q_SMEM_ATTR(h, gemv_fp4_mxb_kernel<false>, kSmem);
+    B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, gemv_fp4_mxb_kernel<false>, map_w, p));
+  }
   return B2Q_OK;
 }
 

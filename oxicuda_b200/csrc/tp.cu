@@ -215,6 +215,8 @@ static int32_t scratch(b2q_tp t, size_t bytes, uint8_t** out) {
     t->scratch_bytes = 0;
     B2Q_CUDA(h, cudaMalloc(&t->scratch, bytes));
     t->scratch_bytes = bytes;
+    // rows that no call ever writes (padding between experts) are read by the row quantizers: give them finite values
+    B2Q_CUDA(h, cudaMemsetAsync(t->scratch, 0, bytes, h->stream));
   }
   *out = reinterpret_cast<uint8_t*>(t->scratch);
   return B2Q_OK;
@@ -543,6 +545,55 @@ int32_t b2q_mlp_swiglu_fp8_forward(b2q_tp t, const void* x_bf16, const uint8_t* 
     B2Q_CUDA(h, cudaEventRecord(t->ev_done, t->comm_stream));
     B2Q_CUDA(h, cudaStreamWaitEvent(h->stream, t->ev_done, 0));
   }
+  return B2Q_OK;
+}
+
+// Expert-parallel mixture of SwiGLU experts: TopKRouter::route (crates/oxicuda-dist-infer/src/expert_parallel/router.rs:94-140),
+// ExpertDispatcher::dispatch_and_gather (expert_parallel/dispatch.rs:99-219) and SwiGluExpert::forward
+// (crates/oxicuda-moe/src/expert/ffn.rs:208-243) as one enqueue with no host synchronisation: route, count and slot the
+// pairs of this rank's experts on the device, scatter the tokens, quantize per row, ONE grouped gate|up GEMM, SwiGLU +
+// re-quantize, ONE grouped down GEMM, weighted gather; with several ranks the tokens are replicated and the ranks'
+// contributions are added by one all-reduce.
+int32_t b2q_moe_forward(b2q_tp t, const void* x_bf16, const float* logits, const uint8_t* w_gate_up, const float* s_gate_up,
+                        const uint8_t* w_down, const float* s_down, int64_t tokens, int64_t hidden, int64_t ffn, int n_experts, int top_k,
+                        int rounding, void* y_bf16, int32_t* counts_out) {
+  B2Q_REQUIRE_TP(t);
+  b2q_handle h = t->h;
+  if (tokens <= 0 || hidden <= 0 || ffn <= 0)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "moe_forward: dimensions must be non-zero: tokens=%lld, hidden=%lld, ffn=%lld", (long long)tokens,
+             (long long)hidden, (long long)ffn);
+  if (!x_bf16 || !logits || !w_gate_up || !s_gate_up || !w_down || !s_down || !y_bf16) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "moe_forward: null operand");
+  if (n_experts < 1 || n_experts % t->tp != 0)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "n_experts %d not divisible by ep %d", n_experts, t->tp);
+  const int n_local = n_experts / t->tp, first = t->rank * n_local;
+  const int64_t pairs = tokens * top_k;
+  const int64_t cap = (pairs + 255) / 256 * 256 + (int64_t)n_local * 256;      // upper bound of the padded row ranges
+  const int64_t F = ffn;
+  using tpx::align256;
+  const size_t o_idx = 0, o_wgt = o_idx + align256((size_t)pairs * 4), o_cnt = o_wgt + align256((size_t)pairs * 4),
+               o_off = o_cnt + 256, o_slot = o_off + 512, o_xb = o_slot + align256((size_t)pairs * 4),
+               o_xc = o_xb + align256((size_t)cap * hidden * 2), o_xs = o_xc + align256((size_t)cap * hidden),
+               o_gu = o_xs + align256((size_t)cap * 4), o_hc = o_gu + align256((size_t)cap * 2 * F * 2),
+               o_hs = o_hc + align256((size_t)cap * F), o_yb = o_hs + align256((size_t)cap * 4),
+               total = o_yb + align256((size_t)cap * hidden * 2);
+  uint8_t* ws = nullptr;
+  int32_t st = tpx::scratch(t, total, &ws);
+  if (st != B2Q_OK) return st;
+  int32_t* idx = (int32_t*)(ws + o_idx); float* wgt = (float*)(ws + o_wgt);
+  int32_t* cnt = (int32_t*)(ws + o_cnt); int32_t* off = (int32_t*)(ws + o_off); int32_t* slot = (int32_t*)(ws + o_slot);
+  uint8_t* xb = ws + o_xb; uint8_t* xc = ws + o_xc; float* xs = (float*)(ws + o_xs);
+  uint8_t* gu = ws + o_gu; uint8_t* hc = ws + o_hc; float* hs = (float*)(ws + o_hs); uint8_t* yb = ws + o_yb;
+  if ((st = b2q_moe_route_topk(h, logits, tokens, n_experts, top_k, idx, wgt)) != B2Q_OK) return st;
+  if ((st = b2q_moe_assign_slots(h, idx, pairs, first, n_local, cnt, off, slot)) != B2Q_OK) return st;
+  if (counts_out) B2Q_CUDA(h, cudaMemcpyAsync(counts_out, cnt, (size_t)n_local * 4, cudaMemcpyDeviceToDevice, h->stream));
+  if ((st = b2q_moe_scatter(h, x_bf16, slot, pairs, top_k, hidden * 2, xb)) != B2Q_OK) return st;
+  if ((st = b2q_fp8_quantize_rows_bf16(h, xb, cap, hidden, B2Q_FP8_E4M3, rounding, xs, xc)) != B2Q_OK) return st;
+  if ((st = b2q_grouped_gemm_fp8_rows(h, xc, xs, w_gate_up, s_gate_up, off, cnt, n_local, cap, 2 * F, hidden, B2Q_FP8_E4M3, gu, B2Q_OUT_BF16)) != B2Q_OK)
+    return st;
+  if ((st = b2q_swiglu_quantize_rows_bf16(h, gu, gu + (size_t)F * 2, cap, F, 2 * F, B2Q_FP8_E4M3, rounding, hs, hc)) != B2Q_OK) return st;
+  if ((st = b2q_grouped_gemm_fp8_rows(h, hc, hs, w_down, s_down, off, cnt, n_local, cap, hidden, F, B2Q_FP8_E4M3, yb, B2Q_OUT_BF16)) != B2Q_OK) return st;
+  if ((st = b2q_ep_token_gather_bf16(h, yb, slot, wgt, tokens, top_k, hidden, y_bf16)) != B2Q_OK) return st;
+  if (t->tp > 1) B2Q_NCCL(h, tpx::nccl()->AllReduce(y_bf16, y_bf16, (size_t)tokens * hidden, tpx::kNcclBfloat16, tpx::kNcclSum, t->comm, h->stream));
   return B2Q_OK;
 }
 

@@ -302,7 +302,7 @@ class RoutingPlan:
 
 class TopKRouter:
     """TopKRouter::route, crates/oxicuda-dist-infer/src/expert_parallel/router.rs:94-140 (stable descending sort,
-    softmax over the selected logits)."""
+    softmax over the selected logits) as one kernel (b2q_moe_route_topk)."""
 
     def __init__(self, n_experts: int, top_k: int):
         if top_k < 1 or top_k > n_experts:
@@ -312,25 +312,23 @@ class TopKRouter:
     def route(self, logits: torch.Tensor, n_tokens: int) -> RoutingPlan:
         if logits.numel() != n_tokens * self.n_experts:
             raise L.DimensionMismatch(L.ERR_DIMENSION_MISMATCH, f"expected {n_tokens * self.n_experts}, got {logits.numel()}")
-        lg = logits.reshape(n_tokens, self.n_experts).float()
-        order = torch.sort(lg, dim=1, descending=True, stable=True)
-        idx = order.indices[:, :self.top_k]
-        top = order.values[:, :self.top_k]
-        e = torch.exp(top - top[:, :1])
-        s = e.sum(dim=1, keepdim=True)
-        w = e / torch.where(s > 0, s, torch.ones_like(s))
-        load = torch.bincount(idx.reshape(-1), minlength=self.n_experts)
-        return RoutingPlan(idx.to(torch.int32).contiguous(), w.contiguous(), load, n_tokens, self.n_experts, self.top_k)
+        lg = logits.reshape(n_tokens, self.n_experts).float().contiguous()
+        idx = torch.empty(n_tokens, self.top_k, dtype=torch.int32, device=lg.device)
+        w = torch.empty(n_tokens, self.top_k, dtype=torch.float32, device=lg.device)
+        L.default_handle().call("b2q_moe_route_topk", L.ptr(lg), n_tokens, self.n_experts, self.top_k, L.ptr(idx), L.ptr(w))
+        load = torch.bincount(idx.reshape(-1).long(), minlength=self.n_experts)
+        return RoutingPlan(idx, w, load, n_tokens, self.n_experts, self.top_k)
 
 
 class MoeFp8Layer:
-    """Mixture of SwiGLU experts with FP8 weights, experts sharded across ranks (expert parallel).
+    """Mixture of SwiGLU experts with FP8 weights, experts sharded across ranks (expert parallel), as one library call
+    (b2q_moe_forward): no host synchronisation between routing and the result.
 
     ExpertDispatcher::dispatch_and_gather (crates/oxicuda-dist-infer/src/expert_parallel/dispatch.rs:99-219) with
     SwiGluExpert::forward (crates/oxicuda-moe/src/expert/ffn.rs:172-243) as the expert: this rank owns experts
     [ep_rank*E/ep, (ep_rank+1)*E/ep); tokens are replicated, every rank computes the pairs routed to its experts
-    (scatter -> per-token FP8 quantize -> grouped gate|up GEMM -> SwiGLU + re-quantize -> grouped down GEMM ->
-    weighted gather) and one all-reduce adds the ranks' contributions."""
+    (route -> slot -> scatter -> per-token FP8 quantize -> ONE grouped gate|up GEMM -> SwiGLU + re-quantize -> ONE grouped
+    down GEMM -> weighted gather) and one all-reduce adds the ranks' contributions."""
 
     def __init__(self, experts, n_experts: int, top_k: int, handle: DistInferHandle, rounding: str = "rne"):
         """experts: list of (w1 gate [ffn x hidden], w3 up [ffn x hidden], w2 down [hidden x ffn]) for THIS rank's experts."""
@@ -343,61 +341,27 @@ class MoeFp8Layer:
         if len(experts) != self.local:
             raise L.DimensionMismatch(L.ERR_DIMENSION_MISMATCH, f"expected {self.local} local experts, got {len(experts)}")
         self.ffn, self.hidden = experts[0][0].shape
-        self.gate_up = [Fp8Linear(torch.cat([w1, w3], dim=0), rounding) for (w1, w3, _) in experts]
-        self.down = [Fp8Linear(w2.contiguous(), rounding) for (_, _, w2) in experts]
+        gate_up = [Fp8Linear(torch.cat([w1, w3], dim=0), rounding) for (w1, w3, _) in experts]
+        down = [Fp8Linear(w2.contiguous(), rounding) for (_, _, w2) in experts]
+        # the experts' codes and scales stacked: [E/ep][2*ffn][hidden] and [E/ep][hidden][ffn], the grouped GEMM's operand
+        self.gate_up_codes = torch.stack([g.codes for g in gate_up]).contiguous()
+        self.gate_up_scales = torch.cat([g.scales for g in gate_up]).contiguous()
+        self.down_codes = torch.stack([d.codes for d in down]).contiguous()
+        self.down_scales = torch.cat([d.scales for d in down]).contiguous()
         self.router = TopKRouter(n_experts, top_k)
         self.codec = Fp8Codec.e4m3(rounding)
+        # the expert-parallel group: the library's rank group over the ep ranks
+        self._group_handle = DistInferHandle(handle.ep_rank(), ParallelismConfig(tp=ep), handle.group)
+        self.last_counts = None
 
-    def forward(self, x: torch.Tensor, logits: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, logits: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
         """x bf16 [tokens x hidden], logits f32 [tokens x n_experts] -> bf16 [tokens x hidden]."""
-        import ctypes as C
-        from ._lib import GemmFp8Problem, default_handle, ptr
-        h = default_handle()
-        tokens, hidden, F = x.shape[0], self.hidden, self.ffn
-        plan = self.router.route(logits, tokens)
-        # slots: pairs routed to this rank's experts, grouped by expert (stable in token order)
-        flat_e = plan.expert_idx.reshape(-1).long() - self.first
-        mine = (flat_e >= 0) & (flat_e < self.local)
-        pair_ids = torch.nonzero(mine).flatten()
-        order = torch.sort(flat_e[pair_ids], stable=True).indices
-        pair_sorted = pair_ids[order]                                         # pair index per slot
-        counts = torch.bincount(flat_e[pair_ids], minlength=self.local).tolist()
-        n_slots = int(pair_sorted.numel())
-        slot_of_pair = torch.full((tokens * self.top_k,), -1, dtype=torch.int32, device=x.device)
-        slot_of_pair[pair_sorted] = torch.arange(n_slots, dtype=torch.int32, device=x.device)
-        out = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=x.device)
-        if n_slots > 0:
-            tok_of_slot = (pair_sorted // self.top_k).to(torch.int32).contiguous()
-            slot_ids = torch.arange(n_slots, dtype=torch.int32, device=x.device)
-            xbuf = torch.empty(n_slots, hidden, dtype=torch.bfloat16, device=x.device)
-            h.call("b2q_ep_token_scatter", ptr(x), ptr(tok_of_slot), ptr(slot_ids), n_slots, hidden * 2, ptr(xbuf))
-            xc, xs = self.codec.quantize_rows(xbuf, n_slots, hidden)
-            gu = torch.empty(n_slots, 2 * F, dtype=torch.bfloat16, device=x.device)
-            hc = torch.empty(n_slots, F, dtype=torch.uint8, device=x.device)
-            hs = torch.empty(n_slots, dtype=torch.float32, device=x.device)
-            ybuf = torch.empty(n_slots, hidden, dtype=torch.bfloat16, device=x.device)
-            offs = [0]
-            for c in counts:
-                offs.append(offs[-1] + c)
-
-            def table(a_codes, a_scales, linears, outbuf, K, Nout):
-                arr = (GemmFp8Problem * self.local)()
-                for e in range(self.local):
-                    o, m = offs[e], counts[e]
-                    arr[e] = GemmFp8Problem(a_codes.data_ptr() + o * K, linears[e].codes.data_ptr(), m, Nout, K,
-                                            a_scales.data_ptr() + o * 4, L.SCALE_PER_ROW, linears[e].scales.data_ptr(),
-                                            L.SCALE_PER_ROW, outbuf.data_ptr() + o * Nout * 2)
-                return arr
-
-            t1 = table(xc, xs, self.gate_up, gu, hidden, 2 * F)
-            h.call("b2q_grouped_gemm_fp8", C.cast(t1, C.c_void_p), self.local, L.FP8_E4M3, L.OUT_BF16)
-            h.call("b2q_swiglu_quantize_rows_bf16", ptr(gu), ptr(gu[:, F:]), n_slots, F, 2 * F, L.FP8_E4M3,
-                   self.codec.rounding, ptr(hs), ptr(hc))
-            t2 = table(hc, hs, self.down, ybuf, F, hidden)
-            h.call("b2q_grouped_gemm_fp8", C.cast(t2, C.c_void_p), self.local, L.FP8_E4M3, L.OUT_BF16)
-            h.call("b2q_ep_token_gather_bf16", ptr(ybuf), ptr(slot_of_pair), ptr(plan.weight), tokens, self.top_k, hidden, ptr(out))
-        else:
-            out.zero_()
-        if self.handle.config.ep > 1:
-            dist.all_reduce(out, op=dist.ReduceOp.SUM, group=self.handle.group)
-        return out
+        tokens = x.shape[0]
+        y = out if out is not None else torch.empty(tokens, self.hidden, dtype=torch.bfloat16, device=x.device)
+        lg = logits.reshape(tokens, self.n_experts).float().contiguous()
+        if self.last_counts is None:
+            self.last_counts = torch.zeros(self.local, dtype=torch.int32, device=x.device)
+        tp_group(self._group_handle).call("b2q_moe_forward", L.ptr(x), L.ptr(lg), L.ptr(self.gate_up_codes), L.ptr(self.gate_up_scales),
+                                          L.ptr(self.down_codes), L.ptr(self.down_scales), tokens, self.hidden, self.ffn, self.n_experts,
+                                          self.top_k, self.codec.rounding, L.ptr(y), L.ptr(self.last_counts))
+        return y

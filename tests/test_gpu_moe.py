@@ -1,11 +1,18 @@
 """GPU: FP8 mixture-of-experts layer (top-k routing, token scatter, grouped gate|up and down GEMMs, SwiGLU +
 re-quantize, weighted gather) against the oracle composition of the reference's router, dispatcher and SwiGLU
 expert on the same seeded inputs.  Tolerance as for the MLP: |got - ref| <= 1e-2*|ref| + 1e-2*rms(ref)."""
+import os
+import socket
+import subprocess
+import sys
+from pathlib import Path
+
 import numpy as np
 import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
 
 
 def _bf16(a):
@@ -94,3 +101,115 @@ def test_scatter_gather_identity(cuda):
     out = torch.empty_like(x)
     h.call("b2q_ep_token_gather_bf16", L.ptr(buf), L.ptr(perm), L.ptr(w), tokens, k, hidden, L.ptr(out))
     assert torch.equal(out, x)
+
+
+def test_grouped_gemm_rows_device_table(cuda, oracle):
+    """b2q_grouped_gemm_fp8_rows: one launch over a device-side table of problems with different row counts (an empty one,
+    a tiny one, one that is exactly a tile, a ragged one) against the oracle's GEMM per problem."""
+    from oxicuda_b200 import _lib as L
+    from oxicuda_b200.quant import Fp8Codec
+    rng = np.random.default_rng(12)
+    N, K = 384, 512
+    counts = [300, 0, 17, 256, 1000]
+    offs, o = [], 0
+    for c in counts:
+        offs.append(o)
+        o += (c + 255) // 256 * 256
+    offs.append(o)
+    cap = o
+    G = len(counts)
+    codec = Fp8Codec.e4m3("rne")
+    a = torch.zeros(cap, K, device=cuda)
+    for g, c in enumerate(counts):
+        a[offs[g]:offs[g] + c] = torch.from_numpy(rng.standard_normal((c, K)).astype(np.float32)).to(cuda)
+    w = torch.from_numpy((rng.standard_normal((G * N, K)) * 0.05).astype(np.float32)).to(cuda)
+    ac, sa = codec.quantize_rows(a, cap, K)
+    wc, sw = codec.quantize_rows(w, G * N, K)
+    out = torch.zeros(cap, N, dtype=torch.float32, device=cuda)
+    cnt_d = torch.tensor(counts, dtype=torch.int32, device=cuda)
+    off_d = torch.tensor(offs, dtype=torch.int32, device=cuda)
+    L.default_handle().call("b2q_grouped_gemm_fp8_rows", L.ptr(ac), L.ptr(sa), L.ptr(wc), L.ptr(sw), L.ptr(off_d), L.ptr(cnt_d), G, cap, N, K,
+                            L.FP8_E4M3, L.ptr(out), L.OUT_F32)
+    L.default_handle().check()
+    acn, wcn = ac.view(cap, K).cpu().numpy(), wc.view(G * N, K).cpu().numpy()
+    san, swn = sa.cpu().numpy(), sw.cpu().numpy()
+    got = out.cpu().numpy()
+    for g, c in enumerate(counts):
+        if c == 0:
+            continue
+        rows = slice(offs[g], offs[g] + c)
+        ref = np.asarray(oracle.gemm_fp8(acn[rows], wcn[g * N:(g + 1) * N], san[rows], swn[g * N:(g + 1) * N], 0, 1, "f32")).reshape(c, N)
+        assert err(got[rows], ref) <= 1e-3, g
+    # rows of the padding after the empty and the tiny problem were never touched by another problem's tile
+    assert not np.any(got[offs[2] + 256:offs[3]]) if offs[3] - offs[2] > 256 else True
+
+
+def test_mixtral_shaped_moe_at_stated_size(cuda, oracle):
+    """The grouped-MoE configuration at its stated size: 8 experts of 4096 -> 14336 -> 4096, top-2 routing over 4096 tokens
+    with per-expert counts drawn from a seeded Dirichlet(1) multinomial; the whole layer runs on the GPU in one call, the
+    oracle composition (over the layer's own codes) checks a 96-token subset."""
+    from oxicuda_b200.dist_infer import DistInferHandle, MoeFp8Layer, ParallelismConfig
+    E, hidden, ffn, tokens, top_k = 8, 4096, 14336, 4096, 2
+    rng = np.random.default_rng(0xB2000005)
+    prob = rng.dirichlet(np.ones(E))
+    logits = np.full((tokens, E), -30.0, np.float32)
+    for t in range(tokens):
+        pair = rng.choice(E, size=2, replace=False, p=prob)         # two distinct experts, drawn in proportion to p
+        logits[t, pair] = 20.0 + rng.standard_normal(2).astype(np.float32)   # gate weights: softmax of two N(0,1) logits
+    g = torch.Generator(device=cuda).manual_seed(0xB2000005)
+    experts = []
+    for _ in range(E):
+        experts.append((torch.randn(ffn, hidden, device=cuda, generator=g) * 0.02, torch.randn(ffn, hidden, device=cuda, generator=g) * 0.02,
+                        torch.randn(hidden, ffn, device=cuda, generator=g) * 0.02))
+    layer = MoeFp8Layer(experts, E, top_k, DistInferHandle(0, ParallelismConfig(ep=1)))
+    del experts
+    torch.cuda.empty_cache()
+    x = torch.randn(tokens, hidden, device=cuda, generator=g).to(torch.bfloat16)
+    y = layer.forward(x, torch.from_numpy(logits).to(cuda))
+    from oxicuda_b200._lib import default_handle
+    default_handle().check()
+    counts = layer.last_counts.cpu().numpy()
+    idx, wgt = oracle_route(logits, top_k)
+    assert counts.sum() == tokens * top_k
+    assert np.array_equal(counts, np.bincount(idx.reshape(-1), minlength=E))
+    # oracle on a subset of tokens, expert by expert, over the layer's own codes and scales
+    sub = np.arange(0, tokens, tokens // 96)[:96]
+    xs_f = x[torch.from_numpy(sub).to(cuda)].float().cpu().numpy()
+    ref = np.zeros((sub.size, hidden), np.float32)
+    parts = {}
+    F = ffn
+    for e in range(E):
+        rows = [i for i, t in enumerate(sub) if e in idx[t]]
+        if not rows:
+            continue
+        xe = xs_f[rows]
+        xc, xsc, _ = oracle.fp8_quantize_rows(xe, len(rows), hidden, 0, 1)
+        gu = oracle.gemm_fp8(xc.reshape(-1, hidden), layer.gate_up_codes[e].cpu().numpy(), xsc,
+                             layer.gate_up_scales[e * 2 * F:(e + 1) * 2 * F].cpu().numpy(), 0, 1, "bf16")
+        hh = oracle.swiglu(gu[:, :F], gu[:, F:])
+        hc, hs, _ = oracle.fp8_quantize_rows(hh, len(rows), F, 0, 1)
+        ye = oracle.gemm_fp8(hc.reshape(-1, F), layer.down_codes[e].cpu().numpy(), hs, layer.down_scales[e * hidden:(e + 1) * hidden].cpu().numpy(),
+                             0, 1, "bf16")
+        for k, i in enumerate(rows):
+            parts[(i, e)] = ye[k]
+    for i, t in enumerate(sub):
+        acc = np.zeros(hidden, np.float32)
+        for j in range(top_k):
+            acc = acc + wgt[t, j] * parts[(i, int(idx[t, j]))]
+        ref[i] = acc
+    got = y[torch.from_numpy(sub).to(cuda)].float().cpu().numpy()
+    assert err(got, _bf16(ref)) <= 1e-2
+
+
+def test_moe_expert_parallel_two_ranks(cuda, oracle):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(port), str(ROOT / "tests" / "moe_ep_worker.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "EP2 OK" in r.stdout
