@@ -134,8 +134,9 @@ int32_t b2q_swiglu_quantize_rows_bf16(b2q_handle h, const void* gate, const void
  * `rows` to 1024 slices per call (B2Q_ERR_BUFFER_TOO_SMALL beyond that, with the reason written to `err`).
  * The first call on each device looks up the array's address; make that call outside stream capture.  All calls on a
  * device share the array, so calls that may overlap on the GPU must be ordered by the caller.  `stream` is a
- * cudaStream_t; `device_status` (optional, 1 x int32 on the device, zeroed by the caller) receives
- * B2Q_ERR_NON_FINITE_FP8 if the input holds NaN/Inf; `err`/`err_len` (optional) receive a message on failure.
+ * cudaStream_t; `device_status` (1 x int32 on the device, zeroed by the caller) receives
+ * B2Q_ERR_NON_FINITE_FP8 if the input holds NaN/Inf; with NULL that detection is off (there is no handle whose status
+ * word could hold it) and non-finite inputs are encoded silently; `err`/`err_len` (optional) receive a message on failure.
  * Same results as b2q_fp8_quantize_rows_f32. */
 int32_t b2q_fp8_quantize_rows_f32_noalloc(const float* x, int64_t rows, int64_t cols, int fmt, int rounding,
                                           float* scales, uint8_t* codes, void* stream, int32_t* device_status,
@@ -428,12 +429,25 @@ int32_t b2q_gemv_fp4_wo(b2q_handle h, const uint8_t* codes, const void* scales, 
                         const void* x_bf16, int64_t tokens, int64_t N, int64_t K, void* out, int out_type);
 
 /* Weight-only FP4 GEMM for any token count (prefill): same operands and semantics as b2q_gemv_fp4_wo plus `format`
- * (B2Q_FP4_E2M1 or B2Q_FP4_INT4) and blocks of 32, 64 or 128.  32 tokens or fewer go to the decode GEMV; above that the
- * weights are expanded to bf16 in the handle's workspace (N*K*2 bytes, kept for later calls) and multiplied on tcgen05
- * (kind::f16, fp32 accumulation).  Fp4GemmConfig::validate order: zero dims, odd K, block size
+ * (B2Q_FP4_E2M1 or B2Q_FP4_INT4) and blocks of 32, 64 or 128.  32 tokens or fewer go to the decode GEMV; above that E2M1
+ * codes with E8M0 scales of block 32 run on the block-scaled tensor-core GEMM (b2q_gemm_fp4_blockscaled, split
+ * activations); what that instruction cannot express (f32 scales, INT4 codes, blocks of 64 / 128) is expanded to bf16 in
+ * the handle's workspace (N*K*2 bytes) and multiplied on tcgen05 (kind::f16, fp32 accumulation).  Fp4GemmConfig::validate order: zero dims, odd K, block size
  * (crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:354-376). */
 int32_t b2q_gemm_fp4_wo(b2q_handle h, const uint8_t* codes, const void* scales, int scale_format, int block, int format,
                         const void* x_bf16, int64_t tokens, int64_t N, int64_t K, void* out, int out_type);
+
+/* The same product on the block-scaled tensor-core instruction (tcgen05.mma kind::mxf8f6f4.block_scale): E2M1 codes and
+ * E8M0 block scales (block 32) feed the MMA as stored, nothing is expanded in HBM.  K % 128 == 0, codes 32-byte aligned.
+ * act_mode: B2Q_FP4_ACT_SPLIT keeps weight-only semantics (every bf16 activation enters as the sum of two E4M3 codes under
+ * its 32-block's power-of-two scale, exact to 2^-18 of the block maximum; 64 tokens per 128-row tile);
+ * B2Q_FP4_ACT_MXFP8 quantizes the activations to one E4M3 code under an E8M0 scale per 32 values (the MX W4A8 recipe,
+ * twice the rate): the result is that of the quantized activations -- no counterpart in the reference, whose
+ * activations stay f32 (parity by composition: the same activation quantizer, then dequantize_fp4 and an f32 matmul).
+ * b2q_gemm_fp4_wo takes this path (SPLIT) for E2M1 codes with E8M0 scales of block 32 and more than 32 tokens. */
+typedef enum { B2Q_FP4_ACT_SPLIT = 0, B2Q_FP4_ACT_MXFP8 = 1 } b2q_fp4_act_mode;
+int32_t b2q_gemm_fp4_blockscaled(b2q_handle h, const uint8_t* codes, const uint8_t* scales_e8m0, const void* x_bf16,
+                                 int64_t tokens, int64_t N, int64_t K, int act_mode, void* out, int out_type);
 
 /* ---- tile heuristics: classify_workload / Fp8TileHeuristic::select crates/oxicuda-blas/src/precision/fp8_ops.rs:67-107,
  *      :239-304; select_fp4_tile fp4_fp6_ops.rs:996-1075; Int8GemmConfig::tile_config int_ops.rs:141-176 ---- */

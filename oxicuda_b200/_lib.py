@@ -178,6 +178,7 @@ SIGNATURES = {
     "b2q_column_linear_forward": (C.c_int32, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _P]),
     "b2q_row_linear_forward_allreduce": (C.c_int32, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P]),
     "b2q_mlp_swiglu_fp8_forward": (C.c_int32, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I, _P]),
+    "b2q_gemm_fp4_blockscaled": (C.c_int32, [_H, _P, _P, _P, _I64, _I64, _I64, _I, _P, _I]),
     "b2q_classify_workload": (C.c_int32, [_U32, _U32, _U32]),
     "b2q_ref_tile_config": (C.c_int32, [_I, _U32, _U32, _U32, C.POINTER(TileConfig)]),
     "b2q_fp8_compute_split_k": (_U32, [_U32, _U32, _U32]),
@@ -263,6 +264,17 @@ class Handle:
 
 
 _default = {}
+
+
+def reset_default_handles():
+    """Drops the cached per-device handles: the next default_handle() creates a new one, which re-reads the B2Q_*
+    experiment switches from the environment (a handle reads them once, when it is created)."""
+    import torch
+    if torch.cuda.is_available():
+        torch.cuda.synchronize()
+    for h in _default.values():
+        h.close()
+    _default.clear()
 
 
 def default_handle(device: int | None = None) -> Handle:

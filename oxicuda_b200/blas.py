@@ -262,6 +262,18 @@ def gemm_fp4_wo(codes: torch.Tensor, scales: torch.Tensor, x: torch.Tensor, N: i
     return out
 
 
+def gemm_fp4_blockscaled(codes: torch.Tensor, scales: torch.Tensor, x: torch.Tensor, N: int, K: int, mxfp8_activations: bool = False,
+                         out: torch.Tensor = None, out_dtype=torch.bfloat16) -> torch.Tensor:
+    """b2q_gemm_fp4_blockscaled: E2M1 codes + E8M0 block-32 scales on tcgen05 kind::mxf8f6f4.block_scale.  Default: split
+    activations (weight-only semantics); mxfp8_activations=True quantizes them to MX E4M3 (W4A8)."""
+    tokens = x.shape[0]
+    if out is None:
+        out = torch.empty(tokens, N, dtype=out_dtype, device=x.device)
+    ot = L.OUT_BF16 if out.dtype == torch.bfloat16 else L.OUT_F32
+    default_handle().call("b2q_gemm_fp4_blockscaled", ptr(codes), ptr(scales), ptr(x), tokens, N, K, 1 if mxfp8_activations else 0, ptr(out), ot)
+    return out
+
+
 # ---- INT4 group-scaled weight-only linear: crates/oxicuda-blas/src/precision/int_ops.rs:196-429, :602-757 ----
 @dataclass
 class Int4GemmConfig:

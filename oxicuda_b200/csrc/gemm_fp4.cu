@@ -46,6 +46,9 @@ extern "C" int32_t b2q_gemm_fp4_wo(b2q_handle h, const uint8_t* codes, const voi
     B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemm_fp4_wo: bad argument");
   if (tokens <= 32 && block == 32 && format == 0 && K % 128 == 0)
     return b2q_gemv_fp4_wo(h, codes, scales, scale_format, block, x_bf16, tokens, N, K, out, out_type);
+  if (scale_format == B2Q_SCALE_E8M0 && block == 32 && format == 0 && K % 128 == 0 && (reinterpret_cast<uintptr_t>(codes) & 31) == 0 &&
+      (reinterpret_cast<uintptr_t>(scales) & 3) == 0 && (reinterpret_cast<uintptr_t>(x_bf16) & 15) == 0)
+    return b2q_gemm_fp4_blockscaled(h, codes, (const uint8_t*)scales, x_bf16, tokens, N, K, B2Q_FP4_ACT_SPLIT, out, out_type);
   if (K % block != 0 || K % 16 != 0) B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "gemm_fp4_wo: K must be a multiple of the block size and of 16, got %lld", (long long)K);
   if (((reinterpret_cast<uintptr_t>(codes) & 7) | (reinterpret_cast<uintptr_t>(x_bf16) & 15)) != 0)
     B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemm_fp4_wo: codes must be 8-byte and activations 16-byte aligned");

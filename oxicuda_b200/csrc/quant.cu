@@ -1039,7 +1039,9 @@ constexpr int kNoAllocWords = 4 * kNoAllocMaxRows + 64;       // 4 keys per slic
 static __device__ __align__(256) uint32_t g_noalloc_scratch[kNoAllocWords];
 
 namespace {
-struct NoAllocDevice { uint32_t* ptr; int sm_count; bool ready; };
+// per-device set-up record; `ready` is published with release / read with acquire, so a second host thread that sees it
+// set also sees ptr and sm_count (two threads racing through the set-up write the same values)
+struct NoAllocDevice { uint32_t* ptr; int sm_count; std::atomic<int> ready; };
 NoAllocDevice g_noalloc_dev[64];
 
 void noalloc_msg(char* err, size_t err_len, const char* fmt, long long a, long long b) {
@@ -1063,7 +1065,7 @@ extern "C" int32_t b2q_fp8_quantize_rows_f32_noalloc(const float* x, int64_t row
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { noalloc_msg(err, err_len, "no current CUDA device (%lld, %lld)", dev, 0); return B2Q_ERR_CUDA; }
   NoAllocDevice& d = g_noalloc_dev[dev];
-  if (!d.ready) {                                             // once per device, with that device current
+  if (!d.ready.load(std::memory_order_acquire)) {             // once per device, with that device current
     void* p = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
     if (e != cudaSuccess || !p) { noalloc_msg(err, err_len, "cudaGetSymbolAddress failed with CUDA error %lld on device %lld", (int)e, dev); return B2Q_ERR_CUDA; }
@@ -1071,7 +1073,7 @@ extern "C" int32_t b2q_fp8_quantize_rows_f32_noalloc(const float* x, int64_t row
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 128;
     d.ptr = (uint32_t*)p;
     d.sm_count = sms;
-    d.ready = true;
+    d.ready.store(1, std::memory_order_release);
   }
   cudaStream_t st = (cudaStream_t)stream;
   uint32_t* keys = d.ptr;

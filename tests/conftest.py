@@ -44,3 +44,19 @@ def cuda():
     _build.build()
     torch.cuda.set_device(0)
     return torch.device("cuda:0")
+
+
+@pytest.fixture
+def switches(monkeypatch):
+    """Sets B2Q_* experiment switches for one test: the library reads them when a handle is created, so the cached
+    default handles are dropped before the test body runs and again after it."""
+    from oxicuda_b200 import _lib
+
+    def set_(**kw):
+        for k, v in kw.items():
+            monkeypatch.setenv(k, str(v))
+        _lib.reset_default_handles()
+
+    yield set_
+    monkeypatch.undo()
+    _lib.reset_default_handles()

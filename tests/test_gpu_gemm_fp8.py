@@ -64,11 +64,11 @@ def test_gemm_fp8_vs_oracle(cuda, oracle, M, N, K):
 
 @pytest.mark.parametrize("M,N,K", [(1, 256, 128), (7, 1000, 1024), (16, 4096, 4096), (17, 300, 256), (33, 640, 2048),
                                    (64, 2304, 1024), (100, 520, 384), (128, 1024, 512), (4, 19000, 256), (2, 40000, 128)])
-def test_weight_stationary_tcgen05_kernel(cuda, oracle, M, N, K, monkeypatch):
+def test_weight_stationary_tcgen05_kernel(cuda, oracle, M, N, K, switches):
     """The few-token kernel (weights as the M = 128 operand), forced on: one tile per CTA, several tiles per CTA
     (19000 and 40000 rows), the even split with partial sums (few rows, long K), ragged last tiles, every token padding."""
     from oxicuda_b200.blas import gemm_fp8
-    monkeypatch.setenv("B2Q_FP8_SKINNY", "1")
+    switches(B2Q_FP8_SKINNY=1)
     rng = np.random.default_rng(M * 11 + N * 5 + K)
     a = rng.standard_normal((M, K)).astype(np.float32)
     w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
@@ -88,13 +88,13 @@ def test_weight_stationary_tcgen05_kernel(cuda, oracle, M, N, K, monkeypatch):
     assert rel_err(got.cpu().numpy(), ref) <= 1e-3
 
 
-def test_weights_written_right_before_the_call(cuda, oracle, monkeypatch):
+def test_weights_written_right_before_the_call(cuda, oracle, switches):
     """With static_weights off the few-token kernel reads nothing before the previous kernel of the stream (here the
     one that produces the weight codes) has completed."""
     from oxicuda_b200.blas import gemm_fp8
     from oxicuda_b200.quant import Fp8Codec
     from oxicuda_b200._lib import default_handle
-    monkeypatch.setenv("B2Q_FP8_SKINNY", "1")
+    switches(B2Q_FP8_SKINNY=1)
     h = default_handle()
     h.set_static_weights(False)
     try:

@@ -45,20 +45,31 @@ def test_ragged_shapes(cuda, oracle, tokens, N, K):
 
 
 @pytest.mark.parametrize("tokens,N,K", [(4, 38400, 1024), (1, 28672, 4096), (32, 14336, 4096), (8, 4096, 14336), (5, 13400, 2560)])
-def test_tensor_core_block_scaled_path(cuda, oracle, tokens, N, K, monkeypatch):
+def test_tensor_core_block_scaled_path(cuda, oracle, tokens, N, K, switches):
     """The tcgen05 kind::mxf8f6f4 kernel, forced on: several whole tiles per CTA (38400 rows = 300 tiles), one tile
     per CTA, the even split with partial sums (4096 rows), a ragged last tile (13400 rows)."""
-    monkeypatch.setenv("B2Q_GEMV_MX", "1")
+    switches(B2Q_GEMV_MX=1)
     assert _case(cuda, oracle, tokens, N, K, 1, 11 * tokens + N, torch.float32) <= 2e-3
     assert _case(cuda, oracle, tokens, N, K, 1, 13 * tokens + N, torch.bfloat16) <= TOL
 
 
-def test_back_to_back_calls_with_different_operands(cuda, oracle, monkeypatch):
+@pytest.mark.parametrize("tokens,N,K", [(1, 28672, 4096), (3, 4096, 4096), (4, 13400, 2560), (5, 14336, 4096), (16, 4096, 14336), (24, 8192, 1024),
+                                        (7, 300, 256)])
+def test_dense_format_mxf4_kernel(cuda, oracle, tokens, N, K, switches):
+    """The tcgen05 kind::mxf4 kernel (dense 4-bit operands, activations as five E2M1 terms), forced on: whole tiles and the
+    even split with partial sums, the in-kernel activation split (up to 4 tokens) and the pre-pass (5 to 24), ragged
+    last tiles.  Five terms leave under 1e-4 of a block's maximum, so the f32 bound of the other kernels holds."""
+    switches(B2Q_GEMV_STREAM=2)
+    assert _case(cuda, oracle, tokens, N, K, 1, 17 * tokens + N, torch.float32) <= 2e-3
+    assert _case(cuda, oracle, tokens, N, K, 1, 19 * tokens + N, torch.bfloat16) <= TOL
+
+
+def test_back_to_back_calls_with_different_operands(cuda, oracle, switches):
     """Consecutive launches overlap their tails (programmatic dependent launch): every call must still see its own
     activations, scales and partial sums."""
     from oxicuda_b200.blas import gemv_fp4_wo
     from oxicuda_b200._lib import default_handle
-    monkeypatch.setenv("B2Q_GEMV_MX", "1")
+    switches(B2Q_GEMV_MX=1)
     rng = np.random.default_rng(7)
     N, K = 4096, 4096
     sets = []
@@ -172,3 +183,37 @@ def test_prefill_fp4_weight_only_gemm(cuda, oracle, tokens, N, K, block):
         got = gemm_fp4_wo(_t(codes, cuda), _t(scales, cuda), x.to(cuda), N, K, block=block, format=Fp4Format.Int4, out_dtype=torch.float32)
         rms = np.sqrt((ref ** 2).mean())
         assert float((np.abs(got.cpu().numpy() - ref) / (np.abs(ref) + rms)).max()) <= TOL
+
+
+@pytest.mark.parametrize("tokens,N,K", [(128, 256, 128), (200, 300, 512), (64, 1024, 4096), (1000, 520, 1024), (4096, 14336, 4096)])
+def test_blockscaled_prefill_gemm(cuda, oracle, tokens, N, K):
+    """b2q_gemm_fp4_blockscaled: the weights feed tcgen05 kind::mxf8f6f4.block_scale as stored.  Split activations keep the
+    weight-only result (<= 1e-2, f32 out 2e-3); MX E4M3 activations match the oracle composed with the same activation
+    quantizer (restated here in numpy over the oracle's E4M3 codec).  The largest case is a stated prefill shape and is
+    checked on a sample of rows."""
+    from oxicuda_b200.blas import MicroScalingConfig, MicroScalingQuantizer, ScalingFormat, gemm_fp4_blockscaled
+    big = tokens * N * K > 2e10
+    g = torch.Generator(device=cuda).manual_seed(tokens + N + K)
+    w = torch.randn(N * K, device=cuda, generator=g) * 0.02
+    codes, scales = MicroScalingQuantizer(MicroScalingConfig(32, ScalingFormat.E8M0)).quantize_fp4(w)
+    x = torch.randn(tokens, K, device=cuda, generator=g).to(torch.bfloat16)
+    rows = np.arange(0, tokens, max(1, tokens // 48))[:48] if big else np.arange(tokens)
+    xs = x[torch.from_numpy(rows).to(cuda)].cpu()
+    xb = xs.view(torch.int16).numpy().view(np.uint16)
+    cn, sn = codes.cpu().numpy(), scales.cpu().numpy()
+    ref = np.asarray(oracle.gemv_fp4(cn, sn, xb, rows.size, N, K, 32, "f32"), np.float64).reshape(rows.size, N)
+    got = gemm_fp4_blockscaled(codes, scales, x, N, K, out_dtype=torch.float32)[torch.from_numpy(rows).to(cuda)].cpu().numpy()
+    assert rel_err(got, ref) <= 2e-3
+    got16 = gemm_fp4_blockscaled(codes, scales, x, N, K)[torch.from_numpy(rows).to(cuda)].float().cpu().numpy()
+    assert rel_err(got16, _t(ref.astype(np.float32), "cpu").to(torch.bfloat16).float().numpy()) <= TOL
+    # W4A8: one E4M3 code per activation under the block's power-of-two scale (smallest 2^e with max / 2^e <= 448)
+    xf = xs.float().numpy().reshape(rows.size, K // 32, 32)
+    amax = np.abs(xf).max(axis=2, keepdims=True)
+    e = np.where(amax > 0, np.ceil(np.log2(np.maximum(amax, 1e-38) / 448.0)), 0.0)
+    e = np.maximum(e, -127.0)
+    q = oracle.fp8_decode(oracle.fp8_encode((xf / np.exp2(e)).astype(np.float32).reshape(-1), 0, 1)[0], 0, 1).reshape(xf.shape) * np.exp2(e)
+    xq = torch.from_numpy(q.reshape(rows.size, K).astype(np.float32)).to(torch.bfloat16)     # exact: four significant bits
+    assert np.array_equal(xq.float().numpy(), q.reshape(rows.size, K).astype(np.float32))
+    ref8 = np.asarray(oracle.gemv_fp4(cn, sn, xq.view(torch.int16).numpy().view(np.uint16), rows.size, N, K, 32, "f32"), np.float64).reshape(rows.size, N)
+    got8 = gemm_fp4_blockscaled(codes, scales, x, N, K, mxfp8_activations=True, out_dtype=torch.float32)[torch.from_numpy(rows).to(cuda)].cpu().numpy()
+    assert rel_err(got8, ref8) <= 2e-3

@@ -72,6 +72,47 @@ def test_mlp_tp1_matches_oracle(cuda, oracle, tokens):
     assert np.median(np.abs(y - ref) / (np.abs(ref) + 1e-6)) < 5e-3
 
 
+@pytest.mark.parametrize("tokens", [1, 64])
+def test_mlp_at_stated_size_hidden8192_ffn28672(cuda, oracle, tokens):
+    """The tensor-parallel MLP configuration at its stated size (hidden 8192, FFN 28672; 1 and 64 tokens): the un-sharded
+    layer through b2q_mlp_swiglu_fp8_forward, and the layer cut into 8 tensor-parallel shards run on this one GPU
+    (every shard's partial, added in rank order), each against the oracle composition over the same codes."""
+    from oxicuda_b200.dist_infer import DistInferHandle, ParallelismConfig, TpFp8Mlp
+    hidden, ffn = 8192, 28672
+    g = torch.Generator(device=cuda).manual_seed(0xB2000003)
+    wg = torch.randn(ffn, hidden, device=cuda, generator=g) * 0.01
+    wu = torch.randn(ffn, hidden, device=cuda, generator=g) * 0.01
+    wd = torch.randn(hidden, ffn, device=cuda, generator=g) * 0.01
+    x = torch.randn(tokens, hidden, device=cuda, generator=g).to(torch.bfloat16)
+    xf = x.float().cpu().numpy()
+    xc, xs, _ = oracle.fp8_quantize_rows(xf, tokens, hidden, 0, 1)
+
+    def oracle_over(shards):
+        total = None
+        for sh in shards:
+            F = sh.local_ffn
+            gu = oracle.gemm_fp8(xc.reshape(tokens, hidden), sh.gate_up.codes.cpu().numpy(), xs, sh.gate_up.scales.cpu().numpy(), 0, 1, "bf16")
+            h = oracle.swiglu(gu[:, :F], gu[:, F:])
+            hc, hs, _ = oracle.fp8_quantize_rows(h, tokens, F, 0, 1)
+            part = _bf16_round(oracle.gemm_fp8(hc.reshape(tokens, F), sh.down.codes.cpu().numpy(), hs, sh.down.scales.cpu().numpy(), 0, 1, "f32"))
+            total = part if total is None else _bf16_round(total + part)
+        return total
+
+    full = TpFp8Mlp(wg, wu, wd, DistInferHandle(0, ParallelismConfig(tp=1)))
+    y = full.forward(x).float().cpu().numpy()
+    assert rel_err(y, oracle_over([full])) <= 1e-2
+    del full
+    shards = [TpFp8Mlp(wg, wu, wd, DistInferHandle(r, ParallelismConfig(tp=8))) for r in range(8)]
+    del wg, wu, wd
+    total = None
+    for sh in shards:                                       # what the 8 ranks compute, one after the other on this GPU
+        part = sh.forward_partial(x).float()
+        total = part if total is None else (total + part).to(torch.bfloat16).float()
+    # eight independent re-quantizations of the SwiGLU result (one per shard) give eight chances for an exp() last-bit
+    # difference to move a row's largest value to the neighbouring E4M3 code: twice the single-layer bound
+    assert rel_err(total.cpu().numpy(), oracle_over(shards)) <= 2e-2
+
+
 def test_swiglu_quantize_kernel_against_oracle(cuda, oracle):
     from oxicuda_b200 import _lib as L
     rng = np.random.default_rng(9)
