@@ -906,12 +906,12 @@ extern "C" int32_t b2q_gemv_fp4_wo(b2q_handle h, const uint8_t* codes, const voi
   const int t = (int)tokens;
   const bool small_n = N <= 2048;
   {
-    // E8M0 scales, up to 24 tokens, matrices with a 256-row tile for (nearly) every SM and 64 MiB of codes or more: the
+    // E8M0 scales, up to 16 tokens, matrices with a 256-row tile for (nearly) every SM and 64 MiB of codes or more: the
     // dense-format kernel (tcgen05 kind::mxf4, twice the bytes in flight; measured 27.9 against 29.8 us on 8192 x 28672).
-    // Below that its fixed cost per call (five-term activation split, six scale copies per stage, partial-sum exchange)
+    // Below that its fixed cost per call (seven-term activation split, six scale copies per stage, partial-sum exchange)
     // loses to the kernels below.  B2Q_GEMV_STREAM=2 / 0 forces it on (wherever it applies) / off.
     const bool pays = N >= 256 * 104 && N * (K / 2) >= ((int64_t)64 << 20);
-    if (scale_format == B2Q_SCALE_E8M0 && t <= 24 && (h->sw.gemv_stream >= 0 ? h->sw.gemv_stream == 2 : pays)) {
+    if (scale_format == B2Q_SCALE_E8M0 && t <= 16 && (h->sw.gemv_stream >= 0 ? h->sw.gemv_stream == 2 : pays)) {
       const int32_t st = b2q_gemv_fp4_mxf4_dispatch(h, codes, scales, x_bf16, t, N, K, out, out_type);
       if (st != B2Q_ERR_UNSUPPORTED) return st;
     }

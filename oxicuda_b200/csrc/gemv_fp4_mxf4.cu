@@ -1,5 +1,5 @@
 // Block-scaled FP4 (E2M1 codes, E8M0 scale per 32) weight-only decode GEMV on tcgen05.mma kind::mxf4: the DENSE 4-bit
-// operand format.     out[t, n] = sum_k x[t, k] * decode(codes[n, k]) * 2^(scale[n, k / 32] - 127)        tokens <= 24
+// operand format.     out[t, n] = sum_k x[t, k] * decode(codes[n, k]) * 2^(scale[n, k / 32] - 127)        tokens <= 16
 // (Fp4GemmConfig / MicroScalingQuantizer semantics, crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:337-395, :879-897.)
 //
 // Why the dense format.  kind::mxf8f6f4 reads 4-bit codes from a padded layout (8 data + 8 pad bytes per 16 codes): a
@@ -7,16 +7,17 @@
 // 1.2-1.5 us round trip that caps an SM at 36-40 GB/s (measured).  kind::mxf4 reads the codes as they are stored: a 32 KiB
 // stage IS 32 KiB of HBM bytes, four stages keep 128 KiB in flight, and an MMA covers K = 64 instead of 32 (half the
 // instructions per byte).  The price: both operands are 4-bit.  Every bf16 activation therefore enters as the sum of
-// FIVE E2M1 terms under power-of-two scales,  x = sum_i 2^(e - s_i) c_i,  s = {0, 2, 5, 8, 11},  e per (token, 32-block)
-// the smallest exponent with max / 2^e <= 6,  c_i = rn_e2m1(residual_i / 2^(e - s_i)).  The residual after the first term
-// is at most 2^e, after the second 2^(e-3), then it shrinks by 8 per term: after five terms it is below 2^(e-12) <=
-// 2^-12 max / 3, i.e. under 1e-4 of the block maximum (bf16 itself carries 2^-9 of each value).  The five terms are five
-// rows of the M = 128 operand with their own scale bytes; the epilogue adds the five accumulator rows of a token.
-// Row of token t, term i: (t / 6) * 32 + i * 6 + t % 6 (one TMEM lane quarter holds six tokens).
+// SEVEN E2M1 terms under power-of-two scales,  x = sum_i 2^(e - s_i) c_i,  s = {0, 2, 5, 8, 11, 14, 17},  e per (token,
+// 32-block) the smallest exponent with max / 2^e <= 6,  c_i = rn_e2m1(residual_i / 2^(e - s_i)).  The residual after the
+// first term is at most 2^e, after the second 2^(e-3), then it shrinks by 8 per term: after seven terms it is below
+// 2^(e-18), i.e. under 2^-19 of the block maximum, and zero for every value of at least 2^-11 of the block maximum (a
+// bf16 value has eight significant bits) -- the accuracy of the two-E4M3-term split of the other tensor-core kernel.
+// The seven terms are seven rows of the M = 128 operand with their own scale bytes; the epilogue adds the seven
+// accumulator rows of a token.  Row of token t, term i: (t / 4) * 32 + i * 4 + t % 4 (a TMEM lane quarter holds four tokens).
 //
 // Structure: one persistent CTA per SM, 4 stages of 256 weight rows x 256 K (32 KiB).  Warp 0 issues the weight copies,
 // warps 6..9 own one ring slot each (weight scale atoms; for up to 4 tokens also the activation terms of the stage, so
-// no pre-pass), warp 10 copies pre-quantized activations (5 to 24 tokens), warp 11 moves the scale atoms into TMEM one
+// no pre-pass), warp 10 copies pre-quantized activations (5 to 16 tokens), warp 11 moves the scale atoms into TMEM one
 // stage ahead of warp 1's MMAs, warps 2..5 are the epilogue.  (256-row tile, K stage) units are split evenly over the
 // SMs; partial sums meet in a workspace, the last CTA to arrive at a tile adds them in CTA order.  Programmatic
 // dependent launch; every mbarrier wait is bounded.
@@ -27,7 +28,7 @@ namespace mxf4 {
 
 using namespace tcx;
 
-constexpr int TILE_N = 256, BK = 256, kStages = 4, kTerms = 5, kTokPerQuarter = 6, kMaxTokens = 24;
+constexpr int TILE_N = 256, BK = 256, kStages = 4, kTerms = 7, kTokPerQuarter = 4, kMaxTokens = 16;
 constexpr int kBytesW = TILE_N * 128;            // 256 rows x 256 codes, dense: 32 KiB of HBM bytes
 constexpr int kBytesA = 128 * 128;               // activation operand: 128 rows x 256 codes
 constexpr int kBytesSf = 3072;                   // weight scale atoms (cell 0/1 x rows 0..127/128..255), activation scale atoms (cell 0/1)
@@ -60,14 +61,14 @@ __device__ __forceinline__ float2 e2m1x2_decode(uint32_t byte) {
   return __half22float2(*reinterpret_cast<const __half2*>(&h));
 }
 __device__ __forceinline__ int term_row(int t, int term) { return (t / kTokPerQuarter) * 32 + term * kTokPerQuarter + t % kTokPerQuarter; }
-__device__ __forceinline__ int term_shift(int i) { return i == 0 ? 0 : 3 * i - 1; }   // 0, 2, 5, 8, 11
+__device__ __forceinline__ int term_shift(int i) { return i == 0 ? 0 : 3 * i - 1; }   // 0, 2, 5, 8, 11, 14, 17
 
 // Block exponent: the smallest e with amax / 2^e <= 6 (= 1.5 * 2^2); 0 for an empty or non-finite block.
 __device__ __forceinline__ int block_exponent(float amax) {
   const uint32_t ab = __float_as_uint(amax);
   int e = (int)((ab >> 23) & 0xFF) - 127 - 2 + ((ab & 0x007FFFFFu) > 0x00400000u ? 1 : 0);
   if (amax == 0.0f || !(amax <= 3.0e38f)) e = 0;
-  return max(e, -110);                                           // keeps every term's exponent e - 11 inside E8M0
+  return max(e, -104);                                           // keeps every term's exponent e - 17 inside E8M0
 }
 // Eight consecutive activations (f[0..7], block exponent e) -> the eight codes of term `i` as one 32-bit word
 // (element j in nibble j), residuals updated in place.
@@ -95,7 +96,7 @@ struct Params {
   void* out;
   int out_type;
   int tokens;
-  int rows;                   // operand rows that hold token terms: 32 per six tokens
+  int rows;                   // operand rows that hold token terms: 32 per four tokens
   int64_t N, K;
   int stages_per_tile, units, per, max_slots;
   uint32_t idesc;
@@ -104,7 +105,7 @@ struct Params {
 };
 
 // ---------------------------------------------------------------------------
-// Activation pre-pass (5 to 24 tokens): one CTA per K stage; thread (token, 32-block) quantizes 32 values into the five
+// Activation pre-pass (5 to 16 tokens): one CTA per K stage; thread (token, 32-block) quantizes 32 values into the five
 // term rows of the stage block (16-byte units XOR-swizzled by row & 7) and writes the block's scale byte of each term row
 // into the stage's two scale atoms (row r, block b: atom b / 4, byte (r % 32) * 16 + (r / 32) * 4 + b % 4).
 // ---------------------------------------------------------------------------
@@ -380,9 +381,9 @@ __global__ void __launch_bounds__(kThreads, 1) gemv_fp4_mxf4_kernel(const __grid
       }
     }
   } else if (warp >= 2 && warp < 6) {
-    // ---------------- epilogue: lane quarter q holds the terms of tokens 6 q .. 6 q + 5 ----------------
+    // ---------------- epilogue: lane quarter q holds the terms of tokens 4 q .. 4 q + 3 ----------------
     const int q = warp & 3;
-    const int t = q * kTokPerQuarter + lane;                     // valid for lane < 6
+    const int t = q * kTokPerQuarter + lane;                     // valid for lane < 4
     const bool has_rows = q * 32 < p.rows;
     uint32_t seg_it = 0;
     bool ok = true;
@@ -590,7 +591,7 @@ int32_t launch(b2q_handle h, const uint8_t* codes, const uint8_t* scales, const 
 }  // namespace mxf4
 
 // Dense-format (kind::mxf4) FP4 decode GEMV; B2Q_ERR_UNSUPPORTED (nothing launched) when the shape or the alignment does
-// not fit: up to 24 tokens, K % 256 == 0, codes 32-byte aligned, scales 8-byte aligned, activations 16-byte aligned.
+// not fit: up to 16 tokens, K % 256 == 0, codes 32-byte aligned, scales 8-byte aligned, activations 16-byte aligned.
 int32_t b2q_gemv_fp4_mxf4_dispatch(b2q_handle h, const uint8_t* codes, const void* scales, const void* x, int tokens, int64_t N, int64_t K,
                                    void* out, int out_type) {
   if (tokens < 1 || tokens > mxf4::kMaxTokens || K % 256 != 0 || N < 1) return B2Q_ERR_UNSUPPORTED;
