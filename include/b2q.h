@@ -326,13 +326,18 @@ int32_t b2q_tp_destroy(b2q_tp t);
  * are attached every row-parallel boundary goes through NCCL. */
 int32_t b2q_tp_exchange_buffer(b2q_tp t, void** ptr, uint8_t* ipc_handle64);
 int32_t b2q_tp_attach_peers(b2q_tp t, const uint8_t* ipc_handles, void* const* direct_ptrs);
-/* Token chunks of the many-token path (0 = automatic, see b2q_tp_plan). */
+/* Chunks of the many-token paths (0 = automatic, see b2q_tp_plan). */
 int32_t b2q_tp_set_chunks(b2q_tp t, int chunks);
 /* The boundary a row-parallel result of tokens x out_features takes: mode 0 none (tp = 1); 1 one-shot and 2 two-shot
  * peer-memory kernel (fp32 partials up to 256 KiB / 4 MiB: every rank pushes its partial into its peers' inboxes over
  * NVLink, waits on per-CTA flags with a one-second limit (B2Q_ERR_TIMEOUT in the status word) and adds the partials in
- * rank order in fp32, the reference's order, row_parallel.rs:202-223); 3 NCCL all-reduce of bf16 partials in `chunks`
- * token chunks, chunk i on the second stream while the GEMMs of chunk i + 1 run.  Pure host function. */
+ * rank order in fp32, the reference's order, row_parallel.rs:202-223); 4 (bf16 results up to 64 MiB, tokens a multiple
+ * of 32 * tp) the reduce-scatter is part of the GEMM: its epilogue stores every row block as bf16 into the inbox of the
+ * rank that owns those rows, then one kernel waits for the peers (same limit), adds the tp partials of its own rows in
+ * rank order in fp32 and pushes the bf16 sums to every rank; `chunks` > 1 cuts the GEMM into column chunks (chosen so
+ * that its tile waves stay the same) and that kernel runs on a second stream under the GEMM of the next chunk;
+ * 3 NCCL all-reduce of bf16 partials (anything else, or no peers attached), `chunks` token chunks.
+ * Every rank gets the same bits in modes 1, 2 and 4.  Pure host function. */
 int32_t b2q_tp_plan(int tp, int peers_attached, int64_t tokens, int64_t out_features, int* mode, int* chunks);
 /* Sum over ranks of fp32 partials [n] -> bf16 on every rank through the peer kernel (n % (4 * tp) == 0, n * 4 <= 4 MiB,
  * peers attached); and the in-place NCCL sum of a bf16 buffer on the handle's stream. */

@@ -59,8 +59,14 @@ struct Params {
   // [group_offsets[g], group_offsets[g] + group_counts[g]) of A (offsets are multiples of 256, so a tile never spans
   // two problems) with rows [g * N, (g + 1) * N) of W and scale_w, and stores into the same rows of out
   const int32_t* group_offsets; const int32_t* group_counts; int groups;
+  // scatter mode of the pair kernel (rs_tp > 0, the row-parallel boundary of a tensor-parallel linear): the tile rows
+  // [o * rs_rows, (o + 1) * rs_rows) belong to rank o; they are stored, as bf16, through that rank's tensor map (its
+  // inbox in peer-mapped memory) at rows rs_rank * rs_rows + (row - o * rs_rows), i.e. into the slot of THIS rank
+  int rs_tp, rs_rank, rs_rows;
 };
 constexpr int kMaxGroups = 64;
+constexpr int kMaxScatterRanks = 8;
+struct ScatterMaps { CUtensorMap m[kMaxScatterRanks]; };
 
 using namespace tcx;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
@@ -185,7 +191,7 @@ struct EpiWarp { uint32_t smem_u; uint8_t* smem_p; uint32_t it; };
 
 template <int KIND>
 __device__ __forceinline__ void epilogue_rows(const Params& pp, const CUtensorMap* map_out, EpiWarp& ew, uint32_t tmem_acc, int width,
-                                              int64_t m_warp0, int lane, int64_t n0, const float* scale_w) {
+                                              int64_t m_warp0, int lane, int64_t n0, const float* scale_w, int64_t m_store) {
   Params p = pp;
   p.scale_w = scale_w;                       // this tile's weight scales (grouped mode: the problem's slice)
   const int64_t m = m_warp0 + lane;
@@ -253,7 +259,7 @@ __device__ __forceinline__ void epilogue_rows(const Params& pp, const CUtensorMa
         fence_async_smem();                                      // the TMA unit reads what the warp just wrote
         __syncwarp();
         if (lane == 0) {
-          tma_store_2d(map_out, ew.smem_u + buf, (int)n, (int)m_warp0);
+          tma_store_2d(map_out, ew.smem_u + buf, (int)n, (int)m_store);     // m_store = m_warp0 except in scatter mode
           tma_store_commit();
         }
         ++ew.it;
@@ -389,7 +395,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       if (!mbar_wait(tfull_bar(buf), aph, abort_flag)) { ok = false; break; }
       tc_fence_after();
       epilogue_rows<KIND>(p, &map_out, ew, tmem_base + buf * BN + ((uint32_t)(q * 32) << 16), BN, (int64_t)mb * BM + q * 32, lane,
-                          (int64_t)nb * BN, p.scale_w);
+                          (int64_t)nb * BN, p.scale_w, (int64_t)mb * BM + q * 32);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(buf));
@@ -482,9 +488,8 @@ __device__ __forceinline__ void umma2(uint32_t tmem_d, uint64_t adesc, uint64_t 
 }
 
 template <int KIND>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                const __grid_constant__ CUtensorMap map_w_half, const __grid_constant__ CUtensorMap map_out, const Params p) {
+__device__ __forceinline__ void gemm_tc2_body(const CUtensorMap& map_a, const CUtensorMap& map_w, const CUtensorMap& map_w_half,
+                                              const CUtensorMap& map_out, const CUtensorMap* scatter_maps, const Params& p) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t epi_base = base + kStages * kStageBytes;
@@ -503,7 +508,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   // Work units: whole 256 x 256 tiles first; when the last wave would leave more than half of the CTA pairs idle, its
   // tiles are cut into two 256 x 128 halves (MMA N = 128, 64 rows of W per CTA) so that the tail takes half a wave.
   // Grouped mode: the units are the 256 x 256 tiles of every problem in turn; the table is read once per CTA.
-  __shared__ int s_gstart[kMaxGroups + 1], s_goff[kMaxGroups], s_gtm[kMaxGroups];
+  // (16-bit entries: with its 225 KiB of stages this CTA leaves just over 1 KiB of the SM's shared memory, which is
+  // what lets a small exchange kernel of another stream become resident beside it)
+  __shared__ int s_gstart[kMaxGroups + 1];
+  __shared__ uint16_t s_goff256[kMaxGroups], s_gtm[kMaxGroups];   // row offset / 256, row tiles
   struct Unit { int a_row, w_row, width, half; int64_t n0; int64_t sw_off; };
   auto unit_coords = [&](int u) {
     Unit c;
@@ -512,7 +520,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       while (g + 1 < p.groups && u >= s_gstart[g + 1]) ++g;
       int mb, nb;
       tile_coords(u - s_gstart[g], s_gtm[g], p.tiles_n, mb, nb);
-      c.a_row = s_goff[g] + mb * 256; c.w_row = g * (int)p.N + nb * BN2; c.width = BN2; c.half = 0;
+      c.a_row = (int)s_goff256[g] * 256 + mb * 256; c.w_row = g * (int)p.N + nb * BN2; c.width = BN2; c.half = 0;
       c.n0 = (int64_t)nb * BN2; c.sw_off = (int64_t)g * p.N;
       return c;
     }
@@ -539,8 +547,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     s_gstart[0] = 0;
     for (int g = 0; g < p.groups; ++g) {
       const int cnt = p.group_counts[g];
-      s_goff[g] = p.group_offsets[g];
-      s_gtm[g] = (cnt + 255) / 256;
+      s_goff256[g] = (uint16_t)(p.group_offsets[g] >> 8);
+      s_gtm[g] = (uint16_t)((cnt + 255) / 256);
       s_gstart[g + 1] = s_gstart[g] + s_gtm[g] * p.tiles_n;
     }
   }
@@ -623,8 +631,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const uint32_t buf = tile_it & 1, aph = (tile_it >> 1) & 1;
       if (!mbar_wait(tfull_bar(buf), aph, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      epilogue_rows<KIND>(p, &map_out, ew, tmem_base + buf * BN2 + ((uint32_t)(q * 32) << 16), c.width,
-                          (int64_t)c.a_row + rank * BM + q * 32, lane, c.n0, p.scale_w ? p.scale_w + c.sw_off : nullptr);
+      const int64_t m_warp0 = (int64_t)c.a_row + rank * BM + q * 32;
+      const CUtensorMap* mo = &map_out;
+      int64_t m_store = m_warp0;
+      if (scatter_maps) {                               // this warp's 32 rows belong to one rank (rs_rows is a multiple of 32)
+        const int owner = min((int)(m_warp0 / p.rs_rows), p.rs_tp - 1);
+        mo = scatter_maps + owner;
+        m_store = (int64_t)p.rs_rank * p.rs_rows + (m_warp0 - (int64_t)owner * p.rs_rows);
+      }
+      epilogue_rows<KIND>(p, mo, ew, tmem_base + buf * BN2 + ((uint32_t)(q * 32) << 16), c.width, m_warp0, lane, c.n0,
+                          p.scale_w ? p.scale_w + c.sw_off : nullptr, m_store);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(tempty_bar(buf), 0));   // the leader's MMA thread waits for both CTAs
@@ -641,6 +657,21 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     tmem_dealloc2(tmem_base, kTmemCols);
   }
   if (threadIdx.x == 0 && s_abort) atomicCAS(p.status, 0, (int)B2Q_ERR_TIMEOUT);
+}
+
+template <int KIND>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                const __grid_constant__ CUtensorMap map_w_half, const __grid_constant__ CUtensorMap map_out, const Params p) {
+  gemm_tc2_body<KIND>(map_a, map_w, map_w_half, map_out, nullptr, p);
+}
+// The same kernel with one output map per rank: each accumulator row block goes to the rank that owns it (its inbox in
+// peer-mapped memory), so the partial sums of a row-parallel linear cross NVLink tile by tile while the MMAs run.
+template <int KIND>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc2_scatter_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                        const __grid_constant__ CUtensorMap map_w_half, const __grid_constant__ ScatterMaps maps, const Params p) {
+  gemm_tc2_body<KIND>(map_a, map_w, map_w_half, maps.m[0], maps.m, p);
 }
 
 }  // namespace two
@@ -691,7 +722,7 @@ int32_t launch(b2q_handle h, const void* a, const void* w, Params p) {
 
 // 256 x 256 pair tiles on clusters of two CTAs.
 template <int KIND>
-int32_t launch2(b2q_handle h, const void* a, const void* w, Params p) {
+int32_t launch2(b2q_handle h, const void* a, const void* w, Params p, const ScatterMaps* scatter = nullptr) {
   CUtensorMap map_a, map_w;
   int32_t st = make_map(h, &map_a, a, p.M, p.K, BM);
   if (st != B2Q_OK) return st;
@@ -700,7 +731,8 @@ int32_t launch2(b2q_handle h, const void* a, const void* w, Params p) {
   CUtensorMap map_w_half, map_out;
   st = make_map(h, &map_w_half, w, p.N, p.K, two::BN2 / 4);
   if (st != B2Q_OK) return st;
-  st = make_out_map(h, &map_out, p);
+  if (scatter) { memset(&map_out, 0, sizeof(map_out)); p.tma_store = 1; }
+  else st = make_out_map(h, &map_out, p);
   if (st != B2Q_OK) return st;
   p.tiles_m = (int)ceil_div64(p.M, 256);
   p.tiles_n = (int)ceil_div64(p.N, two::BN2);
@@ -734,6 +766,14 @@ int32_t launch2(b2q_handle h, const void* a, const void* w, Params p) {
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+  if (scatter) {
+    if constexpr (KIND == kF8) {
+      B2Q_SMEM_ATTR(h, (two::gemm_tc2_scatter_kernel<kF8>), two::kSmem);
+      B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, two::gemm_tc2_scatter_kernel<kF8>, map_a, map_w, map_w_half, *scatter, p));
+      return B2Q_OK;
+    }
+    return B2Q_ERR_UNSUPPORTED;
+  }
   B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, two::gemm_tc2_kernel<KIND>, map_a, map_w, map_w_half, map_out, p));
   return B2Q_OK;
 }
@@ -862,6 +902,33 @@ int32_t gemm_fp8_impl(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t 
   return kid == 1 ? launch<256, kF8>(h, a, w, p) : launch<128, kF8>(h, a, w, p);
 }
 
+// Row-parallel partial product with the reduce-scatter folded into the epilogue: rows [o * M / tp, (o + 1) * M / tp) of
+// a * w^T (bf16) are stored into rank o's inbox (inbox[o], mapped into this process; rank `rank`'s own inbox is local
+// memory) at slot `rank`; an inbox is [tp slots][M / tp rows][N] bf16.  `bias` ([N] or null) is added to this rank's
+// partial.  The caller sums the slots once every rank's kernel has completed.  B2Q_ERR_UNSUPPORTED when the shape does not take the pair kernel.
+int32_t gemm_fp8_scatter(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt, const float* scale_a,
+                         const float* scale_w, const float* bias, void* const* inbox, int tp, int rank) {
+  if (tp < 1 || tp > kMaxScatterRanks || M <= 128 || N <= 128 || M % (32 * tp) != 0 || N % 8 != 0 || K % 16 != 0 ||
+      ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) != 0 || M > 0x7FFFFFFF)
+    return B2Q_ERR_UNSUPPORTED;
+  ScatterMaps maps;
+  memset(&maps, 0, sizeof(maps));
+  for (int r = 0; r < tp; ++r) {
+    if (!inbox[r] || (reinterpret_cast<uintptr_t>(inbox[r]) & 15) != 0) return B2Q_ERR_UNSUPPORTED;
+    int32_t st = b2q_tensor_map_2d(h, &maps.m[r], inbox[r], 2, (uint64_t)N, (uint64_t)M, 64u, 32u);
+    if (st != B2Q_OK) return st;
+  }
+  Params p{};
+  p.M = M; p.N = N; p.K = K;
+  p.scale_a = scale_a; p.scale_a_rows = 1; p.scale_w = scale_w; p.scale_w_rows = 1;
+  p.out = inbox[rank]; p.out_type = B2Q_OUT_BF16; p.status = h->d_status;
+  p.idesc = ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10);
+  p.alpha = 1.0f;
+  if (bias) { p.epi = 1; p.bias = bias; }
+  p.rs_tp = tp; p.rs_rank = rank; p.rs_rows = (int)(M / tp);
+  return launch2<kF8>(h, a, w, p, &maps);
+}
+
 // Grouped launch of the pair kernel: every CTA pair walks the tiles of all problems (table on the device).
 int32_t launch2_grouped(b2q_handle h, const void* a, const void* w, Params p, int64_t capacity_rows) {
   CUtensorMap map_a, map_w, map_w_half, map_out;
@@ -910,7 +977,7 @@ extern "C" int32_t b2q_grouped_gemm_fp8_rows(b2q_handle h, const uint8_t* a, con
     B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "grouped_gemm_fp8_rows: bad argument");
   if (K % 16 != 0 || ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) != 0)
     B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "grouped_gemm_fp8_rows: K must be a multiple of 16 and the operands 16-byte aligned (TMA row pitch)");
-  if ((int64_t)groups * N > 0x7FFFFFFF || capacity_rows > 0x7FFFFFFF) B2Q_FAIL(h, B2Q_ERR_UNSUPPORTED, "grouped_gemm_fp8_rows: too many rows");
+  if ((int64_t)groups * N > 0x7FFFFFFF || capacity_rows > (65535ll << 8)) B2Q_FAIL(h, B2Q_ERR_UNSUPPORTED, "grouped_gemm_fp8_rows: too many rows");
   tc::Params p{};
   p.N = N; p.K = K;
   p.scale_a = scale_a; p.scale_a_rows = 1; p.scale_w = scale_w; p.scale_w_rows = 1;

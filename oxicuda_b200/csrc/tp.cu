@@ -7,12 +7,21 @@
 //     for its peers and adds the inboxes IN RANK ORDER in fp32 (the reference's order, the same bits on every rank).
 //     Above 256 KiB the exchange is two-shot: each rank reduces one slice and pushes the bf16 result to all.
 //     The buffer parity and the flag epoch live in device memory, so the launch can be captured in a CUDA graph;
-//   * for many tokens: the tokens are cut into chunks, and the NCCL all-reduce of chunk i runs on a second stream
-//     while the GEMMs of chunk i + 1 run on the handle's stream.
+//   * for many tokens (bf16 results up to 64 MiB): the reduce-scatter is folded into the GEMM.  The epilogue of the
+//     tcgen05 kernel stores every accumulator row block straight into the inbox of the rank that owns those rows (TMA
+//     stores into peer-mapped memory), so the partial sums cross NVLink tile by tile while the MMAs run; one kernel
+//     then waits for the peers, adds the tp slots of its own rows in rank order in fp32 and pushes the bf16 sums to
+//     every rank.  With several token chunks that kernel runs on a second stream under the GEMMs of the next chunk;
+//   * beyond that, or without peer mappings: NCCL all-reduce per token chunk on the second stream.
 // NCCL is resolved at run time from the library already loaded in the process (no link-time dependency).
 #include "common.cuh"
 #include <dlfcn.h>
 #include <stdlib.h>
+
+namespace tc {
+int32_t gemm_fp8_scatter(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt, const float* scale_a,
+                         const float* scale_w, const float* bias, void* const* inbox, int tp, int rank);
+}
 
 namespace tpx {
 
@@ -52,14 +61,17 @@ static NcclApi* nccl() {
 
 // ---- exchange buffer layout (one per rank, cudaMalloc'ed, mapped into every peer) ---------------------------
 constexpr int kMaxRanks = 8;
-constexpr int kMaxCtas = 64;                                  // CTAs of the exchange kernel (same on every rank)
-constexpr size_t kFlagBytes = 8192;                           // flags[2 barriers][kMaxCtas][kMaxRanks] u32 = 4 KiB, epoch[kMaxCtas] u32
+constexpr int kMaxCtas = 128;                                 // CTAs of an exchange kernel (same on every rank)
+constexpr size_t kFlagBytes = 16384;                          // flags[2 barriers][kMaxCtas][kMaxRanks] u32 = 8 KiB, then epoch[kMaxCtas] u32
 constexpr size_t kOneShotMax = 256 << 10;                     // fp32 partial bytes up to which every rank receives every partial
 constexpr size_t kTwoShotMax = 4 << 20;                       // fp32 partial bytes up to which the peer kernel is used at all
 constexpr size_t kSlotBytes = kTwoShotMax / 2;                // inbox slot per (parity, source rank): a two-shot slice (<= 4 MiB / 2 ranks)
 constexpr size_t kInboxBytes = 2 * kMaxRanks * kSlotBytes;    // 32 MiB
 constexpr size_t kResultBytes = 2 * (kTwoShotMax / 2);        // bf16 result per parity
-constexpr size_t kXbufBytes = kFlagBytes + kInboxBytes + kResultBytes;
+constexpr size_t kBigMax = 64ull << 20;                       // bf16 result bytes up to which the GEMM scatters its partials itself
+constexpr size_t kBigInboxOff = kFlagBytes + kInboxBytes + kResultBytes;   // [chunk][tp slots][rows / tp][N] bf16
+constexpr size_t kBigResultOff = kBigInboxOff + kBigMax;                   // [chunk][rows][N] bf16
+constexpr size_t kXbufBytes = kBigResultOff + kBigMax;
 constexpr uint64_t kWaitLimitNs = 1000000000ull;
 
 struct Peers { uint8_t* base[kMaxRanks]; };
@@ -71,7 +83,7 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) { uint32_t
 __device__ __forceinline__ uint32_t* flag_ptr(uint8_t* base, int which, int cta, int src) {
   return reinterpret_cast<uint32_t*>(base) + (which * kMaxCtas + cta) * kMaxRanks + src;
 }
-__device__ __forceinline__ uint32_t* epoch_ptr(uint8_t* base, int cta) { return reinterpret_cast<uint32_t*>(base + 4096) + cta; }
+__device__ __forceinline__ uint32_t* epoch_ptr(uint8_t* base, int cta) { return reinterpret_cast<uint32_t*>(base + 8192) + cta; }
 __device__ __forceinline__ float4* inbox_ptr(uint8_t* base, int parity, int src) {
   return reinterpret_cast<float4*>(base + kFlagBytes + ((size_t)parity * kMaxRanks + src) * kSlotBytes);
 }
@@ -166,6 +178,71 @@ __global__ void __launch_bounds__(512, 1) tp_allreduce_push_kernel(const Peers p
   }
 }
 
+__device__ __forceinline__ void add8_bf16(float (&acc)[8], const uint4 v, bool first) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float lo = __uint_as_float(w[j] << 16), hi = __uint_as_float(w[j] & 0xFFFF0000u);
+    acc[2 * j] = first ? lo : acc[2 * j] + lo;
+    acc[2 * j + 1] = first ? hi : acc[2 * j + 1] + hi;
+  }
+}
+
+// Second half of the many-token boundary.  Every rank's GEMM has stored its bf16 partial of MY rows into slot `src` of
+// my inbox (kernels that completed before this one was launched, on every rank: the first barrier orders them).  Sum the
+// tp slots in rank order in fp32, write the bf16 sums into y and into every peer's result area, wait again, copy the
+// peers' rows out of my result area.  inbox: [tp][slice16] 16-byte units, result: [tp * slice16], both rows of n16 units;
+// y: the same rows at a pitch of y_pitch16 units (a column range of the full result).
+__global__ void __launch_bounds__(256, 1) tp_reduce_gather_kernel(const Peers peers, int tp, int rank, size_t off_inbox, size_t off_result,
+                                                                   int64_t slice16, int64_t n16, int64_t y_pitch16, uint4* __restrict__ y,
+                                                                   int32_t* status) {
+  __shared__ int s_abort;
+  if (threadIdx.x == 0) s_abort = 0;
+  const int cta = blockIdx.x, G = gridDim.x;
+  uint8_t* my = peers.base[rank];
+  const uint32_t e = *epoch_ptr(my, cta) + 1;
+  __syncthreads();
+  const int64_t per = (slice16 + G - 1) / G, i0 = cta * per, i1 = min(slice16, i0 + per);
+  const int64_t rows_per = slice16 / n16;                                          // rows each rank owns
+  auto y_at = [&](int r, int64_t i) { const int64_t row = i / n16; return y + (r * rows_per + row) * y_pitch16 + (i - row * n16); };
+  bool ok = peer_barrier(peers, tp, rank, 0, e, &s_abort);
+  if (ok) {
+    const uint4* in = reinterpret_cast<const uint4*>(my + off_inbox);
+    for (int64_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
+      uint4 v[kMaxRanks];
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r)
+        if (r < tp) v[r] = __ldcg(in + r * slice16 + i);
+      float acc[8];
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r)
+        if (r < tp) add8_bf16(acc, v[r], r == 0);                // rank order: the reference's summation order
+      uint4 pk;
+      __nv_bfloat162 h0 = __floats2bfloat162_rn(acc[0], acc[1]), h1 = __floats2bfloat162_rn(acc[2], acc[3]);
+      __nv_bfloat162 h2 = __floats2bfloat162_rn(acc[4], acc[5]), h3 = __floats2bfloat162_rn(acc[6], acc[7]);
+      pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+      pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+      *y_at(rank, i) = pk;
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r)
+        if (r < tp && r != rank) reinterpret_cast<uint4*>(peers.base[r] + off_result)[rank * slice16 + i] = pk;
+    }
+    ok = peer_barrier(peers, tp, rank, 1, e, &s_abort);
+  }
+  if (ok) {
+    const uint4* res = reinterpret_cast<const uint4*>(my + off_result);
+    for (int r = 0; r < tp; ++r) {
+      if (r == rank) continue;
+      for (int64_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) *y_at(r, i) = __ldcg(res + r * slice16 + i);
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    *epoch_ptr(my, cta) = e;
+    if (!ok) atomicCAS(status, 0, (int)B2Q_ERR_TIMEOUT);
+  }
+}
+
 // y[t, c] += bias[c]  (bf16 rows, f32 bias)
 __global__ void __launch_bounds__(256) bias_add_bf16_kernel(__nv_bfloat16* __restrict__ y, const float* __restrict__ bias, int64_t rows, int64_t cols) {
   const int64_t total = rows * cols;
@@ -193,6 +270,7 @@ struct b2q_tp_s {
   tpx::nccl_comm_t comm;
   int tp, rank;
   int chunks;                      // token chunks of the many-token path (0 = choose by size)
+  int no_scatter;                  // B2Q_TP_SCATTER=0: many-token boundaries take NCCL (experiments, comparison runs)
   cudaStream_t comm_stream;
   cudaEvent_t ev_ready[16], ev_done;
   uint8_t* xbuf;                   // this rank's exchange buffer
@@ -239,6 +317,52 @@ static int32_t peer_allreduce(b2q_tp t, const float* partial, int64_t n, void* y
   B2Q_LAUNCH_CHECK(h, "tp_allreduce_push_kernel");
   return B2Q_OK;
 }
+// Column chunk `chunk` of `chunks` of a row-parallel linear over all `tokens`: the scatter GEMM over rows
+// [chunk * nc, (chunk + 1) * nc) of W (nc = N / chunks) and the kernel that sums and gathers those columns into y.
+// With several chunks the second kernel runs on the exchange stream, under the GEMM of the next chunk.
+static int32_t scatter_reduce_cols(b2q_tp t, const uint8_t* x_codes, const float* x_scales, const uint8_t* w_codes, const float* w_scales,
+                                   const float* bias, int64_t tokens, int64_t in_local, int64_t N, void* y, int chunk, int chunks) {
+  b2q_handle h = t->h;
+  const int64_t nc = N / chunks;
+  const size_t off = (size_t)chunk * tokens * nc * 2;
+  void* inbox[kMaxRanks] = {};
+  for (int r = 0; r < t->tp; ++r) inbox[r] = t->peers.base[r] + kBigInboxOff + off;
+  int32_t st = tc::gemm_fp8_scatter(h, x_codes, w_codes + (size_t)chunk * nc * in_local, tokens, nc, in_local, B2Q_FP8_E4M3, x_scales,
+                                    w_scales + chunk * nc, bias ? bias + chunk * nc : nullptr, inbox, t->tp, t->rank);
+  if (st == B2Q_ERR_UNSUPPORTED)
+    B2Q_FAIL(h, B2Q_ERR_UNSUPPORTED, "row-parallel scatter GEMM: shape %lld x %lld x %lld not covered", (long long)tokens, (long long)nc, (long long)in_local);
+  if (st != B2Q_OK) return st;
+  cudaStream_t rs = chunks > 1 ? t->comm_stream : h->stream;
+  if (chunks > 1) {
+    B2Q_CUDA(h, cudaEventRecord(t->ev_ready[chunk], h->stream));
+    B2Q_CUDA(h, cudaStreamWaitEvent(rs, t->ev_ready[chunk], 0));
+  }
+  const int64_t n16 = nc * 2 / 16, slice16 = (tokens / t->tp) * n16;
+  int grid = (int)((slice16 + 255) / 256);
+  grid = grid < 1 ? 1 : (grid > kMaxCtas ? kMaxCtas : grid);
+  // 256 threads and no shared memory beyond one word: such a CTA fits beside a resident GEMM CTA
+  tp_reduce_gather_kernel<<<grid, 256, 0, rs>>>(t->peers, t->tp, t->rank, kBigInboxOff + off, kBigResultOff + off, slice16, n16, N * 2 / 16,
+                                                reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(y) + (size_t)chunk * nc * 2), h->d_status);
+  B2Q_LAUNCH_CHECK(h, "tp_reduce_gather_kernel");
+  if (chunks > 1 && chunk == chunks - 1) {
+    B2Q_CUDA(h, cudaEventRecord(t->ev_done, rs));
+    B2Q_CUDA(h, cudaStreamWaitEvent(h->stream, t->ev_done, 0));
+  }
+  return B2Q_OK;
+}
+// Waves of 256 x 256 tiles on the 74 CTA pairs of a B200, as the pair kernel schedules them (a last wave that fills at
+// most half of the pairs runs as half-width tiles and takes half a wave).
+static double gemm_waves(int64_t M, int64_t N) {
+  const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256), pairs = 74;
+  if (tiles <= pairs) return 1.0;
+  const int64_t rem = tiles % pairs;
+  return (double)(tiles / pairs) + (rem == 0 ? 0.0 : (2 * rem <= pairs ? 0.5 : 1.0));
+}
+// Shapes the scatter GEMM and the 16-byte units of the reduce kernel cover (nc: the columns of one chunk).
+static bool scatter_fits(int tp, int64_t tokens, int64_t nc, int64_t in_local) {
+  return tokens > 128 && nc > 128 && tokens % (32 * tp) == 0 && nc % 8 == 0 && in_local % 16 == 0;
+}
+
 static bool peer_path_fits(b2q_tp t, int64_t n) {
   return t->attached && n % (4 * t->tp) == 0 && (size_t)n * 4 <= kTwoShotMax && ((size_t)n * 4 / t->tp) <= kSlotBytes;
 }
@@ -252,6 +376,21 @@ static int32_t add_bias(b2q_handle h, void* y, int out_type, const float* bias, 
   else bias_add_f32_kernel<<<grid, 256, 0, h->stream>>>((float*)y, bias, rows, cols);
   B2Q_LAUNCH_CHECK(h, "bias_add_kernel");
   return B2Q_OK;
+}
+
+// The boundary of one call: the plan for the shape, the caller's chunk override, and the fall-back to NCCL when the
+// operands do not suit the scatter GEMM (K pitch, alignment).
+static void choose_boundary(b2q_tp t, int64_t tokens, int64_t out_features, int64_t in_local, const void* a, const void* w, int* mode,
+                            int* chunks) {
+  b2q_tp_plan(t->tp, t->attached, tokens, out_features, mode, chunks);
+  if (*mode == 4 && (t->no_scatter || in_local % 16 != 0 || ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) != 0)) {
+    *mode = 3;
+    *chunks = 1;
+  }
+  if (t->chunks > 0) {                                       // mode 3: token chunks; mode 4: column chunks
+    if (*mode == 3 && tokens % t->chunks == 0 && (t->chunks == 1 || (tokens / t->chunks) % 256 == 0)) *chunks = t->chunks;
+    if (*mode == 4 && out_features % (8 * t->chunks) == 0 && scatter_fits(t->tp, tokens, out_features / t->chunks, in_local)) *chunks = t->chunks;
+  }
 }
 
 }  // namespace tpx
@@ -305,7 +444,12 @@ int32_t b2q_tp_create(b2q_handle h, void* nccl_comm, int tp, int rank, b2q_tp* o
   t->h = h; t->comm = nccl_comm; t->tp = tp; t->rank = rank;
   const char* ce = getenv("B2Q_TP_CHUNKS");
   t->chunks = ce ? atoi(ce) : 0;
-  bool ok = cudaStreamCreateWithFlags(&t->comm_stream, cudaStreamNonBlocking) == cudaSuccess;
+  const char* se = getenv("B2Q_TP_SCATTER");
+  t->no_scatter = se && atoi(se) == 0;
+  // the exchange stream outranks the GEMM stream: its few CTAs are placed as soon as an SM has room for them
+  int prio_lo = 0, prio_hi = 0;
+  cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi);
+  bool ok = cudaStreamCreateWithPriority(&t->comm_stream, cudaStreamNonBlocking, prio_hi) == cudaSuccess;
   for (int i = 0; i < 16 && ok; ++i) ok = cudaEventCreateWithFlags(&t->ev_ready[i], cudaEventDisableTiming) == cudaSuccess;
   ok = ok && cudaEventCreateWithFlags(&t->ev_done, cudaEventDisableTiming) == cudaSuccess;
   if (ok && tp > 1) {
@@ -377,7 +521,9 @@ int32_t b2q_tp_attach_peers(b2q_tp t, const uint8_t* ipc_handles, void* const* d
 }
 
 // Which boundary a row-parallel result of `tokens` x `out_features` takes: 0 none (tp = 1), 1 one-shot peer kernel,
-// 2 two-shot peer kernel, 3 NCCL in `chunks` token chunks overlapped with the GEMMs.
+// 2 two-shot peer kernel, 4 reduce-scatter stored by the GEMM epilogue into the owners' inboxes + one sum-and-gather
+// kernel per token chunk, 3 NCCL all-reduce per token chunk.  `chunks` is the automatic choice; b2q_tp_set_chunks
+// overrides it where the chunked shapes still fit.
 int32_t b2q_tp_plan(int tp, int peers_attached, int64_t tokens, int64_t out_features, int* mode, int* chunks) {
   if (!mode || !chunks || tp < 1 || tokens < 1 || out_features < 1) return B2Q_ERR_INVALID_ARGUMENT;
   *chunks = 1;
@@ -388,13 +534,18 @@ int32_t b2q_tp_plan(int tp, int peers_attached, int64_t tokens, int64_t out_feat
     *mode = bytes <= tpx::kOneShotMax ? 1 : 2;
     return B2Q_OK;
   }
-  *mode = 3;
-  // chunks of at least 512 tokens, a multiple of 256 tokens each so that GEMM tiles stay whole; at most 8
-  int c = (int)(tokens / 1024);
-  c = c < 1 ? 1 : (c > 8 ? 8 : c);
-  while (c > 1 && (tokens % c != 0 || (tokens / c) % 256 != 0)) --c;
-  *chunks = c;
-  return B2Q_OK;
+  if (peers_attached && (size_t)n * 2 <= tpx::kBigMax && tpx::scatter_fits(tp, tokens, out_features, 16)) {
+    *mode = 4;
+    // column chunks of the GEMM (the sum-and-gather of chunk j runs under the GEMM of chunk j + 1): as many, up to 4,
+    // as leave the GEMM's tile waves unchanged
+    for (int c = 4; c >= 2; c /= 2) {
+      if (out_features % (256 * c) != 0 || !tpx::scatter_fits(tp, tokens, out_features / c, 16)) continue;
+      if (c * tpx::gemm_waves(tokens, out_features / c) <= tpx::gemm_waves(tokens, out_features) + 1e-9) { *chunks = c; break; }
+    }
+    return B2Q_OK;
+  }
+  *mode = 3;                      // one all-reduce after the GEMM measured fastest at tp = 2 and 4 (NCCL's CTAs wait for the
+  return B2Q_OK;                  // persistent GEMM's SMs, so chunks do not overlap)
 }
 
 int32_t b2q_tp_all_reduce_f32_to_bf16(b2q_tp t, const float* partial, int64_t n, void* y_bf16) {
@@ -474,14 +625,21 @@ int32_t b2q_row_linear_forward_allreduce(b2q_tp t, const uint8_t* x_codes, const
     B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "row_linear_forward: dimensions must be non-zero: tokens=%lld, in=%lld, out=%lld", (long long)tokens,
              (long long)in_local, (long long)out_features);
   int mode = 0, chunks = 1;
-  b2q_tp_plan(t->tp, t->attached, tokens, out_features, &mode, &chunks);
-  if (t->chunks > 0 && mode == 3 && tokens % t->chunks == 0) chunks = t->chunks;
+  tpx::choose_boundary(t, tokens, out_features, in_local, x_codes, w_codes, &mode, &chunks);
   uint8_t* ws = nullptr;
   if (mode == 1 || mode == 2) {
     int32_t st = tpx::scratch(t, (size_t)tokens * out_features * 4, &ws);
     if (st != B2Q_OK) return st;
   }
-  if (mode != 3) return row_linear_range(t, x_codes, x_scales, w_codes, w_scales, bias, tokens, in_local, out_features, y, mode, (float*)ws);
+  if (mode < 3) return row_linear_range(t, x_codes, x_scales, w_codes, w_scales, bias, tokens, in_local, out_features, y, mode, (float*)ws);
+  if (mode == 4) {
+    const float* b = t->rank == 0 ? bias : nullptr;           // RowLinear adds the bias on rank 0 only (row_parallel.rs:183-190)
+    for (int c = 0; c < chunks; ++c) {
+      int32_t st = tpx::scatter_reduce_cols(t, x_codes, x_scales, w_codes, w_scales, b, tokens, in_local, out_features, y, c, chunks);
+      if (st != B2Q_OK) return st;
+    }
+    return B2Q_OK;
+  }
   const int64_t ct = tokens / chunks;
   for (int c = 0; c < chunks; ++c) {
     uint8_t* yc = reinterpret_cast<uint8_t*>(y) + (size_t)c * ct * out_features * 2;
@@ -509,8 +667,9 @@ int32_t b2q_mlp_swiglu_fp8_forward(b2q_tp t, const void* x_bf16, const uint8_t* 
              (long long)tokens, (long long)hidden, (long long)ffn_local);
   if (!x_bf16 || !w_gate_up || !s_gate_up || !w_down || !s_down || !y_bf16) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "mlp_swiglu_fp8_forward: null operand");
   int mode = 0, chunks = 1;
-  b2q_tp_plan(t->tp, t->attached, tokens, hidden, &mode, &chunks);
-  if (t->chunks > 0 && mode == 3 && tokens % t->chunks == 0) chunks = t->chunks;
+  tpx::choose_boundary(t, tokens, hidden, ffn_local, w_gate_up, w_down, &mode, &chunks);
+  const int col_chunks = mode == 4 ? chunks : 1;             // mode 4 cuts the down projection's columns, mode 3 the tokens
+  if (mode == 4) chunks = 1;
   const int64_t ct = tokens / chunks;
   const int64_t F = ffn_local;
   // scratch: x codes + scales (all tokens), then per chunk: gate|up bf16, h codes + scales, fp32 partial (peer modes)
@@ -533,6 +692,11 @@ int32_t b2q_mlp_swiglu_fp8_forward(b2q_tp t, const void* x_bf16, const uint8_t* 
     if (st != B2Q_OK) return st;
     st = b2q_swiglu_quantize_rows_bf16(h, gu, gu + (size_t)F * 2, ct, F, 2 * F, B2Q_FP8_E4M3, rounding, hs, hc);
     if (st != B2Q_OK) return st;
+    if (mode == 4) {
+      for (int j = 0; j < col_chunks; ++j)
+        if ((st = tpx::scatter_reduce_cols(t, hc, hs, w_down, s_down, nullptr, ct, F, hidden, yc, j, col_chunks)) != B2Q_OK) return st;
+      continue;
+    }
     st = row_linear_range(t, hc, hs, w_down, s_down, nullptr, ct, F, hidden, yc, mode, pf);
     if (st != B2Q_OK) return st;
     if (mode == 3) {

@@ -1,7 +1,9 @@
 """Worker of tests/test_gpu_tp_mlp.py::test_mlp_tp2_two_ranks: one NCCL rank per GPU.  Checks, against the oracle
 composition with the ranks simulated in order, the tensor-parallel MLP through b2q_mlp_swiglu_fp8_forward on every
-boundary the library has (one-shot and two-shot peer-memory kernel, chunked NCCL all-reduce overlapped with the
-GEMMs), a CUDA-graph replay of the few-token step, and ColumnLinear / RowLinear with a bias."""
+boundary the library has (one-shot and two-shot peer-memory kernel, the GEMM that scatters its partial sums into the
+owners' inboxes followed by the sum-and-gather kernel, in one and in two token chunks, and the NCCL all-reduce), a
+CUDA-graph replay of the few-token step, and ColumnLinear / RowLinear with a bias on the few-token and the many-token
+boundary."""
 import os
 import sys
 from pathlib import Path
@@ -32,7 +34,7 @@ def main():
     t = lambda a: torch.from_numpy(a).to(dev)
     results = {}
     modes = {}
-    for tokens in (1, 64, 200, 4096):
+    for tokens in (1, 64, 200, 4096, 4090):                   # 4090 tokens do not split into 32-row blocks per rank: NCCL
         x, wg, wu, wd = make_inputs(tokens, hidden, ffn)      # the weights depend on the token count (one random stream)
         mlp = TpFp8Mlp(t(wg), t(wu), t(wd), handle)
         xd = t(x).to(torch.bfloat16)
@@ -41,6 +43,17 @@ def main():
         ref = oracle_mlp(api, x, wg, wu, wd, world)
         results[f"mlp_m{tokens}"] = rel_err(y, ref)
         modes[tokens] = group.plan(tokens, hidden)
+        if tokens == 4096:                                 # two token chunks: the second stream sums chunk 0 under chunk 1's GEMMs
+            group.set_chunks(2)
+            y2 = mlp.forward(xd)
+            y3 = mlp.forward(xd)                           # again: the inboxes and flags are reused
+            default_handle().check()
+            group.set_chunks(0)
+            results["mlp_m4096_two_chunks"] = rel_err(y2.float().cpu().numpy(), ref)
+            results["mlp_m4096_two_chunks_repeat_differs"] = float((y2 != y3).any().item())
+            same = y2.clone()
+            dist.broadcast(same, 0)
+            results["mlp_m4096_ranks_differ"] = float((same != y2).any().item())
         if tokens == 64:                                   # the few-token step from a CUDA graph, replayed
             out = torch.empty(tokens, hidden, dtype=torch.bfloat16, device=dev)
             s = torch.cuda.Stream()
@@ -92,12 +105,28 @@ def main():
     ref_row = api.row_linear(np.concatenate(x_parts, 1).astype(np.float32), np.concatenate(w_parts, 1).astype(np.float32), bias, batch,
                              in_f, out_f, world)
     results["row_linear_bias_allreduce"] = rel_err(y_row, ref_row)
+    # the same layer over 2048 tokens: the scatter GEMM carries the bias on rank 0
+    big = 2048
+    xb = rng.standard_normal((big, in_f)).astype(np.float32)
+    xbl = np.ascontiguousarray(xb[:, c0:c1])
+    xblc, xbls = codec.quantize_rows(t(xbl), big, c1 - c0)
+    y_big = row.forward(xblc.view(big, c1 - c0), xbls).float().cpu().numpy()
+    default_handle().check()
+    xb_parts = []
+    for r in range(world):
+        xr = np.ascontiguousarray(xb[:, r * li:(r + 1) * li])
+        c, s_, _ = api.fp8_quantize_rows(xr, big, li, 0, 1)
+        xb_parts.append(api.fp8_decode(c, 0, 1).reshape(big, li) * s_[:, None])
+    ref_big = api.row_linear(np.concatenate(xb_parts, 1).astype(np.float32), np.concatenate(w_parts, 1).astype(np.float32), bias, big, in_f,
+                             out_f, world)
+    results["row_linear_bias_many_tokens"] = rel_err(y_big, ref_big)
+    modes["row2048"] = group.plan(big, out_f)
 
     worst = max(results.values())
     ok = torch.tensor([1 if worst <= 1e-2 else 0], device=dev)
     dist.all_reduce(ok, op=dist.ReduceOp.MIN)
-    expect_modes = {1: 1, 64: 1, 200: 2, 4096: 3}            # 4096 x 512 fp32 partials = 8 MiB: NCCL in 4 overlapped chunks
-    modes_ok = all(modes[k][0] == v for k, v in expect_modes.items()) and modes[4096][1] == 4
+    expect_modes = {1: 1, 64: 1, 200: 2, 4096: 4, 4090: 3, "row2048": 4}
+    modes_ok = all(modes[k][0] == v for k, v in expect_modes.items())
     if rank == 0:
         for k, v in results.items():
             print(f"{k}: rel_err {v:.3e}")
