@@ -189,7 +189,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMV / GEMM / quantizer side measurements")
     ap.add_argument("--chunks", type=int, default=0, help="token chunks of the overlapped all-reduce (0 = automatic)")
     ap.add_argument("--case", default=None,
-                    help="run ONE kernel case a few times and exit (for ncu captures): gemm_fp8:M:N:K | gemv_fp4:K:N:tokens | gemv_int4:K:N:tokens:group | kv_quant:tokens:head_dim:axis:bf16 | rms_quant:rows:cols:residual")
+                    help="run ONE kernel case a few times and exit (for ncu captures): gemm_fp8:M:N:K | gemv_fp4:K:N:tokens | gemv_int4:K:N:tokens:group | kv_quant:tokens:head_dim:axis:bf16 | rms_quant:rows:cols:residual | fp8_quant_rows:rows:cols:bf16 | swiglu_quant:rows:ffn | gemm_fp4_bs:tokens:N:K:mxfp8 | grouped_fp8:experts:rows_each:N:K")
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args()
     if args.case:
@@ -442,8 +442,9 @@ def oracle_mlp_check(shards, x_dev, y_host, rounding):
     total = None
     for sh in shards:
         F = sh.local_ffn
-        gu = api.gemm_fp8(xc.reshape(tokens, hidden), sh.gate_up.codes.cpu().numpy(), xs, sh.gate_up.scales.cpu().numpy(), 0, 1, "bf16")
-        h = api.swiglu(gu[:, :F], gu[:, F:])
+        inter = sh.gu_codes is not None
+        h = api.swiglu_mlp_hidden(xc, xs, (sh.gu_codes if inter else sh.gate_up.codes).cpu().numpy(),
+                                  (sh.gu_scales if inter else sh.gate_up.scales).cpu().numpy(), tokens, hidden, F, inter)
         hc, hs, _ = api.fp8_quantize_rows(h, tokens, F, 0, mode)
         part = api.gemm_fp8(hc.reshape(tokens, F), sh.down.codes.cpu().numpy(), hs, sh.down.scales.cpu().numpy(), 0, 1, "f32")
         total = part if total is None else total + part
@@ -506,6 +507,46 @@ def run_case(case: str, iters: int):
         res = torch.zeros(rows, cols, device=dev, dtype=torch.bfloat16) if with_res else None
         fn = lambda: rms_norm_quantize_fp8(x, gamma, 1e-6, residual=res)
         work, unit = (rows * cols * (3 + (4 if with_res else 0)) + 2 * cols + 4 * rows) / 1e9, "GB/s"
+    elif kind == "fp8_quant_rows":  # fp8_quant_rows:rows:cols:bf16  (per-row absmax / 448 scales, RNE)
+        rows, cols, bf16 = d
+        x = torch.randn(rows, cols, device=dev)
+        x = x.to(torch.bfloat16) if bf16 else x
+        codec = Fp8Codec.e4m3("rne")
+        fn = lambda: codec.quantize_rows(x, rows, cols)
+        work, unit = (rows * cols * (x.element_size() + 1) + 4 * rows) / 1e9, "GB/s"
+    elif kind == "swiglu_quant":    # swiglu_quant:rows:ffn  (silu(gate) * up over a [rows x 2 ffn] bf16 GEMM result, per-row E4M3)
+        from oxicuda_b200._lib import default_handle, ptr
+        import oxicuda_b200._lib as L
+        rows, ffn = d
+        gu = torch.randn(rows, 2 * ffn, device=dev).to(torch.bfloat16)
+        hc = torch.empty(rows, ffn, dtype=torch.uint8, device=dev)
+        hs = torch.empty(rows, device=dev)
+        fn = lambda: default_handle().call("b2q_swiglu_quantize_rows_bf16", ptr(gu), ptr(gu[:, ffn:]), rows, ffn, 2 * ffn, L.FP8_E4M3, L.ROUND_RNE,
+                                           ptr(hs), ptr(hc))
+        work, unit = (rows * ffn * 5 + 4 * rows) / 1e9, "GB/s"
+    elif kind == "gemm_fp4_bs":     # gemm_fp4_bs:tokens:N:K:mxfp8  (block-scaled FP4 prefill GEMM; mxfp8 = 1: W4A8, 0: split activations)
+        from oxicuda_b200.blas import gemm_fp4_blockscaled
+        tokens, n, k, mx = d
+        codes, scales = MicroScalingQuantizer(MicroScalingConfig(32, ScalingFormat.E8M0)).quantize_fp4(torch.randn(n * k, device=dev) * 0.02)
+        x = torch.randn(tokens, k, device=dev).to(torch.bfloat16)
+        out = torch.empty(tokens, n, dtype=torch.bfloat16, device=dev)
+        fn = lambda: gemm_fp4_blockscaled(codes, scales, x, n, k, mxfp8_activations=bool(mx), out=out)
+        work, unit = 2.0 * tokens * n * k / 1e12, "TFLOP/s"
+    elif kind == "grouped_fp8":     # grouped_fp8:experts:rows_each:N:K  (one launch over a device table)
+        from oxicuda_b200._lib import default_handle, ptr
+        import oxicuda_b200._lib as L
+        experts, rows_each, n, k = d
+        pad = (rows_each + 255) // 256 * 256
+        cap = experts * pad
+        a = torch.randint(0, 120, (cap, k), dtype=torch.uint8, device=dev)
+        w = torch.randint(0, 120, (experts * n, k), dtype=torch.uint8, device=dev)
+        sa, sw = torch.ones(cap, device=dev), torch.ones(experts * n, device=dev)
+        off = (torch.arange(experts, device=dev, dtype=torch.int32) * pad).contiguous()
+        cnt = torch.full((experts,), rows_each, dtype=torch.int32, device=dev)
+        out = torch.empty(cap, n, dtype=torch.bfloat16, device=dev)
+        fn = lambda: default_handle().call("b2q_grouped_gemm_fp8_rows", ptr(a), ptr(sa), ptr(w), ptr(sw), ptr(off), ptr(cnt), experts, cap, n, k,
+                                           L.FP8_E4M3, ptr(out), L.OUT_BF16)
+        work, unit = 2.0 * experts * rows_each * n * k / 1e12, "TFLOP/s"
     else:
         raise SystemExit(f"unknown case {case}")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
@@ -736,6 +777,49 @@ def side_measurements(dev, peaks):
     except Exception as exc:                                       # noqa: BLE001
         roof["gemm_i8_4096"] = {"error": repr(exc)}
     del ia, ib, ic
+
+    # ---- block-scaled FP4 prefill GEMM (E2M1 weights, E8M0 block scales) on tcgen05 kind::mxf8f6f4.block_scale ----
+    try:
+        from oxicuda_b200.blas import gemm_fp4_blockscaled
+        tk, Nd, Kd = 4096, 8192, 8192
+        wsets = [msq.quantize_fp4(torch.randn(Nd * Kd, device=dev) * 0.02) for _ in range(4)]      # 4 x 36 MB of codes and scales
+        xs4 = [torch.randn(tk, Kd, device=dev).to(torch.bfloat16) for _ in range(4)]
+        o4 = torch.empty(tk, Nd, dtype=torch.bfloat16, device=dev)
+        fl4 = 2.0 * tk * Nd * Kd
+        row = {"shape": "4096 tokens x N 8192 x K 8192, bf16 activations in, bf16 out; the time includes the activation quantization pre-pass"}
+        for name, mx in (("w4a8_mx_e4m3_activations", True), ("weight_only_split_activations", False)):
+            sec4 = _time_calls(lambda i: gemm_fp4_blockscaled(wsets[i % 4][0], wsets[i % 4][1], xs4[i % 4], Nd, Kd, mxfp8_activations=mx, out=o4), 20, 5)
+            row[name] = {"us": round(sec4 * 1e6, 1), "tflops": round(fl4 / sec4 / 1e12, 1),
+                         "frac_of_2x_bf16_burst": round(fl4 / sec4 / 1e12 / (2 * peaks["bf16_tflops"]), 3)}
+        roof["gemm_fp4_blockscaled"] = row
+        del wsets, xs4, o4
+    except Exception as exc:                                       # noqa: BLE001
+        roof["gemm_fp4_blockscaled"] = {"error": repr(exc)}
+
+    # ---- grouped FP8 MoE layer, Mixtral-shaped (8 experts 4096 -> 14336 -> 4096, top-2 over 4096 tokens), one GPU ----
+    try:
+        from oxicuda_b200.dist_infer import DistInferHandle, MoeFp8Layer, ParallelismConfig
+        E, hid, ffn_e, tk, topk = 8, 4096, 14336, 4096, 2
+        gen = torch.Generator(device=dev).manual_seed(0xB2000005)
+        experts = [(torch.randn(ffn_e, hid, device=dev, generator=gen) * 0.02, torch.randn(ffn_e, hid, device=dev, generator=gen) * 0.02,
+                    torch.randn(hid, ffn_e, device=dev, generator=gen) * 0.02) for _ in range(E)]
+        layer = MoeFp8Layer(experts, E, topk, DistInferHandle(0, ParallelismConfig(ep=1)))
+        del experts
+        # expert popularity ~ Dirichlet(1): logits = log p + Gumbel noise draws experts in proportion to p
+        p = torch.distributions.Dirichlet(torch.ones(E)).sample().to(dev)
+        lg = (p.log()[None, :] - torch.log(-torch.log(torch.rand(tk, E, device=dev, generator=gen)))).float().contiguous()
+        xm = torch.randn(tk, hid, device=dev, generator=gen).to(torch.bfloat16)
+        ym = torch.empty_like(xm)
+        secm = _time_calls(lambda i: layer.forward(xm, lg, out=ym), 10, 3)
+        flm = 2.0 * tk * topk * 3 * hid * ffn_e
+        roof["moe_fp8_mixtral"] = {"experts": E, "top_k": topk, "tokens": tk, "hidden": hid, "ffn": ffn_e, "us": round(secm * 1e6, 1),
+                                   "tflops": round(flm / secm / 1e12, 1), "rows_per_expert": [int(v) for v in layer.last_counts.tolist()],
+                                   "launches_per_call": "route, slot, scatter, quantize, ONE grouped gate|up GEMM, SwiGLU + quantize, ONE grouped down GEMM, gather",
+                                   "frac_of_2x_bf16_sustained": round(flm / secm / 1e12 / (2 * peaks["bf16_tflops_sustained"]), 3)}
+        del layer, xm, ym, lg
+    except Exception as exc:                                       # noqa: BLE001
+        roof["moe_fp8_mixtral"] = {"error": repr(exc)}
+    torch.cuda.empty_cache()
 
     # ---- FP8 W8A8 with few tokens on the 70B-shaped FFN projection: HBM-bound ----
     Kd, Nd = 8192, 28672

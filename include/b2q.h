@@ -291,7 +291,11 @@ int32_t b2q_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M
  * epilogue.rs:99-196).  w_layout = B2Q_W_KN takes the reference's row-major [K x N] operand B (transposed into the
  * handle's workspace on every call: hold weights as [N x K] where that matters).  The prefill tcgen05 kernels apply the
  * epilogue in their store path; few-token shapes run their kernel into the workspace and one elementwise pass. */
-typedef enum { B2Q_EPI_LINEAR = 0, B2Q_EPI_RELU = 1, B2Q_EPI_GELU = 2, B2Q_EPI_BIAS = 3, B2Q_EPI_BIAS_RELU = 4 } b2q_epilogue_op;
+typedef enum { B2Q_EPI_LINEAR = 0, B2Q_EPI_RELU = 1, B2Q_EPI_GELU = 2, B2Q_EPI_BIAS = 3, B2Q_EPI_BIAS_RELU = 4,
+               /* no counterpart in EpilogueOp: w holds gate and up rows interleaved per 128 (b2q_interleave_rows128), n % 256 == 0,
+                * out is [m x n / 2] = silu(gate) * up (SwiGluExpert::forward, crates/oxicuda-moe/src/expert/ffn.rs:208-243);
+                * alpha, beta and bias are not applied */
+               B2Q_EPI_SWIGLU = 5 } b2q_epilogue_op;
 typedef enum { B2Q_W_NK = 0, B2Q_W_KN = 1 } b2q_w_layout;
 typedef struct {
   const uint8_t* a; const uint8_t* w; int64_t m, n, k; int32_t fmt;
@@ -334,8 +338,8 @@ int32_t b2q_tp_set_chunks(b2q_tp t, int chunks);
  * rank order in fp32, the reference's order, row_parallel.rs:202-223); 4 (bf16 results up to 64 MiB, tokens a multiple
  * of 32 * tp) the reduce-scatter is part of the GEMM: its epilogue stores every row block as bf16 into the inbox of the
  * rank that owns those rows, then one kernel waits for the peers (same limit), adds the tp partials of its own rows in
- * rank order in fp32 and pushes the bf16 sums to every rank; `chunks` > 1 cuts the GEMM into column chunks (chosen so
- * that its tile waves stay the same) and that kernel runs on a second stream under the GEMM of the next chunk;
+ * rank order in fp32 and pushes the bf16 sums to every rank; with b2q_tp_set_chunks > 1 the GEMM is cut into column
+ * chunks and that kernel runs on a second stream under the GEMM of the next chunk (the plan itself says 1);
  * 3 NCCL all-reduce of bf16 partials (anything else, or no peers attached), `chunks` token chunks.
  * Every rank gets the same bits in modes 1, 2 and 4.  Pure host function. */
 int32_t b2q_tp_plan(int tp, int peers_attached, int64_t tokens, int64_t out_features, int* mode, int* chunks);
@@ -362,6 +366,19 @@ int32_t b2q_row_linear_forward_allreduce(b2q_tp t, const uint8_t* x_codes, const
 int32_t b2q_mlp_swiglu_fp8_forward(b2q_tp t, const void* x_bf16, const uint8_t* w_gate_up, const float* s_gate_up,
                                    const uint8_t* w_down, const float* s_down, int64_t tokens, int64_t hidden,
                                    int64_t ffn_local, int rounding, void* y_bf16);
+/* The same layer with the layout of the gate | up shard stated.  B2Q_GATE_UP_INTERLEAVED128 (ffn_local % 128 == 0): rows
+ * [256 j, 256 j + 128) are gate rows [128 j, ...), the next 128 the same up rows (and the scales likewise), as
+ * b2q_interleave_rows128 writes them.  One accumulator tile of the gate | up GEMM then holds both projections of the same
+ * hidden units, so above 128 tokens silu(gate) * up is formed in the GEMM epilogue and only h [tokens x ffn_local] bf16 is
+ * written (the bf16 rounding of h, 2^-9, is far below the E4M3 step that follows); few-token steps read the interleaved
+ * GEMM result directly.  No counterpart in the reference, which multiplies the three matrices one after the other. */
+typedef enum { B2Q_GATE_UP_CONCATENATED = 0, B2Q_GATE_UP_INTERLEAVED128 = 1 } b2q_gate_up_layout;
+int32_t b2q_mlp_swiglu_fp8_forward_ex(b2q_tp t, const void* x_bf16, const uint8_t* w_gate_up, const float* s_gate_up,
+                                      const uint8_t* w_down, const float* s_down, int64_t tokens, int64_t hidden,
+                                      int64_t ffn_local, int rounding, int gate_up_layout, void* y_bf16);
+/* out [2 * rows x row_bytes] = the rows of a and of b interleaved per 128 rows (rows % 128 == 0; row_bytes a multiple of
+ * 16, or 4 for a vector of per-row scales): a load-time step, one pass over the weights. */
+int32_t b2q_interleave_rows128(b2q_handle h, const void* a, const void* b, int64_t rows, int64_t row_bytes, void* out);
 
 /* ---- grouped GEMM: grouped_gemm / GroupedGemmProblem crates/oxicuda-blas/src/batched/grouped_gemm.rs:46-78 ----
  * One FP8 GEMM per entry of a host-side problem table (an expert and the tokens routed to it); entries with m == 0 are
@@ -418,6 +435,11 @@ int32_t b2q_moe_scatter(b2q_handle h, const void* x, const int32_t* slot_of_pair
 int32_t b2q_moe_forward(b2q_tp t, const void* x_bf16, const float* logits, const uint8_t* w_gate_up, const float* s_gate_up,
                         const uint8_t* w_down, const float* s_down, int64_t tokens, int64_t hidden, int64_t ffn, int n_experts,
                         int top_k, int rounding, void* y_bf16, int32_t* counts_out);
+/* The same with the layout of every expert's gate | up block stated (see b2q_mlp_swiglu_fp8_forward_ex): with
+ * B2Q_GATE_UP_INTERLEAVED128 (ffn % 128 == 0) silu(gate) * up is formed in the epilogue of the grouped GEMM. */
+int32_t b2q_moe_forward_ex(b2q_tp t, const void* x_bf16, const float* logits, const uint8_t* w_gate_up, const float* s_gate_up,
+                           const uint8_t* w_down, const float* s_down, int64_t tokens, int64_t hidden, int64_t ffn, int n_experts,
+                           int top_k, int rounding, int gate_up_layout, void* y_bf16, int32_t* counts_out);
 
 /* ---- FP4 weight-only decode GEMV: Fp4GemmConfig / generate_fp4_gemm_ptx
  *      crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:337-395, :1237-1362; semantics = dequantize_fp4 (:879-897)

@@ -293,6 +293,31 @@ def swiglu(gate, up):
     return h.reshape(np.shape(gate))
 
 
+def swiglu_mlp_hidden(x_codes, x_scales, w_codes, w_scales, tokens, hidden, F, interleaved=False):
+    """h = silu(gate) * up between the two projections of the FP8 SwiGLU MLP (SwiGluExpert::forward,
+    crates/oxicuda-moe/src/expert/ffn.rs:208-243, over Fp8Codec operands; a composition: the reference has no quantized
+    MLP, parity unpinned).  w_codes [2F x hidden] in one of the two layouts of the library:
+      concatenated (rows [0, F) gate, [F, 2F) up): the gate | up product is a GEMM output, rounded to bf16; h in f32;
+      interleaved per 128 rows (rows [256 j, 256 j + 128) gate rows [128 j, ...), then the same up rows): the product stays
+      in f32 and h is rounded to bf16 (it is what the GEMM writes).
+    The per-row E4M3 quantization that follows amplifies the difference between the two (a few per cent of the elements
+    change code), so each layout is compared with its own statement."""
+    gu = np.asarray(gemm_fp8(np.asarray(x_codes).reshape(tokens, hidden), np.asarray(w_codes).reshape(2 * F, hidden), x_scales, w_scales, 0, 1,
+                             "f32" if interleaved else "bf16"), np.float32).reshape(tokens, 2 * F)
+    if not interleaved:
+        return swiglu(np.ascontiguousarray(gu[:, :F]), np.ascontiguousarray(gu[:, F:]))
+    g4 = gu.reshape(tokens, F // 128, 2, 128)
+    h = swiglu(np.ascontiguousarray(g4[:, :, 0, :]).reshape(tokens, F), np.ascontiguousarray(g4[:, :, 1, :]).reshape(tokens, F))
+    return bf16_bits_to_f32(f32_to_bf16_bits(h)).reshape(tokens, F)
+
+
+def interleave_rows128(a, b):
+    """Rows of a and b interleaved per 128 rows (b2q_interleave_rows128)."""
+    a, b = np.asarray(a), np.asarray(b)
+    F = a.shape[0]
+    return np.stack([a.reshape(F // 128, 128, *a.shape[1:]), b.reshape(F // 128, 128, *b.shape[1:])], axis=1).reshape(2 * F, *a.shape[1:])
+
+
 # ---- heuristics ----
 # ---- KV cache / RMSNorm ----
 def kv_cache_quantize(x, n_tokens, head_dim, bits=8, axis=0):

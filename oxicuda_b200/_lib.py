@@ -29,6 +29,7 @@ FP4_E2M1, FP4_INT4 = 0, 1
 SCALE_F32, SCALE_E8M0 = 0, 1
 SYMMETRIC, ASYMMETRIC = 0, 1
 OUT_BF16, OUT_F32 = 0, 1
+GATE_UP_CONCATENATED, GATE_UP_INTERLEAVED128 = 0, 1
 SCALE_SCALAR, SCALE_PER_ROW = 0, 1
 
 
@@ -160,6 +161,7 @@ SIGNATURES = {
     "b2q_moe_assign_slots": (C.c_int32, [_H, _P, _I64, _I, _I, _P, _P, _P]),
     "b2q_moe_scatter": (C.c_int32, [_H, _P, _P, _I64, _I, _I64, _P]),
     "b2q_moe_forward": (C.c_int32, [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I, _I, _I, _P, _P]),
+    "b2q_moe_forward_ex": (C.c_int32, [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I, _I, _I, _I, _P, _P]),
     "b2q_ep_token_scatter": (C.c_int32, [_H, _P, _P, _P, _I64, _I64, _P]),
     "b2q_ep_token_gather_bf16": (C.c_int32, [_H, _P, _P, _P, _I64, _I, _I64, _P]),
     "b2q_gemv_fp4_wo": (C.c_int32, [_H, _P, _P, _I, _I, _P, _I64, _I64, _I64, _P, _I]),
@@ -178,6 +180,8 @@ SIGNATURES = {
     "b2q_column_linear_forward": (C.c_int32, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P, _P]),
     "b2q_row_linear_forward_allreduce": (C.c_int32, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _P]),
     "b2q_mlp_swiglu_fp8_forward": (C.c_int32, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I, _P]),
+    "b2q_mlp_swiglu_fp8_forward_ex": (C.c_int32, [_P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I, _I, _P]),
+    "b2q_interleave_rows128": (C.c_int32, [_H, _P, _P, _I64, _I64, _P]),
     "b2q_gemm_fp4_blockscaled": (C.c_int32, [_H, _P, _P, _P, _I64, _I64, _I64, _I, _P, _I]),
     "b2q_classify_workload": (C.c_int32, [_U32, _U32, _U32]),
     "b2q_ref_tile_config": (C.c_int32, [_I, _U32, _U32, _U32, C.POINTER(TileConfig)]),

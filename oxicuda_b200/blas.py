@@ -190,6 +190,9 @@ class EpilogueOp(Enum):
     LinearCombinationGelu = 2
     LinearCombinationBias = 3
     LinearCombinationBiasRelu = 4
+    # not in the reference: w holds gate and up rows interleaved per 128, out [M x N / 2] = silu(gate) * up
+    # (SwiGluExpert::forward, crates/oxicuda-moe/src/expert/ffn.rs:208-243)
+    SwiGluPairs = 5
 
     def needs_bias(self) -> bool:
         return self in (EpilogueOp.LinearCombinationBias, EpilogueOp.LinearCombinationBiasRelu)
@@ -200,7 +203,8 @@ def gemm_fp8_ex(a: torch.Tensor, w: torch.Tensor, scale_a: torch.Tensor, scale_w
                 w_is_kn: bool = False, out_dtype=torch.bfloat16, fmt: int = L.FP8_E4M3) -> torch.Tensor:
     """gemm_impl with an EpilogueOp (crates/oxicuda-blas/src/level3/gemm_api.rs:126-231, gemm/epilogue.rs:99-196):
     out = act(alpha * (A . W^T) * scale_a * scale_w + beta * out + bias[col]).  `w` is [N x K], or with w_is_kn the
-    reference's row-major [K x N] operand B.  With beta != 0 `out` must hold C on entry."""
+    reference's row-major [K x N] operand B.  With beta != 0 `out` must hold C on entry.  EpilogueOp.SwiGluPairs: `w`
+    holds gate and up rows interleaved per 128 and out is [M x N / 2] = silu(gate) * up."""
     import ctypes as C
     M, K = a.shape
     if w_is_kn:
@@ -214,7 +218,7 @@ def gemm_fp8_ex(a: torch.Tensor, w: torch.Tensor, scale_a: torch.Tensor, scale_w
     if out is None:
         if beta != 0.0:
             raise L.InvalidArgument(L.ERR_INVALID_ARGUMENT, "beta != 0 needs the C operand in `out`")
-        out = torch.empty(M, N, dtype=out_dtype, device=a.device)
+        out = torch.empty(M, N // 2 if epilogue is EpilogueOp.SwiGluPairs else N, dtype=out_dtype, device=a.device)
     d = L.GemmFp8Desc(a.data_ptr(), w.data_ptr(), M, N, K, fmt, scale_a.data_ptr(), _scale_kind(scale_a, M), scale_w.data_ptr(),
                       _scale_kind(scale_w, N), out.data_ptr(), L.OUT_BF16 if out.dtype == torch.bfloat16 else L.OUT_F32, alpha, beta,
                       bias.data_ptr() if bias is not None else None, epilogue.value, 1 if w_is_kn else 0)

@@ -53,7 +53,9 @@ struct Params {
   int epi;                          // 0: plain scaled store; else the fields below apply
   float alpha, beta;
   const float* bias;                // [N] or null
-  int act;                          // 0 none, 1 relu, 2 gelu as x * sigmoid(1.702 x)
+  int act;                          // 0 none, 1 relu, 2 gelu as x * sigmoid(1.702 x); 3 SwiGLU over column pairs (pair kernel
+                                    // only): columns [256 j, 256 j + 128) of the product are gate, the next 128 up, and
+                                    // out [M x N / 2] gets silu(gate) * up at columns [128 j, 128 j + 128)
   int tma_store;                    // 1: bf16 / f32 rows leave through shared memory and TMA stores (16-byte aligned pitch)
   // grouped mode of the pair kernel (groups > 0, table on the device): problem g multiplies rows
   // [group_offsets[g], group_offsets[g] + group_counts[g]) of A (offsets are multiples of 256, so a tile never spans
@@ -276,6 +278,63 @@ __device__ __forceinline__ void epilogue_rows(const Params& pp, const CUtensorMa
     const int64_t n = n0 + c;
     if (!row_ok || n >= p.N) continue;
     store_chunk<KIND>(p, r, m, n, sa, sw0);
+  }
+}
+
+// SwiGLU over column pairs (Params::act == 3): one warp's 32 rows of a 256-column accumulator tile whose columns
+// [0, 128) are gate and [128, 256) up projections of the same 128 hidden units (the weight rows are interleaved per 128).
+// h = silu(gate) * up with both factors scaled in fp32 (SwiGluExpert::forward, crates/oxicuda-moe/src/expert/ffn.rs:208-243;
+// silu(x) = x / (1 + exp(-x)), crates/oxicuda-lm/src/layer/ffn.rs:25-27), stored as bf16 into out [M x N / 2] through the
+// same staging buffers and TMA stores as the plain epilogue.  The GEMM result itself never reaches memory.
+__device__ __forceinline__ void epilogue_rows_swiglu(const Params& p, const CUtensorMap* map_out, EpiWarp& ew, uint32_t tmem_acc,
+                                                     int64_t m_warp0, int lane, int64_t n0, const float* scale_w) {
+  const int64_t m = m_warp0 + lane;
+  const bool row_ok = m < p.M;
+  const float sa = row_ok && p.scale_a ? (p.scale_a_rows ? p.scale_a[m] : p.scale_a[0]) : 1.0f;
+  const float sw0 = scale_w && !p.scale_w_rows ? scale_w[0] : 1.0f;
+#pragma unroll 1
+  for (int c = 0; c < 128; c += 64) {
+    const uint32_t buf = (ew.it & 1u) * 4096u;
+    uint8_t* row = ew.smem_p + buf + lane * 128;
+#pragma unroll 1
+    for (int sub = 0; sub < 2; ++sub) {
+      uint32_t g[32], u[32];
+      __syncwarp();
+      tmem_ld32(tmem_acc + c + 32 * sub, g);
+      tmem_ld32(tmem_acc + 128 + c + 32 * sub, u);
+      tmem_ld_wait();
+      if (m_warp0 >= p.M) continue;                              // warp-uniform: nothing of these rows is inside the output
+      if (sub == 0) {
+        if (lane == 0) tma_store_wait_read<1>();                 // the store that last read this buffer has read it
+        __syncwarp();
+      }
+      const int64_t ng = n0 + c + 32 * sub;                      // gate column of g[0]; its up column is ng + 128
+#pragma unroll
+      for (int j = 0; j < 32; j += 8) {
+        float h[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const float swg = p.scale_w_rows ? __ldg(scale_w + ng + j + i) : sw0;
+          const float swu = p.scale_w_rows ? __ldg(scale_w + ng + 128 + j + i) : sw0;
+          const float gg = __uint_as_float(g[j + i]) * (sa * swg), uu = __uint_as_float(u[j + i]) * (sa * swu);
+          h[i] = gg * uu * __frcp_rn(1.0f + exp2f(-1.4426950408889634f * gg));
+        }
+        uint4 pk;
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(h[0], h[1]), h1 = __floats2bfloat162_rn(h[2], h[3]);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(h[4], h[5]), h3 = __floats2bfloat162_rn(h[6], h[7]);
+        pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+        pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+        *reinterpret_cast<uint4*>(row + (((sub * 4 + (j >> 3)) ^ (lane & 7)) << 4)) = pk;
+      }
+    }
+    if (m_warp0 >= p.M) continue;
+    fence_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(map_out, ew.smem_u + buf, (int)(n0 / 2 + c), (int)m_warp0);
+      tma_store_commit();
+    }
+    ++ew.it;
   }
 }
 
@@ -639,8 +698,12 @@ __device__ __forceinline__ void gemm_tc2_body(const CUtensorMap& map_a, const CU
         mo = scatter_maps + owner;
         m_store = (int64_t)p.rs_rank * p.rs_rows + (m_warp0 - (int64_t)owner * p.rs_rows);
       }
-      epilogue_rows<KIND>(p, mo, ew, tmem_base + buf * BN2 + ((uint32_t)(q * 32) << 16), c.width, m_warp0, lane, c.n0,
-                          p.scale_w ? p.scale_w + c.sw_off : nullptr, m_store);
+      if (KIND == kF8 && p.act == 3)
+        epilogue_rows_swiglu(p, mo, ew, tmem_base + buf * BN2 + ((uint32_t)(q * 32) << 16), m_warp0, lane, c.n0,
+                             p.scale_w ? p.scale_w + c.sw_off : nullptr);
+      else
+        epilogue_rows<KIND>(p, mo, ew, tmem_base + buf * BN2 + ((uint32_t)(q * 32) << 16), c.width, m_warp0, lane, c.n0,
+                            p.scale_w ? p.scale_w + c.sw_off : nullptr, m_store);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(tempty_bar(buf), 0));   // the leader's MMA thread waits for both CTAs
@@ -690,7 +753,8 @@ int32_t make_out_map(b2q_handle h, CUtensorMap* map, Params& p) {
   if (!p.out || p.c_s32 || p.c_f32) return B2Q_OK;
   const int es = p.out_type == B2Q_OUT_BF16 ? 2 : 4;
   if ((reinterpret_cast<uintptr_t>(p.out) & 15) != 0 || (p.N * es) % 16 != 0) return B2Q_OK;
-  int32_t st = b2q_tensor_map_2d(h, map, p.out, es, (uint64_t)p.N, (uint64_t)p.M, (uint32_t)(128 / es), 32u);
+  const int64_t out_cols = p.act == 3 ? p.N / 2 : p.N;
+  int32_t st = b2q_tensor_map_2d(h, map, p.out, es, (uint64_t)out_cols, (uint64_t)p.M, (uint32_t)(128 / es), 32u);
   if (st == B2Q_OK) p.tma_store = 1;
   return st;
 }
@@ -750,7 +814,8 @@ int32_t launch2(b2q_handle h, const void* a, const void* w, Params p, const Scat
   const int max_pairs = h->sm_count / 2;
   // tail split: when the last wave fills at most half of the pairs, its tiles become two half-width units each
   const int rem = (int)(tiles % max_pairs);
-  const bool split = tiles > max_pairs && rem > 0 && 2 * rem <= max_pairs && h->sw.no_tail_split < 0;
+  // (not in SwiGLU-pair mode: a half-width unit would hold the gate or the up half of a tile only)
+  const bool split = tiles > max_pairs && rem > 0 && 2 * rem <= max_pairs && h->sw.no_tail_split < 0 && p.act != 3;
   p.full_units = split ? (int)(tiles - rem) : (int)tiles;
   p.total_units = split ? (int)(tiles + rem) : (int)tiles;
   const int pairs = (int)(p.total_units < max_pairs ? p.total_units : max_pairs);
@@ -836,6 +901,19 @@ __global__ void __launch_bounds__(256) epilogue_post_kernel(const float* __restr
   }
 }
 
+// SwiGLU over column pairs for the kernels without that epilogue: plain [M x N] f32 with gate at columns
+// [256 j, 256 j + 128) and up at the next 128 -> out [M x N / 2].
+__global__ void __launch_bounds__(256) swiglu_pairs_post_kernel(const float* __restrict__ plain, void* out, int out_type, int64_t M, int64_t N) {
+  const int64_t F = N / 2, total = M * F;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t m = i / F, f = i - m * F, col = ((f >> 7) << 8) + (f & 127);
+    const float g = plain[m * N + col], u = plain[m * N + col + 128];
+    const float v = g * u * __frcp_rn(1.0f + exp2f(-1.4426950408889634f * g));
+    if (out_type == B2Q_OUT_BF16) reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(v);
+    else reinterpret_cast<float*>(out)[i] = v;
+  }
+}
+
 // [K x N] row-major codes -> [N x K] (the layout every kernel here reads): 32 x 32 byte tiles through shared memory.
 __global__ void __launch_bounds__(256) transpose_u8_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_t K, int64_t N) {
   __shared__ uint8_t tile[32][33];
@@ -858,7 +936,9 @@ int32_t gemm_fp8_impl(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t 
     if (h->sw.force_tile == 9) kid = 4;        // "p(air)": the two-CTA kernel
   }
   const bool tma_ok = K % 16 == 0 && ((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(w)) & 15) == 0;
-  const bool fused = (kid == 1 || kid == 2 || kid == 4) && tma_ok;      // the prefill kernels apply the epilogue themselves
+  bool fused = (kid == 1 || kid == 2 || kid == 4) && tma_ok;            // the prefill kernels apply the epilogue themselves
+  if (epi && epi->act == 3)                                             // SwiGLU pairs: the pair kernel with TMA stores of bf16 only
+    fused = kid == 4 && tma_ok && N % 256 == 0 && out_type == B2Q_OUT_BF16 && (reinterpret_cast<uintptr_t>(out) & 15) == 0;
   if (epi && !fused) {
     // few-token / SIMT kernels: plain f32 result into the second workspace (the kernels use the first themselves),
     // then one elementwise pass
@@ -870,7 +950,8 @@ int32_t gemm_fp8_impl(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t 
     const int64_t total = M * N;
     int grid = (int)((total + 255) / 256);
     if (grid > h->sm_count * 8) grid = h->sm_count * 8;
-    epilogue_post_kernel<<<grid, 256, 0, h->stream>>>((const float*)ws, out, out_type, M, N, epi->alpha, epi->beta, epi->bias, epi->act);
+    if (epi->act == 3) swiglu_pairs_post_kernel<<<grid, 256, 0, h->stream>>>((const float*)ws, out, out_type, M, N);
+    else epilogue_post_kernel<<<grid, 256, 0, h->stream>>>((const float*)ws, out, out_type, M, N, epi->alpha, epi->beta, epi->bias, epi->act);
     B2Q_LAUNCH_CHECK(h, "epilogue_post_kernel");
     return B2Q_OK;
   }
@@ -965,10 +1046,22 @@ int32_t launch2_grouped(b2q_handle h, const void* a, const void* w, Params p, in
 
 }  // namespace tc
 
+int32_t b2q_grouped_gemm_fp8_rows_act(b2q_handle h, const uint8_t* a, const float* scale_a, const uint8_t* w, const float* scale_w,
+                                      const int32_t* row_offsets, const int32_t* row_counts, int groups, int64_t capacity_rows, int64_t N, int64_t K,
+                                      int fmt, void* out, int out_type, int act);
 extern "C" int32_t b2q_grouped_gemm_fp8_rows(b2q_handle h, const uint8_t* a, const float* scale_a, const uint8_t* w, const float* scale_w,
                                              const int32_t* row_offsets, const int32_t* row_counts, int groups, int64_t capacity_rows,
                                              int64_t N, int64_t K, int fmt, void* out, int out_type) {
+  return b2q_grouped_gemm_fp8_rows_act(h, a, scale_a, w, scale_w, row_offsets, row_counts, groups, capacity_rows, N, K, fmt, out, out_type, 0);
+}
+// act 3: every problem's weight rows are gate and up rows interleaved per 128 and out is [capacity_rows x N / 2] bf16 =
+// silu(gate) * up (the SwiGLU epilogue of the pair kernel); act 0: the plain product.
+int32_t b2q_grouped_gemm_fp8_rows_act(b2q_handle h, const uint8_t* a, const float* scale_a, const uint8_t* w, const float* scale_w,
+                                      const int32_t* row_offsets, const int32_t* row_counts, int groups, int64_t capacity_rows, int64_t N, int64_t K,
+                                      int fmt, void* out, int out_type, int act) {
   B2Q_REQUIRE_HANDLE(h);
+  if (act == 3 && (N % 256 != 0 || out_type != B2Q_OUT_BF16 || (reinterpret_cast<uintptr_t>(out) & 15) != 0))
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "grouped_gemm_fp8_rows: the SwiGLU epilogue needs N %% 256 == 0 and a 16-byte aligned bf16 output");
   if (groups <= 0 || capacity_rows <= 0 || N <= 0 || K <= 0)
     B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "grouped_gemm_fp8_rows: dimensions must be non-zero: groups=%d, rows=%lld, n=%lld, k=%lld", groups,
              (long long)capacity_rows, (long long)N, (long long)K);
@@ -985,6 +1078,7 @@ extern "C" int32_t b2q_grouped_gemm_fp8_rows(b2q_handle h, const uint8_t* a, con
   p.idesc = ((uint32_t)fmt << 7) | ((uint32_t)fmt << 10);
   p.alpha = 1.0f;
   p.group_offsets = row_offsets; p.group_counts = row_counts; p.groups = groups;
+  if (act == 3) { p.epi = 1; p.act = 3; }
   return tc::launch2_grouped(h, a, w, p, capacity_rows);
 }
 
@@ -1000,7 +1094,9 @@ extern "C" int32_t b2q_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w
 extern "C" int32_t b2q_gemm_fp8_ex(b2q_handle h, const b2q_gemm_fp8_desc* d) {
   B2Q_REQUIRE_HANDLE(h);
   if (!d) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemm_fp8_ex: null descriptor");
-  if (d->epilogue < 0 || d->epilogue > 4) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemm_fp8_ex: unknown epilogue %d", d->epilogue);
+  if (d->epilogue < 0 || d->epilogue > 5) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemm_fp8_ex: unknown epilogue %d", d->epilogue);
+  if (d->epilogue == B2Q_EPI_SWIGLU && (d->n % 256 != 0 || d->alpha != 1.0f || d->beta != 0.0f))
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemm_fp8_ex: the SwiGLU epilogue needs n %% 256 == 0 (gate / up rows interleaved per 128), alpha 1, beta 0");
   if (d->w_layout < 0 || d->w_layout > 1) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemm_fp8_ex: unknown weight layout %d", d->w_layout);
   const bool needs_bias = d->epilogue == B2Q_EPI_BIAS || d->epilogue == B2Q_EPI_BIAS_RELU;
   if (needs_bias && !d->bias) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemm_fp8_ex: this epilogue needs a bias vector");
@@ -1022,7 +1118,8 @@ extern "C" int32_t b2q_gemm_fp8_ex(b2q_handle h, const b2q_gemm_fp8_desc* d) {
     w = wt;
   }
   tc::EpiArgs e{d->alpha, d->beta, needs_bias ? d->bias : nullptr,
-                (d->epilogue == B2Q_EPI_RELU || d->epilogue == B2Q_EPI_BIAS_RELU) ? 1 : (d->epilogue == B2Q_EPI_GELU ? 2 : 0)};
+                (d->epilogue == B2Q_EPI_RELU || d->epilogue == B2Q_EPI_BIAS_RELU) ? 1
+                    : (d->epilogue == B2Q_EPI_GELU ? 2 : (d->epilogue == B2Q_EPI_SWIGLU ? 3 : 0))};
   const bool plain = d->alpha == 1.0f && d->beta == 0.0f && !e.bias && e.act == 0;
   return tc::gemm_fp8_impl(h, d->a, w, d->m, d->n, d->k, d->fmt, d->scale_a, d->scale_a_kind, d->scale_w, d->scale_w_kind, d->out,
                            d->out_type, plain ? nullptr : &e);

@@ -688,7 +688,7 @@ __global__ void __launch_bounds__(1024) fp8_quantize_rows_fused_kernel(const T* 
   }
 }
 
-// Many rows of up to 16384 elements (per-token quantization of a prefill batch): one CTA per row keeps the row in
+// Many rows of up to 65536 elements (per-token quantization of a prefill batch): one CTA per row keeps the row in
 // registers (thread t holds chunks t, t + blockDim, ... of 8 elements), so the input is read once and nothing is
 // divided per element but the value itself.  Same arithmetic as the two-kernel path (finish_row, divide, clamp, encode).
 template <typename T> __device__ __forceinline__ void load_chunk8(const T* row, int c, float (&v)[8]);
@@ -703,57 +703,123 @@ template <> __device__ __forceinline__ void load_chunk8<__nv_bfloat16>(const __n
   for (int j = 0; j < 4; ++j) { v[2 * j] = __uint_as_float(w[j] << 16); v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u); }
 }
 
+// Two RNE codes of (x0, x1) / scale without a division where that is provably the same.  r_lo and r_hi are RN(1 / scale)
+// narrowed and widened by 2^-21: the exact quotient lies between x * r_lo and x * r_hi (three roundings of 2^-24 each
+// against a margin of 2^-21), the saturating conversion is monotonic, so if both ends convert to the same code every
+// value between them does.  Otherwise (a quotient within 2^-20 of a rounding boundary) the IEEE division decides.
+__device__ __forceinline__ uint32_t fp8x2_quotient_rne(float x0, float x1, float scale, float r_lo, float r_hi, int fmt) {
+  const __nv_fp8_interpretation_t f = fmt == 0 ? __NV_E4M3 : __NV_E5M2;
+  uint32_t lo = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(x0, r_lo), __fmul_rn(x1, r_lo)), __NV_SATFINITE, f);
+  const uint32_t hi = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(x0, r_hi), __fmul_rn(x1, r_hi)), __NV_SATFINITE, f);
+  if (lo != hi) lo = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(x0, scale), __fdiv_rn(x1, scale)), __NV_SATFINITE, f);
+  return lo;
+}
+// The bracket needs a normal scale and a normal reciprocal; rows outside (all-zero rows have scale 1) divide.
+__device__ __forceinline__ bool quotient_bracket(float scale, float& r_lo, float& r_hi) {
+  const float r = __frcp_rn(scale);
+  r_lo = __fmul_rn(r, 1.0f - 4.76837158203125e-7f);          // 1 - 2^-21
+  r_hi = __fmul_rn(r, 1.0f + 4.76837158203125e-7f);
+  return scale > 1e-30f && scale < 1e30f;
+}
+
+// raw chunk of 8 elements: two float4 (f32) or one uint4 (bf16)
+template <typename T> struct RawChunk;
+template <> struct RawChunk<float> {
+  float4 a, b;
+  __device__ __forceinline__ void load(const float* row, int c) { a = reinterpret_cast<const float4*>(row)[2 * c]; b = reinterpret_cast<const float4*>(row)[2 * c + 1]; }
+  __device__ __forceinline__ void get(float (&v)[8]) const { v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w; }
+  // |x| as an integer: NaN and infinities compare above every finite value, so one maximum finds both the absmax and bad input
+  __device__ __forceinline__ uint32_t amax_bits(uint32_t m) const {
+    const float v[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+    for (int j = 0; j < 8; ++j) m = max(m, __float_as_uint(v[j]) & 0x7FFFFFFFu);
+    return m;
+  }
+};
+template <> struct RawChunk<__nv_bfloat16> {
+  uint4 q;
+  __device__ __forceinline__ void load(const __nv_bfloat16* row, int c) { q = reinterpret_cast<const uint4*>(row)[c]; }
+  __device__ __forceinline__ void get(float (&v)[8]) const {
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { v[2 * j] = __uint_as_float(w[j] << 16); v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u); }
+  }
+  // two bf16 lanes per word: one packed maximum per word (NaN propagates, so a NaN or an infinity ends up in the
+  // result and is caught by the same integer comparison as in the f32 case)
+  __device__ __forceinline__ uint32_t amax_bits(uint32_t m) const {
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+    __nv_bfloat162 acc = *reinterpret_cast<const __nv_bfloat162*>(&m);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t a = w[j] & 0x7FFF7FFFu;
+      acc = __hmax2_nan(acc, *reinterpret_cast<const __nv_bfloat162*>(&a));
+    }
+    return *reinterpret_cast<const uint32_t*>(&acc);
+  }
+};
+
 // FULL: every thread has all NCH chunks (cols == 8 * NCH * blockDim), so the bounds predicates drop out.
 template <typename T, int NCH, bool FULL>
 __global__ void __launch_bounds__(1024) fp8_quantize_rows_reg_kernel(const T* __restrict__ x, int64_t cols, StatArgs a, int fmt, int rounding,
                                                                      uint8_t* __restrict__ codes) {
-  __shared__ float sh_amax[32];
-  __shared__ int sh_bad[32];
+  __shared__ uint32_t sh_amax[32];
   const int64_t r = blockIdx.x;
   const T* row = x + r * cols;
   const int chunks = (int)(cols >> 3);
-  float v[NCH][8];
-  float amax = 0.0f;
-  int bad = 0;
+  RawChunk<T> raw[NCH];
+  uint32_t mb = 0;
 #pragma unroll
   for (int k = 0; k < NCH; ++k) {
     const int c = (int)threadIdx.x + k * (int)blockDim.x;
-    if (FULL || c < chunks) {
-      load_chunk8<T>(row, c, v[k]);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) { amax = fmaxf(amax, fabsf(v[k][j])); bad |= !isfinite(v[k][j]); }
-    }
+    if (FULL || c < chunks) raw[k].load(row, c);
   }
-  amax = warp_max(amax);
-  bad = __any_sync(0xffffffffu, bad);
-  if ((threadIdx.x & 31) == 0) { sh_amax[threadIdx.x >> 5] = amax; sh_bad[threadIdx.x >> 5] = bad; }
+#pragma unroll
+  for (int k = 0; k < NCH; ++k) {
+    const int c = (int)threadIdx.x + k * (int)blockDim.x;
+    if (FULL || c < chunks) mb = raw[k].amax_bits(mb);
+  }
+  if constexpr (sizeof(T) == 2) {                                                 // the larger lane (NaN: 0x7FFF), as f32 bits
+    const uint32_t hi = mb >> 16, lo = mb & 0xFFFFu;
+    mb = max(hi, lo) << 16;
+  }
+  mb = __reduce_max_sync(0xffffffffu, mb);
+  if ((threadIdx.x & 31) == 0) sh_amax[threadIdx.x >> 5] = mb;
   __syncthreads();
   const int nw = blockDim.x >> 5;
-  amax = (int)(threadIdx.x & 31) < nw ? sh_amax[threadIdx.x & 31] : 0.0f;
-  bad = (int)(threadIdx.x & 31) < nw ? sh_bad[threadIdx.x & 31] : 0;
-  amax = warp_max(amax);
-  bad = __any_sync(0xffffffffu, bad);
+  mb = (int)(threadIdx.x & 31) < nw ? sh_amax[threadIdx.x & 31] : 0u;
+  mb = __reduce_max_sync(0xffffffffu, mb);
+  const int bad = mb >= 0x7F800000u;
+  const float amax = bad ? 0.0f : __uint_as_float(mb);
   if (threadIdx.x == 0) finish_row(a, r, RowStat{0.0f, 0.0f, amax, bad});   // kFp8Scale reads amax and bad only
   const Fp8Fmt F = fp8_fmt(fmt);
   const float scale = amax > 0.0f ? __fdiv_rn(amax, F.max_val) : 1.0f;      // finish_row's value
+  float r_lo, r_hi;
+  const bool bracket = quotient_bracket(scale, r_lo, r_hi);
   uint2* out = reinterpret_cast<uint2*>(codes + r * cols);
 #pragma unroll
   for (int k = 0; k < NCH; ++k) {
     const int c = (int)threadIdx.x + k * (int)blockDim.x;
     if (FULL || c < chunks) {
+      float v[8];
+      raw[k].get(v);
       uint32_t lo = 0, hi = 0;
       if (rounding == 1) {   // the conversion saturates at +-max_val, which is what the clamp of the other path does
         uint32_t p[4];
+        if (bracket) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
-          p[j] = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v[k][2 * j], scale), __fdiv_rn(v[k][2 * j + 1], scale)),
-                                                    __NV_SATFINITE, fmt == 0 ? __NV_E4M3 : __NV_E5M2);
+          for (int j = 0; j < 4; ++j) p[j] = fp8x2_quotient_rne(v[2 * j], v[2 * j + 1], scale, r_lo, r_hi, fmt);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            p[j] = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v[2 * j], scale), __fdiv_rn(v[2 * j + 1], scale)),
+                                                      __NV_SATFINITE, fmt == 0 ? __NV_E4M3 : __NV_E5M2);
+        }
         lo = __byte_perm(p[0], p[1], 0x5410);
         hi = __byte_perm(p[2], p[3], 0x5410);
       } else {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
-          float q = __fdiv_rn(v[k][j], scale);
+          float q = __fdiv_rn(v[j], scale);
           q = q < -F.max_val ? -F.max_val : (q > F.max_val ? F.max_val : q);
           const uint32_t b = fp8_encode_ref_dev(q, F);
           if (j < 4) lo |= b << (8 * j); else hi |= b << (8 * (j - 4));
@@ -766,22 +832,23 @@ __global__ void __launch_bounds__(1024) fp8_quantize_rows_reg_kernel(const T* __
 
 template <typename T>
 int32_t fp8_quantize_rows_impl(b2q_handle h, const T* x, int64_t rows, int64_t cols, int fmt, int rounding,
-                               float* scales, uint8_t* codes) {
+                               float* scales, uint8_t* codes, int flag_nonfinite = 1) {
   if (rows <= 0 || cols <= 0) B2Q_FAIL(h, B2Q_ERR_EMPTY_INPUT, "fp8_quantize_rows: empty input");
   if (!x || !scales || !codes) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "fp8_quantize_rows: null pointer");
   if (fmt < 0 || fmt > 1 || rounding < 0 || rounding > 1) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "fp8_quantize_rows: bad format/rounding");
-  StatArgs a{kFp8Scale, 0, 0, fp8_fmt(fmt).max_val, scales, nullptr, h->d_status, 1};
-  if (cols % 8 == 0 && cols >= 256 && cols <= 16384 && rows <= 0x7FFFFFFF && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+  StatArgs a{kFp8Scale, 0, 0, fp8_fmt(fmt).max_val, scales, nullptr, h->d_status, flag_nonfinite};
+  if (cols % 8 == 0 && cols >= 256 && cols <= 65536 && rows <= 0x7FFFFFFF && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
       (reinterpret_cast<uintptr_t>(codes) & 7) == 0 && (rows >= 64 || cols <= 2048)) {
     const int64_t chunks = cols >> 3;
-    // 1, 2 or 4 chunks of 8 elements per thread; many rows prefer small CTAs (several per SM)
-    const int nch = chunks <= 128 ? 1 : (chunks <= 512 ? 2 : 4);
+    // 1, 2, 4 or 8 chunks of 8 elements per thread; many rows prefer small CTAs (several per SM)
+    const int nch = chunks <= 128 ? 1 : (chunks <= 512 ? 2 : (chunks <= 4096 ? 4 : 8));
     const int threads = (int)((ceil_div64(chunks, nch) + 31) / 32 * 32);
     const bool full = chunks == (int64_t)nch * threads;
 #define ROWS_LAUNCH(N, F) fp8_quantize_rows_reg_kernel<T, N, F><<<(unsigned)rows, threads, 0, h->stream>>>(x, cols, a, fmt, rounding, codes)
     if (nch == 1) { if (full) ROWS_LAUNCH(1, true); else ROWS_LAUNCH(1, false); }
     else if (nch == 2) { if (full) ROWS_LAUNCH(2, true); else ROWS_LAUNCH(2, false); }
-    else { if (full) ROWS_LAUNCH(4, true); else ROWS_LAUNCH(4, false); }
+    else if (nch == 4) { if (full) ROWS_LAUNCH(4, true); else ROWS_LAUNCH(4, false); }
+    else { if (full) ROWS_LAUNCH(8, true); else ROWS_LAUNCH(8, false); }
 #undef ROWS_LAUNCH
     B2Q_LAUNCH_CHECK(h, "fp8_quantize_rows_reg_kernel");
     return B2Q_OK;
@@ -895,6 +962,15 @@ int32_t b2q_fp8_quantize_rows_bf16(b2q_handle h, const void* x, int64_t rows, in
   B2Q_REQUIRE_HANDLE(h);
   return fp8_quantize_rows_impl<__nv_bfloat16>(h, (const __nv_bfloat16*)x, rows, cols, fmt, rounding, scales, codes);
 }
+
+}  // extern "C"
+// Rows of a scratch buffer of which only some hold results (the slots of a mixture-of-experts step; which ones is known
+// on the device only): the unused rows may hold anything, so non-finite input is not recorded as an error.
+int32_t b2q_fp8_quantize_rows_bf16_scratch(b2q_handle h, const void* x, int64_t rows, int64_t cols, int fmt, int rounding, float* scales,
+                                           uint8_t* codes) {
+  return fp8_quantize_rows_impl<__nv_bfloat16>(h, (const __nv_bfloat16*)x, rows, cols, fmt, rounding, scales, codes, 0);
+}
+extern "C" {
 
 int32_t b2q_fp4_block_quantize_f32(b2q_handle h, const float* x, int64_t n, int block, int format, int scale_format,
                                    uint8_t* packed, void* scales) {
@@ -1107,36 +1183,57 @@ __device__ __forceinline__ float swiglu_f32(float g, float u) { return __fdiv_rn
 
 // `split` > 1: a thread-block cluster of `split` CTAs shares a row (few rows, long rows: the decode step); each CTA
 // takes a contiguous slice of the columns and the slices' maxima are exchanged through distributed shared memory.
-__global__ void __launch_bounds__(1024) swiglu_quantize_rows_kernel(const __nv_bfloat16* __restrict__ gate,
-                                                                        const __nv_bfloat16* __restrict__ up, int64_t ld,
+// `inter`: gate and up are interleaved per 128 columns in one row of 2 * cols_all elements (hidden unit f: gate at
+// column 256 (f / 128) + f % 128, up 128 further; `up` is then gate + 128), the input is the f32 product and h is rounded
+// to bf16 before the row maximum and the encoding: the arithmetic of the GEMM epilogue that forms h for many tokens.
+template <typename TIn> __device__ __forceinline__ void load8_f32(const TIn* p, float (&v)[8]);
+template <> __device__ __forceinline__ void load8_f32<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 q = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { v[2 * j] = __uint_as_float(w[j] << 16); v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u); }
+}
+template <> __device__ __forceinline__ void load8_f32<float>(const float* p, float (&v)[8]) {
+  const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <typename TIn> __device__ __forceinline__ float in_as_f32(TIn v);
+template <> __device__ __forceinline__ float in_as_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float in_as_f32<float>(float v) { return v; }
+
+template <typename TIn>
+__global__ void __launch_bounds__(1024) swiglu_quantize_rows_kernel(const TIn* __restrict__ gate, const TIn* __restrict__ up, int64_t ld,
                                                                         int64_t cols_all, int fmt, int rounding, float* scales,
-                                                                        uint8_t* codes, int split) {
+                                                                        uint8_t* codes, int split, int inter) {
   const int64_t r = blockIdx.x / split;
   const int part = (int)(blockIdx.x % split);
   // slices are multiples of 8 columns so that the vector path keeps its alignment
   const int64_t slice = ((cols_all + split - 1) / split + 7) & ~(int64_t)7;
   const int64_t c_begin = min((int64_t)part * slice, cols_all), c_end = min(c_begin + slice, cols_all);
   const int64_t cols = c_end - c_begin;
-  const __nv_bfloat16* g = gate + r * ld + c_begin;
-  const __nv_bfloat16* u = up + r * ld + c_begin;
+  const TIn* g = gate + r * ld;
+  const TIn* u = up + r * ld;
+  auto at = [&](int64_t c) { const int64_t f = c_begin + c; return inter ? ((f >> 7) << 8) + (f & 127) : f; };   // column of unit c_begin + c
+  auto hval = [&](float gv, float uv) {
+    const float h = swiglu_f32(gv, uv);
+    return inter ? __bfloat162float(__float2bfloat16_rn(h)) : h;
+  };
   const Fp8Fmt F = fp8_fmt(fmt);
   __shared__ float sh[32];
   const int nthreads = (int)blockDim.x;                      // kThreads, or 1024 when there are few rows
   float amax = 0.0f;
-  const bool vec = (cols % 8 == 0) && (cols_all % 8 == 0) && (ld % 8 == 0) && ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up)) & 15) == 0;
+  const bool vec = (cols % 8 == 0) && (cols_all % 8 == 0) && (ld % 8 == 0) &&
+                   ((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up)) & (sizeof(TIn) * 8 - 1)) == 0;
   if (vec) {
     for (int64_t c = (int64_t)threadIdx.x * 8; c < cols; c += (int64_t)nthreads * 8) {
-      const uint4 gv = *reinterpret_cast<const uint4*>(g + c), uv = *reinterpret_cast<const uint4*>(u + c);
-      const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+      float gv[8], uv[8];
+      load8_f32<TIn>(g + at(c), gv);
+      load8_f32<TIn>(u + at(c), uv);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        amax = fmaxf(amax, fabsf(swiglu_f32(__uint_as_float(gw[j] << 16), __uint_as_float(uw[j] << 16))));
-        amax = fmaxf(amax, fabsf(swiglu_f32(__uint_as_float(gw[j] & 0xFFFF0000u), __uint_as_float(uw[j] & 0xFFFF0000u))));
-      }
+      for (int j = 0; j < 8; ++j) amax = fmaxf(amax, fabsf(hval(gv[j], uv[j])));
     }
   } else {
-    for (int64_t c = threadIdx.x; c < cols; c += nthreads)
-      amax = fmaxf(amax, fabsf(swiglu_f32(__bfloat162float(g[c]), __bfloat162float(u[c]))));
+    for (int64_t c = threadIdx.x; c < cols; c += nthreads) amax = fmaxf(amax, fabsf(hval(in_as_f32<TIn>(g[at(c)]), in_as_f32<TIn>(u[at(c)]))));
   }
   amax = warp_max(amax);
   if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = amax;
@@ -1161,28 +1258,29 @@ __global__ void __launch_bounds__(1024) swiglu_quantize_rows_kernel(const __nv_b
   uint8_t* out = codes + r * cols_all + c_begin;
   if (vec) {
     for (int64_t c = (int64_t)threadIdx.x * 8; c < cols; c += (int64_t)nthreads * 8) {
-      const uint4 gv = *reinterpret_cast<const uint4*>(g + c), uv = *reinterpret_cast<const uint4*>(u + c);
-      const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w}, uw[4] = {uv.x, uv.y, uv.z, uv.w};
+      float gv[8], uv[8];
+      load8_f32<TIn>(g + at(c), gv);
+      load8_f32<TIn>(u + at(c), uv);
       uint32_t lo = 0, hi = 0;
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const uint32_t c0 = enc(swiglu_f32(__uint_as_float(gw[j] << 16), __uint_as_float(uw[j] << 16)));
-        const uint32_t c1 = enc(swiglu_f32(__uint_as_float(gw[j] & 0xFFFF0000u), __uint_as_float(uw[j] & 0xFFFF0000u)));
-        const uint32_t pair = c0 | (c1 << 8);
-        if (j < 2) lo |= pair << (16 * j); else hi |= pair << (16 * (j - 2));
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t code = enc(hval(gv[j], uv[j]));
+        if (j < 4) lo |= code << (8 * j); else hi |= code << (8 * (j - 4));
       }
       *reinterpret_cast<uint2*>(out + c) = make_uint2(lo, hi);
     }
   } else {
-    for (int64_t c = threadIdx.x; c < cols; c += nthreads)
-      out[c] = (uint8_t)enc(swiglu_f32(__bfloat162float(g[c]), __bfloat162float(u[c])));
+    for (int64_t c = threadIdx.x; c < cols; c += nthreads) out[c] = (uint8_t)enc(hval(in_as_f32<TIn>(g[at(c)]), in_as_f32<TIn>(u[at(c)])));
   }
 }
 }  // namespace
 
-extern "C" int32_t b2q_swiglu_quantize_rows_bf16(b2q_handle h, const void* gate, const void* up, int64_t rows, int64_t cols,
-                                                 int64_t ld, int fmt, int rounding, float* scales, uint8_t* codes) {
-  B2Q_REQUIRE_HANDLE(h);
+// gate | up of one GEMM whose weight rows were interleaved per 128 (see b2q_interleave_rows128): gu [rows x 2 cols] f32.
+int32_t b2q_swiglu_quantize_rows_interleaved(b2q_handle h, const float* gu, int64_t rows, int64_t cols, int fmt, int rounding, float* scales,
+                                             uint8_t* codes);
+template <typename TIn>
+static int32_t swiglu_quantize_rows_launch(b2q_handle h, const TIn* gate, const TIn* up, int64_t rows, int64_t cols, int64_t ld, int fmt,
+                                           int rounding, float* scales, uint8_t* codes, int inter) {
   if (rows <= 0 || cols <= 0) B2Q_FAIL(h, B2Q_ERR_EMPTY_INPUT, "swiglu_quantize_rows: empty input");
   if (!gate || !up || !scales || !codes || ld < cols || fmt < 0 || fmt > 1 || rounding < 0 || rounding > 1)
     B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "swiglu_quantize_rows: bad argument");
@@ -1201,7 +1299,18 @@ extern "C" int32_t b2q_swiglu_quantize_rows_bf16(b2q_handle h, const void* gate,
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, swiglu_quantize_rows_kernel, (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, ld, cols, fmt,
-                                 rounding, scales, codes, split));
+  B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, swiglu_quantize_rows_kernel<TIn>, gate, up, ld, cols, fmt, rounding, scales, codes, split, inter));
   return B2Q_OK;
+}
+
+extern "C" int32_t b2q_swiglu_quantize_rows_bf16(b2q_handle h, const void* gate, const void* up, int64_t rows, int64_t cols,
+                                                 int64_t ld, int fmt, int rounding, float* scales, uint8_t* codes) {
+  B2Q_REQUIRE_HANDLE(h);
+  return swiglu_quantize_rows_launch<__nv_bfloat16>(h, (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, rows, cols, ld, fmt, rounding, scales,
+                                                    codes, 0);
+}
+int32_t b2q_swiglu_quantize_rows_interleaved(b2q_handle h, const float* gu, int64_t rows, int64_t cols, int fmt, int rounding, float* scales,
+                                             uint8_t* codes) {
+  if (cols % 128 != 0) B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "swiglu_quantize_rows: the interleaved layout needs a multiple of 128 columns, got %lld", (long long)cols);
+  return swiglu_quantize_rows_launch<float>(h, gu, gu ? gu + 128 : nullptr, rows, cols, 2 * cols, fmt, rounding, scales, codes, 1);
 }

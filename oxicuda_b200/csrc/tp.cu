@@ -18,7 +18,17 @@
 #include <dlfcn.h>
 #include <stdlib.h>
 
+int32_t b2q_fp8_quantize_rows_bf16_scratch(b2q_handle h, const void* x, int64_t rows, int64_t cols, int fmt, int rounding, float* scales,
+                                           uint8_t* codes);
+int32_t b2q_grouped_gemm_fp8_rows_act(b2q_handle h, const uint8_t* a, const float* scale_a, const uint8_t* w, const float* scale_w,
+                                      const int32_t* row_offsets, const int32_t* row_counts, int groups, int64_t capacity_rows, int64_t N, int64_t K,
+                                      int fmt, void* out, int out_type, int act);
+int32_t b2q_swiglu_quantize_rows_interleaved(b2q_handle h, const float* gu, int64_t rows, int64_t cols, int fmt, int rounding, float* scales,
+                                             uint8_t* codes);
 namespace tc {
+struct EpiArgs { float alpha, beta; const float* bias; int act; };
+int32_t gemm_fp8_impl(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt, const float* scale_a,
+                      int scale_a_kind, const float* scale_w, int scale_w_kind, void* out, int out_type, const EpiArgs* epi);
 int32_t gemm_fp8_scatter(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt, const float* scale_a,
                          const float* scale_w, const float* bias, void* const* inbox, int tp, int rank);
 }
@@ -243,6 +253,18 @@ __global__ void __launch_bounds__(256, 1) tp_reduce_gather_kernel(const Peers pe
   }
 }
 
+// Rows of a and b interleaved in blocks of `block` rows: out rows [2 j block, 2 j block + block) = a rows [j block, ...),
+// the next `block` rows the same rows of b; 16-byte pieces of the rows.
+__global__ void __launch_bounds__(256) interleave_rows_kernel(const uint4* __restrict__ a, const uint4* __restrict__ b, uint4* __restrict__ out,
+                                                              int64_t rows, int64_t row16, int64_t block) {
+  const int64_t total = 2 * rows * row16;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t orow = i / row16, c = i - orow * row16, blk = orow / (2 * block), in = orow - blk * 2 * block;
+    const int64_t src = blk * block + (in < block ? in : in - block);
+    out[i] = (in < block ? a : b)[src * row16 + c];
+  }
+}
+
 // y[t, c] += bias[c]  (bf16 rows, f32 bias)
 __global__ void __launch_bounds__(256) bias_add_bf16_kernel(__nv_bfloat16* __restrict__ y, const float* __restrict__ bias, int64_t rows, int64_t cols) {
   const int64_t total = rows * cols;
@@ -350,14 +372,6 @@ static int32_t scatter_reduce_cols(b2q_tp t, const uint8_t* x_codes, const float
   }
   return B2Q_OK;
 }
-// Waves of 256 x 256 tiles on the 74 CTA pairs of a B200, as the pair kernel schedules them (a last wave that fills at
-// most half of the pairs runs as half-width tiles and takes half a wave).
-static double gemm_waves(int64_t M, int64_t N) {
-  const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256), pairs = 74;
-  if (tiles <= pairs) return 1.0;
-  const int64_t rem = tiles % pairs;
-  return (double)(tiles / pairs) + (rem == 0 ? 0.0 : (2 * rem <= pairs ? 0.5 : 1.0));
-}
 // Shapes the scatter GEMM and the 16-byte units of the reduce kernel cover (nc: the columns of one chunk).
 static bool scatter_fits(int tp, int64_t tokens, int64_t nc, int64_t in_local) {
   return tokens > 128 && nc > 128 && tokens % (32 * tp) == 0 && nc % 8 == 0 && in_local % 16 == 0;
@@ -450,6 +464,10 @@ int32_t b2q_tp_create(b2q_handle h, void* nccl_comm, int tp, int rank, b2q_tp* o
   int prio_lo = 0, prio_hi = 0;
   cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi);
   bool ok = cudaStreamCreateWithPriority(&t->comm_stream, cudaStreamNonBlocking, prio_hi) == cudaSuccess;
+  // an SM keeps one shared-memory split while CTAs are resident: the sum-and-gather kernel asks for the split the GEMM
+  // CTAs run under (all of it shared), or it could not become resident beside them, nor they beside it
+  ok = ok && cudaFuncSetAttribute(tpx::tp_reduce_gather_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                  (int)cudaSharedmemCarveoutMaxShared) == cudaSuccess;
   for (int i = 0; i < 16 && ok; ++i) ok = cudaEventCreateWithFlags(&t->ev_ready[i], cudaEventDisableTiming) == cudaSuccess;
   ok = ok && cudaEventCreateWithFlags(&t->ev_done, cudaEventDisableTiming) == cudaSuccess;
   if (ok && tp > 1) {
@@ -535,14 +553,8 @@ int32_t b2q_tp_plan(int tp, int peers_attached, int64_t tokens, int64_t out_feat
     return B2Q_OK;
   }
   if (peers_attached && (size_t)n * 2 <= tpx::kBigMax && tpx::scatter_fits(tp, tokens, out_features, 16)) {
-    *mode = 4;
-    // column chunks of the GEMM (the sum-and-gather of chunk j runs under the GEMM of chunk j + 1): as many, up to 4,
-    // as leave the GEMM's tile waves unchanged
-    for (int c = 4; c >= 2; c /= 2) {
-      if (out_features % (256 * c) != 0 || !tpx::scatter_fits(tp, tokens, out_features / c, 16)) continue;
-      if (c * tpx::gemm_waves(tokens, out_features / c) <= tpx::gemm_waves(tokens, out_features) + 1e-9) { *chunks = c; break; }
-    }
-    return B2Q_OK;
+    *mode = 4;                    // one chunk: at tp = 2 the sum-and-gather kernel adds 30-40 us to a 64 MiB result, and
+    return B2Q_OK;                // a second GEMM launch plus the stream hand-over cost as much as overlapping half of it saves
   }
   *mode = 3;                      // one all-reduce after the GEMM measured fastest at tp = 2 and 4 (NCCL's CTAs wait for the
   return B2Q_OK;                  // persistent GEMM's SMs, so chunks do not overlap)
@@ -660,8 +672,39 @@ int32_t b2q_row_linear_forward_allreduce(b2q_tp t, const uint8_t* x_codes, const
 // row-parallel GEMM, sum over ranks.  y: bf16 [tokens x hidden], the same on every rank.
 int32_t b2q_mlp_swiglu_fp8_forward(b2q_tp t, const void* x_bf16, const uint8_t* w_gate_up, const float* s_gate_up, const uint8_t* w_down,
                                    const float* s_down, int64_t tokens, int64_t hidden, int64_t ffn_local, int rounding, void* y_bf16) {
+  return b2q_mlp_swiglu_fp8_forward_ex(t, x_bf16, w_gate_up, s_gate_up, w_down, s_down, tokens, hidden, ffn_local, rounding,
+                                       B2Q_GATE_UP_CONCATENATED, y_bf16);
+}
+
+// out (2 * rows x row_bytes) = rows of a and b interleaved per 128: the gate | up weight layout whose GEMM tiles hold both
+// projections of the same 128 hidden units (codes: row_bytes = in_features; scales: row_bytes = 4).
+int32_t b2q_interleave_rows128(b2q_handle h, const void* a, const void* b, int64_t rows, int64_t row_bytes, void* out) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (!a || !b || !out || rows <= 0 || row_bytes <= 0) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "interleave_rows128: bad argument");
+  if (rows % 128 != 0) B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "interleave_rows128: rows must be a multiple of 128, got %lld", (long long)rows);
+  if (row_bytes % 16 != 0 && row_bytes != 4) B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "interleave_rows128: rows of 4 bytes or a multiple of 16 bytes");
+  if (((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) | reinterpret_cast<uintptr_t>(out)) & 15) != 0)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "interleave_rows128: 16-byte aligned pointers");
+  // 128 four-byte rows are one 512-byte row of a matrix interleaved per single row
+  const int64_t krows = row_bytes == 4 ? rows / 128 : rows, row16 = row_bytes == 4 ? 32 : row_bytes / 16, block = row_bytes == 4 ? 1 : 128;
+  const int64_t total = 2 * krows * row16;
+  int grid = (int)((total + 255) / 256);
+  if (grid > h->sm_count * 16) grid = h->sm_count * 16;
+  tpx::interleave_rows_kernel<<<grid, 256, 0, h->stream>>>((const uint4*)a, (const uint4*)b, (uint4*)out, krows, row16, block);
+  B2Q_LAUNCH_CHECK(h, "interleave_rows_kernel");
+  return B2Q_OK;
+}
+
+int32_t b2q_mlp_swiglu_fp8_forward_ex(b2q_tp t, const void* x_bf16, const uint8_t* w_gate_up, const float* s_gate_up, const uint8_t* w_down,
+                                      const float* s_down, int64_t tokens, int64_t hidden, int64_t ffn_local, int rounding, int gate_up_layout,
+                                      void* y_bf16) {
   B2Q_REQUIRE_TP(t);
   b2q_handle h = t->h;
+  if (gate_up_layout != B2Q_GATE_UP_CONCATENATED && gate_up_layout != B2Q_GATE_UP_INTERLEAVED128)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "mlp_swiglu_fp8_forward: unknown gate | up layout %d", gate_up_layout);
+  if (gate_up_layout == B2Q_GATE_UP_INTERLEAVED128 && ffn_local % 128 != 0)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "mlp_swiglu_fp8_forward: the interleaved layout needs ffn_local %% 128 == 0, got %lld", (long long)ffn_local);
+  const bool inter = gate_up_layout == B2Q_GATE_UP_INTERLEAVED128;
   if (tokens <= 0 || hidden <= 0 || ffn_local <= 0)
     B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "mlp_swiglu_fp8_forward: dimensions must be non-zero: tokens=%lld, hidden=%lld, ffn=%lld",
              (long long)tokens, (long long)hidden, (long long)ffn_local);
@@ -674,7 +717,7 @@ int32_t b2q_mlp_swiglu_fp8_forward(b2q_tp t, const void* x_bf16, const uint8_t* 
   const int64_t F = ffn_local;
   // scratch: x codes + scales (all tokens), then per chunk: gate|up bf16, h codes + scales, fp32 partial (peer modes)
   const size_t o_xc = 0, o_xs = o_xc + tpx::align256((size_t)tokens * hidden), o_gu = o_xs + tpx::align256((size_t)tokens * 4),
-               o_hc = o_gu + tpx::align256((size_t)ct * 2 * F * 2), o_hs = o_hc + tpx::align256((size_t)ct * F),
+               o_hc = o_gu + tpx::align256((size_t)ct * 2 * F * (ct <= 128 ? 4 : 2)), o_hs = o_hc + tpx::align256((size_t)ct * F),
                o_pf = o_hs + tpx::align256((size_t)ct * 4),
                total = o_pf + ((mode == 1 || mode == 2) ? tpx::align256((size_t)tokens * hidden * 4) : 0);
   uint8_t* ws = nullptr;
@@ -687,11 +730,29 @@ int32_t b2q_mlp_swiglu_fp8_forward(b2q_tp t, const void* x_bf16, const uint8_t* 
   for (int c = 0; c < chunks; ++c) {
     const uint8_t* xcc = xc + (size_t)c * ct * hidden;
     uint8_t* yc = reinterpret_cast<uint8_t*>(y_bf16) + (size_t)c * ct * hidden * 2;
-    st = b2q_gemm_fp8(h, xcc, w_gate_up, ct, 2 * F, hidden, B2Q_FP8_E4M3, xs + c * ct, B2Q_SCALE_PER_ROW, s_gate_up, B2Q_SCALE_PER_ROW, gu,
-                      B2Q_OUT_BF16);
-    if (st != B2Q_OK) return st;
-    st = b2q_swiglu_quantize_rows_bf16(h, gu, gu + (size_t)F * 2, ct, F, 2 * F, B2Q_FP8_E4M3, rounding, hs, hc);
-    if (st != B2Q_OK) return st;
+    if (inter && ct > 128) {
+      // prefill: SwiGLU in the GEMM epilogue (the gate | up product never reaches memory), then the row quantizer over h
+      const tc::EpiArgs e{1.0f, 0.0f, nullptr, 3};
+      st = tc::gemm_fp8_impl(h, xcc, w_gate_up, ct, 2 * F, hidden, B2Q_FP8_E4M3, xs + c * ct, B2Q_SCALE_PER_ROW, s_gate_up, B2Q_SCALE_PER_ROW,
+                             gu, B2Q_OUT_BF16, &e);
+      if (st != B2Q_OK) return st;
+      st = b2q_fp8_quantize_rows_bf16(h, gu, ct, F, B2Q_FP8_E4M3, rounding, hs, hc);
+      if (st != B2Q_OK) return st;
+    } else if (inter) {
+      // few tokens: the f32 product of the interleaved rows, then h = bf16(silu(gate) * up) and its codes in one kernel
+      // (the arithmetic of the epilogue above, so a layer gives the same numbers whatever the token count)
+      st = b2q_gemm_fp8(h, xcc, w_gate_up, ct, 2 * F, hidden, B2Q_FP8_E4M3, xs + c * ct, B2Q_SCALE_PER_ROW, s_gate_up, B2Q_SCALE_PER_ROW, gu,
+                        B2Q_OUT_F32);
+      if (st != B2Q_OK) return st;
+      st = b2q_swiglu_quantize_rows_interleaved(h, (const float*)gu, ct, F, B2Q_FP8_E4M3, rounding, hs, hc);
+      if (st != B2Q_OK) return st;
+    } else {
+      st = b2q_gemm_fp8(h, xcc, w_gate_up, ct, 2 * F, hidden, B2Q_FP8_E4M3, xs + c * ct, B2Q_SCALE_PER_ROW, s_gate_up, B2Q_SCALE_PER_ROW, gu,
+                        B2Q_OUT_BF16);
+      if (st != B2Q_OK) return st;
+      st = b2q_swiglu_quantize_rows_bf16(h, gu, gu + (size_t)F * 2, ct, F, 2 * F, B2Q_FP8_E4M3, rounding, hs, hc);
+      if (st != B2Q_OK) return st;
+    }
     if (mode == 4) {
       for (int j = 0; j < col_chunks; ++j)
         if ((st = tpx::scatter_reduce_cols(t, hc, hs, w_down, s_down, nullptr, ct, F, hidden, yc, j, col_chunks)) != B2Q_OK) return st;
@@ -721,8 +782,19 @@ int32_t b2q_mlp_swiglu_fp8_forward(b2q_tp t, const void* x_bf16, const uint8_t* 
 int32_t b2q_moe_forward(b2q_tp t, const void* x_bf16, const float* logits, const uint8_t* w_gate_up, const float* s_gate_up,
                         const uint8_t* w_down, const float* s_down, int64_t tokens, int64_t hidden, int64_t ffn, int n_experts, int top_k,
                         int rounding, void* y_bf16, int32_t* counts_out) {
+  return b2q_moe_forward_ex(t, x_bf16, logits, w_gate_up, s_gate_up, w_down, s_down, tokens, hidden, ffn, n_experts, top_k, rounding,
+                            B2Q_GATE_UP_CONCATENATED, y_bf16, counts_out);
+}
+
+int32_t b2q_moe_forward_ex(b2q_tp t, const void* x_bf16, const float* logits, const uint8_t* w_gate_up, const float* s_gate_up,
+                           const uint8_t* w_down, const float* s_down, int64_t tokens, int64_t hidden, int64_t ffn, int n_experts, int top_k,
+                           int rounding, int gate_up_layout, void* y_bf16, int32_t* counts_out) {
   B2Q_REQUIRE_TP(t);
   b2q_handle h = t->h;
+  if (gate_up_layout != B2Q_GATE_UP_CONCATENATED && gate_up_layout != B2Q_GATE_UP_INTERLEAVED128)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "moe_forward: unknown gate | up layout %d", gate_up_layout);
+  if (gate_up_layout == B2Q_GATE_UP_INTERLEAVED128 && ffn % 128 != 0)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "moe_forward: the interleaved layout needs ffn %% 128 == 0, got %lld", (long long)ffn);
   if (tokens <= 0 || hidden <= 0 || ffn <= 0)
     B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "moe_forward: dimensions must be non-zero: tokens=%lld, hidden=%lld, ffn=%lld", (long long)tokens,
              (long long)hidden, (long long)ffn);
@@ -751,10 +823,18 @@ int32_t b2q_moe_forward(b2q_tp t, const void* x_bf16, const float* logits, const
   if ((st = b2q_moe_assign_slots(h, idx, pairs, first, n_local, cnt, off, slot)) != B2Q_OK) return st;
   if (counts_out) B2Q_CUDA(h, cudaMemcpyAsync(counts_out, cnt, (size_t)n_local * 4, cudaMemcpyDeviceToDevice, h->stream));
   if ((st = b2q_moe_scatter(h, x_bf16, slot, pairs, top_k, hidden * 2, xb)) != B2Q_OK) return st;
-  if ((st = b2q_fp8_quantize_rows_bf16(h, xb, cap, hidden, B2Q_FP8_E4M3, rounding, xs, xc)) != B2Q_OK) return st;
-  if ((st = b2q_grouped_gemm_fp8_rows(h, xc, xs, w_gate_up, s_gate_up, off, cnt, n_local, cap, 2 * F, hidden, B2Q_FP8_E4M3, gu, B2Q_OUT_BF16)) != B2Q_OK)
-    return st;
-  if ((st = b2q_swiglu_quantize_rows_bf16(h, gu, gu + (size_t)F * 2, cap, F, 2 * F, B2Q_FP8_E4M3, rounding, hs, hc)) != B2Q_OK) return st;
+  if ((st = b2q_fp8_quantize_rows_bf16_scratch(h, xb, cap, hidden, B2Q_FP8_E4M3, rounding, xs, xc)) != B2Q_OK) return st;
+  if (gate_up_layout == B2Q_GATE_UP_INTERLEAVED128) {
+    // silu(gate) * up in the epilogue of the grouped GEMM: gu receives h [cap x F] bf16
+    if ((st = b2q_grouped_gemm_fp8_rows_act(h, xc, xs, w_gate_up, s_gate_up, off, cnt, n_local, cap, 2 * F, hidden, B2Q_FP8_E4M3, gu, B2Q_OUT_BF16,
+                                            3)) != B2Q_OK)
+      return st;
+    if ((st = b2q_fp8_quantize_rows_bf16_scratch(h, gu, cap, F, B2Q_FP8_E4M3, rounding, hs, hc)) != B2Q_OK) return st;
+  } else {
+    if ((st = b2q_grouped_gemm_fp8_rows(h, xc, xs, w_gate_up, s_gate_up, off, cnt, n_local, cap, 2 * F, hidden, B2Q_FP8_E4M3, gu, B2Q_OUT_BF16)) != B2Q_OK)
+      return st;
+    if ((st = b2q_swiglu_quantize_rows_bf16(h, gu, gu + (size_t)F * 2, cap, F, 2 * F, B2Q_FP8_E4M3, rounding, hs, hc)) != B2Q_OK) return st;
+  }
   if ((st = b2q_grouped_gemm_fp8_rows(h, hc, hs, w_down, s_down, off, cnt, n_local, cap, hidden, F, B2Q_FP8_E4M3, yb, B2Q_OUT_BF16)) != B2Q_OK) return st;
   if ((st = b2q_ep_token_gather_bf16(h, yb, slot, wgt, tokens, top_k, hidden, y_bf16)) != B2Q_OK) return st;
   if (t->tp > 1) B2Q_NCCL(h, tpx::nccl()->AllReduce(y_bf16, y_bf16, (size_t)tokens * hidden, tpx::kNcclBfloat16, tpx::kNcclSum, t->comm, h->stream));

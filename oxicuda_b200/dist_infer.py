@@ -252,6 +252,7 @@ class TpFp8Mlp:
         self.gate_up = Fp8Linear(torch.cat([w_gate[r0:r1], w_up[r0:r1]], dim=0), rounding)   # [2*ffn/tp x hidden]
         self.down = Fp8Linear(w_down[:, c0:c1].contiguous(), rounding)                          # [hidden x ffn/tp]
         self.codec = Fp8Codec.e4m3(rounding)
+        self._interleave()
 
     @classmethod
     def from_shards(cls, w_gate_shard: torch.Tensor, w_up_shard: torch.Tensor, w_down_shard: torch.Tensor,
@@ -263,7 +264,23 @@ class TpFp8Mlp:
         self.gate_up = Fp8Linear(torch.cat([w_gate_shard, w_up_shard], dim=0), rounding)
         self.down = Fp8Linear(w_down_shard.contiguous(), rounding)
         self.codec = Fp8Codec.e4m3(rounding)
+        self._interleave()
         return self
+
+    def _interleave(self):
+        """Load-time step: the gate and up rows (codes and scales) interleaved per 128 rows (b2q_interleave_rows128), the
+        layout whose GEMM tiles hold both projections of the same hidden units so that forward() forms silu(gate) * up in
+        the GEMM epilogue.  Shards whose width is not a multiple of 128 keep the concatenated layout."""
+        from ._lib import default_handle, ptr
+        F = self.local_ffn
+        self.gu_codes = self.gu_scales = None
+        if F % 128 != 0 or self.hidden % 16 != 0:
+            return
+        codes, scales = self.gate_up.codes, self.gate_up.scales
+        self.gu_codes, self.gu_scales = torch.empty_like(codes), torch.empty_like(scales)
+        h = default_handle()
+        h.call("b2q_interleave_rows128", ptr(codes), ptr(codes[F:]), F, self.hidden, ptr(self.gu_codes))
+        h.call("b2q_interleave_rows128", ptr(scales), ptr(scales[F:]), F, 4, ptr(self.gu_scales))
 
     def forward_partial(self, x: torch.Tensor) -> torch.Tensor:
         """x bf16 [tokens x hidden] (replicated) -> this rank's partial of the output, bf16 [tokens x hidden]
@@ -271,8 +288,13 @@ class TpFp8Mlp:
         from ._lib import default_handle, ptr
         tokens = x.shape[0]
         xc, xs = self.codec.quantize_rows(x, tokens, self.hidden)
-        gu = self.gate_up.forward(xc.view(tokens, self.hidden), xs)              # bf16 [tokens x 2F]: gate | up
         F = self.local_ffn
+        if self.gu_codes is not None:                                            # interleaved layout: h leaves the GEMM epilogue as bf16
+            from .blas import EpilogueOp, gemm_fp8_ex
+            h = gemm_fp8_ex(xc.view(tokens, self.hidden), self.gu_codes, xs, self.gu_scales, epilogue=EpilogueOp.SwiGluPairs)
+            hc, hs = self.codec.quantize_rows(h, tokens, F)
+            return self.down.forward(hc.view(tokens, F), hs)
+        gu = self.gate_up.forward(xc.view(tokens, self.hidden), xs)              # bf16 [tokens x 2F]: gate | up
         hc = torch.empty(tokens, F, dtype=torch.uint8, device=x.device)
         hs = torch.empty(tokens, dtype=torch.float32, device=x.device)
         default_handle().call("b2q_swiglu_quantize_rows_bf16", ptr(gu), ptr(gu[:, F:]), tokens, F, 2 * F,
@@ -282,9 +304,11 @@ class TpFp8Mlp:
     def forward(self, x: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
         tokens = x.shape[0]
         y = out if out is not None else torch.empty(tokens, self.hidden, dtype=torch.bfloat16, device=x.device)
-        tp_group(self.handle).call("b2q_mlp_swiglu_fp8_forward", L.ptr(x), L.ptr(self.gate_up.codes), L.ptr(self.gate_up.scales),
-                                   L.ptr(self.down.codes), L.ptr(self.down.scales), tokens, self.hidden, self.local_ffn,
-                                   self.codec.rounding, L.ptr(y))
+        inter = self.gu_codes is not None
+        tp_group(self.handle).call("b2q_mlp_swiglu_fp8_forward_ex", L.ptr(x), L.ptr(self.gu_codes if inter else self.gate_up.codes),
+                                   L.ptr(self.gu_scales if inter else self.gate_up.scales), L.ptr(self.down.codes), L.ptr(self.down.scales),
+                                   tokens, self.hidden, self.local_ffn, self.codec.rounding,
+                                   L.GATE_UP_INTERLEAVED128 if inter else L.GATE_UP_CONCATENATED, L.ptr(y))
         return y
 
 
@@ -344,6 +368,16 @@ class MoeFp8Layer:
         gate_up = [Fp8Linear(torch.cat([w1, w3], dim=0), rounding) for (w1, w3, _) in experts]
         down = [Fp8Linear(w2.contiguous(), rounding) for (_, _, w2) in experts]
         # the experts' codes and scales stacked: [E/ep][2*ffn][hidden] and [E/ep][hidden][ffn], the grouped GEMM's operand
+        # gate and up rows interleaved per 128 where the width allows it (the SwiGLU epilogue of the grouped GEMM)
+        self.interleaved = self.ffn % 128 == 0 and self.hidden % 16 == 0
+        if self.interleaved:
+            from ._lib import default_handle, ptr
+            F, hd = self.ffn, default_handle()
+            for g in gate_up:
+                codes, scales = torch.empty_like(g.codes), torch.empty_like(g.scales)
+                hd.call("b2q_interleave_rows128", ptr(g.codes), ptr(g.codes[F:]), F, self.hidden, ptr(codes))
+                hd.call("b2q_interleave_rows128", ptr(g.scales), ptr(g.scales[F:]), F, 4, ptr(scales))
+                g.codes, g.scales = codes, scales
         self.gate_up_codes = torch.stack([g.codes for g in gate_up]).contiguous()
         self.gate_up_scales = torch.cat([g.scales for g in gate_up]).contiguous()
         self.down_codes = torch.stack([d.codes for d in down]).contiguous()
@@ -361,7 +395,8 @@ class MoeFp8Layer:
         lg = logits.reshape(tokens, self.n_experts).float().contiguous()
         if self.last_counts is None:
             self.last_counts = torch.zeros(self.local, dtype=torch.int32, device=x.device)
-        tp_group(self._group_handle).call("b2q_moe_forward", L.ptr(x), L.ptr(lg), L.ptr(self.gate_up_codes), L.ptr(self.gate_up_scales),
+        tp_group(self._group_handle).call("b2q_moe_forward_ex", L.ptr(x), L.ptr(lg), L.ptr(self.gate_up_codes), L.ptr(self.gate_up_scales),
                                           L.ptr(self.down_codes), L.ptr(self.down_scales), tokens, self.hidden, self.ffn, self.n_experts,
-                                          self.top_k, self.codec.rounding, L.ptr(y), L.ptr(self.last_counts))
+                                          self.top_k, self.codec.rounding,
+                                          L.GATE_UP_INTERLEAVED128 if self.interleaved else L.GATE_UP_CONCATENATED, L.ptr(y), L.ptr(self.last_counts))
         return y

@@ -242,3 +242,44 @@ def test_epilogue_ops_alpha_beta_bias_and_kn_layout(cuda, oracle, M, N, K):
     check(got, plain, 2e-3)
     with pytest.raises(Exception):
         gemm_fp8_ex(ac, wc, sa, sw, epilogue=EpilogueOp.LinearCombinationBias)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(512, 1024, 512), (300, 512, 256), (48, 512, 512), (4096, 2048, 1024)])
+def test_epilogue_swiglu_pairs(cuda, oracle, M, N, K):
+    """EpilogueOp.SwiGluPairs: the gate | up GEMM over rows interleaved per 128 (b2q_interleave_rows128) writes
+    silu(gate) * up [M x N / 2] (SwiGluExpert::forward, crates/oxicuda-moe/src/expert/ffn.rs:208-243; silu of
+    crates/oxicuda-lm/src/layer/ffn.rs:25-27) from the epilogue of the two-CTA kernel (M > 128) or after the few-token
+    kernels (M = 48); checked against the oracle's f32 GEMM of the gate and of the up rows."""
+    from oxicuda_b200._lib import default_handle, ptr
+    from oxicuda_b200.blas import EpilogueOp, gemm_fp8_ex
+    from oxicuda_b200.quant import Fp8Codec
+    rng = np.random.default_rng(M + N + K + 3)
+    F = N // 2
+    a = rng.standard_normal((M, K)).astype(np.float32)
+    wg = (rng.standard_normal((F, K)) * 0.08).astype(np.float32)
+    wu = (rng.standard_normal((F, K)) * 0.08).astype(np.float32)
+    codec = Fp8Codec.e4m3("rne")
+    t = lambda x: torch.from_numpy(np.ascontiguousarray(x)).to(cuda)
+    ac, sa = codec.quantize_rows(t(a), M, K)
+    gc, gs = codec.quantize_rows(t(wg), F, K)
+    uc, us = codec.quantize_rows(t(wu), F, K)
+    ac = ac.view(M, K)
+    wc = torch.empty(N, K, dtype=torch.uint8, device=cuda)
+    sw = torch.empty(N, dtype=torch.float32, device=cuda)
+    h = default_handle()
+    h.call("b2q_interleave_rows128", ptr(gc), ptr(uc), F, K, ptr(wc))
+    h.call("b2q_interleave_rows128", ptr(gs), ptr(us), F, 4, ptr(sw))
+    # the interleaved layout itself: block j of 256 rows = gate rows [128 j, ...) then up rows [128 j, ...)
+    exp_codes = torch.stack([gc.view(F // 128, 128, K), uc.view(F // 128, 128, K)], dim=1).reshape(N, K)
+    exp_scales = torch.stack([gs.view(F // 128, 128), us.view(F // 128, 128)], dim=1).reshape(N)
+    assert torch.equal(wc, exp_codes) and torch.equal(sw, exp_scales)
+    f32 = lambda c, s: np.asarray(oracle.gemm_fp8(ac.cpu().numpy(), c.view(F, K).cpu().numpy(), sa.cpu().numpy(), s.cpu().numpy(), 0, 1, "f32"),
+                                  np.float64).reshape(M, F)
+    g, u = f32(gc, gs), f32(uc, us)
+    ref = g / (1.0 + np.exp(-g)) * u
+    got = gemm_fp8_ex(ac, wc, sa, sw, epilogue=EpilogueOp.SwiGluPairs)
+    h.check()
+    assert got.shape == (M, F)
+    rms = np.sqrt((ref ** 2).mean()) + 1e-30
+    assert float((np.abs(got.double().cpu().numpy() - ref) / (np.abs(ref) + rms)).max()) <= 1e-2

@@ -40,8 +40,10 @@ def oracle_moe(oracle, x, logits, experts, top_k):
         xe = x[toks]
         xc, xs, _ = oracle.fp8_quantize_rows(xe, toks.size, hidden, 0, 1)
         wc, ws, _ = oracle.fp8_quantize_rows(np.concatenate([w1, w3], 0), 2 * F, hidden, 0, 1)
-        gu = oracle.gemm_fp8(xc.reshape(-1, hidden), wc.reshape(2 * F, hidden), xs, ws, 0, 1, "bf16")
-        hh = oracle.swiglu(gu[:, :F], gu[:, F:])
+        inter = F % 128 == 0 and hidden % 16 == 0            # MoeFp8Layer then holds every expert's gate | up rows interleaved per 128
+        if inter:
+            wc, ws = oracle.interleave_rows128(wc.reshape(2 * F, hidden)[:F], wc.reshape(2 * F, hidden)[F:]), oracle.interleave_rows128(ws[:F], ws[F:])
+        hh = oracle.swiglu_mlp_hidden(xc, xs, wc, ws, toks.size, hidden, F, inter)
         hc, hs, _ = oracle.fp8_quantize_rows(hh, toks.size, F, 0, 1)
         w2c, w2s, _ = oracle.fp8_quantize_rows(w2, hidden, F, 0, 1)
         y = oracle.gemm_fp8(hc.reshape(-1, F), w2c.reshape(hidden, F), hs, w2s, 0, 1, "bf16")
@@ -184,9 +186,8 @@ def test_mixtral_shaped_moe_at_stated_size(cuda, oracle):
             continue
         xe = xs_f[rows]
         xc, xsc, _ = oracle.fp8_quantize_rows(xe, len(rows), hidden, 0, 1)
-        gu = oracle.gemm_fp8(xc.reshape(-1, hidden), layer.gate_up_codes[e].cpu().numpy(), xsc,
-                             layer.gate_up_scales[e * 2 * F:(e + 1) * 2 * F].cpu().numpy(), 0, 1, "bf16")
-        hh = oracle.swiglu(gu[:, :F], gu[:, F:])
+        hh = oracle.swiglu_mlp_hidden(xc, xsc, layer.gate_up_codes[e].cpu().numpy(), layer.gate_up_scales[e * 2 * F:(e + 1) * 2 * F].cpu().numpy(),
+                                      len(rows), hidden, F, layer.interleaved)
         hc, hs, _ = oracle.fp8_quantize_rows(hh, len(rows), F, 0, 1)
         ye = oracle.gemm_fp8(hc.reshape(-1, F), layer.down_codes[e].cpu().numpy(), hs, layer.down_scales[e * hidden:(e + 1) * hidden].cpu().numpy(),
                              0, 1, "bf16")

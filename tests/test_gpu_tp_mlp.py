@@ -33,8 +33,10 @@ def oracle_mlp(oracle, x_bf16_as_f32, wg, wu, wd, tp):
     for r in range(tp):
         wgu = np.concatenate([wg[r * F:(r + 1) * F], wu[r * F:(r + 1) * F]], axis=0)
         wc, ws, _ = oracle.fp8_quantize_rows(wgu, 2 * F, hidden, 0, 1)
-        gu = oracle.gemm_fp8(xc, wc.reshape(2 * F, hidden), xs, ws, 0, 1, "bf16")
-        h = oracle.swiglu(gu[:, :F], gu[:, F:])
+        inter = F % 128 == 0 and hidden % 16 == 0            # TpFp8Mlp then holds the gate | up shard interleaved per 128 rows
+        if inter:
+            wc, ws = oracle.interleave_rows128(wc.reshape(2 * F, hidden)[:F], wc.reshape(2 * F, hidden)[F:]), oracle.interleave_rows128(ws[:F], ws[F:])
+        h = oracle.swiglu_mlp_hidden(xc, xs, wc, ws, tokens, hidden, F, inter)
         hc, hs, _ = oracle.fp8_quantize_rows(h, tokens, F, 0, 1)
         wdc, wds, _ = oracle.fp8_quantize_rows(np.ascontiguousarray(wd[:, r * F:(r + 1) * F]), hidden, F, 0, 1)
         part = _bf16_round(oracle.gemm_fp8(hc.reshape(tokens, F), wdc.reshape(hidden, F), hs, wds, 0, 1, "f32"))
@@ -91,8 +93,9 @@ def test_mlp_at_stated_size_hidden8192_ffn28672(cuda, oracle, tokens):
         total = None
         for sh in shards:
             F = sh.local_ffn
-            gu = oracle.gemm_fp8(xc.reshape(tokens, hidden), sh.gate_up.codes.cpu().numpy(), xs, sh.gate_up.scales.cpu().numpy(), 0, 1, "bf16")
-            h = oracle.swiglu(gu[:, :F], gu[:, F:])
+            inter = sh.gu_codes is not None
+            h = oracle.swiglu_mlp_hidden(xc, xs, (sh.gu_codes if inter else sh.gate_up.codes).cpu().numpy(),
+                                         (sh.gu_scales if inter else sh.gate_up.scales).cpu().numpy(), tokens, hidden, F, inter)
             hc, hs, _ = oracle.fp8_quantize_rows(h, tokens, F, 0, 1)
             part = _bf16_round(oracle.gemm_fp8(hc.reshape(tokens, F), sh.down.codes.cpu().numpy(), hs, sh.down.scales.cpu().numpy(), 0, 1, "f32"))
             total = part if total is None else _bf16_round(total + part)

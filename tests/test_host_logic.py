@@ -199,3 +199,48 @@ def test_rust_bindings_cover_the_header(libb2q):
     before = src
     subprocess.run([sys.executable, str(root / "rust" / "b2q-sys" / "gen_ffi.py")], check=True, capture_output=True)
     assert (root / "rust" / "b2q-sys" / "src" / "lib.rs").read_text() == before
+
+
+def test_tp_boundary_plan(libb2q):
+    """b2q_tp_plan (a pure host function): which row-parallel boundary a result of tokens x out_features takes."""
+    def plan(tp, attached, tokens, out):
+        mode, chunks = C.c_int(-1), C.c_int(-1)
+        assert libb2q.b2q_tp_plan(tp, attached, C.c_int64(tokens), C.c_int64(out), C.byref(mode), C.byref(chunks)) == 0
+        return mode.value, chunks.value
+    assert plan(1, 1, 4096, 8192) == (0, 1)                      # one rank: no boundary
+    assert plan(2, 1, 1, 8192) == (1, 1)                         # 32 KiB of fp32 partials: one-shot peer kernel
+    assert plan(8, 1, 8, 8192) == (1, 1)                         # 256 KiB: still one-shot
+    assert plan(2, 1, 64, 8192) == (2, 1)                        # 2 MiB: two-shot peer kernel
+    assert plan(8, 1, 128, 8192) == (2, 1)                       # 4 MiB: the last two-shot size
+    assert plan(8, 1, 4096, 8192) == (4, 1)                      # 64 MiB bf16: reduce-scatter inside the GEMM epilogue
+    assert plan(2, 1, 2048, 768) == (4, 1)
+    assert plan(2, 1, 4090, 8192)[0] == 3                        # rows do not split into 32-row blocks per rank: NCCL
+    assert plan(8, 1, 8192, 8192)[0] == 3                        # 128 MiB: beyond the exchange buffer
+    assert plan(2, 0, 64, 8192)[0] == 3 and plan(2, 0, 4096, 8192)[0] == 3   # no peer mappings: NCCL
+    mode, chunks = C.c_int(), C.c_int()
+    assert libb2q.b2q_tp_plan(0, 1, C.c_int64(1), C.c_int64(1), C.byref(mode), C.byref(chunks)) != 0
+    assert libb2q.b2q_tp_plan(2, 1, C.c_int64(0), C.c_int64(8), C.byref(mode), C.byref(chunks)) != 0
+
+
+def test_oracle_mlp_hidden_layouts(oracle):
+    """oracle/api.py::swiglu_mlp_hidden: the interleaved statement equals the concatenated one up to where h is rounded
+    (f32 gate | up and bf16 h against bf16 gate | up and f32 h), and interleave_rows128 is the layout of the header."""
+    import numpy as np
+    rng = np.random.default_rng(3)
+    tokens, hidden, F = 5, 64, 256
+    x = rng.standard_normal((tokens, hidden)).astype(np.float32)
+    wg = (rng.standard_normal((F, hidden)) * 0.1).astype(np.float32)
+    wu = (rng.standard_normal((F, hidden)) * 0.1).astype(np.float32)
+    xc, xs, _ = oracle.fp8_quantize_rows(x, tokens, hidden, 0, 1)
+    gc, gs, _ = oracle.fp8_quantize_rows(wg, F, hidden, 0, 1)
+    uc, us, _ = oracle.fp8_quantize_rows(wu, F, hidden, 0, 1)
+    gc, uc = gc.reshape(F, hidden), uc.reshape(F, hidden)
+    wi, si = oracle.interleave_rows128(gc, uc), oracle.interleave_rows128(gs, us)
+    assert wi.shape == (2 * F, hidden) and si.shape == (2 * F,)
+    assert np.array_equal(wi[:128], gc[:128]) and np.array_equal(wi[128:256], uc[:128]) and np.array_equal(wi[256:384], gc[128:])
+    assert np.array_equal(si[128:256], us[:128])
+    h_cat = oracle.swiglu_mlp_hidden(xc, xs, np.concatenate([gc, uc]), np.concatenate([gs, us]), tokens, hidden, F, False)
+    h_int = oracle.swiglu_mlp_hidden(xc, xs, wi, si, tokens, hidden, F, True)
+    scale = np.abs(h_cat).max()
+    assert np.abs(h_cat - h_int).max() <= 2.0 ** -6 * scale      # a few bf16 roundings apart
+    assert np.array_equal(oracle.bf16_bits_to_f32(oracle.f32_to_bf16_bits(h_int)).reshape(h_int.shape), h_int)   # h_int is bf16
