@@ -437,6 +437,14 @@ int32_t b2q_moe_forward(b2q_tp t, const void* x_bf16, const float* logits, const
                         int top_k, int rounding, void* y_bf16, int32_t* counts_out);
 /* The same with the layout of every expert's gate | up block stated (see b2q_mlp_swiglu_fp8_forward_ex): with
  * B2Q_GATE_UP_INTERLEAVED128 (ffn % 128 == 0) silu(gate) * up is formed in the epilogue of the grouped GEMM. */
+/* The layer over block-scaled FP4 experts (config 5's FP4 runs): c_gate_up [E/ep][2 * ffn][hidden / 2] and c_down
+ * [E/ep][hidden][ffn / 2] are E2M1 codes (PackedFp4 bytes), s_* one E8M0 byte per 32 codes along K
+ * (MicroScalingQuantizer, fp4_fp6_ops.rs:746-898, with the power-of-two scale rule of b2q_fp4_block_quantize_f32); gate rows
+ * then up rows per expert.  Both grouped GEMMs are ONE launch each of the tcgen05 block-scaled kernel
+ * (b2q_grouped_gemm_fp4_rows); act_mode as in b2q_gemm_fp4_blockscaled; hidden and ffn multiples of 128. */
+int32_t b2q_moe_forward_fp4(b2q_tp t, const void* x_bf16, const float* logits, const uint8_t* c_gate_up, const uint8_t* s_gate_up,
+                            const uint8_t* c_down, const uint8_t* s_down, int64_t tokens, int64_t hidden, int64_t ffn, int n_experts,
+                            int top_k, int act_mode, void* y_bf16, int32_t* counts_out);
 int32_t b2q_moe_forward_ex(b2q_tp t, const void* x_bf16, const float* logits, const uint8_t* w_gate_up, const float* s_gate_up,
                            const uint8_t* w_down, const float* s_down, int64_t tokens, int64_t hidden, int64_t ffn, int n_experts,
                            int top_k, int rounding, int gate_up_layout, void* y_bf16, int32_t* counts_out);
@@ -475,6 +483,14 @@ int32_t b2q_gemm_fp4_wo(b2q_handle h, const uint8_t* codes, const void* scales, 
 typedef enum { B2Q_FP4_ACT_SPLIT = 0, B2Q_FP4_ACT_MXFP8 = 1 } b2q_fp4_act_mode;
 int32_t b2q_gemm_fp4_blockscaled(b2q_handle h, const uint8_t* codes, const uint8_t* scales_e8m0, const void* x_bf16,
                                  int64_t tokens, int64_t N, int64_t K, int act_mode, void* out, int out_type);
+/* grouped_gemm (crates/oxicuda-blas/src/batched/grouped_gemm.rs:46-78) for FP4 weights, table on the device, ONE launch:
+ * problem g multiplies rows [row_offsets[g], row_offsets[g + 1]) of x_bf16 [capacity_rows x K] (offsets multiples of 256;
+ * the last problem runs to capacity_rows) with weights [g * N, (g + 1) * N) of the stacked codes [groups * N x K / 2] and
+ * scales [groups * N x K / 32]; out [capacity_rows x N].  Rows behind a problem's real row count are padding: they are
+ * computed like any other and never read back by the caller. */
+int32_t b2q_grouped_gemm_fp4_rows(b2q_handle h, const uint8_t* codes, const uint8_t* scales_e8m0, const void* x_bf16,
+                                  const int32_t* row_offsets, int groups, int64_t capacity_rows, int64_t N, int64_t K,
+                                  int act_mode, void* out, int out_type);
 
 /* ---- tile heuristics: classify_workload / Fp8TileHeuristic::select crates/oxicuda-blas/src/precision/fp8_ops.rs:67-107,
  *      :239-304; select_fp4_tile fp4_fp6_ops.rs:996-1075; Int8GemmConfig::tile_config int_ops.rs:141-176 ---- */

@@ -52,6 +52,9 @@ struct Params {
   int tiles_m, tiles_n, stages_per_tile;
   uint32_t idesc;
   int32_t* status;
+  // grouped mode (tile_group != null): row tile mt multiplies with the weights of problem tile_group[mt], rows
+  // [g * N, (g + 1) * N) of the stacked codes and scales; the output stays [rows x N]
+  const int32_t* tile_group;
 };
 
 // Activation pre-pass.  One CTA per (row tile, K stage): 128 K values of up to 128 / 64 tokens -> E4M3 codes in the
@@ -162,7 +165,7 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fp4_bs_kernel(const __grid_c
           if (!mbar_wait(empty_bar(s), ph ^ 1, abort_flag, 1)) { ok = false; break; }
           const uint32_t sw = base + s * kStageBytes;
           mbar_expect_tx(full_bar(s), kBytesW / 2 + kBytesA + 512);   // the transaction count of a 4-bit box is the packed byte count
-          tma_load_2d(sw, &map_w, full_bar(s), j * BK, nt * TILE_N);
+          tma_load_2d(sw, &map_w, full_bar(s), j * BK, nt * TILE_N + (p.tile_group ? __ldg(p.tile_group + mt) * (int)p.N : 0));
           tma_load_2d(sw + kBytesW, &map_a, full_bar(s), j * BK, mt * TILE_M);
           bulk_load(sw + kBytesW + kBytesA + 1024, p.xsf + ((size_t)mt * S + j) * 512, 512, full_bar(s));
         }
@@ -185,9 +188,10 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fp4_bs_kernel(const __grid_c
       const int tile = blockIdx.x + (int)(itx / S) * gridDim.x, j = (int)(itx % S);
       int mt, nt;
       tile_mn(tile, mt, nt);
+      const int64_t grow = p.tile_group ? (int64_t)__ldg(p.tile_group + mt) * p.N : 0;
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const int64_t row = min((int64_t)nt * TILE_N + lane + 32 * i, p.N - 1);
+        const int64_t row = grow + min((int64_t)nt * TILE_N + lane + 32 * i, p.N - 1);
         dst[i] = __ldg(reinterpret_cast<const uint32_t*>(p.scales + row * kblocks + j * 4));
       }
     };
@@ -320,12 +324,44 @@ __global__ void __launch_bounds__(kThreads, 1) gemm_fp4_bs_kernel(const __grid_c
 
 static inline size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
+// group of every row tile: the problem whose padded row range holds the tile's first row (ranges start at multiples of
+// 256 rows and are whole tiles); tiles behind the last range take the last problem (their rows are never read back)
+__global__ void __launch_bounds__(256) tile_group_kernel(const int32_t* __restrict__ offsets, int groups, int tiles_m, int rows_per_tile,
+                                                         int32_t* __restrict__ tile_group) {
+  for (int mt = blockIdx.x * blockDim.x + threadIdx.x; mt < tiles_m; mt += gridDim.x * blockDim.x) {
+    const int row = mt * rows_per_tile;
+    int g = 0;
+    while (g + 1 < groups && row >= offsets[g + 1]) ++g;
+    tile_group[mt] = g;
+  }
+}
+
 }  // namespace f4bs
+
+static int32_t gemm_fp4_bs_impl(b2q_handle h, const uint8_t* codes, const uint8_t* scales_e8m0, const void* x_bf16, int64_t tokens, int64_t N,
+                                int64_t K, int act_mode, void* out, int out_type, const int32_t* row_offsets, int groups);
 
 extern "C" int32_t b2q_gemm_fp4_blockscaled(b2q_handle h, const uint8_t* codes, const uint8_t* scales_e8m0, const void* x_bf16, int64_t tokens,
                                             int64_t N, int64_t K, int act_mode, void* out, int out_type) {
-  using namespace f4bs;
   B2Q_REQUIRE_HANDLE(h);
+  return gemm_fp4_bs_impl(h, codes, scales_e8m0, x_bf16, tokens, N, K, act_mode, out, out_type, nullptr, 0);
+}
+
+// Grouped form (the expert GEMMs of a mixture-of-experts layer in ONE launch, table on the device): problem g multiplies
+// rows [row_offsets[g], row_offsets[g + 1]) of x (offsets are multiples of 256; rows behind a problem's real count are
+// padding and are computed like any other) with the weights [g * N, (g + 1) * N) of the stacked codes and scales.
+extern "C" int32_t b2q_grouped_gemm_fp4_rows(b2q_handle h, const uint8_t* codes, const uint8_t* scales_e8m0, const void* x_bf16,
+                                             const int32_t* row_offsets, int groups, int64_t capacity_rows, int64_t N, int64_t K, int act_mode,
+                                             void* out, int out_type) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (groups <= 0 || !row_offsets) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "grouped_gemm_fp4_rows: bad problem table");
+  if ((int64_t)groups * N > 0x7FFFFFFF) B2Q_FAIL(h, B2Q_ERR_UNSUPPORTED, "grouped_gemm_fp4_rows: too many weight rows");
+  return gemm_fp4_bs_impl(h, codes, scales_e8m0, x_bf16, capacity_rows, N, K, act_mode, out, out_type, row_offsets, groups);
+}
+
+static int32_t gemm_fp4_bs_impl(b2q_handle h, const uint8_t* codes, const uint8_t* scales_e8m0, const void* x_bf16, int64_t tokens, int64_t N,
+                                int64_t K, int act_mode, void* out, int out_type, const int32_t* row_offsets, int groups) {
+  using namespace f4bs;
   if (tokens <= 0 || N <= 0 || K <= 0)
     B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "FP4 GEMM dimensions must be non-zero: m=%lld, n=%lld, k=%lld", (long long)N, (long long)tokens, (long long)K);
   if (K % 2 != 0) B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "FP4 GEMM K dimension must be even for packing, got k=%lld", (long long)K);
@@ -341,12 +377,18 @@ extern "C" int32_t b2q_gemm_fp4_blockscaled(b2q_handle h, const uint8_t* codes, 
   if (tiles_m * tiles_n > 0x7FFFFFFF) B2Q_FAIL(h, B2Q_ERR_UNSUPPORTED, "gemm_fp4_blockscaled: too many tiles");
   const int S = (int)(K / BK);
   // workspace: activation codes [tiles_m * 128][K] and the scale atoms [tiles_m][S][512]
-  const size_t xq_bytes = align256((size_t)tiles_m * TILE_M * K), sf_bytes = (size_t)tiles_m * S * 512;
+  const size_t xq_bytes = align256((size_t)tiles_m * TILE_M * K), sf_bytes = align256((size_t)tiles_m * S * 512);
   void* ws = nullptr;
-  int32_t st = b2q_workspace(h, xq_bytes + sf_bytes, &ws);
+  int32_t st = b2q_workspace(h, xq_bytes + sf_bytes + (groups > 0 ? (size_t)tiles_m * 4 : 0), &ws);
   if (st != B2Q_OK) return st;
   uint8_t* xq = reinterpret_cast<uint8_t*>(ws);
   uint8_t* xsf = xq + xq_bytes;
+  int32_t* tile_group = nullptr;
+  if (groups > 0) {
+    tile_group = reinterpret_cast<int32_t*>(xsf + sf_bytes);
+    tile_group_kernel<<<(int)ceil_div64(tiles_m, 256), 256, 0, h->stream>>>(row_offsets, groups, (int)tiles_m, tok_per_tile, tile_group);
+    B2Q_LAUNCH_CHECK(h, "tile_group_kernel");
+  }
   dim3 pg((unsigned)S, (unsigned)tiles_m);
   if (split) x_quant_tile_kernel<true><<<pg, 512, 0, h->stream>>>((const __nv_bfloat16*)x_bf16, tokens, K, xq, xsf);
   else x_quant_tile_kernel<false><<<pg, 512, 0, h->stream>>>((const __nv_bfloat16*)x_bf16, tokens, K, xq, xsf);
@@ -355,7 +397,7 @@ extern "C" int32_t b2q_gemm_fp4_blockscaled(b2q_handle h, const uint8_t* codes, 
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) B2Q_FAIL(h, B2Q_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   CUtensorMap map_w, map_a;
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)N};
+  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)(groups > 0 ? (int64_t)groups * N : N)};
   cuuint64_t strides[1] = {(cuuint64_t)(K / 2)};
   cuuint32_t box[2] = {128, (cuuint32_t)TILE_N};
   cuuint32_t estr[2] = {1, 1};
@@ -373,6 +415,7 @@ extern "C" int32_t b2q_gemm_fp4_blockscaled(b2q_handle h, const uint8_t* codes, 
   // A = E4M3 (0) activations, B = E2M1 (5) weights, both K-major, N = 256, E8M0 scales, M = 128
   p.idesc = (0u << 7) | (5u << 10) | ((uint32_t)(TILE_N >> 3) << 17) | (1u << 23) | ((uint32_t)(TILE_M >> 4) << 24);
   p.status = h->d_status;
+  p.tile_group = tile_group;
   B2Q_SMEM_ATTR(h, gemm_fp4_bs_kernel, kSmem);
   const int64_t tiles = tiles_m * tiles_n;
   const int grid = (int)(tiles < h->sm_count ? tiles : h->sm_count);

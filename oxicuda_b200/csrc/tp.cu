@@ -20,6 +20,9 @@
 
 int32_t b2q_fp8_quantize_rows_bf16_scratch(b2q_handle h, const void* x, int64_t rows, int64_t cols, int fmt, int rounding, float* scales,
                                            uint8_t* codes);
+extern "C" int32_t b2q_grouped_gemm_fp4_rows(b2q_handle h, const uint8_t* codes, const uint8_t* scales_e8m0, const void* x_bf16,
+                                             const int32_t* row_offsets, int groups, int64_t capacity_rows, int64_t N, int64_t K, int act_mode,
+                                             void* out, int out_type);
 int32_t b2q_grouped_gemm_fp8_rows_act(b2q_handle h, const uint8_t* a, const float* scale_a, const uint8_t* w, const float* scale_w,
                                       const int32_t* row_offsets, const int32_t* row_counts, int groups, int64_t capacity_rows, int64_t N, int64_t K,
                                       int fmt, void* out, int out_type, int act);
@@ -262,6 +265,25 @@ __global__ void __launch_bounds__(256) interleave_rows_kernel(const uint4* __res
     const int64_t orow = i / row16, c = i - orow * row16, blk = orow / (2 * block), in = orow - blk * 2 * block;
     const int64_t src = blk * block + (in < block ? in : in - block);
     out[i] = (in < block ? a : b)[src * row16 + c];
+  }
+}
+
+// h[r, f] = silu(gu[r, f]) * gu[r, F + f] (bf16 in and out, fp32 inside), eight columns per thread
+__global__ void __launch_bounds__(256) swiglu_bf16_kernel(const uint4* __restrict__ gu, uint4* __restrict__ hout, int64_t rows, int64_t F8) {
+  const int64_t total = rows * F8;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = i / F8, c = i - r * F8;
+    const uint4 g = gu[r * 2 * F8 + c], u = gu[r * 2 * F8 + F8 + c];
+    const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float g0 = __uint_as_float(gw[j] << 16), g1 = __uint_as_float(gw[j] & 0xFFFF0000u);
+      const float u0 = __uint_as_float(uw[j] << 16), u1 = __uint_as_float(uw[j] & 0xFFFF0000u);
+      const __nv_bfloat162 hv = __floats2bfloat162_rn(__fdiv_rn(g0, 1.0f + expf(-g0)) * u0, __fdiv_rn(g1, 1.0f + expf(-g1)) * u1);
+      o[j] = *reinterpret_cast<const uint32_t*>(&hv);
+    }
+    hout[i] = make_uint4(o[0], o[1], o[2], o[3]);
   }
 }
 
@@ -836,6 +858,54 @@ int32_t b2q_moe_forward_ex(b2q_tp t, const void* x_bf16, const float* logits, co
     if ((st = b2q_swiglu_quantize_rows_bf16(h, gu, gu + (size_t)F * 2, cap, F, 2 * F, B2Q_FP8_E4M3, rounding, hs, hc)) != B2Q_OK) return st;
   }
   if ((st = b2q_grouped_gemm_fp8_rows(h, hc, hs, w_down, s_down, off, cnt, n_local, cap, hidden, F, B2Q_FP8_E4M3, yb, B2Q_OUT_BF16)) != B2Q_OK) return st;
+  if ((st = b2q_ep_token_gather_bf16(h, yb, slot, wgt, tokens, top_k, hidden, y_bf16)) != B2Q_OK) return st;
+  if (t->tp > 1) B2Q_NCCL(h, tpx::nccl()->AllReduce(y_bf16, y_bf16, (size_t)tokens * hidden, tpx::kNcclBfloat16, tpx::kNcclSum, t->comm, h->stream));
+  return B2Q_OK;
+}
+
+// The same layer over block-scaled FP4 experts (E2M1 codes, one E8M0 scale per 32 along K): the two grouped GEMMs run on
+// tcgen05 kind::mxf8f6f4.block_scale with the scattered rows quantized per 32-block to E4M3 (act_mode, see
+// b2q_gemm_fp4_blockscaled); gate | up is concatenated per expert, h = silu(gate) * up is formed in bf16 between them.
+int32_t b2q_moe_forward_fp4(b2q_tp t, const void* x_bf16, const float* logits, const uint8_t* c_gate_up, const uint8_t* s_gate_up,
+                            const uint8_t* c_down, const uint8_t* s_down, int64_t tokens, int64_t hidden, int64_t ffn, int n_experts, int top_k,
+                            int act_mode, void* y_bf16, int32_t* counts_out) {
+  B2Q_REQUIRE_TP(t);
+  b2q_handle h = t->h;
+  if (tokens <= 0 || hidden <= 0 || ffn <= 0)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "moe_forward_fp4: dimensions must be non-zero: tokens=%lld, hidden=%lld, ffn=%lld", (long long)tokens,
+             (long long)hidden, (long long)ffn);
+  if (!x_bf16 || !logits || !c_gate_up || !s_gate_up || !c_down || !s_down || !y_bf16) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "moe_forward_fp4: null operand");
+  if (n_experts < 1 || n_experts % t->tp != 0) B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "n_experts %d not divisible by ep %d", n_experts, t->tp);
+  if (hidden % 128 != 0 || ffn % 128 != 0)
+    B2Q_FAIL(h, B2Q_ERR_UNSUPPORTED, "moe_forward_fp4: hidden and ffn must be multiples of 128, got %lld and %lld", (long long)hidden, (long long)ffn);
+  const int n_local = n_experts / t->tp, first = t->rank * n_local;
+  const int64_t pairs = tokens * top_k;
+  const int64_t cap = (pairs + 255) / 256 * 256 + (int64_t)n_local * 256;
+  const int64_t F = ffn;
+  using tpx::align256;
+  const size_t o_idx = 0, o_wgt = o_idx + align256((size_t)pairs * 4), o_cnt = o_wgt + align256((size_t)pairs * 4), o_off = o_cnt + 256,
+               o_slot = o_off + 512, o_xb = o_slot + align256((size_t)pairs * 4), o_gu = o_xb + align256((size_t)cap * hidden * 2),
+               o_hb = o_gu + align256((size_t)cap * 2 * F * 2), o_yb = o_hb + align256((size_t)cap * F * 2),
+               total = o_yb + align256((size_t)cap * hidden * 2);
+  uint8_t* ws = nullptr;
+  int32_t st = tpx::scratch(t, total, &ws);
+  if (st != B2Q_OK) return st;
+  int32_t* idx = (int32_t*)(ws + o_idx); float* wgt = (float*)(ws + o_wgt);
+  int32_t* cnt = (int32_t*)(ws + o_cnt); int32_t* off = (int32_t*)(ws + o_off); int32_t* slot = (int32_t*)(ws + o_slot);
+  uint8_t* xb = ws + o_xb; uint8_t* gu = ws + o_gu; uint8_t* hb = ws + o_hb; uint8_t* yb = ws + o_yb;
+  if ((st = b2q_moe_route_topk(h, logits, tokens, n_experts, top_k, idx, wgt)) != B2Q_OK) return st;
+  if ((st = b2q_moe_assign_slots(h, idx, pairs, first, n_local, cnt, off, slot)) != B2Q_OK) return st;
+  if (counts_out) B2Q_CUDA(h, cudaMemcpyAsync(counts_out, cnt, (size_t)n_local * 4, cudaMemcpyDeviceToDevice, h->stream));
+  if ((st = b2q_moe_scatter(h, x_bf16, slot, pairs, top_k, hidden * 2, xb)) != B2Q_OK) return st;
+  if ((st = b2q_grouped_gemm_fp4_rows(h, c_gate_up, s_gate_up, xb, off, n_local, cap, 2 * F, hidden, act_mode, gu, B2Q_OUT_BF16)) != B2Q_OK) return st;
+  {
+    const int64_t total8 = cap * (F / 8);
+    int grid = (int)((total8 + 255) / 256);
+    if (grid > h->sm_count * 16) grid = h->sm_count * 16;
+    tpx::swiglu_bf16_kernel<<<grid, 256, 0, h->stream>>>((const uint4*)gu, (uint4*)hb, cap, F / 8);
+    B2Q_LAUNCH_CHECK(h, "swiglu_bf16_kernel");
+  }
+  if ((st = b2q_grouped_gemm_fp4_rows(h, c_down, s_down, hb, off, n_local, cap, hidden, F, act_mode, yb, B2Q_OUT_BF16)) != B2Q_OK) return st;
   if ((st = b2q_ep_token_gather_bf16(h, yb, slot, wgt, tokens, top_k, hidden, y_bf16)) != B2Q_OK) return st;
   if (t->tp > 1) B2Q_NCCL(h, tpx::nccl()->AllReduce(y_bf16, y_bf16, (size_t)tokens * hidden, tpx::kNcclBfloat16, tpx::kNcclSum, t->comm, h->stream));
   return B2Q_OK;

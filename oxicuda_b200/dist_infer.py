@@ -400,3 +400,46 @@ class MoeFp8Layer:
                                           self.top_k, self.codec.rounding,
                                           L.GATE_UP_INTERLEAVED128 if self.interleaved else L.GATE_UP_CONCATENATED, L.ptr(y), L.ptr(self.last_counts))
         return y
+
+
+class MoeFp4Layer:
+    """The mixture of SwiGLU experts with block-scaled FP4 weights (E2M1 codes, E8M0 scale per 32 along K), one library
+    call (b2q_moe_forward_fp4): routing, slotting and scatter on the device, ONE grouped tcgen05 block-scaled GEMM for
+    gate | up, silu(gate) * up in bf16, ONE grouped GEMM for down, weighted gather; expert parallel like MoeFp8Layer.
+
+    Reference items: ExpertDispatcher::dispatch_and_gather (crates/oxicuda-dist-infer/src/expert_parallel/dispatch.rs:99-219),
+    SwiGluExpert::forward (crates/oxicuda-moe/src/expert/ffn.rs:172-243), MicroScalingQuantizer
+    (crates/oxicuda-blas/src/precision/fp4_fp6_ops.rs:746-898)."""
+
+    def __init__(self, experts, n_experts: int, top_k: int, handle: DistInferHandle, mxfp8_activations: bool = True):
+        """experts: list of (w1 gate [ffn x hidden], w3 up [ffn x hidden], w2 down [hidden x ffn]) f32 for THIS rank's experts."""
+        from .blas import MicroScalingConfig, MicroScalingQuantizer, ScalingFormat
+        ep = handle.config.ep
+        if n_experts % ep != 0:
+            raise L.InvalidDimension(L.ERR_INVALID_DIMENSION, f"n_experts {n_experts} not divisible by ep {ep}")
+        self.handle, self.n_experts, self.top_k = handle, n_experts, top_k
+        self.local = n_experts // ep
+        if len(experts) != self.local:
+            raise L.DimensionMismatch(L.ERR_DIMENSION_MISMATCH, f"expected {self.local} local experts, got {len(experts)}")
+        self.ffn, self.hidden = experts[0][0].shape
+        msq = MicroScalingQuantizer(MicroScalingConfig(32, ScalingFormat.E8M0))
+        gu = [msq.quantize_fp4(torch.cat([w1, w3], dim=0).reshape(-1).float().contiguous()) for (w1, w3, _) in experts]
+        dn = [msq.quantize_fp4(w2.reshape(-1).float().contiguous()) for (_, _, w2) in experts]
+        self.gate_up_codes = torch.cat([c.reshape(-1) for c, _ in gu]).contiguous()
+        self.gate_up_scales = torch.cat([s.reshape(-1) for _, s in gu]).contiguous()
+        self.down_codes = torch.cat([c.reshape(-1) for c, _ in dn]).contiguous()
+        self.down_scales = torch.cat([s.reshape(-1) for _, s in dn]).contiguous()
+        self.act_mode = 1 if mxfp8_activations else 0
+        self._group_handle = DistInferHandle(handle.ep_rank(), ParallelismConfig(tp=ep), handle.group)
+        self.last_counts = None
+
+    def forward(self, x: torch.Tensor, logits: torch.Tensor, out: torch.Tensor = None) -> torch.Tensor:
+        tokens = x.shape[0]
+        y = out if out is not None else torch.empty(tokens, self.hidden, dtype=torch.bfloat16, device=x.device)
+        lg = logits.reshape(tokens, self.n_experts).float().contiguous()
+        if self.last_counts is None:
+            self.last_counts = torch.zeros(self.local, dtype=torch.int32, device=x.device)
+        tp_group(self._group_handle).call("b2q_moe_forward_fp4", L.ptr(x), L.ptr(lg), L.ptr(self.gate_up_codes), L.ptr(self.gate_up_scales),
+                                          L.ptr(self.down_codes), L.ptr(self.down_scales), tokens, self.hidden, self.ffn, self.n_experts,
+                                          self.top_k, self.act_mode, L.ptr(y), L.ptr(self.last_counts))
+        return y

@@ -214,3 +214,67 @@ def test_moe_expert_parallel_two_ranks(cuda, oracle):
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=str(ROOT))
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "EP2 OK" in r.stdout
+
+
+def _mx_e4m3(oracle, x):
+    """One E4M3 code per value under a power-of-two scale per 32 values (smallest 2^e with max / 2^e <= 448): the
+    activation quantizer of the block-scaled FP4 GEMM in its W4A8 mode; returns the dequantized values (exact in bf16)."""
+    rows, K = x.shape
+    xf = np.asarray(x, np.float32).reshape(rows, K // 32, 32)
+    amax = np.abs(xf).max(axis=2, keepdims=True)
+    e = np.where(amax > 0, np.ceil(np.log2(np.maximum(amax, 1e-38) / 448.0)), 0.0)
+    e = np.maximum(e, -127.0)
+    q = oracle.fp8_decode(oracle.fp8_encode((xf / np.exp2(e)).astype(np.float32).reshape(-1), 0, 1)[0], 0, 1).reshape(xf.shape) * np.exp2(e)
+    return q.reshape(rows, K).astype(np.float32)
+
+
+def _bits(a):
+    return torch.from_numpy(np.ascontiguousarray(a, np.float32)).to(torch.bfloat16).view(torch.int16).numpy().view(np.uint16)
+
+
+@pytest.mark.parametrize("tokens,n_experts,top_k", [(200, 4, 2), (700, 8, 2)])
+def test_moe_fp4_layer_matches_oracle(cuda, oracle, tokens, n_experts, top_k):
+    """b2q_moe_forward_fp4 / b2q_grouped_gemm_fp4_rows: block-scaled FP4 experts, both grouped GEMMs one launch each of the
+    tcgen05 block-scaled kernel over a device-side table.  Oracle: the router and the gather of the reference, and per expert
+    the activation quantizer above, dequantize_fp4 + f32 dot (the oracle's FP4 product), silu(gate) * up in f32, bf16
+    where the layer stores bf16; over the layer's own codes."""
+    from oxicuda_b200.dist_infer import DistInferHandle, MoeFp4Layer, ParallelismConfig
+    rng = np.random.default_rng(0xB2000006 + tokens)
+    hidden, ffn = 256, 384
+    x = _bf16(rng.standard_normal((tokens, hidden)))
+    logits = rng.standard_normal((tokens, n_experts)).astype(np.float32)
+    if n_experts == 8:
+        logits[:, 5] = -50.0                                        # an expert that receives no token
+    experts = [((rng.standard_normal((ffn, hidden)) * 0.05).astype(np.float32), (rng.standard_normal((ffn, hidden)) * 0.05).astype(np.float32),
+                (rng.standard_normal((hidden, ffn)) * 0.05).astype(np.float32)) for _ in range(n_experts)]
+    t = lambda a: torch.from_numpy(a).to(cuda)
+    layer = MoeFp4Layer([(t(a), t(b), t(c)) for a, b, c in experts], n_experts, top_k, DistInferHandle(0, ParallelismConfig(ep=1)))
+    y = layer.forward(t(x).to(torch.bfloat16), t(logits)).float().cpu().numpy()
+    from oxicuda_b200._lib import default_handle
+    default_handle().check()
+    idx, wgt = oracle_route(logits, top_k)
+    counts = np.bincount(idx.reshape(-1), minlength=n_experts)
+    assert np.array_equal(layer.last_counts.cpu().numpy(), counts.astype(np.int32))
+    F = ffn
+    gc = layer.gate_up_codes.cpu().numpy().reshape(n_experts, 2 * F * hidden // 2)
+    gs = layer.gate_up_scales.cpu().numpy().reshape(n_experts, 2 * F * hidden // 32)
+    dc = layer.down_codes.cpu().numpy().reshape(n_experts, hidden * F // 2)
+    ds = layer.down_scales.cpu().numpy().reshape(n_experts, hidden * F // 32)
+    ys = {}
+    for e in range(n_experts):
+        toks = np.nonzero((idx == e).any(axis=1))[0]
+        if toks.size == 0:
+            continue
+        xq = _mx_e4m3(oracle, x[toks])
+        gu = _bf16(np.asarray(oracle.gemv_fp4(gc[e], gs[e], _bits(xq), toks.size, 2 * F, hidden, 32, "f32")).reshape(toks.size, 2 * F))
+        h = _bf16(oracle.swiglu(np.ascontiguousarray(gu[:, :F]), np.ascontiguousarray(gu[:, F:])))
+        ye = _bf16(np.asarray(oracle.gemv_fp4(dc[e], ds[e], _bits(_mx_e4m3(oracle, h)), toks.size, hidden, F, 32, "f32")).reshape(toks.size, hidden))
+        for i, tk in enumerate(toks):
+            ys[(int(tk), e)] = ye[i]
+    ref = np.zeros((tokens, hidden), np.float32)
+    for tk in range(tokens):
+        acc = np.zeros(hidden, np.float32)
+        for j in range(top_k):
+            acc = acc + wgt[tk, j] * ys[(tk, int(idx[tk, j]))]
+        ref[tk] = acc
+    assert err(y, _bf16(ref)) <= 1e-2
