@@ -816,9 +816,22 @@ def side_measurements(dev, peaks):
                                    "tflops": round(flm / secm / 1e12, 1), "rows_per_expert": [int(v) for v in layer.last_counts.tolist()],
                                    "launches_per_call": "route, slot, scatter, quantize, ONE grouped gate|up GEMM, SwiGLU + quantize, ONE grouped down GEMM, gather",
                                    "frac_of_2x_bf16_sustained": round(flm / secm / 1e12 / (2 * peaks["bf16_tflops_sustained"]), 3)}
-        del layer, xm, ym, lg
+        del layer
+        # the same layer over block-scaled FP4 experts (E2M1, E8M0 per 32), W4A8 activations
+        from oxicuda_b200.dist_infer import MoeFp4Layer
+        gen = torch.Generator(device=dev).manual_seed(0xB2000005)
+        experts = [(torch.randn(ffn_e, hid, device=dev, generator=gen) * 0.02, torch.randn(ffn_e, hid, device=dev, generator=gen) * 0.02,
+                    torch.randn(hid, ffn_e, device=dev, generator=gen) * 0.02) for _ in range(E)]
+        layer4 = MoeFp4Layer(experts, E, topk, DistInferHandle(0, ParallelismConfig(ep=1)))
+        del experts
+        sec4 = _time_calls(lambda i: layer4.forward(xm, lg, out=ym), 10, 3)
+        roof["moe_fp4_mixtral"] = {"us": round(sec4 * 1e6, 1), "tflops": round(flm / sec4 / 1e12, 1), "activations": "MX E4M3 per 32 (W4A8)",
+                                   "weight_bytes": int(E * 3 * hid * ffn_e * (0.5 + 1 / 32)),
+                                   "frac_of_2x_bf16_sustained": round(flm / sec4 / 1e12 / (2 * peaks["bf16_tflops_sustained"]), 3)}
+        del layer4, xm, ym, lg
     except Exception as exc:                                       # noqa: BLE001
-        roof["moe_fp8_mixtral"] = {"error": repr(exc)}
+        roof.setdefault("moe_fp8_mixtral", {"error": repr(exc)})
+        roof.setdefault("moe_fp4_mixtral", {"error": repr(exc)})
     torch.cuda.empty_cache()
 
     # ---- FP8 W8A8 with few tokens on the 70B-shaped FFN projection: HBM-bound ----

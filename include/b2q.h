@@ -492,6 +492,21 @@ int32_t b2q_grouped_gemm_fp4_rows(b2q_handle h, const uint8_t* codes, const uint
                                   const int32_t* row_offsets, int groups, int64_t capacity_rows, int64_t N, int64_t K,
                                   int act_mode, void* out, int out_type);
 
+/* ---- GGML block codecs, the weight formats of GGUF files: crates/oxicuda-quant/src/scheme/ggml.rs
+ *      quantize_q8_0 :243-262, quantize_q4_0 :284-316, quantize_q4_1 :342-372, quantize_q4_k :404-472, dequantize_* :265-506,
+ *      GgmlType :147-185.  Blocks are packed little-endian records in the field order of the reference's structs:
+ *      Q8_0 {d f16, qs i8[32]} 34 bytes; Q4_0 {d, qs u8[16]} 18 (byte i = code i | code i+16 << 4); Q4_1 {d, m, qs[16]} 20;
+ *      Q4_K {d, dmin, scales u8[8], mins u8[8], qs u8[128]} 148 bytes for 256 weights (byte i = code 2i | code 2i+1 << 4).
+ *      Bit-exact with the reference's arithmetic (binary16 scales rounded to nearest even).  Errors as check_block
+ *      (:522-534): EMPTY_INPUT, GROUP_SIZE_MISMATCH. ---- */
+typedef enum { B2Q_GGML_Q8_0 = 0, B2Q_GGML_Q4_0 = 1, B2Q_GGML_Q4_1 = 2, B2Q_GGML_Q4_K = 3 } b2q_ggml_type;
+int64_t b2q_ggml_block_bytes(int type);   /* bytes of one record; -1 for an unknown type */
+int64_t b2q_ggml_block_size(int type);    /* weights per record: 32, or 256 for Q4_K */
+/* w [n] f32 -> blocks [n / block_size records]. */
+int32_t b2q_ggml_quantize_f32(b2q_handle h, int type, const float* w, int64_t n, uint8_t* blocks);
+/* blocks -> out [n] f32 or bf16 (B2Q_OUT_F32 / B2Q_OUT_BF16; bf16 is the f32 value rounded to nearest even). */
+int32_t b2q_ggml_dequantize(b2q_handle h, int type, const uint8_t* blocks, int64_t n, void* out, int out_type);
+
 /* ---- tile heuristics: classify_workload / Fp8TileHeuristic::select crates/oxicuda-blas/src/precision/fp8_ops.rs:67-107,
  *      :239-304; select_fp4_tile fp4_fp6_ops.rs:996-1075; Int8GemmConfig::tile_config int_ops.rs:141-176 ---- */
 typedef struct {

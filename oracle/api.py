@@ -318,6 +318,54 @@ def interleave_rows128(a, b):
     return np.stack([a.reshape(F // 128, 128, *a.shape[1:]), b.reshape(F // 128, 128, *b.shape[1:])], axis=1).reshape(2 * F, *a.shape[1:])
 
 
+# ---- GGML block codecs (crates/oxicuda-quant/src/scheme/ggml.rs) ----
+GGML_Q8_0, GGML_Q4_0, GGML_Q4_1, GGML_Q4_K = 0, 1, 2, 3
+
+
+def ggml_block_bytes(ty):
+    return {0: 34, 1: 18, 2: 20, 3: 148}[ty]
+
+
+def ggml_block_size(ty):
+    return 256 if ty == 3 else 32
+
+
+def ggml_f32_to_f16_bits(x):
+    L = lib()
+    L.orc_ggml_f32_to_f16_bits.restype = C.c_uint16
+    L.orc_ggml_f32_to_f16_bits.argtypes = [C.c_float]
+    return int(L.orc_ggml_f32_to_f16_bits(float(x)))
+
+
+def ggml_f16_to_f32(h):
+    L = lib()
+    L.orc_ggml_f16_to_f32.restype = C.c_float
+    L.orc_ggml_f16_to_f32.argtypes = [C.c_uint16]
+    return float(L.orc_ggml_f16_to_f32(int(h)))
+
+
+def ggml_quantize(w, ty):
+    """Packed block records (uint8) of the flat weights; raises ValueError as check_block does (ggml.rs:522-534)."""
+    w = _f32(w).reshape(-1)
+    L = lib()
+    L.orc_ggml_quantize.restype = C.c_int64
+    out = np.zeros(max(1, w.size // ggml_block_size(ty)) * ggml_block_bytes(ty), np.uint8)
+    nb = L.orc_ggml_quantize(ty, _p(w), _i64(w.size), _p(out))
+    if nb == -1:
+        raise ValueError("EmptyInput")
+    if nb == -2:
+        raise ValueError("GroupSizeMismatch")
+    return out[:nb * ggml_block_bytes(ty)]
+
+
+def ggml_dequantize(blocks, ty):
+    blocks = np.ascontiguousarray(blocks, np.uint8).reshape(-1)
+    n = blocks.size // ggml_block_bytes(ty) * ggml_block_size(ty)
+    out = np.zeros(n, np.float32)
+    lib().orc_ggml_dequantize(ty, _p(blocks), _i64(n), _p(out))
+    return out
+
+
 # ---- heuristics ----
 # ---- KV cache / RMSNorm ----
 def kv_cache_quantize(x, n_tokens, head_dim, bits=8, axis=0):

@@ -954,3 +954,173 @@ uint32_t orc_fp8_split_k(uint32_t m, uint32_t n, uint32_t k) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------
+// GGML block codecs Q8_0 / Q4_0 / Q4_1 / Q4_K: crates/oxicuda-quant/src/scheme/ggml.rs:44-139 (binary16
+// conversions, round to nearest even with subnormals), :243-282 (Q8_0), :284-335 (Q4_0), :342-391 (Q4_1),
+// :404-506 (Q4_K).  Blocks are laid out as packed little-endian records in the field order of the reference's
+// structs: Q8_0 {d f16, qs i8[32]} 34 bytes; Q4_0 {d, qs u8[16]} 18; Q4_1 {d, m, qs[16]} 20;
+// Q4_K {d, dmin, scales u8[8], mins u8[8], qs u8[128]} 148 (the reference keeps the 6-bit values one per byte
+// and packs code 2i with code 2i+1, :459-462).
+// ---------------------------------------------------------------------------------------------------------
+namespace {
+uint16_t ggml_f32_to_f16_bits(float x) {                    // ggml.rs:50-107
+  uint32_t bits; std::memcpy(&bits, &x, 4);
+  const uint16_t sign = (uint16_t)((bits >> 16) & 0x8000u);
+  const int exp = (int)((bits >> 23) & 0xFF);
+  const uint32_t mantissa = bits & 0x007FFFFFu;
+  if (exp == 0xFF) return mantissa != 0 ? (uint16_t)(sign | 0x7E00) : (uint16_t)(sign | 0x7C00);
+  int e = exp - 127 + 15;
+  if (e >= 0x1F) return (uint16_t)(sign | 0x7C00);
+  if (e <= 0) {
+    if (e < -10) return sign;
+    const uint32_t m = mantissa | 0x00800000u;
+    const uint32_t shift = (uint32_t)(14 - e);
+    uint16_t half = (uint16_t)(m >> shift);
+    const uint32_t round_bit = 1u << (shift - 1);
+    if ((m & round_bit) != 0 && ((m & (round_bit - 1)) != 0 || (half & 1) != 0)) half = (uint16_t)(half + 1);
+    return (uint16_t)(sign | half);
+  }
+  uint16_t half_mant = (uint16_t)(mantissa >> 13);
+  const uint32_t round_bit = mantissa & 0x00001000u;
+  if (round_bit != 0 && ((mantissa & 0x00000FFFu) != 0 || (half_mant & 1) != 0)) {
+    half_mant = (uint16_t)(half_mant + 1);
+    if (half_mant == 0x0400) {
+      half_mant = 0;
+      e += 1;
+      if (e >= 0x1F) return (uint16_t)(sign | 0x7C00);
+    }
+  }
+  return (uint16_t)(sign | ((uint16_t)e << 10) | half_mant);
+}
+float ggml_f16_to_f32(uint16_t h) {                          // ggml.rs:110-139
+  const uint32_t sign = ((uint32_t)(h & 0x8000u)) << 16;
+  const uint32_t exp = (h >> 10) & 0x1F, mant = h & 0x03FF;
+  uint32_t bits;
+  if (exp == 0) {
+    if (mant == 0) bits = sign;
+    else {
+      const float magnitude = (float)mant * (1.0f / 16777216.0f);
+      return (sign >> 31) != 0 ? -magnitude : magnitude;
+    }
+  } else if (exp == 0x1F) bits = sign | 0x7F800000u | (mant << 13);
+  else bits = sign | ((exp + (127 - 15)) << 23) | (mant << 13);
+  float f; std::memcpy(&f, &bits, 4);
+  return f;
+}
+inline float ggml_f16_round(float x) { return ggml_f16_to_f32(ggml_f32_to_f16_bits(x)); }
+inline float clampf(float v, float lo, float hi) { return v < lo ? lo : (v > hi ? hi : v); }   // f32::clamp on non-NaN input
+inline void put16(uint8_t* p, uint16_t v) { p[0] = (uint8_t)(v & 0xFF); p[1] = (uint8_t)(v >> 8); }
+inline uint16_t get16(const uint8_t* p) { return (uint16_t)(p[0] | (p[1] << 8)); }
+}  // namespace
+
+extern "C" {
+
+uint16_t orc_ggml_f32_to_f16_bits(float x) { return ggml_f32_to_f16_bits(x); }
+float orc_ggml_f16_to_f32(uint16_t h) { return ggml_f16_to_f32(h); }
+
+// type: 0 Q8_0, 1 Q4_0, 2 Q4_1, 3 Q4_K.  Bytes of one block / weights per block.
+int64_t orc_ggml_block_bytes(int type) { return type == 0 ? 34 : type == 1 ? 18 : type == 2 ? 20 : type == 3 ? 148 : -1; }
+int64_t orc_ggml_block_size(int type) { return type == 3 ? 256 : 32; }
+
+// Returns the number of blocks, -1 for an empty input, -2 for a length that is not a multiple of the block size
+// (check_block, ggml.rs:522-534).
+int64_t orc_ggml_quantize(int type, const float* w, int64_t n, uint8_t* out) {
+  if (n <= 0) return -1;
+  const int64_t bs = orc_ggml_block_size(type), bb = orc_ggml_block_bytes(type);
+  if (n % bs != 0) return -2;
+  const int64_t nb = n / bs;
+  for (int64_t b = 0; b < nb; ++b) {
+    const float* c = w + b * bs;
+    uint8_t* o = out + b * bb;
+    if (type == 0) {                                          // ggml.rs:243-262
+      float amax = 0.0f;
+      for (int i = 0; i < 32; ++i) amax = std::fmax(amax, std::fabs(c[i]));
+      const float d = amax / 127.0f, dq = ggml_f16_round(d), inv = dq > 0.0f ? 1.0f / dq : 0.0f;
+      put16(o, ggml_f32_to_f16_bits(d));
+      for (int i = 0; i < 32; ++i) o[2 + i] = (uint8_t)(int8_t)clampf(std::round(c[i] * inv), -127.0f, 127.0f);
+    } else if (type == 1) {                                   // ggml.rs:284-316
+      float max = 0.0f, amax = 0.0f;
+      for (int i = 0; i < 32; ++i) if (std::fabs(c[i]) > amax) { amax = std::fabs(c[i]); max = c[i]; }
+      const float d = max / -8.0f, dq = ggml_f16_round(d), inv = dq != 0.0f ? 1.0f / dq : 0.0f;
+      uint8_t codes[32];
+      for (int i = 0; i < 32; ++i) codes[i] = (uint8_t)clampf(std::round(c[i] * inv) + 8.0f, 0.0f, 15.0f);
+      put16(o, ggml_f32_to_f16_bits(d));
+      for (int i = 0; i < 16; ++i) o[2 + i] = (uint8_t)(codes[i] | (codes[i + 16] << 4));
+    } else if (type == 2) {                                   // ggml.rs:342-372
+      float mn = std::numeric_limits<float>::infinity(), mx = -std::numeric_limits<float>::infinity();
+      for (int i = 0; i < 32; ++i) { mn = std::fmin(mn, c[i]); mx = std::fmax(mx, c[i]); }
+      const float d = (mx - mn) / 15.0f, dq = ggml_f16_round(d), mq = ggml_f16_round(mn), inv = dq > 0.0f ? 1.0f / dq : 0.0f;
+      uint8_t codes[32];
+      for (int i = 0; i < 32; ++i) codes[i] = (uint8_t)clampf(std::round((c[i] - mq) * inv), 0.0f, 15.0f);
+      put16(o, ggml_f32_to_f16_bits(d));
+      put16(o + 2, ggml_f32_to_f16_bits(mn));
+      for (int i = 0; i < 16; ++i) o[4 + i] = (uint8_t)(codes[i] | (codes[i + 16] << 4));
+    } else {                                                  // ggml.rs:404-472
+      float sub_scales[8], sub_mins[8];
+      for (int sb = 0; sb < 8; ++sb) {
+        float mn = std::numeric_limits<float>::infinity(), mx = -std::numeric_limits<float>::infinity();
+        for (int i = 0; i < 32; ++i) { mn = std::fmin(mn, c[sb * 32 + i]); mx = std::fmax(mx, c[sb * 32 + i]); }
+        mn = std::fmin(mn, 0.0f);
+        sub_scales[sb] = (mx - mn) / 15.0f;
+        sub_mins[sb] = -mn;
+      }
+      float max_scale = 0.0f, max_min = 0.0f;
+      for (int sb = 0; sb < 8; ++sb) { max_scale = std::fmax(max_scale, sub_scales[sb]); max_min = std::fmax(max_min, sub_mins[sb]); }
+      max_min = max_min + 0.0f;                 // (-0.0 + 0.0 = +0.0) f32::max(+0.0, -0.0) may return either zero: the stored dmin is taken as +0
+      const float d = max_scale / 63.0f, dmin = max_min / 63.0f, dq = ggml_f16_round(d), dminq = ggml_f16_round(dmin);
+      const float inv_d = dq > 0.0f ? 1.0f / dq : 0.0f, inv_dmin = dminq > 0.0f ? 1.0f / dminq : 0.0f;
+      uint8_t scales[8], mins[8], codes[256];
+      for (int sb = 0; sb < 8; ++sb) {
+        scales[sb] = (uint8_t)clampf(std::round(sub_scales[sb] * inv_d), 0.0f, 63.0f);
+        mins[sb] = (uint8_t)clampf(std::round(sub_mins[sb] * inv_dmin), 0.0f, 63.0f);
+      }
+      for (int sb = 0; sb < 8; ++sb) {
+        const float sc = dq * (float)scales[sb], mnv = dminq * (float)mins[sb], inv_sc = sc > 0.0f ? 1.0f / sc : 0.0f;
+        for (int i = 0; i < 32; ++i) codes[sb * 32 + i] = (uint8_t)clampf(std::round((c[sb * 32 + i] + mnv) * inv_sc), 0.0f, 15.0f);
+      }
+      put16(o, ggml_f32_to_f16_bits(d));
+      put16(o + 2, ggml_f32_to_f16_bits(dmin));
+      for (int sb = 0; sb < 8; ++sb) { o[4 + sb] = scales[sb]; o[12 + sb] = mins[sb]; }
+      for (int i = 0; i < 128; ++i) o[20 + i] = (uint8_t)(codes[2 * i] | (codes[2 * i + 1] << 4));
+    }
+  }
+  return nb;
+}
+
+// n = number of weights (a multiple of the block size).  ggml.rs:265-276, :319-333, :375-390, :476-503.
+void orc_ggml_dequantize(int type, const uint8_t* blocks, int64_t n, float* out) {
+  const int64_t bs = orc_ggml_block_size(type), bb = orc_ggml_block_bytes(type), nb = n / bs;
+  for (int64_t b = 0; b < nb; ++b) {
+    const uint8_t* p = blocks + b * bb;
+    float* o = out + b * bs;
+    if (type == 0) {
+      const float d = ggml_f16_to_f32(get16(p));
+      for (int i = 0; i < 32; ++i) o[i] = (float)(int8_t)p[2 + i] * d;
+    } else if (type == 1) {
+      const float d = ggml_f16_to_f32(get16(p));
+      for (int i = 0; i < 16; ++i) {
+        o[i] = (float)((int)(p[2 + i] & 0x0F) - 8) * d;
+        o[i + 16] = (float)((int)(p[2 + i] >> 4) - 8) * d;
+      }
+    } else if (type == 2) {
+      const float d = ggml_f16_to_f32(get16(p)), m = ggml_f16_to_f32(get16(p + 2));
+      for (int i = 0; i < 16; ++i) {
+        o[i] = (float)(p[4 + i] & 0x0F) * d + m;
+        o[i + 16] = (float)(p[4 + i] >> 4) * d + m;
+      }
+    } else {
+      const float d = ggml_f16_to_f32(get16(p)), dmin = ggml_f16_to_f32(get16(p + 2));
+      for (int sb = 0; sb < 8; ++sb) {
+        const float sc = d * (float)p[4 + sb], mn = dmin * (float)p[12 + sb];
+        for (int i = 0; i < 32; ++i) {
+          const int k = sb * 32 + i;
+          const float q = (float)((k & 1) ? (p[20 + (k >> 1)] >> 4) : (p[20 + (k >> 1)] & 0x0F));
+          o[k] = sc * q - mn;
+        }
+      }
+    }
+  }
+}
+
+}  // extern "C"

@@ -285,3 +285,55 @@ impl<'h> KvCacheQuantizer<'h> {
         })
     }
 }
+
+// ---- GGML block codecs, crates/oxicuda-quant/src/scheme/ggml.rs:147-518 -------------------------------------------
+/// `GgmlType` (`ggml.rs:147-185`).
+#[derive(Debug, Clone, Copy, PartialEq, Eq)]
+#[allow(non_camel_case_types)]
+pub enum GgmlType { Q8_0 = 0, Q4_0 = 1, Q4_1 = 2, Q4_K = 3 }
+impl GgmlType {
+    pub fn block_size(self) -> usize { if self == GgmlType::Q4_K { 256 } else { 32 } }
+    /// Bytes of one packed record: the reference struct's fields in order, little-endian.
+    pub fn block_bytes(self) -> usize { match self { GgmlType::Q8_0 => 34, GgmlType::Q4_0 => 18, GgmlType::Q4_1 => 20, GgmlType::Q4_K => 148 } }
+}
+/// `BlockQ8_0` (`ggml.rs:189-195`); the other block structs unpack the same way from their records.
+#[derive(Debug, Clone, PartialEq, Eq)]
+pub struct BlockQ8_0 { pub d: u16, pub qs: [i8; 32] }
+
+pub struct GgmlCodec<'h> { handle: &'h BlasHandle }
+impl<'h> GgmlCodec<'h> {
+    pub fn new(handle: &'h BlasHandle) -> Self { Self { handle } }
+    /// Packed records of the weights: `quantize_q8_0 / q4_0 / q4_1 / q4_k` (`ggml.rs:243-472`).
+    pub fn quantize_records(&self, weights: &[f32], ty: GgmlType) -> QuantResult<Vec<u8>> {
+        let w = DeviceBuffer::from_host(weights)?;
+        let out = DeviceBuffer::<u8>::alloc((weights.len() / ty.block_size()).max(1) * ty.block_bytes())?;
+        map_status(self.handle, unsafe { sys::b2q_ggml_quantize_f32(self.handle.raw(), ty as i32, w.as_device_ptr() as *const f32, weights.len() as i64, out.as_device_ptr() as *mut u8) })?;
+        out.to_host()
+    }
+    /// `quantize_q8_0` with the reference's return type.
+    pub fn quantize_q8_0(&self, weights: &[f32]) -> QuantResult<Vec<BlockQ8_0>> {
+        let rec = self.quantize_records(weights, GgmlType::Q8_0)?;
+        Ok(rec.chunks_exact(34).map(|r| {
+            let mut qs = [0i8; 32];
+            for (q, &b) in qs.iter_mut().zip(&r[2..]) { *q = b as i8; }
+            BlockQ8_0 { d: u16::from_le_bytes([r[0], r[1]]), qs }
+        }).collect())
+    }
+    /// `dequantize_*` (`ggml.rs:265-506`) over packed records.
+    pub fn dequantize_records(&self, records: &[u8], ty: GgmlType) -> QuantResult<Vec<f32>> {
+        let n = records.len() / ty.block_bytes() * ty.block_size();
+        let r = DeviceBuffer::from_host(records)?;
+        let out = DeviceBuffer::<f32>::alloc(n)?;
+        map_status(self.handle, unsafe { sys::b2q_ggml_dequantize(self.handle.raw(), ty as i32, r.as_device_ptr() as *const u8, n as i64, out.as_device_ptr() as *mut c_void, sys::B2Q_OUT_F32) })?;
+        out.to_host()
+    }
+    /// Records already in HBM (a GGUF tensor-data region uploaded as it is) -> bf16 weights in HBM.
+    pub fn dequantize_bf16_device(&self, records: CUdeviceptr, n_weights: usize, ty: GgmlType, out_bf16: CUdeviceptr) -> QuantResult<()> {
+        map_status(self.handle, unsafe { sys::b2q_ggml_dequantize(self.handle.raw(), ty as i32, records as *const u8, n_weights as i64, out_bf16 as *mut c_void, sys::B2Q_OUT_BF16) })
+    }
+    /// `fake_quantize` (`ggml.rs:511-518`).
+    pub fn fake_quantize(&self, weights: &[f32], ty: GgmlType) -> QuantResult<Vec<f32>> {
+        let rec = self.quantize_records(weights, ty)?;
+        self.dequantize_records(&rec, ty)
+    }
+}
