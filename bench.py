@@ -418,7 +418,9 @@ def main():
             "cpu_baseline": cpu,
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": TOKENS * HIDDEN * 2, "d2h_bytes_per_step": TOKENS * HIDDEN * 2,
                     "steps": e2e_steps},
-            "gpu_launches": args.steps * (1 + 3 * max(1, tp_summary["boundary"]["m4096"]["chunks"])),
+            # this library's kernels per timed step and rank: quantize x, gate|up GEMM (SwiGLU in its epilogue), quantize h, then the
+            # down GEMM and, on the scatter boundary, the sum-and-gather kernel once per column chunk (NCCL's kernels are not counted)
+            "gpu_launches": args.steps * _launches_per_step(tp_summary["boundary"]["m4096"], args.chunks),
             "clocks": clocks,
             "extras": extras,
         }
@@ -695,6 +697,15 @@ def quantizer_measurements(dev, peaks):
     run("rms_norm_quantize_fp8_bf16_8192x8192", n * 3, lambda: h.call("b2q_rms_norm_quantize_fp8_bf16", ptr(x16), None, ptr(gamma), rows, cols, 1e-6, 0, 1, ptr(sc), ptr(u8), None))
     run("rms_norm_quantize_fp8_bf16_residual_8192x8192", n * 7, lambda: h.call("b2q_rms_norm_quantize_fp8_bf16", ptr(x16), ptr(res16), ptr(gamma), rows, cols, 1e-6, 0, 1, ptr(sc), ptr(u8), None))
     return res
+
+
+def _launches_per_step(boundary, chunks_override):
+    mode, chunks = boundary["mode"], max(1, chunks_override or boundary["chunks"])
+    if mode == 4:
+        return 3 + 2 * chunks
+    if mode == 3:
+        return 1 + 3 * chunks          # token chunks repeat the two GEMMs and the quantizer
+    return 4
 
 
 def side_measurements(dev, peaks):

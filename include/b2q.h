@@ -330,6 +330,13 @@ int32_t b2q_tp_destroy(b2q_tp t);
  * are attached every row-parallel boundary goes through NCCL. */
 int32_t b2q_tp_exchange_buffer(b2q_tp t, void** ptr, uint8_t* ipc_handle64);
 int32_t b2q_tp_attach_peers(b2q_tp t, const uint8_t* ipc_handles, void* const* direct_ptrs);
+/* The row-parallel partial product with the reduce-scatter folded into its epilogue (the first half of boundary mode 4,
+ * usable on its own): out = a [M x K] . w [N x K]^T with per-row scales (+ bias [N] on the rank that carries it), bf16;
+ * rows [o * M / tp, (o + 1) * M / tp) are stored into inbox[o] -- rank o's buffer [tp][M / tp][N] bf16, a device pointer
+ * valid on this GPU (peer-mapped, or local for o == rank) -- at slot `rank`.  Nothing waits in this kernel: the caller
+ * orders the readers behind every rank's launch.  M > 128, N > 128, M % (32 * tp) == 0, N % 8 == 0, K % 16 == 0. */
+int32_t b2q_gemm_fp8_scatter(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,
+                             const float* scale_a, const float* scale_w, const float* bias, void* const* inbox, int tp, int rank);
 /* Chunks of the many-token paths (0 = automatic, see b2q_tp_plan). */
 int32_t b2q_tp_set_chunks(b2q_tp t, int chunks);
 /* The boundary a row-parallel result of tokens x out_features takes: mode 0 none (tp = 1); 1 one-shot and 2 two-shot

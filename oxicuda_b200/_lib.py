@@ -161,6 +161,7 @@ SIGNATURES = {
     "b2q_moe_assign_slots": (C.c_int32, [_H, _P, _I64, _I, _I, _P, _P, _P]),
     "b2q_moe_scatter": (C.c_int32, [_H, _P, _P, _I64, _I, _I64, _P]),
     "b2q_moe_forward": (C.c_int32, [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I, _I, _I, _P, _P]),
+    "b2q_gemm_fp8_scatter": (C.c_int32, [_H, _P, _P, _I64, _I64, _I64, _I, _P, _P, _P, _P, _I, _I]),
     "b2q_ggml_block_bytes": (C.c_int64, [_I]),
     "b2q_ggml_block_size": (C.c_int64, [_I]),
     "b2q_ggml_quantize_f32": (C.c_int32, [_H, _I, _P, _I64, _P]),

@@ -47,15 +47,16 @@ __global__ void __launch_bounds__(T * T) gemm_fp8_simt_kernel(const uint8_t* __r
 
 }  // namespace
 
+// out_cols: the columns of out when they are not N (the SwiGLU-pair epilogue writes N / 2); 0 = N.
 int32_t b2q_validate_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,
-                              const float* scale_a, int ka, const float* scale_w, int kw, void* out, int out_type) {
+                              const float* scale_a, int ka, const float* scale_w, int kw, void* out, int out_type, int64_t out_cols) {
   // Order follows the reference's gemm_impl: dimensions first, then argument checks, then overlap.
   if (M <= 0 || N <= 0 || K <= 0)
     B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "FP8 GEMM dimensions must be non-zero: m=%lld, n=%lld, k=%lld", (long long)M, (long long)N, (long long)K);
   if (!a || !w || !out || !scale_a || !scale_w) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemm_fp8: null pointer");
   if (fmt < 0 || fmt > 1 || ka < 0 || ka > 1 || kw < 0 || kw > 1 || out_type < 0 || out_type > 1)
     B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemm_fp8: bad enum value");
-  const uintptr_t c0 = reinterpret_cast<uintptr_t>(out), c1 = c0 + (size_t)(M * N) * (out_type == B2Q_OUT_BF16 ? 2 : 4);
+  const uintptr_t c0 = reinterpret_cast<uintptr_t>(out), c1 = c0 + (size_t)(M * (out_cols > 0 ? out_cols : N)) * (out_type == B2Q_OUT_BF16 ? 2 : 4);
   const uintptr_t a0 = reinterpret_cast<uintptr_t>(a), a1 = a0 + (size_t)(M * K);
   const uintptr_t w0 = reinterpret_cast<uintptr_t>(w), w1 = w0 + (size_t)(N * K);
   if ((c0 < a1 && a0 < c1) || (c0 < w1 && w0 < c1))
@@ -67,7 +68,7 @@ extern "C" int32_t b2q_gemm_fp8_simt(b2q_handle h, const uint8_t* a, const uint8
                                      int decode_mode, const float* scale_a, int scale_a_kind, const float* scale_w,
                                      int scale_w_kind, void* out, int out_type) {
   B2Q_REQUIRE_HANDLE(h);
-  int32_t st = b2q_validate_gemm_fp8(h, a, w, M, N, K, fmt, scale_a, scale_a_kind, scale_w, scale_w_kind, out, out_type);
+  int32_t st = b2q_validate_gemm_fp8(h, a, w, M, N, K, fmt, scale_a, scale_a_kind, scale_w, scale_w_kind, out, out_type, 0);
   if (st != B2Q_OK) return st;
   if (decode_mode < 0 || decode_mode > 1) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemm_fp8_simt: bad decode mode");
   dim3 grid((unsigned)ceil_div64(N, T), (unsigned)ceil_div64(M, T));

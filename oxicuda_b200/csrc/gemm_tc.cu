@@ -65,6 +65,10 @@ struct Params {
   // [o * rs_rows, (o + 1) * rs_rows) belong to rank o; they are stored, as bf16, through that rank's tensor map (its
   // inbox in peer-mapped memory) at rows rs_rank * rs_rows + (row - o * rs_rows), i.e. into the slot of THIS rank
   int rs_tp, rs_rank, rs_rows;
+  // tile rasterisation of the pair kernel: groups of group_m row tiles sweep the columns (0: GROUP_M); with group_rot the
+  // groups are walked starting at group group_rot (scatter mode: every rank starts at another owner's rows, so no rank's
+  // NVLink ingress is the target of all the others at once)
+  int group_m, group_rot;
 };
 constexpr int kMaxGroups = 64;
 constexpr int kMaxScatterRanks = 8;
@@ -95,11 +99,17 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
 }
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr) { return make_desc_sw128(smem_addr); }
 
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& mb, int& nb) {
-  const int group_size = GROUP_M * tiles_n;
-  const int group = tile / group_size;
-  const int first_m = group * GROUP_M;
-  const int gm = min(tiles_m - first_m, GROUP_M);
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& mb, int& nb, int group_m = GROUP_M, int group_rot = 0) {
+  const int group_size = group_m * tiles_n;
+  int group = tile / group_size;
+  const int in_tile = tile - group * group_size;
+  if (group_rot) {                                     // only with tiles_m % group_m == 0: all groups are whole
+    const int ngroups = tiles_m / group_m;
+    group = (group + group_rot) % ngroups;
+    tile = group * group_size + in_tile;
+  }
+  const int first_m = group * group_m;
+  const int gm = min(tiles_m - first_m, group_m);
   const int in_group = tile - group * group_size;
   mb = first_m + in_group % gm;
   nb = in_group / gm;
@@ -286,14 +296,18 @@ __device__ __forceinline__ void epilogue_rows(const Params& pp, const CUtensorMa
 // h = silu(gate) * up with both factors scaled in fp32 (SwiGluExpert::forward, crates/oxicuda-moe/src/expert/ffn.rs:208-243;
 // silu(x) = x / (1 + exp(-x)), crates/oxicuda-lm/src/layer/ffn.rs:25-27), stored as bf16 into out [M x N / 2] through the
 // same staging buffers and TMA stores as the plain epilogue.  The GEMM result itself never reaches memory.
-__device__ __forceinline__ void epilogue_rows_swiglu(const Params& p, const CUtensorMap* map_out, EpiWarp& ew, uint32_t tmem_acc,
+// `width` accumulator columns: gate in the first half, up in the second (256 for a whole tile, 128 for a half unit of
+// the last wave: 64 gate and the matching 64 up columns); n0 = the gate column (row of W) of accumulator column 0.
+__device__ __forceinline__ void epilogue_rows_swiglu(const Params& p, const CUtensorMap* map_out, EpiWarp& ew, uint32_t tmem_acc, int width,
                                                      int64_t m_warp0, int lane, int64_t n0, const float* scale_w) {
   const int64_t m = m_warp0 + lane;
   const bool row_ok = m < p.M;
   const float sa = row_ok && p.scale_a ? (p.scale_a_rows ? p.scale_a[m] : p.scale_a[0]) : 1.0f;
   const float sw0 = scale_w && !p.scale_w_rows ? scale_w[0] : 1.0f;
+  const int half_w = width >> 1;
+  const int64_t out0 = (n0 >> 8) * 128 + (n0 & 255);             // column of out [M x N / 2] that gate column n0 maps to
 #pragma unroll 1
-  for (int c = 0; c < 128; c += 64) {
+  for (int c = 0; c < half_w; c += 64) {
     const uint32_t buf = (ew.it & 1u) * 4096u;
     uint8_t* row = ew.smem_p + buf + lane * 128;
 #pragma unroll 1
@@ -301,7 +315,7 @@ __device__ __forceinline__ void epilogue_rows_swiglu(const Params& p, const CUte
       uint32_t g[32], u[32];
       __syncwarp();
       tmem_ld32(tmem_acc + c + 32 * sub, g);
-      tmem_ld32(tmem_acc + 128 + c + 32 * sub, u);
+      tmem_ld32(tmem_acc + half_w + c + 32 * sub, u);
       tmem_ld_wait();
       if (m_warp0 >= p.M) continue;                              // warp-uniform: nothing of these rows is inside the output
       if (sub == 0) {
@@ -331,7 +345,7 @@ __device__ __forceinline__ void epilogue_rows_swiglu(const Params& p, const CUte
     fence_async_smem();
     __syncwarp();
     if (lane == 0) {
-      tma_store_2d(map_out, ew.smem_u + buf, (int)(n0 / 2 + c), (int)m_warp0);
+      tma_store_2d(map_out, ew.smem_u + buf, (int)(out0 + c), (int)m_warp0);
       tma_store_commit();
     }
     ++ew.it;
@@ -586,8 +600,15 @@ __device__ __forceinline__ void gemm_tc2_body(const CUtensorMap& map_a, const CU
     int tile, mb, nb;
     if (u < p.full_units) { tile = u; c.half = 0; c.width = BN2; }
     else { const int v = u - p.full_units; tile = p.full_units + (v >> 1); c.half = v & 1; c.width = BN2 / 2; }
-    tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
-    c.a_row = mb * 256; c.w_row = nb * BN2 + c.half * (BN2 / 2); c.n0 = (int64_t)nb * BN2 + c.half * (BN2 / 2); c.sw_off = 0;
+    tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb, p.group_m > 0 ? p.group_m : GROUP_M, p.group_rot);
+    c.a_row = mb * 256; c.sw_off = 0;
+    if (p.act == 3) {
+      // SwiGLU pairs: a half unit takes 64 gate and the matching 64 up columns (CTA 0 loads the gate rows, CTA 1 the up rows);
+      // n0 is the gate column of the unit's first accumulator column
+      c.w_row = nb * BN2 + c.half * (BN2 / 4); c.n0 = (int64_t)nb * BN2 + c.half * (BN2 / 4);
+    } else {
+      c.w_row = nb * BN2 + c.half * (BN2 / 2); c.n0 = (int64_t)nb * BN2 + c.half * (BN2 / 2);
+    }
     return c;
   };
   const int num_kb = (int)((p.K + BK - 1) / BK);
@@ -638,7 +659,7 @@ __device__ __forceinline__ void gemm_tc2_body(const CUtensorMap& map_a, const CU
           if (rank == 0) mbar_expect_tx(full_bar(s), bytes);
           tma_load_2d_pair(sa, &map_a, leader_full, kb * BK, c.a_row + (int)rank * BM);
           if (width == BN2) tma_load_2d_pair(sb, &map_w, leader_full, kb * BK, c.w_row + (int)rank * (BN2 / 2));
-          else tma_load_2d_pair(sb, &map_w_half, leader_full, kb * BK, c.w_row + (int)rank * (BN2 / 4));
+          else tma_load_2d_pair(sb, &map_w_half, leader_full, kb * BK, c.w_row + (int)rank * (p.act == 3 ? BN2 / 2 : BN2 / 4));
         }
       }
       if (!ok) {   // give copies already issued time to land before shared memory is released
@@ -699,7 +720,7 @@ __device__ __forceinline__ void gemm_tc2_body(const CUtensorMap& map_a, const CU
         m_store = (int64_t)p.rs_rank * p.rs_rows + (m_warp0 - (int64_t)owner * p.rs_rows);
       }
       if (KIND == kF8 && p.act == 3)
-        epilogue_rows_swiglu(p, mo, ew, tmem_base + buf * BN2 + ((uint32_t)(q * 32) << 16), m_warp0, lane, c.n0,
+        epilogue_rows_swiglu(p, mo, ew, tmem_base + buf * BN2 + ((uint32_t)(q * 32) << 16), c.width, m_warp0, lane, c.n0,
                              p.scale_w ? p.scale_w + c.sw_off : nullptr);
       else
         epilogue_rows<KIND>(p, mo, ew, tmem_base + buf * BN2 + ((uint32_t)(q * 32) << 16), c.width, m_warp0, lane, c.n0,
@@ -814,8 +835,8 @@ int32_t launch2(b2q_handle h, const void* a, const void* w, Params p, const Scat
   const int max_pairs = h->sm_count / 2;
   // tail split: when the last wave fills at most half of the pairs, its tiles become two half-width units each
   const int rem = (int)(tiles % max_pairs);
-  // (not in SwiGLU-pair mode: a half-width unit would hold the gate or the up half of a tile only)
-  const bool split = tiles > max_pairs && rem > 0 && 2 * rem <= max_pairs && h->sw.no_tail_split < 0 && p.act != 3;
+  // (in SwiGLU-pair mode a half unit is 64 gate and the matching 64 up columns)
+  const bool split = tiles > max_pairs && rem > 0 && 2 * rem <= max_pairs && h->sw.no_tail_split < 0;
   p.full_units = split ? (int)(tiles - rem) : (int)tiles;
   p.total_units = split ? (int)(tiles + rem) : (int)tiles;
   const int pairs = (int)(p.total_units < max_pairs ? p.total_units : max_pairs);
@@ -846,7 +867,7 @@ int32_t launch2(b2q_handle h, const void* a, const void* w, Params p, const Scat
 }  // namespace tc
 
 int32_t b2q_validate_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,
-                              const float* scale_a, int ka, const float* scale_w, int kw, void* out, int out_type);
+                              const float* scale_a, int ka, const float* scale_w, int kw, void* out, int out_type, int64_t out_cols);
 
 int32_t b2q_gemm_fp8_skinny_dispatch(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,
                                      const float* scale_a, int ka, const float* scale_w, int kw, void* out, int out_type);
@@ -1007,6 +1028,16 @@ int32_t gemm_fp8_scatter(b2q_handle h, const uint8_t* a, const uint8_t* w, int64
   p.alpha = 1.0f;
   if (bias) { p.epi = 1; p.bias = bias; }
   p.rs_tp = tp; p.rs_rank = rank; p.rs_rows = (int)(M / tp);
+  // one raster group per owner (or several owners per group when an owner has less than a row tile), walked from the
+  // next rank's rows on: at every moment the ranks store into different inboxes
+  const int64_t tiles_m = ceil_div64(M, 256);
+  const int gm = p.rs_rows >= 256 && p.rs_rows % 256 == 0 ? (p.rs_rows / 256 < GROUP_M ? p.rs_rows / 256 : GROUP_M) : 0;
+  if (gm > 0 && tiles_m % gm == 0) {
+    p.group_m = gm;
+    const int ngroups = (int)(tiles_m / gm);
+    // rs_rows / 256 row tiles per owner, gm per group: the group in which the next rank's rows start
+    p.group_rot = (int)(((int64_t)((rank + 1) % tp) * (p.rs_rows / 256) / gm) % ngroups);
+  }
   return launch2<kF8>(h, a, w, p, &maps);
 }
 
@@ -1082,11 +1113,25 @@ int32_t b2q_grouped_gemm_fp8_rows_act(b2q_handle h, const uint8_t* a, const floa
   return tc::launch2_grouped(h, a, w, p, capacity_rows);
 }
 
+extern "C" int32_t b2q_gemm_fp8_scatter(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,
+                                        const float* scale_a, const float* scale_w, const float* bias, void* const* inbox, int tp, int rank) {
+  B2Q_REQUIRE_HANDLE(h);
+  if (M <= 0 || N <= 0 || K <= 0)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_DIMENSION, "GEMM dimensions must be non-zero: m=%lld, n=%lld, k=%lld", (long long)M, (long long)N, (long long)K);
+  if (!a || !w || !scale_a || !scale_w || !inbox || fmt < 0 || fmt > 1 || tp < 1 || tp > tc::kMaxScatterRanks || rank < 0 || rank >= tp)
+    B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemm_fp8_scatter: bad argument");
+  int32_t st = tc::gemm_fp8_scatter(h, a, w, M, N, K, fmt, scale_a, scale_w, bias, inbox, tp, rank);
+  if (st == B2Q_ERR_UNSUPPORTED)
+    B2Q_FAIL(h, B2Q_ERR_UNSUPPORTED, "gemm_fp8_scatter: needs M > 128, N > 128, M %% (32 * tp) == 0, N %% 8 == 0, K %% 16 == 0 and 16-byte aligned operands "
+             "(m=%lld, n=%lld, k=%lld, tp=%d)", (long long)M, (long long)N, (long long)K, tp);
+  return st;
+}
+
 extern "C" int32_t b2q_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,
                                 const float* scale_a, int scale_a_kind, const float* scale_w, int scale_w_kind, void* out,
                                 int out_type) {
   B2Q_REQUIRE_HANDLE(h);
-  int32_t st = b2q_validate_gemm_fp8(h, a, w, M, N, K, fmt, scale_a, scale_a_kind, scale_w, scale_w_kind, out, out_type);
+  int32_t st = b2q_validate_gemm_fp8(h, a, w, M, N, K, fmt, scale_a, scale_a_kind, scale_w, scale_w_kind, out, out_type, 0);
   if (st != B2Q_OK) return st;
   return tc::gemm_fp8_impl(h, a, w, M, N, K, fmt, scale_a, scale_a_kind, scale_w, scale_w_kind, out, out_type, nullptr);
 }
@@ -1101,7 +1146,7 @@ extern "C" int32_t b2q_gemm_fp8_ex(b2q_handle h, const b2q_gemm_fp8_desc* d) {
   const bool needs_bias = d->epilogue == B2Q_EPI_BIAS || d->epilogue == B2Q_EPI_BIAS_RELU;
   if (needs_bias && !d->bias) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "gemm_fp8_ex: this epilogue needs a bias vector");
   int32_t st = b2q_validate_gemm_fp8(h, d->a, d->w, d->m, d->n, d->k, d->fmt, d->scale_a, d->scale_a_kind, d->scale_w, d->scale_w_kind,
-                                     d->out, d->out_type);
+                                     d->out, d->out_type, d->epilogue == B2Q_EPI_SWIGLU ? d->n / 2 : 0);
   if (st != B2Q_OK) return st;
   const uint8_t* w = d->w;
   if (d->w_layout == B2Q_W_KN) {

@@ -5,9 +5,6 @@
 // grouped_gemm (crates/oxicuda-blas/src/batched/grouped_gemm.rs:46-78).
 #include "common.cuh"
 
-int32_t b2q_validate_gemm_fp8(b2q_handle h, const uint8_t* a, const uint8_t* w, int64_t M, int64_t N, int64_t K, int fmt,
-                              const float* scale_a, int ka, const float* scale_w, int kw, void* out, int out_type);
-
 namespace {
 
 // expert_buf[slot[i]] = in[token[i]] for every routed (token, expert) pair i; one warp per pair, 16-byte copies.

@@ -244,9 +244,14 @@ __global__ void __launch_bounds__(256, 1) tp_reduce_gather_kernel(const Peers pe
   }
   if (ok) {
     const uint4* res = reinterpret_cast<const uint4*>(my + off_result);
-    for (int r = 0; r < tp; ++r) {
-      if (r == rank) continue;
-      for (int64_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) *y_at(r, i) = __ldcg(res + r * slice16 + i);
+    for (int64_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) {   // every peer's piece in flight at once
+      uint4 v[kMaxRanks];
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r)
+        if (r < tp && r != rank) v[r] = __ldcg(res + r * slice16 + i);
+#pragma unroll
+      for (int r = 0; r < kMaxRanks; ++r)
+        if (r < tp && r != rank) *y_at(r, i) = v[r];
     }
   }
   __syncthreads();

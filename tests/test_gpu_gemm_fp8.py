@@ -245,12 +245,13 @@ def test_epilogue_ops_alpha_beta_bias_and_kn_layout(cuda, oracle, M, N, K):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("M,N,K", [(512, 1024, 512), (300, 512, 256), (48, 512, 512), (4096, 2048, 1024)])
+@pytest.mark.parametrize("M,N,K", [(512, 1024, 512), (300, 512, 256), (48, 512, 512), (4096, 2048, 1024), (2560, 2048, 256), (2304, 2304 * 2, 128)])
 def test_epilogue_swiglu_pairs(cuda, oracle, M, N, K):
     """EpilogueOp.SwiGluPairs: the gate | up GEMM over rows interleaved per 128 (b2q_interleave_rows128) writes
     silu(gate) * up [M x N / 2] (SwiGluExpert::forward, crates/oxicuda-moe/src/expert/ffn.rs:208-243; silu of
     crates/oxicuda-lm/src/layer/ffn.rs:25-27) from the epilogue of the two-CTA kernel (M > 128) or after the few-token
-    kernels (M = 48); checked against the oracle's f32 GEMM of the gate and of the up rows."""
+    kernels (M = 48); checked against the oracle's f32 GEMM of the gate and of the up rows.  The last two shapes have 80
+    and 162 tiles on 74 CTA pairs: their last wave runs as half units of 64 gate + 64 up columns."""
     from oxicuda_b200._lib import default_handle, ptr
     from oxicuda_b200.blas import EpilogueOp, gemm_fp8_ex
     from oxicuda_b200.quant import Fp8Codec
@@ -283,3 +284,39 @@ def test_epilogue_swiglu_pairs(cuda, oracle, M, N, K):
     assert got.shape == (M, F)
     rms = np.sqrt((ref ** 2).mean()) + 1e-30
     assert float((np.abs(got.double().cpu().numpy() - ref) / (np.abs(ref) + rms)).max()) <= 1e-2
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tp,M,N,K", [(2, 512, 384, 256), (4, 1024, 512, 512), (8, 2048, 256, 128), (4, 384, 1024, 1024)])
+def test_scatter_gemm_fills_every_owner_slot(cuda, tp, M, N, K):
+    """b2q_gemm_fp8_scatter, the GEMM half of the many-token row-parallel boundary, with all tp ranks played one after the
+    other on this GPU (the inboxes are plain local buffers; nothing in this kernel waits): after rank r's launch, slot r
+    of owner o's inbox holds rows [o M / tp, (o + 1) M / tp) of rank r's partial product, bit for bit what b2q_gemm_fp8
+    writes, with the bias on rank 0 only; slots of other ranks stay untouched."""
+    import ctypes as C
+    from oxicuda_b200 import _lib as L
+    from oxicuda_b200.blas import gemm_fp8, gemm_fp8_ex, EpilogueOp
+    from oxicuda_b200.quant import Fp8Codec
+    g = torch.Generator(device=cuda).manual_seed(tp * 1000 + M)
+    codec = Fp8Codec.e4m3("rne")
+    rows = M // tp
+    inbox = [torch.full((tp, rows, N), -7.0, dtype=torch.bfloat16, device=cuda) for _ in range(tp)]
+    ptrs = (C.c_void_p * tp)(*[t.data_ptr() for t in inbox])
+    bias = torch.randn(N, device=cuda, generator=g)
+    h = L.default_handle()
+    want = []
+    for r in range(tp):
+        ac, sa = codec.quantize_rows(torch.randn(M, K, device=cuda, generator=g), M, K)
+        wc, sw = codec.quantize_rows(torch.randn(N, K, device=cuda, generator=g) * 0.05, N, K)
+        ac, wc = ac.view(M, K), wc.view(N, K)
+        h.call("b2q_gemm_fp8_scatter", L.ptr(ac), L.ptr(wc), M, N, K, L.FP8_E4M3, L.ptr(sa), L.ptr(sw), L.ptr(bias) if r == 0 else None, ptrs, tp, r)
+        want.append(gemm_fp8_ex(ac, wc, sa, sw, bias=bias, epilogue=EpilogueOp.LinearCombinationBias) if r == 0 else gemm_fp8(ac, wc, sa, sw))
+        h.check()
+        for o in range(tp):                                   # slots of ranks that have not run yet are untouched
+            for later in range(r + 1, tp):
+                assert bool((inbox[o][later] == -7.0).all())
+    for r in range(tp):
+        for o in range(tp):
+            assert torch.equal(inbox[o][r], want[r][o * rows:(o + 1) * rows]), (r, o)
+    with pytest.raises(L.UnsupportedOperation):
+        h.call("b2q_gemm_fp8_scatter", L.ptr(ac), L.ptr(wc), 100, N, K, L.FP8_E4M3, L.ptr(sa), L.ptr(sw), None, ptrs, tp, 0)
