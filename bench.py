@@ -189,9 +189,12 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMV / GEMM / quantizer side measurements")
     ap.add_argument("--chunks", type=int, default=0, help="token chunks of the overlapped all-reduce (0 = automatic)")
     ap.add_argument("--case", default=None,
-                    help="run ONE kernel case a few times and exit (for ncu captures): gemm_fp8:M:N:K | gemv_fp4:K:N:tokens | gemv_int4:K:N:tokens:group | kv_quant:tokens:head_dim:axis:bf16 | rms_quant:rows:cols:residual | fp8_quant_rows:rows:cols:bf16 | swiglu_quant:rows:ffn | gemm_fp4_bs:tokens:N:K:mxfp8 | grouped_fp8:experts:rows_each:N:K")
+                    help="run ONE kernel case a few times and exit (for ncu captures): gemm_fp8:M:N:K | gemv_fp4:K:N:tokens | gemv_int4:K:N:tokens:group | kv_quant:tokens:head_dim:axis:bf16 | rms_quant:rows:cols:residual | fp8_quant_rows:rows:cols:bf16 | swiglu_quant:rows:ffn | gemm_fp4_bs:tokens:N:K:mxfp8 | grouped_fp8:experts:rows_each:N:K | tp_breakdown (under torchrun: the headline layer's pieces timed one by one on every rank)")
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args()
+    if args.case == "tp_breakdown":
+        run_tp_breakdown(args.iters)
+        return
     if args.case:
         run_case(args.case, args.iters)
         return
@@ -452,6 +455,77 @@ def oracle_mlp_check(shards, x_dev, y_host, rounding):
         total = part if total is None else total + part
     ref = torch.from_numpy(np.ascontiguousarray(total, np.float32)).to(torch.bfloat16).float()
     return _rel_err(y_host, ref)
+
+
+def run_tp_breakdown(iters: int):
+    """Under torchrun, one rank per GPU: the headline layer (this rank's shard) as a whole and piece by piece, CUDA events
+    around `iters` back-to-back calls after 3 warm-up calls, maximum over ranks.  `boundary` = whole layer minus the same
+    layer without its row-parallel boundary; `down_scatter_local` is the scatter GEMM storing into local buffers (the cost
+    of the epilogue without NVLink)."""
+    import ctypes as C
+    import torch
+    import torch.distributed as dist
+    from oxicuda_b200 import _lib as L
+    from oxicuda_b200._lib import default_handle, ptr
+    from oxicuda_b200.blas import EpilogueOp, gemm_fp8, gemm_fp8_ex
+    from oxicuda_b200.dist_infer import DistInferHandle, ParallelismConfig, TpFp8Mlp, tp_group
+    rank, world, lr = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(lr)
+    dev = torch.device("cuda", lr)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    h = DistInferHandle(rank, ParallelismConfig(tp=world))
+    iters = max(iters, 10)
+
+    def timeit(fn):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(iters):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / iters], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return round(float(t.item()) * 1e3, 1)
+
+    F = FFN // world
+    gen = torch.Generator(device=dev).manual_seed(1 + rank)
+    mk = lambda r, c: torch.randn(r, c, device=dev, generator=gen) * 0.01
+    mlp = TpFp8Mlp.from_shards(mk(F, HIDDEN), mk(F, HIDDEN), mk(HIDDEN, F), h)
+    x = torch.randn(TOKENS, HIDDEN, device=dev).to(torch.bfloat16)
+    y = torch.empty_like(x)
+    out = {"tp": world, "unit": "us", "layer": timeit(lambda: mlp.forward(x, out=y)), "layer_without_boundary": timeit(lambda: mlp.forward_partial(x))}
+    out["boundary"] = round(out["layer"] - out["layer_without_boundary"], 1)
+    codec = mlp.codec
+    xc, xs = codec.quantize_rows(x, TOKENS, HIDDEN)
+    out["quantize_x"] = timeit(lambda: codec.quantize_rows(x, TOKENS, HIDDEN))
+    hb = torch.empty(TOKENS, F, dtype=torch.bfloat16, device=dev)
+    out["gate_up_gemm_with_swiglu"] = timeit(lambda: gemm_fp8_ex(xc.view(TOKENS, HIDDEN), mlp.gu_codes, xs, mlp.gu_scales, out=hb, epilogue=EpilogueOp.SwiGluPairs))
+    hc, hs = codec.quantize_rows(hb, TOKENS, F)
+    out["quantize_h"] = timeit(lambda: codec.quantize_rows(hb, TOKENS, F))
+    yd = torch.empty(TOKENS, HIDDEN, dtype=torch.bfloat16, device=dev)
+    out["down_gemm"] = timeit(lambda: gemm_fp8(hc.view(TOKENS, F), mlp.down.codes, hs, mlp.down.scales, out=yd))
+    if world > 1:
+        rows = TOKENS // world
+        local = [torch.empty(world, rows, HIDDEN, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+        lp = (C.c_void_p * world)(*[t.data_ptr() for t in local])
+        hd = default_handle()
+        out["down_scatter_local"] = timeit(lambda: hd.call("b2q_gemm_fp8_scatter", ptr(hc), ptr(mlp.down.codes), TOKENS, HIDDEN, F, L.FP8_E4M3, ptr(hs),
+                                                           ptr(mlp.down.scales), None, lp, world, rank))
+        nvlink_bytes = 2 * (world - 1) / world * TOKENS * HIDDEN * 2        # per rank and direction: scatter + gather
+        out["nvlink_bytes_per_rank"] = int(nvlink_bytes)
+        out["boundary_floor_us_at_770GBs"] = round(nvlink_bytes / 770e9 * 1e6, 1)
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        tp_group(h).close()
+        dist.destroy_process_group()
 
 
 def run_case(case: str, iters: int):

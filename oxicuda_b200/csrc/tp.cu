@@ -206,7 +206,10 @@ __device__ __forceinline__ void add8_bf16(float (&acc)[8], const uint4 v, bool f
 // tp slots in rank order in fp32, write the bf16 sums into y and into every peer's result area, wait again, copy the
 // peers' rows out of my result area.  inbox: [tp][slice16] 16-byte units, result: [tp * slice16], both rows of n16 units;
 // y: the same rows at a pitch of y_pitch16 units (a column range of the full result).
-__global__ void __launch_bounds__(256, 1) tp_reduce_gather_kernel(const Peers peers, int tp, int rank, size_t off_inbox, size_t off_result,
+// TPM: ranks the instance covers (2, 4 or 8); U: pieces per thread and round, chosen so that TPM * U = 8 loads of 16 bytes
+// are in flight per thread whatever the group size (the kernel is bound by NVLink and HBM latency, not by arithmetic).
+template <int TPM, int U>
+__global__ void __launch_bounds__(512, 1) tp_reduce_gather_kernel(const Peers peers, int tp, int rank, size_t off_inbox, size_t off_result,
                                                                    int64_t slice16, int64_t n16, int64_t y_pitch16, uint4* __restrict__ y,
                                                                    int32_t* status) {
   __shared__ int s_abort;
@@ -218,40 +221,58 @@ __global__ void __launch_bounds__(256, 1) tp_reduce_gather_kernel(const Peers pe
   const int64_t per = (slice16 + G - 1) / G, i0 = cta * per, i1 = min(slice16, i0 + per);
   const int64_t rows_per = slice16 / n16;                                          // rows each rank owns
   auto y_at = [&](int r, int64_t i) { const int64_t row = i / n16; return y + (r * rows_per + row) * y_pitch16 + (i - row * n16); };
+  const int64_t step = (int64_t)blockDim.x * U;
   bool ok = peer_barrier(peers, tp, rank, 0, e, &s_abort);
   if (ok) {
     const uint4* in = reinterpret_cast<const uint4*>(my + off_inbox);
-    for (int64_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
-      uint4 v[kMaxRanks];
+    for (int64_t ib = i0 + threadIdx.x; ib < i1; ib += step) {
+      uint4 v[U][TPM];
 #pragma unroll
-      for (int r = 0; r < kMaxRanks; ++r)
-        if (r < tp) v[r] = __ldcg(in + r * slice16 + i);
-      float acc[8];
+      for (int u = 0; u < U; ++u) {
+        const int64_t i = ib + (int64_t)u * blockDim.x;
 #pragma unroll
-      for (int r = 0; r < kMaxRanks; ++r)
-        if (r < tp) add8_bf16(acc, v[r], r == 0);                // rank order: the reference's summation order
-      uint4 pk;
-      __nv_bfloat162 h0 = __floats2bfloat162_rn(acc[0], acc[1]), h1 = __floats2bfloat162_rn(acc[2], acc[3]);
-      __nv_bfloat162 h2 = __floats2bfloat162_rn(acc[4], acc[5]), h3 = __floats2bfloat162_rn(acc[6], acc[7]);
-      pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
-      pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
-      *y_at(rank, i) = pk;
+        for (int r = 0; r < TPM; ++r)
+          if (r < tp && i < i1) v[u][r] = __ldcg(in + r * slice16 + i);
+      }
 #pragma unroll
-      for (int r = 0; r < kMaxRanks; ++r)
-        if (r < tp && r != rank) reinterpret_cast<uint4*>(peers.base[r] + off_result)[rank * slice16 + i] = pk;
+      for (int u = 0; u < U; ++u) {
+        const int64_t i = ib + (int64_t)u * blockDim.x;
+        if (i >= i1) continue;
+        float acc[8];
+#pragma unroll
+        for (int r = 0; r < TPM; ++r)
+          if (r < tp) add8_bf16(acc, v[u][r], r == 0);             // rank order: the reference's summation order
+        uint4 pk;
+        __nv_bfloat162 h0 = __floats2bfloat162_rn(acc[0], acc[1]), h1 = __floats2bfloat162_rn(acc[2], acc[3]);
+        __nv_bfloat162 h2 = __floats2bfloat162_rn(acc[4], acc[5]), h3 = __floats2bfloat162_rn(acc[6], acc[7]);
+        pk.x = *reinterpret_cast<uint32_t*>(&h0); pk.y = *reinterpret_cast<uint32_t*>(&h1);
+        pk.z = *reinterpret_cast<uint32_t*>(&h2); pk.w = *reinterpret_cast<uint32_t*>(&h3);
+        *y_at(rank, i) = pk;
+#pragma unroll
+        for (int r = 0; r < TPM; ++r)
+          if (r < tp && r != rank) reinterpret_cast<uint4*>(peers.base[r] + off_result)[rank * slice16 + i] = pk;
+      }
     }
     ok = peer_barrier(peers, tp, rank, 1, e, &s_abort);
   }
   if (ok) {
     const uint4* res = reinterpret_cast<const uint4*>(my + off_result);
-    for (int64_t i = i0 + threadIdx.x; i < i1; i += blockDim.x) {   // every peer's piece in flight at once
-      uint4 v[kMaxRanks];
+    for (int64_t ib = i0 + threadIdx.x; ib < i1; ib += step) {     // every peer's pieces in flight at once
+      uint4 v[U][TPM];
 #pragma unroll
-      for (int r = 0; r < kMaxRanks; ++r)
-        if (r < tp && r != rank) v[r] = __ldcg(res + r * slice16 + i);
+      for (int u = 0; u < U; ++u) {
+        const int64_t i = ib + (int64_t)u * blockDim.x;
 #pragma unroll
-      for (int r = 0; r < kMaxRanks; ++r)
-        if (r < tp && r != rank) *y_at(r, i) = v[r];
+        for (int r = 0; r < TPM; ++r)
+          if (r < tp && r != rank && i < i1) v[u][r] = __ldcg(res + r * slice16 + i);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int64_t i = ib + (int64_t)u * blockDim.x;
+#pragma unroll
+        for (int r = 0; r < TPM; ++r)
+          if (r < tp && r != rank && i < i1) *y_at(r, i) = v[u][r];
+      }
     }
   }
   __syncthreads();
@@ -387,11 +408,19 @@ static int32_t scatter_reduce_cols(b2q_tp t, const uint8_t* x_codes, const float
     B2Q_CUDA(h, cudaStreamWaitEvent(rs, t->ev_ready[chunk], 0));
   }
   const int64_t n16 = nc * 2 / 16, slice16 = (tokens / t->tp) * n16;
-  int grid = (int)((slice16 + 255) / 256);
+  // alone on the stream: 512 threads per CTA; under the next chunk's GEMM: 256 threads and no shared memory beyond one word,
+  // a CTA that fits beside a resident GEMM CTA
+  const int threads = chunks > 1 ? 256 : 512;
+  int grid = (int)((slice16 + threads - 1) / threads);
   grid = grid < 1 ? 1 : (grid > kMaxCtas ? kMaxCtas : grid);
-  // 256 threads and no shared memory beyond one word: such a CTA fits beside a resident GEMM CTA
-  tp_reduce_gather_kernel<<<grid, 256, 0, rs>>>(t->peers, t->tp, t->rank, kBigInboxOff + off, kBigResultOff + off, slice16, n16, N * 2 / 16,
-                                                reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(y) + (size_t)chunk * nc * 2), h->d_status);
+  uint4* yc = reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(y) + (size_t)chunk * nc * 2);
+#define B2Q_RG_LAUNCH(TPM, U)                                                                                                          \
+  tp_reduce_gather_kernel<TPM, U><<<grid, threads, 0, rs>>>(t->peers, t->tp, t->rank, kBigInboxOff + off, kBigResultOff + off, slice16, n16, \
+                                                            N * 2 / 16, yc, h->d_status)
+  if (t->tp <= 2) B2Q_RG_LAUNCH(2, 4);
+  else if (t->tp <= 4) B2Q_RG_LAUNCH(4, 2);
+  else B2Q_RG_LAUNCH(8, 1);
+#undef B2Q_RG_LAUNCH
   B2Q_LAUNCH_CHECK(h, "tp_reduce_gather_kernel");
   if (chunks > 1 && chunk == chunks - 1) {
     B2Q_CUDA(h, cudaEventRecord(t->ev_done, rs));
@@ -493,7 +522,11 @@ int32_t b2q_tp_create(b2q_handle h, void* nccl_comm, int tp, int rank, b2q_tp* o
   bool ok = cudaStreamCreateWithPriority(&t->comm_stream, cudaStreamNonBlocking, prio_hi) == cudaSuccess;
   // an SM keeps one shared-memory split while CTAs are resident: the sum-and-gather kernel asks for the split the GEMM
   // CTAs run under (all of it shared), or it could not become resident beside them, nor they beside it
-  ok = ok && cudaFuncSetAttribute(tpx::tp_reduce_gather_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+  ok = ok && cudaFuncSetAttribute(tpx::tp_reduce_gather_kernel<2, 4>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                  (int)cudaSharedmemCarveoutMaxShared) == cudaSuccess;
+  ok = ok && cudaFuncSetAttribute(tpx::tp_reduce_gather_kernel<4, 2>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                  (int)cudaSharedmemCarveoutMaxShared) == cudaSuccess;
+  ok = ok && cudaFuncSetAttribute(tpx::tp_reduce_gather_kernel<8, 1>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                   (int)cudaSharedmemCarveoutMaxShared) == cudaSuccess;
   for (int i = 0; i < 16 && ok; ++i) ok = cudaEventCreateWithFlags(&t->ev_ready[i], cudaEventDisableTiming) == cudaSuccess;
   ok = ok && cudaEventCreateWithFlags(&t->ev_done, cudaEventDisableTiming) == cudaSuccess;
