@@ -540,11 +540,12 @@ def run_case(case: str, iters: int):
         print(json.dumps(quantizer_measurements(dev, load_peaks()), indent=1))
         return
     d = [int(v) for v in dims]
-    if kind == "gemm_fp8":
+    if kind in ("gemm_fp8", "gemm_fp8_rows"):      # gemm_fp8: per-tensor scales; gemm_fp8_rows: per-token and per-output-row scales
         m, n, k = d
         codec = Fp8Codec.e4m3("rne")
-        ac, sa = codec.quantize_rows(torch.randn(m, k, device=dev), 1, m * k)
-        wc, sw = codec.quantize_rows(torch.randn(n, k, device=dev) * 0.02, 1, n * k)
+        rows = kind == "gemm_fp8_rows"
+        ac, sa = codec.quantize_rows(torch.randn(m, k, device=dev), m if rows else 1, k if rows else m * k)
+        wc, sw = codec.quantize_rows(torch.randn(n, k, device=dev) * 0.02, n if rows else 1, k if rows else n * k)
         out = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
         fn = lambda: gemm_fp8(ac.view(m, k), wc.view(n, k), sa, sw, out=out)
         work, unit = 2.0 * m * n * k / 1e12, "TFLOP/s"

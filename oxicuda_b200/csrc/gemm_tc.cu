@@ -126,6 +126,17 @@ __device__ __forceinline__ float epi_apply(const Params& p, float v, float c_old
   return v;
 }
 
+// Eight consecutive per-column weight scales (every lane of the warp needs the same eight: one 16-byte load serves four).
+__device__ __forceinline__ void load_sw8(const float* scale_w, int64_t n, int64_t N, bool vec, float (&sw)[8]) {
+  if (vec) {
+    const float4 a = __ldg(reinterpret_cast<const float4*>(scale_w + n)), b = __ldg(reinterpret_cast<const float4*>(scale_w + n + 4));
+    sw[0] = a.x; sw[1] = a.y; sw[2] = a.z; sw[3] = a.w; sw[4] = b.x; sw[5] = b.y; sw[6] = b.z; sw[7] = b.w;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sw[i] = n + i < N ? __ldg(scale_w + n + i) : 0.0f;
+  }
+}
+
 // Scales, converts and stores 32 consecutive accumulator columns of one output row.
 template <int KIND>
 __device__ __forceinline__ void store_chunk(const Params& p, const uint32_t (&r)[32], int64_t m, int64_t n, float sa, float sw0) {
@@ -201,14 +212,34 @@ __device__ __forceinline__ void store_chunk(const Params& p, const uint32_t (&r)
 // TMA clips rows >= M and columns >= N.  Other outputs (INT8 accumulators, odd pitches) store from registers.
 struct EpiWarp { uint32_t smem_u; uint8_t* smem_p; uint32_t it; };
 
+// The scales one warp needs for one unit, fetched BEFORE the accumulator is waited for (so their latency hides behind the
+// MMAs instead of sitting in every chunk of the epilogue): sa, the scale of this lane's row, and eight consecutive
+// per-column weight scales per lane, handed round with shuffles.  Plain: lane l holds columns [8 l, 8 l + 8) of the
+// unit.  SwiGLU pairs: lanes [0, width / 16) hold the gate columns, the next width / 16 lanes the matching up columns
+// (128 rows of W further on).
+struct TileScales { float sw[8]; float sa; };
+__device__ __forceinline__ TileScales prefetch_scales(const Params& p, const float* scale_w, int64_t n0, int width, int64_t m, bool swiglu, int lane) {
+  TileScales t;
+  t.sa = (m < p.M && p.scale_a) ? (p.scale_a_rows ? __ldg(p.scale_a + m) : __ldg(p.scale_a)) : 1.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) t.sw[i] = 1.0f;
+  if (scale_w && p.scale_w_rows) {
+    const int half_l = width >> 4;
+    const bool live = swiglu ? lane < 2 * half_l : 8 * lane < width;
+    const int64_t idx = !swiglu ? n0 + 8 * lane : (lane < half_l ? n0 + 8 * lane : n0 + 128 + 8 * (lane - half_l));
+    if (live) load_sw8(scale_w, idx, p.N, idx + 8 <= p.N && (reinterpret_cast<uintptr_t>(scale_w + idx) & 15) == 0, t.sw);
+  }
+  return t;
+}
+
 template <int KIND>
 __device__ __forceinline__ void epilogue_rows(const Params& pp, const CUtensorMap* map_out, EpiWarp& ew, uint32_t tmem_acc, int width,
-                                              int64_t m_warp0, int lane, int64_t n0, const float* scale_w, int64_t m_store) {
+                                              int64_t m_warp0, int lane, int64_t n0, const float* scale_w, int64_t m_store, const TileScales& ts) {
   Params p = pp;
   p.scale_w = scale_w;                       // this tile's weight scales (grouped mode: the problem's slice)
   const int64_t m = m_warp0 + lane;
   const bool row_ok = m < p.M;
-  const float sa = row_ok && p.scale_a ? (p.scale_a_rows ? p.scale_a[m] : p.scale_a[0]) : 1.0f;
+  const float sa = ts.sa;
   const float sw0 = p.scale_w && !p.scale_w_rows ? p.scale_w[0] : 1.0f;
   if constexpr (KIND != kI8) {
     if (p.tma_store) {
@@ -230,12 +261,13 @@ __device__ __forceinline__ void epilogue_rows(const Params& pp, const CUtensorMa
         if (bf16) {
 #pragma unroll
           for (int j = 0; j < 64; j += 8) {
-            float v[8];
+            float v[8], sw[8];
+            if (p.scale_w_rows) {                                // columns c + j .. c + j + 7 of the unit: lane (c + j) / 8 holds them
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const float sw = p.scale_w_rows ? (n + j + i < p.N ? __ldg(p.scale_w + n + j + i) : 0.0f) : sw0;
-              v[i] = __uint_as_float(r[j + i]) * (sa * sw);
+              for (int i = 0; i < 8; ++i) sw[i] = __shfl_sync(0xffffffffu, ts.sw[i], (c + j) >> 3);
             }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[j + i]) * (sa * (p.scale_w_rows ? sw[i] : sw0));
             if (p.epi) {
 #pragma unroll
               for (int i = 0; i < 8; ++i) {
@@ -255,9 +287,16 @@ __device__ __forceinline__ void epilogue_rows(const Params& pp, const CUtensorMa
 #pragma unroll
           for (int j = 0; j < 32; j += 4) {
             float v[4];
+            float4 sw4 = make_float4(sw0, sw0, sw0, sw0);
+            if (p.scale_w_rows) {
+              const int src = (c + j) >> 3;
+              sw4.x = __shfl_sync(0xffffffffu, ts.sw[(j & 4) + 0], src); sw4.y = __shfl_sync(0xffffffffu, ts.sw[(j & 4) + 1], src);
+              sw4.z = __shfl_sync(0xffffffffu, ts.sw[(j & 4) + 2], src); sw4.w = __shfl_sync(0xffffffffu, ts.sw[(j & 4) + 3], src);
+            }
+            const float swa[4] = {sw4.x, sw4.y, sw4.z, sw4.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const float sw = p.scale_w_rows ? (n + j + i < p.N ? __ldg(p.scale_w + n + j + i) : 0.0f) : sw0;
+              const float sw = swa[i];
               v[i] = __uint_as_float(r[j + i]) * (sa * sw);
               if (p.epi) {
                 const bool in = row_ok && n + j + i < p.N;
@@ -299,10 +338,8 @@ __device__ __forceinline__ void epilogue_rows(const Params& pp, const CUtensorMa
 // `width` accumulator columns: gate in the first half, up in the second (256 for a whole tile, 128 for a half unit of
 // the last wave: 64 gate and the matching 64 up columns); n0 = the gate column (row of W) of accumulator column 0.
 __device__ __forceinline__ void epilogue_rows_swiglu(const Params& p, const CUtensorMap* map_out, EpiWarp& ew, uint32_t tmem_acc, int width,
-                                                     int64_t m_warp0, int lane, int64_t n0, const float* scale_w) {
-  const int64_t m = m_warp0 + lane;
-  const bool row_ok = m < p.M;
-  const float sa = row_ok && p.scale_a ? (p.scale_a_rows ? p.scale_a[m] : p.scale_a[0]) : 1.0f;
+                                                     int64_t m_warp0, int lane, int64_t n0, const float* scale_w, const TileScales& ts) {
+  const float sa = ts.sa;
   const float sw0 = scale_w && !p.scale_w_rows ? scale_w[0] : 1.0f;
   const int half_w = width >> 1;
   const int64_t out0 = (n0 >> 8) * 128 + (n0 & 255);             // column of out [M x N / 2] that gate column n0 maps to
@@ -325,11 +362,19 @@ __device__ __forceinline__ void epilogue_rows_swiglu(const Params& p, const CUte
       const int64_t ng = n0 + c + 32 * sub;                      // gate column of g[0]; its up column is ng + 128
 #pragma unroll
       for (int j = 0; j < 32; j += 8) {
-        float h[8];
+        float h[8], swgv[8], swuv[8];
+        if (p.scale_w_rows) {                                    // gate column c + 32 sub + j of the unit and its up partner
+          const int src = (c + 32 * sub + j) >> 3;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            swgv[i] = __shfl_sync(0xffffffffu, ts.sw[i], src);
+            swuv[i] = __shfl_sync(0xffffffffu, ts.sw[i], (width >> 4) + src);
+          }
+        }
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const float swg = p.scale_w_rows ? __ldg(scale_w + ng + j + i) : sw0;
-          const float swu = p.scale_w_rows ? __ldg(scale_w + ng + 128 + j + i) : sw0;
+          const float swg = p.scale_w_rows ? swgv[i] : sw0;
+          const float swu = p.scale_w_rows ? swuv[i] : sw0;
           const float gg = __uint_as_float(g[j + i]) * (sa * swg), uu = __uint_as_float(u[j + i]) * (sa * swu);
           h[i] = gg * uu * __frcp_rn(1.0f + exp2f(-1.4426950408889634f * gg));
         }
@@ -465,10 +510,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
       int mb, nb;
       tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
       const uint32_t buf = tile_it & 1, aph = (tile_it >> 1) & 1;
+      const TileScales ts = prefetch_scales(p, p.scale_w, (int64_t)nb * BN, BN, (int64_t)mb * BM + q * 32 + lane, false, lane);
       if (!mbar_wait(tfull_bar(buf), aph, abort_flag)) { ok = false; break; }
       tc_fence_after();
       epilogue_rows<KIND>(p, &map_out, ew, tmem_base + buf * BN + ((uint32_t)(q * 32) << 16), BN, (int64_t)mb * BM + q * 32, lane,
-                          (int64_t)nb * BN, p.scale_w, (int64_t)mb * BM + q * 32);
+                          (int64_t)nb * BN, p.scale_w, (int64_t)mb * BM + q * 32, ts);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(buf));
@@ -709,9 +755,11 @@ __device__ __forceinline__ void gemm_tc2_body(const CUtensorMap& map_a, const CU
     for (int u = pair; u < total_units && ok; u += num_pairs, ++tile_it) {
       const Unit c = unit_coords(u);
       const uint32_t buf = tile_it & 1, aph = (tile_it >> 1) & 1;
+      const int64_t m_warp0 = (int64_t)c.a_row + rank * BM + q * 32;
+      const bool swiglu = KIND == kF8 && p.act == 3;
+      const TileScales ts = prefetch_scales(p, p.scale_w ? p.scale_w + c.sw_off : nullptr, c.n0, c.width, m_warp0 + lane, swiglu, lane);
       if (!mbar_wait(tfull_bar(buf), aph, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      const int64_t m_warp0 = (int64_t)c.a_row + rank * BM + q * 32;
       const CUtensorMap* mo = &map_out;
       int64_t m_store = m_warp0;
       if (scatter_maps) {                               // this warp's 32 rows belong to one rank (rs_rows is a multiple of 32)
@@ -719,12 +767,12 @@ __device__ __forceinline__ void gemm_tc2_body(const CUtensorMap& map_a, const CU
         mo = scatter_maps + owner;
         m_store = (int64_t)p.rs_rank * p.rs_rows + (m_warp0 - (int64_t)owner * p.rs_rows);
       }
-      if (KIND == kF8 && p.act == 3)
+      if (swiglu)
         epilogue_rows_swiglu(p, mo, ew, tmem_base + buf * BN2 + ((uint32_t)(q * 32) << 16), c.width, m_warp0, lane, c.n0,
-                             p.scale_w ? p.scale_w + c.sw_off : nullptr);
+                             p.scale_w ? p.scale_w + c.sw_off : nullptr, ts);
       else
         epilogue_rows<KIND>(p, mo, ew, tmem_base + buf * BN2 + ((uint32_t)(q * 32) << 16), c.width, m_warp0, lane, c.n0,
-                            p.scale_w ? p.scale_w + c.sw_off : nullptr, m_store);
+                            p.scale_w ? p.scale_w + c.sw_off : nullptr, m_store, ts);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(tempty_bar(buf), 0));   // the leader's MMA thread waits for both CTAs
