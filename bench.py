@@ -30,6 +30,7 @@ sys.path.insert(0, str(ROOT))
 # Headline workload, the same at every GPU count (strong scaling): the tensor-parallel FP8 SwiGLU MLP of a
 # 70B-shaped layer (hidden 8192, FFN 28672, 4096 tokens): gate/up column-parallel, down row-parallel, sum over ranks.
 HIDDEN, FFN, TOKENS = 8192, 28672, 4096
+NCU_DRAM_BYTES_GATE_UP_TP1 = 1916283392 + 229755136      # gate | up GEMM with the SwiGLU epilogue, 4096 x 57344 x 8192
 FLOP_PER_STEP = 6.0 * TOKENS * HIDDEN * FFN
 WORKLOAD = "tp_fp8_e4m3_swiglu_mlp_hidden8192_ffn28672_tokens4096_bf16out"
 M = N = K = 4096                                    # the single-GEMM configuration, reported in roofline.gemm_fp8_4096
@@ -406,7 +407,11 @@ def main():
         cfg.update({"encoder": args.rounding, "l2": "weights alone (705 MB / tp per rank) exceed the 126 MB L2; activations rotate over 3 sets",
                     "tile": f"{tile.tile_m}x{tile.tile_n}x{tile.tile_k}", "kernel_id": kid})
         roofline = {"bound": "tensor", "kernel": f"gemm_tc2_kernel<fp8> on this rank's gate|up GEMM {TOKENS}x{2 * F}x{HIDDEN}",
-                    "achieved": gemm_tflops, "peak": fp8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak, "traffic": None,
+                    "achieved": gemm_tflops, "peak": fp8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak,
+                    # dram__bytes_read.sum + dram__bytes_write.sum of this launch at tp = 1 (one-pass ncu capture of the bench command,
+                    # profiles/tp_mlp_step_launches.md); not captured for the shards of tp > 1
+                    "traffic": NCU_DRAM_BYTES_GATE_UP_TP1 if world == 1 else None,
+                    "algorithmic_bytes": TOKENS * HIDDEN + 2 * F * HIDDEN + TOKENS * F * 2,
                     "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}): the step runs for milliseconds under the power cap, "
                                    "and dense FP8 issues at twice the bf16 rate",
                     "frac_of_nominal_4500": gemm_tflops / 4500.0, "us_per_launch": gemm_sec * 1e6,

@@ -703,16 +703,41 @@ template <> __device__ __forceinline__ void load_chunk8<__nv_bfloat16>(const __n
   for (int j = 0; j < 4; ++j) { v[2 * j] = __uint_as_float(w[j] << 16); v[2 * j + 1] = __uint_as_float(w[j] & 0xFFFF0000u); }
 }
 
-// Two RNE codes of (x0, x1) / scale without a division where that is provably the same.  r_lo and r_hi are RN(1 / scale)
+// RNE codes of x / scale without a division where that is provably the same.  r_lo and r_hi are RN(1 / scale)
 // narrowed and widened by 2^-21: the exact quotient lies between x * r_lo and x * r_hi (three roundings of 2^-24 each
 // against a margin of 2^-21), the saturating conversion is monotonic, so if both ends convert to the same code every
 // value between them does.  Otherwise (a quotient within 2^-20 of a rounding boundary) the IEEE division decides.
-__device__ __forceinline__ uint32_t fp8x2_quotient_rne(float x0, float x1, float scale, float r_lo, float r_hi, int fmt) {
-  const __nv_fp8_interpretation_t f = fmt == 0 ? __NV_E4M3 : __NV_E5M2;
-  uint32_t lo = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(x0, r_lo), __fmul_rn(x1, r_lo)), __NV_SATFINITE, f);
-  const uint32_t hi = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__fmul_rn(x0, r_hi), __fmul_rn(x1, r_hi)), __NV_SATFINITE, f);
-  if (lo != hi) lo = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(x0, scale), __fdiv_rn(x1, scale)), __NV_SATFINITE, f);
-  return lo;
+// (x0, x1) * r in one instruction: the packed fp32 multiply of sm_100 (each lane rounded to nearest even, as __fmul_rn).
+__device__ __forceinline__ float2 mul2_rn(float x0, float x1, float r) {
+  float2 o;
+  asm("{\n\t.reg .b64 a, b, c;\n\tmov.b64 a, {%2, %3};\n\tmov.b64 b, {%4, %4};\n\tmul.rn.f32x2 c, a, b;\n\tmov.b64 {%0, %1}, c;\n\t}"
+      : "=f"(o.x), "=f"(o.y) : "f"(x0), "f"(x1), "f"(r));
+  return o;
+}
+// Eight RNE codes of v / scale.  With the bracket: both ends of every pair are converted and compared once per eight
+// values; if any pair disagrees (about one chunk in 10^4) the eight are divided.  The format is a template parameter so
+// that one conversion instruction is emitted, not a selection between two.
+template <bool E5M2>
+__device__ __forceinline__ void fp8x8_quotient_rne(const float (&v)[8], float scale, float r_lo, float r_hi, bool bracket, uint32_t& lo, uint32_t& hi) {
+  constexpr __nv_fp8_interpretation_t f = E5M2 ? __NV_E5M2 : __NV_E4M3;
+  uint32_t p[4];
+  bool redo = !bracket;
+  if (bracket) {
+    uint32_t diff = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      p[j] = (uint32_t)__nv_cvt_float2_to_fp8x2(mul2_rn(v[2 * j], v[2 * j + 1], r_lo), __NV_SATFINITE, f);
+      diff |= p[j] ^ (uint32_t)__nv_cvt_float2_to_fp8x2(mul2_rn(v[2 * j], v[2 * j + 1], r_hi), __NV_SATFINITE, f);
+    }
+    redo = diff != 0;
+  }
+  if (redo) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      p[j] = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v[2 * j], scale), __fdiv_rn(v[2 * j + 1], scale)), __NV_SATFINITE, f);
+  }
+  lo = __byte_perm(p[0], p[1], 0x5410);
+  hi = __byte_perm(p[2], p[3], 0x5410);
 }
 // The bracket needs a normal scale and a normal reciprocal; rows outside (all-zero rows have scale 1) divide.
 __device__ __forceinline__ bool quotient_bracket(float scale, float& r_lo, float& r_hi) {
@@ -759,73 +784,94 @@ template <> struct RawChunk<__nv_bfloat16> {
 };
 
 // FULL: every thread has all NCH chunks (cols == 8 * NCH * blockDim), so the bounds predicates drop out.
-template <typename T, int NCH, bool FULL>
-__global__ void __launch_bounds__(1024) fp8_quantize_rows_reg_kernel(const T* __restrict__ x, int64_t cols, StatArgs a, int fmt, int rounding,
-                                                                     uint8_t* __restrict__ codes) {
-  __shared__ uint32_t sh_amax[32];
-  const int64_t r = blockIdx.x;
-  const T* row = x + r * cols;
+// A CTA walks rows blockIdx.x, blockIdx.x + gridDim.x, ...  PIPE (long rows, CTAs of 512 threads or more, of which only one or
+// two fit an SM): the NEXT row's chunks are fetched before the current row is reduced and encoded, so loads stay in flight
+// through the barrier (4096 x 28672 bf16: 105 -> 88 us).  Short rows run one row per CTA with many CTAs per SM, where the
+// second register set only costs occupancy (8192 x 8192 bf16: 45 us without, 50 us with).
+template <typename T, int NCH, bool FULL, bool PIPE>
+__global__ void __launch_bounds__(1024) fp8_quantize_rows_reg_kernel(const T* __restrict__ x, int64_t rows, int64_t cols, StatArgs a, int fmt,
+                                                                     int rounding, uint8_t* __restrict__ codes) {
+  __shared__ uint32_t sh_amax[2][32];
   const int chunks = (int)(cols >> 3);
-  RawChunk<T> raw[NCH];
-  uint32_t mb = 0;
-#pragma unroll
-  for (int k = 0; k < NCH; ++k) {
-    const int c = (int)threadIdx.x + k * (int)blockDim.x;
-    if (FULL || c < chunks) raw[k].load(row, c);
-  }
-#pragma unroll
-  for (int k = 0; k < NCH; ++k) {
-    const int c = (int)threadIdx.x + k * (int)blockDim.x;
-    if (FULL || c < chunks) mb = raw[k].amax_bits(mb);
-  }
-  if constexpr (sizeof(T) == 2) {                                                 // the larger lane (NaN: 0x7FFF), as f32 bits
-    const uint32_t hi = mb >> 16, lo = mb & 0xFFFFu;
-    mb = max(hi, lo) << 16;
-  }
-  mb = __reduce_max_sync(0xffffffffu, mb);
-  if ((threadIdx.x & 31) == 0) sh_amax[threadIdx.x >> 5] = mb;
-  __syncthreads();
-  const int nw = blockDim.x >> 5;
-  mb = (int)(threadIdx.x & 31) < nw ? sh_amax[threadIdx.x & 31] : 0u;
-  mb = __reduce_max_sync(0xffffffffu, mb);
-  const int bad = mb >= 0x7F800000u;
-  const float amax = bad ? 0.0f : __uint_as_float(mb);
-  if (threadIdx.x == 0) finish_row(a, r, RowStat{0.0f, 0.0f, amax, bad});   // kFp8Scale reads amax and bad only
   const Fp8Fmt F = fp8_fmt(fmt);
-  const float scale = amax > 0.0f ? __fdiv_rn(amax, F.max_val) : 1.0f;      // finish_row's value
-  float r_lo, r_hi;
-  const bool bracket = quotient_bracket(scale, r_lo, r_hi);
-  uint2* out = reinterpret_cast<uint2*>(codes + r * cols);
+  // the next row's chunks are held only where two sets fit the register budget of a 1024-thread CTA (up to 16 registers
+  // a set: bf16 rows of up to 32768 elements, f32 rows of up to 4096); longer rows load at the top of their iteration
+  constexpr bool PREFETCH = PIPE && sizeof(RawChunk<T>) * NCH <= 64;
+  RawChunk<T> raw[NCH], nxt[PREFETCH ? NCH : 1];
+  int64_t r = blockIdx.x;
+  if (PREFETCH && r < rows) {
 #pragma unroll
-  for (int k = 0; k < NCH; ++k) {
-    const int c = (int)threadIdx.x + k * (int)blockDim.x;
-    if (FULL || c < chunks) {
-      float v[8];
-      raw[k].get(v);
-      uint32_t lo = 0, hi = 0;
-      if (rounding == 1) {   // the conversion saturates at +-max_val, which is what the clamp of the other path does
-        uint32_t p[4];
-        if (bracket) {
+    for (int k = 0; k < NCH; ++k) {
+      const int c = (int)threadIdx.x + k * (int)blockDim.x;
+      if (FULL || c < chunks) raw[k].load(x + r * cols, c);
+    }
+  }
+  for (int it = 0; r < rows && (PIPE || it == 0); r += gridDim.x, ++it) {     // !PIPE: one row per CTA (the grid is the row count)
+    const int64_t rn = r + gridDim.x;
+    if constexpr (PREFETCH) {
+      if (rn < rows) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) p[j] = fp8x2_quotient_rne(v[2 * j], v[2 * j + 1], scale, r_lo, r_hi, fmt);
-        } else {
-#pragma unroll
-          for (int j = 0; j < 4; ++j)
-            p[j] = (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v[2 * j], scale), __fdiv_rn(v[2 * j + 1], scale)),
-                                                      __NV_SATFINITE, fmt == 0 ? __NV_E4M3 : __NV_E5M2);
-        }
-        lo = __byte_perm(p[0], p[1], 0x5410);
-        hi = __byte_perm(p[2], p[3], 0x5410);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          float q = __fdiv_rn(v[j], scale);
-          q = q < -F.max_val ? -F.max_val : (q > F.max_val ? F.max_val : q);
-          const uint32_t b = fp8_encode_ref_dev(q, F);
-          if (j < 4) lo |= b << (8 * j); else hi |= b << (8 * (j - 4));
+        for (int k = 0; k < NCH; ++k) {
+          const int c = (int)threadIdx.x + k * (int)blockDim.x;
+          if (FULL || c < chunks) nxt[k].load(x + rn * cols, c);
         }
       }
-      out[c] = make_uint2(lo, hi);
+    } else {
+#pragma unroll
+      for (int k = 0; k < NCH; ++k) {
+        const int c = (int)threadIdx.x + k * (int)blockDim.x;
+        if (FULL || c < chunks) raw[k].load(x + r * cols, c);
+      }
+    }
+    uint32_t mb = 0;
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      const int c = (int)threadIdx.x + k * (int)blockDim.x;
+      if (FULL || c < chunks) mb = raw[k].amax_bits(mb);
+    }
+    if constexpr (sizeof(T) == 2) {                                               // the larger lane (NaN: 0x7FFF), as f32 bits
+      const uint32_t hi = mb >> 16, lo = mb & 0xFFFFu;
+      mb = max(hi, lo) << 16;
+    }
+    mb = __reduce_max_sync(0xffffffffu, mb);
+    uint32_t* sh = sh_amax[it & 1];                                               // two sets: one barrier per row is enough
+    if ((threadIdx.x & 31) == 0) sh[threadIdx.x >> 5] = mb;
+    __syncthreads();
+    const int nw = blockDim.x >> 5;
+    mb = (int)(threadIdx.x & 31) < nw ? sh[threadIdx.x & 31] : 0u;
+    mb = __reduce_max_sync(0xffffffffu, mb);
+    const int bad = mb >= 0x7F800000u;
+    const float amax = bad ? 0.0f : __uint_as_float(mb);
+    if (threadIdx.x == 0) finish_row(a, r, RowStat{0.0f, 0.0f, amax, bad});   // kFp8Scale reads amax and bad only
+    const float scale = amax > 0.0f ? __fdiv_rn(amax, F.max_val) : 1.0f;      // finish_row's value
+    float r_lo, r_hi;
+    const bool bracket = quotient_bracket(scale, r_lo, r_hi);
+    uint2* out = reinterpret_cast<uint2*>(codes + r * cols);
+#pragma unroll
+    for (int k = 0; k < NCH; ++k) {
+      const int c = (int)threadIdx.x + k * (int)blockDim.x;
+      if (FULL || c < chunks) {
+        float v[8];
+        raw[k].get(v);
+        uint32_t lo = 0, hi = 0;
+        if (rounding == 1) {   // the conversion saturates at +-max_val, which is what the clamp of the other path does
+          if (fmt == 0) fp8x8_quotient_rne<false>(v, scale, r_lo, r_hi, bracket, lo, hi);
+          else fp8x8_quotient_rne<true>(v, scale, r_lo, r_hi, bracket, lo, hi);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float q = __fdiv_rn(v[j], scale);
+            q = q < -F.max_val ? -F.max_val : (q > F.max_val ? F.max_val : q);
+            const uint32_t b = fp8_encode_ref_dev(q, F);
+            if (j < 4) lo |= b << (8 * j); else hi |= b << (8 * (j - 4));
+          }
+        }
+        out[c] = make_uint2(lo, hi);
+      }
+    }
+    if constexpr (PREFETCH) {
+#pragma unroll
+      for (int k = 0; k < NCH; ++k) raw[k] = nxt[k];
     }
   }
 }
@@ -837,18 +883,27 @@ int32_t fp8_quantize_rows_impl(b2q_handle h, const T* x, int64_t rows, int64_t c
   if (!x || !scales || !codes) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "fp8_quantize_rows: null pointer");
   if (fmt < 0 || fmt > 1 || rounding < 0 || rounding > 1) B2Q_FAIL(h, B2Q_ERR_INVALID_ARGUMENT, "fp8_quantize_rows: bad format/rounding");
   StatArgs a{kFp8Scale, 0, 0, fp8_fmt(fmt).max_val, scales, nullptr, h->d_status, flag_nonfinite};
-  if (cols % 8 == 0 && cols >= 256 && cols <= 65536 && rows <= 0x7FFFFFFF && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
+  if (cols % 8 == 0 && cols >= 256 && cols <= (sizeof(T) == 2 ? 65536 : 32768) && rows <= 0x7FFFFFFF && (reinterpret_cast<uintptr_t>(x) & 15) == 0 &&
       (reinterpret_cast<uintptr_t>(codes) & 7) == 0 && (rows >= 64 || cols <= 2048)) {
     const int64_t chunks = cols >> 3;
     // 1, 2, 4 or 8 chunks of 8 elements per thread; many rows prefer small CTAs (several per SM)
     const int nch = chunks <= 128 ? 1 : (chunks <= 512 ? 2 : (chunks <= 4096 ? 4 : 8));
     const int threads = (int)((ceil_div64(chunks, nch) + 31) / 32 * 32);
     const bool full = chunks == (int64_t)nch * threads;
-#define ROWS_LAUNCH(N, F) fp8_quantize_rows_reg_kernel<T, N, F><<<(unsigned)rows, threads, 0, h->stream>>>(x, cols, a, fmt, rounding, codes)
+    // enough CTAs to fill every SM's thread slots; each walks rows with a stride of the grid
+    const bool pipe = threads >= 512;
+    const int by_threads = 2048 / threads, by_regs = 65536 / (threads * 64);          // the pipelined kernels use up to 64 registers
+    const int64_t resident = (int64_t)h->sm_count * (by_regs < 1 ? 1 : (by_regs < by_threads ? by_regs : by_threads));
+    const unsigned grid = (unsigned)(!pipe || rows < resident ? rows : resident);
+#define ROWS_LAUNCH(N, F)                                                                                                          \
+  do {                                                                                                                             \
+    if (pipe) fp8_quantize_rows_reg_kernel<T, N, F, true><<<grid, threads, 0, h->stream>>>(x, rows, cols, a, fmt, rounding, codes); \
+    else fp8_quantize_rows_reg_kernel<T, N, F, false><<<grid, threads, 0, h->stream>>>(x, rows, cols, a, fmt, rounding, codes);     \
+  } while (0)
     if (nch == 1) { if (full) ROWS_LAUNCH(1, true); else ROWS_LAUNCH(1, false); }
     else if (nch == 2) { if (full) ROWS_LAUNCH(2, true); else ROWS_LAUNCH(2, false); }
     else if (nch == 4) { if (full) ROWS_LAUNCH(4, true); else ROWS_LAUNCH(4, false); }
-    else { if (full) ROWS_LAUNCH(8, true); else ROWS_LAUNCH(8, false); }
+    else if constexpr (sizeof(T) == 2) { if (full) ROWS_LAUNCH(8, true); else ROWS_LAUNCH(8, false); }
 #undef ROWS_LAUNCH
     B2Q_LAUNCH_CHECK(h, "fp8_quantize_rows_reg_kernel");
     return B2Q_OK;
