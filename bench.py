@@ -408,8 +408,8 @@ def main():
                     "tile": f"{tile.tile_m}x{tile.tile_n}x{tile.tile_k}", "kernel_id": kid})
         roofline = {"bound": "tensor", "kernel": f"gemm_tc2_kernel<fp8> on this rank's gate|up GEMM {TOKENS}x{2 * F}x{HIDDEN}",
                     "achieved": gemm_tflops, "peak": fp8_peak, "unit": "TFLOP/s", "frac": gemm_tflops / fp8_peak,
-                    # dram__bytes_read.sum + dram__bytes_write.sum of this launch at tp = 1 (one-pass ncu capture of the bench command,
-                    # profiles/tp_mlp_step_launches.md); not captured for the shards of tp > 1
+                    # dram__bytes_read.sum + dram__bytes_write.sum of this launch at tp = 1 (one-pass ncu capture of this very
+                    # command with --steps 2 --warmup 3 --no-extras); not captured for the shards of tp > 1
                     "traffic": NCU_DRAM_BYTES_GATE_UP_TP1 if world == 1 else None,
                     "algorithmic_bytes": TOKENS * HIDDEN + 2 * F * HIDDEN + TOKENS * F * 2,
                     "peak_source": f"2 x bf16_tflops_sustained of MEASURED_PEAKS.json ({peaks['source']}): the step runs for milliseconds under the power cap, "
