@@ -30,7 +30,7 @@ sys.path.insert(0, str(ROOT))
 # Headline workload, the same at every GPU count (strong scaling): the tensor-parallel FP8 SwiGLU MLP of a
 # 70B-shaped layer (hidden 8192, FFN 28672, 4096 tokens): gate/up column-parallel, down row-parallel, sum over ranks.
 HIDDEN, FFN, TOKENS = 8192, 28672, 4096
-NCU_DRAM_BYTES_GATE_UP_TP1 = 1916283392 + 229755136      # gate | up GEMM with the SwiGLU epilogue, 4096 x 57344 x 8192
+NCU_DRAM_BYTES_GATE_UP_TP1 = 668990720 + 225613056      # gate | up GEMM with the SwiGLU epilogue, 4096 x 57344 x 8192
 FLOP_PER_STEP = 6.0 * TOKENS * HIDDEN * FFN
 WORKLOAD = "tp_fp8_e4m3_swiglu_mlp_hidden8192_ffn28672_tokens4096_bf16out"
 M = N = K = 4096                                    # the single-GEMM configuration, reported in roofline.gemm_fp8_4096

@@ -34,7 +34,7 @@ struct b2q_handle_s {
   // Experiment switches (environment variables B2Q_*), read once when the handle is created: -1 = not set.
   struct Switches {
     int no_tail_split, force_tile, fp8_skinny, skinny_pdl, mx_streamk, mx_debug, mx_pdl, mx_inline, e8c_db, gemv_mx, gemv_cluster,
-        gemv_exact, int4_small, gemv_stream;
+        gemv_exact, int4_small, gemv_stream, force_group_m;
   } sw;
   // encoded TMA descriptors, direct-mapped by a hash of their key (128 bytes each; see b2q_tensor_map_2d)
   struct MapEntry { uint64_t key[4]; unsigned char map[128]; int valid; };

@@ -869,6 +869,14 @@ int32_t launch2(b2q_handle h, const void* a, const void* w, Params p, const Scat
   if (st != B2Q_OK) return st;
   p.tiles_m = (int)ceil_div64(p.M, 256);
   p.tiles_n = (int)ceil_div64(p.N, two::BN2);
+  if (p.group_m == 0 && !scatter) {
+    // row tiles per raster group: as many as keep the group's A panel (group_m x 256 x K bytes) within about 48 MB of the
+    // 126 MB L2 while the weight tiles stream past it once per group; at least GROUP_M, at most all of them
+    const int64_t fit = (48ll << 20) / (256 * (p.K > 0 ? p.K : 1));
+    int gm = (int)(fit < GROUP_M ? GROUP_M : (fit > 64 ? 64 : fit));
+    if (h->sw.force_group_m > 0) gm = h->sw.force_group_m;
+    p.group_m = gm < p.tiles_m ? gm : (p.tiles_m > 0 ? p.tiles_m : 1);
+  }
   const uint32_t idesc_fmt = p.idesc;
   uint32_t shape = ((uint32_t)((two::BN2 / 2) >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
   p.idesc_half = KIND == kF8 ? (idesc_fmt | (1u << 4) | shape)
