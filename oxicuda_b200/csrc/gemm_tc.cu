@@ -8,8 +8,10 @@
 //   warp 1      allocates TMEM and issues tcgen05.mma (one elected thread), the
 //               accumulator (128 lanes x BN fp32/s32 columns) lives in TMEM and is
 //               double-buffered so the epilogue of tile i overlaps the MMAs of i+1;
-//   warps 2..5  epilogue: tcgen05.ld of their 32-lane quarter, scale, convert to
-//               bf16/f32 (or raw s32), vectorised global stores.
+//   warps 2..5  epilogue: the tile's scales are fetched before the accumulator is waited for, then tcgen05.ld of
+//               their 32-lane quarter, scale (alpha / beta / bias / activation, or SwiGLU over column pairs), convert
+//               to bf16/f32 into a swizzled shared-memory buffer, one TMA store per buffer (raw s32 and odd pitches:
+//               vectorised global stores).
 // Every mbarrier wait is bounded (wall-clock limit); on expiry the kernel records
 // B2Q_ERR_TIMEOUT in the status word, drains what it issued, frees TMEM and returns.
 #include "tc_common.cuh"

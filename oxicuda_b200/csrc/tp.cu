@@ -11,8 +11,10 @@
 //     tcgen05 kernel stores every accumulator row block straight into the inbox of the rank that owns those rows (TMA
 //     stores into peer-mapped memory), so the partial sums cross NVLink tile by tile while the MMAs run; one kernel
 //     then waits for the peers, adds the tp slots of its own rows in rank order in fp32 and pushes the bf16 sums to
-//     every rank.  With several token chunks that kernel runs on a second stream under the GEMMs of the next chunk;
-//   * beyond that, or without peer mappings: NCCL all-reduce per token chunk on the second stream.
+//     every rank.  The ranks walk the row blocks from different starting owners, so no inbox is the target of all the
+//     others at once.  Optionally (b2q_tp_set_chunks) the GEMM is cut into column chunks and that kernel runs on a
+//     second stream under the GEMM of the next chunk;
+//   * beyond that, or without peer mappings: NCCL all-reduce (optionally per token chunk on the second stream).
 // NCCL is resolved at run time from the library already loaded in the process (no link-time dependency).
 #include "common.cuh"
 #include <dlfcn.h>
