@@ -34,7 +34,7 @@ struct b2q_handle_s {
   // Experiment switches (environment variables B2Q_*), read once when the handle is created: -1 = not set.
   struct Switches {
     int no_tail_split, force_tile, fp8_skinny, skinny_pdl, mx_streamk, mx_debug, mx_pdl, mx_inline, e8c_db, gemv_mx, gemv_cluster,
-        gemv_exact, int4_small, gemv_stream, force_group_m;
+        gemv_exact, int4_small, gemv_stream, force_group_m, chain_pdl;
   } sw;
   // encoded TMA descriptors, direct-mapped by a hash of their key (128 bytes each; see b2q_tensor_map_2d)
   struct MapEntry { uint64_t key[4]; unsigned char map[128]; int valid; };
@@ -234,3 +234,26 @@ __device__ __forceinline__ float warp_min(float v) {
   for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
 }
+
+// Programmatic dependent launch for the small kernels of a decode step (row quantizer, SwiGLU quantizer, peer all-reduce):
+// b2q_pdl_entry() is the first statement of such a kernel.  It waits for the previous kernel of the stream to complete
+// (a no-op for a normal launch) and then lets the NEXT kernel start launching while this one runs; that kernel waits
+// the same way before it touches memory, so the only thing that overlaps is launch latency.  B2Q_PDL_LAUNCH enqueues a
+// kernel so (h->sw.chain_pdl = 0, B2Q_CHAIN_PDL=0, launches normally).
+#ifdef __CUDACC__
+__device__ __forceinline__ void b2q_pdl_entry() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+template <typename... KArgs, typename... Args>
+static inline cudaError_t b2q_pdl_launch(bool pdl, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif

@@ -117,7 +117,8 @@ int32_t b2q_create(b2q_handle* out, int device) {
   h->sw.gemv_exact = sw("B2Q_GEMV_EXACT");
   h->sw.int4_small = sw("B2Q_INT4_SMALL");
   h->sw.gemv_stream = sw("B2Q_GEMV_STREAM");
-  h->sw.force_group_m = sw("B2Q_GEMM_GROUP_M");     // row tiles per raster group of the pair kernel (experiments)
+  h->sw.force_group_m = sw("B2Q_GEMM_GROUP_M");
+  h->sw.chain_pdl = sw("B2Q_CHAIN_PDL");            // 0: the small kernels of a decode step launch without programmatic dependent launch     // row tiles per raster group of the pair kernel (experiments)
   *out = h;
   return B2Q_OK;
 }

@@ -663,6 +663,7 @@ __global__ void __launch_bounds__(1024) fp8_quantize_rows_fused_kernel(const T* 
                                                                        uint8_t* codes) {
   __shared__ RowStat sh[32];
   __shared__ float s_scale;
+  b2q_pdl_entry();
   const int64_t r = blockIdx.x;
   const T* row = x + r * cols;
   RowStat s = scan_segment<T>(row, 0, cols, (int)threadIdx.x, (int)blockDim.x);
@@ -792,6 +793,7 @@ template <typename T, int NCH, bool FULL, bool PIPE>
 __global__ void __launch_bounds__(1024) fp8_quantize_rows_reg_kernel(const T* __restrict__ x, int64_t rows, int64_t cols, StatArgs a, int fmt,
                                                                      int rounding, uint8_t* __restrict__ codes) {
   __shared__ uint32_t sh_amax[2][32];
+  b2q_pdl_entry();
   const int chunks = (int)(cols >> 3);
   const Fp8Fmt F = fp8_fmt(fmt);
   // the next row's chunks are held only where two sets fit the register budget of a 1024-thread CTA (up to 16 registers
@@ -897,8 +899,9 @@ int32_t fp8_quantize_rows_impl(b2q_handle h, const T* x, int64_t rows, int64_t c
     const unsigned grid = (unsigned)(!pipe || rows < resident ? rows : resident);
 #define ROWS_LAUNCH(N, F)                                                                                                          \
   do {                                                                                                                             \
-    if (pipe) fp8_quantize_rows_reg_kernel<T, N, F, true><<<grid, threads, 0, h->stream>>>(x, rows, cols, a, fmt, rounding, codes); \
-    else fp8_quantize_rows_reg_kernel<T, N, F, false><<<grid, threads, 0, h->stream>>>(x, rows, cols, a, fmt, rounding, codes);     \
+    const bool pdl = h->sw.chain_pdl != 0;                                                                                          \
+    if (pipe) B2Q_CUDA(h, b2q_pdl_launch(pdl, fp8_quantize_rows_reg_kernel<T, N, F, true>, dim3(grid), dim3(threads), 0, h->stream, x, rows, cols, a, fmt, rounding, codes)); \
+    else B2Q_CUDA(h, b2q_pdl_launch(pdl, fp8_quantize_rows_reg_kernel<T, N, F, false>, dim3(grid), dim3(threads), 0, h->stream, x, rows, cols, a, fmt, rounding, codes));     \
   } while (0)
     if (nch == 1) { if (full) ROWS_LAUNCH(1, true); else ROWS_LAUNCH(1, false); }
     else if (nch == 2) { if (full) ROWS_LAUNCH(2, true); else ROWS_LAUNCH(2, false); }
@@ -909,7 +912,8 @@ int32_t fp8_quantize_rows_impl(b2q_handle h, const T* x, int64_t rows, int64_t c
     return B2Q_OK;
   }
   if (rows <= 128 && cols >= 2048 && cols <= (1 << 20)) {
-    fp8_quantize_rows_fused_kernel<T><<<(unsigned)rows, 1024, 0, h->stream>>>(x, cols, a, fmt, rounding, codes);
+    B2Q_CUDA(h, b2q_pdl_launch(h->sw.chain_pdl != 0, fp8_quantize_rows_fused_kernel<T>, dim3((unsigned)rows), dim3(1024), 0, h->stream, x, cols, a,
+                               fmt, rounding, codes));
     B2Q_LAUNCH_CHECK(h, "fp8_quantize_rows_fused_kernel");
     return B2Q_OK;
   }
@@ -1260,6 +1264,7 @@ template <typename TIn>
 __global__ void __launch_bounds__(1024) swiglu_quantize_rows_kernel(const TIn* __restrict__ gate, const TIn* __restrict__ up, int64_t ld,
                                                                         int64_t cols_all, int fmt, int rounding, float* scales,
                                                                         uint8_t* codes, int split, int inter) {
+  b2q_pdl_entry();
   const int64_t r = blockIdx.x / split;
   const int part = (int)(blockIdx.x % split);
   // slices are multiples of 8 columns so that the vector path keeps its alignment
@@ -1347,13 +1352,15 @@ static int32_t swiglu_quantize_rows_launch(b2q_handle h, const TIn* gate, const 
   cfg.gridDim = dim3((unsigned)(rows * split));
   cfg.blockDim = dim3((unsigned)threads);
   cfg.stream = h->stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = (unsigned)split;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = h->sw.chain_pdl != 0 ? 2 : 1;
   B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, swiglu_quantize_rows_kernel<TIn>, gate, up, ld, cols, fmt, rounding, scales, codes, split, inter));
   return B2Q_OK;
 }

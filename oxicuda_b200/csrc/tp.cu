@@ -135,6 +135,7 @@ template <bool TWO_SHOT>
 __global__ void __launch_bounds__(512, 1) tp_allreduce_push_kernel(const Peers peers, int tp, int rank, const float4* __restrict__ partial,
                                                                     int64_t n4, uint2* __restrict__ y, int32_t* status) {
   __shared__ int s_abort;
+  b2q_pdl_entry();
   if (threadIdx.x == 0) s_abort = 0;
   const int cta = blockIdx.x, G = gridDim.x;
   uint8_t* my = peers.base[rank];
@@ -383,9 +384,11 @@ static int32_t peer_allreduce(b2q_tp t, const float* partial, int64_t n, void* y
   if (two) grid = (int)((n4 / t->tp + 511) / 512);
   grid = grid < 1 ? 1 : (grid > kMaxCtas ? kMaxCtas : grid);
   if (two)
-    tp_allreduce_push_kernel<true><<<grid, 512, 0, h->stream>>>(t->peers, t->tp, t->rank, (const float4*)partial, n4, (uint2*)y, h->d_status);
+    B2Q_CUDA(h, b2q_pdl_launch(h->sw.chain_pdl != 0, tp_allreduce_push_kernel<true>, dim3(grid), dim3(512), 0, h->stream, t->peers, t->tp, t->rank,
+                               (const float4*)partial, n4, (uint2*)y, h->d_status));
   else
-    tp_allreduce_push_kernel<false><<<grid, 512, 0, h->stream>>>(t->peers, t->tp, t->rank, (const float4*)partial, n4, (uint2*)y, h->d_status);
+    B2Q_CUDA(h, b2q_pdl_launch(h->sw.chain_pdl != 0, tp_allreduce_push_kernel<false>, dim3(grid), dim3(512), 0, h->stream, t->peers, t->tp, t->rank,
+                               (const float4*)partial, n4, (uint2*)y, h->d_status));
   B2Q_LAUNCH_CHECK(h, "tp_allreduce_push_kernel");
   return B2Q_OK;
 }
