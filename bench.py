@@ -509,18 +509,20 @@ def run_tp_breakdown(iters: int):
     out["boundary"] = round(out["layer"] - out["layer_without_boundary"], 1)
     codec = mlp.codec
     xc, xs = codec.quantize_rows(x, TOKENS, HIDDEN)
-    out["quantize_x"] = timeit(lambda: codec.quantize_rows(x, TOKENS, HIDDEN))
+    hd = default_handle()
+    # the quantizers through the C ABI into preallocated outputs: the host mirror's two allocations per call cost more than
+    # these kernels take
+    out["quantize_x"] = timeit(lambda: hd.call("b2q_fp8_quantize_rows_bf16", ptr(x), TOKENS, HIDDEN, L.FP8_E4M3, codec.rounding, ptr(xs), ptr(xc)))
     hb = torch.empty(TOKENS, F, dtype=torch.bfloat16, device=dev)
     out["gate_up_gemm_with_swiglu"] = timeit(lambda: gemm_fp8_ex(xc.view(TOKENS, HIDDEN), mlp.gu_codes, xs, mlp.gu_scales, out=hb, epilogue=EpilogueOp.SwiGluPairs))
     hc, hs = codec.quantize_rows(hb, TOKENS, F)
-    out["quantize_h"] = timeit(lambda: codec.quantize_rows(hb, TOKENS, F))
+    out["quantize_h"] = timeit(lambda: hd.call("b2q_fp8_quantize_rows_bf16", ptr(hb), TOKENS, F, L.FP8_E4M3, codec.rounding, ptr(hs), ptr(hc)))
     yd = torch.empty(TOKENS, HIDDEN, dtype=torch.bfloat16, device=dev)
     out["down_gemm"] = timeit(lambda: gemm_fp8(hc.view(TOKENS, F), mlp.down.codes, hs, mlp.down.scales, out=yd))
     if world > 1:
         rows = TOKENS // world
         local = [torch.empty(world, rows, HIDDEN, dtype=torch.bfloat16, device=dev) for _ in range(world)]
         lp = (C.c_void_p * world)(*[t.data_ptr() for t in local])
-        hd = default_handle()
         out["down_scatter_local"] = timeit(lambda: hd.call("b2q_gemm_fp8_scatter", ptr(hc), ptr(mlp.down.codes), TOKENS, HIDDEN, F, L.FP8_E4M3, ptr(hs),
                                                            ptr(mlp.down.scales), None, lp, world, rank))
         nvlink_bytes = 2 * (world - 1) / world * TOKENS * HIDDEN * 2        # per rank and direction: scatter + gather
