@@ -190,7 +190,7 @@ def main():
     ap.add_argument("--no-extras", action="store_true", help="skip the GEMV / GEMM / quantizer side measurements")
     ap.add_argument("--chunks", type=int, default=0, help="token chunks of the overlapped all-reduce (0 = automatic)")
     ap.add_argument("--case", default=None,
-                    help="run ONE kernel case a few times and exit (for ncu captures): gemm_fp8:M:N:K | gemv_fp4:K:N:tokens | gemv_int4:K:N:tokens:group | kv_quant:tokens:head_dim:axis:bf16 | rms_quant:rows:cols:residual | fp8_quant_rows:rows:cols:bf16 | swiglu_quant:rows:ffn | gemm_fp4_bs:tokens:N:K:mxfp8 | grouped_fp8:experts:rows_each:N:K | tp_breakdown (under torchrun: the headline layer's pieces timed one by one on every rank)")
+                    help="run ONE kernel case a few times and exit (for ncu captures): gemm_fp8:M:N:K | gemv_fp4:K:N:tokens | gemv_int4:K:N:tokens:group | kv_quant:tokens:head_dim:axis:bf16 | rms_quant:rows:cols:residual | fp8_quant_rows:rows:cols:bf16 | swiglu_quant:rows:ffn | gemm_fp4_bs:tokens:N:K:mxfp8 | grouped_fp8:experts:rows_each:N:K | wq_gemv:rows:cols:group:bits:split_k | wq_dequant:rows:cols:group:bits:bf16 | tp_breakdown (under torchrun: the headline layer's pieces timed one by one on every rank)")
     ap.add_argument("--iters", type=int, default=3)
     args = ap.parse_args()
     if args.case == "tp_breakdown":
@@ -631,6 +631,23 @@ def run_case(case: str, iters: int):
         fn = lambda: default_handle().call("b2q_grouped_gemm_fp8_rows", ptr(a), ptr(sa), ptr(w), ptr(sw), ptr(off), ptr(cnt), experts, cap, n, k,
                                            L.FP8_E4M3, ptr(out), L.OUT_BF16)
         work, unit = 2.0 * experts * rows_each * n * k / 1e12, "TFLOP/s"
+    elif kind in ("wq_gemv", "wq_dequant"):   # wq_gemv:rows:cols:group:bits:split_k | wq_dequant:rows:cols:group:bits:bf16  (GPTQ / AWQ packed weights)
+        from oxicuda_b200._lib import default_handle, ptr
+        import oxicuda_b200._lib as L
+        rows, cols, group, bits, last = d
+        words = rows * cols // (32 // bits)
+        packed = torch.randint(-2**31, 2**31 - 1, (words,), dtype=torch.int32, device=dev)
+        scales = torch.rand(rows * cols // group, device=dev) * 0.01
+        if kind == "wq_gemv":
+            x, y = torch.randn(cols, device=dev), torch.empty(rows, device=dev)
+            fn = lambda: default_handle().call("b2q_fused_dequant_gemv_f32", ptr(packed), ptr(scales), None, ptr(x), rows, cols, group, bits, last, ptr(y))
+            work = (4 * words + 4 * rows * cols // group + 4 * cols + 4 * rows) / 1e9
+        else:
+            out = torch.empty(rows, cols, dtype=torch.bfloat16 if last else torch.float32, device=dev)
+            fn = lambda: default_handle().call("b2q_wq_dequantize", ptr(packed), ptr(scales), None, rows, cols, group, bits, ptr(out),
+                                               L.OUT_BF16 if last else L.OUT_F32)
+            work = (4 * words + 4 * rows * cols // group + rows * cols * out.element_size()) / 1e9
+        unit = "GB/s"
     else:
         raise SystemExit(f"unknown case {case}")
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)

@@ -514,6 +514,45 @@ int32_t b2q_ggml_quantize_f32(b2q_handle h, int type, const float* w, int64_t n,
 /* blocks -> out [n] f32 or bf16 (B2Q_OUT_F32 / B2Q_OUT_BF16; bf16 is the f32 value rounded to nearest even). */
 int32_t b2q_ggml_dequantize(b2q_handle h, int type, const uint8_t* blocks, int64_t n, void* out, int out_type);
 
+/* ---- GPTQ / AWQ weight-only group quantization: crates/oxicuda-dnn/src/quantize/gptq_awq.rs.  The five kernels that
+ *      WeightQuantPlan generates, each with the reference kernel's own arithmetic.  Layout (QuantizedWeight :210-232):
+ *      codes packed 32 / bits to a u32 over the FLAT row-major matrix (element e in word e / epu at bits
+ *      [(e % epu) * bits, +bits); epu = 16, 10, 8, 4 for bits = 2, 3, 4, 8), scales and zero points f32
+ *      [rows x cols / group_size].  Validation as WeightQuantPlan::new (:254-283) and GptqConfig::validate (:102-127):
+ *      INVALID_DIMENSION for an empty matrix, INVALID_ARGUMENT for bits outside {2, 3, 4, 8}, a zero group size or
+ *      cols % group_size != 0. ---- */
+/* quantized_weight_info().packed_weight_elements (:996-1027): ceil(rows * cols / epu); -1 for a bad argument. */
+int64_t b2q_wq_packed_words(int64_t rows, int64_t cols, int bits);
+/* dnn_gptq_quantize_f32 (:329-499), the reference's simplified quantizer (no inverse-Hessian update):
+ * q = clamp(rni(w / max(hessian_diag[col], 1e-6)) (+ 2^(bits-1), floored at 0, when symmetric), 0, 2^bits - 1);
+ * scales[row, group] = max(hessian_diag[last column of the group], 1e-6) / (2^bits - 1) (the value the reference's
+ * column loop leaves there).  packed needs no clearing (the reference ORs into a zeroed buffer).  Bit-exact. */
+int32_t b2q_gptq_quantize_f32(b2q_handle h, const float* weight, const float* hessian_diag, int64_t rows, int64_t cols,
+                              int64_t group_size, int bits, int symmetric, uint32_t* packed, float* scales);
+/* dnn_gptq_dequantize_f32 (:509-616): out[e] = q * scale (zeros == NULL: the symmetric kernel) or (q - zero) * scale;
+ * out f32 or bf16 (the f32 value rounded to nearest even).  Bit-exact. */
+int32_t b2q_wq_dequantize(b2q_handle h, const uint32_t* packed, const float* scales, const float* zeros, int64_t rows,
+                          int64_t cols, int64_t group_size, int bits, void* out, int out_type);
+/* dnn_awq_scale_search_f32 (:626-713): scale_out[c] = a * rsqrt.approx(a), a = max(|act_stats[c]|, 1e-7) (the
+ * reference's stand-in for act^alpha: its alpha grid and weight operand are not read, best_alpha is not written). */
+int32_t b2q_awq_scale_search_f32(b2q_handle h, const float* act_stats, int64_t num_channels, float* scale_out);
+/* dnn_awq_quantize_f32 (:723-857): q = min(max(rni(w * channel_scales[col] / max(group_scales[row, group], 1e-12)), 0),
+ * 2^bits - 1); group_scales is an INPUT; zeros (may be NULL: AwqConfig.zero_point = false) is filled with 0.0 as the
+ * reference does.  bits 4 or 8 (AwqConfig::validate :174-199).  Bit-exact. */
+int32_t b2q_awq_quantize_f32(b2q_handle h, const float* weight, const float* channel_scales, const float* group_scales,
+                             int64_t rows, int64_t cols, int64_t group_size, int bits, uint32_t* packed, float* zeros);
+/* dnn_fused_dequant_gemv_f32 (:867-986): y[row] = sum over col = 0 .. cols-1, in that order, of
+ * fma(float(q) * scales[row, col / group_size], x[col], acc), f32.  The reference reads row r at word r * (cols / epu),
+ * which agrees with the flat packing of the kernels above only when epu divides cols: that is required here
+ * (INVALID_ARGUMENT otherwise).  zeros == NULL is the reference kernel (it ignores zero points); with zeros the term
+ * is (float(q) - zero) * scale, as b2q_wq_dequantize has it.
+ * split_k = 1: the reference's summation order, bit-exact.  2, 4, 8: the columns are cut into that many contiguous
+ * segments, each summed in order by its own thread, the partial sums added in segment order (deterministic; differs
+ * from split_k = 1 by rounding only) - more threads for matrices with few rows.  0: the library's choice. */
+int32_t b2q_fused_dequant_gemv_f32(b2q_handle h, const uint32_t* packed, const float* scales, const float* zeros,
+                                   const float* x, int64_t rows, int64_t cols, int64_t group_size, int bits, int split_k,
+                                   float* y);
+
 /* ---- tile heuristics: classify_workload / Fp8TileHeuristic::select crates/oxicuda-blas/src/precision/fp8_ops.rs:67-107,
  *      :239-304; select_fp4_tile fp4_fp6_ops.rs:996-1075; Int8GemmConfig::tile_config int_ops.rs:141-176 ---- */
 typedef struct {

@@ -512,3 +512,55 @@ def tile_config(dtype, m, n, k):
 
 def fp8_split_k(m, n, k):
     return int(lib().orc_fp8_split_k(C.c_uint32(m), C.c_uint32(n), C.c_uint32(k)))
+
+
+# ---- GPTQ / AWQ kernels of oxicuda-dnn (crates/oxicuda-dnn/src/quantize/gptq_awq.rs) ----
+def wq_packed_words(rows, cols, bits):
+    """quantized_weight_info().packed_weight_elements (gptq_awq.rs:996-1001)."""
+    epu = 32 // bits
+    return (rows * cols + epu - 1) // epu
+
+
+def gptq_quantize(w, hessian_diag, rows, cols, group, bits, symmetric):
+    """dnn_gptq_quantize_f32 -> (packed u32 [ceil(rows*cols/epu)], scales f32 [rows x cols/group])."""
+    w, hd = _f32(w).reshape(-1), _f32(hessian_diag).reshape(-1)
+    packed = np.zeros(wq_packed_words(rows, cols, bits), np.uint32)
+    scales = np.zeros(rows * (cols // group), np.float32)
+    lib().orc_gptq_quantize(_p(w), _p(hd), _i64(rows), _i64(cols), _i64(group), int(bits), int(bool(symmetric)), _p(packed), _p(scales))
+    return packed, scales
+
+
+def wq_dequantize(packed, scales, zeros, rows, cols, group, bits):
+    """dnn_gptq_dequantize_f32 -> f32 [rows*cols]; zeros None = the symmetric kernel."""
+    packed = np.ascontiguousarray(packed, np.uint32)
+    scales = _f32(scales).reshape(-1)
+    zeros = None if zeros is None else _f32(zeros).reshape(-1)
+    out = np.zeros(rows * cols, np.float32)
+    lib().orc_wq_dequantize(_p(packed), _p(scales), _p(zeros), _i64(rows), _i64(cols), _i64(group), int(bits), _p(out))
+    return out
+
+
+def awq_scale_search(act_stats):
+    act = _f32(act_stats).reshape(-1)
+    out = np.zeros(act.size, np.float32)
+    lib().orc_awq_scale_search(_p(act), _i64(act.size), _p(out))
+    return out
+
+
+def awq_quantize(w, channel_scales, group_scales, rows, cols, group, bits, zero_point=True):
+    """dnn_awq_quantize_f32 -> (packed u32, zeros f32 [rows x cols/group] or None)."""
+    w, cs, gs = _f32(w).reshape(-1), _f32(channel_scales).reshape(-1), _f32(group_scales).reshape(-1)
+    packed = np.zeros(wq_packed_words(rows, cols, bits), np.uint32)
+    zeros = np.full(rows * (cols // group), np.nan, np.float32) if zero_point else None
+    lib().orc_awq_quantize(_p(w), _p(cs), _p(gs), _i64(rows), _i64(cols), _i64(group), int(bits), _p(packed), _p(zeros))
+    return packed, zeros
+
+
+def fused_dequant_gemv(packed, scales, zeros, x, rows, cols, group, bits):
+    """dnn_fused_dequant_gemv_f32 -> y f32 [rows], the reference's column-ascending fma chain."""
+    packed = np.ascontiguousarray(packed, np.uint32)
+    scales, x = _f32(scales).reshape(-1), _f32(x).reshape(-1)
+    zeros = None if zeros is None else _f32(zeros).reshape(-1)
+    y = np.zeros(rows, np.float32)
+    lib().orc_fused_dequant_gemv(_p(packed), _p(scales), _p(zeros), _p(x), _i64(rows), _i64(cols), _i64(group), int(bits), _p(y))
+    return y

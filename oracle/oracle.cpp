@@ -1124,3 +1124,107 @@ void orc_ggml_dequantize(int type, const uint8_t* blocks, int64_t n, float* out)
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// GPTQ / AWQ kernels of oxicuda-dnn (crates/oxicuda-dnn/src/quantize/gptq_awq.rs), each PTX instruction of the generated
+// kernels restated in C: div.rn / mul.rn / add.rn / sub.rn / fma.rn are the IEEE operations, cvt.rni.f32.f32 is
+// nearbyintf under the default rounding mode, max.f32 / min.f32 return the non-NaN operand (fmaxf / fminf),
+// cvt.rzi.u32.f32 truncates (its inputs are clamped to [0, 255] first).
+// ---------------------------------------------------------------------------
+namespace {
+inline int wq_epu(int bits) { return 32 / bits; }
+}  // namespace
+
+extern "C" {
+
+// dnn_gptq_quantize_f32 (:329-499): one thread per row walks the columns upwards; packed must arrive zeroed (atomic OR)
+// and is cleared here; scale[row, group] is overwritten by every column of the group.
+void orc_gptq_quantize(const float* w, const float* hdiag, int64_t rows, int64_t cols, int64_t group, int bits, int symmetric, uint32_t* packed,
+                       float* scales) {
+  const int epu = wq_epu(bits);
+  const float qmax = (float)((1u << bits) - 1u), half = (float)(1u << (bits - 1));
+  const int64_t total = rows * cols, gpr = cols / group;
+  std::memset(packed, 0, (size_t)((total + epu - 1) / epu) * 4);
+  for (int64_t row = 0; row < rows; ++row) {
+    for (int64_t col = 0; col < cols; ++col) {
+      const int64_t e = row * cols + col;
+      const float safe_h = fmaxf(hdiag[col], 1e-6f);                // MIN_DAMP (:29), max.f32 (:425)
+      const float scaled = w[e] / safe_h;                          // div.rn (:429)
+      float rounded = nearbyintf(scaled);                          // cvt.rni (:433)
+      if (symmetric) rounded = fmaxf(rounded + half, 0.0f);        // add.rn, max.f32 (:452-453)
+      float clamped = fminf(rounded, qmax);                        // (:456)
+      clamped = fmaxf(clamped, 0.0f);                              // (:457)
+      const uint32_t q = (uint32_t)clamped;                        // cvt.rzi.u32.f32 (:461)
+      scales[row * gpr + col / group] = safe_h / qmax;             // (:466-467)
+      packed[e / epu] |= q << ((e % epu) * bits);                  // (:471-489)
+    }
+  }
+}
+
+// dnn_gptq_dequantize_f32 (:509-616); zeros == NULL is the symmetric kernel.
+void orc_wq_dequantize(const uint32_t* packed, const float* scales, const float* zeros, int64_t rows, int64_t cols, int64_t group, int bits,
+                       float* out) {
+  const int epu = wq_epu(bits);
+  const uint32_t mask = (1u << bits) - 1u;
+  const int64_t gpr = cols / group;
+  for (int64_t e = 0; e < rows * cols; ++e) {
+    const float qf = (float)((packed[e / epu] >> ((e % epu) * bits)) & mask);    // shr, and, cvt.rn.f32.u32 (:560-567)
+    const int64_t s_idx = (e / cols) * gpr + (e % cols) / group;                 // (:570-584)
+    out[e] = zeros ? (qf - zeros[s_idx]) * scales[s_idx] : qf * scales[s_idx];   // (:592-603)
+  }
+}
+
+// dnn_awq_scale_search_f32 (:626-713): a * rsqrt.approx(a); the approximate reciprocal square root is restated as the
+// correctly rounded 1 / sqrt(a), so callers compare with a tolerance of a few units in the last place.
+void orc_awq_scale_search(const float* act, int64_t n, float* out) {
+  for (int64_t i = 0; i < n; ++i) {
+    const float a = fmaxf(fabsf(act[i]), 1e-7f);                   // abs, max.f32 (:683-688)
+    const float rsq = (float)(1.0 / std::sqrt((double)a));
+    out[i] = a * rsq;                                              // mul.rn (:695)
+  }
+}
+
+// dnn_awq_quantize_f32 (:723-857): group scales are an input; zeros (may be NULL) receive 0.0.
+void orc_awq_quantize(const float* w, const float* ch_scales, const float* g_scales, int64_t rows, int64_t cols, int64_t group, int bits,
+                      uint32_t* packed, float* zeros) {
+  const int epu = wq_epu(bits);
+  const float qmax = (float)((1u << bits) - 1u);
+  const int64_t total = rows * cols, gpr = cols / group;
+  std::memset(packed, 0, (size_t)((total + epu - 1) / epu) * 4);
+  for (int64_t e = 0; e < total; ++e) {
+    const int64_t col = e % cols, s_idx = (e / cols) * gpr + col / group;
+    const float w_scaled = w[e] * ch_scales[col];                  // mul.rn (:777)
+    const float safe = fmaxf(g_scales[s_idx], 1e-12f);             // (:799-802)
+    const float rounded = nearbyintf(w_scaled / safe);             // div.rn, cvt.rni (:803-807)
+    float clamped = fmaxf(rounded, 0.0f);                          // (:818)
+    clamped = fminf(clamped, qmax);                                // (:819)
+    packed[e / epu] |= (uint32_t)clamped << ((e % epu) * bits);    // (:822-841)
+    if (zeros) zeros[s_idx] = 0.0f;                                // (:845-849)
+  }
+}
+
+// dnn_fused_dequant_gemv_f32 (:867-986): one thread per row, packed words upwards, the values of a word upwards;
+// row r starts at word r * (cols / epu).  zeros != NULL is the library's extension ((q - zero) * scale).
+void orc_fused_dequant_gemv(const uint32_t* packed, const float* scales, const float* zeros, const float* x, int64_t rows, int64_t cols,
+                            int64_t group, int bits, float* y) {
+  const int epu = wq_epu(bits);
+  const uint32_t mask = (1u << bits) - 1u;
+  const int64_t packed_cols = cols / epu, gpr = cols / group;
+#pragma omp parallel for schedule(static)
+  for (int64_t row = 0; row < rows; ++row) {
+    float acc = 0.0f;
+    for (int64_t pw = 0; pw < packed_cols; ++pw) {
+      const uint32_t word = packed[row * packed_cols + pw];
+      for (int sub = 0; sub < epu; ++sub) {
+        const int64_t col = pw * epu + sub;
+        const float qf = (float)((word >> (sub * bits)) & mask);
+        const int64_t s_idx = row * gpr + col / group;
+        const float dq = zeros ? (qf - zeros[s_idx]) * scales[s_idx] : qf * scales[s_idx];   // mul.rn (:961)
+        acc = fmaf(dq, x[col], acc);                                                          // fma.rn (:966)
+      }
+    }
+    y[row] = acc;
+  }
+}
+
+}  // extern "C"

@@ -15,7 +15,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "libb2q.so"
-SOURCES = ["handle.cu", "quant.cu", "kv_cache.cu", "norm_quant.cu", "dnn_quant.cu", "int8.cu", "gemm_fp8_simt.cu", "gemm_tc.cu", "gemv_fp4.cu", "gemv_fp4_mx.cu", "gemv_fp4_mxf4.cu", "gemv_int4.cu", "gemv_fp8.cu", "gemm_fp8_skinny.cu", "moe.cu", "gemm_fp4.cu", "gemm_fp4_bs.cu", "tp.cu", "ggml.cu"]
+SOURCES = ["handle.cu", "quant.cu", "kv_cache.cu", "norm_quant.cu", "dnn_quant.cu", "int8.cu", "gemm_fp8_simt.cu", "gemm_tc.cu", "gemv_fp4.cu", "gemv_fp4_mx.cu", "gemv_fp4_mxf4.cu", "gemv_int4.cu", "gemv_fp8.cu", "gemm_fp8_skinny.cu", "moe.cu", "gemm_fp4.cu", "gemm_fp4_bs.cu", "tp.cu", "ggml.cu", "gptq_awq.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr",

@@ -166,6 +166,12 @@ SIGNATURES = {
     "b2q_ggml_block_size": (C.c_int64, [_I]),
     "b2q_ggml_quantize_f32": (C.c_int32, [_H, _I, _P, _I64, _P]),
     "b2q_ggml_dequantize": (C.c_int32, [_H, _I, _P, _I64, _P, _I]),
+    "b2q_wq_packed_words": (C.c_int64, [_I64, _I64, _I]),
+    "b2q_gptq_quantize_f32": (C.c_int32, [_H, _P, _P, _I64, _I64, _I64, _I, _I, _P, _P]),
+    "b2q_wq_dequantize": (C.c_int32, [_H, _P, _P, _P, _I64, _I64, _I64, _I, _P, _I]),
+    "b2q_awq_scale_search_f32": (C.c_int32, [_H, _P, _I64, _P]),
+    "b2q_awq_quantize_f32": (C.c_int32, [_H, _P, _P, _P, _I64, _I64, _I64, _I, _P, _P]),
+    "b2q_fused_dequant_gemv_f32": (C.c_int32, [_H, _P, _P, _P, _P, _I64, _I64, _I64, _I, _I, _P]),
     "b2q_moe_forward_fp4": (C.c_int32, [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I, _I, _I, _P, _P]),
     "b2q_grouped_gemm_fp4_rows": (C.c_int32, [_H, _P, _P, _P, _P, _I, _I64, _I64, _I64, _I, _P, _I]),
     "b2q_moe_forward_ex": (C.c_int32, [_P, _P, _P, _P, _P, _P, _P, _I64, _I64, _I64, _I, _I, _I, _I, _P, _P]),
