@@ -10,7 +10,7 @@
 // The reference packs with one atomic OR per element into a zeroed buffer; here one thread assembles a whole word, so the
 // output needs no clearing and no atomics.  The reference GEMV runs one thread per row with a stride of cols / epu words
 // between its loads (every load its own sector); here a CTA of 128 rows stages [128 rows x 32 words] tiles through shared
-// memory with 16-byte asynchronous copies, double-buffered, and every thread walks its own row in the reference's
+// memory with 16-byte asynchronous copies, two or four chunks deep, and every thread walks its own row in the reference's
 // column order, so that the sum is the reference's bit for bit.  With split_k > 1 a cluster of CTAs cuts the columns into
 // contiguous segments (each summed in order, the partial sums added in segment order through distributed shared memory):
 // more threads per row for matrices with few rows, at the price of a different association of the sum.
@@ -199,6 +199,10 @@ __global__ void __launch_bounds__(kThreads) awq_quantize_kernel(const float* __r
 constexpr int GV_ROWS = 128;      // rows per CTA, one thread each
 constexpr int GV_WCH = 32;        // packed words of every row per staged chunk
 constexpr int GV_STRIDE = 36;     // words between rows of the tile: 16-byte aligned, conflict-free for 16-byte reads
+// STAGES chunks in shared memory, STAGES - 1 in flight while one is consumed.  One thread per row gives a matrix of 28672
+// rows six warps per SM: four stages then keep enough bytes in flight (86 against 98 us); with the columns split there
+// are CTAs to spare and two stages (five CTAs per SM instead of two) are faster (78 against 90 us).
+constexpr size_t gv_smem_bytes(int stages, int epu) { return (size_t)stages * (GV_ROWS * GV_STRIDE * 4 + GV_WCH * epu * 4); }
 
 __device__ __forceinline__ void cp_async4(void* smem, const void* g) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(smem)), "l"(g) : "memory");
@@ -210,14 +214,16 @@ __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commi
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
 // ALIGNED: group % epu == 0, so a word never straddles two groups and the group test runs once per word.
-template <int BITS, bool HAS_ZERO, bool ALIGNED>
-__global__ void __launch_bounds__(GV_ROWS) fused_dequant_gemv_kernel(const uint32_t* __restrict__ packed, const float* __restrict__ scales,
+template <int BITS, bool HAS_ZERO, bool ALIGNED, int GV_STAGES>
+__global__ void __launch_bounds__(GV_ROWS, 2) fused_dequant_gemv_kernel(const uint32_t* __restrict__ packed, const float* __restrict__ scales,
                                                                      const float* __restrict__ zeros, const float* __restrict__ x,
                                                                      float* __restrict__ y, int64_t rows, int64_t cols, int64_t group, int split,
                                                                      int chunks_per_split, int vec) {
   constexpr int EPU = 32 / BITS;
-  __shared__ __align__(16) uint32_t tile[2][GV_ROWS * GV_STRIDE];
-  __shared__ __align__(16) float xs[2][GV_WCH * EPU];
+  // GV_STAGES buffers of [128 rows x 36 words] codes, then GV_STAGES buffers of the 32 * EPU activations of a chunk
+  extern __shared__ __align__(16) uint8_t gv_smem[];
+  uint32_t (*tile)[GV_ROWS * GV_STRIDE] = reinterpret_cast<uint32_t (*)[GV_ROWS * GV_STRIDE]>(gv_smem);
+  float (*xs)[GV_WCH * EPU] = reinterpret_cast<float (*)[GV_WCH * EPU]>(gv_smem + (size_t)GV_STAGES * GV_ROWS * GV_STRIDE * 4);
   __shared__ float red[GV_ROWS];
   const int tid = threadIdx.x;
   const int ks = (int)(blockIdx.x % (unsigned)split);
@@ -277,20 +283,72 @@ __global__ void __launch_bounds__(GV_ROWS) fused_dequant_gemv_kernel(const uint3
   };
 
   float acc = 0.0f;
-  if (c_begin < c_end) stage(c_begin, 0);
+  // one commit group per chunk slot, empty past the last chunk, so that "all but the newest GV_STAGES - 2 groups are
+  // complete" always means "this iteration's chunk has landed"
+  for (int st = 0; st < GV_STAGES - 1; ++st) {
+    if (c_begin + st < c_end) stage(c_begin + st, st); else cp_async_commit();
+  }
   for (int c = c_begin; c < c_end; ++c) {
-    const int buf = (c - c_begin) & 1;
-    if (c + 1 < c_end) {
-      stage(c + 1, buf ^ 1);
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
-    }
-    __syncthreads();
+    const int buf = (c - c_begin) % GV_STAGES;
+    cp_async_wait<GV_STAGES - 2>();
+    __syncthreads();                                     // chunk c is visible; every row is done with the buffer of chunk c - 1
+    if (c + GV_STAGES - 1 < c_end) stage(c + GV_STAGES - 1, (c - c_begin + GV_STAGES - 1) % GV_STAGES); else cp_async_commit();
     if (row < rows) {
       const int nw = (int)min((int64_t)GV_WCH, P - (int64_t)c * GV_WCH);
       const uint4* trow = reinterpret_cast<const uint4*>(&tile[buf][tid * GV_STRIDE]);
-      for (int w4 = 0; w4 * 4 < nw; ++w4) {
+      bool done = false;
+      if constexpr (ALIGNED && BITS != 3) {
+        // Full chunk and groups that end on 16-byte reads of the tile: no test per word.  Up to 32 values at a time
+        // are unpacked and scaled (independent work) before their fused multiply-adds join the sum one after another.
+        if (nw == GV_WCH && group % (4 * EPU) == 0) {
+          constexpr int STEP_WORDS = BITS == 2 ? 2 : 4;
+          constexpr int NV = STEP_WORDS * EPU;
+          // branch-free group step (selects and one clamped look-ahead load per 16-byte read), so that the whole chunk is
+          // one basic block and the scheduler can overlap the unpacking of later values with the dependent sum
+#pragma unroll
+          for (int w4 = 0; w4 < GV_WCH / 4; ++w4) {
+            {
+              const bool adv = cig == group;
+              const int64_t gn = min(g + 2, gpr - 1);
+              const float s_ld = __ldg(srow + gn);
+              s = adv ? s_next : s;
+              s_next = adv ? s_ld : s_next;
+              if (HAS_ZERO) {
+                const float z_ld = __ldg(zrow + gn);
+                z = adv ? z_next : z;
+                z_next = adv ? z_ld : z_next;
+              }
+              g += adv ? 1 : 0;
+              cig = adv ? 0 : cig;
+            }
+            const uint4 v = trow[w4];
+            const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int st = 0; st < 4 / STEP_WORDS; ++st) {
+              float xr[NV], dq[NV];
+              const float4* xq = reinterpret_cast<const float4*>(&xs[buf][(w4 * 4 + st * STEP_WORDS) * EPU]);
+#pragma unroll
+              for (int i = 0; i < NV / 4; ++i) {
+                const float4 f = xq[i];
+                xr[4 * i] = f.x; xr[4 * i + 1] = f.y; xr[4 * i + 2] = f.z; xr[4 * i + 3] = f.w;
+              }
+#pragma unroll
+              for (int k = 0; k < STEP_WORDS; ++k) {
+                float qv[EPU];
+                unpack_word_f32<BITS>(wv[st * STEP_WORDS + k], qv);
+#pragma unroll
+                for (int sub = 0; sub < EPU; ++sub)
+                  dq[k * EPU + sub] = HAS_ZERO ? __fmul_rn(__fsub_rn(qv[sub], z), s) : __fmul_rn(qv[sub], s);
+              }
+#pragma unroll
+              for (int j = 0; j < NV; ++j) acc = __fmaf_rn(dq[j], xr[j], acc);
+            }
+            cig += 4 * EPU;
+          }
+          done = true;
+        }
+      }
+      for (int w4 = 0; !done && w4 * 4 < nw; ++w4) {
         const uint4 v = trow[w4];
         const uint32_t wv[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
@@ -324,7 +382,6 @@ __global__ void __launch_bounds__(GV_ROWS) fused_dequant_gemv_kernel(const uint3
         }
       }
     }
-    __syncthreads();                                     // every row is done with this buffer before it is staged again
   }
 
   if (split > 1) {
@@ -342,14 +399,16 @@ __global__ void __launch_bounds__(GV_ROWS) fused_dequant_gemv_kernel(const uint3
   }
 }
 
-template <int BITS, bool HAS_ZERO, bool ALIGNED>
-int32_t launch_gemv_t(b2q_handle h, const uint32_t* packed, const float* scales, const float* zeros, const float* x, float* y, int64_t rows,
+template <int BITS, bool HAS_ZERO, bool ALIGNED, int STAGES>
+int32_t launch_gemv_s(b2q_handle h, const uint32_t* packed, const float* scales, const float* zeros, const float* x, float* y, int64_t rows,
                       int64_t cols, int64_t group, int split, int cps, int vec) {
   const int64_t row_tiles = ceil_div64(rows, GV_ROWS);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(row_tiles * split));
   cfg.blockDim = dim3(GV_ROWS);
-  cfg.dynamicSmemBytes = 0;
+  const size_t smem = gv_smem_bytes(STAGES, 32 / BITS);
+  B2Q_SMEM_ATTR(h, (fused_dequant_gemv_kernel<BITS, HAS_ZERO, ALIGNED, STAGES>), smem);
+  cfg.dynamicSmemBytes = smem;
   cfg.stream = h->stream;
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -358,9 +417,15 @@ int32_t launch_gemv_t(b2q_handle h, const uint32_t* packed, const float* scales,
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = split > 1 ? 1 : 0;
-  B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, fused_dequant_gemv_kernel<BITS, HAS_ZERO, ALIGNED>, packed, scales, zeros, x, y, rows, cols, group, split, cps,
+  B2Q_CUDA(h, cudaLaunchKernelEx(&cfg, fused_dequant_gemv_kernel<BITS, HAS_ZERO, ALIGNED, STAGES>, packed, scales, zeros, x, y, rows, cols, group, split, cps,
                                  vec));
   return B2Q_OK;
+}
+template <int BITS, bool HAS_ZERO, bool ALIGNED>
+int32_t launch_gemv_t(b2q_handle h, const uint32_t* packed, const float* scales, const float* zeros, const float* x, float* y, int64_t rows,
+                      int64_t cols, int64_t group, int split, int cps, int vec) {
+  return split == 1 ? launch_gemv_s<BITS, HAS_ZERO, ALIGNED, 4>(h, packed, scales, zeros, x, y, rows, cols, group, split, cps, vec)
+                    : launch_gemv_s<BITS, HAS_ZERO, ALIGNED, 2>(h, packed, scales, zeros, x, y, rows, cols, group, split, cps, vec);
 }
 template <int BITS>
 int32_t launch_gemv(b2q_handle h, const uint32_t* packed, const float* scales, const float* zeros, const float* x, float* y, int64_t rows,
