@@ -944,6 +944,26 @@ def side_measurements(dev, peaks):
         roof.setdefault("moe_fp4_mixtral", {"error": repr(exc)})
     torch.cuda.empty_cache()
 
+    # ---- GPTQ / AWQ fused dequant GEMV (4-bit codes, f32 scales per 128) on the same 8192 -> 28672 projection ----
+    try:
+        from oxicuda_b200._lib import default_handle, ptr
+        rows_q, cols_q, grp_q = 28672, 8192, 128
+        qsets = [(torch.randint(-2**31, 2**31 - 1, (rows_q * cols_q // 8,), dtype=torch.int32, device=dev),
+                  torch.rand(rows_q * cols_q // grp_q, device=dev) * 0.01) for _ in range(3)]      # 3 x 125 MB > L2
+        xq, yq = torch.randn(cols_q, device=dev), torch.empty(rows_q, device=dev)
+        hq = default_handle()
+        qbytes = rows_q * cols_q // 2 + 4 * rows_q * cols_q // grp_q + 4 * cols_q + 4 * rows_q
+        ent = {"rows": rows_q, "cols": cols_q, "bits": 4, "group": grp_q, "bytes": qbytes,
+               "timing": "CUDA events over back-to-back calls on rotating weight copies; [us, GB/s, fraction of the measured HBM peak]"}
+        for name, split in (("reference_order", 1), ("split_columns", 0)):
+            secq = _time_calls(lambda i: hq.call("b2q_fused_dequant_gemv_f32", ptr(qsets[i % 3][0]), ptr(qsets[i % 3][1]), None, ptr(xq), rows_q,
+                                                 cols_q, grp_q, 4, split, ptr(yq)), 12, 3)
+            ent[name] = [round(secq * 1e6, 1), round(qbytes / secq / 1e9, 1), round(qbytes / secq / 1e9 / hbm, 3)]
+        roof["gptq_awq_gemv"] = ent
+        del qsets, xq, yq
+    except Exception as exc:                                       # noqa: BLE001
+        roof["gptq_awq_gemv"] = {"error": repr(exc)}
+
     # ---- FP8 W8A8 with few tokens on the 70B-shaped FFN projection: HBM-bound ----
     Kd, Nd = 8192, 28672
     fw = []
