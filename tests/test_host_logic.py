@@ -201,7 +201,7 @@ def test_rust_bindings_cover_the_header(libb2q):
     assert (root / "rust" / "b2q-sys" / "src" / "lib.rs").read_text() == before
     # every item the wrapper crates take from the bindings exists there (the crates cannot be compiled here)
     declared = names | set(re.findall(r"pub const (B2Q_[A-Z0-9_]+)", src)) | set(re.findall(r"pub (?:type|struct) (b2q_[a-z0-9_]+)", src))
-    for crate in ("oxicuda-blas-b200", "oxicuda-quant-b200", "oxicuda-dist-infer-b200"):
+    for crate in ("oxicuda-blas-b200", "oxicuda-quant-b200", "oxicuda-dist-infer-b200", "oxicuda-dnn-b200"):
         used = set(re.findall(r"sys::([A-Za-z0-9_]+)", (root / "rust" / crate / "src" / "lib.rs").read_text()))
         assert used <= declared, (crate, sorted(used - declared))
 
