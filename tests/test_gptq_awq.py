@@ -237,7 +237,8 @@ def test_awq_kernels(cuda, oracle):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("bits,rows,cols,group", [(4, 3, 64, 32), (4, 300, 4096, 128), (8, 130, 1024, 64), (2, 129, 2048, 32), (3, 5, 640, 128),
-                                                  (3, 200, 1280, 64), (4, 1000, 8192, 128), (4, 64, 96, 32)])
+                                                  (3, 200, 1280, 64), (4, 1000, 8192, 128), (4, 64, 96, 32),
+                                                  (4, 7, 40, 8), (8, 9, 36, 12), (2, 3, 48, 16)])      # rows of 5, 9, 3 words: 4-byte copies
 def test_fused_dequant_gemv_reference_order_bit_exact(cuda, oracle, bits, rows, cols, group):
     """gpu_tests/quantize.rs:840-903 (3 x 64, groups of 32; bound 1e-4) and larger, ragged shapes: the sum runs in the
     reference's order, so the result equals the restated kernel's bit for bit; with zero points likewise."""
