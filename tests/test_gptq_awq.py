@@ -28,6 +28,32 @@ def pack_flat(codes, bits):
     return words.astype(np.uint32)
 
 
+class Lcg:
+    """The generator of the reference's GPU tests (crates/oxicuda-dnn/src/gpu_tests/mod.rs:169-194)."""
+
+    def __init__(self, seed):
+        self.state = seed
+
+    def next_u32(self):
+        self.state = (self.state * 6364136223846793005 + 1442695040888963407) & ((1 << 64) - 1)
+        return self.state >> 32
+
+    def range_f32(self, lo, hi):
+        return np.float32(lo + (hi - lo) * (self.next_u32() / 4294967296.0))
+
+
+def reference_gpu_test_inputs(seed, scale_hi, with_x):
+    """The operands of gptq_dequantize_numeric (seed 0xABCD_1234, scales in [0.02, 0.4)) and fused_dequant_gemv_numeric
+    (seed 0x55AA_9933, scales in [0.02, 0.3), x in [-2, 2)): 3 x 64, groups of 32, drawn in the reference's order
+    (gpu_tests/quantize.rs:789-799, :846-857)."""
+    rows, cols, group = 3, 64, 32
+    lcg = Lcg(seed)
+    nib = np.array([lcg.next_u32() % 16 for _ in range(rows * cols)], np.uint32)
+    scales = np.array([lcg.range_f32(0.02, scale_hi) for _ in range(rows * (cols // group))], np.float32)
+    x = np.array([lcg.range_f32(-2.0, 2.0) for _ in range(cols)], np.float32) if with_x else None
+    return rows, cols, group, nib, scales, x
+
+
 # ---------------------------------------------------------------------------
 # host mirror: the reference's unit tests
 # ---------------------------------------------------------------------------
@@ -136,6 +162,24 @@ def test_oracle_dequantize_and_gemv_closed_forms(oracle):
         assert np.array_equal(oracle.wq_dequantize(pack_flat(q, bits), s, z, rows, cols, group, bits), (q.astype(np.float32) - zx) * sx)
 
 
+def test_oracle_on_the_reference_gpu_test_inputs(oracle):
+    """gptq_dequantize_numeric and fused_dequant_gemv_numeric (gpu_tests/quantize.rs:783-903) on their own operands: the
+    oracle equals the reference tests' CPU expressions exactly (their bounds are 1e-5 and 1e-4 relative)."""
+    rows, cols, group, nib, scales, _ = reference_gpu_test_inputs(0xABCD_1234, 0.4, False)
+    gpr = cols // group
+    cpu = np.array([np.float32(nib[e]) * scales[(e // cols) * gpr + (e % cols) // group] for e in range(rows * cols)], np.float32)
+    assert np.array_equal(oracle.wq_dequantize(pack_flat(nib, 4), scales, None, rows, cols, group, 4), cpu)
+    rows, cols, group, nib, scales, x = reference_gpu_test_inputs(0x55AA_9933, 0.3, True)
+    cpu = np.zeros(rows, np.float32)
+    for r in range(rows):
+        acc = np.float32(0)
+        for c in range(cols):
+            dq = np.float32(nib[r * cols + c]) * scales[r * gpr + c // group]
+            acc = np.float32(np.float64(dq) * np.float64(x[c]) + np.float64(acc))        # f32::mul_add
+        cpu[r] = acc
+    assert np.array_equal(oracle.fused_dequant_gemv(pack_flat(nib, 4), scales, None, x, rows, cols, group, 4), cpu)
+
+
 def test_oracle_quantizers_closed_forms(oracle):
     """dnn_gptq_quantize_f32 / dnn_awq_* written out in numpy (round-half-even, the clamps in the kernel's order)."""
     rng = np.random.default_rng(6)
@@ -199,16 +243,17 @@ def test_gptq_quantize_and_dequantize_bit_exact(cuda, oracle, bits, sym, rows, c
 
 
 @pytest.mark.gpu
-def test_gptq_dequantize_reference_case(cuda, oracle):
-    """gpu_tests/quantize.rs:783-838: 3 x 64, groups of 32, random nibbles and scales in [0.02, 0.4]; the reference's
-    bound is 1e-5 relative, here the values are equal."""
-    rng = np.random.default_rng(0xABCD)
-    rows, cols, group = 3, 64, 32
-    nib = rng.integers(0, 16, rows * cols).astype(np.uint32)
-    scales = rng.uniform(0.02, 0.4, rows * (cols // group)).astype(np.float32)
-    out = _plan(rows, cols, group).gptq_dequantize(_t(pack_flat(nib, 4).view(np.int32), cuda), _t(scales, cuda))
-    cpu = nib.astype(np.float32) * np.repeat(scales.reshape(rows, -1), group, axis=1).reshape(-1)
-    assert np.array_equal(out.cpu().numpy().reshape(-1), cpu)
+def test_reference_gpu_test_cases(cuda, oracle):
+    """gptq_dequantize_numeric and fused_dequant_gemv_numeric on the reference tests' own operands
+    (gpu_tests/quantize.rs:783-903; bounds there 1e-5 and 1e-4 relative): equal to the oracle bit for bit."""
+    rows, cols, group, nib, scales, _ = reference_gpu_test_inputs(0xABCD_1234, 0.4, False)
+    packed = pack_flat(nib, 4)
+    out = _plan(rows, cols, group).gptq_dequantize(_t(packed.view(np.int32), cuda), _t(scales, cuda))
+    assert np.array_equal(out.cpu().numpy().reshape(-1), oracle.wq_dequantize(packed, scales, None, rows, cols, group, 4))
+    rows, cols, group, nib, scales, x = reference_gpu_test_inputs(0x55AA_9933, 0.3, True)
+    packed = pack_flat(nib, 4)
+    y = _plan(rows, cols, group).fused_dequant_gemv(_t(packed.view(np.int32), cuda), _t(scales, cuda), _t(x, cuda))
+    assert np.array_equal(y.cpu().numpy(), oracle.fused_dequant_gemv(packed, scales, None, x, rows, cols, group, 4))
 
 
 @pytest.mark.gpu
